@@ -1,0 +1,272 @@
+/*
+ * vkgrad_b200 -- C ABI of the B200 (sm_100a) training-step library.
+ *
+ * This is the whole boundary between the Python object model (kernels.Matmul,
+ * autograd.Linear/AdamW/TrainStep, transformer.GPT, dataparallel.Replica) and
+ * the CUDA code.  Plain pointers and sizes only; every entry returns an int
+ * status (0 = OK, non-zero = failed, message in vkg_last_error()) and never
+ * throws or aborts, mirroring the reference runtime's `_check` (vk.py:132-134),
+ * which turns every non-zero VkResult into VkError.
+ *
+ * Each declaration cites the reference interface it replaces (file:line in
+ * BrettKnox/vkgrad).  All compute entries enqueue on the device's stream and
+ * return without synchronising unless stated otherwise, so the same calls can
+ * be issued between vkg_graph_begin/vkg_graph_end to record a replayable step
+ * (reference: vk.Graph.record, vk.py:842-868).
+ *
+ * dtypes: VKG_F32 = 0, VKG_F16 = 1, VKG_BF16 = 2.
+ */
+#ifndef VKGRAD_B200_H
+#define VKGRAD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VKG_F32 0
+#define VKG_F16 1
+#define VKG_BF16 2
+
+#define VKG_ACT_NONE 0
+#define VKG_ACT_GELU 1 /* tanh form, kernels.py:624-629 */
+#define VKG_ACT_RELU 2 /* extension: the reference has GELU only */
+
+typedef struct vkg_device vkg_device;
+typedef struct vkg_graph vkg_graph;
+typedef struct vkg_comm vkg_comm;
+
+/* ---- runtime: replaces vk.Device / vk.Buffer / vk.Graph ------------------ */
+
+/* Thread-local message of the last failed call (vk.VkError text, vk.py:128). */
+const char* vkg_last_error(void);
+/* Library version string. */
+const char* vkg_version(void);
+/* Number of CUDA devices visible; 0 (not an error) when there is no GPU. */
+int vkg_device_count(int* count);
+
+/* vk.Device() (vk.py:892): binds CUDA device `ordinal`, creates its stream. */
+int vkg_device_create(int ordinal, vkg_device** out);
+/* vk.Device.destroy (vk.py:1342). */
+int vkg_device_destroy(vkg_device* dev);
+/* Device.name and the numbers callers print (vk.py:1074-1100). */
+int vkg_device_info(vkg_device* dev, char* name, size_t name_cap, int* sm_count,
+                    size_t* total_bytes, int* cc_major, int* cc_minor);
+/* Opaque cudaStream_t of the device, for callers that interoperate. */
+void* vkg_device_stream(vkg_device* dev);
+/* Waits for the stream; reports a kernel error flag (bounded waits that gave
+ * up) as a failure, like the reference's 10 s fence timeout (vk.py:1335-1339). */
+int vkg_sync(vkg_device* dev);
+
+/* dev.buffer(size, kind) (vk.py:1256, memory kinds vk.py:1161-1200).
+ * kind 0 "device": HBM only.  kind 1 "shared": pinned, mapped host memory the
+ * GPU reads in place (host writes are visible without flush, mnist.py:170).
+ * kind 2 "cached": HBM plus a pinned host mirror; vkg_upload/vkg_download are
+ * Buffer.flush / Buffer.invalidate (vk.py:598-610).
+ * dptr is what kernels take; hptr is the numpy-visible address or NULL. */
+int vkg_alloc(vkg_device* dev, size_t bytes, int kind, void** dptr, void** hptr);
+int vkg_free(vkg_device* dev, void* dptr, void* hptr, int kind);
+/* Buffer.flush: host mirror -> device (synchronous). */
+int vkg_upload(vkg_device* dev, void* dptr, const void* hptr, size_t bytes);
+/* Buffer.invalidate: device -> host mirror (synchronous). */
+int vkg_download(vkg_device* dev, void* hptr, const void* dptr, size_t bytes);
+/* dev.copy(src,dst,size) (vk.py:1267): enqueued device-side copy. */
+int vkg_copy(vkg_device* dev, void* dst, const void* src, size_t bytes);
+/* Enqueued copies between pinned host memory and the device, for the
+ * end-to-end path (inputs up, loss down) inside a recorded step. */
+int vkg_copy_h2d_async(vkg_device* dev, void* dptr, const void* hptr, size_t bytes);
+int vkg_copy_d2h_async(vkg_device* dev, void* hptr, const void* dptr, size_t bytes);
+/* K["zero"] / arena_zero (kernels.py:853, dataparallel.py:60). */
+int vkg_memset0(vkg_device* dev, void* dptr, size_t bytes);
+
+/* Event timing around enqueued work: Device.run returns seconds (vk.py:1295). */
+int vkg_timer_begin(vkg_device* dev);
+int vkg_timer_end(vkg_device* dev, double* seconds); /* synchronises */
+
+/* vk.Graph (vk.py:807-889): capture everything enqueued between begin/end. */
+int vkg_graph_begin(vkg_device* dev);
+int vkg_graph_end(vkg_device* dev, vkg_graph** out);
+/* Graph.submit(): launch, wait, return GPU seconds (vk.py:877-889). */
+int vkg_graph_launch(vkg_device* dev, vkg_graph* g, double* seconds);
+/* Launch without waiting (pipelined steps). */
+int vkg_graph_launch_async(vkg_device* dev, vkg_graph* g);
+int vkg_graph_destroy(vkg_graph* g);
+/* Number of kernel nodes in a finished graph (Graph.n_dispatch, vk.py:868). */
+int vkg_graph_kernel_count(vkg_graph* g, int* count);
+
+/* ---- the GEMM trio: replaces kernels.Matmul (kernels.py:32-138, 232-315) -- */
+
+/*
+ * C[M x N] = op(A) * op(B), 16-bit inputs, fp32 accumulation on tcgen05.
+ *   trans_a = 0: A stored M x K (lda >= K).  trans_a = 1: A stored K x M
+ *                (the dW = X^T dY form, kernels.py:112-118).
+ *   trans_b = 0: B stored K x N (ldb >= N).  trans_b = 1: B stored N x K
+ *                (the dX = dY W^T form, kernels.py:120-126).
+ * Batched form (kernels.py:58-64, 98-102): batch index z = z0 + nb0 * z1 with
+ * z0 < nb0, z1 < nb1; operand X is offset by z0*sX0 + z1*sX1 elements.  Two
+ * strides let attention heads be addressed inside a (rows, 3D) projection
+ * without the split_qkv / merge_heads permutes (tkernels.py:195-300).
+ * Epilogue, in order (each optional):  v = acc; v += bias[col];
+ * pre[row,col] = v (fp32);  v = act(v);  v *= act'(dact_z[row,col]);
+ * v += residual[row,col];  C = v (c_dtype);  C2 = f16(v).
+ * These fuse bias_gelu / bias / bias_gelu_bwd16 / residual / to16
+ * (kernels.py:709-749, tkernels.py:364-387) into the producing GEMM.
+ * Overwrites C like the reference (callers rely on it, transformer.py:367).
+ * Leading dimensions are in elements; A/B pointers and lda/ldb*2 bytes must be
+ * 16-byte aligned, N % 8 == 0.  No tile-multiple restriction (the reference
+ * raises VkError for ragged shapes, kernels.py:274-276; here edges are
+ * predicated).
+ */
+typedef struct vkg_gemm_args {
+  int32_t trans_a, trans_b;
+  int32_t M, N, K;
+  int32_t nb0, nb1;          /* batch extents; 1,1 when not batched */
+  int32_t in_dtype;          /* VKG_F16 or VKG_BF16 */
+  const void* A; int64_t lda, sA0, sA1;
+  const void* B; int64_t ldb, sB0, sB1;
+  void* C; int64_t ldc, sC0, sC1; int32_t c_dtype; /* VKG_F32 / VKG_F16 / VKG_BF16 */
+  int32_t act;               /* VKG_ACT_* applied to v */
+  void* C2;                  /* optional f16 copy of the result, same ldc/strides */
+  const float* bias;         /* optional, length N */
+  float* pre;                /* optional fp32 pre-activation, same ldc/strides */
+  const float* dact_z;       /* optional: multiply by act'(z), z fp32 same layout */
+  int32_t dact;              /* VKG_ACT_* whose derivative multiplies */
+  const float* residual;     /* optional fp32, same ldc/strides */
+  int32_t tile_n;            /* 0 = choose; else 64/128/192/256 */
+  int32_t max_ctas;          /* 0 = one per SM */
+  float alpha;               /* 0 treated as 1: scales acc before bias */
+} vkg_gemm_args;
+
+int vkg_gemm(vkg_device* dev, const vkg_gemm_args* args);
+
+/* ---- MLP-step fused ops: replaces kernels.make_kernels (kernels.py:699-862) */
+
+/* bias_gelu (kernels.py:709-718): z = acc + bias[i % ncol]; y16 = f16(act(z)). */
+int vkg_bias_act(vkg_device* dev, const float* acc, const float* bias, float* z,
+                 void* y16, int64_t n, int ncol, int act);
+/* bias_gelu_bwd / bwd16 (kernels.py:721-739): g = dy * act'(z); dz32 optional. */
+int vkg_bias_act_bwd(vkg_device* dev, const float* dy, const float* z, void* dz16,
+                     float* dz32, int64_t n, int act);
+/* bias (kernels.py:742-749): z = acc + bias[i % ncol]. */
+int vkg_bias(vkg_device* dev, const float* acc, const float* bias, float* z,
+             int64_t n, int ncol);
+/* col_sum (kernels.py:753-761): sums[c] = sum_r g[r*ncol + c], fp32 input. */
+int vkg_col_sum(vkg_device* dev, const float* g, float* sums, int ncol, int nrow);
+/* softmax_ce / softmax_ce_w (kernels.py:766-827).  Per row: loss, and
+ * dl = (softmax - onehot) * (w ? w[row] : grad_scale); classes >= ncls are
+ * masked to exactly 0.  grad_scale is 1/rows for the reference's mean, times a
+ * static loss scale when one is used.  dl16 is written in f16; dl32 optional. */
+int vkg_softmax_ce(vkg_device* dev, const float* logits, const uint32_t* labels,
+                   const float* w, void* dl16, float* dl32, float* loss,
+                   int rows, int stride, int ncls, float grad_scale);
+/* adamw (kernels.py:832-851): hp = {lr,b1,b2,bc1,bc2,eps,(gscale)} read from
+ * memory at run time so a recorded step replays with new values
+ * (autograd.py:313-323).  hp[6], when non-zero, multiplies the gradient first:
+ * the 1/(workers * loss_scale) of grad_pull (dataparallel.py:69-73) fused in. */
+int vkg_adamw(vkg_device* dev, float* w, const float* g, float* m, float* v,
+              void* w16, const float* hp, int64_t n, float wd);
+/* All parameter tensors in one launch (the reference issues one dispatch per
+ * tensor, autograd.py:331-335).  Arrays of length ntensors live on the host;
+ * the table is copied to device memory owned by `table` (opaque, reusable). */
+int vkg_adamw_table_create(vkg_device* dev, int ntensors, float* const* w,
+                           const float* const* g, float* const* m, float* const* v,
+                           void* const* w16, const int64_t* n, const float* wd,
+                           void** table);
+int vkg_adamw_table_destroy(vkg_device* dev, void* table);
+int vkg_adamw_multi(vkg_device* dev, void* table, const float* hp);
+/* cast16 / to16 (kernels.py:857-860, tkernels.py:384-387). */
+int vkg_cast16(vkg_device* dev, const float* src, void* dst16, int64_t n);
+
+/* ---- transformer ops: replaces tkernels.make_transformer_kernels --------- */
+
+/* layernorm (tkernels.py:32-54): eps 1e-5, biased variance; saves mu, rstd. */
+int vkg_layernorm(vkg_device* dev, const float* x, const float* gamma,
+                  const float* beta, void* y16, float* mu, float* rstd,
+                  int rows, int D);
+/* layernorm_bwd (tkernels.py:58-88).  dx = LN'(dy) [+ dres when given];
+ * dx16 optional f16 copy; dyxh16/dy16 optional (the reference's inputs to its
+ * column sums).  When dgamma/dbeta are given they receive the column sums of
+ * dy*xhat and dy directly (deterministic two-stage reduction through
+ * `scratch`, which must hold vkg_layernorm_bwd_scratch_floats(rows, D)). */
+int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* x,
+                      const float* gamma, const float* mu, const float* rstd,
+                      const float* dres, float* dx, void* dx16, void* dyxh16,
+                      void* dy16, float* dgamma, float* dbeta, float* scratch,
+                      int rows, int D);
+int64_t vkg_layernorm_bwd_scratch_floats(int rows, int D);
+/* attn_softmax / attn_softmax_doc (tkernels.py:105-161): causal, scaled;
+ * seg (optional) restricts a query to keys >= seg[b*T+q]; rows = nbh*T. */
+int vkg_attn_softmax(vkg_device* dev, const float* s, const uint32_t* seg,
+                     void* p16, int64_t rows, int T, int H, float scale);
+/* attn_softmax_bwd (tkernels.py:167-188): ds = P*(dP - sum dP*P)*scale. */
+int vkg_attn_softmax_bwd(vkg_device* dev, const float* dp, const void* p16,
+                         void* ds16, int64_t rows, int T, float scale);
+/* split_qkv / merge_qkv_grad / merge_heads / split_heads (tkernels.py:195-300). */
+int vkg_split_qkv(vkg_device* dev, const float* qkv, const float* bias, void* q16,
+                  void* k16, void* v16, int64_t n, int D, int T, int H, int hd);
+int vkg_merge_qkv_grad(vkg_device* dev, const float* dq, const float* dk,
+                       const float* dv, void* dqkv16, int64_t n, int D, int T,
+                       int H, int hd);
+int vkg_merge_heads(vkg_device* dev, const float* src, void* y16, int64_t n, int D,
+                    int T, int H, int hd);
+int vkg_split_heads(vkg_device* dev, const float* src, void* dst16, int64_t n,
+                    int D, int T, int H, int hd);
+/* col_sum_zero + col_sum_chunk(16) (tkernels.py:238-270, transformer.py:30-36):
+ * sums[c] (+)= sum_r g[r*ncol+c].  Deterministic: fixed-order partial sums in
+ * `scratch` (vkg_col_sum_scratch_floats(ncol, nrow) floats), no atomics.
+ * g_dtype VKG_F32 or VKG_F16; accumulate != 0 adds into sums instead of
+ * overwriting (the reference's chunk kernel adds into a zeroed buffer). */
+int vkg_col_sum_det(vkg_device* dev, const void* g, int g_dtype, float* sums,
+                    float* scratch, int ncol, int nrow, int accumulate);
+int64_t vkg_col_sum_scratch_floats(int ncol, int nrow);
+/* embed / embed_doc (tkernels.py:303-313, 334-345). */
+int vkg_embed(vkg_device* dev, const float* tok, const float* pos,
+              const uint32_t* ids, const uint32_t* seg, float* x, int64_t n, int D,
+              int T);
+/* embed_bwd / embed_doc_bwd (tkernels.py:317-360): scatter-add into dtok, dpos. */
+int vkg_embed_bwd(vkg_device* dev, const float* dx, const uint32_t* ids,
+                  const uint32_t* seg, float* dtok, float* dpos, int64_t n, int D,
+                  int T);
+/* residual (tkernels.py:364-371): out = res + acc + bias[i % D]. */
+int vkg_residual(vkg_device* dev, const float* acc, const float* bias,
+                 const float* res, float* out, int64_t n, int D);
+/* add (tkernels.py:373-377); out16 optional f16 copy. */
+int vkg_add(vkg_device* dev, const float* a, const float* b, float* out,
+            void* out16, int64_t n);
+/* add_bias (tkernels.py:380-382): x[i] += bias[i % ncol]. */
+int vkg_add_bias(vkg_device* dev, float* x, const float* bias, int64_t n, int ncol);
+
+/* ---- data parallel: replaces dataparallel.make_reduce_kernels ------------ */
+
+/* grad_add (dataparallel.py:54-58): arena[off+i] += g[i]. */
+int vkg_grad_add(vkg_device* dev, const float* g, float* arena, int64_t n,
+                 int64_t off);
+/* grad_pull (dataparallel.py:69-73): g[i] = arena[off+i] * scale. */
+int vkg_grad_pull(vkg_device* dev, const float* arena, float* g, int64_t n,
+                  int64_t off, float scale);
+/* Bucket pack/unpack with the loss-unscale cast fused: dst16 = f16/bf16(src*scale)
+ * and dst32 = float(src16)*scale. */
+int vkg_bucket_pack16(vkg_device* dev, const float* src, void* dst16, int dtype,
+                      int64_t n, float scale);
+int vkg_bucket_unpack16(vkg_device* dev, const void* src16, int dtype, float* dst,
+                        int64_t n, float scale);
+
+/* NCCL replaces the shared host arena + atomicAdd push (dataparallel.py:40-47,
+ * 119-126).  The unique id is 128 bytes, made on rank 0 and passed to the other
+ * ranks by the caller (file, socket or a torch.distributed store). */
+int vkg_comm_unique_id(uint8_t id[128]);
+int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint8_t id[128],
+                    vkg_comm** out);
+int vkg_comm_destroy(vkg_comm* comm);
+/* In-place sum over ranks of `count` elements of dtype, on the device stream. */
+int vkg_allreduce_sum(vkg_comm* comm, void* buf, int64_t count, int dtype);
+/* max over ranks of one host double (timing), and a barrier. */
+int vkg_comm_max_double(vkg_comm* comm, double* value);
+int vkg_comm_barrier(vkg_comm* comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VKGRAD_B200_H */

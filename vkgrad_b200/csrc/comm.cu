@@ -1,0 +1,150 @@
+// Data-parallel gradient exchange: NCCL all-reduce over NVLink / NVSwitch in
+// place of the reference's shared host arena + float atomicAdd
+// (dataparallel.py:40-47, 119-126).  NCCL is opened with dlopen at first use so
+// the library loads (and single-GPU work runs) on a machine without it.
+#include <dlfcn.h>
+
+#include "common.cuh"
+
+namespace {
+
+typedef struct ncclComm* ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+enum { NCCL_SUM = 0, NCCL_MAX = 2 };
+enum { NCCL_FLOAT16 = 6, NCCL_FLOAT32 = 7, NCCL_FLOAT64 = 8, NCCL_BFLOAT16 = 9 };
+
+struct NcclApi {
+  void* handle = nullptr;
+  int (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  int (*CommDestroy)(ncclComm_t) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  const char* (*GetLastError)(ncclComm_t) = nullptr;
+};
+
+NcclApi g_nccl;
+std::mutex g_nccl_mu;
+
+int load_nccl() {
+  std::lock_guard<std::mutex> lock(g_nccl_mu);
+  if (g_nccl.handle) return 0;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  void* h = nullptr;
+  for (const char* n : names) {
+    // RTLD_NOLOAD first: reuse a copy the process already holds.
+    h = dlopen(n, RTLD_NOW | RTLD_NOLOAD);
+    if (!h) h = dlopen(n, RTLD_NOW | RTLD_LOCAL);
+    if (h) break;
+  }
+  if (!h) {
+    vkg_set_error("NCCL not found (libnccl.so.2): %s", dlerror());
+    return 1;
+  }
+  NcclApi api;
+  api.handle = h;
+  api.GetUniqueId = (int (*)(ncclUniqueId*))dlsym(h, "ncclGetUniqueId");
+  api.CommInitRank = (int (*)(ncclComm_t*, int, ncclUniqueId, int))dlsym(h, "ncclCommInitRank");
+  api.CommDestroy = (int (*)(ncclComm_t))dlsym(h, "ncclCommDestroy");
+  api.AllReduce = (int (*)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t))dlsym(
+      h, "ncclAllReduce");
+  api.GetErrorString = (const char* (*)(int))dlsym(h, "ncclGetErrorString");
+  api.GetLastError = (const char* (*)(ncclComm_t))dlsym(h, "ncclGetLastError");
+  if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllReduce ||
+      !api.GetErrorString) {
+    vkg_set_error("libnccl is missing a required symbol");
+    return 1;
+  }
+  g_nccl = api;
+  return 0;
+}
+
+}  // namespace
+
+struct vkg_comm {
+  vkg_device* dev = nullptr;
+  ncclComm_t comm = nullptr;
+  int rank = 0, nranks = 1;
+  double* scratch_dev = nullptr;
+};
+
+#define VKG_NCCL(expr)                                                              \
+  do {                                                                              \
+    int _r = (expr);                                                                \
+    if (_r != 0) {                                                                  \
+      vkg_set_error("%s failed: %s", #expr, g_nccl.GetErrorString(_r));             \
+      return 1;                                                                     \
+    }                                                                               \
+  } while (0)
+
+extern "C" int vkg_comm_unique_id(uint8_t id[128]) {
+  if (!id) VKG_FAIL("null id");
+  if (load_nccl()) return 1;
+  ncclUniqueId uid;
+  VKG_NCCL(g_nccl.GetUniqueId(&uid));
+  memcpy(id, uid.internal, 128);
+  return 0;
+}
+
+extern "C" int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint8_t id[128],
+                               vkg_comm** out) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(out && id, "comm_create: null argument");
+  VKG_REQUIRE(nranks >= 1 && rank >= 0 && rank < nranks, "comm_create: rank %d of %d", rank, nranks);
+  if (load_nccl()) return 1;
+  ncclUniqueId uid;
+  memcpy(uid.internal, id, 128);
+  vkg_comm* c = new vkg_comm();
+  c->dev = dev;
+  c->rank = rank;
+  c->nranks = nranks;
+  int r = g_nccl.CommInitRank(&c->comm, nranks, uid, rank);
+  if (r != 0) {
+    delete c;
+    VKG_FAIL("ncclCommInitRank failed: %s", g_nccl.GetErrorString(r));
+  }
+  cudaError_t e = cudaMalloc(&c->scratch_dev, 64);
+  if (e != cudaSuccess) {
+    g_nccl.CommDestroy(c->comm);
+    delete c;
+    VKG_FAIL("comm_create: %s", cudaGetErrorString(e));
+  }
+  *out = c;
+  return 0;
+}
+
+extern "C" int vkg_comm_destroy(vkg_comm* comm) {
+  if (!comm) return 0;
+  if (comm->dev) cudaSetDevice(comm->dev->ordinal);
+  if (comm->dev) cudaStreamSynchronize(comm->dev->stream);
+  if (comm->scratch_dev) cudaFree(comm->scratch_dev);
+  if (comm->comm) g_nccl.CommDestroy(comm->comm);
+  delete comm;
+  return 0;
+}
+
+extern "C" int vkg_allreduce_sum(vkg_comm* comm, void* buf, int64_t count, int dtype) {
+  VKG_REQUIRE(comm && buf && count > 0, "allreduce: bad arguments");
+  if (vkg_bind(comm->dev)) return 1;
+  int t = dtype == VKG_F32 ? NCCL_FLOAT32 : dtype == VKG_F16 ? NCCL_FLOAT16 : dtype == VKG_BF16 ? NCCL_BFLOAT16 : -1;
+  VKG_REQUIRE(t >= 0, "allreduce: unknown dtype %d", dtype);
+  VKG_NCCL(g_nccl.AllReduce(buf, buf, (size_t)count, t, NCCL_SUM, comm->comm, comm->dev->stream));
+  return 0;
+}
+
+extern "C" int vkg_comm_max_double(vkg_comm* comm, double* value) {
+  VKG_REQUIRE(comm && value, "comm_max_double: bad arguments");
+  if (vkg_bind(comm->dev)) return 1;
+  cudaStream_t s = comm->dev->stream;
+  VKG_CUDA(cudaMemcpyAsync(comm->scratch_dev, value, sizeof(double), cudaMemcpyHostToDevice, s));
+  VKG_NCCL(g_nccl.AllReduce(comm->scratch_dev, comm->scratch_dev, 1, NCCL_FLOAT64, NCCL_MAX,
+                            comm->comm, s));
+  VKG_CUDA(cudaMemcpyAsync(value, comm->scratch_dev, sizeof(double), cudaMemcpyDeviceToHost, s));
+  VKG_CUDA(cudaStreamSynchronize(s));
+  return 0;
+}
+
+extern "C" int vkg_comm_barrier(vkg_comm* comm) {
+  double v = 0.0;
+  return vkg_comm_max_double(comm, &v);
+}

@@ -1,0 +1,141 @@
+// Shared host-side plumbing for the vkgrad_b200 C ABI: the device object, the
+// thread-local error string, and launch checking.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include "../../include/vkgrad_b200.h"
+
+// Error codes written by kernels into vkg_device::err_flag (host-mapped).
+#define VKG_ERR_WAIT_TIMEOUT 1u   // a bounded mbarrier wait gave up
+
+struct vkg_device {
+  int ordinal = 0;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  size_t total_bytes = 0;
+  char name[128] = {0};
+  // Host-mapped words kernels can write: [0] error code, [1] detail.
+  volatile uint32_t* err_host = nullptr;
+  uint32_t* err_dev = nullptr;
+  bool capturing = false;
+  // cuTensorMapEncodeTiled, resolved at run time so the library loads on a
+  // machine without a driver.
+  void* encode_tiled = nullptr;
+  size_t gemm_smem_optin = 0;
+  bool gemm_attr_set = false;
+};
+
+struct vkg_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  int kernel_nodes = 0;
+};
+
+void vkg_set_error(const char* fmt, ...);
+
+#define VKG_FAIL(...)            \
+  do {                           \
+    vkg_set_error(__VA_ARGS__);  \
+    return 1;                    \
+  } while (0)
+
+#define VKG_CUDA(expr)                                                          \
+  do {                                                                          \
+    cudaError_t _e = (expr);                                                    \
+    if (_e != cudaSuccess) {                                                    \
+      vkg_set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),     \
+                    __FILE__, __LINE__);                                        \
+      return 1;                                                                 \
+    }                                                                           \
+  } while (0)
+
+#define VKG_REQUIRE(cond, ...)   \
+  do {                           \
+    if (!(cond)) {               \
+      vkg_set_error(__VA_ARGS__);\
+      return 1;                  \
+    }                            \
+  } while (0)
+
+// Makes `dev` current on this thread and checks the launch that just happened.
+static inline int vkg_bind(vkg_device* dev) {
+  if (!dev) {
+    vkg_set_error("null device");
+    return 1;
+  }
+  cudaError_t e = cudaSetDevice(dev->ordinal);
+  if (e != cudaSuccess) {
+    vkg_set_error("cudaSetDevice(%d): %s", dev->ordinal, cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+
+static inline int vkg_check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    vkg_set_error("launch of %s failed: %s", what, cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+
+static inline unsigned vkg_blocks(int64_t n, int per_block, int64_t cap = (1ll << 31) - 1) {
+  int64_t b = (n + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  if (b > cap) b = cap;
+  return (unsigned)b;
+}
+
+// ---- device helpers shared by the elementwise kernels ----------------------
+
+__device__ __forceinline__ float vkg_gelu(float x) {
+  const float c = 0.7978845608028654f;  // sqrt(2/pi)
+  float x3 = x * x * x;
+  return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x3)));
+}
+
+__device__ __forceinline__ float vkg_dgelu(float x) {
+  const float c = 0.7978845608028654f;
+  float x3 = x * x * x;
+  float t = tanhf(c * (x + 0.044715f * x3));
+  float sech2 = 1.0f - t * t;
+  return 0.5f * (1.0f + t) + 0.5f * x * sech2 * c * (1.0f + 3.0f * 0.044715f * x * x);
+}
+
+__device__ __forceinline__ float vkg_act(float v, int act) {
+  if (act == VKG_ACT_GELU) return vkg_gelu(v);
+  if (act == VKG_ACT_RELU) return v > 0.0f ? v : 0.0f;
+  return v;
+}
+
+__device__ __forceinline__ float vkg_dact(float z, int act) {
+  if (act == VKG_ACT_GELU) return vkg_dgelu(z);
+  if (act == VKG_ACT_RELU) return z > 0.0f ? 1.0f : 0.0f;
+  return 1.0f;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}

@@ -1,0 +1,929 @@
+// Streaming and row kernels of the training step: everything the reference
+// generates as GLSL in kernels.make_kernels (kernels.py:699-862) and
+// tkernels.make_transformer_kernels (tkernels.py:17-389).  All are HBM-bound;
+// accesses are coalesced and vectorised where alignment allows, reductions are
+// warp/CTA shuffles, and the column sums are deterministic (fixed-order partial
+// sums in caller-provided scratch) instead of float atomics.
+#include "common.cuh"
+
+namespace {
+
+constexpr int TPB = 256;
+
+__device__ __forceinline__ void store16(void* p, int64_t i, float v) {
+  reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+
+// ---- flat elementwise -------------------------------------------------------
+
+__global__ void k_bias_act(const float* __restrict__ acc, const float* __restrict__ bias,
+                           float* __restrict__ z, __half* __restrict__ y16, int64_t n, int ncol,
+                           int act) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float v = acc[i] + bias[i % ncol];
+    if (z) z[i] = v;
+    if (y16) y16[i] = __float2half_rn(vkg_act(v, act));
+  }
+}
+
+__global__ void k_bias_act_bwd(const float* __restrict__ dy, const float* __restrict__ z,
+                               __half* __restrict__ dz16, float* __restrict__ dz32, int64_t n,
+                               int act) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float g = dy[i] * vkg_dact(z[i], act);
+    if (dz16) dz16[i] = __float2half_rn(g);
+    if (dz32) dz32[i] = g;
+  }
+}
+
+__global__ void k_cast16(const float* __restrict__ src, __half* __restrict__ dst, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[i] = __float2half_rn(src[i]);
+}
+
+__global__ void k_cast16_v4(const float4* __restrict__ src, uint2* __restrict__ dst, int64_t n4) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n4; i += stride) {
+    float4 v = src[i];
+    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&a);
+    o.y = *reinterpret_cast<uint32_t*>(&b);
+    dst[i] = o;
+  }
+}
+
+__global__ void k_residual(const float* __restrict__ acc, const float* __restrict__ bias,
+                           const float* __restrict__ res, float* __restrict__ out, int64_t n, int D) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) out[i] = res[i] + acc[i] + bias[i % D];
+}
+
+__global__ void k_add(const float* __restrict__ a, const float* __restrict__ b,
+                      float* __restrict__ out, __half* __restrict__ out16, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float v = a[i] + b[i];
+    if (out) out[i] = v;
+    if (out16) out16[i] = __float2half_rn(v);
+  }
+}
+
+__global__ void k_add_bias(float* __restrict__ x, const float* __restrict__ bias, int64_t n,
+                           int ncol) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) x[i] += bias[i % ncol];
+}
+
+__global__ void k_grad_add(const float* __restrict__ g, float* __restrict__ arena, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) arena[i] += g[i];
+}
+
+__global__ void k_grad_pull(const float* __restrict__ arena, float* __restrict__ g, int64_t n,
+                            float scale) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) g[i] = arena[i] * scale;
+}
+
+template <typename T16>
+__global__ void k_pack16(const float* __restrict__ src, T16* __restrict__ dst, int64_t n,
+                         float scale) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[i] = T16(src[i] * scale);
+}
+
+template <typename T16>
+__global__ void k_unpack16(const T16* __restrict__ src, float* __restrict__ dst, int64_t n,
+                           float scale) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[i] = float(src[i]) * scale;
+}
+
+// ---- head permutes ------------------------------------------------------------
+
+__global__ void k_split_qkv(const float* __restrict__ qkv, const float* __restrict__ bias,
+                            __half* __restrict__ q16, __half* __restrict__ k16,
+                            __half* __restrict__ v16, int64_t n, int D, int T, int H, int hd) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    int d = (int)(i % D);
+    int64_t bt = i / D;
+    int t = (int)(bt % T);
+    int64_t b = bt / T;
+    int h = d / hd, j = d % hd;
+    int64_t dst = ((b * H + h) * T + t) * hd + j;
+    int64_t src = bt * 3 * D + d;
+    q16[dst] = __float2half_rn(qkv[src] + bias[d]);
+    k16[dst] = __float2half_rn(qkv[src + D] + bias[d + D]);
+    v16[dst] = __float2half_rn(qkv[src + 2 * D] + bias[d + 2 * D]);
+  }
+}
+
+__global__ void k_merge_qkv_grad(const float* __restrict__ dq, const float* __restrict__ dk,
+                                 const float* __restrict__ dv, __half* __restrict__ dqkv16,
+                                 int64_t n, int D, int T, int H, int hd) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    int d = (int)(i % D);
+    int64_t bt = i / D;
+    int t = (int)(bt % T);
+    int64_t b = bt / T;
+    int h = d / hd, j = d % hd;
+    int64_t src = ((b * H + h) * T + t) * hd + j;
+    int64_t dst = bt * 3 * D + d;
+    dqkv16[dst] = __float2half_rn(dq[src]);
+    dqkv16[dst + D] = __float2half_rn(dk[src]);
+    dqkv16[dst + 2 * D] = __float2half_rn(dv[src]);
+  }
+}
+
+__global__ void k_merge_heads(const float* __restrict__ src, __half* __restrict__ y16, int64_t n,
+                              int D, int T, int H, int hd) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    int d = (int)(i % D);
+    int64_t bt = i / D;
+    int t = (int)(bt % T);
+    int64_t b = bt / T;
+    int h = d / hd, j = d % hd;
+    y16[i] = __float2half_rn(src[((b * H + h) * T + t) * hd + j]);
+  }
+}
+
+__global__ void k_split_heads(const float* __restrict__ src, __half* __restrict__ dst16, int64_t n,
+                              int D, int T, int H, int hd) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    int d = (int)(i % D);
+    int64_t bt = i / D;
+    int t = (int)(bt % T);
+    int64_t b = bt / T;
+    int h = d / hd, j = d % hd;
+    dst16[((b * H + h) * T + t) * hd + j] = __float2half_rn(src[i]);
+  }
+}
+
+// ---- embeddings -----------------------------------------------------------------
+
+__global__ void k_embed(const float* __restrict__ tok, const float* __restrict__ pos,
+                        const uint32_t* __restrict__ ids, const uint32_t* __restrict__ seg,
+                        float* __restrict__ x, int64_t n, int D, int T) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    int d = (int)(i % D);
+    int64_t bt = i / D;
+    int t = (int)(bt % T);
+    if (seg) t -= (int)seg[bt];
+    x[i] = tok[(int64_t)ids[bt] * D + d] + pos[(int64_t)t * D + d];
+  }
+}
+
+__global__ void k_embed_bwd(const float* __restrict__ dx, const uint32_t* __restrict__ ids,
+                            const uint32_t* __restrict__ seg, float* __restrict__ dtok,
+                            float* __restrict__ dpos, int64_t n, int D, int T) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    int d = (int)(i % D);
+    int64_t bt = i / D;
+    int t = (int)(bt % T);
+    if (seg) t -= (int)seg[bt];
+    float g = dx[i];
+    atomicAdd(dtok + (int64_t)ids[bt] * D + d, g);
+    atomicAdd(dpos + (int64_t)t * D + d, g);
+  }
+}
+
+// ---- column sums ------------------------------------------------------------------
+
+// The reference's col_sum: one thread per column over fp32 rows (kernels.py:753).
+__global__ void k_col_sum(const float* __restrict__ g, float* __restrict__ sums, int ncol,
+                          int nrow) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ncol) return;
+  float s = 0.f;
+  for (int r = 0; r < nrow; ++r) s += g[(int64_t)r * ncol + c];
+  sums[c] = s;
+}
+
+constexpr int CS_COLS = 64;    // columns per block (2 per lane)
+constexpr int CS_WARPS = 8;
+
+// Stage 1: block (cx, chunk) sums rows [chunk*rpc, ...) of its 64 columns into
+// partial[chunk][col].  Warps stride the rows; lanes own column pairs.
+template <typename T>
+__global__ void k_col_sum_partial(const T* __restrict__ g, float* __restrict__ partial, int ncol,
+                                  int nrow, int rows_per_chunk) {
+  __shared__ float red[CS_WARPS][CS_COLS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * CS_COLS + lane * 2;
+  const int r0 = blockIdx.y * rows_per_chunk;
+  const int r1 = min(nrow, r0 + rows_per_chunk);
+  float s0 = 0.f, s1 = 0.f;
+  if (c + 1 < ncol) {
+    for (int r = r0 + warp; r < r1; r += CS_WARPS) {
+      const T* p = g + (int64_t)r * ncol + c;
+      s0 += float(p[0]);
+      s1 += float(p[1]);
+    }
+  } else if (c < ncol) {
+    for (int r = r0 + warp; r < r1; r += CS_WARPS) s0 += float(g[(int64_t)r * ncol + c]);
+  }
+  red[warp][lane * 2] = s0;
+  red[warp][lane * 2 + 1] = s1;
+  __syncthreads();
+  if (threadIdx.x < CS_COLS) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < CS_WARPS; ++w) s += red[w][threadIdx.x];
+    int col = blockIdx.x * CS_COLS + threadIdx.x;
+    if (col < ncol) partial[(int64_t)blockIdx.y * ncol + col] = s;
+  }
+}
+
+// Stage 2: fixed-order sum of the partials.
+__global__ void k_col_sum_final(const float* __restrict__ partial, float* __restrict__ sums,
+                                int ncol, int nchunk, int accumulate) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ncol) return;
+  float s = 0.f;
+  for (int k = 0; k < nchunk; ++k) s += partial[(int64_t)k * ncol + c];
+  sums[c] = accumulate ? sums[c] + s : s;
+}
+
+// ---- softmax + cross entropy ---------------------------------------------------------
+
+// One CTA per row.  Online max/sum in one pass, then one pass writing the
+// gradient; the second read of the row comes out of L2.
+__global__ void __launch_bounds__(TPB)
+k_softmax_ce(const float* __restrict__ logits, const uint32_t* __restrict__ labels,
+             const float* __restrict__ w, __half* __restrict__ dl16, float* __restrict__ dl32,
+             float* __restrict__ loss, int stride, int ncls, float grad_scale) {
+  __shared__ float s_m[TPB / 32], s_s[TPB / 32];
+  __shared__ float s_logz;
+  const int row = blockIdx.x;
+  const float* x = logits + (int64_t)row * stride;
+  __half* d16 = dl16 ? dl16 + (int64_t)row * stride : nullptr;
+  float* d32 = dl32 ? dl32 + (int64_t)row * stride : nullptr;
+  float wi = grad_scale;
+  if (w) {
+    wi = w[row];
+    if (wi == 0.0f) {
+      for (int c = threadIdx.x; c < stride; c += TPB) {
+        if (d16) d16[c] = __float2half_rn(0.f);
+        if (d32) d32[c] = 0.f;
+      }
+      if (threadIdx.x == 0) loss[row] = 0.f;
+      return;
+    }
+  }
+  float m = -1e30f, s = 0.f;
+  for (int c = threadIdx.x; c < ncls; c += TPB) {
+    float v = x[c];
+    if (v > m) {
+      s = s * __expf(m - v) + 1.0f;
+      m = v;
+    } else {
+      s += __expf(v - m);
+    }
+  }
+  // combine (m, s) pairs across the warp, then across warps
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    float mm = fmaxf(m, m2);
+    s = s * __expf(m - mm) + s2 * __expf(m2 - mm);
+    m = mm;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    s_m[warp] = m;
+    s_s[warp] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float mm = s_m[0], ss = s_s[0];
+    for (int k = 1; k < TPB / 32; ++k) {
+      float m2 = s_m[k], s2 = s_s[k];
+      float mx = fmaxf(mm, m2);
+      ss = ss * __expf(mm - mx) + s2 * __expf(m2 - mx);
+      mm = mx;
+    }
+    float logz = mm + logf(ss);
+    s_logz = logz;
+    loss[row] = logz - x[labels[row]];
+  }
+  __syncthreads();
+  const float logz = s_logz;
+  const int y = (int)labels[row];
+  for (int c = threadIdx.x; c < stride; c += TPB) {
+    float gv = 0.f;
+    if (c < ncls) gv = (__expf(x[c] - logz) - (c == y ? 1.0f : 0.0f)) * wi;
+    if (d16) d16[c] = __float2half_rn(gv);
+    if (d32) d32[c] = gv;
+  }
+}
+
+// ---- layernorm ----------------------------------------------------------------------------
+
+// One warp per row, lanes stride the row (the reference's layout, tkernels.py:32-54).
+__global__ void k_layernorm(const float* __restrict__ x, const float* __restrict__ gamma,
+                            const float* __restrict__ beta, __half* __restrict__ y16,
+                            float* __restrict__ mu, float* __restrict__ rstd, int rows, int D) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  const float* xr = x + (int64_t)row * D;
+  float s = 0.f;
+  for (int d = lane; d < D; d += 32) s += xr[d];
+  const float m = warp_sum(s) / (float)D;
+  float v = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    float t = xr[d] - m;
+    v += t * t;
+  }
+  const float r = rsqrtf(warp_sum(v) / (float)D + 1e-5f);
+  if (lane == 0) {
+    mu[row] = m;
+    rstd[row] = r;
+  }
+  __half* yr = y16 + (int64_t)row * D;
+  for (int d = lane; d < D; d += 32) yr[d] = __float2half_rn((xr[d] - m) * r * gamma[d] + beta[d]);
+}
+
+constexpr int LNB_WARPS = 4;
+
+// Backward.  Each CTA owns a contiguous band of rows; warp w handles rows
+// band0+w, band0+w+4, ...  Per-column partial sums of dy*xhat and dy are kept
+// in the warp's private shared-memory strip, combined across the CTA's warps
+// and written to scratch[block][2][D]; k_ln_param_final adds the blocks up in
+// a fixed order.
+__global__ void __launch_bounds__(LNB_WARPS * 32)
+k_layernorm_bwd(const float* __restrict__ dy, const float* __restrict__ x,
+                const float* __restrict__ gamma, const float* __restrict__ mu,
+                const float* __restrict__ rstd, const float* __restrict__ dres,
+                float* __restrict__ dx, __half* __restrict__ dx16, __half* __restrict__ dyxh16,
+                __half* __restrict__ dy16, float* __restrict__ scratch, int rows, int D,
+                int rows_per_block) {
+  extern __shared__ float acc[];  // [LNB_WARPS][2][D] when scratch != nullptr
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* a_g = acc + (size_t)warp * 2 * D;
+  float* a_b = a_g + D;
+  if (scratch) {
+    for (int d = lane; d < D; d += 32) {
+      a_g[d] = 0.f;
+      a_b[d] = 0.f;
+    }
+  }
+  const int r0 = blockIdx.x * rows_per_block;
+  const int r1 = min(rows, r0 + rows_per_block);
+  const float inv = 1.0f / (float)D;
+  for (int row = r0 + warp; row < r1; row += LNB_WARPS) {
+    const int64_t base = (int64_t)row * D;
+    const float m = mu[row], r = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      float dyv = dy[base + d];
+      float xh = (x[base + d] - m) * r;
+      float dxh = dyv * gamma[d];
+      s1 += dxh;
+      s2 += dxh * xh;
+      if (dyxh16) dyxh16[base + d] = __float2half_rn(dyv * xh);
+      if (dy16) dy16[base + d] = __float2half_rn(dyv);
+      if (scratch) {
+        a_g[d] += dyv * xh;
+        a_b[d] += dyv;
+      }
+    }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    for (int d = lane; d < D; d += 32) {
+      float xh = (x[base + d] - m) * r;
+      float dxh = dy[base + d] * gamma[d];
+      float o = r * (dxh - s1 * inv - xh * s2 * inv);
+      if (dres) o += dres[base + d];
+      if (dx) dx[base + d] = o;
+      if (dx16) dx16[base + d] = __float2half_rn(o);
+    }
+  }
+  if (scratch) {
+    __syncthreads();
+    float* out = scratch + (size_t)blockIdx.x * 2 * D;
+    for (int d = threadIdx.x; d < 2 * D; d += blockDim.x) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < LNB_WARPS; ++w) s += acc[(size_t)w * 2 * D + d];
+      out[d] = s;
+    }
+  }
+}
+
+__global__ void k_ln_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma,
+                                 float* __restrict__ dbeta, int D, int nblocks) {
+  int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  float g = 0.f, b = 0.f;
+  for (int k = 0; k < nblocks; ++k) {
+    g += scratch[(size_t)k * 2 * D + d];
+    b += scratch[(size_t)k * 2 * D + D + d];
+  }
+  dgamma[d] = g;
+  dbeta[d] = b;
+}
+
+// ---- attention softmax ---------------------------------------------------------------------
+
+// One warp per (batch*head, query) row; causal; optional packed-sample start.
+__global__ void k_attn_softmax(const float* __restrict__ s, const uint32_t* __restrict__ seg,
+                               __half* __restrict__ p16, int64_t rows, int T, int H, float scale) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  const int64_t base = row * T;
+  const int q = (int)(row % T);
+  int st = 0;
+  if (seg) st = (int)seg[(row / T / H) * T + q];
+  float mx = -1e30f;
+  for (int j = st + lane; j <= q; j += 32) mx = fmaxf(mx, s[base + j] * scale);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int j = st + lane; j <= q; j += 32) sum += __expf(s[base + j] * scale - mx);
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
+  for (int j = lane; j < T; j += 32) {
+    float v = 0.f;
+    if (j >= st && j <= q) v = __expf(s[base + j] * scale - mx) * inv;
+    p16[base + j] = __float2half_rn(v);
+  }
+}
+
+__global__ void k_attn_softmax_bwd(const float* __restrict__ dp, const __half* __restrict__ p16,
+                                   __half* __restrict__ ds16, int64_t rows, int T, float scale) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  const int64_t base = row * T;
+  const int q = (int)(row % T);
+  float dot = 0.f;
+  for (int j = lane; j <= q; j += 32) dot += dp[base + j] * __half2float(p16[base + j]);
+  dot = warp_sum(dot);
+  for (int j = lane; j < T; j += 32) {
+    float v = 0.f;
+    if (j <= q) v = __half2float(p16[base + j]) * (dp[base + j] - dot) * scale;
+    ds16[base + j] = __float2half_rn(v);
+  }
+}
+
+// ---- AdamW -----------------------------------------------------------------------------------
+
+__device__ __forceinline__ void adamw_one(float& w, float g, float& m, float& v, float lr, float b1,
+                                          float b2, float bc1, float bc2, float eps, float wd) {
+  m = b1 * m + (1.0f - b1) * g;
+  v = b2 * v + (1.0f - b2) * g * g;
+  float mh = m / bc1;
+  float vh = v / bc2;
+  w -= lr * (mh / (sqrtf(vh) + eps) + wd * w);
+}
+
+__global__ void k_adamw(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ m,
+                        float* __restrict__ v, __half* __restrict__ w16,
+                        const float* __restrict__ hp, int64_t n, float wd) {
+  const float lr = hp[0], b1 = hp[1], b2 = hp[2], bc1 = hp[3], bc2 = hp[4], eps = hp[5];
+  const float gs = hp[6] != 0.0f ? hp[6] : 1.0f;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float wi = w[i], mi = m[i], vi = v[i];
+    adamw_one(wi, g[i] * gs, mi, vi, lr, b1, b2, bc1, bc2, eps, wd);
+    w[i] = wi;
+    m[i] = mi;
+    v[i] = vi;
+    if (w16) w16[i] = __float2half_rn(wi);
+  }
+}
+
+struct AdamTensor {
+  float* w;
+  const float* g;
+  float* m;
+  float* v;
+  __half* w16;
+  int64_t n;
+  float wd;
+  int pad;
+};
+
+constexpr int ADAM_CHUNK = 4096;  // elements per block
+
+// One launch for every parameter tensor: block b looks up (tensor, chunk).
+__global__ void __launch_bounds__(TPB)
+k_adamw_multi(const AdamTensor* __restrict__ tensors, const int2* __restrict__ blockmap,
+              const float* __restrict__ hp) {
+  const float lr = hp[0], b1 = hp[1], b2 = hp[2], bc1 = hp[3], bc2 = hp[4], eps = hp[5];
+  const float gs = hp[6] != 0.0f ? hp[6] : 1.0f;
+  const int2 bm = blockmap[blockIdx.x];
+  const AdamTensor t = tensors[bm.x];
+  const int64_t lo = (int64_t)bm.y * ADAM_CHUNK;
+  const int64_t hi = min(t.n, lo + ADAM_CHUNK);
+  const bool vec = (((uintptr_t)t.w | (uintptr_t)t.g | (uintptr_t)t.m | (uintptr_t)t.v) & 15) == 0 &&
+                   ((uintptr_t)t.w16 & 7) == 0;
+  if (vec) {
+    for (int64_t i = lo + threadIdx.x * 4; i + 3 < hi; i += TPB * 4) {
+      float4 w = *reinterpret_cast<float4*>(t.w + i);
+      float4 g = *reinterpret_cast<const float4*>(t.g + i);
+      float4 m = *reinterpret_cast<float4*>(t.m + i);
+      float4 v = *reinterpret_cast<float4*>(t.v + i);
+      adamw_one(w.x, g.x * gs, m.x, v.x, lr, b1, b2, bc1, bc2, eps, t.wd);
+      adamw_one(w.y, g.y * gs, m.y, v.y, lr, b1, b2, bc1, bc2, eps, t.wd);
+      adamw_one(w.z, g.z * gs, m.z, v.z, lr, b1, b2, bc1, bc2, eps, t.wd);
+      adamw_one(w.w, g.w * gs, m.w, v.w, lr, b1, b2, bc1, bc2, eps, t.wd);
+      *reinterpret_cast<float4*>(t.w + i) = w;
+      *reinterpret_cast<float4*>(t.m + i) = m;
+      *reinterpret_cast<float4*>(t.v + i) = v;
+      if (t.w16) {
+        __half2 a = __floats2half2_rn(w.x, w.y), b = __floats2half2_rn(w.z, w.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&a);
+        o.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(t.w16 + i) = o;
+      }
+    }
+    // ragged tail of this chunk (chunk length not a multiple of 4)
+    int64_t tail = lo + ((hi - lo) & ~(int64_t)3);
+    for (int64_t i = tail + threadIdx.x; i < hi; i += TPB) {
+      float wi = t.w[i], mi = t.m[i], vi = t.v[i];
+      adamw_one(wi, t.g[i] * gs, mi, vi, lr, b1, b2, bc1, bc2, eps, t.wd);
+      t.w[i] = wi; t.m[i] = mi; t.v[i] = vi;
+      if (t.w16) t.w16[i] = __float2half_rn(wi);
+    }
+  } else {
+    for (int64_t i = lo + threadIdx.x; i < hi; i += TPB) {
+      float wi = t.w[i], mi = t.m[i], vi = t.v[i];
+      adamw_one(wi, t.g[i] * gs, mi, vi, lr, b1, b2, bc1, bc2, eps, t.wd);
+      t.w[i] = wi; t.m[i] = mi; t.v[i] = vi;
+      if (t.w16) t.w16[i] = __float2half_rn(wi);
+    }
+  }
+}
+
+struct AdamTable {
+  AdamTensor* tensors = nullptr;
+  int2* blockmap = nullptr;
+  int nblocks = 0;
+};
+
+inline unsigned flat_grid(vkg_device* dev, int64_t n) {
+  return vkg_blocks(n, TPB, (int64_t)dev->sm_count * 16);
+}
+
+}  // namespace
+
+// ---- C ABI -----------------------------------------------------------------------------------
+
+extern "C" int vkg_bias_act(vkg_device* dev, const float* acc, const float* bias, float* z, void* y16,
+                            int64_t n, int ncol, int act) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(acc && bias && n > 0 && ncol > 0, "bias_act: bad arguments");
+  k_bias_act<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(acc, bias, z, (__half*)y16, n, ncol, act);
+  return vkg_check_launch("bias_act");
+}
+
+extern "C" int vkg_bias_act_bwd(vkg_device* dev, const float* dy, const float* z, void* dz16,
+                                float* dz32, int64_t n, int act) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(dy && z && n > 0, "bias_act_bwd: bad arguments");
+  k_bias_act_bwd<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(dy, z, (__half*)dz16, dz32, n, act);
+  return vkg_check_launch("bias_act_bwd");
+}
+
+extern "C" int vkg_bias(vkg_device* dev, const float* acc, const float* bias, float* z, int64_t n,
+                        int ncol) {
+  return vkg_bias_act(dev, acc, bias, z, nullptr, n, ncol, VKG_ACT_NONE);
+}
+
+extern "C" int vkg_col_sum(vkg_device* dev, const float* g, float* sums, int ncol, int nrow) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(g && sums && ncol > 0 && nrow > 0, "col_sum: bad arguments");
+  k_col_sum<<<vkg_blocks(ncol, 128), 128, 0, dev->stream>>>(g, sums, ncol, nrow);
+  return vkg_check_launch("col_sum");
+}
+
+static int col_sum_chunks(int ncol, int nrow) {
+  int col_blocks = (ncol + CS_COLS - 1) / CS_COLS;
+  int want = (592 + col_blocks - 1) / col_blocks;  // ~4 CTAs per SM on 148 SMs
+  int max_chunks = (nrow + 31) / 32;               // at least 32 rows per chunk
+  if (want > max_chunks) want = max_chunks;
+  if (want < 1) want = 1;
+  if (want > 1024) want = 1024;
+  return want;
+}
+
+extern "C" int64_t vkg_col_sum_scratch_floats(int ncol, int nrow) {
+  if (ncol <= 0 || nrow <= 0) return 0;
+  return (int64_t)col_sum_chunks(ncol, nrow) * ncol;
+}
+
+extern "C" int vkg_col_sum_det(vkg_device* dev, const void* g, int g_dtype, float* sums,
+                               float* scratch, int ncol, int nrow, int accumulate) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(g && sums && scratch && ncol > 0 && nrow > 0, "col_sum_det: bad arguments");
+  VKG_REQUIRE(g_dtype == VKG_F32 || g_dtype == VKG_F16, "col_sum_det: dtype must be f32 or f16");
+  int nchunk = col_sum_chunks(ncol, nrow);
+  int rpc = (nrow + nchunk - 1) / nchunk;
+  dim3 grid((ncol + CS_COLS - 1) / CS_COLS, nchunk);
+  if (g_dtype == VKG_F16)
+    k_col_sum_partial<__half><<<grid, CS_WARPS * 32, 0, dev->stream>>>((const __half*)g, scratch,
+                                                                        ncol, nrow, rpc);
+  else
+    k_col_sum_partial<float><<<grid, CS_WARPS * 32, 0, dev->stream>>>((const float*)g, scratch, ncol,
+                                                                       nrow, rpc);
+  if (vkg_check_launch("col_sum_partial")) return 1;
+  k_col_sum_final<<<vkg_blocks(ncol, 128), 128, 0, dev->stream>>>(scratch, sums, ncol, nchunk,
+                                                                  accumulate);
+  return vkg_check_launch("col_sum_final");
+}
+
+extern "C" int vkg_softmax_ce(vkg_device* dev, const float* logits, const uint32_t* labels,
+                              const float* w, void* dl16, float* dl32, float* loss, int rows,
+                              int stride, int ncls, float grad_scale) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(logits && labels && loss && rows > 0 && stride >= ncls && ncls > 0,
+              "softmax_ce: bad arguments");
+  k_softmax_ce<<<rows, TPB, 0, dev->stream>>>(logits, labels, w, (__half*)dl16, dl32, loss, stride,
+                                              ncls, grad_scale);
+  return vkg_check_launch("softmax_ce");
+}
+
+extern "C" int vkg_adamw(vkg_device* dev, float* w, const float* g, float* m, float* v, void* w16,
+                         const float* hp, int64_t n, float wd) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(w && g && m && v && hp && n > 0, "adamw: bad arguments");
+  k_adamw<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(w, g, m, v, (__half*)w16, hp, n, wd);
+  return vkg_check_launch("adamw");
+}
+
+extern "C" int vkg_adamw_table_create(vkg_device* dev, int ntensors, float* const* w,
+                                      const float* const* g, float* const* m, float* const* v,
+                                      void* const* w16, const int64_t* n, const float* wd,
+                                      void** table) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(ntensors > 0 && w && g && m && v && n && wd && table, "adamw_table: bad arguments");
+  std::vector<AdamTensor> ts(ntensors);
+  std::vector<int2> map;
+  for (int i = 0; i < ntensors; ++i) {
+    VKG_REQUIRE(n[i] > 0 && w[i] && g[i] && m[i] && v[i], "adamw_table: tensor %d is empty", i);
+    ts[i].w = w[i]; ts[i].g = g[i]; ts[i].m = m[i]; ts[i].v = v[i];
+    ts[i].w16 = w16 ? (__half*)w16[i] : nullptr;
+    ts[i].n = n[i]; ts[i].wd = wd[i]; ts[i].pad = 0;
+    int chunks = (int)((n[i] + ADAM_CHUNK - 1) / ADAM_CHUNK);
+    for (int c = 0; c < chunks; ++c) map.push_back(make_int2(i, c));
+  }
+  AdamTable* t = new AdamTable();
+  t->nblocks = (int)map.size();
+  cudaError_t e = cudaMalloc(&t->tensors, ts.size() * sizeof(AdamTensor));
+  if (e == cudaSuccess) e = cudaMalloc(&t->blockmap, map.size() * sizeof(int2));
+  if (e == cudaSuccess)
+    e = cudaMemcpy(t->tensors, ts.data(), ts.size() * sizeof(AdamTensor), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess)
+    e = cudaMemcpy(t->blockmap, map.data(), map.size() * sizeof(int2), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    if (t->tensors) cudaFree(t->tensors);
+    if (t->blockmap) cudaFree(t->blockmap);
+    delete t;
+    VKG_FAIL("adamw_table: %s", cudaGetErrorString(e));
+  }
+  *table = t;
+  return 0;
+}
+
+extern "C" int vkg_adamw_table_destroy(vkg_device* dev, void* table) {
+  if (!table) return 0;
+  if (vkg_bind(dev)) return 1;
+  AdamTable* t = (AdamTable*)table;
+  cudaFree(t->tensors);
+  cudaFree(t->blockmap);
+  delete t;
+  return 0;
+}
+
+extern "C" int vkg_adamw_multi(vkg_device* dev, void* table, const float* hp) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(table && hp, "adamw_multi: bad arguments");
+  AdamTable* t = (AdamTable*)table;
+  k_adamw_multi<<<t->nblocks, TPB, 0, dev->stream>>>(t->tensors, t->blockmap, hp);
+  return vkg_check_launch("adamw_multi");
+}
+
+extern "C" int vkg_cast16(vkg_device* dev, const float* src, void* dst16, int64_t n) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(src && dst16 && n > 0, "cast16: bad arguments");
+  if ((n & 3) == 0 && (((uintptr_t)src & 15) == 0) && (((uintptr_t)dst16 & 7) == 0)) {
+    k_cast16_v4<<<flat_grid(dev, n / 4), TPB, 0, dev->stream>>>((const float4*)src, (uint2*)dst16,
+                                                                n / 4);
+  } else {
+    k_cast16<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(src, (__half*)dst16, n);
+  }
+  return vkg_check_launch("cast16");
+}
+
+extern "C" int vkg_layernorm(vkg_device* dev, const float* x, const float* gamma, const float* beta,
+                             void* y16, float* mu, float* rstd, int rows, int D) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(x && gamma && beta && y16 && mu && rstd && rows > 0 && D > 0, "layernorm: bad arguments");
+  const int wpb = 4;
+  k_layernorm<<<(rows + wpb - 1) / wpb, wpb * 32, 0, dev->stream>>>(x, gamma, beta, (__half*)y16, mu,
+                                                                    rstd, rows, D);
+  return vkg_check_launch("layernorm");
+}
+
+static int ln_bwd_blocks(int rows) {
+  int b = (rows + LNB_WARPS - 1) / LNB_WARPS;  // at least one row per warp
+  if (b > 592) b = 592;
+  if (b < 1) b = 1;
+  return b;
+}
+
+extern "C" int64_t vkg_layernorm_bwd_scratch_floats(int rows, int D) {
+  if (rows <= 0 || D <= 0) return 0;
+  return (int64_t)ln_bwd_blocks(rows) * 2 * D;
+}
+
+extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* x, const float* gamma,
+                                 const float* mu, const float* rstd, const float* dres, float* dx,
+                                 void* dx16, void* dyxh16, void* dy16, float* dgamma, float* dbeta,
+                                 float* scratch, int rows, int D) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(dy && x && gamma && mu && rstd && rows > 0 && D > 0, "layernorm_bwd: bad arguments");
+  const bool fused = dgamma != nullptr || dbeta != nullptr;
+  if (fused) VKG_REQUIRE(dgamma && dbeta && scratch, "layernorm_bwd: dgamma, dbeta and scratch go together");
+  int nblocks = ln_bwd_blocks(rows);
+  int rpb = (rows + nblocks - 1) / nblocks;
+  nblocks = (rows + rpb - 1) / rpb;
+  size_t smem = fused ? (size_t)LNB_WARPS * 2 * D * sizeof(float) : 0;
+  VKG_REQUIRE(smem <= 48 * 1024, "layernorm_bwd: fused parameter sums support D <= %d", 48 * 1024 / (LNB_WARPS * 8));
+  k_layernorm_bwd<<<nblocks, LNB_WARPS * 32, smem, dev->stream>>>(
+      dy, x, gamma, mu, rstd, dres, dx, (__half*)dx16, (__half*)dyxh16, (__half*)dy16,
+      fused ? scratch : nullptr, rows, D, rpb);
+  if (vkg_check_launch("layernorm_bwd")) return 1;
+  if (fused) {
+    k_ln_param_final<<<vkg_blocks(D, 128), 128, 0, dev->stream>>>(scratch, dgamma, dbeta, D, nblocks);
+    return vkg_check_launch("ln_param_final");
+  }
+  return 0;
+}
+
+extern "C" int vkg_attn_softmax(vkg_device* dev, const float* s, const uint32_t* seg, void* p16,
+                                int64_t rows, int T, int H, float scale) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(s && p16 && rows > 0 && T > 0, "attn_softmax: bad arguments");
+  const int wpb = 8;
+  k_attn_softmax<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, dev->stream>>>(
+      s, seg, (__half*)p16, rows, T, H > 0 ? H : 1, scale);
+  return vkg_check_launch("attn_softmax");
+}
+
+extern "C" int vkg_attn_softmax_bwd(vkg_device* dev, const float* dp, const void* p16, void* ds16,
+                                    int64_t rows, int T, float scale) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(dp && p16 && ds16 && rows > 0 && T > 0, "attn_softmax_bwd: bad arguments");
+  const int wpb = 8;
+  k_attn_softmax_bwd<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, dev->stream>>>(
+      dp, (const __half*)p16, (__half*)ds16, rows, T, scale);
+  return vkg_check_launch("attn_softmax_bwd");
+}
+
+extern "C" int vkg_split_qkv(vkg_device* dev, const float* qkv, const float* bias, void* q16,
+                             void* k16, void* v16, int64_t n, int D, int T, int H, int hd) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(qkv && bias && q16 && k16 && v16 && n > 0, "split_qkv: bad arguments");
+  k_split_qkv<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(qkv, bias, (__half*)q16, (__half*)k16,
+                                                          (__half*)v16, n, D, T, H, hd);
+  return vkg_check_launch("split_qkv");
+}
+
+extern "C" int vkg_merge_qkv_grad(vkg_device* dev, const float* dq, const float* dk, const float* dv,
+                                  void* dqkv16, int64_t n, int D, int T, int H, int hd) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(dq && dk && dv && dqkv16 && n > 0, "merge_qkv_grad: bad arguments");
+  k_merge_qkv_grad<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(dq, dk, dv, (__half*)dqkv16, n, D, T,
+                                                               H, hd);
+  return vkg_check_launch("merge_qkv_grad");
+}
+
+extern "C" int vkg_merge_heads(vkg_device* dev, const float* src, void* y16, int64_t n, int D, int T,
+                               int H, int hd) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(src && y16 && n > 0, "merge_heads: bad arguments");
+  k_merge_heads<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(src, (__half*)y16, n, D, T, H, hd);
+  return vkg_check_launch("merge_heads");
+}
+
+extern "C" int vkg_split_heads(vkg_device* dev, const float* src, void* dst16, int64_t n, int D,
+                               int T, int H, int hd) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(src && dst16 && n > 0, "split_heads: bad arguments");
+  k_split_heads<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(src, (__half*)dst16, n, D, T, H, hd);
+  return vkg_check_launch("split_heads");
+}
+
+extern "C" int vkg_embed(vkg_device* dev, const float* tok, const float* pos, const uint32_t* ids,
+                         const uint32_t* seg, float* x, int64_t n, int D, int T) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(tok && pos && ids && x && n > 0, "embed: bad arguments");
+  k_embed<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(tok, pos, ids, seg, x, n, D, T);
+  return vkg_check_launch("embed");
+}
+
+extern "C" int vkg_embed_bwd(vkg_device* dev, const float* dx, const uint32_t* ids,
+                             const uint32_t* seg, float* dtok, float* dpos, int64_t n, int D, int T) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(dx && ids && dtok && dpos && n > 0, "embed_bwd: bad arguments");
+  k_embed_bwd<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(dx, ids, seg, dtok, dpos, n, D, T);
+  return vkg_check_launch("embed_bwd");
+}
+
+extern "C" int vkg_residual(vkg_device* dev, const float* acc, const float* bias, const float* res,
+                            float* out, int64_t n, int D) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(acc && bias && res && out && n > 0, "residual: bad arguments");
+  k_residual<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(acc, bias, res, out, n, D);
+  return vkg_check_launch("residual");
+}
+
+extern "C" int vkg_add(vkg_device* dev, const float* a, const float* b, float* out, void* out16,
+                       int64_t n) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(a && b && (out || out16) && n > 0, "add: bad arguments");
+  k_add<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(a, b, out, (__half*)out16, n);
+  return vkg_check_launch("add");
+}
+
+extern "C" int vkg_add_bias(vkg_device* dev, float* x, const float* bias, int64_t n, int ncol) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(x && bias && n > 0 && ncol > 0, "add_bias: bad arguments");
+  k_add_bias<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(x, bias, n, ncol);
+  return vkg_check_launch("add_bias");
+}
+
+extern "C" int vkg_grad_add(vkg_device* dev, const float* g, float* arena, int64_t n, int64_t off) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(g && arena && n > 0 && off >= 0, "grad_add: bad arguments");
+  k_grad_add<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(g, arena + off, n);
+  return vkg_check_launch("grad_add");
+}
+
+extern "C" int vkg_grad_pull(vkg_device* dev, const float* arena, float* g, int64_t n, int64_t off,
+                             float scale) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(g && arena && n > 0 && off >= 0, "grad_pull: bad arguments");
+  k_grad_pull<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(arena + off, g, n, scale);
+  return vkg_check_launch("grad_pull");
+}
+
+extern "C" int vkg_bucket_pack16(vkg_device* dev, const float* src, void* dst16, int dtype, int64_t n,
+                                 float scale) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(src && dst16 && n > 0, "bucket_pack16: bad arguments");
+  if (dtype == VKG_F16)
+    k_pack16<__half><<<flat_grid(dev, n), TPB, 0, dev->stream>>>(src, (__half*)dst16, n, scale);
+  else if (dtype == VKG_BF16)
+    k_pack16<__nv_bfloat16><<<flat_grid(dev, n), TPB, 0, dev->stream>>>(src, (__nv_bfloat16*)dst16, n,
+                                                                         scale);
+  else
+    VKG_FAIL("bucket_pack16: dtype must be f16 or bf16");
+  return vkg_check_launch("bucket_pack16");
+}
+
+extern "C" int vkg_bucket_unpack16(vkg_device* dev, const void* src16, int dtype, float* dst,
+                                   int64_t n, float scale) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(src16 && dst && n > 0, "bucket_unpack16: bad arguments");
+  if (dtype == VKG_F16)
+    k_unpack16<__half><<<flat_grid(dev, n), TPB, 0, dev->stream>>>((const __half*)src16, dst, n, scale);
+  else if (dtype == VKG_BF16)
+    k_unpack16<__nv_bfloat16><<<flat_grid(dev, n), TPB, 0, dev->stream>>>((const __nv_bfloat16*)src16,
+                                                                           dst, n, scale);
+  else
+    VKG_FAIL("bucket_unpack16: dtype must be f16 or bf16");
+  return vkg_check_launch("bucket_unpack16");
+}
