@@ -1,0 +1,172 @@
+"""Generates the golden fixtures in this folder from the reference's own numpy code.
+
+    python tests/golden/make_golden.py [/path/to/vkgrad]
+
+The reference (BrettKnox/vkgrad) loads libvulkan when `vk` is imported, and every
+module imports `vk`, so a stub `vk` module is placed in sys.modules first; only
+the reference's numpy functions are executed:
+
+  kernels.matmul_reference                 (kernels.py:606-610)
+  test_autograd.numpy_forward_backward     (test_autograd.py:21-46)
+  test_transformer.np_model                (test_transformer.py:38-151)
+  examples.hetero_mnist.cpu_backward       (examples/hetero_mnist.py:38-68)
+
+Inputs come from numpy seeds with the same draws the reference's tests make
+(test_kernels.py:10-16, test_autograd.py:53-75, test_transformer.py:222-243),
+so the fixtures store the reference's outputs plus a digest of the inputs.
+The fixtures are what travels: the GPU box has no copy of the reference.
+"""
+
+import hashlib
+import os
+import sys
+import types
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import vkgrad_numpy as orc  # noqa: E402  (input generators only)
+
+
+def import_reference(path):
+    stub = types.ModuleType("vk")
+
+    class VkError(RuntimeError):
+        pass
+
+    class Device:
+        def __init__(self, *a, **k):
+            raise VkError("stub: no Vulkan here")
+
+    stub.VkError, stub.Device = VkError, Device
+    sys.modules["vk"] = stub
+    sys.path.insert(0, path)
+    import kernels as ref_kernels
+    import test_autograd as ref_test_autograd
+    import test_transformer as ref_test_transformer
+    from examples import hetero_mnist as ref_hetero
+    return ref_kernels, ref_test_autograd, ref_test_transformer, ref_hetero
+
+
+def digest(*arrays):
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return np.frombuffer(h.digest()[:8], dtype=np.uint64)[0]
+
+
+MATMUL_CASES = [  # (m, n, k, trans_a, trans_b): test_kernels.py:47-66
+    (256, 256, 256, False, False), (128, 128, 128, False, False),
+    (512, 256, 128, False, False), (256, 512, 256, False, False),
+    (64, 64, 512, False, False), (256, 256, 256, True, False),
+    (256, 256, 256, False, True)]
+
+
+def matmul_inputs(m, n, k, ta, tb, seed=0):
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((k, m) if ta else (m, k)).astype(np.float16)
+    b = rng.standard_normal((n, k) if tb else (k, n)).astype(np.float16)
+    return a, b
+
+
+def mlp_inputs(batch=16, n_in=32, n_hid=16, n_cls=4, pad=16, seed=0):
+    """Same draws, in the same order, as test_autograd.build (test_autograd.py:53-68)."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((batch, n_in)).astype(np.float16).astype(np.float32)
+    y = rng.integers(0, n_cls, batch).astype(np.uint32)
+    params = []
+    for shape in ((n_in, n_hid), (n_hid,), (n_hid, pad), (pad,)):
+        std = np.sqrt(2.0 / shape[0]) if len(shape) == 2 else 0.1
+        params.append(rng.standard_normal(shape).astype(np.float32) * np.float32(std))
+    return x, y, params
+
+
+GPT_CASES = {  # name: (B, T, D, H, L, vocab, tie, packed)
+    "gpt_untied": (2, 16, 32, 2, 2, 16, False, False),
+    "gpt_tied": (2, 16, 32, 2, 2, 16, True, False),
+    "gpt_packed": (2, 64, 32, 2, 2, 16, True, True),
+}
+
+
+def gpt_inputs(name):
+    B, T, D, H, L, vocab, tie, packed = GPT_CASES[name]
+    rows = B * T
+    pad_vocab = ((vocab + 15) // 16) * 16
+    P = orc.make_gpt_params(D, H, L, T, pad_vocab, seed=7, std=0.08, bias_std=0.1, tie=tie)
+    if not tie:
+        P["head.b"] = (np.random.default_rng(8).standard_normal(pad_vocab)).astype(np.float32)
+    rng = np.random.default_rng(0)
+    ids = rng.integers(0, vocab, rows).astype(np.uint32)
+    tgt = rng.integers(0, vocab, rows).astype(np.uint32)
+    seg = w = None
+    if packed:  # test_transformer.py:282-287
+        seg = np.zeros(rows, np.uint32)
+        for b, starts in enumerate(((0, 23, 40, 57), (0, 5, 33))):
+            for s, e in zip(starts, starts[1:] + (T,)):
+                seg[b * T + s:b * T + e] = s
+        w = rng.uniform(0.5, 2.0, rows).astype(np.float32)
+        w[rng.random(rows) < 0.3] = 0.0
+    return dict(B=B, T=T, D=D, H=H, L=L, vocab=vocab, pad_vocab=pad_vocab, tie=tie), P, ids, tgt, seg, w
+
+
+def flatten_grads(G, L):
+    out = {}
+    for k, v in G.items():
+        if isinstance(v, dict):
+            for kk, vv in v.items():
+                out[f"{k}.{kk}"] = np.asarray(vv, np.float32)
+        else:
+            out[k] = np.asarray(v, np.float32)
+    return out
+
+
+def main():
+    ref_path = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    rk, rta, rtt, rh = import_reference(ref_path)
+
+    mm = {}
+    for i, (m, n, k, ta, tb) in enumerate(MATMUL_CASES):
+        a, b = matmul_inputs(m, n, k, ta, tb)
+        c = rk.matmul_reference(a, b, ta, tb)
+        mm[f"c{i}_shape"] = np.array([m, n, k, int(ta), int(tb)])
+        mm[f"c{i}_in"] = np.array([digest(a, b)], dtype=np.uint64)
+        mm[f"c{i}_sample"] = c[::7, ::5].astype(np.float32)
+        mm[f"c{i}_sum"] = np.array([c.astype(np.float64).sum(), np.abs(c).astype(np.float64).sum()])
+    ones = rk.matmul_reference(np.ones((64, 1024), np.float16), np.ones((1024, 64), np.float16))
+    mm["ones_k1024"] = np.array([ones.min(), ones.max()], np.float32)  # test_kernels.py:69-100
+    np.savez_compressed(os.path.join(HERE, "matmul.npz"), **mm)
+
+    mlp = {}
+    for seed in range(5):
+        x, y, params = mlp_inputs(seed=seed)
+        loss, dW1, db1, dW2, db2 = rta.numpy_forward_backward(x, *params, y, 4)
+        mlp[f"s{seed}_in"] = np.array([digest(x, y, *params)], dtype=np.uint64)
+        mlp[f"s{seed}_loss"] = np.array([loss], np.float64)
+        for nm, g in zip(("dW1", "db1", "dW2", "db2"), (dW1, db1, dW2, db2)):
+            mlp[f"s{seed}_{nm}"] = g.astype(np.float32)
+    # the heterogeneous example's CPU worker: same model, different code
+    x, y, params = mlp_inputs(seed=0)
+    loss_h, grads_h = rh.cpu_backward(x, y.astype(np.int64), *params, 4)
+    mlp["hetero_loss"] = np.array([loss_h], np.float64)
+    for nm, g in zip(("dW1", "db1", "dW2", "db2"), grads_h):
+        mlp[f"hetero_{nm}"] = np.asarray(g, np.float32)
+    np.savez_compressed(os.path.join(HERE, "mlp.npz"), **mlp)
+
+    for name in GPT_CASES:
+        cfg, P, ids, tgt, seg, w = gpt_inputs(name)
+        loss, G = rtt.np_model(P, ids.astype(np.int64), tgt.astype(np.int64), cfg["B"], cfg["T"],
+                               cfg["D"], cfg["H"], cfg["L"], cfg["vocab"], cfg["pad_vocab"],
+                               seg=seg, weights=w)
+        flat = flatten_grads(G, cfg["L"])
+        flat["loss"] = np.array([loss], np.float64)
+        flat["inputs_digest"] = np.array([digest(ids, tgt, P["tok"], P["b0"]["qkv.W"])], np.uint64)
+        np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **flat)
+        print(f"{name}: loss {loss:.6f}, {len(flat) - 2} gradient tensors")
+    print("fixtures written to", HERE)
+
+
+if __name__ == "__main__":
+    main()

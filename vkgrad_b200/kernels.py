@@ -282,17 +282,21 @@ class Elementwise:
     `launch(buffers, n, *args)` enqueues the C entry point on the device stream.
     """
 
-    def __init__(self, dev, name, launch, n_buffers):
+    def __init__(self, dev, name, launch, n_buffers, prepare=None):
         self.dev, self.name, self._launch, self.n_buffers = dev, name, launch, n_buffers
+        # prepare(buffers, n, *args) runs when the op is called or recorded (never
+        # inside a capture) and may allocate; its result is passed to launch.
+        self._prepare = prepare
         self.kernel = self
 
     def __call__(self, buffers, n, *args, repeat=1, graph=None):
         if len(buffers) != self.n_buffers:
             raise VkError(f"{self.name}: expected {self.n_buffers} buffers, got {len(buffers)}")
         bufs = list(buffers)
+        extra = () if self._prepare is None else (self._prepare(bufs, int(n), *args),)
 
         def go():
-            self._launch(bufs, int(n), *args)
+            self._launch(bufs, int(n), *args, *extra)
 
         if graph is not None:
             graph.add(go, self.name, sum(b.size for b in bufs))
