@@ -1,0 +1,198 @@
+"""MLP step parity on the GPU: the reference's test_autograd.py checks against the
+fixture its numpy model produced, against the rounding-faithful oracle, and the
+BASELINE MLP shape (784-256-256-10, batch 256, GELU and ReLU)."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import make_golden as mg  # noqa: E402
+from oracle import vkgrad_numpy as orc  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def relerr(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-8))
+
+
+def build(dev, x, y, params, sizes, n_cls, pad, act="gelu"):
+    from vkgrad_b200.autograd import MLP, Ctx
+    ctx = Ctx(dev)
+    batch = x.shape[0]
+    model = MLP(ctx, batch, list(sizes), n_cls, pad_classes=pad, act=act)
+    for p, w in zip(model.params(), params):
+        p.set(w)
+    xb = ctx.buf(x.size * 2, "shared")
+    xb.array(np.float16, x.shape)[:] = x.astype(np.float16)
+    xb.flush()
+    yb = ctx.buf(batch * 4, "shared")
+    yb.array(np.uint32, (batch,))[:] = y
+    yb.flush()
+    return ctx, model, xb, yb
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_gradients_against_reference_fixture(dev, seed):
+    """test_autograd.py:78-103 with its tolerances: loss abs 2e-3, gradients rel 2e-2."""
+    z = np.load(os.path.join(GOLD, "mlp.npz"))
+    x, y, params = mg.mlp_inputs(seed=seed)
+    ctx, model, xb, yb = build(dev, x, y, params, (32, 16), 4, 16)
+    try:
+        loss = model.forward_backward(xb, yb)
+        assert abs(loss - z[f"s{seed}_loss"][0]) < 2e-3
+        for p, nm in zip(model.params(), ("dW1", "db1", "dW2", "db2")):
+            assert relerr(p.grad_numpy(), z[f"s{seed}_{nm}"]) < 2e-2, nm
+    finally:
+        ctx.destroy()
+
+
+@pytest.mark.parametrize("act", ["gelu", "relu"])
+def test_baseline_mlp_against_faithful_oracle(dev, act):
+    """784-256-256-10, batch 256: loss and every gradient within 1e-3 of the oracle
+    that rounds to fp16 where the kernels do."""
+    x, y, params = orc.make_mlp_case(256, (784, 256, 256), 10, 16, seed=0)
+    ctx, model, xb, yb = build(dev, x, y, params, (784, 256, 256), 10, 16, act=act)
+    try:
+        loss = model.forward_backward(xb, yb)
+        ref_loss, grads = orc.mlp_forward_backward(x.astype(np.float32), params, y, 10, act=act,
+                                                   faithful=True)
+        assert abs(loss - ref_loss) < 1e-3 * abs(ref_loss)
+        for p, g in zip(model.params(), grads):
+            # ReLU: a unit whose pre-activation rounds across 0 flips its mask; allow 2e-3
+            assert relerr(p.grad_numpy(), g) < (1e-3 if act == "gelu" else 2e-3), p.name
+        f32_loss, f32_grads = orc.mlp_forward_backward(x.astype(np.float32), params, y, 10, act=act)
+        assert abs(loss - f32_loss) < 2e-3
+        for p, g in zip(model.params(), f32_grads):
+            assert relerr(p.grad_numpy(), g) < 2e-2, p.name
+    finally:
+        ctx.destroy()
+
+
+def test_reference_semantics_backward(dev):
+    """Linear.backward(dout16, dout32) as the reference's tape calls it
+    (autograd.py:202-228): gradient of the OUTPUT in, dx32 out."""
+    from vkgrad_b200.autograd import Ctx, Linear
+    rng = np.random.default_rng(0)
+    B, I, O = 32, 48, 24
+    ctx = Ctx(dev)
+    try:
+        lin = Linear(ctx, B, I, O, activation=True, need_dx=True, name="t")
+        W = (rng.standard_normal((I, O)) * 0.2).astype(np.float32)
+        b = (rng.standard_normal(O) * 0.1).astype(np.float32)
+        lin.W.set(W)
+        lin.b.set(b)
+        x = rng.standard_normal((B, I)).astype(np.float16)
+        dout = rng.standard_normal((B, O)).astype(np.float32)
+        xb = ctx.buf(x.nbytes, "cached"); xb.array(np.float16, x.shape)[:] = x; xb.flush()
+        d32 = ctx.buf(dout.nbytes, "cached"); d32.array(np.float32, dout.shape)[:] = dout; d32.flush()
+        d16 = ctx.buf(dout.size * 2, "cached"); d16.array(np.float16, dout.shape)[:] = dout; d16.flush()
+        tape = []
+        lin.forward(xb, tape)
+        assert len(tape) == 1
+        _, dx = tape[0](d16, d32)
+        W16 = orc.r16(W)
+        z = x.astype(np.float32) @ W16 + b
+        dz = dout * orc.dgelu(z)
+        tmp = dev.buffer(B * I * 4, "cached")
+        dev.copy(dx, tmp, B * I * 4); tmp.invalidate()
+        assert relerr(tmp.array(np.float32, (B, I)), orc.r16(dz) @ W16.T) < 1e-3
+        assert relerr(lin.W.grad_numpy(), x.astype(np.float32).T @ orc.r16(dz)) < 1e-3
+        assert relerr(lin.b.grad_numpy(), dz.sum(0)) < 1e-4
+        tmp.destroy()
+    finally:
+        ctx.destroy()
+
+
+def test_recorded_step_equals_eager_and_adamw_matches_oracle(dev):
+    """TrainStep (one CUDA graph) reproduces the eager step bit for bit, and three
+    AdamW steps track the oracle's AdamW on the oracle's gradients."""
+    from vkgrad_b200.autograd import AdamW, TrainStep
+    x, y, params = orc.make_mlp_case(64, (64, 32), 8, 16, seed=3)
+    ctx, model, xb, yb = build(dev, x, y, params, (64, 32), 8, 16)
+    ctx2, model2, xb2, yb2 = build(dev, x, y, params, (64, 32), 8, 16)
+    try:
+        opt = AdamW(ctx, model.params(), lr=1e-2)
+        step = TrainStep(model, opt, xb, yb)
+        assert step.graph.n_kernels >= 10
+        opt2 = AdamW(ctx2, model2.params(), lr=1e-2)
+        w = [p.copy() for p in params]
+        m = [np.zeros_like(p) for p in params]
+        v = [np.zeros_like(p) for p in params]
+        for t in range(1, 4):
+            loss, dt = step(1e-2)
+            assert dt > 0
+            loss2 = model2.forward_backward(xb2, yb2)
+            opt2.step(1e-2)
+            assert loss == loss2
+            ref_loss, grads = orc.mlp_forward_backward(x.astype(np.float32), w, y, 8, faithful=True)
+            assert abs(loss - ref_loss) < 1e-3 * abs(ref_loss)
+            for i in range(len(w)):
+                wd = 0.0 if w[i].ndim == 1 else 0.01
+                w[i], m[i], v[i], _ = orc.adamw_step(w[i], grads[i], m[i], v[i], t, lr=1e-2, wd=wd)
+        for p, p2, wr in zip(model.params(), model2.params(), w):
+            assert np.array_equal(p.numpy(), p2.numpy()), "graph replay differs from eager"
+            assert np.abs(p.numpy() - wr).max() < 2e-3, p.name
+            # the fp16 mirror is refreshed by the optimiser kernel
+            tmp = dev.buffer(p.n * 2, "cached")
+            dev.copy(p.w16, tmp, p.n * 2); tmp.invalidate()
+            assert np.array_equal(tmp.array(np.float16, p.shape), p.numpy().astype(np.float16))
+            tmp.destroy()
+    finally:
+        ctx.destroy()
+        ctx2.destroy()
+
+
+def test_adamw_decreases_loss(dev):
+    """test_autograd.py:152-166: overfit one batch, loss falls below 20 %."""
+    from vkgrad_b200.autograd import AdamW
+    rng = np.random.default_rng(5)
+    batch, n_in, n_hid, n_cls, pad = 32, 64, 32, 8, 16
+    x = rng.standard_normal((batch, n_in)).astype(np.float16)
+    y = rng.integers(0, n_cls, batch).astype(np.uint32)
+    params = []
+    for shape in ((n_in, n_hid), (n_hid,), (n_hid, pad), (pad,)):
+        std = np.sqrt(2.0 / shape[0]) if len(shape) == 2 else 0.1
+        params.append(rng.standard_normal(shape).astype(np.float32) * np.float32(std))
+    ctx, model, xb, yb = build(dev, x, y, params, (n_in, n_hid), n_cls, pad)
+    try:
+        opt = AdamW(ctx, model.params(), lr=3e-3)
+        first = model.forward_backward(xb, yb)
+        for _ in range(200):
+            model.forward_backward(xb, yb)
+            opt.step()
+        last = model.forward_backward(xb, yb)
+        assert last < first * 0.2, f"loss {first:.4f} -> {last:.4f}"
+    finally:
+        ctx.destroy()
+
+
+def test_finite_differences(dev):
+    """test_autograd.py:106-149: central differences on each tensor's two largest
+    gradient entries (ranked by the float64 oracle), eps 0.05, 5 % tolerance."""
+    x, y, params = mg.mlp_inputs(seed=3)
+    ctx, model, xb, yb = build(dev, x, y, params, (32, 16), 4, 16)
+    try:
+        ps = list(model.params())
+        refs = orc.mlp_forward_backward(x.astype(np.float64), [p.astype(np.float64) for p in params],
+                                        y, 4)[1]
+        model.forward_backward(xb, yb)
+        grads = [p.grad_numpy() for p in ps]
+        eps = 0.05
+        for p, ref, grad in zip(ps, refs, grads):
+            w = p.numpy().copy()
+            for flat in np.argsort(-np.abs(ref).ravel())[:2]:
+                i = np.unravel_index(flat, ref.shape)
+                wp = w.copy(); wp[i] += eps; p.set(wp)
+                lp = model.forward_backward(xb, yb)
+                wm = w.copy(); wm[i] -= eps; p.set(wm)
+                lm = model.forward_backward(xb, yb)
+                p.set(w)
+                fd = (lp - lm) / (2 * eps)
+                assert abs(fd - float(grad[i])) / abs(ref[i]) < 0.05, p.name
+    finally:
+        ctx.destroy()

@@ -1,0 +1,240 @@
+"""GEMM trio parity on the GPU, through the C ABI: the reference's own kernel tests
+(test_kernels.py) against the golden fixture and the CPU oracle, plus ragged,
+batched and fused-epilogue cases the reference cannot express."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import make_golden as mg  # noqa: E402
+from oracle import vkgrad_numpy as orc  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+TOL = 2e-3  # the reference's kernel tolerance: max|got-ref| / max|ref| (test_kernels.py:34-36)
+
+
+def up(dev, arr, kind="cached"):
+    b = dev.buffer(arr.nbytes, kind)
+    b.array(arr.dtype, arr.shape)[...] = arr
+    b.flush()
+    return b
+
+
+def down(dev, buf, dtype, shape):
+    if buf.kind == "device":
+        tmp = dev.buffer(buf.size, "cached")
+        dev.copy(buf, tmp, buf.size)
+        tmp.invalidate()
+        out = tmp.array(dtype, shape).copy()
+        tmp.destroy()
+        return out
+    buf.invalidate()
+    return buf.array(dtype, shape).copy()
+
+
+def relerr(got, ref):
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-6))
+
+
+@pytest.mark.parametrize("i", range(len(mg.MATMUL_CASES)))
+def test_reference_kernel_cases(dev, i):
+    """test_kernels.py:47-66 shapes through kernels.Matmul with its own buffer kinds."""
+    from vkgrad_b200.kernels import Matmul
+    m, n, k, ta, tb = mg.MATMUL_CASES[i]
+    a, b = mg.matmul_inputs(m, n, k, ta, tb)
+    ba, bb = up(dev, a, "shared"), up(dev, b, "shared")
+    bc = dev.buffer(m * n * 4, "cached")
+    bc.array(np.float32)[:] = np.nan
+    bc.flush()
+    mm = Matmul(dev, 2, 2, 2, ta, tb)
+    mm(ba, bb, bc, m, n, k)
+    got = down(dev, bc, np.float32, (m, n))
+    z = np.load(os.path.join(GOLD, "matmul.npz"))
+    assert relerr(got[::7, ::5], z[f"c{i}_sample"]) < TOL
+    assert relerr(got, orc.matmul16(a, b, ta, tb)) < TOL
+    for x in (ba, bb, bc):
+        x.destroy()
+
+
+def test_accumulate_is_f32(dev):
+    """All-ones 64x64x1024 must be exactly 1024 (test_kernels.py:69-100)."""
+    from vkgrad_b200.kernels import Matmul
+    m = n = 64
+    k = 1024
+    ba = up(dev, np.ones((m, k), np.float16), "shared")
+    bb = up(dev, np.ones((k, n), np.float16), "shared")
+    bc = dev.buffer(m * n * 4, "cached")
+    Matmul(dev, 1, 2, 2)(ba, bb, bc, m, n, k)
+    got = down(dev, bc, np.float32, (m, n))
+    assert np.all(got == float(k))
+    for x in (ba, bb, bc):
+        x.destroy()
+
+
+@pytest.mark.parametrize("m,n,k,ta,tb", [
+    (32, 16, 32, False, False), (32, 96, 16, False, True), (16, 32, 32, True, False),
+    (200, 72, 40, False, False), (136, 264, 200, True, True), (1, 8, 8, False, False),
+    (300, 520, 72, False, True), (520, 24, 136, True, False)])
+@pytest.mark.parametrize("tile_n", [0, 64, 256])
+def test_ragged_shapes(dev, m, n, k, ta, tb, tile_n):
+    """Edges that are not tile multiples (the reference raises VkError for these)."""
+    from vkgrad_b200.kernels import gemm
+    rng = np.random.default_rng(m * 7 + n)
+    a = rng.standard_normal((k, m) if ta else (m, k)).astype(np.float16)
+    b = rng.standard_normal((n, k) if tb else (k, n)).astype(np.float16)
+    ba, bb = up(dev, a), up(dev, b)
+    guard = 64
+    bc = up(dev, np.full(m * n + guard, np.nan, np.float32))
+    gemm(dev, ba, bb, bc, m, n, k, ta, tb, tile_n=tile_n)
+    full = down(dev, bc, np.float32, (m * n + guard,))
+    assert np.isnan(full[m * n:]).all(), "wrote past the end of C"
+    assert relerr(full[:m * n].reshape(m, n), orc.matmul16(a, b, ta, tb)) < TOL
+    for x in (ba, bb, bc):
+        x.destroy()
+
+
+def test_misaligned_shape_is_rejected(dev):
+    from vkgrad_b200.kernels import Matmul
+    from vkgrad_b200.vk import VkError
+    ba, bb, bc = (dev.buffer(4096, "device") for _ in range(3))
+    with pytest.raises(VkError):
+        Matmul(dev)(ba, bb, bc, 16, 12, 16)     # n not a multiple of 8
+    with pytest.raises(VkError):
+        Matmul(dev)(ba, bb, bc, 16, 16, 20)     # row pitch of A not 16-byte aligned
+    for x in (ba, bb, bc):
+        x.destroy()
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False)])
+def test_batched_dense_stack(dev, ta, tb):
+    """kernels.Matmul(batched=True) with element strides (kernels.py:58-64)."""
+    from vkgrad_b200.kernels import Matmul
+    nb, m, n, k = 6, 64, 48, 32
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((nb,) + ((k, m) if ta else (m, k))).astype(np.float16)
+    b = rng.standard_normal((nb,) + ((n, k) if tb else (k, n))).astype(np.float16)
+    ba, bb = up(dev, a), up(dev, b)
+    bc = dev.buffer(nb * m * n * 4, "cached")
+    Matmul(dev, 1, 1, 1, ta, tb, batched=True)(ba, bb, bc, m, n, k, nbatch=nb,
+                                               strides=(m * k, k * n, m * n))
+    got = down(dev, bc, np.float32, (nb, m, n))
+    ref = np.stack([orc.matmul16(a[i], b[i], ta, tb) for i in range(nb)])
+    assert relerr(got, ref) < TOL
+    for x in (ba, bb, bc):
+        x.destroy()
+
+
+def test_heads_addressed_in_place(dev):
+    """Q K^T per (batch, head) read straight out of a (rows, 3D) projection, and
+    P V written into the merged (rows, D) layout: what Attention does instead of
+    split_qkv / merge_heads (tkernels.py:195-300)."""
+    from vkgrad_b200._lib import F16
+    from vkgrad_b200.kernels import gemm
+    B, T, H, hd = 2, 48, 3, 16
+    D = H * hd
+    rng = np.random.default_rng(9)
+    qkv = rng.standard_normal((B * T, 3 * D)).astype(np.float16)
+    bq = up(dev, qkv)
+    bs = dev.buffer(B * H * T * T * 4, "cached")
+    gemm(dev, bq, bq, bs, T, T, hd, trans_b=True, nb0=H, nb1=B, lda=3 * D, ldb=3 * D, ldc=T,
+         sa=(hd, T * 3 * D), sb=(hd, T * 3 * D), sc=(T * T, H * T * T), a_off=0, b_off=D)
+    got = down(dev, bs, np.float32, (B, H, T, T))
+    q = qkv[:, :D].reshape(B, T, H, hd).transpose(0, 2, 1, 3).astype(np.float32)
+    k = qkv[:, D:2 * D].reshape(B, T, H, hd).transpose(0, 2, 1, 3).astype(np.float32)
+    v = qkv[:, 2 * D:].reshape(B, T, H, hd).transpose(0, 2, 1, 3).astype(np.float32)
+    assert relerr(got, q @ k.transpose(0, 1, 3, 2)) < TOL
+    p = rng.random((B, H, T, T)).astype(np.float16)
+    bp = up(dev, p)
+    bo = up(dev, np.zeros((B * T, D), np.float16))
+    gemm(dev, bp, bq, bo, T, hd, T, nb0=H, nb1=B, lda=T, ldb=3 * D, ldc=D,
+         sa=(T * T, H * T * T), sb=(hd, T * 3 * D), sc=(hd, T * D), b_off=2 * D, c_dtype=F16)
+    got = down(dev, bo, np.float16, (B * T, D)).astype(np.float32)
+    ref = (p.astype(np.float32) @ v).transpose(0, 2, 1, 3).reshape(B * T, D)
+    assert relerr(got, ref) < 2e-3
+    for x in (bq, bs, bp, bo):
+        x.destroy()
+
+
+@pytest.mark.parametrize("act", ["gelu", "relu"])
+def test_fused_epilogue(dev, act):
+    """bias + saved pre-activation + activation + fp16 narrowing in one GEMM; and the
+    backward form: activation derivative and residual in the epilogue."""
+    from vkgrad_b200._lib import ACT_GELU, ACT_RELU, F16, F32
+    from vkgrad_b200.kernels import gemm
+    code = {"gelu": ACT_GELU, "relu": ACT_RELU}[act]
+    f, df = orc.ACTS[act]
+    m, n, k = 200, 136, 72
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    w = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float16)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    ba, bw, bb, br = up(dev, a), up(dev, w), up(dev, bias), up(dev, res)
+    by = dev.buffer(m * n * 2, "cached")
+    bz = dev.buffer(m * n * 4, "cached")
+    gemm(dev, ba, bw, by, m, n, k, c_dtype=F16, bias=bb, pre=bz, act=code)
+    z_ref = orc.matmul16(a, w) + bias
+    assert relerr(down(dev, bz, np.float32, (m, n)), z_ref) < 1e-5
+    y = down(dev, by, np.float16, (m, n)).astype(np.float32)
+    assert relerr(y, f(z_ref)) < 1e-3
+    # backward-style epilogue: out = acc * act'(z) + residual, fp32 plus an fp16 copy
+    bo = dev.buffer(m * n * 4, "cached")
+    bo16 = dev.buffer(m * n * 2, "cached")
+    gemm(dev, ba, bw, bo, m, n, k, c_dtype=F32, dact_z=bz, dact=code, residual=br, c2=bo16)
+    ref = orc.matmul16(a, w) * df(z_ref) + res
+    got = down(dev, bo, np.float32, (m, n))
+    if act == "relu":   # derivative flips at z == 0 only; exclude values within rounding of 0
+        mask = np.abs(z_ref) > 1e-4
+        assert relerr(got[mask], ref[mask]) < 1e-5
+    else:
+        assert relerr(got, ref) < 1e-5
+        assert relerr(down(dev, bo16, np.float16, (m, n)).astype(np.float32), ref) < 1e-3
+    for x in (ba, bw, bb, br, by, bz, bo, bo16):
+        x.destroy()
+
+
+def test_bf16_inputs(dev):
+    """bf16 operands (the reference has f16 only): checked against bf16-rounded numpy."""
+    from vkgrad_b200._lib import BF16
+    from vkgrad_b200.kernels import gemm
+    m, n, k = 128, 128, 256
+    rng = np.random.default_rng(4)
+
+    def to_bf16(x):
+        u = x.astype(np.float32).view(np.uint32)
+        u = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+        return u.astype(np.uint16)
+
+    a32 = rng.standard_normal((m, k)).astype(np.float32)
+    b32 = rng.standard_normal((k, n)).astype(np.float32)
+    a16, b16 = to_bf16(a32), to_bf16(b32)
+    widen = lambda u: (u.astype(np.uint32) << 16).view(np.float32)
+    ba, bb = up(dev, a16), up(dev, b16)
+    bc = dev.buffer(m * n * 4, "cached")
+    gemm(dev, ba, bb, bc, m, n, k, in_dtype=BF16)
+    assert relerr(down(dev, bc, np.float32, (m, n)), widen(a16) @ widen(b16)) < TOL
+    for x in (ba, bb, bc):
+        x.destroy()
+
+
+def test_large_shape_linearity(dev):
+    """At a BASELINE size (4096 x 3072 x 768) the oracle is still quick, and
+    linearity gives a size-independent check: (2A) B == 2 (A B) exactly."""
+    from vkgrad_b200.kernels import gemm
+    m, k, n = 4096, 768, 3072
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    w = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float16)
+    ba, ba2, bw = up(dev, a), up(dev, (a * np.float16(2)).astype(np.float16)), up(dev, w)
+    bc, bc2 = dev.buffer(m * n * 4, "cached"), dev.buffer(m * n * 4, "cached")
+    gemm(dev, ba, bw, bc, m, n, k)
+    gemm(dev, ba2, bw, bc2, m, n, k)
+    c, c2 = down(dev, bc, np.float32, (m, n)), down(dev, bc2, np.float32, (m, n))
+    assert np.array_equal(c2, 2 * c)
+    assert relerr(c, orc.matmul16(a, w)) < TOL
+    for x in (ba, ba2, bw, bc, bc2):
+        x.destroy()

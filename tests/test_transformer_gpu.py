@@ -1,0 +1,196 @@
+"""GPT step parity on the GPU: the reference's test_transformer.py cases against the
+fixtures its np_model produced (its tolerances: loss 5e-3, gradients 3e-2) and
+against the rounding-faithful oracle (1e-3)."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import make_golden as mg  # noqa: E402
+from oracle import vkgrad_numpy as orc  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def relerr(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-8))
+
+
+def load_params(model, P):
+    model.tok.set(P["tok"])
+    model.pos.set(P["pos"])
+    model.lnf.g.set(P["lnf.g"])
+    model.lnf.b.set(P["lnf.b"])
+    if not model.tie:
+        model.head.W.set(P["head.W"])
+        model.head.b.set(P["head.b"])
+    for i, b in enumerate(model.blocks):
+        p = P[f"b{i}"]
+        for name, param in (("ln1.g", b.ln1.g), ("ln1.b", b.ln1.b), ("ln2.g", b.ln2.g),
+                            ("ln2.b", b.ln2.b), ("qkv.W", b.attn.qkv.W), ("qkv.b", b.attn.qkv.b),
+                            ("proj.W", b.attn.proj.W), ("proj.b", b.attn.proj.b),
+                            ("fc1.W", b.fc1.W), ("fc1.b", b.fc1.b), ("fc2.W", b.fc2.W),
+                            ("fc2.b", b.fc2.b)):
+            param.set(p[name])
+
+
+def model_grads(model):
+    out = {"lnf.g": model.lnf.g, "lnf.b": model.lnf.b, "pos": model.pos, "tok": model.tok}
+    if not model.tie:
+        out["head.W"], out["head.b"] = model.head.W, model.head.b
+    for i, b in enumerate(model.blocks):
+        for name, param in (("ln1.g", b.ln1.g), ("ln1.b", b.ln1.b), ("ln2.g", b.ln2.g),
+                            ("ln2.b", b.ln2.b), ("qkv.W", b.attn.qkv.W), ("qkv.b", b.attn.qkv.b),
+                            ("proj.W", b.attn.proj.W), ("proj.b", b.attn.proj.b),
+                            ("fc1.W", b.fc1.W), ("fc1.b", b.fc1.b), ("fc2.W", b.fc2.W),
+                            ("fc2.b", b.fc2.b)):
+            out[f"b{i}.{name}"] = param
+    return {k: p.grad_numpy() for k, p in out.items()}
+
+
+def expected(flat, tie):
+    """Reference-side gradient per model tensor (test_transformer.py:185-204)."""
+    exp = dict(flat)
+    if tie:
+        exp["tok"] = flat["tok"] + flat["head.W"].T
+        exp.pop("head.W")
+        exp.pop("head.b")
+    return exp
+
+
+def shared(ctx, arr):
+    b = ctx.buf(arr.nbytes, "shared")
+    b.array(arr.dtype, arr.shape)[:] = arr
+    b.flush()
+    return b
+
+
+def run_case(dev, name, staged=False):
+    from vkgrad_b200.transformer import GPT, TCtx
+    cfg, P, ids, tgt, seg, w = mg.gpt_inputs(name)
+    ctx = TCtx(dev)
+    try:
+        model = GPT(ctx, cfg["B"], cfg["T"], cfg["D"], cfg["H"], cfg["L"], cfg["vocab"],
+                    tie=cfg["tie"])
+        assert model.pad_vocab == cfg["pad_vocab"]
+        load_params(model, P)
+        idb, tgb = shared(ctx, ids), shared(ctx, tgt)
+        segb = None if seg is None else shared(ctx, seg)
+        wb = None if w is None else shared(ctx, w)
+        if staged:
+            graphs = {}
+
+            def stage(s):
+                if s not in graphs:
+                    graphs[s] = dev.graph(f"stage{s}")
+                return graphs[s]
+            model.record(idb, tgb, stage, seg=segb, weights=wb)
+            assert sorted(graphs) == list(range(model.n_stages()))
+            for s in sorted(graphs):
+                graphs[s].finish()
+                graphs[s].submit()
+        else:
+            graph = dev.graph("test")
+            model.record(idb, tgb, graph, seg=segb, weights=wb)
+            graph.finish()
+            graph.submit()
+        model.loss.invalidate()
+        per_row = model.loss.array(np.float32, (model.rows,)).copy()
+        if w is None:
+            loss = float(per_row.mean())
+        else:
+            assert not per_row[w == 0].any(), "rows with weight 0 must report loss 0"
+            loss = float((per_row * w).sum())
+        return cfg, P, ids, tgt, seg, w, loss, model_grads(model)
+    finally:
+        ctx.destroy()
+
+
+@pytest.mark.parametrize("name,staged", [("gpt_untied", False), ("gpt_tied", False),
+                                         ("gpt_packed", True)])
+def test_gpt_against_reference_fixture(dev, name, staged):
+    cfg, P, ids, tgt, seg, w, loss, got = run_case(dev, name, staged)
+    z = np.load(os.path.join(GOLD, f"{name}.npz"))
+    ref_loss = z["loss"][0]
+    assert abs(loss - ref_loss) / abs(ref_loss) < 5e-3
+    exp = expected({k: z[k] for k in z.files if k not in ("loss", "inputs_digest")}, cfg["tie"])
+    assert set(exp) == set(got)
+    bad = {k: relerr(got[k], exp[k].reshape(got[k].shape)) for k in exp}
+    assert max(bad.values()) < 3e-2, sorted(bad.items(), key=lambda kv: -kv[1])[:5]
+
+
+@pytest.mark.parametrize("name,staged", [("gpt_untied", False), ("gpt_tied", False),
+                                         ("gpt_packed", False)])
+def test_gpt_against_faithful_oracle(dev, name, staged):
+    """north-star tolerance: 1e-3 on the loss and on fp32-accumulated gradients, against
+    the oracle that rounds to fp16 at the kernels' storage points."""
+    cfg, P, ids, tgt, seg, w, loss, got = run_case(dev, name, staged)
+    ref_loss, G, _ = orc.gpt_forward_backward(P, ids, tgt, cfg["B"], cfg["T"], cfg["D"], cfg["H"],
+                                              cfg["L"], cfg["vocab"], seg=seg, weights=w,
+                                              faithful=True)
+    assert abs(loss - ref_loss) < 1e-3 * abs(ref_loss)
+    exp = expected(mg.flatten_grads(G, cfg["L"]), cfg["tie"])
+    errs = {k: relerr(got[k], exp[k].reshape(got[k].shape)) for k in exp}
+    # fp16 rounding of a value that sits on a rounding boundary can differ between the
+    # GPU's fp32 sum order and numpy's; its effect stays a few 1e-4 of the tensor's max.
+    assert max(errs.values()) < 2e-3, sorted(errs.items(), key=lambda kv: -kv[1])[:5]
+    assert np.median(list(errs.values())) < 1e-3
+
+
+def test_negative_control_seg_matters(dev):
+    """test_transformer.py:320-329: against an oracle that ignores seg the packed
+    result must be far off, i.e. the check can fail."""
+    cfg, P, ids, tgt, seg, w, loss, got = run_case(dev, "gpt_packed")
+    _, G, _ = orc.gpt_forward_backward(P, ids, tgt, cfg["B"], cfg["T"], cfg["D"], cfg["H"],
+                                       cfg["L"], cfg["vocab"], weights=w)
+    worst = max(relerr(got["pos"], G["pos"]), relerr(got["b0.qkv.W"], G["b0"]["qkv.W"]))
+    assert worst > 10 * 3e-2
+
+
+def test_eval_recording_writes_no_gradient(dev):
+    """record(backward=False) leaves gradients untouched and gives the training loss
+    (transformer.py:360-361, test_accum.py:75-136)."""
+    from vkgrad_b200.transformer import GPT, TCtx
+    cfg, P, ids, tgt, _, _ = mg.gpt_inputs("gpt_tied")
+    ctx = TCtx(dev)
+    try:
+        model = GPT(ctx, cfg["B"], cfg["T"], cfg["D"], cfg["H"], cfg["L"], cfg["vocab"], tie=True)
+        load_params(model, P)
+        idb, tgb = shared(ctx, ids), shared(ctx, tgt)
+        g_train = dev.graph("train"); model.record(idb, tgb, g_train); g_train.finish()
+        g_eval = dev.graph("eval"); model.record(idb, tgb, g_eval, backward=False); g_eval.finish()
+        g_train.submit()
+        train_loss = model.read_loss()
+        before = model.blocks[0].fc1.W.grad_numpy()
+        tgb.array(np.uint32)[:] = (tgt + 1) % cfg["vocab"]
+        g_eval.submit()
+        assert np.array_equal(before, model.blocks[0].fc1.W.grad_numpy())
+        tgb.array(np.uint32)[:] = tgt
+        g_eval.submit()
+        assert abs(model.read_loss() - train_loss) <= 1e-6 * abs(train_loss)
+    finally:
+        ctx.destroy()
+
+
+def test_loss_scale_cancels(dev):
+    """A static loss scale S multiplies every gradient by exactly S (a power of two),
+    which AdamW's gradient scale then divides out."""
+    from vkgrad_b200.transformer import GPT, TCtx
+    cfg, P, ids, tgt, _, _ = mg.gpt_inputs("gpt_tied")
+    grads = []
+    for S in (1.0, 64.0):
+        ctx = TCtx(dev)
+        try:
+            model = GPT(ctx, cfg["B"], cfg["T"], cfg["D"], cfg["H"], cfg["L"], cfg["vocab"],
+                        tie=True, loss_scale=S)
+            load_params(model, P)
+            g = dev.graph("s"); model.record(shared(ctx, ids), shared(ctx, tgt), g); g.finish()
+            g.submit()
+            grads.append(model.blocks[1].attn.qkv.W.grad_numpy() / S)
+        finally:
+            ctx.destroy()
+    assert relerr(grads[1], grads[0]) < 2e-3

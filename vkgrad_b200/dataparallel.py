@@ -1,0 +1,288 @@
+"""Data-parallel training: replicated weights, summed gradients, identical steps.
+
+Same classes as the reference's dataparallel.py -- `HostArena` (77), `Replica`
+(102: push_gradients, zero_arena, step_from_arena), `GradAccum` (153),
+`make_reduce_kernels` (28) -- and the same arithmetic: gradients of all workers
+are summed, scaled by 1/workers when they are read back (dataparallel.py:63-73,
+131-144), and every replica applies the identical AdamW step, so replicas that
+start identical stay bit-identical.
+
+What carries the sum is different.  The reference imports one host allocation
+into every device and lets each device atomicAdd its gradients into it
+(dataparallel.py:40-47).  Here there is one process per GPU and the sum is an
+NCCL all-reduce over NVLink/NVSwitch of ONE flat fp32 bucket: `Replica` re-homes
+every parameter's gradient buffer into a single contiguous allocation (params()
+order, the reference's offset table, dataparallel.py:110-117), so the dW GEMMs
+write straight into the bucket and no pack/unpack pass exists.  The 1/workers
+(and 1/loss_scale) factor is folded into AdamW's gradient read instead of a
+separate pull pass.
+
+Several logical replicas inside one process (the reference's
+examples/ddp_mnist.py) still work: without a communicator, `HostArena` is a
+device buffer the replicas of that process add into, with the reference's
+zero / push / pull sequence.
+"""
+
+import ctypes as C
+import os
+import socket
+import struct
+import time
+
+import numpy as np
+
+from ._lib import F32
+from .kernels import Elementwise
+from .vk import VkError, _check
+
+
+def make_reduce_kernels(dev):
+    """push / add / zero / pull under the reference's names (dataparallel.py:28-74).
+    One process drives one stream here, so push needs no atomics and equals add."""
+    lib, h = dev.lib, dev.handle
+    K = {}
+    add = lambda b, n, off: _check(lib.vkg_grad_add(h, b[0].dptr, b[1].dptr, n, int(off)), "grad_add")
+    K["push"] = Elementwise(dev, "grad_push", add, 2)
+    K["add"] = Elementwise(dev, "grad_add", add, 2)
+    K["zero"] = Elementwise(dev, "arena_zero", lambda b, n: _check(
+        lib.vkg_memset0(h, b[0].dptr, n * 4), "arena_zero"), 1)
+    K["pull"] = Elementwise(dev, "grad_pull", lambda b, n, off, scale: _check(
+        lib.vkg_grad_pull(h, b[0].dptr, b[1].dptr, n, int(off), float(scale)), "grad_pull"), 2)
+    return K
+
+
+# ---- communicator ---------------------------------------------------------------------
+
+def exchange_unique_id(rank, world, make_id, addr="127.0.0.1", port=29617, timeout=120.0):
+    """Rank 0 makes the 128-byte NCCL id and hands it to every other rank over TCP.
+
+    make_id is called on rank 0 only.  No torch, no files: a listener on
+    (addr, port) that serves world-1 connections."""
+    if world == 1:
+        return make_id()
+    if rank == 0:
+        uid = make_id()
+        srv = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+        srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        srv.bind((addr, port))
+        srv.listen(world)
+        srv.settimeout(timeout)
+        served = 0
+        try:
+            while served < world - 1:
+                conn, _ = srv.accept()
+                with conn:
+                    conn.sendall(struct.pack("<I", len(uid)) + uid)
+                served += 1
+        except socket.timeout:
+            raise VkError(f"rendezvous: only {served} of {world - 1} ranks connected "
+                          f"within {timeout:.0f} s")
+        finally:
+            srv.close()
+        return uid
+    deadline = time.monotonic() + timeout
+    last = None
+    while time.monotonic() < deadline:
+        try:
+            with socket.create_connection((addr, port), timeout=5.0) as s:
+                head = _recv_exact(s, 4)
+                (n,) = struct.unpack("<I", head)
+                return _recv_exact(s, n)
+        except (ConnectionRefusedError, socket.timeout, OSError) as e:
+            last = e
+            time.sleep(0.2)
+    raise VkError(f"rendezvous: rank {rank} could not reach rank 0 at {addr}:{port}: {last}")
+
+
+def _recv_exact(s, n):
+    out = b""
+    while len(out) < n:
+        chunk = s.recv(n - len(out))
+        if not chunk:
+            raise OSError("connection closed during rendezvous")
+        out += chunk
+    return out
+
+
+class Comm:
+    """An NCCL communicator bound to one Device (one process per GPU)."""
+
+    def __init__(self, dev, rank, world, unique_id):
+        self.dev, self.rank, self.world = dev, rank, world
+        uid = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        h = C.c_void_p()
+        _check(dev.lib.vkg_comm_create(dev.handle, rank, world, uid, C.byref(h)), "comm_create")
+        self.handle = h
+
+    @staticmethod
+    def make_unique_id(lib):
+        uid = (C.c_uint8 * 128)()
+        _check(lib.vkg_comm_unique_id(uid), "comm_unique_id")
+        return bytes(uid)
+
+    @classmethod
+    def from_env(cls, dev, port_offset=101):
+        """Build from RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT (torchrun's variables)."""
+        rank = int(os.environ.get("RANK", "0"))
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+        port = (int(os.environ.get("MASTER_PORT", "29500")) + port_offset) % 65536
+        uid = exchange_unique_id(rank, world, lambda: cls.make_unique_id(dev.lib), addr, port)
+        return cls(dev, rank, world, uid)
+
+    def allreduce_sum(self, buf, count, dtype=F32, offset_bytes=0):
+        _check(self.dev.lib.vkg_allreduce_sum(self.handle, buf.dptr + offset_bytes, count, dtype),
+               "allreduce")
+
+    def max_double(self, value):
+        v = C.c_double(float(value))
+        _check(self.dev.lib.vkg_comm_max_double(self.handle, C.byref(v)), "comm_max")
+        return v.value
+
+    def barrier(self):
+        _check(self.dev.lib.vkg_comm_barrier(self.handle), "barrier")
+
+    def destroy(self):
+        if self.handle:
+            self.dev.lib.vkg_comm_destroy(self.handle)
+            self.handle = None
+
+
+# ---- arena / replicas --------------------------------------------------------------------
+
+class HostArena:
+    """The flat gradient exchange buffer (dataparallel.py:77-99).
+
+    In the reference this is host memory imported by every device.  Here it is
+    device memory, allocated on first use by a replica's device, that logical
+    replicas inside one process add into; with a communicator it is not used at
+    all (the bucket is all-reduced in place)."""
+
+    def __init__(self, n_floats, alignment=4096):
+        self.n = int(n_floats)
+        # room for the 16-byte alignment padding between tensors of the flat bucket
+        self.nbytes = ((self.n * 4 + 16384 + alignment - 1) // alignment) * alignment
+        self._buffers = {}
+
+    def buffer_for(self, dev):
+        key = dev.ordinal
+        if key not in self._buffers:
+            self._buffers[key] = dev.buffer(self.nbytes, "device")
+        return self._buffers[key]
+
+    def destroy(self):
+        for b in self._buffers.values():
+            b.destroy()
+        self._buffers = {}
+
+
+def flatten_gradients(ctx, params):
+    """Re-home every p.g32 into one contiguous device buffer, in params() order.
+    Returns (bucket, offsets_in_floats, total_floats).  Must run before a step is
+    recorded: recorded launches keep the pointers they were recorded with."""
+    offs, off = [], 0
+    for p in params:
+        offs.append(off)
+        off += (p.n + 3) // 4 * 4          # keep every tensor 16-byte aligned
+    bucket = ctx.buf(max(off, 4) * 4, "device")
+    _check(ctx.dev.lib.vkg_memset0(ctx.dev.handle, bucket.dptr, bucket.size), "zero bucket")
+    for p, o in zip(params, offs):
+        old = p.g32
+        p.g32 = bucket.view(o * 4, p.n * 4)
+        if old in ctx._owned:
+            ctx._owned.remove(old)
+            old.destroy()
+    return bucket, offs, off
+
+
+class Replica:
+    """One device's copy of the model plus its part in the exchange (dataparallel.py:102-150).
+
+    build(dev) -> (ctx, model, opt, xbuf, ybuf).  With `comm`, push_gradients is an
+    all-reduce of the flat bucket; without it the replica adds into `arena`."""
+
+    def __init__(self, dev, build, arena=None, comm=None):
+        self.dev = dev
+        self.comm = comm
+        self.ctx, self.model, self.opt, self.xbuf, self.ybuf = build(dev)
+        self.K = make_reduce_kernels(dev)
+        self.params = list(self.model.params())
+        self.bucket, self.offsets, self.total = flatten_gradients(self.ctx, self.params)
+        self.arena = arena
+        self.arena_buf = None
+        if comm is None:
+            if arena is None:
+                raise VkError("Replica needs an arena (in-process replicas) or a comm (NCCL)")
+            assert self.total <= arena.nbytes // 4, \
+                f"arena too small: need {self.total}, have {arena.nbytes // 4}"
+            self.arena_buf = arena.buffer_for(dev)
+        self.loss_scale = float(getattr(self.model, "loss_scale", 1.0))
+
+    def zero_arena(self, graph=None):
+        if self.arena_buf is not None:
+            self.K["zero"]([self.arena_buf], self.total, graph=graph)
+
+    def push_gradients(self, graph=None):
+        """Contribute this replica's gradients to the sum."""
+        if self.comm is not None:
+            comm, bucket, total = self.comm, self.bucket, self.total
+            if comm.world > 1:
+                thunk = lambda: comm.allreduce_sum(bucket, total)
+                if graph is not None:
+                    graph.add(thunk, "nccl_allreduce", total * 4)
+                else:
+                    thunk()
+            return
+        self.dev.sync()
+        self.K["push"]([self.bucket, self.arena_buf], self.total, 0, graph=graph)
+
+    def record_step(self, graph, n_workers=None):
+        """Record all-reduce + AdamW after a recorded forward/backward."""
+        w = n_workers if n_workers is not None else (self.comm.world if self.comm else 1)
+        self.opt.grad_scale = 1.0 / (max(w, 1) * self.loss_scale)
+        self.push_gradients(graph=graph)
+        self.opt.record(graph)
+
+    def step_from_arena(self, lr, n_workers=1):
+        """AdamW from the summed gradient, scaled back to a mean (dataparallel.py:131-144)."""
+        scale = 1.0 / (max(n_workers, 1) * self.loss_scale)
+        if self.arena_buf is not None:
+            self.opt.grad_scale = 0.0
+            self.K["pull"]([self.arena_buf, self.bucket], self.total, 0, scale)
+        else:
+            self.opt.grad_scale = scale
+        self.opt.step(lr)
+
+    def destroy(self):
+        self.ctx.destroy()
+
+
+class GradAccum:
+    """Gradient accumulation over microbatches on one device (dataparallel.py:153-207):
+    the same sum with the workers separated in time."""
+
+    def __init__(self, ctx, params, accum=1):
+        self.ctx, self.params, self.accum = ctx, list(params), accum
+        self.K = make_reduce_kernels(ctx.dev)
+        offs, off = [], 0
+        for p in self.params:
+            offs.append(off)
+            off += p.n
+        self.offsets, self.total = offs, off
+        self.arena = ctx.buf(off * 4, "device")
+
+    def record_push(self, graph):
+        for p, o in zip(self.params, self.offsets):
+            self.K["add"]([p.g32, self.arena], p.n, o, graph=graph)
+
+    def record_zero(self, graph):
+        self.K["zero"]([self.arena], self.total, graph=graph)
+
+    def record_apply(self, graph, opt, scale=None):
+        sc = (1.0 / self.accum) if scale is None else scale
+        for p, o in zip(self.params, self.offsets):
+            self.K["pull"]([self.arena, p.g32], p.n, o, sc, graph=graph)
+        opt.record(graph)
+
+    def destroy(self):
+        pass
