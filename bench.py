@@ -1,0 +1,401 @@
+#!/usr/bin/env python3
+"""Headline benchmark: GPT-2-small-shaped full training steps (forward + backward +
+all-reduce + AdamW, fp16 operands / fp32 accumulate) on N B200s, tokens per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload gpt2-small|gpt-24l|mlp] [--gemm-trio]
+
+N > 1 is launched one process per GPU by torch.distributed.run (RANK / LOCAL_RANK /
+WORLD_SIZE / MASTER_ADDR / MASTER_PORT from the environment); ranks find each other
+over a TCP socket and exchange gradients with NCCL.  Rank 0 prints ONE JSON line.
+
+Keys beyond the base contract:
+  value     device-timed (CUDA events, max over ranks) tokens/s, inputs resident in HBM
+  e2e       wall-clock tokens/s through DataParallelStep.__call__ with pinned host
+            inputs copied up and the per-row loss copied down every step
+  roofline  all tcgen05 GEMM launches of one step, each shape timed with CUDA events
+            in this process: achieved = algorithmic FLOP / time, peak = measured
+            cuBLAS bf16 burst TFLOP/s of MEASURED_PEAKS.json
+  cpu_baseline  the CPU oracle (numpy restatement of the reference's step) on a
+            bounded sample, rank 0 only
+`--impl reference` times that CPU oracle alone with all host threads.
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, T, D, H, L, vocab)
+    "gpt2-small": (8, 1024, 768, 12, 12, 50257),
+    "gpt-24l": (4, 1024, 1024, 16, 24, 50257),
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def step_flops(B, T, D, H, L, V):
+    """Algorithmic FLOP of one step: 2*M*N*K over every matmul the reference records
+    (full T x T attention, tied head)."""
+    R, hd, Vp = B * T, D // H, (V + 15) // 16 * 16
+    per_layer = 3 * 2 * R * D * (3 * D + D + 4 * D + 4 * D)      # fwd + dW + dX of four linears
+    per_layer += 6 * 2 * (B * H) * T * T * hd                     # six batched attention matmuls
+    head = 3 * 2 * R * D * Vp
+    return L * per_layer + head
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1 + 0.2] or [r for _, r in self.rows[-3:]]
+        sm = [float(r[0]) for r in rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = set()
+        for r in rows:
+            for nm, v in zip(names, r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(rows)}
+
+
+# ---- CPU oracle arm ---------------------------------------------------------------------
+
+_CPU_PARAMS = {}
+
+
+def cpu_step_seconds(B, T, D, H, L, V, seed=0, repeats=1):
+    """One full oracle step (fwd + bwd + AdamW on every tensor) at batch B; seconds."""
+    from oracle import vkgrad_numpy as orc
+    Vp = (V + 15) // 16 * 16
+    key = (T, D, H, L, Vp, seed)
+    if key not in _CPU_PARAMS:
+        _CPU_PARAMS.clear()
+        _CPU_PARAMS[key] = orc.make_gpt_params(D, H, L, T, Vp, seed=seed, tie=True)
+    P = _CPU_PARAMS[key]
+    rng = np.random.default_rng(seed + 1)
+    ids = rng.integers(0, V, B * T).astype(np.uint32)
+    tgt = rng.integers(0, V, B * T).astype(np.uint32)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        loss, G, _ = orc.gpt_forward_backward(P, ids, tgt, B, T, D, H, L, V)
+        G["tok"] = G["tok"] + G.pop("head.W").T
+        G.pop("head.b")
+        for k, g in G.items():
+            items = g.items() if isinstance(g, dict) else [(None, g)]
+            for kk, gg in items:
+                w = P[k][kk] if kk is not None else P[k]
+                m = np.zeros_like(w)
+                out = orc.adamw_step(w, gg, m, m, 1, wd=0.01 if w.ndim == 2 else 0.0)
+                if kk is not None:
+                    P[k][kk] = out[0]
+                else:
+                    P[k] = out[0]
+        P["head.W"] = P["tok"].T
+        best = min(best, time.perf_counter() - t0)
+    return best, loss
+
+
+def cpu_sample_shape(name, budget_s, n_steps):
+    """Largest (B, T) sample of the workload whose n_steps fit the time budget."""
+    B, T, D, H, L, V = WORKLOADS[name]
+    t_probe, _ = cpu_step_seconds(1, 64, D, H, L, V)
+    per_token = t_probe / 64
+    for cand_T in (T, T // 2, T // 4, T // 8):
+        est = per_token * cand_T * (1.0 + 0.25 * cand_T / T) * n_steps
+        if est <= budget_s:
+            return 1, cand_T
+    return 1, T // 16
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    name = args.workload
+    B, T, D, H, L, V = WORKLOADS[name]
+    sb, st = cpu_sample_shape(name, 150.0, args.steps + args.warmup)
+    for _ in range(args.warmup):
+        cpu_step_seconds(sb, st, D, H, L, V)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step_seconds(sb, st, D, H, L, V)
+    dt = time.perf_counter() - t0
+    tok_s = args.steps * sb * st / dt
+    cores = os.cpu_count()
+    sample = (f"{sb}x{st} tokens per step, full {L}-layer model, fwd+bwd+AdamW in numpy "
+              f"(oracle/vkgrad_numpy.py restating the reference's np_model)")
+    line = {
+        "impl": "reference", "metric": "gpt_train_tokens_per_s", "value": tok_s, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "tokens_per_step": sb * st, "parallelism": "cpu"},
+        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- GPU arm ---------------------------------------------------------------------------------
+
+def gemm_shape_table(B, T, D, H, L, V):
+    """(count per step, kwargs for kernels.gemm) for every distinct GEMM of the step."""
+    R, hd, Vp = B * T, D // H, (V + 15) // 16 * 16
+    t = []
+    for (i, o) in ((D, 3 * D), (D, D), (D, 4 * D), (4 * D, D)):
+        t.append((L, dict(m=R, n=o, k=i, ta=False, tb=False)))          # Y  = X W
+        t.append((L, dict(m=i, n=o, k=R, ta=True, tb=False)))           # dW = X^T dY
+        t.append((L, dict(m=R, n=i, k=o, ta=False, tb=True)))           # dX = dY W^T
+    nb = B * H
+    t.append((2 * L, dict(m=T, n=T, k=hd, ta=False, tb=True, nb=nb)))   # QK^T, dP
+    t.append((2 * L, dict(m=T, n=hd, k=T, ta=False, tb=False, nb=nb)))  # PV, dQ
+    t.append((2 * L, dict(m=T, n=hd, k=T, ta=True, tb=False, nb=nb)))   # dV, dK
+    t.append((1, dict(m=R, n=Vp, k=D, ta=False, tb=True)))              # logits
+    t.append((1, dict(m=R, n=D, k=Vp, ta=False, tb=False)))             # dh
+    t.append((1, dict(m=Vp, n=D, k=R, ta=True, tb=False)))              # dtok (head share)
+    return t
+
+
+def time_gemm_shapes(dev, table):
+    """CUDA-event time of each shape (back-to-back launches on the device stream)."""
+    from vkgrad_b200.kernels import gemm
+    total_t, total_f, rows = 0.0, 0.0, []
+    for count, s in table:
+        nb = s.get("nb", 1)
+        m, n, k = s["m"], s["n"], s["k"]
+        a = dev.buffer(nb * m * k * 2, "device")
+        b = dev.buffer(nb * k * n * 2, "device")
+        c = dev.buffer(nb * m * n * 4, "device")
+        kw = dict(trans_a=s["ta"], trans_b=s["tb"], nb0=nb, sa=(m * k, 0), sb=(k * n, 0),
+                  sc=(m * n, 0))
+        gemm(dev, a, b, c, m, n, k, repeat=2, **kw)
+        reps = 10
+        t = min(gemm(dev, a, b, c, m, n, k, repeat=reps, **kw) / reps for _ in range(3))
+        fl = 2.0 * m * n * k * nb
+        rows.append({"m": m, "n": n, "k": k, "ta": int(s["ta"]), "tb": int(s["tb"]), "batch": nb,
+                     "count": count, "us": t * 1e6, "tflops": fl / t / 1e12})
+        total_t += count * t
+        total_f += count * fl
+        for x in (a, b, c):
+            x.destroy()
+    return total_f, total_t, rows
+
+
+def run_gpu_arm(args):
+    from vkgrad_b200 import vk
+    from vkgrad_b200.autograd import AdamW
+    from vkgrad_b200.dataparallel import Comm, DataParallelStep, Replica
+    from vkgrad_b200.transformer import GPT, TCtx
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 needs one process per GPU: launch with "
+                             "python -m torch.distributed.run --nproc-per-node N bench.py ...")
+    name = args.workload
+    B, T, D, H, L, V = WORKLOADS[name]
+    R = B * T
+    peaks, peak_src = load_peaks()
+
+    dev = vk.Device(local)
+    comm = Comm.from_env(dev) if world > 1 else None
+    loss_scale = float(args.loss_scale)
+
+    def build(d):
+        ctx = TCtx(d)
+        model = GPT(ctx, B, T, D, H, L, V, tie=True, loss_scale=loss_scale)
+        rng = np.random.default_rng(0)          # identical weights on every rank
+        for p in model.params():
+            if p.name.endswith(".g"):
+                p.set(np.ones(p.shape, np.float32))
+            elif len(p.shape) == 1:
+                p.set(np.zeros(p.shape, np.float32))
+            else:
+                p.set((rng.standard_normal(p.shape) * 0.02).astype(np.float32))
+        opt = AdamW(ctx, model.params(), lr=6e-4, wd=0.01)
+        return ctx, model, opt, ctx.buf(R * 4, "shared"), ctx.buf(R * 4, "shared")
+
+    rep = Replica(dev, build, comm=comm)
+    ctx, model = rep.ctx, rep.model
+    ids_dev, tgt_dev = ctx.buf(R * 4), ctx.buf(R * 4)
+    ids_host, tgt_host = rep.xbuf, rep.ybuf
+    rng = np.random.default_rng(1000 + rank)    # each rank its own token stream
+    batches = [(rng.integers(0, V, R).astype(np.uint32), rng.integers(0, V, R).astype(np.uint32))
+               for _ in range(4)]
+    ids_host.array(np.uint32)[:] = batches[0][0]
+    tgt_host.array(np.uint32)[:] = batches[0][1]
+    dev.copy(ids_host, ids_dev, R * 4)
+    dev.copy(tgt_host, tgt_dev, R * 4)
+
+    core = DataParallelStep(rep, ids_dev, tgt_dev, name="step_resident")
+    e2e = DataParallelStep(rep, ids_dev, tgt_dev, host_ids=ids_host, host_targets=tgt_host,
+                           name="step_e2e")
+    lr = 6e-4
+
+    def barrier():
+        dev.sync()
+        if comm is not None:
+            comm.barrier()
+        dev.sync()
+
+    # ---- device-timed: K steps back to back, inputs resident -------------------------------
+    for _ in range(args.warmup):
+        core.enqueue(lr)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    t_wall0 = time.perf_counter()
+    import ctypes as C
+    vk._check(dev.lib.vkg_timer_begin(dev.handle), "timer")
+    for _ in range(args.steps):
+        core.enqueue(lr)
+    sec = C.c_double(0.0)
+    vk._check(dev.lib.vkg_timer_end(dev.handle, C.byref(sec)), "timer")
+    barrier()
+    t_wall1 = time.perf_counter()
+    dt = comm.max_double(sec.value) if comm is not None else sec.value
+    loss_core = model.read_loss()
+
+    # ---- end to end: host inputs in, loss out, every step ----------------------------------
+    for i in range(max(1, min(args.warmup, 3))):
+        e2e(lr)
+    barrier()
+    t0 = time.perf_counter()
+    last_loss = None
+    for i in range(args.steps):
+        bi, bt = batches[i % len(batches)]
+        ids_host.array(np.uint32)[:] = bi
+        tgt_host.array(np.uint32)[:] = bt
+        last_loss, _ = e2e(lr)
+    dev.sync()
+    dt_e2e = time.perf_counter() - t0
+    t_wall2 = time.perf_counter()
+    if comm is not None:
+        dt_e2e = comm.max_double(dt_e2e)
+    clocks = sampler.stop(t_wall0, t_wall2) if sampler else None
+
+    # replicas must still be bit-identical (the reference's drift == 0 claim)
+    drift = 0.0
+    if comm is not None:
+        w = model.blocks[0].fc1.W.numpy().astype(np.float64)
+        chk = float(np.abs(w).sum())
+        drift = comm.max_double(chk) - (-comm.max_double(-chk))
+
+    tokens_step = R * world
+    line = None
+    if rank == 0:
+        flops_total, gemm_t, rows = time_gemm_shapes(dev, gemm_shape_table(B, T, D, H, L, V))
+        achieved = flops_total / gemm_t / 1e12
+        peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        alg = step_flops(B, T, D, H, L, V)
+        cpu = None
+        if not args.no_cpu:
+            sb, st = cpu_sample_shape(name, 25.0, 1)
+            t_cpu, _ = cpu_step_seconds(sb, st, D, H, L, V)
+            cpu = {"value": sb * st / t_cpu, "unit": "tokens/s", "cores": os.cpu_count(),
+                   "kind": "port",
+                   "sample": f"one step of {sb}x{st} tokens, full {L}-layer model, numpy oracle"}
+        ms = dt / args.steps * 1e3
+        line = {
+            "metric": "gpt_train_tokens_per_s", "value": tokens_step * args.steps / dt,
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": name, "layers": L, "d_model": D, "heads": H, "ctx": T,
+                       "vocab": V, "tied": True, "batch_per_gpu": f"{B}x{T}",
+                       "global_batch_tokens": tokens_step, "parallelism": f"dp{world}",
+                       "loss_scale": loss_scale, "optimizer": "AdamW",
+                       "l2": "working set per step >> 126 MB L2 (no flush needed)"},
+            "e2e": {"value": tokens_step * args.steps / dt_e2e, "unit": "tokens/s",
+                    "h2d_bytes_per_step": 2 * R * 4, "d2h_bytes_per_step": R * 4,
+                    "ms_per_step": dt_e2e / args.steps * 1e3},
+            "gpu_launches": core.n_kernels * args.steps,
+            "launches_per_step": core.n_kernels,
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "gemm_tcgen05_kernel (all GEMM launches of one step)",
+                         "gemm_ms_per_step": gemm_t * 1e3},
+            "step_tensor_frac": alg / (dt / args.steps) / 1e12 / peak,
+            "algorithmic_tflop_per_step": alg / 1e12,
+            "cpu_baseline": cpu,
+            "loss": {"resident": loss_core, "e2e": last_loss},
+            "replica_drift": drift,
+        }
+        if args.gemm_trio:
+            line["gemm_shapes"] = rows
+    barrier()
+    if comm is not None:
+        comm.destroy()
+    rep.destroy()
+    dev.destroy()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gpt2-small", choices=sorted(WORKLOADS))
+    ap.add_argument("--loss-scale", type=float, default=4096.0)
+    ap.add_argument("--gemm-trio", action="store_true", help="add per-shape GEMM timings")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle timing")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

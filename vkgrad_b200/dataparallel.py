@@ -199,7 +199,8 @@ class Replica:
     """One device's copy of the model plus its part in the exchange (dataparallel.py:102-150).
 
     build(dev) -> (ctx, model, opt, xbuf, ybuf).  With `comm`, push_gradients is an
-    all-reduce of the flat bucket; without it the replica adds into `arena`."""
+    all-reduce of the flat bucket; with `arena` the replica adds into it; with
+    neither it is a single worker."""
 
     def __init__(self, dev, build, arena=None, comm=None):
         self.dev = dev
@@ -210,9 +211,7 @@ class Replica:
         self.bucket, self.offsets, self.total = flatten_gradients(self.ctx, self.params)
         self.arena = arena
         self.arena_buf = None
-        if comm is None:
-            if arena is None:
-                raise VkError("Replica needs an arena (in-process replicas) or a comm (NCCL)")
+        if comm is None and arena is not None:
             assert self.total <= arena.nbytes // 4, \
                 f"arena too small: need {self.total}, have {arena.nbytes // 4}"
             self.arena_buf = arena.buffer_for(dev)
@@ -233,6 +232,8 @@ class Replica:
                 else:
                     thunk()
             return
+        if self.arena_buf is None:
+            return                      # a single worker: its gradient is the sum
         self.dev.sync()
         self.K["push"]([self.bucket, self.arena_buf], self.total, 0, graph=graph)
 
@@ -255,6 +256,48 @@ class Replica:
 
     def destroy(self):
         self.ctx.destroy()
+
+
+class DataParallelStep:
+    """One recorded data-parallel training step: (inputs up) -> forward/backward ->
+    all-reduce of the flat gradient bucket -> AdamW -> (loss down).
+
+    The multi-GPU counterpart of autograd.TrainStep; with one worker it is the same
+    step without the all-reduce.  host_ids/host_targets, when given, are pinned
+    host buffers copied to the device inside the step, so per-step data written by
+    the caller is picked up by every replay.
+    """
+
+    def __init__(self, replica, ids_dev, targets_dev, host_ids=None, host_targets=None,
+                 name="dp_step", **record_kwargs):
+        self.replica = replica
+        self.model, self.opt = replica.model, replica.opt
+        dev = replica.dev
+        lib, h = dev.lib, dev.handle
+        self.graph = dev.graph(name)
+        if host_ids is not None:
+            pairs = [(ids_dev, host_ids), (targets_dev, host_targets)]
+
+            def upload():
+                for d, s in pairs:
+                    _check(lib.vkg_copy_h2d_async(h, d.dptr, s.hptr, min(d.size, s.size)), "h2d")
+            self.graph.add(upload, "h2d_inputs", sum(min(d.size, s.size) for d, s in pairs))
+            self.graph.n_dispatch -= 1
+        self.model.record(ids_dev, targets_dev, self.graph, **record_kwargs)
+        replica.record_step(self.graph)
+        self.graph.finish()
+        self.n_dispatch = self.graph.n_dispatch
+        self.n_kernels = self.graph.n_kernels
+
+    def __call__(self, lr=None):
+        self.opt.advance(lr)
+        dt = self.graph.submit()
+        return self.model.read_loss(), dt
+
+    def enqueue(self, lr=None):
+        """Advance the schedule and launch without waiting (pair with dev.sync())."""
+        self.opt.advance(lr)
+        self.graph.submit_async()
 
 
 class GradAccum:
