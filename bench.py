@@ -303,6 +303,18 @@ def run_gpu_arm(args):
     dt = comm.max_double(sec.value) if comm is not None else sec.value
     loss_core = model.read_loss()
 
+    if args.profile:
+        # launch-list runs: only the resident steps above, nothing else on the device
+        if rank == 0:
+            print(json.dumps({"profile_only": True, "ms_per_step": dt / args.steps * 1e3,
+                              "launches_per_step": core.n_kernels}), flush=True)
+        barrier()
+        if comm is not None:
+            comm.destroy()
+        rep.destroy()
+        dev.destroy()
+        return
+
     # ---- end to end: host inputs in, loss out, every step ----------------------------------
     for i in range(max(1, min(args.warmup, 3))):
         e2e(lr)
@@ -390,6 +402,8 @@ def main():
     ap.add_argument("--loss-scale", type=float, default=4096.0)
     ap.add_argument("--gemm-trio", action="store_true", help="add per-shape GEMM timings")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle timing")
+    ap.add_argument("--profile", action="store_true",
+                    help="run only the device-resident steps (for an ncu launch list)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -438,17 +438,121 @@ k_layernorm_bwd(const float* __restrict__ dy, const float* __restrict__ x,
   }
 }
 
-__global__ void k_ln_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma,
-                                 float* __restrict__ dbeta, int D, int nblocks) {
-  int d = blockIdx.x * blockDim.x + threadIdx.x;
-  if (d >= D) return;
-  float g = 0.f, b = 0.f;
-  for (int k = 0; k < nblocks; ++k) {
-    g += scratch[(size_t)k * 2 * D + d];
-    b += scratch[(size_t)k * 2 * D + D + d];
+constexpr int LNF_SLICES = 8;
+
+// Fixed-order reduction of the per-block partials: 32 columns x 8 slices per CTA,
+// each slice adds every 8th block, then the slices are added in order.
+__global__ void __launch_bounds__(32 * LNF_SLICES)
+k_ln_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma,
+                 float* __restrict__ dbeta, int D, int nblocks) {
+  __shared__ float red[LNF_SLICES][32];
+  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;  // column in [0, 2D): gamma part then beta part
+  float s = 0.f;
+  if (c < 2 * D)
+    for (int k = slice; k < nblocks; k += LNF_SLICES) s += scratch[(size_t)k * 2 * D + c];
+  red[slice][lane] = s;
+  __syncthreads();
+  if (slice == 0 && c < 2 * D) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < LNF_SLICES; ++k) t += red[k][lane];
+    if (c < D) dgamma[c] = t; else dbeta[c - D] = t;
   }
-  dgamma[d] = g;
-  dbeta[d] = b;
+}
+
+// Vectorised backward for D = 128 * NV: a warp owns a row, each lane holds NV float4
+// of x and dy in registers, and keeps its columns' dgamma/dbeta partial sums in
+// registers across all the rows it visits.
+constexpr int LNV_WARPS = 8;
+
+template <int NV>
+__global__ void __launch_bounds__(LNV_WARPS * 32)
+k_layernorm_bwd_vec(const float* __restrict__ dy, const float* __restrict__ x,
+                    const float* __restrict__ gamma, const float* __restrict__ mu,
+                    const float* __restrict__ rstd, const float* __restrict__ dres,
+                    float* __restrict__ dx, __half* __restrict__ dx16,
+                    float* __restrict__ scratch, int rows) {
+  constexpr int D = NV * 128;
+  __shared__ float red[LNV_WARPS][32 * 4 + 4];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float4 g[NV], ag[NV], ab[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    g[i] = *reinterpret_cast<const float4*>(gamma + (i * 32 + lane) * 4);
+    ag[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const float inv = 1.0f / (float)D;
+  const int warps_total = gridDim.x * LNV_WARPS;
+  for (int row = blockIdx.x * LNV_WARPS + warp; row < rows; row += warps_total) {
+    const size_t base = (size_t)row * D;
+    const float m = mu[row], r = rstd[row];
+    float4 xv[NV], dv[NV];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      xv[i] = *reinterpret_cast<const float4*>(x + base + (i * 32 + lane) * 4);
+      dv[i] = *reinterpret_cast<const float4*>(dy + base + (i * 32 + lane) * 4);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      xv[i].x = (xv[i].x - m) * r; xv[i].y = (xv[i].y - m) * r;
+      xv[i].z = (xv[i].z - m) * r; xv[i].w = (xv[i].w - m) * r;
+      float a0 = dv[i].x * g[i].x, a1 = dv[i].y * g[i].y, a2 = dv[i].z * g[i].z, a3 = dv[i].w * g[i].w;
+      s1 += a0 + a1 + a2 + a3;
+      s2 += a0 * xv[i].x + a1 * xv[i].y + a2 * xv[i].z + a3 * xv[i].w;
+      ag[i].x += dv[i].x * xv[i].x; ag[i].y += dv[i].y * xv[i].y;
+      ag[i].z += dv[i].z * xv[i].z; ag[i].w += dv[i].w * xv[i].w;
+      ab[i].x += dv[i].x; ab[i].y += dv[i].y; ab[i].z += dv[i].z; ab[i].w += dv[i].w;
+    }
+    s1 = warp_sum(s1) * inv;
+    s2 = warp_sum(s2) * inv;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float4 o;
+      o.x = r * (dv[i].x * g[i].x - s1 - xv[i].x * s2);
+      o.y = r * (dv[i].y * g[i].y - s1 - xv[i].y * s2);
+      o.z = r * (dv[i].z * g[i].z - s1 - xv[i].z * s2);
+      o.w = r * (dv[i].w * g[i].w - s1 - xv[i].w * s2);
+      const size_t off = base + (i * 32 + lane) * 4;
+      if (dres) {
+        float4 d = *reinterpret_cast<const float4*>(dres + off);
+        o.x += d.x; o.y += d.y; o.z += d.z; o.w += d.w;
+      }
+      if (dx) *reinterpret_cast<float4*>(dx + off) = o;
+      if (dx16) {
+        __half2 a = __floats2half2_rn(o.x, o.y), b = __floats2half2_rn(o.z, o.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a);
+        u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(dx16 + off) = u;
+      }
+    }
+  }
+  if (scratch) {
+    // add the CTA's warps in a fixed order, one 128-column group at a time
+    float* out = scratch + (size_t)blockIdx.x * 2 * D;
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float4 v = part == 0 ? ag[i] : ab[i];
+        __syncthreads();
+        *reinterpret_cast<float4*>(&red[warp][lane * 4]) = v;
+        __syncthreads();
+        if (warp == 0) {
+          float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int w = 0; w < LNV_WARPS; ++w) {
+            float4 u = *reinterpret_cast<const float4*>(&red[w][lane * 4]);
+            t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+          }
+          *reinterpret_cast<float4*>(out + part * D + (i * 32 + lane) * 4) = t;
+        }
+      }
+    }
+  }
 }
 
 // ---- attention softmax ---------------------------------------------------------------------
@@ -758,7 +862,7 @@ extern "C" int vkg_layernorm(vkg_device* dev, const float* x, const float* gamma
 
 static int ln_bwd_blocks(int rows) {
   int b = (rows + LNB_WARPS - 1) / LNB_WARPS;  // at least one row per warp
-  if (b > 592) b = 592;
+  if (b > 296) b = 296;
   if (b < 1) b = 1;
   return b;
 }
@@ -766,6 +870,14 @@ static int ln_bwd_blocks(int rows) {
 extern "C" int64_t vkg_layernorm_bwd_scratch_floats(int rows, int D) {
   if (rows <= 0 || D <= 0) return 0;
   return (int64_t)ln_bwd_blocks(rows) * 2 * D;
+}
+
+template <int NV>
+static void launch_ln_bwd_vec(vkg_device* dev, int nblocks, const float* dy, const float* x,
+                              const float* gamma, const float* mu, const float* rstd,
+                              const float* dres, float* dx, void* dx16, float* scratch, int rows) {
+  k_layernorm_bwd_vec<NV><<<nblocks, LNV_WARPS * 32, 0, dev->stream>>>(
+      dy, x, gamma, mu, rstd, dres, dx, (__half*)dx16, scratch, rows);
 }
 
 extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* x, const float* gamma,
@@ -777,16 +889,39 @@ extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* 
   const bool fused = dgamma != nullptr || dbeta != nullptr;
   if (fused) VKG_REQUIRE(dgamma && dbeta && scratch, "layernorm_bwd: dgamma, dbeta and scratch go together");
   int nblocks = ln_bwd_blocks(rows);
-  int rpb = (rows + nblocks - 1) / nblocks;
-  nblocks = (rows + rpb - 1) / rpb;
-  size_t smem = fused ? (size_t)LNB_WARPS * 2 * D * sizeof(float) : 0;
-  VKG_REQUIRE(smem <= 48 * 1024, "layernorm_bwd: fused parameter sums support D <= %d", 48 * 1024 / (LNB_WARPS * 8));
-  k_layernorm_bwd<<<nblocks, LNB_WARPS * 32, smem, dev->stream>>>(
-      dy, x, gamma, mu, rstd, dres, dx, (__half*)dx16, (__half*)dyxh16, (__half*)dy16,
-      fused ? scratch : nullptr, rows, D, rpb);
-  if (vkg_check_launch("layernorm_bwd")) return 1;
+  const bool aligned = ((((uintptr_t)dy | (uintptr_t)x | (uintptr_t)gamma | (uintptr_t)dres |
+                          (uintptr_t)dx | (uintptr_t)scratch) & 15) == 0) && (((uintptr_t)dx16 & 7) == 0);
+  if (D % 128 == 0 && D <= 1024 && !dyxh16 && !dy16 && aligned) {
+    // register-resident rows; every CTA writes its partial sums (possibly zero)
+    int nb = (rows + LNV_WARPS - 1) / LNV_WARPS;
+    if (nb > nblocks) nb = nblocks;
+    float* sc = fused ? scratch : nullptr;
+    switch (D / 128) {
+      case 1: launch_ln_bwd_vec<1>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
+      case 2: launch_ln_bwd_vec<2>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
+      case 3: launch_ln_bwd_vec<3>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
+      case 4: launch_ln_bwd_vec<4>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
+      case 5: launch_ln_bwd_vec<5>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
+      case 6: launch_ln_bwd_vec<6>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
+      case 7: launch_ln_bwd_vec<7>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
+      default: launch_ln_bwd_vec<8>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
+    }
+    if (vkg_check_launch("layernorm_bwd_vec")) return 1;
+    nblocks = nb;
+  } else {
+    int rpb = (rows + nblocks - 1) / nblocks;
+    nblocks = (rows + rpb - 1) / rpb;
+    size_t smem = fused ? (size_t)LNB_WARPS * 2 * D * sizeof(float) : 0;
+    VKG_REQUIRE(smem <= 48 * 1024, "layernorm_bwd: fused parameter sums support D <= %d",
+                48 * 1024 / (LNB_WARPS * 8));
+    k_layernorm_bwd<<<nblocks, LNB_WARPS * 32, smem, dev->stream>>>(
+        dy, x, gamma, mu, rstd, dres, dx, (__half*)dx16, (__half*)dyxh16, (__half*)dy16,
+        fused ? scratch : nullptr, rows, D, rpb);
+    if (vkg_check_launch("layernorm_bwd")) return 1;
+  }
   if (fused) {
-    k_ln_param_final<<<vkg_blocks(D, 128), 128, 0, dev->stream>>>(scratch, dgamma, dbeta, D, nblocks);
+    k_ln_param_final<<<(2 * D + 31) / 32, 32 * LNF_SLICES, 0, dev->stream>>>(scratch, dgamma, dbeta, D,
+                                                                             nblocks);
     return vkg_check_launch("ln_param_final");
   }
   return 0;
