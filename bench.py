@@ -227,6 +227,27 @@ def time_gemm_shapes(dev, table):
     return total_f, total_t, rows
 
 
+def run_single_gemm(args):
+    """--gemm M,N,K,ta,tb,batch[,c16]: one GEMM shape, `steps` launches; for ncu captures."""
+    from vkgrad_b200 import vk
+    from vkgrad_b200._lib import F16, F32
+    from vkgrad_b200.kernels import gemm
+    vals = [int(x) for x in args.gemm.split(",")]
+    m, n, k, ta, tb, nb = vals[:6]
+    c16 = len(vals) > 6 and vals[6]
+    dev = vk.Device(0)
+    a = dev.buffer(nb * m * k * 2, "device")
+    b = dev.buffer(nb * k * n * 2, "device")
+    c = dev.buffer(nb * m * n * 4, "device")
+    kw = dict(trans_a=bool(ta), trans_b=bool(tb), nb0=nb, sa=(m * k, 0), sb=(k * n, 0),
+              sc=(m * n, 0), c_dtype=F16 if c16 else F32, tile_n=args.tile_n)
+    gemm(dev, a, b, c, m, n, k, repeat=max(args.warmup, 1), **kw)
+    t = gemm(dev, a, b, c, m, n, k, repeat=args.steps, **kw) / args.steps
+    print(json.dumps({"gemm": args.gemm, "us": t * 1e6,
+                      "tflops": 2.0 * m * n * k * nb / t / 1e12}), flush=True)
+    dev.destroy()
+
+
 def run_gpu_arm(args):
     from vkgrad_b200 import vk
     from vkgrad_b200.autograd import AdamW
@@ -404,8 +425,13 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle timing")
     ap.add_argument("--profile", action="store_true",
                     help="run only the device-resident steps (for an ncu launch list)")
+    ap.add_argument("--gemm", default=None,
+                    help="M,N,K,ta,tb,batch[,c16]: time one GEMM shape instead of the step")
+    ap.add_argument("--tile-n", type=int, default=0)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.gemm:
+        run_single_gemm(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

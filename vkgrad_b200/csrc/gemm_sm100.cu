@@ -4,10 +4,12 @@
 // overlaps the main loop of tile i+1) -> tcgen05.ld epilogue with the fused
 // bias / activation / activation-derivative / residual / narrowing.
 //
-// One persistent CTA per SM, 192 threads:
+// One persistent CTA per SM, 320 threads:
 //   warp 0      TMA producer (one lane)
 //   warp 1      TMEM allocation + MMA issue (one lane)
-//   warps 2..5  epilogue; warp w owns TMEM lanes 32*(w%4) .. +31
+//   warps 2..9  epilogue; warp w reads TMEM lanes 32*(w%4) .. +31 and takes every
+//               other 32-column chunk.  The epilogue is instruction-issue bound, so
+//               it gets two warps per scheduler and a compile-time feature mask.
 //
 // Transposed operands are never materialised (the reference makes the same
 // point for its cooperative-matrix loads, kernels.py:45-49): "A stored K x M"
@@ -26,11 +28,14 @@ constexpr int BK = 64;             // K elements per stage = 128 bytes of f16 = 
 constexpr int UMMA_K = 16;         // K per tcgen05.mma.kind::f16
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int MAX_STAGES = 8;
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;       // two per TMEM lane quarter, each takes alternate 32-column chunks
+constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int TMEM_COLS = 512;     // whole TMEM: two 256-column accumulators
 constexpr int ACC_COLS = 256;
 constexpr int RING_BYTES = 196608; // shared-memory ring budget
-constexpr int SMEM_BYTES = RING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;  // one 32x32 fp32 chunk per epilogue warp (XOR-swizzled)
+constexpr int SMEM_BYTES = RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024 /*align slack*/ +
+                           256 /*barriers*/;
 constexpr int GROUP_M = 8;         // m-tiles per rasterisation band
 constexpr long long WAIT_BUDGET_CYCLES = 2000000000ll;  // ~1 s
 
@@ -178,100 +183,109 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int t) {
   return c;
 }
 
-// Eight consecutive columns of one row through the fused epilogue.
-__device__ __forceinline__ void epilogue8(const GemmParams& p, const uint32_t* acc, long long off,
-                                          int col, bool vec) {
-  float v[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[j]) * p.alpha;
-  if (p.bias) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] += __ldg(p.bias + col + j);
-  }
-  if (p.pre) {
-    if (vec) {
-      *reinterpret_cast<float4*>(p.pre + off) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(p.pre + off + 4) = make_float4(v[4], v[5], v[6], v[7]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) p.pre[off + j] = v[j];
-    }
-  }
-  if (p.act) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = vkg_act(v[j], p.act);
-  }
-  if (p.dact_z) {
-    float z[8];
-    if (vec) {
-      float4 a = *reinterpret_cast<const float4*>(p.dact_z + off);
-      float4 b = *reinterpret_cast<const float4*>(p.dact_z + off + 4);
-      z[0] = a.x; z[1] = a.y; z[2] = a.z; z[3] = a.w;
-      z[4] = b.x; z[5] = b.y; z[6] = b.z; z[7] = b.w;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) z[j] = p.dact_z[off + j];
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] *= vkg_dact(z[j], p.dact);
-  }
-  if (p.residual) {
-    if (vec) {
-      float4 a = *reinterpret_cast<const float4*>(p.residual + off);
-      float4 b = *reinterpret_cast<const float4*>(p.residual + off + 4);
-      v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
-      v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] += p.residual[off + j];
-    }
-  }
-  if (p.c_dtype == VKG_F32) {
-    float* c = reinterpret_cast<float*>(p.C) + off;
-    if (vec) {
-      *reinterpret_cast<float4*>(c) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(c + 4) = make_float4(v[4], v[5], v[6], v[7]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) c[j] = v[j];
-    }
-  } else if (p.c_dtype == VKG_F16) {
-    __half* c = reinterpret_cast<__half*>(p.C) + off;
-    if (vec) {
-      __half2 h[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-      *reinterpret_cast<uint4*>(c) = *reinterpret_cast<uint4*>(h);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) c[j] = __float2half_rn(v[j]);
-    }
+// Compile-time epilogue feature mask.  E_GENERIC reads every flag (and the vector
+// alignment flag) at run time; the specialised masks assume 16-byte aligned operands.
+enum : int {
+  E_BIAS = 1, E_PRE = 2, E_ACT = 4, E_DACT = 8, E_RES = 16, E_C2 = 32, E_F16 = 64, E_BF16 = 128,
+  E_GENERIC = 1 << 20
+};
+
+template <typename T2, typename T>
+__device__ __forceinline__ void store4_16(T* c, const float* v, bool vec);
+
+template <>
+__device__ __forceinline__ void store4_16<__half2, __half>(__half* c, const float* v, bool vec) {
+  if (vec) {
+    __half2 h[2] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3])};
+    *reinterpret_cast<uint2*>(c) = *reinterpret_cast<uint2*>(h);
   } else {
-    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
-    if (vec) {
-      __nv_bfloat162 h[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-      *reinterpret_cast<uint4*>(c) = *reinterpret_cast<uint4*>(h);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) c[j] = __float2bfloat16_rn(v[j]);
-    }
-  }
-  if (p.C2) {
-    __half* c = reinterpret_cast<__half*>(p.C2) + off;
-    if (vec) {
-      __half2 h[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-      *reinterpret_cast<uint4*>(c) = *reinterpret_cast<uint4*>(h);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) c[j] = __float2half_rn(v[j]);
-    }
+    for (int j = 0; j < 4; ++j) c[j] = __float2half_rn(v[j]);
   }
 }
 
+template <>
+__device__ __forceinline__ void store4_16<__nv_bfloat162, __nv_bfloat16>(__nv_bfloat16* c,
+                                                                         const float* v, bool vec) {
+  if (vec) {
+    __nv_bfloat162 h[2] = {__floats2bfloat162_rn(v[0], v[1]), __floats2bfloat162_rn(v[2], v[3])};
+    *reinterpret_cast<uint2*>(c) = *reinterpret_cast<uint2*>(h);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+
+// Four consecutive columns of one row through the fused epilogue.  Called in the
+// coalesced layout: the 8 lanes of a quarter-warp cover 32 consecutive columns of
+// one row, so every global access of the warp is four full 128-byte rows.
+template <int MODE>
+__device__ __forceinline__ void epilogue4(const GemmParams& p, float4 a, long long off, int col) {
+  constexpr bool G = (MODE & E_GENERIC) != 0;
+  const bool vec = G ? (p.vec_ok != 0) : true;
+  const bool has_bias = G ? (p.bias != nullptr) : (MODE & E_BIAS) != 0;
+  const bool has_pre = G ? (p.pre != nullptr) : (MODE & E_PRE) != 0;
+  const bool has_act = G ? (p.act != 0) : (MODE & E_ACT) != 0;
+  const bool has_dact = G ? (p.dact_z != nullptr) : (MODE & E_DACT) != 0;
+  const bool has_res = G ? (p.residual != nullptr) : (MODE & E_RES) != 0;
+  const bool has_c2 = G ? (p.C2 != nullptr) : (MODE & E_C2) != 0;
+  const int c_dtype = G ? p.c_dtype : ((MODE & E_F16) ? VKG_F16 : (MODE & E_BF16) ? VKG_BF16 : VKG_F32);
+  float v[4] = {a.x * p.alpha, a.y * p.alpha, a.z * p.alpha, a.w * p.alpha};
+  if (has_bias) {
+    const float4 b = vec ? __ldg(reinterpret_cast<const float4*>(p.bias + col))
+                         : make_float4(p.bias[col], p.bias[col + 1], p.bias[col + 2], p.bias[col + 3]);
+    v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
+  }
+  if (has_pre) {
+    if (vec) {
+      *reinterpret_cast<float4*>(p.pre + off) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) p.pre[off + j] = v[j];
+    }
+  }
+  if (has_act) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = vkg_act(v[j], p.act);
+  }
+  if (has_dact) {
+    float z[4];
+    if (vec) {
+      const float4 t = *reinterpret_cast<const float4*>(p.dact_z + off);
+      z[0] = t.x; z[1] = t.y; z[2] = t.z; z[3] = t.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) z[j] = p.dact_z[off + j];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] *= vkg_dact(z[j], p.dact);
+  }
+  if (has_res) {
+    if (vec) {
+      const float4 t = *reinterpret_cast<const float4*>(p.residual + off);
+      v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] += p.residual[off + j];
+    }
+  }
+  if (c_dtype == VKG_F32) {
+    float* c = reinterpret_cast<float*>(p.C) + off;
+    if (vec) {
+      *reinterpret_cast<float4*>(c) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) c[j] = v[j];
+    }
+  } else if (c_dtype == VKG_F16) {
+    store4_16<__half2, __half>(reinterpret_cast<__half*>(p.C) + off, v, vec);
+  } else {
+    store4_16<__nv_bfloat162, __nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(p.C) + off, v, vec);
+  }
+  if (has_c2) store4_16<__half2, __half>(reinterpret_cast<__half*>(p.C2) + off, v, vec);
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmParams p) {
@@ -281,9 +295,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t b_stage_bytes = (uint32_t)p.bn * 128u;
   const uint32_t stage_bytes = A_STAGE_BYTES + b_stage_bytes;
-  // Barrier block sits after the ring.
-  uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + RING_BYTES);
-  const uint32_t bar_base = base + RING_BYTES;
+  // Epilogue staging (one swizzled 32x32 fp32 chunk per epilogue warp), then the barrier block.
+  float* epi_stage = reinterpret_cast<float*>(gen_base + RING_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES);
+  const uint32_t bar_base = base + RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
   // full[s] at +8s, empty[s] at +64+8s, tmem_full[a] at +128+8a, tmem_empty[a] at +144+8a
   const uint32_t full0 = bar_base, empty0 = bar_base + 64, tfull0 = bar_base + 128,
                  tempty0 = bar_base + 144;
@@ -300,7 +315,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull0 + 8 * a, 1);
-      mbar_init(tempty0 + 8 * a, 4);
+      mbar_init(tempty0 + 8 * a, EPI_WARPS);
     }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -405,24 +420,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       TileCoord tc = tile_coord(p, t);
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.err, 0x400u + acc)) break;
       tcgen05_fence_after();
-      const int row = tc.m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
-      const long long row_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1 +
-                                (long long)row * p.ldc;
+      // TMEM gives each lane one row; the chunk is transposed through shared memory so
+      // that global loads and stores are row-contiguous (8 lanes x 16 B per row).  Rows
+      // are 128 B apart with the 16-byte chunk index XOR-ed by (row & 7): conflict-free
+      // both for the row-per-lane writes and the row-contiguous reads.
+      uint8_t* stage = reinterpret_cast<uint8_t*>(epi_stage) + (warp - 2) * EPI_STAGE_BYTES;
+      const int sub_row = lane >> 3;        // 0..3: row within a group of four
+      const int sub_chunk = lane & 7;       // which 16-byte chunk (4 columns) of the row
+      const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
+      const int row_base = tc.m0 + q * 32;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
-      for (int c0 = 0; c0 < p.bn; c0 += 32) {
+      for (int c0 = 32 * ((warp - 2) >> 2); c0 < p.bn; c0 += 64) {
         if (tc.n0 + c0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld16(t_row + c0, r);
         tmem_ld16(t_row + c0 + 16, r + 16);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row_ok) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int col = tc.n0 + c0 + 8 * j;
-            if (col < p.N) epilogue8(p, r + 8 * j, row_off + col, col, p.vec_ok != 0);
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+              make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        __syncwarp();
+        const int col = tc.n0 + c0 + sub_chunk * 4;
+        if (col < p.N) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 4 * i + sub_row;
+            const int row = row_base + rr;
+            if (row < p.M) {
+              const float4 a = *reinterpret_cast<const float4*>(
+                  stage + rr * 128 + ((sub_chunk ^ (rr & 7)) << 4));
+              epilogue4<MODE>(p, a, batch_off + (long long)row * p.ldc + col, col);
+            }
           }
         }
+        __syncwarp();
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -450,6 +482,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                  : "memory");
   }
 }
+
+typedef void (*GemmKernel)(const CUtensorMap, const CUtensorMap, const GemmParams);
+struct Specialised {
+  int mode;
+  GemmKernel fn;
+};
+#define VKG_SPEC(m) {(m), gemm_tcgen05_kernel<(m)>}
+// The epilogues the training step uses; anything else runs the generic kernel.
+const Specialised kSpecialised[] = {
+    VKG_SPEC(0),                                   // fp32 out: dW, dX into layernorm, scores
+    VKG_SPEC(E_F16),                               // fp16 out: attention products, dO
+    VKG_SPEC(E_BIAS),                              // fp32 out + bias: logits of an untied head
+    VKG_SPEC(E_BIAS | E_F16),                      // qkv projection
+    VKG_SPEC(E_BIAS | E_RES),                      // proj / fc2 forward: + bias + residual
+    VKG_SPEC(E_BIAS | E_PRE | E_ACT | E_F16),      // fc1 forward: bias, keep z, GELU, narrow
+    VKG_SPEC(E_DACT | E_F16),                      // fc2 dX: * GELU'(z), narrow
+};
+const int kNumSpecialised = sizeof(kSpecialised) / sizeof(kSpecialised[0]);
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -551,9 +601,9 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   p.err = dev->err_dev;
   // 16-byte vector accesses in the epilogue need every touched array aligned
   // for its element width at every (row, 8-column group).
-  bool vec = (a->ldc % 8 == 0) && (a->sC0 % 8 == 0) && (a->sC1 % 8 == 0);
-  const void* ptrs[5] = {a->C, a->C2, a->pre, a->dact_z, a->residual};
-  for (int i = 0; i < 5; ++i)
+  bool vec = (a->ldc % 4 == 0) && (a->sC0 % 4 == 0) && (a->sC1 % 4 == 0);
+  const void* ptrs[6] = {a->C, a->C2, a->pre, a->dact_z, a->residual, a->bias};
+  for (int i = 0; i < 6; ++i)
     if (ptrs[i] && ((uintptr_t)ptrs[i] & 15)) vec = false;
   p.vec_ok = vec ? 1 : 0;
 
@@ -581,14 +631,25 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
     VKG_REQUIRE((size_t)SMEM_BYTES <= dev->gemm_smem_optin,
                 "gemm needs %d bytes of shared memory, device offers %zu", SMEM_BYTES,
                 dev->gemm_smem_optin);
-    VKG_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  SMEM_BYTES));
+    VKG_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<E_GENERIC>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    for (int i = 0; i < kNumSpecialised; ++i)
+      VKG_CUDA(cudaFuncSetAttribute(kSpecialised[i].fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES));
     dev->gemm_attr_set = true;
   }
   long long total_tiles = (long long)p.tiles_m * p.tiles_n * batch;
   VKG_REQUIRE(total_tiles < (1ll << 31), "gemm: too many tiles");
   int ctas = a->max_ctas > 0 ? a->max_ctas : dev->sm_count;
   if (ctas > total_tiles) ctas = (int)total_tiles;
-  gemm_tcgen05_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(tmA, tmB, p);
+  int mode = (a->bias ? E_BIAS : 0) | (a->pre ? E_PRE : 0) | (a->act ? E_ACT : 0) |
+             (a->dact_z ? E_DACT : 0) | (a->residual ? E_RES : 0) | (a->C2 ? E_C2 : 0) |
+             (a->c_dtype == VKG_F16 ? E_F16 : a->c_dtype == VKG_BF16 ? E_BF16 : 0);
+  GemmKernel fn = gemm_tcgen05_kernel<E_GENERIC>;
+  if (vec) {
+    for (int i = 0; i < kNumSpecialised; ++i)
+      if (kSpecialised[i].mode == mode) fn = kSpecialised[i].fn;
+  }
+  fn<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(tmA, tmB, p);
   return vkg_check_launch("gemm_tcgen05_kernel");
 }
