@@ -240,7 +240,7 @@ def run_single_gemm(args):
     b = dev.buffer(nb * k * n * 2, "device")
     c = dev.buffer(nb * m * n * 4, "device")
     kw = dict(trans_a=bool(ta), trans_b=bool(tb), nb0=nb, sa=(m * k, 0), sb=(k * n, 0),
-              sc=(m * n, 0), c_dtype=F16 if c16 else F32, tile_n=args.tile_n)
+              sc=(m * n, 0), c_dtype=F16 if c16 else F32, tile_n=args.tile_n, split_k=args.split_k)
     gemm(dev, a, b, c, m, n, k, repeat=max(args.warmup, 1), **kw)
     t = gemm(dev, a, b, c, m, n, k, repeat=args.steps, **kw) / args.steps
     print(json.dumps({"gemm": args.gemm, "us": t * 1e6,
@@ -428,6 +428,7 @@ def main():
     ap.add_argument("--gemm", default=None,
                     help="M,N,K,ta,tb,batch[,c16]: time one GEMM shape instead of the step")
     ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--split-k", type=int, default=0)
     args = ap.parse_args()
     if args.gemm:
         run_single_gemm(args)

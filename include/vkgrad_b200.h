@@ -137,6 +137,20 @@ typedef struct vkg_gemm_args {
   int32_t tile_n;            /* 0 = choose; else 64/128/192/256 */
   int32_t max_ctas;          /* 0 = one per SM */
   float alpha;               /* 0 treated as 1: scales acc before bias */
+  int32_t split_k;           /* K cut into slices: each slice's partial tile goes to
+                                `workspace` and a second kernel adds the slices in order
+                                (deterministic).  Plain fp32 epilogue, unbatched only.
+                                0 = library decides (splits only if a workspace is given),
+                                1 = never, n > 1 = exactly n slices. */
+  void* workspace;           /* scratch for the slices: slices * M * N floats */
+  int64_t workspace_bytes;
+  int32_t causal;            /* attention shortcuts for square (T x T) causal operands:
+                                1: C is lower-triangular -- tiles wholly above the diagonal
+                                   are skipped and left untouched (scores, dP);
+                                2: A (M x K) is lower-triangular -- k-blocks right of the
+                                   tile's last row are skipped (P V, dS K);
+                                3: A stored K x M is lower-triangular in (k, m) -- k-blocks
+                                   before the tile's first row are skipped (P^T dO, dS^T Q). */
 } vkg_gemm_args;
 
 int vkg_gemm(vkg_device* dev, const vkg_gemm_args* args);
@@ -197,12 +211,18 @@ int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* x,
                       int rows, int D);
 int64_t vkg_layernorm_bwd_scratch_floats(int rows, int D);
 /* attn_softmax / attn_softmax_doc (tkernels.py:105-161): causal, scaled;
- * seg (optional) restricts a query to keys >= seg[b*T+q]; rows = nbh*T. */
+ * seg (optional) restricts a query to keys >= seg[b*T+q]; rows = nbh*T.
+ * fill_block = 0 writes the zeros above the diagonal to the end of the row as
+ * the reference does; fill_block = n > 0 stops at the end of the n-wide column
+ * block holding the diagonal, for consumers that use vkg_gemm's causal modes
+ * and never read further. */
 int vkg_attn_softmax(vkg_device* dev, const float* s, const uint32_t* seg,
-                     void* p16, int64_t rows, int T, int H, float scale);
+                     void* p16, int64_t rows, int T, int H, float scale,
+                     int fill_block);
 /* attn_softmax_bwd (tkernels.py:167-188): ds = P*(dP - sum dP*P)*scale. */
 int vkg_attn_softmax_bwd(vkg_device* dev, const float* dp, const void* p16,
-                         void* ds16, int64_t rows, int T, float scale);
+                         void* ds16, int64_t rows, int T, float scale,
+                         int fill_block);
 /* split_qkv / merge_qkv_grad / merge_heads / split_heads (tkernels.py:195-300). */
 int vkg_split_qkv(vkg_device* dev, const float* qkv, const float* bias, void* q16,
                   void* k16, void* v16, int64_t n, int D, int T, int H, int hd);

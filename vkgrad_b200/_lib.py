@@ -40,6 +40,10 @@ class GemmArgs(C.Structure):
         ("tile_n", C.c_int32),
         ("max_ctas", C.c_int32),
         ("alpha", C.c_float),
+        ("split_k", C.c_int32),
+        ("workspace", vp),
+        ("workspace_bytes", i64),
+        ("causal", C.c_int32),
     ]
 
 
@@ -86,8 +90,8 @@ _SIGNATURES = {
     "vkg_layernorm": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32]),
     "vkg_layernorm_bwd": (i32, [vp] + [vp] * 13 + [i32, i32]),
     "vkg_layernorm_bwd_scratch_floats": (i64, [i32, i32]),
-    "vkg_attn_softmax": (i32, [vp, vp, vp, vp, i64, i32, i32, f32]),
-    "vkg_attn_softmax_bwd": (i32, [vp, vp, vp, vp, i64, i32, f32]),
+    "vkg_attn_softmax": (i32, [vp, vp, vp, vp, i64, i32, i32, f32, i32]),
+    "vkg_attn_softmax_bwd": (i32, [vp, vp, vp, vp, i64, i32, f32, i32]),
     "vkg_split_qkv": (i32, [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32]),
     "vkg_merge_qkv_grad": (i32, [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32]),
     "vkg_merge_heads": (i32, [vp, vp, vp, i64, i32, i32, i32, i32]),

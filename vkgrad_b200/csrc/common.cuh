@@ -102,16 +102,24 @@ static inline unsigned vkg_blocks(int64_t n, int per_block, int64_t cap = (1ll <
 
 // ---- device helpers shared by the elementwise kernels ----------------------
 
+// tanh(u) = 1 - 2 / (1 + e^{2u}) with the hardware exp2 and reciprocal: absolute error
+// about 1e-7 (it saturates cleanly to +-1), a handful of instructions instead of the
+// branchy libm tanhf.  GELU only ever uses 1 + tanh and 1 - tanh^2, so absolute
+// accuracy is what matters; the GEMM epilogues that call this are issue-bound.
+__device__ __forceinline__ float vkg_tanh(float u) {
+  return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
+}
+
 __device__ __forceinline__ float vkg_gelu(float x) {
   const float c = 0.7978845608028654f;  // sqrt(2/pi)
   float x3 = x * x * x;
-  return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x3)));
+  return 0.5f * x * (1.0f + vkg_tanh(c * (x + 0.044715f * x3)));
 }
 
 __device__ __forceinline__ float vkg_dgelu(float x) {
   const float c = 0.7978845608028654f;
   float x3 = x * x * x;
-  float t = tanhf(c * (x + 0.044715f * x3));
+  float t = vkg_tanh(c * (x + 0.044715f * x3));
   float sech2 = 1.0f - t * t;
   return 0.5f * (1.0f + t) + 0.5f * x * sech2 * c * (1.0f + 3.0f * 0.044715f * x * x);
 }

@@ -44,6 +44,8 @@ struct GemmParams {
   int nb0, nb1;
   int tiles_m, tiles_n;
   int bn, stages, num_kb;
+  int split_k, kb_per_split;   // split_k > 1: z1 is the K slice, not a batch index
+  int causal;                  // 0 none, 1 skip tiles above the diagonal, 2/3 clip the K range
   int a_mn, b_mn;
   uint32_t idesc;
   int c_dtype, act, dact, vec_ok;
@@ -183,6 +185,26 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int t) {
   return c;
 }
 
+// K-block range of a work unit: everything, slice z1 when K is split, or the part of K
+// a causal operand is non-zero in.  nkb == 0 means the tile is skipped by every role.
+__device__ __forceinline__ void kb_range(const GemmParams& p, const TileCoord& c, int& kb0, int& nkb) {
+  if (p.split_k > 1) {
+    kb0 = c.z1 * p.kb_per_split;
+    nkb = min(p.kb_per_split, p.num_kb - kb0);
+  } else {
+    kb0 = 0;
+    nkb = p.num_kb;
+    if (p.causal == 1) {
+      if (c.n0 > c.m0 + BM - 1) nkb = 0;                  // wholly above the diagonal
+    } else if (p.causal == 2) {
+      nkb = min(p.num_kb, (c.m0 + BM + BK - 1) / BK);    // A[m, k] = 0 for k > m
+    } else if (p.causal == 3) {
+      kb0 = c.m0 / BK;                                    // A^T[k, m] = 0 for k < m
+      nkb = p.num_kb - kb0;
+    }
+  }
+}
+
 // Compile-time epilogue feature mask.  E_GENERIC reads every flag (and the vector
 // alignment flag) at run time; the specialised masks assume 16-byte aligned operands.
 enum : int {
@@ -216,11 +238,28 @@ __device__ __forceinline__ void store4_16<__nv_bfloat162, __nv_bfloat16>(__nv_bf
   }
 }
 
-// Four consecutive columns of one row through the fused epilogue.  Called in the
-// coalesced layout: the 8 lanes of a quarter-warp cover 32 consecutive columns of
-// one row, so every global access of the warp is four full 128-byte rows.
+__device__ __forceinline__ float4 ld4(const float* p, long long off, bool vec) {
+  if (vec) return *reinterpret_cast<const float4*>(p + off);
+  return make_float4(p[off], p[off + 1], p[off + 2], p[off + 3]);
+}
+
+__device__ __forceinline__ void st4(float* p, long long off, float4 v, bool vec) {
+  if (vec) {
+    *reinterpret_cast<float4*>(p + off) = v;
+  } else {
+    p[off] = v.x; p[off + 1] = v.y; p[off + 2] = v.z; p[off + 3] = v.w;
+  }
+}
+
+// One lane's share of a 32x32 chunk through the fused epilogue: eight rows (4*i +
+// sub_row), four consecutive columns each.  In this layout the 8 lanes of a
+// quarter-warp cover 32 consecutive columns of one row, so every global access of the
+// warp is four full 128-byte rows.  All loads of one kind are issued before the first
+// dependent use: C may alias the inputs as far as the compiler knows, so a
+// load-compute-store loop would serialise eight memory round trips.
 template <int MODE>
-__device__ __forceinline__ void epilogue4(const GemmParams& p, float4 a, long long off, int col) {
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, float4 (&v)[8],
+                                               const long long (&off)[8], unsigned ok, int col) {
   constexpr bool G = (MODE & E_GENERIC) != 0;
   const bool vec = G ? (p.vec_ok != 0) : true;
   const bool has_bias = G ? (p.bias != nullptr) : (MODE & E_BIAS) != 0;
@@ -230,59 +269,60 @@ __device__ __forceinline__ void epilogue4(const GemmParams& p, float4 a, long lo
   const bool has_res = G ? (p.residual != nullptr) : (MODE & E_RES) != 0;
   const bool has_c2 = G ? (p.C2 != nullptr) : (MODE & E_C2) != 0;
   const int c_dtype = G ? p.c_dtype : ((MODE & E_F16) ? VKG_F16 : (MODE & E_BF16) ? VKG_BF16 : VKG_F32);
-  float v[4] = {a.x * p.alpha, a.y * p.alpha, a.z * p.alpha, a.w * p.alpha};
-  if (has_bias) {
-    const float4 b = vec ? __ldg(reinterpret_cast<const float4*>(p.bias + col))
-                         : make_float4(p.bias[col], p.bias[col + 1], p.bias[col + 2], p.bias[col + 3]);
-    v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
+  float4 extra[8];
+  if (has_dact) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      extra[i] = (ok >> i) & 1u ? ld4(p.dact_z, off[i], vec) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (has_bias) b = ld4(p.bias, col, vec);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[i].x = v[i].x * p.alpha + b.x; v[i].y = v[i].y * p.alpha + b.y;
+    v[i].z = v[i].z * p.alpha + b.z; v[i].w = v[i].w * p.alpha + b.w;
   }
   if (has_pre) {
-    if (vec) {
-      *reinterpret_cast<float4*>(p.pre + off) = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) p.pre[off + j] = v[j];
-    }
+    for (int i = 0; i < 8; ++i)
+      if ((ok >> i) & 1u) st4(p.pre, off[i], v[i], vec);
   }
   if (has_act) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = vkg_act(v[j], p.act);
+    for (int i = 0; i < 8; ++i) {
+      v[i].x = vkg_act(v[i].x, p.act); v[i].y = vkg_act(v[i].y, p.act);
+      v[i].z = vkg_act(v[i].z, p.act); v[i].w = vkg_act(v[i].w, p.act);
+    }
   }
   if (has_dact) {
-    float z[4];
-    if (vec) {
-      const float4 t = *reinterpret_cast<const float4*>(p.dact_z + off);
-      z[0] = t.x; z[1] = t.y; z[2] = t.z; z[3] = t.w;
-    } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) z[j] = p.dact_z[off + j];
+    for (int i = 0; i < 8; ++i) {
+      v[i].x *= vkg_dact(extra[i].x, p.dact); v[i].y *= vkg_dact(extra[i].y, p.dact);
+      v[i].z *= vkg_dact(extra[i].z, p.dact); v[i].w *= vkg_dact(extra[i].w, p.dact);
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] *= vkg_dact(z[j], p.dact);
   }
   if (has_res) {
-    if (vec) {
-      const float4 t = *reinterpret_cast<const float4*>(p.residual + off);
-      v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
-    } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] += p.residual[off + j];
+    for (int i = 0; i < 8; ++i)
+      extra[i] = (ok >> i) & 1u ? ld4(p.residual, off[i], vec) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[i].x += extra[i].x; v[i].y += extra[i].y; v[i].z += extra[i].z; v[i].w += extra[i].w;
     }
   }
-  if (c_dtype == VKG_F32) {
-    float* c = reinterpret_cast<float*>(p.C) + off;
-    if (vec) {
-      *reinterpret_cast<float4*>(c) = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) c[j] = v[j];
+  for (int i = 0; i < 8; ++i) {
+    if (!((ok >> i) & 1u)) continue;
+    const float f[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+    if (c_dtype == VKG_F32) {
+      st4(reinterpret_cast<float*>(p.C), off[i], v[i], vec);
+    } else if (c_dtype == VKG_F16) {
+      store4_16<__half2, __half>(reinterpret_cast<__half*>(p.C) + off[i], f, vec);
+    } else {
+      store4_16<__nv_bfloat162, __nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(p.C) + off[i], f, vec);
     }
-  } else if (c_dtype == VKG_F16) {
-    store4_16<__half2, __half>(reinterpret_cast<__half*>(p.C) + off, v, vec);
-  } else {
-    store4_16<__nv_bfloat162, __nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(p.C) + off, v, vec);
+    if (has_c2) store4_16<__half2, __half>(reinterpret_cast<__half*>(p.C2) + off[i], f, vec);
   }
-  if (has_c2) store4_16<__half2, __half>(reinterpret_cast<__half*>(p.C2) + off, v, vec);
 }
 
 template <int MODE>
@@ -333,7 +373,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * p.nb1;
+  const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * (p.split_k > 1 ? p.split_k : p.nb1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -342,7 +382,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileCoord tc = tile_coord(p, t);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        int kb0, nkb;
+        kb_range(p, tc, kb0, nkb);
+        if (p.split_k > 1) tc.z1 = 0;   // operands are not batched along the slice index
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag, p.err, 0x100u + stage)) {
             ok = false;
             break;
@@ -351,7 +394,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           mbar_expect_tx(fb, stage_bytes);
           const uint32_t sa = base + stage * stage_bytes;
           const uint32_t sb = sa + A_STAGE_BYTES;
-          const int k0 = kb * BK;
+          const int k0 = (kb0 + kb) * BK;
           if (!p.a_mn) {
             tma_load_4d(sa, &tmA, fb, k0, tc.m0, tc.z0, tc.z1);
           } else {
@@ -379,10 +422,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int kb0, nkb;
+        kb_range(p, tile_coord(p, t), kb0, nkb);
+        if (nkb <= 0) continue;   // skipped tile: no accumulator, no epilogue
         if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag, p.err, 0x200u + acc)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.err, 0x300u + stage)) {
             ok = false;
             break;
@@ -418,6 +464,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       TileCoord tc = tile_coord(p, t);
+      {
+        int kb0, nkb;
+        kb_range(p, tc, kb0, nkb);
+        if (nkb <= 0) continue;
+      }
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.err, 0x400u + acc)) break;
       tcgen05_fence_after();
       // TMEM gives each lane one row; the chunk is transposed through shared memory so
@@ -443,16 +494,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         __syncwarp();
         const int col = tc.n0 + c0 + sub_chunk * 4;
         if (col < p.N) {
+          float4 v[8];
+          long long off[8];
+          unsigned ok = 0;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int rr = 4 * i + sub_row;
             const int row = row_base + rr;
-            if (row < p.M) {
-              const float4 a = *reinterpret_cast<const float4*>(
-                  stage + rr * 128 + ((sub_chunk ^ (rr & 7)) << 4));
-              epilogue4<MODE>(p, a, batch_off + (long long)row * p.ldc + col, col);
-            }
+            v[i] = *reinterpret_cast<const float4*>(stage + rr * 128 + ((sub_chunk ^ (rr & 7)) << 4));
+            off[i] = batch_off + (long long)row * p.ldc + col;
+            ok |= (row < p.M ? 1u : 0u) << i;
           }
+          epilogue_chunk<MODE>(p, v, off, ok, col);
         }
         __syncwarp();
       }
@@ -480,6 +533,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"((uint32_t)TMEM_COLS)
                  : "memory");
+  }
+}
+
+// Adds the K slices of a split GEMM in slice order and writes C (fp32, row pitch ldc).
+__global__ void k_splitk_reduce(const float4* __restrict__ ws, float* __restrict__ C, int M, int N4,
+                                long long ldc, int splits) {
+  const long long per = (long long)M * N4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 a = ws[i];
+    for (int s = 1; s < splits; ++s) {
+      const float4 b = ws[i + s * per];
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    const long long r = i / N4, c = i - r * N4;
+    *reinterpret_cast<float4*>(C + r * ldc + c * 4) = a;
   }
 }
 
@@ -535,24 +604,44 @@ int make_map(vkg_device* dev, CUtensorMap* map, const void* ptr, int dtype, int6
   return 0;
 }
 
-int pick_tile_n(int M, int N, int batch, int sms) {
-  int tiles_m = (M + BM - 1) / BM;
-  int best = 64;
-  long long best_cost = -1;
+// Tile width and K split for one GEMM, from a small time model (microseconds).
+// Measured on B200: a k-block (64 K-elements, four tcgen05.mma) costs about the same
+// 0.36 us whether the tile is 64 or 256 columns wide, so narrow tiles waste the tensor
+// core; an epilogue costs ~3.5 us per 128x256 fp32 tile.  When the grid cannot fill
+// the SMs with wide tiles (the dW shapes: few output tiles, K = rows of the batch),
+// K is split across CTAs and a second pass adds the slices.
+void plan_gemm(int M, int N, int K, int batch, int sms, bool may_split, int64_t ws_bytes,
+               int force_bn, int force_split, int* out_bn, int* out_split) {
+  const int tiles_m = (M + BM - 1) / BM;
+  const int num_kb = (K + BK - 1) / BK;
+  const int n_round = ((N + 63) / 64) * 64;
   const int cand[4] = {256, 192, 128, 64};
-  int n_round = ((N + 63) / 64) * 64;
+  double best = -1.0;
+  *out_bn = 64;
+  *out_split = 1;
   for (int i = 0; i < 4; ++i) {
-    int bn = cand[i];
-    if (bn > n_round && bn != 64) continue;
-    long long tiles = (long long)tiles_m * ((N + bn - 1) / bn) * batch;
-    long long waves = (tiles + sms - 1) / sms;
-    long long cost = waves * (bn + 24);
-    if (best_cost < 0 || cost < best_cost) {
-      best_cost = cost;
-      best = bn;
+    const int bn = cand[i];
+    if (force_bn ? bn != force_bn : (bn > n_round && bn != 64)) continue;
+    const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn) * batch;
+    const double t_kb = bn >= 256 ? 0.34 : 0.36;
+    const double t_epi = 3.5 * bn / 256.0;
+    for (int sp = 1; sp <= 16; ++sp) {
+      if (force_split > 0 && sp != force_split) continue;
+      if (sp > 1) {
+        if (!may_split || num_kb / sp < 4) break;
+        if ((int64_t)sp * M * N * 4 > ws_bytes) break;
+      }
+      const long long waves = (tiles * sp + sms - 1) / sms;
+      const int kbs = (num_kb + sp - 1) / sp;
+      double t = waves * (kbs * t_kb + t_epi);
+      if (sp > 1) t += (double)(sp + 1) * M * N * 4.0 / 4.0e6 + 4.0;
+      if (best < 0 || t < best) {
+        best = t;
+        *out_bn = bn;
+        *out_split = sp;
+      }
     }
   }
-  return best;
 }
 
 }  // namespace
@@ -572,10 +661,18 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   const int batch = nb0 * nb1;
   VKG_REQUIRE(a->ldc >= a->N, "gemm: ldc %lld < N %d", (long long)a->ldc, a->N);
 
-  int bn = a->tile_n;
-  if (bn == 0) bn = pick_tile_n(a->M, a->N, batch, dev->sm_count);
-  VKG_REQUIRE(bn == 64 || bn == 128 || bn == 192 || bn == 256, "gemm: tile_n %d not in {64,128,192,256}",
-              bn);
+  VKG_REQUIRE(a->tile_n == 0 || a->tile_n == 64 || a->tile_n == 128 || a->tile_n == 192 ||
+                  a->tile_n == 256, "gemm: tile_n %d not in {64,128,192,256}", a->tile_n);
+  const bool plain_f32 = !a->bias && !a->pre && !a->act && !a->dact_z && !a->residual && !a->C2 &&
+                         a->c_dtype == VKG_F32 && (a->alpha == 0.0f || a->alpha == 1.0f);
+  const bool may_split = plain_f32 && batch == 1 && a->causal == 0 && a->workspace && a->N % 4 == 0 &&
+                         a->ldc % 4 == 0 && (((uintptr_t)a->C | (uintptr_t)a->workspace) & 15) == 0;
+  VKG_REQUIRE(a->split_k <= 1 || may_split,
+              "gemm: split_k needs an unbatched GEMM with a plain fp32 output, a 16-byte aligned "
+              "workspace, and N, ldc multiples of 4");
+  int bn = 0, want_split = 1;
+  plan_gemm(a->M, a->N, a->K, batch, dev->sm_count, may_split && a->split_k != 1,
+            a->workspace_bytes, a->tile_n, a->split_k > 1 ? a->split_k : 0, &bn, &want_split);
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -599,6 +696,25 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   p.dact_z = a->dact_z; p.residual = a->residual;
   p.alpha = a->alpha == 0.0f ? 1.0f : a->alpha;
   p.err = dev->err_dev;
+  p.split_k = 1;
+  p.kb_per_split = p.num_kb;
+  VKG_REQUIRE(a->causal >= 0 && a->causal <= 3, "gemm: causal mode %d unknown", a->causal);
+  p.causal = a->causal;
+  if (want_split > 1) {
+    int splits = want_split < p.num_kb ? want_split : p.num_kb;
+    p.kb_per_split = (p.num_kb + splits - 1) / splits;
+    splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;   // no empty slice
+    if (splits > 1) {
+      VKG_REQUIRE(a->workspace_bytes >= (int64_t)splits * a->M * a->N * 4,
+                  "gemm: split_k workspace too small (%lld bytes for %d slices of %d x %d)",
+                  (long long)a->workspace_bytes, splits, a->M, a->N);
+      p.split_k = splits;
+      p.C = a->workspace;
+      p.ldc = a->N;
+      p.sC0 = 0;
+      p.sC1 = (long long)a->M * a->N;
+    }
+  }
   // 16-byte vector accesses in the epilogue need every touched array aligned
   // for its element width at every (row, 8-column group).
   bool vec = (a->ldc % 4 == 0) && (a->sC0 % 4 == 0) && (a->sC1 % 4 == 0);
@@ -638,7 +754,7 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
                                     SMEM_BYTES));
     dev->gemm_attr_set = true;
   }
-  long long total_tiles = (long long)p.tiles_m * p.tiles_n * batch;
+  long long total_tiles = (long long)p.tiles_m * p.tiles_n * batch * p.split_k;
   VKG_REQUIRE(total_tiles < (1ll << 31), "gemm: too many tiles");
   int ctas = a->max_ctas > 0 ? a->max_ctas : dev->sm_count;
   if (ctas > total_tiles) ctas = (int)total_tiles;
@@ -651,5 +767,12 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
       if (kSpecialised[i].mode == mode) fn = kSpecialised[i].fn;
   }
   fn<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(tmA, tmB, p);
-  return vkg_check_launch("gemm_tcgen05_kernel");
+  if (vkg_check_launch("gemm_tcgen05_kernel")) return 1;
+  if (p.split_k > 1) {
+    const long long n4 = (long long)a->M * (a->N / 4);
+    k_splitk_reduce<<<vkg_blocks(n4, 256, (int64_t)dev->sm_count * 8), 256, 0, dev->stream>>>(
+        (const float4*)a->workspace, (float*)a->C, a->M, a->N / 4, a->ldc, p.split_k);
+    return vkg_check_launch("splitk_reduce");
+  }
+  return 0;
 }

@@ -225,38 +225,73 @@ __global__ void k_col_sum(const float* __restrict__ g, float* __restrict__ sums,
   sums[c] = s;
 }
 
-constexpr int CS_COLS = 64;    // columns per block (2 per lane)
 constexpr int CS_WARPS = 8;
 
-// Stage 1: block (cx, chunk) sums rows [chunk*rpc, ...) of its 64 columns into
-// partial[chunk][col].  Warps stride the rows; lanes own column pairs.
+template <typename T> struct ColVec;
+template <> struct ColVec<__half> {   // 8 columns per lane: one 16-byte load per row
+  static constexpr int N = 8;
+  __device__ static void add(const __half* p, float* s) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __half22float2(h[j]);
+      s[2 * j] += f.x;
+      s[2 * j + 1] += f.y;
+    }
+  }
+};
+template <> struct ColVec<float> {    // 4 columns per lane
+  static constexpr int N = 4;
+  __device__ static void add(const float* p, float* s) {
+    float4 u = *reinterpret_cast<const float4*>(p);
+    s[0] += u.x; s[1] += u.y; s[2] += u.z; s[3] += u.w;
+  }
+};
+
+// Stage 1: block (cx, chunk) sums rows [chunk*rpc, ...) of its 32*N columns into
+// partial[chunk][col].  Warps stride the rows; each lane owns N adjacent columns and
+// reads them with one 16-byte load per row (scalar loads when ncol is not a multiple
+// of N or the base is unaligned).
 template <typename T>
-__global__ void k_col_sum_partial(const T* __restrict__ g, float* __restrict__ partial, int ncol,
-                                  int nrow, int rows_per_chunk) {
-  __shared__ float red[CS_WARPS][CS_COLS];
+__global__ void __launch_bounds__(CS_WARPS * 32)
+k_col_sum_partial(const T* __restrict__ g, float* __restrict__ partial, int ncol, int nrow,
+                  int rows_per_chunk, int vec_ok) {
+  constexpr int N = ColVec<T>::N;
+  __shared__ float red[CS_WARPS][32 * N + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int c = blockIdx.x * CS_COLS + lane * 2;
+  const int c = (blockIdx.x * 32 + lane) * N;
   const int r0 = blockIdx.y * rows_per_chunk;
   const int r1 = min(nrow, r0 + rows_per_chunk);
-  float s0 = 0.f, s1 = 0.f;
-  if (c + 1 < ncol) {
-    for (int r = r0 + warp; r < r1; r += CS_WARPS) {
-      const T* p = g + (int64_t)r * ncol + c;
-      s0 += float(p[0]);
-      s1 += float(p[1]);
-    }
-  } else if (c < ncol) {
-    for (int r = r0 + warp; r < r1; r += CS_WARPS) s0 += float(g[(int64_t)r * ncol + c]);
-  }
-  red[warp][lane * 2] = s0;
-  red[warp][lane * 2 + 1] = s1;
-  __syncthreads();
-  if (threadIdx.x < CS_COLS) {
-    float s = 0.f;
+  float s[N];
 #pragma unroll
-    for (int w = 0; w < CS_WARPS; ++w) s += red[w][threadIdx.x];
-    int col = blockIdx.x * CS_COLS + threadIdx.x;
-    if (col < ncol) partial[(int64_t)blockIdx.y * ncol + col] = s;
+  for (int j = 0; j < N; ++j) s[j] = 0.f;
+  if (vec_ok) {
+    if (c < ncol) {
+      int r = r0 + warp;
+      for (; r + 3 * CS_WARPS < r1; r += 4 * CS_WARPS) {   // four rows in flight per lane
+        ColVec<T>::add(g + (int64_t)r * ncol + c, s);
+        ColVec<T>::add(g + (int64_t)(r + CS_WARPS) * ncol + c, s);
+        ColVec<T>::add(g + (int64_t)(r + 2 * CS_WARPS) * ncol + c, s);
+        ColVec<T>::add(g + (int64_t)(r + 3 * CS_WARPS) * ncol + c, s);
+      }
+      for (; r < r1; r += CS_WARPS) ColVec<T>::add(g + (int64_t)r * ncol + c, s);
+    }
+  } else {
+    for (int r = r0 + warp; r < r1; r += CS_WARPS)
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        if (c + j < ncol) s[j] += float(g[(int64_t)r * ncol + c + j]);
+  }
+#pragma unroll
+  for (int j = 0; j < N; ++j) red[warp][lane * N + j] = s[j];
+  __syncthreads();
+  for (int t = threadIdx.x; t < 32 * N; t += CS_WARPS * 32) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < CS_WARPS; ++w) a += red[w][t];
+    int col = blockIdx.x * 32 * N + t;
+    if (col < ncol) partial[(int64_t)blockIdx.y * ncol + col] = a;
   }
 }
 
@@ -559,7 +594,8 @@ k_layernorm_bwd_vec(const float* __restrict__ dy, const float* __restrict__ x,
 
 // One warp per (batch*head, query) row; causal; optional packed-sample start.
 __global__ void k_attn_softmax(const float* __restrict__ s, const uint32_t* __restrict__ seg,
-                               __half* __restrict__ p16, int64_t rows, int T, int H, float scale) {
+                               __half* __restrict__ p16, int64_t rows, int T, int H, float scale,
+                               int fill_block) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
   if (row >= rows) return;
@@ -574,7 +610,10 @@ __global__ void k_attn_softmax(const float* __restrict__ s, const uint32_t* __re
   for (int j = st + lane; j <= q; j += 32) sum += __expf(s[base + j] * scale - mx);
   sum = warp_sum(sum);
   const float inv = 1.0f / sum;
-  for (int j = lane; j < T; j += 32) {
+  // zeros above the diagonal: to the end of the row, or only to the end of the
+  // fill_block-wide tile the consumer's causal K range stops at
+  const int jend = fill_block > 0 ? min(T, (q / fill_block + 1) * fill_block) : T;
+  for (int j = lane; j < jend; j += 32) {
     float v = 0.f;
     if (j >= st && j <= q) v = __expf(s[base + j] * scale - mx) * inv;
     p16[base + j] = __float2half_rn(v);
@@ -582,7 +621,8 @@ __global__ void k_attn_softmax(const float* __restrict__ s, const uint32_t* __re
 }
 
 __global__ void k_attn_softmax_bwd(const float* __restrict__ dp, const __half* __restrict__ p16,
-                                   __half* __restrict__ ds16, int64_t rows, int T, float scale) {
+                                   __half* __restrict__ ds16, int64_t rows, int T, float scale,
+                                   int fill_block) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
   if (row >= rows) return;
@@ -591,7 +631,8 @@ __global__ void k_attn_softmax_bwd(const float* __restrict__ dp, const __half* _
   float dot = 0.f;
   for (int j = lane; j <= q; j += 32) dot += dp[base + j] * __half2float(p16[base + j]);
   dot = warp_sum(dot);
-  for (int j = lane; j < T; j += 32) {
+  const int jend = fill_block > 0 ? min(T, (q / fill_block + 1) * fill_block) : T;
+  for (int j = lane; j < jend; j += 32) {
     float v = 0.f;
     if (j <= q) v = __half2float(p16[base + j]) * (dp[base + j] - dot) * scale;
     ds16[base + j] = __float2half_rn(v);
@@ -733,7 +774,7 @@ extern "C" int vkg_col_sum(vkg_device* dev, const float* g, float* sums, int nco
 }
 
 static int col_sum_chunks(int ncol, int nrow) {
-  int col_blocks = (ncol + CS_COLS - 1) / CS_COLS;
+  int col_blocks = (ncol + 127) / 128;             // the narrower (fp32) block width
   int want = (592 + col_blocks - 1) / col_blocks;  // ~4 CTAs per SM on 148 SMs
   int max_chunks = (nrow + 31) / 32;               // at least 32 rows per chunk
   if (want > max_chunks) want = max_chunks;
@@ -754,13 +795,15 @@ extern "C" int vkg_col_sum_det(vkg_device* dev, const void* g, int g_dtype, floa
   VKG_REQUIRE(g_dtype == VKG_F32 || g_dtype == VKG_F16, "col_sum_det: dtype must be f32 or f16");
   int nchunk = col_sum_chunks(ncol, nrow);
   int rpc = (nrow + nchunk - 1) / nchunk;
-  dim3 grid((ncol + CS_COLS - 1) / CS_COLS, nchunk);
+  const int per_block = 32 * (g_dtype == VKG_F16 ? 8 : 4);
+  const int vec_ok = (ncol % (per_block / 32) == 0) && (((uintptr_t)g & 15) == 0);
+  dim3 grid((ncol + per_block - 1) / per_block, nchunk);
   if (g_dtype == VKG_F16)
     k_col_sum_partial<__half><<<grid, CS_WARPS * 32, 0, dev->stream>>>((const __half*)g, scratch,
-                                                                        ncol, nrow, rpc);
+                                                                        ncol, nrow, rpc, vec_ok);
   else
     k_col_sum_partial<float><<<grid, CS_WARPS * 32, 0, dev->stream>>>((const float*)g, scratch, ncol,
-                                                                       nrow, rpc);
+                                                                       nrow, rpc, vec_ok);
   if (vkg_check_launch("col_sum_partial")) return 1;
   k_col_sum_final<<<vkg_blocks(ncol, 128), 128, 0, dev->stream>>>(scratch, sums, ncol, nchunk,
                                                                   accumulate);
@@ -928,22 +971,22 @@ extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* 
 }
 
 extern "C" int vkg_attn_softmax(vkg_device* dev, const float* s, const uint32_t* seg, void* p16,
-                                int64_t rows, int T, int H, float scale) {
+                                int64_t rows, int T, int H, float scale, int fill_block) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(s && p16 && rows > 0 && T > 0, "attn_softmax: bad arguments");
   const int wpb = 8;
   k_attn_softmax<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, dev->stream>>>(
-      s, seg, (__half*)p16, rows, T, H > 0 ? H : 1, scale);
+      s, seg, (__half*)p16, rows, T, H > 0 ? H : 1, scale, fill_block);
   return vkg_check_launch("attn_softmax");
 }
 
 extern "C" int vkg_attn_softmax_bwd(vkg_device* dev, const float* dp, const void* p16, void* ds16,
-                                    int64_t rows, int T, float scale) {
+                                    int64_t rows, int T, float scale, int fill_block) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(dp && p16 && ds16 && rows > 0 && T > 0, "attn_softmax_bwd: bad arguments");
   const int wpb = 8;
   k_attn_softmax_bwd<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, dev->stream>>>(
-      dp, (const __half*)p16, (__half*)ds16, rows, T, scale);
+      dp, (const __half*)p16, (__half*)ds16, rows, T, scale, fill_block);
   return vkg_check_launch("attn_softmax_bwd");
 }
 

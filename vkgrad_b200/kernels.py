@@ -35,6 +35,7 @@ CONFIGS = [(sg, wm, wn, lds)
            if sg * 32 <= 1024 and wm * wn <= 16]
 
 TILE_N_CHOICES = (64, 128, 192, 256)
+SPLIT_K_MAX_TILE_BYTES = 16 << 20   # outputs larger than this already fill the GPU
 
 
 def _ptr(buf):
@@ -51,7 +52,7 @@ def gemm(dev, a, b, c, m, n, k, trans_a=False, trans_b=False, graph=None, repeat
          nb0=1, nb1=1, lda=None, ldb=None, ldc=None, sa=(0, 0), sb=(0, 0), sc=(0, 0),
          a_off=0, b_off=0, c_off=0, in_dtype=F16, c_dtype=F32, bias=None, act=ACT_NONE,
          pre=None, dact_z=None, dact=ACT_NONE, residual=None, c2=None, tile_n=0,
-         max_ctas=0, alpha=1.0, name="gemm"):
+         max_ctas=0, alpha=1.0, split_k=0, causal=0, name="gemm"):
     """C = op(A) op(B) with the fused epilogue of vkg_gemm (include/vkgrad_b200.h).
 
     Offsets (a_off, b_off, c_off) are in elements and apply to C, c2, pre,
@@ -84,6 +85,15 @@ def gemm(dev, a, b, c, m, n, k, trans_a=False, trans_b=False, graph=None, repeat
     args.tile_n = int(tile_n)
     args.max_ctas = int(max_ctas)
     args.alpha = float(alpha)
+    args.split_k = int(split_k)
+    args.causal = int(causal)
+    plain = (bias is None and pre is None and dact_z is None and residual is None and c2 is None
+             and act == ACT_NONE and c_dtype == F32 and alpha == 1.0)
+    if split_k != 1 and plain and nb0 * nb1 == 1 and m * n * 4 <= SPLIT_K_MAX_TILE_BYTES:
+        # few output tiles, long K (the dW shapes): give the library room to split K
+        ws = dev.scratch((int(split_k) if split_k > 1 else 8) * m * n * 4)
+        args.workspace = ws.dptr
+        args.workspace_bytes = ws.size
     lib, h = dev.lib, dev.handle
 
     def go():

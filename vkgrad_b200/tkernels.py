@@ -32,14 +32,14 @@ def make_transformer_kernels(dev):
                               b[5].dptr, None, b[6].dptr, b[7].dptr, None, None, None,
                               n // W, int(D)), "layernorm_bwd"))
     op("attn_softmax", 2, lambda b, n, T, scale: _check(
-        lib.vkg_attn_softmax(h, b[0].dptr, None, b[1].dptr, n // W, int(T), 1, float(scale)),
+        lib.vkg_attn_softmax(h, b[0].dptr, None, b[1].dptr, n // W, int(T), 1, float(scale), 0),
         "attn_softmax"))
     op("attn_softmax_doc", 3, lambda b, n, T, H, scale: _check(
         lib.vkg_attn_softmax(h, b[0].dptr, b[1].dptr, b[2].dptr, n // W, int(T), int(H),
-                             float(scale)), "attn_softmax_doc"))
+                             float(scale), 0), "attn_softmax_doc"))
     op("attn_softmax_bwd", 3, lambda b, n, T, scale: _check(
         lib.vkg_attn_softmax_bwd(h, b[0].dptr, b[1].dptr, b[2].dptr, n // W, int(T),
-                                 float(scale)), "attn_softmax_bwd"))
+                                 float(scale), 0), "attn_softmax_bwd"))
     op("split_qkv", 5, lambda b, n, D, T, H, hd: _check(
         lib.vkg_split_qkv(h, b[0].dptr, b[1].dptr, b[2].dptr, b[3].dptr, b[4].dptr, n,
                           int(D), int(T), int(H), int(hd)), "split_qkv"))

@@ -33,6 +33,7 @@ from .tkernels import make_transformer_kernels
 from .vk import _check
 
 NCHUNK = 32  # kept for callers that pass it to col_sum_chunk (transformer.py:20)
+CAUSAL_BLOCK = 128  # row-tile height of the GEMM: where its causal K ranges stop
 _LN_FUSED_MAX_D = 1536  # shared-memory limit of the fused dgamma/dbeta reduction
 
 
@@ -178,7 +179,7 @@ class Attention:
 
     def _bgemm(self, a, b, c, m, n, k, graph, ta=False, tb=False, a_in_qkv=None, b_in_qkv=None,
                c_in_qkv=None, a_merged=False, b_merged=False, c_merged=False, c_dtype=F32,
-               name="attn"):
+               causal=0, name="attn"):
         """One GEMM per (head, batch): nb0 = H heads, nb1 = B sequences.
 
         *_in_qkv = i selects slice i (0 q, 1 k, 2 v) of a (rows, 3D) matrix;
@@ -198,25 +199,26 @@ class Attention:
         return gemm(self.ctx.dev, a, b, c, m, n, k, ta, tb, graph=graph, nb0=H, nb1=self.B,
                     lda=A["ld"], ldb=Bm["ld"], ldc=Cm["ld"], sa=A["s"], sb=Bm["s"], sc=Cm["s"],
                     a_off=A["off"], b_off=Bm["off"], c_off=Cm["off"], c_dtype=c_dtype,
-                    name=f"{self.name}.{name}")
+                    causal=causal, name=f"{self.name}.{name}")
 
     def forward(self, x16, graph=None, seg=None, out=None, residual=None):
         """Returns proj(attn(x)) + bias (+ residual) in fp32 (`out` or proj.acc)."""
         c, lib, h = self.ctx, self.ctx.dev.lib, self.ctx.dev.handle
         T, hd = self.T, self.hd
         self.qkv.forward(x16, graph=graph, out=self.qkv16, c_dtype=F16)
-        # scores = Q K^T per head
+        # scores = Q K^T per head; tiles wholly above the diagonal are never computed,
+        # and nothing downstream reads past the 128-wide block that holds the diagonal
         self._bgemm(self.qkv16, self.qkv16, self.scores, T, T, hd, graph, tb=True,
-                    a_in_qkv=0, b_in_qkv=1, name="qk")
+                    a_in_qkv=0, b_in_qkv=1, causal=1, name="qk")
         seg_p = None if seg is None else seg.dptr
 
         def soft():
             _check(lib.vkg_attn_softmax(h, self.scores.dptr, seg_p, self.p16.dptr, self.nbh * T, T,
-                                        self.H, float(self.scale)), "attn_softmax")
+                                        self.H, float(self.scale), CAUSAL_BLOCK), "attn_softmax")
         c.launch(graph, soft, "attn_softmax", self.nbh * T * T * 6)
         # out = P V, written head-merged as fp16
         self._bgemm(self.p16, self.qkv16, self.ao16, T, hd, T, graph, b_in_qkv=2, c_merged=True,
-                    c_dtype=F16, name="pv")
+                    c_dtype=F16, causal=2, name="pv")
         return self.proj.forward(self.ao16, graph=graph, out=out, residual=residual)
 
     def backward(self, dy16, graph=None):
@@ -226,20 +228,21 @@ class Attention:
         self.proj.backward(dy16, need_dx=True, graph=graph, dx=self.dao16, dx_dtype=F16)
         # dV = P^T dO  -> slice 2 of dqkv
         self._bgemm(self.p16, self.dao16, self.dqkv16, T, hd, T, graph, ta=True, b_merged=True,
-                    c_in_qkv=2, c_dtype=F16, name="dv")
+                    c_in_qkv=2, c_dtype=F16, causal=3, name="dv")
         # dP = dO V^T
         self._bgemm(self.dao16, self.qkv16, self.dp32, T, T, hd, graph, tb=True, a_merged=True,
-                    b_in_qkv=2, name="dp")
+                    b_in_qkv=2, causal=1, name="dp")
 
         def soft_bwd():
             _check(lib.vkg_attn_softmax_bwd(h, self.dp32.dptr, self.p16.dptr, self.ds16.dptr,
-                                            self.nbh * T, T, float(self.scale)), "attn_softmax_bwd")
+                                            self.nbh * T, T, float(self.scale), CAUSAL_BLOCK),
+                   "attn_softmax_bwd")
         c.launch(graph, soft_bwd, "attn_softmax_bwd", self.nbh * T * T * 8)
         # dQ = dS K -> slice 0 ; dK = dS^T Q -> slice 1
         self._bgemm(self.ds16, self.qkv16, self.dqkv16, T, hd, T, graph, b_in_qkv=1, c_in_qkv=0,
-                    c_dtype=F16, name="dq")
+                    c_dtype=F16, causal=2, name="dq")
         self._bgemm(self.ds16, self.qkv16, self.dqkv16, T, hd, T, graph, ta=True, b_in_qkv=0,
-                    c_in_qkv=1, c_dtype=F16, name="dk")
+                    c_in_qkv=1, c_dtype=F16, causal=3, name="dk")
         return self.qkv.backward(self.dqkv16, need_dx=True, graph=graph)
 
 
