@@ -257,6 +257,10 @@ def run_gpu_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        # a rank stuck in rendezvous or a collective dumps every thread's stack and exits
+        import faulthandler
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             raise SystemExit("--gpus N > 1 needs one process per GPU: launch with "
@@ -427,6 +431,8 @@ def main():
                     help="run only the device-resident steps (for an ncu launch list)")
     ap.add_argument("--gemm", default=None,
                     help="M,N,K,ta,tb,batch[,c16]: time one GEMM shape instead of the step")
+    ap.add_argument("--watchdog", type=int, default=900,
+                    help="seconds after which a multi-GPU rank dumps its stacks and exits")
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--split-k", type=int, default=0)
     args = ap.parse_args()

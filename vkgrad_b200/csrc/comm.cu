@@ -109,6 +109,18 @@ extern "C" int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint
     delete c;
     VKG_FAIL("comm_create: %s", cudaGetErrorString(e));
   }
+  // One small collective now, outside any capture: NCCL sets its channels up lazily
+  // on the first call, which allocates and synchronises.
+  cudaMemsetAsync(c->scratch_dev, 0, 64, dev->stream);
+  r = g_nccl.AllReduce(c->scratch_dev, c->scratch_dev, 1, NCCL_FLOAT64, NCCL_MAX, c->comm, dev->stream);
+  e = cudaStreamSynchronize(dev->stream);
+  if (r != 0 || e != cudaSuccess) {
+    cudaFree(c->scratch_dev);
+    g_nccl.CommDestroy(c->comm);
+    delete c;
+    VKG_FAIL("comm_create: first collective failed (%s / %s)", r ? g_nccl.GetErrorString(r) : "ok",
+             cudaGetErrorString(e));
+  }
   *out = c;
   return 0;
 }

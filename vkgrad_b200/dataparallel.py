@@ -260,44 +260,67 @@ class Replica:
 
 class DataParallelStep:
     """One recorded data-parallel training step: (inputs up) -> forward/backward ->
-    all-reduce of the flat gradient bucket -> AdamW -> (loss down).
+    all-reduce of the flat gradient bucket -> AdamW.
 
     The multi-GPU counterpart of autograd.TrainStep; with one worker it is the same
     step without the all-reduce.  host_ids/host_targets, when given, are pinned
     host buffers copied to the device inside the step, so per-step data written by
     the caller is picked up by every replay.
+
+    With more than one worker the step is two CUDA graphs with the NCCL call
+    enqueued between them on the same stream (no host synchronisation in between);
+    in_graph=True captures the all-reduce into a single graph instead.
     """
 
     def __init__(self, replica, ids_dev, targets_dev, host_ids=None, host_targets=None,
-                 name="dp_step", **record_kwargs):
+                 name="dp_step", in_graph=False, **record_kwargs):
         self.replica = replica
         self.model, self.opt = replica.model, replica.opt
-        dev = replica.dev
+        dev = self.dev = replica.dev
         lib, h = dev.lib, dev.handle
-        self.graph = dev.graph(name)
+        g = dev.graph(name)
         if host_ids is not None:
             pairs = [(ids_dev, host_ids), (targets_dev, host_targets)]
 
             def upload():
                 for d, s in pairs:
                     _check(lib.vkg_copy_h2d_async(h, d.dptr, s.hptr, min(d.size, s.size)), "h2d")
-            self.graph.add(upload, "h2d_inputs", sum(min(d.size, s.size) for d, s in pairs))
-            self.graph.n_dispatch -= 1
-        self.model.record(ids_dev, targets_dev, self.graph, **record_kwargs)
-        replica.record_step(self.graph)
-        self.graph.finish()
-        self.n_dispatch = self.graph.n_dispatch
-        self.n_kernels = self.graph.n_kernels
-
-    def __call__(self, lr=None):
-        self.opt.advance(lr)
-        dt = self.graph.submit()
-        return self.model.read_loss(), dt
+            g.add(upload, "h2d_inputs", sum(min(d.size, s.size) for d, s in pairs))
+            g.n_dispatch -= 1
+        self.model.record(ids_dev, targets_dev, g, **record_kwargs)
+        comm = replica.comm
+        self.between = None
+        self.graphs = [g]
+        workers = comm.world if comm is not None else 1
+        self.opt.grad_scale = 1.0 / (workers * replica.loss_scale)
+        if comm is not None and comm.world > 1 and not in_graph:
+            g.finish()
+            bucket, total = replica.bucket, replica.total
+            self.between = lambda: comm.allreduce_sum(bucket, total)
+            g = dev.graph(name + "_opt")
+            self.graphs.append(g)
+        else:
+            replica.push_gradients(graph=g)
+        self.opt.record(g)
+        g.finish()
+        self.n_dispatch = sum(x.n_dispatch for x in self.graphs)
+        self.n_kernels = sum(x.n_kernels for x in self.graphs)
 
     def enqueue(self, lr=None):
         """Advance the schedule and launch without waiting (pair with dev.sync())."""
         self.opt.advance(lr)
-        self.graph.submit_async()
+        self.graphs[0].submit_async()
+        if self.between is not None:
+            self.between()
+            self.graphs[1].submit_async()
+
+    def __call__(self, lr=None):
+        lib, h = self.dev.lib, self.dev.handle
+        _check(lib.vkg_timer_begin(h), "timer")
+        self.enqueue(lr)
+        s = C.c_double(0.0)
+        _check(lib.vkg_timer_end(h, C.byref(s)), "step")
+        return self.model.read_loss(), s.value
 
 
 class GradAccum:
