@@ -241,6 +241,21 @@ int vkg_split_heads(vkg_device* dev, const float* src, void* dst16, int64_t n,
 int vkg_col_sum_det(vkg_device* dev, const void* g, int g_dtype, float* sums,
                     float* scratch, int ncol, int nrow, int accumulate);
 int64_t vkg_col_sum_scratch_floats(int ncol, int nrow);
+/* No counterpart in the reference.  The same deterministic column sum as
+ * vkg_col_sum_det for callers that are not allowed to allocate device memory
+ * (a plugin inside a process that owns the allocator, a latency-critical loop,
+ * code running inside a stream capture): the partial sums go to a 4 MiB array
+ * built into the library instead of caller scratch, and the call performs no
+ * cudaMalloc / cudaFree.  Shapes whose partial sums need more than
+ * vkg_col_sum_static_max_floats() floats (see vkg_col_sum_scratch_floats) are
+ * refused with an error.  The first call on each device looks the array's
+ * device address up (cudaGetSymbolAddress); make that first call before any
+ * stream capture begins.  All calls on a device share the one array: two calls
+ * whose kernels may overlap on the GPU (different streams or devices handles on
+ * the same GPU) race on it, so keep them on one stream. */
+int vkg_col_sum_static(vkg_device* dev, const void* g, int g_dtype, float* sums,
+                       int ncol, int nrow, int accumulate);
+int64_t vkg_col_sum_static_max_floats(void);
 /* embed / embed_doc (tkernels.py:303-313, 334-345). */
 int vkg_embed(vkg_device* dev, const float* tok, const float* pos,
               const uint32_t* ids, const uint32_t* seg, float* x, int64_t n, int D,

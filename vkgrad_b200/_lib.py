@@ -98,6 +98,8 @@ _SIGNATURES = {
     "vkg_split_heads": (i32, [vp, vp, vp, i64, i32, i32, i32, i32]),
     "vkg_col_sum_det": (i32, [vp, vp, i32, vp, vp, i32, i32, i32]),
     "vkg_col_sum_scratch_floats": (i64, [i32, i32]),
+    "vkg_col_sum_static": (i32, [vp, vp, i32, vp, i32, i32, i32]),
+    "vkg_col_sum_static_max_floats": (i64, []),
     "vkg_embed": (i32, [vp, vp, vp, vp, vp, vp, i64, i32, i32]),
     "vkg_embed_bwd": (i32, [vp, vp, vp, vp, vp, vp, i64, i32, i32]),
     "vkg_residual": (i32, [vp, vp, vp, vp, vp, i64, i32]),
@@ -117,7 +119,8 @@ _SIGNATURES = {
 
 # Entries whose int return value is not a status code.
 _NOT_STATUS = {"vkg_last_error", "vkg_version", "vkg_device_stream",
-               "vkg_layernorm_bwd_scratch_floats", "vkg_col_sum_scratch_floats"}
+               "vkg_layernorm_bwd_scratch_floats", "vkg_col_sum_scratch_floats",
+               "vkg_col_sum_static_max_floats"}
 
 _lib = None
 

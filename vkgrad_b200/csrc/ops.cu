@@ -810,6 +810,77 @@ extern "C" int vkg_col_sum_det(vkg_device* dev, const void* g, int g_dtype, floa
   return vkg_check_launch("col_sum_final");
 }
 
+// ---- column sums for callers that cannot allocate -----------------------------------
+//
+// Some hosts of this library may not call cudaMalloc once they are running: a plugin
+// loaded into a process whose memory pool is owned by someone else, a real-time loop
+// that must not take the allocator's locks, or code between the begin and end of a
+// stream capture, where allocation is refused.  For them the partial sums of the
+// two-stage column reduction live in a fixed array inside the library image instead
+// of caller-provided scratch.  Every GPU that loads the library carries the array
+// (4 MiB) until the process exits.
+constexpr int64_t COLSUM_STATIC_FLOATS = 1 << 20;
+static __device__ __align__(256) float g_colsum_static[COLSUM_STATIC_FLOATS];
+
+namespace {
+std::mutex g_colsum_static_mu;
+std::map<int, float*> g_colsum_static_ptr;   // device ordinal -> device address of the array
+
+// The array's name is only a host-side handle here; kernels need its device address,
+// which differs per device and is looked up once per device with that device current.
+int colsum_static_address(vkg_device* dev, float** out) {
+  std::lock_guard<std::mutex> lock(g_colsum_static_mu);
+  auto it = g_colsum_static_ptr.find(dev->ordinal);
+  if (it != g_colsum_static_ptr.end()) {
+    *out = it->second;
+    return 0;
+  }
+  float* ptr = nullptr;
+  cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_colsum_static);
+  if (e != cudaSuccess || ptr == nullptr) {
+    vkg_set_error("col_sum_static: cudaGetSymbolAddress failed on device %d: %s", dev->ordinal,
+                  cudaGetErrorString(e));
+    return 1;
+  }
+  g_colsum_static_ptr[dev->ordinal] = ptr;
+  *out = ptr;
+  return 0;
+}
+}  // namespace
+
+extern "C" int64_t vkg_col_sum_static_max_floats(void) { return COLSUM_STATIC_FLOATS; }
+
+extern "C" int vkg_col_sum_static(vkg_device* dev, const void* g, int g_dtype, float* sums, int ncol,
+                                  int nrow, int accumulate) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(g && sums && ncol > 0 && nrow > 0, "col_sum_static: bad arguments");
+  VKG_REQUIRE(g_dtype == VKG_F32 || g_dtype == VKG_F16, "col_sum_static: dtype must be f32 or f16");
+  const int64_t need = vkg_col_sum_scratch_floats(ncol, nrow);
+  VKG_REQUIRE(need <= COLSUM_STATIC_FLOATS,
+              "col_sum_static: %d columns x %d rows needs %lld floats of partial sums, the built-in "
+              "array holds %lld; use vkg_col_sum_det with your own scratch",
+              ncol, nrow, (long long)need, (long long)COLSUM_STATIC_FLOATS);
+  float* scratch = nullptr;
+  if (colsum_static_address(dev, &scratch)) return 1;
+  // Every partial the final pass reads is overwritten by the first pass of this same
+  // call, so nothing left behind by an earlier call needs clearing.
+  int nchunk = col_sum_chunks(ncol, nrow);
+  int rpc = (nrow + nchunk - 1) / nchunk;
+  const int per_block = 32 * (g_dtype == VKG_F16 ? 8 : 4);
+  const int vec_ok = (ncol % (per_block / 32) == 0) && (((uintptr_t)g & 15) == 0);
+  dim3 grid((ncol + per_block - 1) / per_block, nchunk);
+  if (g_dtype == VKG_F16)
+    k_col_sum_partial<__half><<<grid, CS_WARPS * 32, 0, dev->stream>>>((const __half*)g, scratch,
+                                                                        ncol, nrow, rpc, vec_ok);
+  else
+    k_col_sum_partial<float><<<grid, CS_WARPS * 32, 0, dev->stream>>>((const float*)g, scratch, ncol,
+                                                                       nrow, rpc, vec_ok);
+  if (vkg_check_launch("col_sum_static partial")) return 1;
+  k_col_sum_final<<<vkg_blocks(ncol, 128), 128, 0, dev->stream>>>(scratch, sums, ncol, nchunk,
+                                                                  accumulate);
+  return vkg_check_launch("col_sum_static final");
+}
+
 extern "C" int vkg_softmax_ce(vkg_device* dev, const float* logits, const uint32_t* labels,
                               const float* w, void* dl16, float* dl32, float* loss, int rows,
                               int stride, int ncls, float grad_scale) {
