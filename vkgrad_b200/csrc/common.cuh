@@ -102,26 +102,41 @@ static inline unsigned vkg_blocks(int64_t n, int per_block, int64_t cap = (1ll <
 
 // ---- device helpers shared by the elementwise kernels ----------------------
 
-// tanh(u) = 1 - 2 / (1 + e^{2u}) with the hardware exp2 and reciprocal: absolute error
-// about 1e-7 (it saturates cleanly to +-1), a handful of instructions instead of the
-// branchy libm tanhf.  GELU only ever uses 1 + tanh and 1 - tanh^2, so absolute
-// accuracy is what matters; the GEMM epilogues that call this are issue-bound.
-__device__ __forceinline__ float vkg_tanh(float u) {
-  return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
+// GELU in its tanh form (kernels.py:624-636) written through the logistic function:
+//   0.5 x (1 + tanh(u)) = x * s,   s = 1 / (1 + e^{-2u}),   u = c (x + a x^3)
+//   d/dx               = s + x s (1 - s) * 2c (1 + 3a x^2)
+// Algebraically identical, no cancellation, and 7 / 10 instructions (one ex2 and one
+// rcp on the special-function unit) instead of libm tanhf: the GEMM epilogues that call
+// these are instruction-issue bound.
+__device__ __forceinline__ float vkg_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float vkg_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// s = 1 / (1 + exp(-2 c (x + a x^3))), with -2 c log2(e) folded into the polynomial
+__device__ __forceinline__ float vkg_gelu_gate(float x, float x2) {
+  const float k1 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
+  const float k3 = k1 * 0.044715f;
+  return vkg_rcp(1.0f + vkg_ex2(x * fmaf(x2, k3, k1)));
 }
 
 __device__ __forceinline__ float vkg_gelu(float x) {
-  const float c = 0.7978845608028654f;  // sqrt(2/pi)
-  float x3 = x * x * x;
-  return 0.5f * x * (1.0f + vkg_tanh(c * (x + 0.044715f * x3)));
+  return x * vkg_gelu_gate(x, x * x);
 }
 
 __device__ __forceinline__ float vkg_dgelu(float x) {
-  const float c = 0.7978845608028654f;
-  float x3 = x * x * x;
-  float t = vkg_tanh(c * (x + 0.044715f * x3));
-  float sech2 = 1.0f - t * t;
-  return 0.5f * (1.0f + t) + 0.5f * x * sech2 * c * (1.0f + 3.0f * 0.044715f * x * x);
+  const float c2 = 2.0f * 0.7978845608028654f;
+  const float x2 = x * x;
+  const float s = vkg_gelu_gate(x, x2);
+  const float w = fmaf(x2, c2 * 3.0f * 0.044715f, c2);   // 2c (1 + 3a x^2)
+  return fmaf(x * fmaf(-s, s, s), w, s);
 }
 
 __device__ __forceinline__ float vkg_act(float v, int act) {
