@@ -223,6 +223,15 @@ int vkg_attn_softmax(vkg_device* dev, const float* s, const uint32_t* seg,
 int vkg_attn_softmax_bwd(vkg_device* dev, const float* dp, const void* p16,
                          void* ds16, int64_t rows, int T, float scale,
                          int fill_block);
+/* Fused causal attention, head dimension 64: one kernel for
+ * QK^T matmul + attn_softmax(_doc) + PV matmul (transformer.py:141-157,
+ * tkernels.py:105-161) with no T x T tensor in memory.  qkv16 is the (B*T, 3D)
+ * fp16 projection with the qkv bias already added; out16 receives the
+ * head-merged (B*T, D) fp16 attention output (what merge_heads produces,
+ * tkernels.py:274-286); lse2 (B*H, T) receives log2(sum_j exp(scale * s_ij)),
+ * which the backward kernels use to rebuild P. */
+int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* seg,
+                 void* out16, float* lse2, int B, int T, int H, int hd, float scale);
 /* split_qkv / merge_qkv_grad / merge_heads / split_heads (tkernels.py:195-300). */
 int vkg_split_qkv(vkg_device* dev, const float* qkv, const float* bias, void* q16,
                   void* k16, void* v16, int64_t n, int D, int T, int H, int hd);

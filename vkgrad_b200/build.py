@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libvkgrad_b200.so")
 STAMP = os.path.join(HERE, "csrc", ".build_stamp")
-SOURCES = ["runtime.cu", "gemm_sm100.cu", "ops.cu", "comm.cu"]
+SOURCES = ["runtime.cu", "gemm_sm100.cu", "attn_sm100.cu", "ops.cu", "comm.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -1,0 +1,322 @@
+// Fused causal attention for sm_100a, head dimension 64: replaces the reference's
+// per-layer chain  QK^T matmul -> attn_softmax -> PV matmul  (transformer.py:144-155)
+// and its backward chain (transformer.py:167-182) without ever writing the T x T score,
+// probability or gradient tensors to HBM.
+//
+// Forward, one CTA per (128-query tile, head, sequence), 192 threads:
+//   warp 0      TMA producer: Q once, then K tiles (pass 1), then K and V tiles (pass 2)
+//   warp 1      TMEM allocation + single-thread tcgen05.mma issue
+//   warps 2..5  softmax: TMEM lane = query row, so every thread owns one row and the
+//               row maximum / sum need no cross-thread reduction
+// Two passes over the key tiles instead of the usual running rescale of O:
+//   pass 1  S = Q K^T  -> row max m and row sum l (online)
+//   pass 2  S again, P = exp(S - m) / l rounded to fp16 into swizzled shared memory,
+//           O += P V accumulated in TMEM
+// QK^T has K = 64, so doing it twice costs little and keeps O free of rescaling.
+// The fp16 rounding points are the reference's: P is rounded before P V
+// (tkernels.py:123), O is stored fp16 (tkernels.py:284).
+// Every wait is bounded (see tcgen05.cuh); a wait that gives up flags the error word,
+// all roles leave their loops, TMEM is freed and the CTA returns.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace {
+
+using namespace tc05;
+
+constexpr int FA_T = 128;          // query / key tile
+constexpr int FA_HD = 64;          // head dimension
+constexpr int FA_TILE_BYTES = FA_T * FA_HD * 2;  // 16 KB: one 128 x 64 fp16 tile, 128 B rows
+constexpr int FA_THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnParams {
+  int B, T, H, D;
+  int nqt;                 // query tiles per sequence
+  float cscale;            // softmax scale * log2(e)
+  float scale;
+  const uint32_t* seg;     // optional packed-sample starts (b*T + t)
+  __half* out;             // forward: O, head-merged (rows, D)
+  float* lse2;             // (B*H, T): row log2-sum-exp of the scaled scores
+  const float* delta;      // backward: rowsum(dO * O), (B*H, T)
+  __half* dqkv;            // backward: (rows, 3D)
+  uint32_t* err;
+};
+
+// forward shared memory map (offsets from a 1024-aligned base)
+constexpr int FW_Q = 0;
+constexpr int FW_K = FW_Q + FA_TILE_BYTES;            // two K stages
+constexpr int FW_V = FW_K + 2 * FA_TILE_BYTES;        // one V stage
+constexpr int FW_P = FW_V + FA_TILE_BYTES;            // P: two 64-key blocks of 128 rows x 128 B
+constexpr int FW_BAR = FW_P + 2 * FA_TILE_BYTES;
+constexpr int FW_SMEM = FW_BAR + 256 + 1024;
+
+// 16-byte chunk `c8` (8 keys) of 64-key block `kb`, row r, in the 128B-swizzled layout
+// both TMA and the UMMA descriptors use.
+__device__ __forceinline__ uint32_t p_offset(int kb, int r, int c8) {
+  return (uint32_t)(kb * FA_TILE_BYTES + r * 128 + ((c8 ^ (r & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar = base + FW_BAR;
+  // barriers: 0 q_full, 1-2 k_full, 3-4 k_empty, 5 v_full, 6 v_empty, 7 s_full, 8 s_free,
+  //           9 p_full, 10 p_free, 11 o_full
+  auto B_ = [bar](int i) { return bar + 8u * i; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + FW_BAR + 128);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + FW_BAR + 136);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int HB = p.H * p.B;
+  const int qt = p.nqt - 1 - (int)(blockIdx.x / HB);   // heaviest query tiles first
+  const int hb = blockIdx.x % HB;
+  const int h = hb % p.H, b = hb / p.H;
+  const int q0 = qt * FA_T;
+  const int nj = qt + 1;                                 // key tiles 0..qt
+  const int row0 = b * p.T;                              // first row of this sequence
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 12; ++i) mbar_init(B_(i), (i == 8 || i == 9) ? 4 : 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 256);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(B_(0), FA_TILE_BYTES);
+      tma_load_2d(base + FW_Q, &tm, B_(0), h * FA_HD, row0 + q0);
+      int it = 0;
+      for (int pass = 0; pass < 2 && ok; ++pass) {
+        for (int j = 0; j < nj && ok; ++j, ++it) {
+          const int s = it & 1;
+          ok = mbar_wait(B_(3 + s), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x1100u + s);
+          if (!ok) break;
+          mbar_expect_tx(B_(1 + s), FA_TILE_BYTES);
+          tma_load_2d(base + FW_K + s * FA_TILE_BYTES, &tm, B_(1 + s), p.D + h * FA_HD,
+                      row0 + j * FA_T);
+          if (pass == 1) {
+            ok = mbar_wait(B_(6), (j & 1) ^ 1u, abort_flag, p.err, 0x1200u);
+            if (!ok) break;
+            mbar_expect_tx(B_(5), FA_TILE_BYTES);
+            tma_load_2d(base + FW_V, &tm, B_(5), 2 * p.D + h * FA_HD, row0 + j * FA_T);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);     // Q K^T: both K-major, N = 128 keys
+      const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);    // P V: P K-major, V MN-major, N = 64
+      bool ok = mbar_wait(B_(0), 0, abort_flag, p.err, 0x2000u);
+      int it = 0;
+      for (int pass = 0; pass < 2 && ok; ++pass) {
+        for (int j = 0; j < nj && ok; ++j, ++it) {
+          const int s = it & 1;
+          ok = mbar_wait(B_(1 + s), (it >> 1) & 1, abort_flag, p.err, 0x2100u + s) &&
+               mbar_wait(B_(8), (it & 1) ^ 1u, abort_flag, p.err, 0x2200u);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t sq = base + FW_Q, sk = base + FW_K + s * FA_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
+                     idesc_s, k ? 1u : 0u);
+          umma_commit(B_(3 + s));   // K stage free once these retire
+          umma_commit(B_(7));       // S ready
+          if (pass == 1) {
+            ok = mbar_wait(B_(9), j & 1, abort_flag, p.err, 0x2300u) &&
+                 mbar_wait(B_(5), j & 1, abort_flag, p.err, 0x2400u);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t sp = base + FW_P, sv = base + FW_V;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              umma_f16(tO,
+                       make_smem_desc(sp + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
+                       make_smem_desc(sv + kk * 2048, 8192, 1024), idesc_o, (j | kk) ? 1u : 0u);
+            umma_commit(B_(6));     // V free
+            umma_commit(B_(10));    // P free
+          }
+        }
+      }
+      if (ok) umma_commit(B_(11));
+    }
+  } else {
+    const int qr = (warp & 3) * 32 + lane;      // row within the tile = TMEM lane
+    const int qi = q0 + qr;                     // query index in the sequence
+    const bool q_ok = qi < p.T;
+    const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
+    const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
+    float m = -1e30f, l = 0.f, inv_l = 0.f;
+    bool ok = true;
+    int it = 0;
+    for (int pass = 0; pass < 2 && ok; ++pass) {
+      for (int j = 0; j < nj && ok; ++j, ++it) {
+        ok = mbar_wait(B_(7), it & 1, abort_flag, p.err, 0x3100u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const bool need_mask = (j == qt) || (p.seg != nullptr);
+        if (pass == 1) {
+          ok = mbar_wait(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x3200u);
+          if (!ok) break;
+        }
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld16(tS + t_lane + c * 32, r);
+          tmem_ld16(tS + t_lane + c * 32 + 16, r + 16);
+          tmem_wait_ld();
+          float t[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            t[e] = __uint_as_float(r[e]) * p.cscale;
+            if (need_mask) {
+              const int key = j * FA_T + c * 32 + e;
+              if (key > qi || key < st) t[e] = -1e30f;
+            }
+          }
+          if (pass == 0) {
+            float cm = m;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) cm = fmaxf(cm, t[e]);
+            float sum = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sum += t[e] <= -1e29f ? 0.f : vkg_ex2(t[e] - cm);
+            l = l * vkg_ex2(m - cm) + sum;
+            m = cm;
+          } else {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              __half2 hv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float a = t[u * 8 + 2 * e], bb = t[u * 8 + 2 * e + 1];
+                hv[e] = __floats2half2_rn(a <= -1e29f ? 0.f : vkg_ex2(a - m) * inv_l,
+                                          bb <= -1e29f ? 0.f : vkg_ex2(bb - m) * inv_l);
+              }
+              const int cc = c * 4 + u;
+              *reinterpret_cast<uint4*>(gbase + FW_P + p_offset(cc >> 3, qr, cc & 7)) =
+                  *reinterpret_cast<uint4*>(hv);
+            }
+          }
+        }
+        tcgen05_fence_before();
+        if (pass == 1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(B_(8));                    // S may be overwritten
+          if (pass == 1) mbar_arrive(B_(9));     // P is in shared memory
+        }
+      }
+      if (pass == 0) {
+        // masked entries contributed exp2(-1e30 - m) = 0; l >= 1 because key == query is valid
+        inv_l = 1.0f / l;
+        if (q_ok) p.lse2[(size_t)(b * p.H + h) * p.T + qi] = m + log2f(l);
+      }
+    }
+    if (ok) ok = mbar_wait(B_(11), 0, abort_flag, p.err, 0x3300u);
+    if (ok) {
+      tcgen05_fence_after();
+      uint32_t r[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(tO + t_lane + c * 16, r + c * 16);
+      tmem_wait_ld();
+      if (q_ok) {
+        __half* dst = p.out + (size_t)(row0 + qi) * p.D + h * FA_HD;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          __half2 hv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            hv[e] = __floats2half2_rn(__uint_as_float(r[u * 8 + 2 * e]),
+                                      __uint_as_float(r[u * 8 + 2 * e + 1]));
+          *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 2-D map over a row-major fp16 matrix (rows x cols), 64-column x 128-row boxes.
+int make_map_2d(vkg_device* dev, CUtensorMap* map, const void* ptr, int64_t cols, int64_t rows,
+                const char* what) {
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(cols * 2)};
+  cuuint32_t box[2] = {FA_HD, FA_T};
+  cuuint32_t estr[2] = {1, 1};
+  if (((uintptr_t)ptr & 15) || ((cols * 2) & 15)) {
+    vkg_set_error("attention operand %s must be 16-byte aligned with a 16-byte row pitch", what);
+    return 1;
+  }
+  CUresult r = ((EncodeTiledFn)dev->encode_tiled)(
+      map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    vkg_set_error("cuTensorMapEncodeTiled failed for %s with code %d", what, (int)r);
+    return 1;
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* seg, void* out16,
+                            float* lse2, int B, int T, int H, int hd, float scale) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(qkv16 && out16 && lse2 && B > 0 && T > 0 && H > 0, "attn_fwd: bad arguments");
+  VKG_REQUIRE(hd == FA_HD, "attn_fwd: head dimension must be %d (got %d)", FA_HD, hd);
+  VKG_REQUIRE(((uintptr_t)out16 & 15) == 0, "attn_fwd: output must be 16-byte aligned");
+  const int D = H * hd;
+  CUtensorMap tm;
+  if (make_map_2d(dev, &tm, qkv16, 3 * (int64_t)D, (int64_t)B * T, "qkv")) return 1;
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = B; p.T = T; p.H = H; p.D = D;
+  p.nqt = (T + FA_T - 1) / FA_T;
+  p.scale = scale;
+  p.cscale = scale * LOG2E;
+  p.seg = seg;
+  p.out = (__half*)out16;
+  p.lse2 = lse2;
+  p.err = dev->err_dev;
+  static bool attr_set = false;
+  if (!attr_set) {
+    VKG_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  FW_SMEM));
+    attr_set = true;
+  }
+  const long long ctas = (long long)p.nqt * H * B;
+  VKG_REQUIRE(ctas < (1ll << 31), "attn_fwd: too many tiles");
+  attn_fwd_kernel<<<(unsigned)ctas, FA_THREADS, FW_SMEM, dev->stream>>>(tm, p);
+  return vkg_check_launch("attn_fwd_kernel");
+}

@@ -20,8 +20,11 @@
 // sets an error word the host reads at the next synchronisation, the CTA
 // stops issuing work, frees its TMEM and returns.
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
+
+using namespace tc05;
 
 constexpr int BM = 128;            // rows of C per tile = UMMA M
 constexpr int BK = 64;             // K elements per stage = 128 bytes of f16 = one swizzle row
@@ -37,7 +40,6 @@ constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;  // one 32x32 fp32 chunk per epilog
 constexpr int SMEM_BYTES = RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024 /*align slack*/ +
                            256 /*barriers*/;
 constexpr int GROUP_M = 8;         // m-tiles per rasterisation band
-constexpr long long WAIT_BUDGET_CYCLES = 2000000000ll;  // ~1 s
 
 struct GemmParams {
   int M, N, K;
@@ -59,110 +61,6 @@ struct GemmParams {
   float alpha;
   uint32_t* err;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-
-// Bounded wait.  Returns false when the wait gave up or another role already
-// flagged an abort; the caller then leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* err, uint32_t where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
-        *abort_flag = 1u;
-        if (atomicCAS(err, 0u, VKG_ERR_WAIT_TIMEOUT) == 0u) err[1] = where;
-        __threadfence_system();
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%2, %3, %4, %5}], [%6];"
-      ::"r"(dst), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell version field.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= 1ull << 46;  // descriptor version for sm_100
-  d |= 2ull << 61;  // SWIZZLE_128B
-  return d;
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                         uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
 
 struct TileCoord {
   int z0, z1, m0, n0;
@@ -605,9 +503,9 @@ int make_map(vkg_device* dev, CUtensorMap* map, const void* ptr, int dtype, int6
 }
 
 // Tile width and K split for one GEMM, from a small time model (microseconds).
-// Measured on B200: a k-block (64 K-elements, four tcgen05.mma) costs about the same
-// 0.36 us whether the tile is 64 or 256 columns wide, so narrow tiles waste the tensor
-// core; an epilogue costs ~3.5 us per 128x256 fp32 tile.  When the grid cannot fill
+// Measured on B200: a k-block (64 K-elements, four tcgen05.mma) costs 0.33 us even for a
+// 64-column tile and only 0.41 us for 256 columns, so narrow tiles waste the tensor
+// core; an epilogue costs ~4.4 us per 128x256 tile.  When the grid cannot fill
 // the SMs with wide tiles (the dW shapes: few output tiles, K = rows of the batch),
 // K is split across CTAs and a second pass adds the slices.
 void plan_gemm(int M, int N, int K, int batch, int sms, bool may_split, int64_t ws_bytes,
@@ -623,8 +521,9 @@ void plan_gemm(int M, int N, int K, int batch, int sms, bool may_split, int64_t 
     const int bn = cand[i];
     if (force_bn ? bn != force_bn : (bn > n_round && bn != 64)) continue;
     const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn) * batch;
-    const double t_kb = bn >= 256 ? 0.34 : 0.36;
-    const double t_epi = 3.5 * bn / 256.0;
+    // measured per k-block at K = 6144: 0.41 / 0.36 / 0.33 / 0.33 us for 256 / 192 / 128 / 64
+    const double t_kb = bn >= 256 ? 0.41 : bn >= 192 ? 0.36 : 0.33;
+    const double t_epi = 4.4 * bn / 256.0;
     for (int sp = 1; sp <= 16; ++sp) {
       if (force_split > 0 && sp != force_split) continue;
       if (sp > 1) {
