@@ -232,6 +232,15 @@ int vkg_attn_softmax_bwd(vkg_device* dev, const float* dp, const void* p16,
  * which the backward kernels use to rebuild P. */
 int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* seg,
                  void* out16, float* lse2, int B, int T, int H, int hd, float scale);
+/* Backward of vkg_attn_fwd: the reference's split_heads, four batched matmuls,
+ * attn_softmax_bwd and merge_qkv_grad (transformer.py:160-186, tkernels.py:167-232)
+ * as three launches: delta = rowsum(dO * O), a dK/dV kernel (one CTA per key tile)
+ * and a dQ kernel (one CTA per query tile), both rebuilding P from lse2.
+ * dout16 is the (B*T, D) fp16 gradient of out16; dqkv16 (B*T, 3D) fp16 receives
+ * [dQ | dK | dV]; delta is B*H*T floats of scratch.  Deterministic (no atomics). */
+int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout16,
+                 const void* out16, const float* lse2, const uint32_t* seg,
+                 void* dqkv16, float* delta, int B, int T, int H, int hd, float scale);
 /* split_qkv / merge_qkv_grad / merge_heads / split_heads (tkernels.py:195-300). */
 int vkg_split_qkv(vkg_device* dev, const float* qkv, const float* bias, void* q16,
                   void* k16, void* v16, int64_t n, int D, int T, int H, int hd);

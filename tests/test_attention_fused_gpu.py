@@ -73,3 +73,50 @@ def test_forward(dev, B, T, H, packed):
     assert np.abs(get(bl, np.float32, (B, H, T)) - lse2).max() < 1e-3
     for x in (bq, bo, bl) + (() if bs is None else (bs,)):
         x.destroy()
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 320, 2), (1, 1024, 2), (2, 72, 1)])
+@pytest.mark.parametrize("packed", [False, True])
+def test_backward(dev, B, T, H, packed):
+    from vkgrad_b200.vk import _check
+    hd, D = 64, H * 64
+    rng = np.random.default_rng(7 * T + H)
+    qkv = rng.standard_normal((B * T, 3 * D)).astype(np.float16)
+    dout = (0.1 * rng.standard_normal((B * T, D))).astype(np.float16)
+    seg = None
+    if packed:
+        seg = np.zeros((B, T), np.uint32)
+        seg[:, T // 2:] = T // 2
+        seg = seg.reshape(-1)
+    scale = 1.0 / np.sqrt(hd)
+    bq, bdo = up(dev, qkv), up(dev, dout)
+    bo = up(dev, np.zeros((B * T, D), np.float16))
+    bl = up(dev, np.zeros((B * H, T), np.float32))
+    bdelta = up(dev, np.zeros((B * H, T), np.float32))
+    bdq = up(dev, np.full((B * T, 3 * D), np.nan, np.float16))
+    bs = None if seg is None else up(dev, seg)
+    segp = None if bs is None else bs.dptr
+    _check(dev.lib.vkg_attn_fwd(dev.handle, bq.dptr, segp, bo.dptr, bl.dptr, B, T, H, hd, scale),
+           "attn_fwd")
+    outs = []
+    for _ in range(2):
+        _check(dev.lib.vkg_attn_bwd(dev.handle, bq.dptr, bdo.dptr, bo.dptr, bl.dptr, segp, bdq.dptr,
+                                    bdelta.dptr, B, T, H, hd, scale), "attn_bwd")
+        dev.sync()
+        outs.append(get(bdq, np.float16, (B * T, 3 * D)).astype(np.float32))
+    assert np.array_equal(outs[0], outs[1]), "backward is not deterministic"
+    got = outs[0]
+    assert np.isfinite(got).all()
+    q, k, v, p, o, lse2, mask = reference_attention(qkv, B, T, H, scale, seg)
+    dao = dout.astype(np.float32).reshape(B, T, H, hd).transpose(0, 2, 1, 3)
+    dv = p.transpose(0, 1, 3, 2) @ dao
+    dp = dao @ v.transpose(0, 1, 3, 2)
+    ds = orc.r16(p * (dp - (dp * p).sum(-1, keepdims=True)) * scale)
+    dq = ds @ k
+    dk = ds.transpose(0, 1, 3, 2) @ q
+    merge = lambda t: t.transpose(0, 2, 1, 3).reshape(B * T, D)
+    for name, ref, sl in (("dq", dq, slice(0, D)), ("dk", dk, slice(D, 2 * D)),
+                          ("dv", dv, slice(2 * D, 3 * D))):
+        assert relerr(got[:, sl], merge(ref)) < 3e-3, name
+    for x in (bq, bdo, bo, bl, bdelta, bdq) + (() if bs is None else (bs,)):
+        x.destroy()

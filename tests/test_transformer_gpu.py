@@ -196,12 +196,14 @@ def test_loss_scale_cancels(dev):
     assert relerr(grads[1], grads[0]) < 2e-3
 
 
-@pytest.mark.parametrize("T,H,D", [(384, 2, 64), (320, 1, 64)])
-def test_long_context_causal_tiles(dev, T, H, D):
-    """Sequences longer than one 128-row tile: score tiles above the diagonal are
-    skipped and the P/dS products clip their K range, so results must still match the
-    oracle, and memory the skipped tiles never wrote must not leak in (it is filled
-    with NaN first)."""
+@pytest.mark.parametrize("T,H,D,fused", [(384, 2, 64, None), (320, 1, 64, False),
+                                         (320, 1, 64, True), (384, 2, 128, True)])
+def test_long_context_causal_tiles(dev, T, H, D, fused):
+    """Sequences longer than one 128-row tile, through both attention paths.  Unfused
+    (batched GEMMs + softmax): score tiles above the diagonal are skipped and the P/dS
+    products clip their K range; memory the skipped tiles never wrote must not leak in
+    (it is filled with NaN first).  Fused (head dimension 64): the tcgen05 attention
+    kernels.  Both must match the oracle."""
     from vkgrad_b200.transformer import GPT, TCtx
     B, L, V = 2, 1, 64
     Vp = 64
@@ -211,11 +213,13 @@ def test_long_context_causal_tiles(dev, T, H, D):
     tgt = rng.integers(0, V, B * T).astype(np.uint32)
     ctx = TCtx(dev)
     try:
-        model = GPT(ctx, B, T, D, H, L, V, tie=True)
+        model = GPT(ctx, B, T, D, H, L, V, tie=True, fused_attention=fused)
         load_params(model, P)
         att = model.blocks[0].attn
-        for buf, dt in ((att.scores, np.float32), (att.dp32, np.float32), (att.p16, np.float16),
-                        (att.ds16, np.float16)):
+        assert att.fused == (D // H == 64 if fused is None else fused)
+        poison = [] if att.fused else [(att.scores, np.float32), (att.dp32, np.float32),
+                                       (att.p16, np.float16), (att.ds16, np.float16)]
+        for buf, dt in poison:
             tmp = dev.buffer(buf.size, "cached")
             tmp.array(dt)[:] = np.nan
             tmp.flush()

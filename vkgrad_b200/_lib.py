@@ -93,6 +93,7 @@ _SIGNATURES = {
     "vkg_attn_softmax": (i32, [vp, vp, vp, vp, i64, i32, i32, f32, i32]),
     "vkg_attn_softmax_bwd": (i32, [vp, vp, vp, vp, i64, i32, f32, i32]),
     "vkg_attn_fwd": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32]),
+    "vkg_attn_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32]),
     "vkg_split_qkv": (i32, [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32]),
     "vkg_merge_qkv_grad": (i32, [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32]),
     "vkg_merge_heads": (i32, [vp, vp, vp, i64, i32, i32, i32, i32]),

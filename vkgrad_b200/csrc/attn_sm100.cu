@@ -261,6 +261,391 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   }
 }
 
+// ---- backward --------------------------------------------------------------------------
+//
+// delta[row, h] = sum_d dO * O (equals sum_j dP_ij P_ij of tkernels.py:176-179).
+__global__ void attn_delta_kernel(const __half* __restrict__ dout, const __half* __restrict__ out,
+                                  float* __restrict__ delta, int B, int T, int H) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;   // (row, h)
+  if (item >= (long long)B * T * H) return;
+  const int h = (int)(item % H);
+  const long long row = item / H;
+  const int b = (int)(row / T), t = (int)(row % T);
+  const size_t off = (size_t)row * H * FA_HD + h * FA_HD + lane * 2;
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(dout + off));
+  const float2 o = __half22float2(*reinterpret_cast<const __half2*>(out + off));
+  const float s = warp_sum(a.x * o.x + a.y * o.y);
+  if (lane == 0) delta[(size_t)(b * H + h) * T + t] = s;
+}
+
+// One 32-key chunk of a (query row, key tile) pair: rebuild P from S and the saved
+// log-sum-exp, form dS = P (dP - delta) scale, and write both (fp16) into the swizzled
+// [query row][key] layout.  `sp` / `sds` may be null.
+__device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rdp, int c, int r,
+                                          int key0, int qi, int st, bool q_ok, bool need_mask,
+                                          float cscale, float scale, float lse2, float delta,
+                                          uint8_t* sp, uint8_t* sds) {
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    __half2 hp[4], hd[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float pv[2], dv[2];
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const int idx = u * 8 + 2 * e + w;
+        const int key = key0 + c * 32 + idx;
+        bool valid = q_ok;
+        if (need_mask) valid = valid && key <= qi && key >= st;
+        const float pr = valid ? vkg_ex2(__uint_as_float(rs[idx]) * cscale - lse2) : 0.f;
+        pv[w] = pr;
+        dv[w] = pr * (__uint_as_float(rdp[idx]) - delta) * scale;
+      }
+      hp[e] = __floats2half2_rn(pv[0], pv[1]);
+      hd[e] = __floats2half2_rn(dv[0], dv[1]);
+    }
+    const int cc = c * 4 + u;
+    const uint32_t off = p_offset(cc >> 3, r, cc & 7);
+    if (sp) *reinterpret_cast<uint4*>(sp + off) = *reinterpret_cast<uint4*>(hp);
+    if (sds) {
+      // dS must be built from the ROUNDED P, as the unfused path reads p16 back
+      // (tkernels.py:182): recompute from the fp16 values just formed
+      __half2 hd2[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 pf = __half22float2(hp[e]);
+        hd2[e] = __floats2half2_rn(
+            pf.x * (__uint_as_float(rdp[u * 8 + 2 * e]) - delta) * scale,
+            pf.y * (__uint_as_float(rdp[u * 8 + 2 * e + 1]) - delta) * scale);
+      }
+      *reinterpret_cast<uint4*>(sds + off) = *reinterpret_cast<uint4*>(hd2);
+    }
+    (void)hd;
+  }
+}
+
+// dK / dV: one CTA per (key tile, head, sequence); loops over the query tiles at or
+// below the diagonal.  TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384).
+constexpr int KV_K = 0, KV_V = FA_TILE_BYTES, KV_Q = 2 * FA_TILE_BYTES, KV_DO = 4 * FA_TILE_BYTES,
+              KV_P = 6 * FA_TILE_BYTES, KV_DS = 8 * FA_TILE_BYTES, KV_BAR = 10 * FA_TILE_BYTES,
+              KV_SMEM = KV_BAR + 256 + 1024;
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
+                   const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar = base + KV_BAR;
+  // 0 kv_full, 1-2 qd_full, 3-4 qd_empty, 5 sdp_full, 6 sdp_free, 7 pds_full, 8 pds_free, 9 out_full
+  auto B_ = [bar](int i) { return bar + 8u * i; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 128);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 136);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int HB = p.H * p.B;
+  const int kt = (int)(blockIdx.x / HB);            // key tile; tile 0 has the most work, first
+  const int hb = blockIdx.x % HB;
+  const int h = hb % p.H, b = hb / p.H;
+  const int row0 = b * p.T, k0 = kt * FA_T;
+  const int ni = p.nqt - kt;                         // query tiles kt .. nqt-1
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 10; ++i) mbar_init(B_(i), (i == 6 || i == 7) ? 4 : 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 320;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(B_(0), 2 * FA_TILE_BYTES);
+      tma_load_2d(base + KV_K, &tm, B_(0), p.D + h * FA_HD, row0 + k0);
+      tma_load_2d(base + KV_V, &tm, B_(0), 2 * p.D + h * FA_HD, row0 + k0);
+      for (int it = 0; it < ni; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait(B_(3 + s), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4100u + s)) break;
+        mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
+        const int qrow = row0 + (kt + it) * FA_T;
+        tma_load_2d(base + KV_Q + s * FA_TILE_BYTES, &tm, B_(1 + s), h * FA_HD, qrow);
+        tma_load_2d(base + KV_DO + s * FA_TILE_BYTES, &tmdo, B_(1 + s), h * FA_HD, qrow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);    // [q x hd] . [key x hd]^T
+      const uint32_t idesc_g = make_idesc(0, 1, 1, FA_HD);   // [q x key]^T . [q x hd]
+      bool ok = mbar_wait(B_(0), 0, abort_flag, p.err, 0x4200u);
+      for (int it = 0; it < ni && ok; ++it) {
+        const int s = it & 1;
+        ok = mbar_wait(B_(1 + s), (it >> 1) & 1, abort_flag, p.err, 0x4300u + s) &&
+             mbar_wait(B_(6), (it & 1) ^ 1u, abort_flag, p.err, 0x4400u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
+        const uint32_t sk = base + KV_K, sv = base + KV_V;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
+                   idesc_s, k ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tdP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024),
+                   idesc_s, k ? 1u : 0u);
+        umma_commit(B_(5));
+        ok = mbar_wait(B_(7), it & 1, abort_flag, p.err, 0x4500u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t sp = base + KV_P, sds = base + KV_DS;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)      // K = 128 query rows, 16 at a time
+          umma_f16(tdV, make_smem_desc(sp + kk * 2048, FA_TILE_BYTES, 1024),
+                   make_smem_desc(sdo + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tdK, make_smem_desc(sds + kk * 2048, FA_TILE_BYTES, 1024),
+                   make_smem_desc(sq + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
+        umma_commit(B_(3 + s));   // Q / dO stage free
+        umma_commit(B_(8));       // P / dS free
+      }
+      if (ok) umma_commit(B_(9));
+    }
+  } else {
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
+    bool ok = true;
+    for (int it = 0; it < ni && ok; ++it) {
+      const int qt = kt + it;
+      const int qi = qt * FA_T + r;
+      const bool q_ok = qi < p.T;
+      const size_t sidx = (size_t)(b * p.H + h) * p.T + (q_ok ? qi : 0);
+      const float lse2 = p.lse2[sidx], delta = p.delta[sidx];
+      const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
+      const bool need_mask = (qt == kt) || (p.seg != nullptr);
+      ok = mbar_wait(B_(5), it & 1, abort_flag, p.err, 0x4600u) &&
+           mbar_wait(B_(8), (it & 1) ^ 1u, abort_flag, p.err, 0x4700u);
+      if (!ok) break;
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rdp[32];
+        tmem_ld16(tS + t_lane + c * 32, rs);
+        tmem_ld16(tS + t_lane + c * 32 + 16, rs + 16);
+        tmem_ld16(tdP + t_lane + c * 32, rdp);
+        tmem_ld16(tdP + t_lane + c * 32 + 16, rdp + 16);
+        tmem_wait_ld();
+        bwd_chunk(rs, rdp, c, r, k0, qi, st, q_ok, need_mask, p.cscale, p.scale, lse2, delta,
+                  gbase + KV_P, gbase + KV_DS);
+      }
+      tcgen05_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(B_(6));
+        mbar_arrive(B_(7));
+      }
+    }
+    if (ok) ok = mbar_wait(B_(9), 0, abort_flag, p.err, 0x4800u);
+    if (ok) {
+      tcgen05_fence_after();
+      const int key = k0 + r;     // accumulator rows are keys here
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        uint32_t rr[64];
+        const uint32_t t = (which == 0 ? tdV : tdK) + t_lane;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld16(t + c * 16, rr + c * 16);
+        tmem_wait_ld();
+        if (key < p.T) {
+          __half* dst = p.dqkv + (size_t)(row0 + key) * 3 * p.D + (which == 0 ? 2 : 1) * p.D + h * FA_HD;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            __half2 hv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              hv[e] = __floats2half2_rn(__uint_as_float(rr[u * 8 + 2 * e]),
+                                        __uint_as_float(rr[u * 8 + 2 * e + 1]));
+            *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// dQ: one CTA per (query tile, head, sequence); loops over the key tiles up to the
+// diagonal.  TMEM: S [0,128) dP [128,256) dQ [256,320).
+constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_K = 2 * FA_TILE_BYTES, DQ_V = 4 * FA_TILE_BYTES,
+              DQ_DS = 6 * FA_TILE_BYTES, DQ_BAR = 8 * FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
+                  const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar = base + DQ_BAR;
+  // 0 qd_full, 1-2 kv_full, 3-4 kv_empty, 5 sdp_full, 6 sdp_free, 7 ds_full, 8 ds_free, 9 out_full
+  auto B_ = [bar](int i) { return bar + 8u * i; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 128);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 136);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int HB = p.H * p.B;
+  const int qt = p.nqt - 1 - (int)(blockIdx.x / HB);
+  const int hb = blockIdx.x % HB;
+  const int h = hb % p.H, b = hb / p.H;
+  const int row0 = b * p.T, q0 = qt * FA_T;
+  const int nj = qt + 1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 10; ++i) mbar_init(B_(i), (i == 6 || i == 7) ? 4 : 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(B_(0), 2 * FA_TILE_BYTES);
+      tma_load_2d(base + DQ_Q, &tm, B_(0), h * FA_HD, row0 + q0);
+      tma_load_2d(base + DQ_DO, &tmdo, B_(0), h * FA_HD, row0 + q0);
+      for (int j = 0; j < nj; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(B_(3 + s), ((j >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5100u + s)) break;
+        mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
+        tma_load_2d(base + DQ_K + s * FA_TILE_BYTES, &tm, B_(1 + s), p.D + h * FA_HD, row0 + j * FA_T);
+        tma_load_2d(base + DQ_V + s * FA_TILE_BYTES, &tm, B_(1 + s), 2 * p.D + h * FA_HD,
+                    row0 + j * FA_T);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
+      const uint32_t idesc_q = make_idesc(0, 0, 1, FA_HD);   // dS (K-major) . K (MN-major), N = 64
+      bool ok = mbar_wait(B_(0), 0, abort_flag, p.err, 0x5200u);
+      for (int j = 0; j < nj && ok; ++j) {
+        const int s = j & 1;
+        ok = mbar_wait(B_(1 + s), (j >> 1) & 1, abort_flag, p.err, 0x5300u + s) &&
+             mbar_wait(B_(6), (j & 1) ^ 1u, abort_flag, p.err, 0x5400u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t sq = base + DQ_Q, sdo = base + DQ_DO;
+        const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES, sv = base + DQ_V + s * FA_TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
+                   idesc_s, k ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tdP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024),
+                   idesc_s, k ? 1u : 0u);
+        umma_commit(B_(5));
+        ok = mbar_wait(B_(7), j & 1, abort_flag, p.err, 0x5500u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t sds = base + DQ_DS;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)      // K = 128 keys
+          umma_f16(tdQ, make_smem_desc(sds + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
+                   make_smem_desc(sk + kk * 2048, 8192, 1024), idesc_q, (j | kk) ? 1u : 0u);
+        umma_commit(B_(3 + s));   // K / V stage free
+        umma_commit(B_(8));       // dS free
+      }
+      if (ok) umma_commit(B_(9));
+    }
+  } else {
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
+    const int qi = q0 + r;
+    const bool q_ok = qi < p.T;
+    const size_t sidx = (size_t)(b * p.H + h) * p.T + (q_ok ? qi : 0);
+    const float lse2 = p.lse2[sidx], delta = p.delta[sidx];
+    const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
+    bool ok = true;
+    for (int j = 0; j < nj && ok; ++j) {
+      const bool need_mask = (j == qt) || (p.seg != nullptr);
+      ok = mbar_wait(B_(5), j & 1, abort_flag, p.err, 0x5600u) &&
+           mbar_wait(B_(8), (j & 1) ^ 1u, abort_flag, p.err, 0x5700u);
+      if (!ok) break;
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rdp[32];
+        tmem_ld16(tS + t_lane + c * 32, rs);
+        tmem_ld16(tS + t_lane + c * 32 + 16, rs + 16);
+        tmem_ld16(tdP + t_lane + c * 32, rdp);
+        tmem_ld16(tdP + t_lane + c * 32 + 16, rdp + 16);
+        tmem_wait_ld();
+        bwd_chunk(rs, rdp, c, r, j * FA_T, qi, st, q_ok, need_mask, p.cscale, p.scale, lse2, delta,
+                  nullptr, gbase + DQ_DS);
+      }
+      tcgen05_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(B_(6));
+        mbar_arrive(B_(7));
+      }
+    }
+    if (ok) ok = mbar_wait(B_(9), 0, abort_flag, p.err, 0x5800u);
+    if (ok) {
+      tcgen05_fence_after();
+      uint32_t rr[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(tdQ + t_lane + c * 16, rr + c * 16);
+      tmem_wait_ld();
+      if (q_ok) {
+        __half* dst = p.dqkv + (size_t)(row0 + qi) * 3 * p.D + h * FA_HD;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          __half2 hv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            hv[e] = __floats2half2_rn(__uint_as_float(rr[u * 8 + 2 * e]),
+                                      __uint_as_float(rr[u * 8 + 2 * e + 1]));
+          *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -319,4 +704,46 @@ extern "C" int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* 
   VKG_REQUIRE(ctas < (1ll << 31), "attn_fwd: too many tiles");
   attn_fwd_kernel<<<(unsigned)ctas, FA_THREADS, FW_SMEM, dev->stream>>>(tm, p);
   return vkg_check_launch("attn_fwd_kernel");
+}
+
+extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout16, const void* out16,
+                            const float* lse2, const uint32_t* seg, void* dqkv16, float* delta,
+                            int B, int T, int H, int hd, float scale) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(qkv16 && dout16 && out16 && lse2 && dqkv16 && delta && B > 0 && T > 0 && H > 0,
+              "attn_bwd: bad arguments");
+  VKG_REQUIRE(hd == FA_HD, "attn_bwd: head dimension must be %d (got %d)", FA_HD, hd);
+  VKG_REQUIRE(((uintptr_t)dqkv16 & 15) == 0, "attn_bwd: dqkv must be 16-byte aligned");
+  const int D = H * hd;
+  CUtensorMap tm, tmdo;
+  if (make_map_2d(dev, &tm, qkv16, 3 * (int64_t)D, (int64_t)B * T, "qkv")) return 1;
+  if (make_map_2d(dev, &tmdo, dout16, (int64_t)D, (int64_t)B * T, "dO")) return 1;
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = B; p.T = T; p.H = H; p.D = D;
+  p.nqt = (T + FA_T - 1) / FA_T;
+  p.scale = scale;
+  p.cscale = scale * LOG2E;
+  p.seg = seg;
+  p.lse2 = const_cast<float*>(lse2);
+  p.delta = delta;
+  p.dqkv = (__half*)dqkv16;
+  p.err = dev->err_dev;
+  static bool attr_set = false;
+  if (!attr_set) {
+    VKG_CUDA(cudaFuncSetAttribute(attn_bwd_kv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  KV_SMEM));
+    VKG_CUDA(cudaFuncSetAttribute(attn_bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  DQ_SMEM));
+    attr_set = true;
+  }
+  const long long items = (long long)B * T * H;
+  attn_delta_kernel<<<(unsigned)((items + 7) / 8), 256, 0, dev->stream>>>(
+      (const __half*)dout16, (const __half*)out16, delta, B, T, H);
+  if (vkg_check_launch("attn_delta_kernel")) return 1;
+  const unsigned ctas = (unsigned)((long long)p.nqt * H * B);
+  attn_bwd_kv_kernel<<<ctas, FA_THREADS, KV_SMEM, dev->stream>>>(tm, tmdo, p);
+  if (vkg_check_launch("attn_bwd_kv_kernel")) return 1;
+  attn_bwd_q_kernel<<<ctas, FA_THREADS, DQ_SMEM, dev->stream>>>(tm, tmdo, p);
+  return vkg_check_launch("attn_bwd_q_kernel");
 }

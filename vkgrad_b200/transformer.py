@@ -34,6 +34,7 @@ from .vk import _check
 
 NCHUNK = 32  # kept for callers that pass it to col_sum_chunk (transformer.py:20)
 CAUSAL_BLOCK = 128  # row-tile height of the GEMM: where its causal K ranges stop
+FUSED_HEAD_DIM = 64  # head size the fused attention kernels are written for
 _LN_FUSED_MAX_D = 1536  # shared-memory limit of the fused dgamma/dbeta reduction
 
 
@@ -157,21 +158,28 @@ class Attention:
     """Causal multi-head attention as batched GEMMs over (batch, head) plus the
     row softmax (transformer.py:107-186), with heads addressed by strides."""
 
-    def __init__(self, ctx, B, T, D, H, name=""):
+    def __init__(self, ctx, B, T, D, H, name="", fused=None):
         self.ctx, self.B, self.T, self.D, self.H = ctx, B, T, D, H
         self.hd = D // H
         self.rows = B * T
         self.nbh = B * H
         self.scale = 1.0 / np.sqrt(self.hd)
         self.name = name
+        # head dimension 64 (GPT-2 shapes) runs the fused tcgen05 attention kernels:
+        # no T x T tensor is ever written.  Other head sizes use batched GEMMs + softmax.
+        self.fused = (self.hd == FUSED_HEAD_DIM) if fused is None else bool(fused)
         self.qkv = Dense(ctx, self.rows, D, 3 * D, name + ".qkv")
         self.proj = Dense(ctx, self.rows, D, D, name + ".proj", scale=np.sqrt(2.0 / D) * 0.5)
         att = self.nbh * T * T
         self.qkv16 = ctx.buf(self.rows * 3 * D * 2)
-        self.p16 = ctx.buf(att * 2)
         self.ao16 = ctx.buf(self.rows * D * 2)
         self.dao16 = ctx.buf(self.rows * D * 2)
         self.dqkv16 = ctx.buf(self.rows * 3 * D * 2)
+        if self.fused:
+            self.lse2 = ctx.buf(self.nbh * T * 4)
+            self.delta = ctx.shared_buf("attn_delta", self.nbh * T * 4)
+            return
+        self.p16 = ctx.buf(att * 2)
         # dead after the layer's softmax / softmax backward: shared by all layers
         self.scores = ctx.shared_buf("attn_scores", att * 4)
         self.dp32 = ctx.shared_buf("attn_dp", att * 4)
@@ -206,6 +214,15 @@ class Attention:
         c, lib, h = self.ctx, self.ctx.dev.lib, self.ctx.dev.handle
         T, hd = self.T, self.hd
         self.qkv.forward(x16, graph=graph, out=self.qkv16, c_dtype=F16)
+        self._seg = seg
+        if self.fused:
+            seg_f = None if seg is None else seg.dptr
+
+            def fwd():
+                _check(lib.vkg_attn_fwd(h, self.qkv16.dptr, seg_f, self.ao16.dptr, self.lse2.dptr,
+                                        self.B, T, self.H, hd, float(self.scale)), "attn_fwd")
+            c.launch(graph, fwd, "attn_fwd", self.rows * self.D * 8)
+            return self.proj.forward(self.ao16, graph=graph, out=out, residual=residual)
         # scores = Q K^T per head; tiles wholly above the diagonal are never computed,
         # and nothing downstream reads past the 128-wide block that holds the diagonal
         self._bgemm(self.qkv16, self.qkv16, self.scores, T, T, hd, graph, tb=True,
@@ -226,6 +243,15 @@ class Attention:
         c, lib, h = self.ctx, self.ctx.dev.lib, self.ctx.dev.handle
         T, hd = self.T, self.hd
         self.proj.backward(dy16, need_dx=True, graph=graph, dx=self.dao16, dx_dtype=F16)
+        if self.fused:
+            seg_f = None if self._seg is None else self._seg.dptr
+
+            def bwd():
+                _check(lib.vkg_attn_bwd(h, self.qkv16.dptr, self.dao16.dptr, self.ao16.dptr,
+                                        self.lse2.dptr, seg_f, self.dqkv16.dptr, self.delta.dptr,
+                                        self.B, T, self.H, hd, float(self.scale)), "attn_bwd")
+            c.launch(graph, bwd, "attn_bwd", self.rows * self.D * 16)
+            return self.qkv.backward(self.dqkv16, need_dx=True, graph=graph)
         # dV = P^T dO  -> slice 2 of dqkv
         self._bgemm(self.p16, self.dao16, self.dqkv16, T, hd, T, graph, ta=True, b_merged=True,
                     c_in_qkv=2, c_dtype=F16, causal=3, name="dv")
@@ -249,12 +275,12 @@ class Attention:
 class Block:
     """Pre-LN block: x + attn(ln1(x)), then + fc2(gelu(fc1(ln2(.)))) (transformer.py:189-250)."""
 
-    def __init__(self, ctx, B, T, D, H, name=""):
+    def __init__(self, ctx, B, T, D, H, name="", fused_attention=None):
         self.ctx = ctx
         self.rows = B * T
         self.D = D
         self.ln1 = LayerNorm(ctx, self.rows, D, name + ".ln1")
-        self.attn = Attention(ctx, B, T, D, H, name + ".attn")
+        self.attn = Attention(ctx, B, T, D, H, name + ".attn", fused=fused_attention)
         self.ln2 = LayerNorm(ctx, self.rows, D, name + ".ln2")
         self.fc1 = Dense(ctx, self.rows, D, 4 * D, name + ".fc1")
         self.fc2 = Dense(ctx, self.rows, 4 * D, D, name + ".fc2",
@@ -296,7 +322,7 @@ class Block:
 
 class GPT:
     def __init__(self, ctx, B, T, D, H, n_layer, vocab, pad_vocab=None, tie=False,
-                 loss_scale=1.0):
+                 loss_scale=1.0, fused_attention=None):
         self.ctx, self.B, self.T, self.D = ctx, B, T, D
         self.rows = B * T
         self.vocab = vocab
@@ -307,7 +333,8 @@ class GPT:
                          (rng.standard_normal((self.pad_vocab, D)) * 0.02).astype(np.float32), "tok")
         self.pos = Param(ctx, (T, D), (rng.standard_normal((T, D)) * 0.02).astype(np.float32), "pos")
         self.x0 = ctx.buf(self.rows * D * 4)
-        self.blocks = [Block(ctx, B, T, D, H, f"b{i}") for i in range(n_layer)]
+        self.blocks = [Block(ctx, B, T, D, H, f"b{i}", fused_attention=fused_attention)
+                       for i in range(n_layer)]
         self.lnf = LayerNorm(ctx, self.rows, D, "lnf")
         self.tie = tie
         self.logits = ctx.buf(self.rows * self.pad_vocab * 4)
