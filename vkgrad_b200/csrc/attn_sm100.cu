@@ -27,7 +27,9 @@ using namespace tc05;
 constexpr int FA_T = 128;          // query / key tile
 constexpr int FA_HD = 64;          // head dimension
 constexpr int FA_TILE_BYTES = FA_T * FA_HD * 2;  // 16 KB: one 128 x 64 fp16 tile, 128 B rows
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;      // producer + MMA + eight softmax warps
+constexpr int FA_SOFTMAX_WARPS = 8;
+constexpr int BW_THREADS = 320;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnParams {
@@ -49,7 +51,8 @@ constexpr int FW_K = FW_Q + FA_TILE_BYTES;            // two K stages
 constexpr int FW_V = FW_K + 2 * FA_TILE_BYTES;        // one V stage
 constexpr int FW_P = FW_V + FA_TILE_BYTES;            // P: two 64-key blocks of 128 rows x 128 B
 constexpr int FW_BAR = FW_P + 2 * FA_TILE_BYTES;
-constexpr int FW_SMEM = FW_BAR + 256 + 1024;
+constexpr int FW_XCHG = FW_BAR + 256;                 // [2][128] floats: row statistics exchange
+constexpr int FW_SMEM = FW_XCHG + 1024 + 1024;
 
 // 16-byte chunk `c8` (8 keys) of 64-key block `kb`, row r, in the 128B-swizzled layout
 // both TMA and the UMMA descriptors use.
@@ -79,7 +82,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   const int row0 = b * p.T;                              // first row of this sequence
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 12; ++i) mbar_init(B_(i), (i == 8 || i == 9) ? 4 : 1);
+    for (int i = 0; i < 12; ++i) mbar_init(B_(i), (i == 8 || i == 9) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -119,128 +122,150 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);     // Q K^T: both K-major, N = 128 keys
       const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);    // P V: P K-major, V MN-major, N = 64
       bool ok = mbar_wait(B_(0), 0, abort_flag, p.err, 0x2000u);
-      int it = 0;
-      for (int pass = 0; pass < 2 && ok; ++pass) {
-        for (int j = 0; j < nj && ok; ++j, ++it) {
-          const int s = it & 1;
-          ok = mbar_wait(B_(1 + s), (it >> 1) & 1, abort_flag, p.err, 0x2100u + s) &&
-               mbar_wait(B_(8), (it & 1) ^ 1u, abort_flag, p.err, 0x2200u);
+      const uint32_t sq = base + FW_Q;
+      // S number n (n counts both passes): wait for its K stage and for the softmax warps
+      // to have pulled the previous S out of TMEM, then issue Q K^T.
+      auto issue_s = [&](int n) -> bool {
+        const int s = n & 1;
+        if (!(mbar_wait(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x2100u + s) &&
+              mbar_wait(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x2200u)))
+          return false;
+        tcgen05_fence_after();
+        const uint32_t sk = base + FW_K + s * FA_TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
+                   idesc_s, k ? 1u : 0u);
+        umma_commit(B_(3 + s));   // K stage free once these retire
+        umma_commit(B_(7));       // S ready
+        return true;
+      };
+      // pass 1: S only.  Pass 2 is software-pipelined: S(j+1) is issued before P(j) V, so
+      // the tensor core works on the next scores while the softmax warps finish P(j).
+      int n = 0;
+      for (; n < nj && ok; ++n) ok = issue_s(n);
+      if (ok) ok = issue_s(n++);
+      for (int j = 0; j < nj && ok; ++j) {
+        if (j + 1 < nj) {
+          ok = issue_s(n++);
           if (!ok) break;
-          tcgen05_fence_after();
-          const uint32_t sq = base + FW_Q, sk = base + FW_K + s * FA_TILE_BYTES;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
-                     idesc_s, k ? 1u : 0u);
-          umma_commit(B_(3 + s));   // K stage free once these retire
-          umma_commit(B_(7));       // S ready
-          if (pass == 1) {
-            ok = mbar_wait(B_(9), j & 1, abort_flag, p.err, 0x2300u) &&
-                 mbar_wait(B_(5), j & 1, abort_flag, p.err, 0x2400u);
-            if (!ok) break;
-            tcgen05_fence_after();
-            const uint32_t sp = base + FW_P, sv = base + FW_V;
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              umma_f16(tO,
-                       make_smem_desc(sp + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                       make_smem_desc(sv + kk * 2048, 8192, 1024), idesc_o, (j | kk) ? 1u : 0u);
-            umma_commit(B_(6));     // V free
-            umma_commit(B_(10));    // P free
-          }
         }
+        ok = mbar_wait(B_(9), j & 1, abort_flag, p.err, 0x2300u) &&
+             mbar_wait(B_(5), j & 1, abort_flag, p.err, 0x2400u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t sp = base + FW_P, sv = base + FW_V;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tO, make_smem_desc(sp + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
+                   make_smem_desc(sv + kk * 2048, 8192, 1024), idesc_o, (j | kk) ? 1u : 0u);
+        umma_commit(B_(6));     // V free
+        umma_commit(B_(10));    // P free
       }
       if (ok) umma_commit(B_(11));
     }
   } else {
+    // Softmax: two warps per TMEM lane quarter; `half` picks which 64 of the tile's 128
+    // keys this warp handles.  Each thread owns one query row of its half.
+    const int half = (warp - 2) >> 2;
     const int qr = (warp & 3) * 32 + lane;      // row within the tile = TMEM lane
     const int qi = q0 + qr;                     // query index in the sequence
     const bool q_ok = qi < p.T;
     const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
     const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
-    float m = -1e30f, l = 0.f, inv_l = 0.f;
+    float* xchg = reinterpret_cast<float*>(gbase + FW_XCHG);   // [2][128] row statistics
+    float m = -1e30f, l = 0.f;
     bool ok = true;
     int it = 0;
-    for (int pass = 0; pass < 2 && ok; ++pass) {
-      for (int j = 0; j < nj && ok; ++j, ++it) {
-        ok = mbar_wait(B_(7), it & 1, abort_flag, p.err, 0x3100u);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const bool need_mask = (j == qt) || (p.seg != nullptr);
-        if (pass == 1) {
-          ok = mbar_wait(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x3200u);
-          if (!ok) break;
+    // pass 1: row maximum of the scaled scores (no exponentials)
+    for (int j = 0; j < nj && ok; ++j, ++it) {
+      ok = mbar_wait(B_(7), it & 1, abort_flag, p.err, 0x3100u);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const bool need_mask = (j == qt) || (p.seg != nullptr);
+      uint32_t r[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, r + c * 16);
+      tmem_wait_ld();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(8));        // S may be overwritten
+#pragma unroll
+      for (int e = 0; e < 64; ++e) {
+        float t = __uint_as_float(r[e]) * p.cscale;
+        if (need_mask) {
+          const int key = j * FA_T + half * 64 + e;
+          if (key > qi || key < st) t = -1e30f;
         }
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld16(tS + t_lane + c * 32, r);
-          tmem_ld16(tS + t_lane + c * 32 + 16, r + 16);
-          tmem_wait_ld();
-          float t[32];
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            t[e] = __uint_as_float(r[e]) * p.cscale;
-            if (need_mask) {
-              const int key = j * FA_T + c * 32 + e;
-              if (key > qi || key < st) t[e] = -1e30f;
-            }
-          }
-          if (pass == 0) {
-            float cm = m;
-#pragma unroll
-            for (int e = 0; e < 32; ++e) cm = fmaxf(cm, t[e]);
-            float sum = 0.f;
-#pragma unroll
-            for (int e = 0; e < 32; ++e) sum += t[e] <= -1e29f ? 0.f : vkg_ex2(t[e] - cm);
-            l = l * vkg_ex2(m - cm) + sum;
-            m = cm;
-          } else {
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              __half2 hv[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float a = t[u * 8 + 2 * e], bb = t[u * 8 + 2 * e + 1];
-                hv[e] = __floats2half2_rn(a <= -1e29f ? 0.f : vkg_ex2(a - m) * inv_l,
-                                          bb <= -1e29f ? 0.f : vkg_ex2(bb - m) * inv_l);
-              }
-              const int cc = c * 4 + u;
-              *reinterpret_cast<uint4*>(gbase + FW_P + p_offset(cc >> 3, qr, cc & 7)) =
-                  *reinterpret_cast<uint4*>(hv);
-            }
-          }
-        }
-        tcgen05_fence_before();
-        if (pass == 1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(B_(8));                    // S may be overwritten
-          if (pass == 1) mbar_arrive(B_(9));     // P is in shared memory
-        }
-      }
-      if (pass == 0) {
-        // masked entries contributed exp2(-1e30 - m) = 0; l >= 1 because key == query is valid
-        inv_l = 1.0f / l;
-        if (q_ok) p.lse2[(size_t)(b * p.H + h) * p.T + qi] = m + log2f(l);
+        m = fmaxf(m, t);
       }
     }
+    xchg[half * 128 + qr] = m;
+    asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight softmax warps
+    m = fmaxf(xchg[qr], xchg[128 + qr]);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    // pass 2: P = exp2(t - m) rounded to fp16 (normalised by 1/l at the very end), l in fp32
+    for (int j = 0; j < nj && ok; ++j, ++it) {
+      ok = mbar_wait(B_(7), it & 1, abort_flag, p.err, 0x3150u);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const bool need_mask = (j == qt) || (p.seg != nullptr);
+      uint32_t r[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, r + c * 16);
+      tmem_wait_ld();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(8));
+      ok = mbar_wait(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x3200u);   // P buffer free
+      if (!ok) break;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        __half2 hv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float pv[2];
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            const int idx = u * 8 + 2 * e + w;
+            const float t = __uint_as_float(r[idx]) * p.cscale;
+            bool valid = true;
+            if (need_mask) {
+              const int key = j * FA_T + half * 64 + idx;
+              valid = key <= qi && key >= st;
+            }
+            pv[w] = valid ? vkg_ex2(t - m) : 0.f;
+          }
+          l += pv[0] + pv[1];
+          hv[e] = __floats2half2_rn(pv[0], pv[1]);
+        }
+        *reinterpret_cast<uint4*>(gbase + FW_P + p_offset(half, qr, u)) = *reinterpret_cast<uint4*>(hv);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(9));        // this warp's part of P is in shared memory
+    }
+    xchg[half * 128 + qr] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l = xchg[qr] + xchg[128 + qr];
+    const float inv_l = 1.0f / l;               // l >= 1: key == query is always valid
+    if (half == 0 && q_ok) p.lse2[(size_t)(b * p.H + h) * p.T + qi] = m + log2f(l);
     if (ok) ok = mbar_wait(B_(11), 0, abort_flag, p.err, 0x3300u);
     if (ok) {
       tcgen05_fence_after();
-      uint32_t r[64];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld16(tO + t_lane + c * 16, r + c * 16);
+      uint32_t r[32];                            // this half's 32 of the 64 output columns
+      tmem_ld16(tO + t_lane + half * 32, r);
+      tmem_ld16(tO + t_lane + half * 32 + 16, r + 16);
       tmem_wait_ld();
       if (q_ok) {
-        __half* dst = p.out + (size_t)(row0 + qi) * p.D + h * FA_HD;
+        __half* dst = p.out + (size_t)(row0 + qi) * p.D + h * FA_HD + half * 32;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < 4; ++u) {
           __half2 hv[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            hv[e] = __floats2half2_rn(__uint_as_float(r[u * 8 + 2 * e]),
-                                      __uint_as_float(r[u * 8 + 2 * e + 1]));
+            hv[e] = __floats2half2_rn(__uint_as_float(r[u * 8 + 2 * e]) * inv_l,
+                                      __uint_as_float(r[u * 8 + 2 * e + 1]) * inv_l);
           *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
         }
       }
@@ -281,10 +306,11 @@ __global__ void attn_delta_kernel(const __half* __restrict__ dout, const __half*
 
 // One 32-key chunk of a (query row, key tile) pair: rebuild P from S and the saved
 // log-sum-exp, form dS = P (dP - delta) scale, and write both (fp16) into the swizzled
-// [query row][key] layout.  `sp` / `sds` may be null.
+// [query row][key] layout.  `sp` may be null.  nlse = -lse2, dsc = -delta * scale, so
+// each element costs two FMAs, one exp2, one multiply and the conversions.
 __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rdp, int c, int r,
                                           int key0, int qi, int st, bool q_ok, bool need_mask,
-                                          float cscale, float scale, float lse2, float delta,
+                                          float cscale, float scale, float nlse, float dsc,
                                           uint8_t* sp, uint8_t* sds) {
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
@@ -295,12 +321,14 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rd
 #pragma unroll
       for (int w = 0; w < 2; ++w) {
         const int idx = u * 8 + 2 * e + w;
-        const int key = key0 + c * 32 + idx;
         bool valid = q_ok;
-        if (need_mask) valid = valid && key <= qi && key >= st;
-        const float pr = valid ? vkg_ex2(__uint_as_float(rs[idx]) * cscale - lse2) : 0.f;
+        if (need_mask) {
+          const int key = key0 + c * 32 + idx;
+          valid = valid && key <= qi && key >= st;
+        }
+        const float pr = valid ? vkg_ex2(fmaf(__uint_as_float(rs[idx]), cscale, nlse)) : 0.f;
         pv[w] = pr;
-        dv[w] = pr * (__uint_as_float(rdp[idx]) - delta) * scale;
+        dv[w] = pr * fmaf(__uint_as_float(rdp[idx]), scale, dsc);
       }
       hp[e] = __floats2half2_rn(pv[0], pv[1]);
       hd[e] = __floats2half2_rn(dv[0], dv[1]);
@@ -308,20 +336,7 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rd
     const int cc = c * 4 + u;
     const uint32_t off = p_offset(cc >> 3, r, cc & 7);
     if (sp) *reinterpret_cast<uint4*>(sp + off) = *reinterpret_cast<uint4*>(hp);
-    if (sds) {
-      // dS must be built from the ROUNDED P, as the unfused path reads p16 back
-      // (tkernels.py:182): recompute from the fp16 values just formed
-      __half2 hd2[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 pf = __half22float2(hp[e]);
-        hd2[e] = __floats2half2_rn(
-            pf.x * (__uint_as_float(rdp[u * 8 + 2 * e]) - delta) * scale,
-            pf.y * (__uint_as_float(rdp[u * 8 + 2 * e + 1]) - delta) * scale);
-      }
-      *reinterpret_cast<uint4*>(sds + off) = *reinterpret_cast<uint4*>(hd2);
-    }
-    (void)hd;
+    *reinterpret_cast<uint4*>(sds + off) = *reinterpret_cast<uint4*>(hd);
   }
 }
 
@@ -331,7 +346,7 @@ constexpr int KV_K = 0, KV_V = FA_TILE_BYTES, KV_Q = 2 * FA_TILE_BYTES, KV_DO = 
               KV_P = 6 * FA_TILE_BYTES, KV_DS = 8 * FA_TILE_BYTES, KV_BAR = 10 * FA_TILE_BYTES,
               KV_SMEM = KV_BAR + 256 + 1024;
 
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
                    const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -351,7 +366,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
   const int ni = p.nqt - kt;                         // query tiles kt .. nqt-1
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 10; ++i) mbar_init(B_(i), (i == 6 || i == 7) ? 4 : 1);
+    for (int i = 0; i < 10; ++i) mbar_init(B_(i), (i == 6 || i == 7) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -382,14 +397,14 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);    // [q x hd] . [key x hd]^T
       const uint32_t idesc_g = make_idesc(0, 1, 1, FA_HD);   // [q x key]^T . [q x hd]
       bool ok = mbar_wait(B_(0), 0, abort_flag, p.err, 0x4200u);
-      for (int it = 0; it < ni && ok; ++it) {
-        const int s = it & 1;
-        ok = mbar_wait(B_(1 + s), (it >> 1) & 1, abort_flag, p.err, 0x4300u + s) &&
-             mbar_wait(B_(6), (it & 1) ^ 1u, abort_flag, p.err, 0x4400u);
-        if (!ok) break;
+      const uint32_t sk = base + KV_K, sv = base + KV_V;
+      auto issue_sdp = [&](int n) -> bool {   // S = Q_n K^T and dP = dO_n V^T
+        const int s = n & 1;
+        if (!(mbar_wait(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x4300u + s) &&
+              mbar_wait(B_(6), (n & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
+          return false;
         tcgen05_fence_after();
         const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
-        const uint32_t sk = base + KV_K, sv = base + KV_V;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
@@ -399,9 +414,21 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           umma_f16(tdP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024),
                    idesc_s, k ? 1u : 0u);
         umma_commit(B_(5));
+        return true;
+      };
+      // software pipeline: the next tile's S / dP are issued before this tile's dV / dK, so
+      // the tensor core is busy while the softmax warps turn S, dP into P, dS
+      if (ok) ok = issue_sdp(0);
+      for (int it = 0; it < ni && ok; ++it) {
+        const int s = it & 1;
+        if (it + 1 < ni) {
+          ok = issue_sdp(it + 1);
+          if (!ok) break;
+        }
         ok = mbar_wait(B_(7), it & 1, abort_flag, p.err, 0x4500u);
         if (!ok) break;
         tcgen05_fence_after();
+        const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
         const uint32_t sp = base + KV_P, sds = base + KV_DS;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)      // K = 128 query rows, 16 at a time
@@ -417,6 +444,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       if (ok) umma_commit(B_(9));
     }
   } else {
+    const int half = (warp - 2) >> 2;            // which 64 of the tile's 128 keys
     const int r = (warp & 3) * 32 + lane;
     const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
     bool ok = true;
@@ -425,54 +453,51 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       const int qi = qt * FA_T + r;
       const bool q_ok = qi < p.T;
       const size_t sidx = (size_t)(b * p.H + h) * p.T + (q_ok ? qi : 0);
-      const float lse2 = p.lse2[sidx], delta = p.delta[sidx];
+      const float nlse = -p.lse2[sidx], dsc = -p.delta[sidx] * p.scale;
       const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
       const bool need_mask = (qt == kt) || (p.seg != nullptr);
-      ok = mbar_wait(B_(5), it & 1, abort_flag, p.err, 0x4600u) &&
-           mbar_wait(B_(8), (it & 1) ^ 1u, abort_flag, p.err, 0x4700u);
+      ok = mbar_wait(B_(5), it & 1, abort_flag, p.err, 0x4600u);
       if (!ok) break;
       tcgen05_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rdp[32];
-        tmem_ld16(tS + t_lane + c * 32, rs);
-        tmem_ld16(tS + t_lane + c * 32 + 16, rs + 16);
-        tmem_ld16(tdP + t_lane + c * 32, rdp);
-        tmem_ld16(tdP + t_lane + c * 32 + 16, rdp + 16);
-        tmem_wait_ld();
-        bwd_chunk(rs, rdp, c, r, k0, qi, st, q_ok, need_mask, p.cscale, p.scale, lse2, delta,
-                  gbase + KV_P, gbase + KV_DS);
-      }
+      uint32_t rs[64], rdp[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, rs + c * 16);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(tdP + t_lane + half * 64 + c * 16, rdp + c * 16);
+      tmem_wait_ld();
       tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(6));          // S / dP may be overwritten
+      ok = mbar_wait(B_(8), (it & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // P / dS buffers free
+      if (!ok) break;
+      bwd_chunk(rs, rdp, 2 * half, r, k0, qi, st, q_ok, need_mask, p.cscale, p.scale, nlse, dsc,
+                gbase + KV_P, gbase + KV_DS);
+      bwd_chunk(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, q_ok, need_mask, p.cscale, p.scale,
+                nlse, dsc, gbase + KV_P, gbase + KV_DS);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(B_(6));
-        mbar_arrive(B_(7));
-      }
+      if (lane == 0) mbar_arrive(B_(7));
     }
     if (ok) ok = mbar_wait(B_(9), 0, abort_flag, p.err, 0x4800u);
     if (ok) {
       tcgen05_fence_after();
       const int key = k0 + r;     // accumulator rows are keys here
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        uint32_t rr[64];
-        const uint32_t t = (which == 0 ? tdV : tdK) + t_lane;
+      // half 0 stores dV (slice 2 of dqkv), half 1 stores dK (slice 1)
+      uint32_t rr[64];
+      const uint32_t t = (half == 0 ? tdV : tdK) + t_lane;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld16(t + c * 16, rr + c * 16);
-        tmem_wait_ld();
-        if (key < p.T) {
-          __half* dst = p.dqkv + (size_t)(row0 + key) * 3 * p.D + (which == 0 ? 2 : 1) * p.D + h * FA_HD;
+      for (int c = 0; c < 4; ++c) tmem_ld16(t + c * 16, rr + c * 16);
+      tmem_wait_ld();
+      if (key < p.T) {
+        __half* dst = p.dqkv + (size_t)(row0 + key) * 3 * p.D + (half == 0 ? 2 : 1) * p.D + h * FA_HD;
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            __half2 hv[4];
+        for (int u = 0; u < 8; ++u) {
+          __half2 hv[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              hv[e] = __floats2half2_rn(__uint_as_float(rr[u * 8 + 2 * e]),
-                                        __uint_as_float(rr[u * 8 + 2 * e + 1]));
-            *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
-          }
+          for (int e = 0; e < 4; ++e)
+            hv[e] = __floats2half2_rn(__uint_as_float(rr[u * 8 + 2 * e]),
+                                      __uint_as_float(rr[u * 8 + 2 * e + 1]));
+          *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
         }
       }
     }
@@ -496,7 +521,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
 constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_K = 2 * FA_TILE_BYTES, DQ_V = 4 * FA_TILE_BYTES,
               DQ_DS = 6 * FA_TILE_BYTES, DQ_BAR = 8 * FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
 
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
                   const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -516,7 +541,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   const int nj = qt + 1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 10; ++i) mbar_init(B_(i), (i == 6 || i == 7) ? 4 : 1);
+    for (int i = 0; i < 10; ++i) mbar_init(B_(i), (i == 6 || i == 7) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -547,13 +572,13 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
       const uint32_t idesc_q = make_idesc(0, 0, 1, FA_HD);   // dS (K-major) . K (MN-major), N = 64
       bool ok = mbar_wait(B_(0), 0, abort_flag, p.err, 0x5200u);
-      for (int j = 0; j < nj && ok; ++j) {
-        const int s = j & 1;
-        ok = mbar_wait(B_(1 + s), (j >> 1) & 1, abort_flag, p.err, 0x5300u + s) &&
-             mbar_wait(B_(6), (j & 1) ^ 1u, abort_flag, p.err, 0x5400u);
-        if (!ok) break;
+      const uint32_t sq = base + DQ_Q, sdo = base + DQ_DO;
+      auto issue_sdp = [&](int n) -> bool {   // S = Q K_n^T and dP = dO V_n^T
+        const int s = n & 1;
+        if (!(mbar_wait(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x5300u + s) &&
+              mbar_wait(B_(6), (n & 1) ^ 1u, abort_flag, p.err, 0x5400u)))
+          return false;
         tcgen05_fence_after();
-        const uint32_t sq = base + DQ_Q, sdo = base + DQ_DO;
         const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES, sv = base + DQ_V + s * FA_TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
@@ -564,9 +589,19 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
           umma_f16(tdP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024),
                    idesc_s, k ? 1u : 0u);
         umma_commit(B_(5));
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int j = 0; j < nj && ok; ++j) {
+        const int s = j & 1;
+        if (j + 1 < nj) {
+          ok = issue_sdp(j + 1);
+          if (!ok) break;
+        }
         ok = mbar_wait(B_(7), j & 1, abort_flag, p.err, 0x5500u);
         if (!ok) break;
         tcgen05_fence_after();
+        const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES;
         const uint32_t sds = base + DQ_DS;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)      // K = 128 keys
@@ -578,50 +613,50 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       if (ok) umma_commit(B_(9));
     }
   } else {
+    const int half = (warp - 2) >> 2;
     const int r = (warp & 3) * 32 + lane;
     const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
     const int qi = q0 + r;
     const bool q_ok = qi < p.T;
     const size_t sidx = (size_t)(b * p.H + h) * p.T + (q_ok ? qi : 0);
-    const float lse2 = p.lse2[sidx], delta = p.delta[sidx];
+    const float nlse = -p.lse2[sidx], dsc = -p.delta[sidx] * p.scale;
     const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
     bool ok = true;
     for (int j = 0; j < nj && ok; ++j) {
       const bool need_mask = (j == qt) || (p.seg != nullptr);
-      ok = mbar_wait(B_(5), j & 1, abort_flag, p.err, 0x5600u) &&
-           mbar_wait(B_(8), (j & 1) ^ 1u, abort_flag, p.err, 0x5700u);
+      ok = mbar_wait(B_(5), j & 1, abort_flag, p.err, 0x5600u);
       if (!ok) break;
       tcgen05_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rdp[32];
-        tmem_ld16(tS + t_lane + c * 32, rs);
-        tmem_ld16(tS + t_lane + c * 32 + 16, rs + 16);
-        tmem_ld16(tdP + t_lane + c * 32, rdp);
-        tmem_ld16(tdP + t_lane + c * 32 + 16, rdp + 16);
-        tmem_wait_ld();
-        bwd_chunk(rs, rdp, c, r, j * FA_T, qi, st, q_ok, need_mask, p.cscale, p.scale, lse2, delta,
-                  nullptr, gbase + DQ_DS);
-      }
+      uint32_t rs[64], rdp[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, rs + c * 16);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(tdP + t_lane + half * 64 + c * 16, rdp + c * 16);
+      tmem_wait_ld();
       tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(6));
+      ok = mbar_wait(B_(8), (j & 1) ^ 1u, abort_flag, p.err, 0x5700u);
+      if (!ok) break;
+      bwd_chunk(rs, rdp, 2 * half, r, j * FA_T, qi, st, q_ok, need_mask, p.cscale, p.scale, nlse, dsc,
+                nullptr, gbase + DQ_DS);
+      bwd_chunk(rs + 32, rdp + 32, 2 * half + 1, r, j * FA_T, qi, st, q_ok, need_mask, p.cscale,
+                p.scale, nlse, dsc, nullptr, gbase + DQ_DS);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(B_(6));
-        mbar_arrive(B_(7));
-      }
+      if (lane == 0) mbar_arrive(B_(7));
     }
     if (ok) ok = mbar_wait(B_(9), 0, abort_flag, p.err, 0x5800u);
     if (ok) {
       tcgen05_fence_after();
-      uint32_t rr[64];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld16(tdQ + t_lane + c * 16, rr + c * 16);
+      uint32_t rr[32];                             // this half's 32 of the 64 dQ columns
+      tmem_ld16(tdQ + t_lane + half * 32, rr);
+      tmem_ld16(tdQ + t_lane + half * 32 + 16, rr + 16);
       tmem_wait_ld();
       if (q_ok) {
-        __half* dst = p.dqkv + (size_t)(row0 + qi) * 3 * p.D + h * FA_HD;
+        __half* dst = p.dqkv + (size_t)(row0 + qi) * 3 * p.D + h * FA_HD + half * 32;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < 4; ++u) {
           __half2 hv[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
@@ -742,8 +777,8 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
       (const __half*)dout16, (const __half*)out16, delta, B, T, H);
   if (vkg_check_launch("attn_delta_kernel")) return 1;
   const unsigned ctas = (unsigned)((long long)p.nqt * H * B);
-  attn_bwd_kv_kernel<<<ctas, FA_THREADS, KV_SMEM, dev->stream>>>(tm, tmdo, p);
+  attn_bwd_kv_kernel<<<ctas, BW_THREADS, KV_SMEM, dev->stream>>>(tm, tmdo, p);
   if (vkg_check_launch("attn_bwd_kv_kernel")) return 1;
-  attn_bwd_q_kernel<<<ctas, FA_THREADS, DQ_SMEM, dev->stream>>>(tm, tmdo, p);
+  attn_bwd_q_kernel<<<ctas, BW_THREADS, DQ_SMEM, dev->stream>>>(tm, tmdo, p);
   return vkg_check_launch("attn_bwd_q_kernel");
 }

@@ -27,12 +27,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+  // The last operand is a suspend-time hint in nanoseconds: the thread may sleep in
+  // hardware until the phase completes or the hint expires, instead of burning issue
+  // slots that the compute warps on the same scheduler need.
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(20000u)
       : "memory");
   return ok;
 }
