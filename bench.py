@@ -184,22 +184,59 @@ def run_reference_arm(args):
 
 # ---- GPU arm ---------------------------------------------------------------------------------
 
-def gemm_shape_table(B, T, D, H, L, V):
-    """(count per step, kwargs for kernels.gemm) for every distinct GEMM of the step."""
+def gemm_shape_table(B, T, D, H, L, V, fused_attention=True):
+    """(count per step, shape) for every distinct launch of gemm_tcgen05_kernel in a step.
+    With head dimension 64 attention runs in the fused attention kernels, so the six
+    batched matmuls per layer of the reference's plan are not GEMM launches here."""
     R, hd, Vp = B * T, D // H, (V + 15) // 16 * 16
     t = []
     for (i, o) in ((D, 3 * D), (D, D), (D, 4 * D), (4 * D, D)):
         t.append((L, dict(m=R, n=o, k=i, ta=False, tb=False)))          # Y  = X W
         t.append((L, dict(m=i, n=o, k=R, ta=True, tb=False)))           # dW = X^T dY
         t.append((L, dict(m=R, n=i, k=o, ta=False, tb=True)))           # dX = dY W^T
-    nb = B * H
-    t.append((2 * L, dict(m=T, n=T, k=hd, ta=False, tb=True, nb=nb)))   # QK^T, dP
-    t.append((2 * L, dict(m=T, n=hd, k=T, ta=False, tb=False, nb=nb)))  # PV, dQ
-    t.append((2 * L, dict(m=T, n=hd, k=T, ta=True, tb=False, nb=nb)))   # dV, dK
+    if not fused_attention:
+        nb = B * H
+        t.append((2 * L, dict(m=T, n=T, k=hd, ta=False, tb=True, nb=nb, causal=1)))   # QK^T, dP
+        t.append((2 * L, dict(m=T, n=hd, k=T, ta=False, tb=False, nb=nb, causal=2)))  # PV, dQ
+        t.append((2 * L, dict(m=T, n=hd, k=T, ta=True, tb=False, nb=nb, causal=3)))   # dV, dK
     t.append((1, dict(m=R, n=Vp, k=D, ta=False, tb=True)))              # logits
     t.append((1, dict(m=R, n=D, k=Vp, ta=False, tb=False)))             # dh
     t.append((1, dict(m=Vp, n=D, k=R, ta=True, tb=False)))              # dtok (head share)
     return t
+
+
+def time_attention(dev, B, T, H, hd):
+    """CUDA-event time of the fused attention forward and backward for one layer."""
+    import ctypes as C
+    from vkgrad_b200.vk import _check
+    D = H * hd
+    lib, h = dev.lib, dev.handle
+    qkv = dev.buffer(B * T * 3 * D * 2, "device")
+    dout = dev.buffer(B * T * D * 2, "device")
+    out = dev.buffer(B * T * D * 2, "device")
+    dqkv = dev.buffer(B * T * 3 * D * 2, "device")
+    lse = dev.buffer(B * H * T * 4, "device")
+    delta = dev.buffer(B * H * T * 4, "device")
+    for b in (qkv, dout):
+        _check(lib.vkg_memset0(h, b.dptr, b.size), "memset")
+    scale = 1.0 / np.sqrt(hd)
+
+    def fwd():
+        _check(lib.vkg_attn_fwd(h, qkv.dptr, None, out.dptr, lse.dptr, B, T, H, hd, scale), "fwd")
+
+    def bwd():
+        _check(lib.vkg_attn_bwd(h, qkv.dptr, dout.dptr, out.dptr, lse.dptr, None, dqkv.dptr,
+                                delta.dptr, B, T, H, hd, scale), "bwd")
+    res = {}
+    for name, fn in (("fwd_us", fwd), ("bwd_us", bwd)):
+        dev.run_op(fn, 2)
+        res[name] = min(dev.run_op(fn, 10) / 10 for _ in range(3)) * 1e6
+    flop = 2.0 * (B * H) * T * T * hd
+    res["fwd_tflops_full_TxT"] = 2 * flop / res["fwd_us"] / 1e6
+    res["bwd_tflops_full_TxT"] = 4 * flop / res["bwd_us"] / 1e6
+    for b in (qkv, dout, out, dqkv, lse, delta):
+        b.destroy()
+    return res
 
 
 def time_gemm_shapes(dev, table):
@@ -213,7 +250,7 @@ def time_gemm_shapes(dev, table):
         b = dev.buffer(nb * k * n * 2, "device")
         c = dev.buffer(nb * m * n * 4, "device")
         kw = dict(trans_a=s["ta"], trans_b=s["tb"], nb0=nb, sa=(m * k, 0), sb=(k * n, 0),
-                  sc=(m * n, 0))
+                  sc=(m * n, 0), causal=s.get("causal", 0))
         gemm(dev, a, b, c, m, n, k, repeat=2, **kw)
         reps = 10
         t = min(gemm(dev, a, b, c, m, n, k, repeat=reps, **kw) / reps for _ in range(3))
@@ -368,7 +405,10 @@ def run_gpu_arm(args):
     tokens_step = R * world
     line = None
     if rank == 0:
-        flops_total, gemm_t, rows = time_gemm_shapes(dev, gemm_shape_table(B, T, D, H, L, V))
+        fused = (D // H) == 64
+        flops_total, gemm_t, rows = time_gemm_shapes(
+            dev, gemm_shape_table(B, T, D, H, L, V, fused_attention=fused))
+        attn = time_attention(dev, B, T, H, D // H) if fused else None
         achieved = flops_total / gemm_t / 1e12
         peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
         alg = step_flops(B, T, D, H, L, V)
@@ -397,9 +437,14 @@ def run_gpu_arm(args):
             "launches_per_step": core.n_kernels,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
-                         "kernel": "gemm_tcgen05_kernel (all GEMM launches of one step)",
-                         "gemm_ms_per_step": gemm_t * 1e3},
+                         "frac": achieved / peak, "traffic": 59.7e6, "peak_source": peak_src,
+                         "kernel": "gemm_tcgen05_kernel (all its launches in one step)",
+                         "traffic_note": "ncu dram read+write bytes of ONE launch of the "
+                                         "8192x3072x768 fp32-out shape (algorithmic minimum 118 MB; "
+                                         "the output largely stays in L2); see profiles/",
+                         "gemm_ms_per_step": gemm_t * 1e3,
+                         "gemm_tflop_per_step": flops_total / 1e12},
+            "attention_per_layer": attn,
             "step_tensor_frac": alg / (dt / args.steps) / 1e12 / peak,
             "algorithmic_tflop_per_step": alg / 1e12,
             "cpu_baseline": cpu,

@@ -47,10 +47,12 @@ def test_step_flops_matches_the_reference_dispatch_count():
     import bench
     assert abs(bench.step_flops(8, 1024, 768, 12, 12, 50257) - 7.0001e12) < 1e9
     assert abs(bench.step_flops(4, 1024, 1024, 16, 24, 50257) - 9.9238e12) < 2e9
-    table = bench.gemm_shape_table(8, 1024, 768, 12, 12, 50257)
+    table = bench.gemm_shape_table(8, 1024, 768, 12, 12, 50257, fused_attention=False)
     total = sum(c * 2.0 * s["m"] * s["n"] * s["k"] * s.get("nb", 1) for c, s in table)
     assert abs(total - bench.step_flops(8, 1024, 768, 12, 12, 50257)) < 1e6
     assert sum(c for c, _ in table) == 219
+    # with the fused attention kernels the six batched matmuls per layer are not GEMM launches
+    assert sum(c for c, _ in bench.gemm_shape_table(8, 1024, 768, 12, 12, 50257)) == 219 - 72
 
 
 def _rdzv_worker(rank, world, port, q):
