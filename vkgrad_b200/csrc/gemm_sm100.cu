@@ -4,12 +4,12 @@
 // overlaps the main loop of tile i+1) -> tcgen05.ld epilogue with the fused
 // bias / activation / activation-derivative / residual / narrowing.
 //
-// One persistent CTA per SM, 320 threads:
-//   warp 0      TMA producer (one lane)
-//   warp 1      TMEM allocation + MMA issue (one lane)
-//   warps 2..9  epilogue; warp w reads TMEM lanes 32*(w%4) .. +31 and takes every
-//               other 32-column chunk.  The epilogue is instruction-issue bound, so
-//               it gets two warps per scheduler and a compile-time feature mask.
+// One persistent CTA per SM, 576 threads:
+//   warp 0       TMA producer (one lane)
+//   warp 1       TMEM allocation + MMA issue (one lane)
+//   warps 2..17  epilogue; warp w reads TMEM lanes 32*(w%4) .. +31 and takes every
+//                fourth 16-column chunk.  The epilogue is instruction-issue / latency
+//                bound, so it gets four warps per scheduler and a compile-time mask.
 //
 // Transposed operands are never materialised (the reference makes the same
 // point for its cooperative-matrix loads, kernels.py:45-49): "A stored K x M"
@@ -31,12 +31,12 @@ constexpr int BK = 64;             // K elements per stage = 128 bytes of f16 = 
 constexpr int UMMA_K = 16;         // K per tcgen05.mma.kind::f16
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int MAX_STAGES = 8;
-constexpr int EPI_WARPS = 8;       // two per TMEM lane quarter, each takes alternate 32-column chunks
+constexpr int EPI_WARPS = 16;      // four per TMEM lane quarter, each takes every fourth 16-column chunk
 constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int TMEM_COLS = 512;     // whole TMEM: two 256-column accumulators
 constexpr int ACC_COLS = 256;
 constexpr int RING_BYTES = 196608; // shared-memory ring budget
-constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;  // one 32x32 fp32 chunk per epilogue warp (XOR-swizzled)
+constexpr int EPI_STAGE_BYTES = 32 * 16 * 4;  // one 32x16 fp32 chunk per epilogue warp (XOR-swizzled)
 constexpr int SMEM_BYTES = RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024 /*align slack*/ +
                            256 /*barriers*/;
 constexpr int GROUP_M = 8;         // m-tiles per rasterisation band
@@ -149,15 +149,15 @@ __device__ __forceinline__ void st4(float* p, long long off, float4 v, bool vec)
   }
 }
 
-// One lane's share of a 32x32 chunk through the fused epilogue: eight rows (4*i +
-// sub_row), four consecutive columns each.  In this layout the 8 lanes of a
-// quarter-warp cover 32 consecutive columns of one row, so every global access of the
-// warp is four full 128-byte rows.  All loads of one kind are issued before the first
+// One lane's share of a 32x16 chunk through the fused epilogue: four rows (8*i +
+// sub_row), four consecutive columns each.  In this layout four lanes cover the 16
+// columns (64 bytes) of one row, so every global access of the warp is eight
+// row-contiguous 64-byte pieces.  All loads of one kind are issued before the first
 // dependent use: C may alias the inputs as far as the compiler knows, so a
 // load-compute-store loop would serialise eight memory round trips.
 template <int MODE>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, float4 (&v)[8],
-                                               const long long (&off)[8], unsigned ok, int col) {
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, float4 (&v)[4],
+                                               const long long (&off)[4], unsigned ok, int col) {
   constexpr bool G = (MODE & E_GENERIC) != 0;
   const bool vec = G ? (p.vec_ok != 0) : true;
   const bool has_bias = G ? (p.bias != nullptr) : (MODE & E_BIAS) != 0;
@@ -167,49 +167,49 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, float4 (&v)[
   const bool has_res = G ? (p.residual != nullptr) : (MODE & E_RES) != 0;
   const bool has_c2 = G ? (p.C2 != nullptr) : (MODE & E_C2) != 0;
   const int c_dtype = G ? p.c_dtype : ((MODE & E_F16) ? VKG_F16 : (MODE & E_BF16) ? VKG_BF16 : VKG_F32);
-  float4 extra[8];
+  float4 extra[4];
   if (has_dact) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
       extra[i] = (ok >> i) & 1u ? ld4(p.dact_z, off[i], vec) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
   if (has_bias) b = ld4(p.bias, col, vec);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 4; ++i) {
     v[i].x = v[i].x * p.alpha + b.x; v[i].y = v[i].y * p.alpha + b.y;
     v[i].z = v[i].z * p.alpha + b.z; v[i].w = v[i].w * p.alpha + b.w;
   }
   if (has_pre) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
       if ((ok >> i) & 1u) st4(p.pre, off[i], v[i], vec);
   }
   if (has_act) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       v[i].x = vkg_act(v[i].x, p.act); v[i].y = vkg_act(v[i].y, p.act);
       v[i].z = vkg_act(v[i].z, p.act); v[i].w = vkg_act(v[i].w, p.act);
     }
   }
   if (has_dact) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       v[i].x *= vkg_dact(extra[i].x, p.dact); v[i].y *= vkg_dact(extra[i].y, p.dact);
       v[i].z *= vkg_dact(extra[i].z, p.dact); v[i].w *= vkg_dact(extra[i].w, p.dact);
     }
   }
   if (has_res) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
       extra[i] = (ok >> i) & 1u ? ld4(p.residual, off[i], vec) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       v[i].x += extra[i].x; v[i].y += extra[i].y; v[i].z += extra[i].z; v[i].w += extra[i].w;
     }
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 4; ++i) {
     if (!((ok >> i) & 1u)) continue;
     const float f[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
     if (c_dtype == VKG_F32) {
@@ -370,36 +370,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.err, 0x400u + acc)) break;
       tcgen05_fence_after();
       // TMEM gives each lane one row; the chunk is transposed through shared memory so
-      // that global loads and stores are row-contiguous (8 lanes x 16 B per row).  Rows
-      // are 128 B apart with the 16-byte chunk index XOR-ed by (row & 7): conflict-free
+      // that global loads and stores are row-contiguous (4 lanes x 16 B per row).  Rows
+      // are 64 B apart with the 16-byte chunk index XOR-ed by (row >> 1) & 3: conflict-free
       // both for the row-per-lane writes and the row-contiguous reads.
       uint8_t* stage = reinterpret_cast<uint8_t*>(epi_stage) + (warp - 2) * EPI_STAGE_BYTES;
-      const int sub_row = lane >> 3;        // 0..3: row within a group of four
-      const int sub_chunk = lane & 7;       // which 16-byte chunk (4 columns) of the row
+      const int sub_row = lane >> 2;        // 0..7: row within a group of eight
+      const int sub_chunk = lane & 3;       // which 16-byte chunk (4 columns) of the row
       const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
       const int row_base = tc.m0 + q * 32;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
-      for (int c0 = 32 * ((warp - 2) >> 2); c0 < p.bn; c0 += 64) {
+      for (int c0 = 16 * ((warp - 2) >> 2); c0 < p.bn; c0 += 64) {
         if (tc.n0 + c0 >= p.N) break;  // uniform across the warp
-        uint32_t r[32];
+        uint32_t r[16];
         tmem_ld16(t_row + c0, r);
-        tmem_ld16(t_row + c0 + 16, r + 16);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
               make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
         __syncwarp();
         const int col = tc.n0 + c0 + sub_chunk * 4;
         if (col < p.N) {
-          float4 v[8];
-          long long off[8];
+          float4 v[4];
+          long long off[4];
           unsigned ok = 0;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = 4 * i + sub_row;
+          for (int i = 0; i < 4; ++i) {
+            const int rr = 8 * i + sub_row;
             const int row = row_base + rr;
-            v[i] = *reinterpret_cast<const float4*>(stage + rr * 128 + ((sub_chunk ^ (rr & 7)) << 4));
+            v[i] = *reinterpret_cast<const float4*>(stage + rr * 64 + ((sub_chunk ^ ((rr >> 1) & 3)) << 4));
             off[i] = batch_off + (long long)row * p.ldc + col;
             ok |= (row < p.M ? 1u : 0u) << i;
           }
