@@ -203,12 +203,15 @@ int vkg_layernorm(vkg_device* dev, const float* x, const float* gamma,
  * dx16 optional f16 copy; dyxh16/dy16 optional (the reference's inputs to its
  * column sums).  When dgamma/dbeta are given they receive the column sums of
  * dy*xhat and dy directly (deterministic two-stage reduction through
- * `scratch`, which must hold vkg_layernorm_bwd_scratch_floats(rows, D)). */
+ * `scratch`, which must hold vkg_layernorm_bwd_scratch_floats(rows, D)).
+ * dxsum (optional, D % 128 == 0, D <= 1024) also receives the column sums of dx:
+ * the bias gradient of the Dense that consumes dx (Dense.backward's col_sum,
+ * transformer.py:99), saving that pass. */
 int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* x,
                       const float* gamma, const float* mu, const float* rstd,
                       const float* dres, float* dx, void* dx16, void* dyxh16,
-                      void* dy16, float* dgamma, float* dbeta, float* scratch,
-                      int rows, int D);
+                      void* dy16, float* dgamma, float* dbeta, float* dxsum,
+                      float* scratch, int rows, int D);
 int64_t vkg_layernorm_bwd_scratch_floats(int rows, int D);
 /* attn_softmax / attn_softmax_doc (tkernels.py:105-161): causal, scaled;
  * seg (optional) restricts a query to keys >= seg[b*T+q]; rows = nbh*T.

@@ -153,12 +153,15 @@ def test_layernorm_forward_backward(dev, pool, K, rows, D):
     bres = pool.up(dres)
     dx2, dx16 = pool.out(np.float32, x.shape), pool.out(np.float16, x.shape)
     dg, db = pool.out(np.float32, (D,)), pool.out(np.float32, (D,))
+    dxs = pool.out(np.float32, (D,))
+    with_dxsum = D % 128 == 0 and D <= 1024
     scratch = dev.scratch(lib.vkg_layernorm_bwd_scratch_floats(rows, D) * 4)
     runs = []
     for _ in range(2):
         _check(lib.vkg_layernorm_bwd(h, bdy.dptr, bx.dptr, bg.dptr, mu.dptr, rstd.dptr, bres.dptr,
                                      dx2.dptr, dx16.dptr, None, None, dg.dptr, db.dptr,
-                                     scratch.dptr, rows, D), "ln_bwd")
+                                     dxs.dptr if with_dxsum else None, scratch.dptr, rows, D),
+               "ln_bwd")
         dev.sync()
         runs.append((pool.get(dg, np.float32, (D,)), pool.get(db, np.float32, (D,))))
     assert np.array_equal(runs[0][0], runs[1][0]) and np.array_equal(runs[0][1], runs[1][1])
@@ -166,6 +169,8 @@ def test_layernorm_forward_backward(dev, pool, K, rows, D):
     assert relerr(pool.get(dx16, np.float16, x.shape).astype(np.float32), dxr + dres) < 1e-3
     assert relerr(runs[0][0], dgr) < 1e-4
     assert relerr(runs[0][1], dbr) < 1e-4
+    if with_dxsum:   # column sums of the output: the consuming Dense's bias gradient
+        assert relerr(pool.get(dxs, np.float32, (D,)), (dxr + dres).sum(0)) < 1e-4
 
 
 @pytest.mark.parametrize("T", [16, 64, 200])

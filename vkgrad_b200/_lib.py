@@ -88,7 +88,7 @@ _SIGNATURES = {
     "vkg_adamw_multi": (i32, [vp, vp, vp]),
     "vkg_cast16": (i32, [vp, vp, vp, i64]),
     "vkg_layernorm": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32]),
-    "vkg_layernorm_bwd": (i32, [vp] + [vp] * 13 + [i32, i32]),
+    "vkg_layernorm_bwd": (i32, [vp] + [vp] * 14 + [i32, i32]),
     "vkg_layernorm_bwd_scratch_floats": (i64, [i32, i32]),
     "vkg_attn_softmax": (i32, [vp, vp, vp, vp, i64, i32, i32, f32, i32]),
     "vkg_attn_softmax_bwd": (i32, [vp, vp, vp, vp, i64, i32, f32, i32]),

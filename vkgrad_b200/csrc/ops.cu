@@ -479,20 +479,24 @@ constexpr int LNF_SLICES = 8;
 // each slice adds every 8th block, then the slices are added in order.
 __global__ void __launch_bounds__(32 * LNF_SLICES)
 k_ln_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma,
-                 float* __restrict__ dbeta, int D, int nblocks) {
+                 float* __restrict__ dbeta, float* __restrict__ dxsum, int D, int nblocks,
+                 int nparts) {
   __shared__ float red[LNF_SLICES][32];
   const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + lane;  // column in [0, 2D): gamma part then beta part
+  const int c = blockIdx.x * 32 + lane;  // column in [0, nparts*D): gamma, beta, (dx) parts
+  const int W = nparts * D;
   float s = 0.f;
-  if (c < 2 * D)
-    for (int k = slice; k < nblocks; k += LNF_SLICES) s += scratch[(size_t)k * 2 * D + c];
+  if (c < W)
+    for (int k = slice; k < nblocks; k += LNF_SLICES) s += scratch[(size_t)k * W + c];
   red[slice][lane] = s;
   __syncthreads();
-  if (slice == 0 && c < 2 * D) {
+  if (slice == 0 && c < W) {
     float t = 0.f;
 #pragma unroll
     for (int k = 0; k < LNF_SLICES; ++k) t += red[k][lane];
-    if (c < D) dgamma[c] = t; else dbeta[c - D] = t;
+    if (c < D) dgamma[c] = t;
+    else if (c < 2 * D) dbeta[c - D] = t;
+    else dxsum[c - 2 * D] = t;
   }
 }
 
@@ -507,16 +511,17 @@ k_layernorm_bwd_vec(const float* __restrict__ dy, const float* __restrict__ x,
                     const float* __restrict__ gamma, const float* __restrict__ mu,
                     const float* __restrict__ rstd, const float* __restrict__ dres,
                     float* __restrict__ dx, __half* __restrict__ dx16,
-                    float* __restrict__ scratch, int rows) {
+                    float* __restrict__ scratch, int rows, int nparts) {
   constexpr int D = NV * 128;
   __shared__ float red[LNV_WARPS][32 * 4 + 4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float4 g[NV], ag[NV], ab[NV];
+  float4 g[NV], ag[NV], ab[NV], ax[NV];   // ax: column sums of the output (nparts == 3)
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     g[i] = *reinterpret_cast<const float4*>(gamma + (i * 32 + lane) * 4);
     ag[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    ax[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   const float inv = 1.0f / (float)D;
   const int warps_total = gridDim.x * LNV_WARPS;
@@ -563,16 +568,18 @@ k_layernorm_bwd_vec(const float* __restrict__ dy, const float* __restrict__ x,
         u.y = *reinterpret_cast<uint32_t*>(&b);
         *reinterpret_cast<uint2*>(dx16 + off) = u;
       }
+      ax[i].x += o.x; ax[i].y += o.y; ax[i].z += o.z; ax[i].w += o.w;
     }
   }
   if (scratch) {
     // add the CTA's warps in a fixed order, one 128-column group at a time
-    float* out = scratch + (size_t)blockIdx.x * 2 * D;
+    float* out = scratch + (size_t)blockIdx.x * nparts * D;
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
+    for (int part = 0; part < 3; ++part) {
+      if (part >= nparts) break;
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
-        float4 v = part == 0 ? ag[i] : ab[i];
+        float4 v = part == 0 ? ag[i] : part == 1 ? ab[i] : ax[i];
         __syncthreads();
         *reinterpret_cast<float4*>(&red[warp][lane * 4]) = v;
         __syncthreads();
@@ -983,25 +990,29 @@ static int ln_bwd_blocks(int rows) {
 
 extern "C" int64_t vkg_layernorm_bwd_scratch_floats(int rows, int D) {
   if (rows <= 0 || D <= 0) return 0;
-  return (int64_t)ln_bwd_blocks(rows) * 2 * D;
+  return (int64_t)ln_bwd_blocks(rows) * 3 * D;
 }
 
 template <int NV>
 static void launch_ln_bwd_vec(vkg_device* dev, int nblocks, const float* dy, const float* x,
                               const float* gamma, const float* mu, const float* rstd,
-                              const float* dres, float* dx, void* dx16, float* scratch, int rows) {
+                              const float* dres, float* dx, void* dx16, float* scratch, int rows,
+                              int nparts) {
   k_layernorm_bwd_vec<NV><<<nblocks, LNV_WARPS * 32, 0, dev->stream>>>(
-      dy, x, gamma, mu, rstd, dres, dx, (__half*)dx16, scratch, rows);
+      dy, x, gamma, mu, rstd, dres, dx, (__half*)dx16, scratch, rows, nparts);
 }
 
 extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* x, const float* gamma,
                                  const float* mu, const float* rstd, const float* dres, float* dx,
                                  void* dx16, void* dyxh16, void* dy16, float* dgamma, float* dbeta,
-                                 float* scratch, int rows, int D) {
+                                 float* dxsum, float* scratch, int rows, int D) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(dy && x && gamma && mu && rstd && rows > 0 && D > 0, "layernorm_bwd: bad arguments");
   const bool fused = dgamma != nullptr || dbeta != nullptr;
   if (fused) VKG_REQUIRE(dgamma && dbeta && scratch, "layernorm_bwd: dgamma, dbeta and scratch go together");
+  const int nparts = dxsum ? 3 : 2;
+  VKG_REQUIRE(!dxsum || (fused && D % 128 == 0 && D <= 1024 && !dyxh16 && !dy16),
+              "layernorm_bwd: dxsum needs dgamma/dbeta and D a multiple of 128 up to 1024");
   int nblocks = ln_bwd_blocks(rows);
   const bool aligned = ((((uintptr_t)dy | (uintptr_t)x | (uintptr_t)gamma | (uintptr_t)dres |
                           (uintptr_t)dx | (uintptr_t)scratch) & 15) == 0) && (((uintptr_t)dx16 & 7) == 0);
@@ -1011,14 +1022,14 @@ extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* 
     if (nb > nblocks) nb = nblocks;
     float* sc = fused ? scratch : nullptr;
     switch (D / 128) {
-      case 1: launch_ln_bwd_vec<1>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
-      case 2: launch_ln_bwd_vec<2>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
-      case 3: launch_ln_bwd_vec<3>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
-      case 4: launch_ln_bwd_vec<4>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
-      case 5: launch_ln_bwd_vec<5>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
-      case 6: launch_ln_bwd_vec<6>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
-      case 7: launch_ln_bwd_vec<7>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
-      default: launch_ln_bwd_vec<8>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows); break;
+      case 1: launch_ln_bwd_vec<1>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows, nparts); break;
+      case 2: launch_ln_bwd_vec<2>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows, nparts); break;
+      case 3: launch_ln_bwd_vec<3>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows, nparts); break;
+      case 4: launch_ln_bwd_vec<4>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows, nparts); break;
+      case 5: launch_ln_bwd_vec<5>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows, nparts); break;
+      case 6: launch_ln_bwd_vec<6>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows, nparts); break;
+      case 7: launch_ln_bwd_vec<7>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows, nparts); break;
+      default: launch_ln_bwd_vec<8>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows, nparts); break;
     }
     if (vkg_check_launch("layernorm_bwd_vec")) return 1;
     nblocks = nb;
@@ -1034,8 +1045,10 @@ extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* 
     if (vkg_check_launch("layernorm_bwd")) return 1;
   }
   if (fused) {
-    k_ln_param_final<<<(2 * D + 31) / 32, 32 * LNF_SLICES, 0, dev->stream>>>(scratch, dgamma, dbeta, D,
-                                                                             nblocks);
+    VKG_REQUIRE(!dxsum || (D % 128 == 0 && D <= 1024 && aligned),
+                "layernorm_bwd: dxsum needs 16-byte aligned operands");
+    k_ln_param_final<<<(nparts * D + 31) / 32, 32 * LNF_SLICES, 0, dev->stream>>>(
+        scratch, dgamma, dbeta, dxsum, D, nblocks, nparts);
     return vkg_check_launch("ln_param_final");
   }
   return 0;

@@ -29,7 +29,7 @@ def make_transformer_kernels(dev):
                           n // W, int(D)), "layernorm"))
     op("layernorm_bwd", 8, lambda b, n, D: _check(
         lib.vkg_layernorm_bwd(h, b[0].dptr, b[1].dptr, b[2].dptr, b[3].dptr, b[4].dptr, None,
-                              b[5].dptr, None, b[6].dptr, b[7].dptr, None, None, None,
+                              b[5].dptr, None, b[6].dptr, b[7].dptr, None, None, None, None,
                               n // W, int(D)), "layernorm_bwd"))
     op("attn_softmax", 2, lambda b, n, T, scale: _check(
         lib.vkg_attn_softmax(h, b[0].dptr, None, b[1].dptr, n // W, int(T), 1, float(scale), 0),

@@ -76,20 +76,29 @@ class LayerNorm:
         self.ctx.launch(graph, go, "layernorm", self.rows * self.D * 6)
         return self.y16
 
-    def backward(self, dy32, graph=None, dres=None):
-        """dx = LN'(dy) (+ dres); also writes dx16, g.g32 and b.g32.  Returns dx."""
+    def can_sum_dx(self):
+        """Whether backward() can also produce the column sums of dx (the bias gradient
+        of the Dense that consumes dx) in the same pass."""
+        return self.D % 128 == 0 and self.D <= 1024
+
+    def backward(self, dy32, graph=None, dres=None, dxsum=None):
+        """dx = LN'(dy) (+ dres); also writes dx16, g.g32 and b.g32, and, when dxsum is
+        given (see can_sum_dx), the column sums of dx into it.  Returns dx."""
         c, dev = self.ctx, self.ctx.dev
         lib, h = dev.lib, dev.handle
         R, D = self.rows, self.D
         x32 = self.x32
         dres_p = None if dres is None else dres.dptr
+        if dxsum is not None and not self.can_sum_dx():
+            raise ValueError("dxsum needs D to be a multiple of 128 and at most 1024")
+        dxsum_p = None if dxsum is None else dxsum.dptr
         if D <= _LN_FUSED_MAX_D:
             scratch = dev.scratch(lib.vkg_layernorm_bwd_scratch_floats(R, D) * 4)
 
             def go():
                 _check(lib.vkg_layernorm_bwd(h, dy32.dptr, x32.dptr, self.g.w32.dptr, self.mu.dptr,
                                              self.rstd.dptr, dres_p, self.dx.dptr, self.dx16.dptr,
-                                             None, None, self.g.g32.dptr, self.b.g32.dptr,
+                                             None, None, self.g.g32.dptr, self.b.g32.dptr, dxsum_p,
                                              scratch.dptr, R, D), "layernorm_bwd")
             c.launch(graph, go, "layernorm_bwd", R * D * 18)
         else:
@@ -99,7 +108,7 @@ class LayerNorm:
             def go():
                 _check(lib.vkg_layernorm_bwd(h, dy32.dptr, x32.dptr, self.g.w32.dptr, self.mu.dptr,
                                              self.rstd.dptr, dres_p, self.dx.dptr, self.dx16.dptr,
-                                             dyxh.dptr, dy16.dptr, None, None, None, R, D),
+                                             dyxh.dptr, dy16.dptr, None, None, None, None, R, D),
                        "layernorm_bwd")
             c.launch(graph, go, "layernorm_bwd", R * D * 22)
             c.col_sum(dyxh, self.g.g32, D, R, graph=graph)
@@ -137,12 +146,15 @@ class Dense:
         return out
 
     def backward(self, dy16, need_dx=True, graph=None, dx=None, dx_dtype=F32, dact_z=None,
-                 dact=ACT_NONE):
+                 dact=ACT_NONE, bias_grad_done=False):
+        """bias_grad_done: the producer of dy16 already wrote b.g32 (LayerNorm.backward's
+        dxsum), so the column-sum pass is skipped."""
         c, dev = self.ctx, self.ctx.dev
         R, I, O = self.rows, self.in_f, self.out_f
         gemm(dev, self.x16, dy16, self.W.g32, I, O, R, trans_a=True, graph=graph,
              name=f"{self.name}.dW")
-        c.col_sum(dy16, self.b.g32, O, R, graph=graph)
+        if not bias_grad_done:
+            c.col_sum(dy16, self.b.g32, O, R, graph=graph)
         if not need_dx:
             return None
         if dx is None:
@@ -238,11 +250,12 @@ class Attention:
                     c_dtype=F16, causal=2, name="pv")
         return self.proj.forward(self.ao16, graph=graph, out=out, residual=residual)
 
-    def backward(self, dy16, graph=None):
+    def backward(self, dy16, graph=None, proj_bias_grad_done=False):
         """dy16: gradient of the projection's output.  Returns d(ln1 output), fp32."""
         c, lib, h = self.ctx, self.ctx.dev.lib, self.ctx.dev.handle
         T, hd = self.T, self.hd
-        self.proj.backward(dy16, need_dx=True, graph=graph, dx=self.dao16, dx_dtype=F16)
+        self.proj.backward(dy16, need_dx=True, graph=graph, dx=self.dao16, dx_dtype=F16,
+                           bias_grad_done=proj_bias_grad_done)
         if self.fused:
             seg_f = None if self._seg is None else self._seg.dptr
 
@@ -300,17 +313,24 @@ class Block:
         self.fc2.forward(self.h16, graph=graph, out=self.res2, residual=self.res1)
         return self.res2
 
-    def backward(self, d32, d16, graph=None):
+    def backward(self, d32, d16, graph=None, fc2_bias_grad_done=False, below=None):
         """d32/d16: gradient of the block output in both precisions.
-        Returns the gradient of the block input as (fp32, fp16)."""
+        Returns the gradient of the block input as (fp32, fp16).
+
+        fc2_bias_grad_done: whoever produced d16 already reduced its column sums into
+        fc2.b.g32.  below: the block that consumes this block's input gradient; its fc2
+        bias gradient is then produced by this block's last layernorm backward."""
         # MLP branch; the residual sends the same gradient down both paths.
         self.fc2.backward(d16, graph=graph, dx=self.dh16, dx_dtype=F16, dact_z=self.z1,
-                          dact=ACT_GELU)
+                          dact=ACT_GELU, bias_grad_done=fc2_bias_grad_done)
         dln2 = self.fc1.backward(self.dh16, graph=graph)
-        dres1 = self.ln2.backward(dln2, graph=graph, dres=d32)
+        fuse = self.ln2.can_sum_dx()
+        dres1 = self.ln2.backward(dln2, graph=graph, dres=d32,
+                                  dxsum=self.attn.proj.b.g32 if fuse else None)
         # attention branch
-        dln1 = self.attn.backward(self.ln2.dx16, graph=graph)
-        dx = self.ln1.backward(dln1, graph=graph, dres=dres1)
+        dln1 = self.attn.backward(self.ln2.dx16, graph=graph, proj_bias_grad_done=fuse)
+        dx = self.ln1.backward(dln1, graph=graph, dres=dres1,
+                               dxsum=below.fc2.b.g32 if (below is not None and fuse) else None)
         return dx, self.ln1.dx16
 
     def params(self):
@@ -427,10 +447,13 @@ class GPT:
             def zero_tok():
                 _check(lib.vkg_memset0(h, self.tok.g32.dptr, self.tok.n * 4), "zero tok grad")
             c.launch(gh, zero_tok, "zero", self.tok.n * 4)
-        d32 = self.lnf.backward(d, graph=gh)
+        fuse = self.lnf.can_sum_dx() and L > 0
+        d32 = self.lnf.backward(d, graph=gh, dxsum=self.blocks[-1].fc2.b.g32 if fuse else None)
         d16 = self.lnf.dx16
-        for k, b in enumerate(reversed(self.blocks)):
-            d32, d16 = b.backward(d32, d16, graph=g(L + 2 + k))
+        for k in range(L):
+            i = L - 1 - k
+            d32, d16 = self.blocks[i].backward(d32, d16, graph=g(L + 2 + k), fc2_bias_grad_done=fuse,
+                                               below=self.blocks[i - 1] if i > 0 else None)
         ge = g(2 * L + 2)
         seg_p = None if seg is None else seg.dptr
 
