@@ -104,7 +104,8 @@ def test_column_sums(dev, pool, K, nrow, ncol):
     assert relerr(pool.get(s3, np.float32, (ncol,)), g.sum(0) + 1.0) < 1e-5
 
 
-@pytest.mark.parametrize("rows,stride,ncls", [(16, 16, 10), (64, 272, 257), (8, 50272, 50257)])
+@pytest.mark.parametrize("rows,stride,ncls", [(16, 16, 10), (64, 272, 257), (8, 50272, 50257),
+                                              (4, 16384, 16000), (4, 36864, 36001)])
 def test_softmax_ce(dev, pool, K, rows, stride, ncls):
     rng = np.random.default_rng(2)
     logits = (3 * rng.standard_normal((rows, stride))).astype(np.float32)

@@ -291,17 +291,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
 // delta[row, h] = sum_d dO * O (equals sum_j dP_ij P_ij of tkernels.py:176-179).
 __global__ void attn_delta_kernel(const __half* __restrict__ dout, const __half* __restrict__ out,
                                   float* __restrict__ delta, int B, int T, int H) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;   // (row, h)
-  if (item >= (long long)B * T * H) return;
-  const int h = (int)(item % H);
-  const long long row = item / H;
-  const int b = (int)(row / T), t = (int)(row % T);
-  const size_t off = (size_t)row * H * FA_HD + h * FA_HD + lane * 2;
-  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(dout + off));
-  const float2 o = __half22float2(*reinterpret_cast<const __half2*>(out + off));
-  const float s = warp_sum(a.x * o.x + a.y * o.y);
-  if (lane == 0) delta[(size_t)(b * H + h) * T + t] = s;
+  // eight lanes per (row, head): one 16-byte load of dO and of O each
+  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;   // (row, h)
+  const int sub = threadIdx.x & 7;
+  const bool live = item < (long long)B * T * H;
+  float s = 0.f;
+  int h = 0;
+  long long row = 0;
+  if (live) {
+    h = (int)(item % H);
+    row = item / H;
+    const size_t off = (size_t)row * H * FA_HD + h * FA_HD + sub * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(dout + off);
+    const uint4 o = *reinterpret_cast<const uint4*>(out + off);
+    const __half2* ah = reinterpret_cast<const __half2*>(&a);
+    const __half2* oh = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __half22float2(ah[i]), y = __half22float2(oh[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  if (live && sub == 0) {
+    const int b = (int)(row / T), t = (int)(row % T);
+    delta[(size_t)(b * H + h) * T + t] = s;
+  }
 }
 
 // One 32-key chunk of a (query row, key tile) pair: rebuild P from S and the saved
@@ -773,7 +790,8 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
     attr_set = true;
   }
   const long long items = (long long)B * T * H;
-  attn_delta_kernel<<<(unsigned)((items + 7) / 8), 256, 0, dev->stream>>>(
+  VKG_REQUIRE((((uintptr_t)dout16 | (uintptr_t)out16) & 15) == 0, "attn_bwd: dO and O must be 16-byte aligned");
+  attn_delta_kernel<<<(unsigned)((items * 8 + 255) / 256), 256, 0, dev->stream>>>(
       (const __half*)dout16, (const __half*)out16, delta, B, T, H);
   if (vkg_check_launch("attn_delta_kernel")) return 1;
   const unsigned ctas = (unsigned)((long long)p.nqt * H * B);

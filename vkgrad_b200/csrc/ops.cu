@@ -379,6 +379,104 @@ k_softmax_ce(const float* __restrict__ logits, const uint32_t* __restrict__ labe
   }
 }
 
+// Register-resident variant for wide rows (the GPT head: 50 272 columns): one CTA of
+// 768 threads per row, every thread keeps up to NV float4 of the row in registers, so
+// the logits are read from HBM exactly once and the gradient is written from registers.
+constexpr int CE_THREADS = 768;
+
+template <int NV>
+__global__ void __launch_bounds__(CE_THREADS)
+k_softmax_ce_reg(const float* __restrict__ logits, const uint32_t* __restrict__ labels,
+                 const float* __restrict__ w, __half* __restrict__ dl16, float* __restrict__ dl32,
+                 float* __restrict__ loss, int stride, int ncls, float grad_scale) {
+  __shared__ float s_red[CE_THREADS / 32];
+  __shared__ float s_bcast;
+  const int row = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const float* x = logits + (size_t)row * stride;
+  const int n4 = stride >> 2;
+  float wi = grad_scale;
+  bool skip = false;
+  if (w) {
+    wi = w[row];
+    skip = wi == 0.0f;
+  }
+  float4 v[NV];
+  float m = -1e30f;
+  if (!skip) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c4 = tid + i * CE_THREADS;
+      v[i] = c4 < n4 ? *reinterpret_cast<const float4*>(x + 4 * c4) : make_float4(0, 0, 0, 0);
+      const int c = 4 * c4;
+      if (c + 0 < ncls) m = fmaxf(m, v[i].x);
+      if (c + 1 < ncls) m = fmaxf(m, v[i].y);
+      if (c + 2 < ncls) m = fmaxf(m, v[i].z);
+      if (c + 3 < ncls) m = fmaxf(m, v[i].w);
+    }
+  }
+  m = warp_max(m);
+  if (lane == 0) s_red[warp] = m;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < CE_THREADS / 32 ? s_red[lane] : -1e30f;
+    t = warp_max(t);
+    if (lane == 0) s_bcast = t;
+  }
+  __syncthreads();
+  m = s_bcast;
+  float sum = 0.f;
+  if (!skip) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = 4 * (tid + i * CE_THREADS);
+      // keep exp(x - m) in place of x: it is what the gradient needs
+      v[i].x = c + 0 < ncls ? __expf(v[i].x - m) : 0.f;
+      v[i].y = c + 1 < ncls ? __expf(v[i].y - m) : 0.f;
+      v[i].z = c + 2 < ncls ? __expf(v[i].z - m) : 0.f;
+      v[i].w = c + 3 < ncls ? __expf(v[i].w - m) : 0.f;
+      sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  sum = warp_sum(sum);
+  __syncthreads();
+  if (lane == 0) s_red[warp] = sum;
+  __syncthreads();
+  if (warp == 0) {
+    float t = warp_sum(lane < CE_THREADS / 32 ? s_red[lane] : 0.f);
+    if (lane == 0) s_bcast = t;
+  }
+  __syncthreads();
+  sum = s_bcast;
+  const int y = (int)labels[row];
+  if (tid == 0) loss[row] = skip ? 0.f : (m + logf(sum)) - x[y];
+  const float k = skip ? 0.f : wi / sum;
+  __half* d16 = dl16 ? dl16 + (size_t)row * stride : nullptr;
+  float* d32 = dl32 ? dl32 + (size_t)row * stride : nullptr;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c4 = tid + i * CE_THREADS;
+    if (c4 >= n4) continue;
+    const int c = 4 * c4;
+    float4 g = skip ? make_float4(0, 0, 0, 0)
+                    : make_float4(v[i].x * k, v[i].y * k, v[i].z * k, v[i].w * k);
+    if (!skip && y >= c && y < c + 4) {
+      if (y == c) g.x -= wi;
+      else if (y == c + 1) g.y -= wi;
+      else if (y == c + 2) g.z -= wi;
+      else g.w -= wi;
+    }
+    if (d16) {
+      __half2 a = __floats2half2_rn(g.x, g.y), b = __floats2half2_rn(g.z, g.w);
+      uint2 u;
+      u.x = *reinterpret_cast<uint32_t*>(&a);
+      u.y = *reinterpret_cast<uint32_t*>(&b);
+      *reinterpret_cast<uint2*>(d16 + c) = u;
+    }
+    if (d32) *reinterpret_cast<float4*>(d32 + c) = g;
+  }
+}
+
 // ---- layernorm ----------------------------------------------------------------------------
 
 // One warp per row, lanes stride the row (the reference's layout, tkernels.py:32-54).
@@ -404,6 +502,50 @@ __global__ void k_layernorm(const float* __restrict__ x, const float* __restrict
   }
   __half* yr = y16 + (int64_t)row * D;
   for (int d = lane; d < D; d += 32) yr[d] = __float2half_rn((xr[d] - m) * r * gamma[d] + beta[d]);
+}
+
+// D = 128 * NV: the row lives in registers (NV float4 per lane), one read of x.
+template <int NV>
+__global__ void k_layernorm_vec(const float* __restrict__ x, const float* __restrict__ gamma,
+                                const float* __restrict__ beta, __half* __restrict__ y16,
+                                float* __restrict__ mu, float* __restrict__ rstd, int rows) {
+  constexpr int D = NV * 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  const float* xr = x + (size_t)row * D;
+  float4 v[NV];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    v[i] = *reinterpret_cast<const float4*>(xr + (i * 32 + lane) * 4);
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  const float m = warp_sum(s) * (1.0f / D);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    v[i].x -= m; v[i].y -= m; v[i].z -= m; v[i].w -= m;
+    q += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+  }
+  const float r = rsqrtf(warp_sum(q) * (1.0f / D) + 1e-5f);
+  if (lane == 0) {
+    mu[row] = m;
+    rstd[row] = r;
+  }
+  __half* yr = y16 + (size_t)row * D;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 4;
+    const float4 g = *reinterpret_cast<const float4*>(gamma + c);
+    const float4 b = *reinterpret_cast<const float4*>(beta + c);
+    __half2 lo = __floats2half2_rn(v[i].x * r * g.x + b.x, v[i].y * r * g.y + b.y);
+    __half2 hi = __floats2half2_rn(v[i].z * r * g.z + b.z, v[i].w * r * g.w + b.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&lo);
+    u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(yr + c) = u;
+  }
 }
 
 constexpr int LNB_WARPS = 4;
@@ -894,6 +1036,21 @@ extern "C" int vkg_softmax_ce(vkg_device* dev, const float* logits, const uint32
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(logits && labels && loss && rows > 0 && stride >= ncls && ncls > 0,
               "softmax_ce: bad arguments");
+  const bool aligned = stride % 4 == 0 && (((uintptr_t)logits | (uintptr_t)dl32) & 15) == 0 &&
+                       ((uintptr_t)dl16 & 7) == 0;
+  const int n4 = stride / 4;
+  if (aligned && n4 > 4 * CE_THREADS && n4 <= 17 * CE_THREADS) {
+    // wide rows: one read of the logits, everything else from registers
+    const int nv = (n4 + CE_THREADS - 1) / CE_THREADS;
+#define VKG_CE(NV)                                                                              \
+  k_softmax_ce_reg<NV><<<rows, CE_THREADS, 0, dev->stream>>>(logits, labels, w, (__half*)dl16, dl32, \
+                                                             loss, stride, ncls, grad_scale)
+    if (nv <= 8) VKG_CE(8);
+    else if (nv <= 12) VKG_CE(12);
+    else VKG_CE(17);
+#undef VKG_CE
+    return vkg_check_launch("softmax_ce_reg");
+  }
   k_softmax_ce<<<rows, TPB, 0, dev->stream>>>(logits, labels, w, (__half*)dl16, dl32, loss, stride,
                                               ncls, grad_scale);
   return vkg_check_launch("softmax_ce");
@@ -976,6 +1133,25 @@ extern "C" int vkg_layernorm(vkg_device* dev, const float* x, const float* gamma
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(x && gamma && beta && y16 && mu && rstd && rows > 0 && D > 0, "layernorm: bad arguments");
   const int wpb = 4;
+  const bool aligned = ((((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)beta) & 15) == 0) &&
+                       (((uintptr_t)y16 & 7) == 0);
+  if (aligned && D % 128 == 0 && D <= 1024) {
+    const unsigned grid = (rows + wpb - 1) / wpb;
+#define VKG_LN(NV) \
+  k_layernorm_vec<NV><<<grid, wpb * 32, 0, dev->stream>>>(x, gamma, beta, (__half*)y16, mu, rstd, rows)
+    switch (D / 128) {
+      case 1: VKG_LN(1); break;
+      case 2: VKG_LN(2); break;
+      case 3: VKG_LN(3); break;
+      case 4: VKG_LN(4); break;
+      case 5: VKG_LN(5); break;
+      case 6: VKG_LN(6); break;
+      case 7: VKG_LN(7); break;
+      default: VKG_LN(8); break;
+    }
+#undef VKG_LN
+    return vkg_check_launch("layernorm_vec");
+  }
   k_layernorm<<<(rows + wpb - 1) / wpb, wpb * 32, 0, dev->stream>>>(x, gamma, beta, (__half*)y16, mu,
                                                                     rstd, rows, D);
   return vkg_check_launch("layernorm");
