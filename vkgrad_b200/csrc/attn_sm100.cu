@@ -190,19 +190,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(8));        // S may be overwritten
+      // the scale is positive, so the maximum of the raw scores is enough here
+      if (need_mask) {
 #pragma unroll
-      for (int e = 0; e < 64; ++e) {
-        float t = __uint_as_float(r[e]) * p.cscale;
-        if (need_mask) {
+        for (int e = 0; e < 64; ++e) {
           const int key = j * FA_T + half * 64 + e;
-          if (key > qi || key < st) t = -1e30f;
+          if (key <= qi && key >= st) m = fmaxf(m, __uint_as_float(r[e]));
         }
-        m = fmaxf(m, t);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) m = fmaxf(m, __uint_as_float(r[e]));
       }
     }
     xchg[half * 128 + qr] = m;
     asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight softmax warps
-    m = fmaxf(xchg[qr], xchg[128 + qr]);
+    m = fmaxf(xchg[qr], xchg[128 + qr]) * p.cscale;  // row maximum of the scaled scores
+    const float nm = -m;
     asm volatile("bar.sync 1, 256;" ::: "memory");
     // pass 2: P = exp2(t - m) rounded to fp16 (normalised by 1/l at the very end), l in fp32
     for (int j = 0; j < nj && ok; ++j, ++it) {
@@ -228,13 +231,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
 #pragma unroll
           for (int w = 0; w < 2; ++w) {
             const int idx = u * 8 + 2 * e + w;
-            const float t = __uint_as_float(r[idx]) * p.cscale;
-            bool valid = true;
+            float pr = vkg_ex2(fmaf(__uint_as_float(r[idx]), p.cscale, nm));
             if (need_mask) {
               const int key = j * FA_T + half * 64 + idx;
-              valid = key <= qi && key >= st;
+              if (key > qi || key < st) pr = 0.f;
             }
-            pv[w] = valid ? vkg_ex2(t - m) : 0.f;
+            pv[w] = pr;
           }
           l += pv[0] + pv[1];
           hv[e] = __floats2half2_rn(pv[0], pv[1]);
@@ -323,12 +325,15 @@ __global__ void attn_delta_kernel(const __half* __restrict__ dout, const __half*
 
 // One 32-key chunk of a (query row, key tile) pair: rebuild P from S and the saved
 // log-sum-exp, form dS = P (dP - delta) scale, and write both (fp16) into the swizzled
-// [query row][key] layout.  `sp` may be null.  nlse = -lse2, dsc = -delta * scale, so
-// each element costs two FMAs, one exp2, one multiply and the conversions.
+// [query row][key] layout.  `sp` may be null.  nlse = -lse2 (or -inf for a row past the
+// end of the sequence, which makes its P exactly 0), dsc = -delta * scale: each element
+// costs two FMAs, one exp2, one multiply and the conversions.  MASK adds the per-element
+// causal / packed-sample test and is only compiled into the tiles that need it.
+template <bool MASK>
 __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rdp, int c, int r,
-                                          int key0, int qi, int st, bool q_ok, bool need_mask,
-                                          float cscale, float scale, float nlse, float dsc,
-                                          uint8_t* sp, uint8_t* sds) {
+                                          int key0, int qi, int st, float cscale, float scale,
+                                          float nlse, float dsc, uint8_t* sp, uint8_t* sds) {
+  const uint32_t row_off = (uint32_t)(r * 128), rx = (uint32_t)(r & 7);
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     __half2 hp[4], hd[4];
@@ -338,12 +343,11 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rd
 #pragma unroll
       for (int w = 0; w < 2; ++w) {
         const int idx = u * 8 + 2 * e + w;
-        bool valid = q_ok;
-        if (need_mask) {
+        float pr = vkg_ex2(fmaf(__uint_as_float(rs[idx]), cscale, nlse));
+        if (MASK) {
           const int key = key0 + c * 32 + idx;
-          valid = valid && key <= qi && key >= st;
+          if (key > qi || key < st) pr = 0.f;
         }
-        const float pr = valid ? vkg_ex2(fmaf(__uint_as_float(rs[idx]), cscale, nlse)) : 0.f;
         pv[w] = pr;
         dv[w] = pr * fmaf(__uint_as_float(rdp[idx]), scale, dsc);
       }
@@ -351,7 +355,7 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rd
       hd[e] = __floats2half2_rn(dv[0], dv[1]);
     }
     const int cc = c * 4 + u;
-    const uint32_t off = p_offset(cc >> 3, r, cc & 7);
+    const uint32_t off = (uint32_t)((cc >> 3) * FA_TILE_BYTES) + row_off + ((((uint32_t)cc & 7u) ^ rx) << 4);
     if (sp) *reinterpret_cast<uint4*>(sp + off) = *reinterpret_cast<uint4*>(hp);
     *reinterpret_cast<uint4*>(sds + off) = *reinterpret_cast<uint4*>(hd);
   }
@@ -359,9 +363,11 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rd
 
 // dK / dV: one CTA per (key tile, head, sequence); loops over the query tiles at or
 // below the diagonal.  TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384).
+// P and dS are double-buffered (buffer = iteration & 1) so the softmax warps can build the
+// next tile's P / dS while the tensor core still reads the previous ones for dV / dK.
 constexpr int KV_K = 0, KV_V = FA_TILE_BYTES, KV_Q = 2 * FA_TILE_BYTES, KV_DO = 4 * FA_TILE_BYTES,
-              KV_P = 6 * FA_TILE_BYTES, KV_DS = 8 * FA_TILE_BYTES, KV_BAR = 10 * FA_TILE_BYTES,
-              KV_SMEM = KV_BAR + 256 + 1024;
+              KV_P = 6 * FA_TILE_BYTES, KV_DS = 8 * FA_TILE_BYTES, KV_PDS_STRIDE = 4 * FA_TILE_BYTES,
+              KV_BAR = 14 * FA_TILE_BYTES, KV_SMEM = KV_BAR + 256 + 1024;
 
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
@@ -370,7 +376,8 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar = base + KV_BAR;
-  // 0 kv_full, 1-2 qd_full, 3-4 qd_empty, 5 sdp_full, 6 sdp_free, 7 pds_full, 8 pds_free, 9 out_full
+  // 0 kv_full, 1-2 qd_full, 3-4 qd_empty, 5 sdp_full, 6 sdp_free, 7/10 pds_full[2],
+  // 8/11 pds_free[2], 9 out_full
   auto B_ = [bar](int i) { return bar + 8u * i; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 128);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 136);
@@ -383,7 +390,8 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
   const int ni = p.nqt - kt;                         // query tiles kt .. nqt-1
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 10; ++i) mbar_init(B_(i), (i == 6 || i == 7) ? FA_SOFTMAX_WARPS : 1);
+    for (int i = 0; i < 12; ++i)
+      mbar_init(B_(i), (i == 6 || i == 7 || i == 10) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -442,11 +450,12 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           ok = issue_sdp(it + 1);
           if (!ok) break;
         }
-        ok = mbar_wait(B_(7), it & 1, abort_flag, p.err, 0x4500u);
+        const int pb = it & 1;     // P / dS buffer of this iteration
+        ok = mbar_wait(B_(7 + 3 * pb), (it >> 1) & 1, abort_flag, p.err, 0x4500u);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
-        const uint32_t sp = base + KV_P, sds = base + KV_DS;
+        const uint32_t sp = base + KV_P + pb * KV_PDS_STRIDE, sds = base + KV_DS + pb * KV_PDS_STRIDE;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)      // K = 128 query rows, 16 at a time
           umma_f16(tdV, make_smem_desc(sp + kk * 2048, FA_TILE_BYTES, 1024),
@@ -455,8 +464,8 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
         for (int kk = 0; kk < 8; ++kk)
           umma_f16(tdK, make_smem_desc(sds + kk * 2048, FA_TILE_BYTES, 1024),
                    make_smem_desc(sq + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
-        umma_commit(B_(3 + s));   // Q / dO stage free
-        umma_commit(B_(8));       // P / dS free
+        umma_commit(B_(3 + s));        // Q / dO stage free
+        umma_commit(B_(8 + 3 * pb));   // this P / dS buffer free
       }
       if (ok) umma_commit(B_(9));
     }
@@ -470,7 +479,8 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       const int qi = qt * FA_T + r;
       const bool q_ok = qi < p.T;
       const size_t sidx = (size_t)(b * p.H + h) * p.T + (q_ok ? qi : 0);
-      const float nlse = -p.lse2[sidx], dsc = -p.delta[sidx] * p.scale;
+      // a row past the end of the sequence gets lse = +inf, hence P = 0 and dS = 0
+      const float nlse = q_ok ? -p.lse2[sidx] : -INFINITY, dsc = -p.delta[sidx] * p.scale;
       const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
       const bool need_mask = (qt == kt) || (p.seg != nullptr);
       ok = mbar_wait(B_(5), it & 1, abort_flag, p.err, 0x4600u);
@@ -485,15 +495,23 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(6));          // S / dP may be overwritten
-      ok = mbar_wait(B_(8), (it & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // P / dS buffers free
+      const int pb = it & 1;
+      ok = mbar_wait(B_(8 + 3 * pb), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // buffer free
       if (!ok) break;
-      bwd_chunk(rs, rdp, 2 * half, r, k0, qi, st, q_ok, need_mask, p.cscale, p.scale, nlse, dsc,
-                gbase + KV_P, gbase + KV_DS);
-      bwd_chunk(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, q_ok, need_mask, p.cscale, p.scale,
-                nlse, dsc, gbase + KV_P, gbase + KV_DS);
+      uint8_t* sp = gbase + KV_P + pb * KV_PDS_STRIDE;
+      uint8_t* sds = gbase + KV_DS + pb * KV_PDS_STRIDE;
+      if (need_mask) {
+        bwd_chunk<true>(rs, rdp, 2 * half, r, k0, qi, st, p.cscale, p.scale, nlse, dsc, sp, sds);
+        bwd_chunk<true>(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, p.cscale, p.scale, nlse, dsc,
+                        sp, sds);
+      } else {
+        bwd_chunk<false>(rs, rdp, 2 * half, r, k0, qi, st, p.cscale, p.scale, nlse, dsc, sp, sds);
+        bwd_chunk<false>(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, p.cscale, p.scale, nlse, dsc,
+                         sp, sds);
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(B_(7));
+      if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
     }
     if (ok) ok = mbar_wait(B_(9), 0, abort_flag, p.err, 0x4800u);
     if (ok) {
@@ -536,7 +554,8 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
 // dQ: one CTA per (query tile, head, sequence); loops over the key tiles up to the
 // diagonal.  TMEM: S [0,128) dP [128,256) dQ [256,320).
 constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_K = 2 * FA_TILE_BYTES, DQ_V = 4 * FA_TILE_BYTES,
-              DQ_DS = 6 * FA_TILE_BYTES, DQ_BAR = 8 * FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
+              DQ_DS = 6 * FA_TILE_BYTES, DQ_DS_STRIDE = 2 * FA_TILE_BYTES,   // dS double-buffered
+              DQ_BAR = 10 * FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
 
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
@@ -545,7 +564,8 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar = base + DQ_BAR;
-  // 0 qd_full, 1-2 kv_full, 3-4 kv_empty, 5 sdp_full, 6 sdp_free, 7 ds_full, 8 ds_free, 9 out_full
+  // 0 qd_full, 1-2 kv_full, 3-4 kv_empty, 5 sdp_full, 6 sdp_free, 7/10 ds_full[2],
+  // 8/11 ds_free[2], 9 out_full
   auto B_ = [bar](int i) { return bar + 8u * i; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 128);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 136);
@@ -558,7 +578,8 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   const int nj = qt + 1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 10; ++i) mbar_init(B_(i), (i == 6 || i == 7) ? FA_SOFTMAX_WARPS : 1);
+    for (int i = 0; i < 12; ++i)
+      mbar_init(B_(i), (i == 6 || i == 7 || i == 10) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -615,17 +636,18 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
           ok = issue_sdp(j + 1);
           if (!ok) break;
         }
-        ok = mbar_wait(B_(7), j & 1, abort_flag, p.err, 0x5500u);
+        const int pb = j & 1;
+        ok = mbar_wait(B_(7 + 3 * pb), (j >> 1) & 1, abort_flag, p.err, 0x5500u);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES;
-        const uint32_t sds = base + DQ_DS;
+        const uint32_t sds = base + DQ_DS + pb * DQ_DS_STRIDE;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)      // K = 128 keys
           umma_f16(tdQ, make_smem_desc(sds + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
                    make_smem_desc(sk + kk * 2048, 8192, 1024), idesc_q, (j | kk) ? 1u : 0u);
-        umma_commit(B_(3 + s));   // K / V stage free
-        umma_commit(B_(8));       // dS free
+        umma_commit(B_(3 + s));        // K / V stage free
+        umma_commit(B_(8 + 3 * pb));   // this dS buffer free
       }
       if (ok) umma_commit(B_(9));
     }
@@ -636,7 +658,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
     const int qi = q0 + r;
     const bool q_ok = qi < p.T;
     const size_t sidx = (size_t)(b * p.H + h) * p.T + (q_ok ? qi : 0);
-    const float nlse = -p.lse2[sidx], dsc = -p.delta[sidx] * p.scale;
+    const float nlse = q_ok ? -p.lse2[sidx] : -INFINITY, dsc = -p.delta[sidx] * p.scale;
     const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
     bool ok = true;
     for (int j = 0; j < nj && ok; ++j) {
@@ -653,15 +675,22 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(6));
-      ok = mbar_wait(B_(8), (j & 1) ^ 1u, abort_flag, p.err, 0x5700u);
+      const int pb = j & 1;
+      ok = mbar_wait(B_(8 + 3 * pb), ((j >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
       if (!ok) break;
-      bwd_chunk(rs, rdp, 2 * half, r, j * FA_T, qi, st, q_ok, need_mask, p.cscale, p.scale, nlse, dsc,
-                nullptr, gbase + DQ_DS);
-      bwd_chunk(rs + 32, rdp + 32, 2 * half + 1, r, j * FA_T, qi, st, q_ok, need_mask, p.cscale,
-                p.scale, nlse, dsc, nullptr, gbase + DQ_DS);
+      uint8_t* sds = gbase + DQ_DS + pb * DQ_DS_STRIDE;
+      if (need_mask) {
+        bwd_chunk<true>(rs, rdp, 2 * half, r, j * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
+        bwd_chunk<true>(rs + 32, rdp + 32, 2 * half + 1, r, j * FA_T, qi, st, p.cscale, p.scale, nlse,
+                        dsc, nullptr, sds);
+      } else {
+        bwd_chunk<false>(rs, rdp, 2 * half, r, j * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
+        bwd_chunk<false>(rs + 32, rdp + 32, 2 * half + 1, r, j * FA_T, qi, st, p.cscale, p.scale, nlse,
+                         dsc, nullptr, sds);
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(B_(7));
+      if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
     }
     if (ok) ok = mbar_wait(B_(9), 0, abort_flag, p.err, 0x5800u);
     if (ok) {
