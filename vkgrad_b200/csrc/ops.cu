@@ -615,10 +615,10 @@ k_layernorm_bwd(const float* __restrict__ dy, const float* __restrict__ x,
   }
 }
 
-constexpr int LNF_SLICES = 8;
+constexpr int LNF_SLICES = 32;
 
-// Fixed-order reduction of the per-block partials: 32 columns x 8 slices per CTA,
-// each slice adds every 8th block, then the slices are added in order.
+// Fixed-order reduction of the per-block partials: 32 columns x 32 slices per CTA,
+// each slice adds every 32nd block, then the slices are added in order.
 __global__ void __launch_bounds__(32 * LNF_SLICES)
 k_ln_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma,
                  float* __restrict__ dbeta, float* __restrict__ dxsum, int D, int nblocks,
