@@ -239,6 +239,23 @@ def time_attention(dev, B, T, H, hd):
     return res
 
 
+_RANDOM_BLOCK = None
+
+
+def fill_random16(dev, buf):
+    """Fill a device buffer with N(0,1) fp16 values: timings on zero operands would
+    flatter a power-limited tensor core."""
+    global _RANDOM_BLOCK
+    if _RANDOM_BLOCK is None:
+        _RANDOM_BLOCK = np.random.default_rng(7).standard_normal(8 << 20).astype(np.float16)
+    blk = _RANDOM_BLOCK
+    for off in range(0, buf.size, blk.nbytes):
+        n = min(blk.nbytes, buf.size - off)
+        rc = dev.lib.vkg_upload(dev.handle, buf.dptr + off, blk.ctypes.data, n)
+        if rc:
+            raise RuntimeError("upload of random operands failed")
+
+
 def time_gemm_shapes(dev, table):
     """CUDA-event time of each shape (back-to-back launches on the device stream)."""
     from vkgrad_b200.kernels import gemm
@@ -249,6 +266,8 @@ def time_gemm_shapes(dev, table):
         a = dev.buffer(nb * m * k * 2, "device")
         b = dev.buffer(nb * k * n * 2, "device")
         c = dev.buffer(nb * m * n * 4, "device")
+        fill_random16(dev, a)
+        fill_random16(dev, b)
         kw = dict(trans_a=s["ta"], trans_b=s["tb"], nb0=nb, sa=(m * k, 0), sb=(k * n, 0),
                   sc=(m * n, 0), causal=s.get("causal", 0))
         gemm(dev, a, b, c, m, n, k, repeat=2, **kw)
@@ -276,8 +295,11 @@ def run_single_gemm(args):
     a = dev.buffer(nb * m * k * 2, "device")
     b = dev.buffer(nb * k * n * 2, "device")
     c = dev.buffer(nb * m * n * 4, "device")
+    fill_random16(dev, a)
+    fill_random16(dev, b)
     kw = dict(trans_a=bool(ta), trans_b=bool(tb), nb0=nb, sa=(m * k, 0), sb=(k * n, 0),
-              sc=(m * n, 0), c_dtype=F16 if c16 else F32, tile_n=args.tile_n, split_k=args.split_k)
+              sc=(m * n, 0), c_dtype=F16 if c16 else F32, tile_n=args.tile_n, split_k=args.split_k,
+              max_ctas=args.max_ctas)
     gemm(dev, a, b, c, m, n, k, repeat=max(args.warmup, 1), **kw)
     t = gemm(dev, a, b, c, m, n, k, repeat=args.steps, **kw) / args.steps
     print(json.dumps({"gemm": args.gemm, "us": t * 1e6,
@@ -470,6 +492,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gpt2-small", choices=sorted(WORKLOADS))
     ap.add_argument("--loss-scale", type=float, default=4096.0)
+    ap.add_argument("--max-ctas", type=int, default=0, help="with --gemm: cap the persistent grid")
     ap.add_argument("--gemm-trio", action="store_true", help="add per-shape GEMM timings")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle timing")
     ap.add_argument("--profile", action="store_true",
