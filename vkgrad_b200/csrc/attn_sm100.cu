@@ -54,10 +54,52 @@ constexpr int FW_BAR = FW_P + 2 * FA_TILE_BYTES;
 constexpr int FW_XCHG = FW_BAR + 256;                 // [2][128] floats: row statistics exchange
 constexpr int FW_SMEM = FW_XCHG + 1024 + 1024;
 
-// 16-byte chunk `c8` (8 keys) of 64-key block `kb`, row r, in the 128B-swizzled layout
-// both TMA and the UMMA descriptors use.
-__device__ __forceinline__ uint32_t p_offset(int kb, int r, int c8) {
-  return (uint32_t)(kb * FA_TILE_BYTES + r * 128 + ((c8 ^ (r & 7)) << 4));
+// P and dS tiles use the 128B-swizzled layout of TMA and the UMMA descriptors: 16-byte
+// piece c8 (8 keys) of row r of a 64-key block sits at r * 128 + ((c8 ^ (r & 7)) << 4).
+
+// Row maximum over this thread's 64 raw scores of one key tile.  MASK adds the causal /
+// packed-sample test and is compiled only into the tiles that need it.
+template <bool MASK>
+__device__ __forceinline__ float fwd_max_tile(const uint32_t (&r)[64], int key0, int qi, int st, float m) {
+#pragma unroll
+  for (int e = 0; e < 64; ++e) {
+    if (MASK) {
+      const int key = key0 + e;
+      if (key > qi || key < st) continue;
+    }
+    m = fmaxf(m, __uint_as_float(r[e]));
+  }
+  return m;
+}
+
+// P = exp2(s * cscale - m) for this thread's 64 scores, rounded to fp16 into the swizzled
+// row `prow` (x = row & 7); returns the fp32 sum of the row's part.
+template <bool MASK>
+__device__ __forceinline__ float fwd_p_tile(const uint32_t (&r)[64], int key0, int qi, int st, float cscale,
+                                         float nm, uint8_t* prow, uint32_t x) {
+  float l = 0.f;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    __half2 hv[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float pv[2];
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const int idx = u * 8 + 2 * e + w;
+        float pr = vkg_ex2(fmaf(__uint_as_float(r[idx]), cscale, nm));
+        if (MASK) {
+          const int key = key0 + idx;
+          if (key > qi || key < st) pr = 0.f;
+        }
+        pv[w] = pr;
+      }
+      l += pv[0] + pv[1];
+      hv[e] = __floats2half2_rn(pv[0], pv[1]);
+    }
+    *reinterpret_cast<uint4*>(prow + (((uint32_t)u ^ x) << 4)) = *reinterpret_cast<uint4*>(hv);
+  }
+  return l;
 }
 
 __global__ void __launch_bounds__(FA_THREADS, 2)
@@ -103,13 +145,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       for (int pass = 0; pass < 2 && ok; ++pass) {
         for (int j = 0; j < nj && ok; ++j, ++it) {
           const int s = it & 1;
-          ok = mbar_wait(B_(3 + s), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x1100u + s);
+          ok = mbar_wait<true>(B_(3 + s), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x1100u + s);
           if (!ok) break;
           mbar_expect_tx(B_(1 + s), FA_TILE_BYTES);
           tma_load_2d(base + FW_K + s * FA_TILE_BYTES, &tm, B_(1 + s), p.D + h * FA_HD,
                       row0 + j * FA_T);
           if (pass == 1) {
-            ok = mbar_wait(B_(6), (j & 1) ^ 1u, abort_flag, p.err, 0x1200u);
+            ok = mbar_wait<true>(B_(6), (j & 1) ^ 1u, abort_flag, p.err, 0x1200u);
             if (!ok) break;
             mbar_expect_tx(B_(5), FA_TILE_BYTES);
             tma_load_2d(base + FW_V, &tm, B_(5), 2 * p.D + h * FA_HD, row0 + j * FA_T);
@@ -121,14 +163,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);     // Q K^T: both K-major, N = 128 keys
       const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);    // P V: P K-major, V MN-major, N = 64
-      bool ok = mbar_wait(B_(0), 0, abort_flag, p.err, 0x2000u);
+      bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x2000u);
       const uint32_t sq = base + FW_Q;
       // S number n (n counts both passes): wait for its K stage and for the softmax warps
       // to have pulled the previous S out of TMEM, then issue Q K^T.
       auto issue_s = [&](int n) -> bool {
         const int s = n & 1;
-        if (!(mbar_wait(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x2100u + s) &&
-              mbar_wait(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x2200u)))
+        if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x2100u + s) &&
+              mbar_wait<true>(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x2200u)))
           return false;
         tcgen05_fence_after();
         const uint32_t sk = base + FW_K + s * FA_TILE_BYTES;
@@ -150,8 +192,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
           ok = issue_s(n++);
           if (!ok) break;
         }
-        ok = mbar_wait(B_(9), j & 1, abort_flag, p.err, 0x2300u) &&
-             mbar_wait(B_(5), j & 1, abort_flag, p.err, 0x2400u);
+        ok = mbar_wait<true>(B_(9), j & 1, abort_flag, p.err, 0x2300u) &&
+             mbar_wait<true>(B_(5), j & 1, abort_flag, p.err, 0x2400u);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t sp = base + FW_P, sv = base + FW_V;
@@ -179,7 +221,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     int it = 0;
     // pass 1: row maximum of the scaled scores (no exponentials)
     for (int j = 0; j < nj && ok; ++j, ++it) {
-      ok = mbar_wait(B_(7), it & 1, abort_flag, p.err, 0x3100u);
+      ok = mbar_wait<true>(B_(7), it & 1, abort_flag, p.err, 0x3100u);
       if (!ok) break;
       tcgen05_fence_after();
       const bool need_mask = (j == qt) || (p.seg != nullptr);
@@ -191,16 +233,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(8));        // S may be overwritten
       // the scale is positive, so the maximum of the raw scores is enough here
-      if (need_mask) {
-#pragma unroll
-        for (int e = 0; e < 64; ++e) {
-          const int key = j * FA_T + half * 64 + e;
-          if (key <= qi && key >= st) m = fmaxf(m, __uint_as_float(r[e]));
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 64; ++e) m = fmaxf(m, __uint_as_float(r[e]));
-      }
+      if (need_mask) m = fwd_max_tile<true>(r, j * FA_T + half * 64, qi, st, m);
+      else m = fwd_max_tile<false>(r, 0, 0, 0, m);
     }
     xchg[half * 128 + qr] = m;
     asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight softmax warps
@@ -209,7 +243,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     asm volatile("bar.sync 1, 256;" ::: "memory");
     // pass 2: P = exp2(t - m) rounded to fp16 (normalised by 1/l at the very end), l in fp32
     for (int j = 0; j < nj && ok; ++j, ++it) {
-      ok = mbar_wait(B_(7), it & 1, abort_flag, p.err, 0x3150u);
+      ok = mbar_wait<true>(B_(7), it & 1, abort_flag, p.err, 0x3150u);
       if (!ok) break;
       tcgen05_fence_after();
       const bool need_mask = (j == qt) || (p.seg != nullptr);
@@ -220,29 +254,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(8));
-      ok = mbar_wait(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x3200u);   // P buffer free
+      ok = mbar_wait<true>(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x3200u);   // P buffer free
       if (!ok) break;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        __half2 hv[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float pv[2];
-#pragma unroll
-          for (int w = 0; w < 2; ++w) {
-            const int idx = u * 8 + 2 * e + w;
-            float pr = vkg_ex2(fmaf(__uint_as_float(r[idx]), p.cscale, nm));
-            if (need_mask) {
-              const int key = j * FA_T + half * 64 + idx;
-              if (key > qi || key < st) pr = 0.f;
-            }
-            pv[w] = pr;
-          }
-          l += pv[0] + pv[1];
-          hv[e] = __floats2half2_rn(pv[0], pv[1]);
-        }
-        *reinterpret_cast<uint4*>(gbase + FW_P + p_offset(half, qr, u)) = *reinterpret_cast<uint4*>(hv);
-      }
+      uint8_t* prow = gbase + FW_P + half * FA_TILE_BYTES + qr * 128;
+      if (need_mask) l += fwd_p_tile<true>(r, j * FA_T + half * 64, qi, st, p.cscale, nm, prow, qr & 7);
+      else l += fwd_p_tile<false>(r, 0, 0, 0, p.cscale, nm, prow, qr & 7);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(9));        // this warp's part of P is in shared memory
@@ -252,7 +268,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     l = xchg[qr] + xchg[128 + qr];
     const float inv_l = 1.0f / l;               // l >= 1: key == query is always valid
     if (half == 0 && q_ok) p.lse2[(size_t)(b * p.H + h) * p.T + qi] = m + log2f(l);
-    if (ok) ok = mbar_wait(B_(11), 0, abort_flag, p.err, 0x3300u);
+    if (ok) ok = mbar_wait<true>(B_(11), 0, abort_flag, p.err, 0x3300u);
     if (ok) {
       tcgen05_fence_after();
       uint32_t r[32];                            // this half's 32 of the 64 output columns
@@ -410,7 +426,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       tma_load_2d(base + KV_V, &tm, B_(0), 2 * p.D + h * FA_HD, row0 + k0);
       for (int it = 0; it < ni; ++it) {
         const int s = it & 1;
-        if (!mbar_wait(B_(3 + s), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4100u + s)) break;
+        if (!mbar_wait<true>(B_(3 + s), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4100u + s)) break;
         mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
         const int qrow = row0 + (kt + it) * FA_T;
         tma_load_2d(base + KV_Q + s * FA_TILE_BYTES, &tm, B_(1 + s), h * FA_HD, qrow);
@@ -421,12 +437,12 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);    // [q x hd] . [key x hd]^T
       const uint32_t idesc_g = make_idesc(0, 1, 1, FA_HD);   // [q x key]^T . [q x hd]
-      bool ok = mbar_wait(B_(0), 0, abort_flag, p.err, 0x4200u);
+      bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x4200u);
       const uint32_t sk = base + KV_K, sv = base + KV_V;
       auto issue_sdp = [&](int n) -> bool {   // S = Q_n K^T and dP = dO_n V^T
         const int s = n & 1;
-        if (!(mbar_wait(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x4300u + s) &&
-              mbar_wait(B_(6), (n & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
+        if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x4300u + s) &&
+              mbar_wait<true>(B_(6), (n & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
           return false;
         tcgen05_fence_after();
         const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
@@ -451,7 +467,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           if (!ok) break;
         }
         const int pb = it & 1;     // P / dS buffer of this iteration
-        ok = mbar_wait(B_(7 + 3 * pb), (it >> 1) & 1, abort_flag, p.err, 0x4500u);
+        ok = mbar_wait<true>(B_(7 + 3 * pb), (it >> 1) & 1, abort_flag, p.err, 0x4500u);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
@@ -474,16 +490,29 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
     const int r = (warp & 3) * 32 + lane;
     const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
     bool ok = true;
+    // row statistics of query tile kt + it; the next tile's are fetched one iteration ahead
+    const float* lse_h = p.lse2 + (size_t)(b * p.H + h) * p.T;
+    const float* delta_h = p.delta + (size_t)(b * p.H + h) * p.T;
+    auto row_stat = [&](int qi, float& lse, float& dl, int& st) {
+      const bool q_ok = qi < p.T;
+      const int i = q_ok ? qi : 0;
+      lse = lse_h[i];
+      dl = delta_h[i];
+      st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
+    };
+    float lse_n, dl_n;
+    int st_n;
+    row_stat(kt * FA_T + r, lse_n, dl_n, st_n);
     for (int it = 0; it < ni && ok; ++it) {
       const int qt = kt + it;
       const int qi = qt * FA_T + r;
       const bool q_ok = qi < p.T;
-      const size_t sidx = (size_t)(b * p.H + h) * p.T + (q_ok ? qi : 0);
       // a row past the end of the sequence gets lse = +inf, hence P = 0 and dS = 0
-      const float nlse = q_ok ? -p.lse2[sidx] : -INFINITY, dsc = -p.delta[sidx] * p.scale;
-      const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
+      const float nlse = q_ok ? -lse_n : -INFINITY, dsc = -dl_n * p.scale;
+      const int st = st_n;
+      if (it + 1 < ni) row_stat(qi + FA_T, lse_n, dl_n, st_n);
       const bool need_mask = (qt == kt) || (p.seg != nullptr);
-      ok = mbar_wait(B_(5), it & 1, abort_flag, p.err, 0x4600u);
+      ok = mbar_wait<true>(B_(5), it & 1, abort_flag, p.err, 0x4600u);
       if (!ok) break;
       tcgen05_fence_after();
       uint32_t rs[64], rdp[64];
@@ -496,7 +525,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(6));          // S / dP may be overwritten
       const int pb = it & 1;
-      ok = mbar_wait(B_(8 + 3 * pb), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // buffer free
+      ok = mbar_wait<true>(B_(8 + 3 * pb), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // buffer free
       if (!ok) break;
       uint8_t* sp = gbase + KV_P + pb * KV_PDS_STRIDE;
       uint8_t* sds = gbase + KV_DS + pb * KV_PDS_STRIDE;
@@ -513,7 +542,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
     }
-    if (ok) ok = mbar_wait(B_(9), 0, abort_flag, p.err, 0x4800u);
+    if (ok) ok = mbar_wait<true>(B_(9), 0, abort_flag, p.err, 0x4800u);
     if (ok) {
       tcgen05_fence_after();
       const int key = k0 + r;     // accumulator rows are keys here
@@ -598,7 +627,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       tma_load_2d(base + DQ_DO, &tmdo, B_(0), h * FA_HD, row0 + q0);
       for (int j = 0; j < nj; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(B_(3 + s), ((j >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5100u + s)) break;
+        if (!mbar_wait<true>(B_(3 + s), ((j >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5100u + s)) break;
         mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
         tma_load_2d(base + DQ_K + s * FA_TILE_BYTES, &tm, B_(1 + s), p.D + h * FA_HD, row0 + j * FA_T);
         tma_load_2d(base + DQ_V + s * FA_TILE_BYTES, &tm, B_(1 + s), 2 * p.D + h * FA_HD,
@@ -609,12 +638,12 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
       const uint32_t idesc_q = make_idesc(0, 0, 1, FA_HD);   // dS (K-major) . K (MN-major), N = 64
-      bool ok = mbar_wait(B_(0), 0, abort_flag, p.err, 0x5200u);
+      bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x5200u);
       const uint32_t sq = base + DQ_Q, sdo = base + DQ_DO;
       auto issue_sdp = [&](int n) -> bool {   // S = Q K_n^T and dP = dO V_n^T
         const int s = n & 1;
-        if (!(mbar_wait(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x5300u + s) &&
-              mbar_wait(B_(6), (n & 1) ^ 1u, abort_flag, p.err, 0x5400u)))
+        if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x5300u + s) &&
+              mbar_wait<true>(B_(6), (n & 1) ^ 1u, abort_flag, p.err, 0x5400u)))
           return false;
         tcgen05_fence_after();
         const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES, sv = base + DQ_V + s * FA_TILE_BYTES;
@@ -637,7 +666,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
           if (!ok) break;
         }
         const int pb = j & 1;
-        ok = mbar_wait(B_(7 + 3 * pb), (j >> 1) & 1, abort_flag, p.err, 0x5500u);
+        ok = mbar_wait<true>(B_(7 + 3 * pb), (j >> 1) & 1, abort_flag, p.err, 0x5500u);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES;
@@ -663,7 +692,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
     bool ok = true;
     for (int j = 0; j < nj && ok; ++j) {
       const bool need_mask = (j == qt) || (p.seg != nullptr);
-      ok = mbar_wait(B_(5), j & 1, abort_flag, p.err, 0x5600u);
+      ok = mbar_wait<true>(B_(5), j & 1, abort_flag, p.err, 0x5600u);
       if (!ok) break;
       tcgen05_fence_after();
       uint32_t rs[64], rdp[64];
@@ -676,7 +705,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(6));
       const int pb = j & 1;
-      ok = mbar_wait(B_(8 + 3 * pb), ((j >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
+      ok = mbar_wait<true>(B_(8 + 3 * pb), ((j >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
       if (!ok) break;
       uint8_t* sds = gbase + DQ_DS + pb * DQ_DS_STRIDE;
       if (need_mask) {
@@ -692,7 +721,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
     }
-    if (ok) ok = mbar_wait(B_(9), 0, abort_flag, p.err, 0x5800u);
+    if (ok) ok = mbar_wait<true>(B_(9), 0, abort_flag, p.err, 0x5800u);
     if (ok) {
       tcgen05_fence_after();
       uint32_t rr[32];                             // this half's 32 of the 64 dQ columns

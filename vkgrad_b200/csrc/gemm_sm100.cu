@@ -31,12 +31,12 @@ constexpr int BK = 64;             // K elements per stage = 128 bytes of f16 = 
 constexpr int UMMA_K = 16;         // K per tcgen05.mma.kind::f16
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int MAX_STAGES = 8;
-constexpr int EPI_WARPS = 8;       // two per TMEM lane quarter, each takes every other 32-column chunk
+constexpr int EPI_WARPS = 16;      // four per TMEM lane quarter, each takes every fourth 16-column chunk
 constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int TMEM_COLS = 512;     // whole TMEM: two 256-column accumulators
 constexpr int ACC_COLS = 256;
 constexpr int RING_BYTES = 196608; // shared-memory ring budget
-constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;  // one 32x32 fp32 chunk per epilogue warp (XOR-swizzled)
+constexpr int EPI_STAGE_BYTES = 32 * 16 * 4;  // one 32x16 fp32 chunk per epilogue warp (XOR-swizzled)
 constexpr int SMEM_BYTES = RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024 /*align slack*/ +
                            256 /*barriers*/;
 constexpr int GROUP_M = 8;         // m-tiles per rasterisation band
@@ -149,9 +149,10 @@ __device__ __forceinline__ void st4(float* p, long long off, float4 v, bool vec)
   }
 }
 
-// Half of one lane's share of a 32x32 chunk through the fused epilogue: four rows,
-// four consecutive columns each.  Eight lanes cover the 32 columns (128 bytes) of one
-// row, so every global access of the warp is four whole lines.  All loads of one kind are issued before the first
+// One lane's share of a 32x16 chunk through the fused epilogue: four rows (8*i +
+// sub_row), four consecutive columns each.  In this layout four lanes cover the 16
+// columns (64 bytes) of one row, so every global access of the warp is eight
+// row-contiguous 64-byte pieces.  All loads of one kind are issued before the first
 // dependent use: C may alias the inputs as far as the compiler knows, so a
 // load-compute-store loop would serialise eight memory round trips.
 template <int MODE>
@@ -174,17 +175,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, float4 (&v)[
   }
   float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
   if (has_bias) b = ld4(p.bias, col, vec);
-  if (G) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[i].x = v[i].x * p.alpha + b.x; v[i].y = v[i].y * p.alpha + b.y;
-      v[i].z = v[i].z * p.alpha + b.z; v[i].w = v[i].w * p.alpha + b.w;
-    }
-  } else if (has_bias) {   // the specialised kernels only run with alpha == 1
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
-    }
+  for (int i = 0; i < 4; ++i) {
+    v[i].x = v[i].x * p.alpha + b.x; v[i].y = v[i].y * p.alpha + b.y;
+    v[i].z = v[i].z * p.alpha + b.z; v[i].w = v[i].w * p.alpha + b.w;
   }
   if (has_pre) {
 #pragma unroll
@@ -375,70 +369,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.err, 0x400u + acc)) break;
       tcgen05_fence_after();
-      // TMEM gives each lane one row; a 32x32 chunk is transposed through shared memory so
-      // that eight lanes cover one whole 128-byte line of a row: every global access of
-      // the warp is four full lines.  Rows are 128 B apart with the 16-byte piece index
-      // XOR-ed by row & 7: conflict-free both for the row-per-lane writes and the
-      // row-contiguous reads.
+      // TMEM gives each lane one row; the chunk is transposed through shared memory so
+      // that global loads and stores are row-contiguous (4 lanes x 16 B per row).  Rows
+      // are 64 B apart with the 16-byte chunk index XOR-ed by (row >> 1) & 3: conflict-free
+      // both for the row-per-lane writes and the row-contiguous reads.
       uint8_t* stage = reinterpret_cast<uint8_t*>(epi_stage) + (warp - 2) * EPI_STAGE_BYTES;
-      const int sub_row = lane >> 3;        // 0..3: row within a group of four
-      const int sub_chunk = lane & 7;       // which 16-byte piece (4 columns) of the row
+      const int sub_row = lane >> 2;        // 0..7: row within a group of eight
+      const int sub_chunk = lane & 3;       // which 16-byte chunk (4 columns) of the row
+      const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
       const int row_base = tc.m0 + q * 32;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
-      // per tile: the eight output rows of this lane and which of them exist
-      long long roff[8];
-      unsigned ok = 0;
-      {
-        const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
+      for (int c0 = 16 * ((warp - 2) >> 2); c0 < p.bn; c0 += 64) {
+        if (tc.n0 + c0 >= p.N) break;  // uniform across the warp
+        uint32_t r[16];
+        tmem_ld16(t_row + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int row = row_base + 4 * i + sub_row;
-          roff[i] = batch_off + (long long)row * p.ldc + tc.n0 + sub_chunk * 4;
-          ok |= (row < p.M ? 1u : 0u) << i;
-        }
-      }
-      uint8_t* st_row = stage + lane * 128;
-      const uint32_t st_x = (uint32_t)(lane & 7);
-      // row 4i + sub_row: (row & 7) = 4 (i & 1) + sub_row
-      const uint8_t* ld_even = stage + sub_row * 128 + ((sub_chunk ^ sub_row) << 4);
-      const uint8_t* ld_odd = stage + (4 + sub_row) * 128 + ((sub_chunk ^ (4 + sub_row)) << 4);
-      const int ncols = min(p.bn, p.N - tc.n0);   // columns of this tile that exist
-      auto chunk = [&](const uint32_t (&r)[32], int c0) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(st_row + (((uint32_t)j ^ st_x) << 4)) =
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
               make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
         __syncwarp();
-        if (c0 + sub_chunk * 4 < ncols) {
+        const int col = tc.n0 + c0 + sub_chunk * 4;
+        if (col < p.N) {
+          float4 v[4];
+          long long off[4];
+          unsigned ok = 0;
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            float4 v[4];
-            long long off[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int ii = 4 * h + i;   // row 4 ii + sub_row, 1024 bytes per pair of groups
-              v[i] = *reinterpret_cast<const float4*>(((ii & 1) ? ld_odd : ld_even) + (ii >> 1) * 1024);
-              off[i] = roff[ii] + c0;
-            }
-            epilogue_chunk<MODE>(p, v, off, (ok >> (4 * h)) & 15u, tc.n0 + c0 + sub_chunk * 4);
+          for (int i = 0; i < 4; ++i) {
+            const int rr = 8 * i + sub_row;
+            const int row = row_base + rr;
+            v[i] = *reinterpret_cast<const float4*>(stage + rr * 64 + ((sub_chunk ^ ((rr >> 1) & 3)) << 4));
+            off[i] = batch_off + (long long)row * p.ldc + col;
+            ok |= (row < p.M ? 1u : 0u) << i;
           }
+          epilogue_chunk<MODE>(p, v, off, ok, col);
         }
         __syncwarp();
-      };
-      // The TMEM load of the next chunk is in flight while this one goes out.
-      uint32_t ra[32], rb[32];
-      int c0 = 32 * ((warp - 2) >> 2);
-      if (c0 < ncols) tmem_ld32(t_row + c0, ra);
-      while (c0 < ncols) {
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 64 < ncols) tmem_ld32(t_row + c0 + 64, rb);
-        chunk(ra, c0);
-        c0 += 64;
-        if (c0 >= ncols) break;
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 64 < ncols) tmem_ld32(t_row + c0 + 64, ra);
-        chunk(rb, c0);
-        c0 += 64;
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -694,7 +660,7 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
              (a->dact_z ? E_DACT : 0) | (a->residual ? E_RES : 0) | (a->C2 ? E_C2 : 0) |
              (a->c_dtype == VKG_F16 ? E_F16 : a->c_dtype == VKG_BF16 ? E_BF16 : 0);
   GemmKernel fn = gemm_tcgen05_kernel<E_GENERIC>;
-  if (vec && p.alpha == 1.0f) {
+  if (vec) {
     for (int i = 0; i < kNumSpecialised; ++i)
       if (kSpecialised[i].mode == mode) fn = kSpecialised[i].fn;
   }

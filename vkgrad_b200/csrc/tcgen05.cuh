@@ -40,15 +40,30 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+// Non-blocking test of the phase: for hand-offs that sit on a kernel's critical chain,
+// where the wake-up delay of a suspended try_wait costs more than the polling does.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 // Bounded wait.  Returns false when the wait gave up or another role already
-// flagged an abort; the caller then leaves its loop.
+// flagged an abort; the caller then leaves its loop.  SPIN polls instead of suspending.
+template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* err, uint32_t where) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (SPIN ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (SPIN ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
@@ -106,11 +121,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
         "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-  tmem_ld16(taddr, r);
-  tmem_ld16(taddr + 16, r + 16);
 }
 
 __device__ __forceinline__ void tcgen05_fence_before() {
