@@ -295,14 +295,26 @@ k_col_sum_partial(const T* __restrict__ g, float* __restrict__ partial, int ncol
   }
 }
 
-// Stage 2: fixed-order sum of the partials.
-__global__ void k_col_sum_final(const float* __restrict__ partial, float* __restrict__ sums,
-                                int ncol, int nchunk, int accumulate) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= ncol) return;
+// Stage 2: fixed-order sum of the partials.  A CTA owns 32 columns; its 8 warps each
+// add every 8th chunk, then the eight slices are added in order.
+constexpr int CSF_SLICES = 8;
+__global__ void __launch_bounds__(32 * CSF_SLICES)
+k_col_sum_final(const float* __restrict__ partial, float* __restrict__ sums, int ncol, int nchunk,
+                int accumulate) {
+  __shared__ float red[CSF_SLICES][32];
+  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int k = 0; k < nchunk; ++k) s += partial[(int64_t)k * ncol + c];
-  sums[c] = accumulate ? sums[c] + s : s;
+  if (c < ncol)
+    for (int k = slice; k < nchunk; k += CSF_SLICES) s += partial[(int64_t)k * ncol + c];
+  red[slice][lane] = s;
+  __syncthreads();
+  if (slice == 0 && c < ncol) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < CSF_SLICES; ++k) t += red[k][lane];
+    sums[c] = accumulate ? sums[c] + t : t;
+  }
 }
 
 // ---- softmax + cross entropy ---------------------------------------------------------
@@ -388,7 +400,7 @@ template <int NV>
 __global__ void __launch_bounds__(CE_THREADS)
 k_softmax_ce_reg(const float* __restrict__ logits, const uint32_t* __restrict__ labels,
                  const float* __restrict__ w, __half* __restrict__ dl16, float* __restrict__ dl32,
-                 float* __restrict__ loss, int stride, int ncls, float grad_scale) {
+                 float* __restrict__ loss, int stride, int ncls, float grad_scale, int pf_rows) {
   __shared__ float s_red[CE_THREADS / 32];
   __shared__ float s_bcast;
   const int row = blockIdx.x;
@@ -414,6 +426,14 @@ k_softmax_ce_reg(const float* __restrict__ logits, const uint32_t* __restrict__ 
       if (c + 2 < ncls) m = fmaxf(m, v[i].z);
       if (c + 3 < ncls) m = fmaxf(m, v[i].w);
     }
+  }
+  // Only one CTA of this size fits an SM, so its load, reduce and store phases do not
+  // overlap: pull the row that the CTA after this one on the same SM will want into L2
+  // now, which keeps HBM streaming while this row is reduced and written.
+  if (row + pf_rows < (int)gridDim.x) {
+    const char* nx = reinterpret_cast<const char*>(logits + (size_t)(row + pf_rows) * stride);
+    for (int o = tid * 128; o < stride * 4; o += CE_THREADS * 128)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + o));
   }
   m = warp_max(m);
   if (lane == 0) s_red[warp] = m;
@@ -923,8 +943,8 @@ extern "C" int vkg_col_sum(vkg_device* dev, const float* g, float* sums, int nco
 }
 
 static int col_sum_chunks(int ncol, int nrow) {
-  int col_blocks = (ncol + 127) / 128;             // the narrower (fp32) block width
-  int want = (592 + col_blocks - 1) / col_blocks;  // ~4 CTAs per SM on 148 SMs
+  int col_blocks = (ncol + 255) / 256;               // the fp16 block width (fp32 blocks are 128)
+  int want = (1184 + col_blocks - 1) / col_blocks;   // ~8 CTAs per SM on 148 SMs
   int max_chunks = (nrow + 31) / 32;               // at least 32 rows per chunk
   if (want > max_chunks) want = max_chunks;
   if (want < 1) want = 1;
@@ -954,8 +974,8 @@ extern "C" int vkg_col_sum_det(vkg_device* dev, const void* g, int g_dtype, floa
     k_col_sum_partial<float><<<grid, CS_WARPS * 32, 0, dev->stream>>>((const float*)g, scratch, ncol,
                                                                        nrow, rpc, vec_ok);
   if (vkg_check_launch("col_sum_partial")) return 1;
-  k_col_sum_final<<<vkg_blocks(ncol, 128), 128, 0, dev->stream>>>(scratch, sums, ncol, nchunk,
-                                                                  accumulate);
+  k_col_sum_final<<<(ncol + 31) / 32, 32 * CSF_SLICES, 0, dev->stream>>>(scratch, sums, ncol, nchunk,
+                                                                         accumulate);
   return vkg_check_launch("col_sum_final");
 }
 
@@ -1025,8 +1045,8 @@ extern "C" int vkg_col_sum_static(vkg_device* dev, const void* g, int g_dtype, f
     k_col_sum_partial<float><<<grid, CS_WARPS * 32, 0, dev->stream>>>((const float*)g, scratch, ncol,
                                                                        nrow, rpc, vec_ok);
   if (vkg_check_launch("col_sum_static partial")) return 1;
-  k_col_sum_final<<<vkg_blocks(ncol, 128), 128, 0, dev->stream>>>(scratch, sums, ncol, nchunk,
-                                                                  accumulate);
+  k_col_sum_final<<<(ncol + 31) / 32, 32 * CSF_SLICES, 0, dev->stream>>>(scratch, sums, ncol, nchunk,
+                                                                         accumulate);
   return vkg_check_launch("col_sum_static final");
 }
 
@@ -1044,7 +1064,8 @@ extern "C" int vkg_softmax_ce(vkg_device* dev, const float* logits, const uint32
     const int nv = (n4 + CE_THREADS - 1) / CE_THREADS;
 #define VKG_CE(NV)                                                                              \
   k_softmax_ce_reg<NV><<<rows, CE_THREADS, 0, dev->stream>>>(logits, labels, w, (__half*)dl16, dl32, \
-                                                             loss, stride, ncls, grad_scale)
+                                                             loss, stride, ncls, grad_scale,     \
+                                                             dev->sm_count * (NV <= 8 ? 2 : 1))
     if (nv <= 8) VKG_CE(8);
     else if (nv <= 12) VKG_CE(12);
     else VKG_CE(17);
