@@ -459,7 +459,7 @@ def run_gpu_arm(args):
             "launches_per_step": core.n_kernels,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": 59.7e6, "peak_source": peak_src,
+                         "frac": achieved / peak, "traffic": 66.1e6, "peak_source": peak_src,
                          "kernel": "gemm_tcgen05_kernel (all its launches in one step)",
                          "traffic_note": "ncu dram read+write bytes of ONE launch of the "
                                          "8192x3072x768 fp32-out shape (algorithmic minimum 118 MB; "
