@@ -3,7 +3,7 @@
 all-reduce + AdamW, fp16 operands / fp32 accumulate) on N B200s, tokens per second.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload gpt2-small|gpt-24l|mlp] [--gemm-trio]
+                    [--workload gpt2-small|gpt-24l] [--gemm-trio] [--trio-table]
 
 N > 1 is launched one process per GPU by torch.distributed.run (RANK / LOCAL_RANK /
 WORLD_SIZE / MASTER_ADDR / MASTER_PORT from the environment); ranks find each other
@@ -39,7 +39,8 @@ WORKLOADS = {
     "gpt2-small": (8, 1024, 768, 12, 12, 50257),
     "gpt-24l": (4, 1024, 1024, 16, 24, 50257),
 }
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+                  "nvlink_gbs": 770.0}   # nvlink: peer copy per direction measured on this pool
 
 
 def load_peaks():
@@ -239,16 +240,16 @@ def time_attention(dev, B, T, H, hd):
     return res
 
 
-_RANDOM_BLOCK = None
+_RANDOM_BLOCKS = {}
 
 
-def fill_random16(dev, buf):
-    """Fill a device buffer with N(0,1) fp16 values: timings on zero operands would
+def fill_random16(dev, buf, scale=1.0):
+    """Fill a device buffer with N(0, scale^2) fp16 values: timings on zero operands would
     flatter a power-limited tensor core."""
-    global _RANDOM_BLOCK
-    if _RANDOM_BLOCK is None:
-        _RANDOM_BLOCK = np.random.default_rng(7).standard_normal(8 << 20).astype(np.float16)
-    blk = _RANDOM_BLOCK
+    blk = _RANDOM_BLOCKS.get(scale)
+    if blk is None:
+        blk = (np.random.default_rng(7).standard_normal(8 << 20) * scale).astype(np.float16)
+        _RANDOM_BLOCKS[scale] = blk
     for off in range(0, buf.size, blk.nbytes):
         n = min(blk.nbytes, buf.size - off)
         rc = dev.lib.vkg_upload(dev.handle, buf.dptr + off, blk.ctypes.data, n)
@@ -281,6 +282,51 @@ def time_gemm_shapes(dev, table):
         for x in (a, b, c):
             x.destroy()
     return total_f, total_t, rows
+
+
+TRIO_SHAPES = [(m, k, n) for m in (4096, 16384)
+               for (k, n) in ((768, 768), (768, 3072), (3072, 768), (1024, 4096))]
+
+
+def run_trio_table(args):
+    """--trio-table: the GEMM-trio microbench, Y = X W, dX = dY W^T, dW = X^T dY with fp32
+    outputs on M in {4096, 16384} x four (K, N); X, dY ~ N(0,1), W ~ N(0, 1/K).  One JSON line."""
+    from vkgrad_b200 import vk
+    from vkgrad_b200.kernels import gemm
+    dev = vk.Device(0)
+    peaks, peak_src = load_peaks()
+    peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    rows, tot_f, tot_t = [], 0.0, 0.0
+    for m, k, n in TRIO_SHAPES:
+        x, w, dy = dev.buffer(m * k * 2, "device"), dev.buffer(k * n * 2, "device"), \
+            dev.buffer(m * n * 2, "device")
+        out = dev.buffer(4 * max(m * n, m * k, k * n), "device")
+        fill_random16(dev, x)
+        fill_random16(dev, dy)
+        fill_random16(dev, w, scale=float(k) ** -0.5)
+        ops = [("Y", (x, w, out, m, n, k), {}),
+               ("dX", (dy, w, out, m, k, n), {"trans_b": True}),
+               ("dW", (x, dy, out, k, n, m), {"trans_a": True})]
+        for name, a, kw in ops:
+            gemm(dev, *a, repeat=max(args.warmup, 3), **kw)
+            reps = max(args.steps, 11)
+            t = min(gemm(dev, *a, repeat=reps, **kw) / reps for _ in range(3))
+            fl = 2.0 * m * n * k
+            rows.append({"op": name, "m": m, "k": k, "n": n, "us": t * 1e6, "tflops": fl / t / 1e12,
+                         "frac_of_peak": fl / t / 1e12 / peak})
+            tot_f += fl
+            tot_t += t
+        for b in (x, w, dy, out):
+            b.destroy()
+    print(json.dumps({"metric": "gemm_trio_tflops", "value": tot_f / tot_t / 1e12, "unit": "TFLOP/s",
+                      "n_gpus": 1, "higher_is_better": True, "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": "gemm-trio", "shapes": len(TRIO_SHAPES), "ops": 3,
+                                 "out_dtype": "f32"},
+                      "roofline": {"bound": "tensor", "achieved": tot_f / tot_t / 1e12, "peak": peak,
+                                   "unit": "TFLOP/s", "frac": tot_f / tot_t / 1e12 / peak,
+                                   "peak_source": peak_src},
+                      "rows": rows}), flush=True)
+    dev.destroy()
 
 
 def run_single_gemm(args):
@@ -424,6 +470,22 @@ def run_gpu_arm(args):
         chk = float(np.abs(w).sum())
         drift = comm.max_double(chk) - (-comm.max_double(-chk))
 
+    # the exchange step alone: fp32 all-reduce of the flat gradient bucket, max over ranks
+    nvlink = None
+    if comm is not None:
+        reps = 5
+        barrier()
+        t_ar = dev.run_op(lambda: comm.allreduce_sum(rep.bucket, rep.total), reps) / reps
+        t_ar = comm.max_double(t_ar)
+        bucket_bytes = rep.total * 4
+        wire = 2.0 * (world - 1) / world * bucket_bytes      # per GPU, per direction
+        nv_peak = float(peaks.get("nvlink_gbs", FALLBACK_PEAKS["nvlink_gbs"]))
+        nvlink = {"bucket_bytes": bucket_bytes, "wire_bytes_per_gpu": wire,
+                  "allreduce_ms": t_ar * 1e3, "achieved": wire / t_ar / 1e9, "peak": nv_peak,
+                  "unit": "GB/s", "frac": wire / t_ar / 1e9 / nv_peak,
+                  "peak_note": "peer-copy bandwidth per direction measured on this pool",
+                  "overlapped": False}
+
     tokens_step = R * world
     line = None
     if rank == 0:
@@ -472,6 +534,7 @@ def run_gpu_arm(args):
             "cpu_baseline": cpu,
             "loss": {"resident": loss_core, "e2e": last_loss},
             "replica_drift": drift,
+            "nvlink": nvlink,
         }
         if args.gemm_trio:
             line["gemm_shapes"] = rows
@@ -493,6 +556,8 @@ def main():
     ap.add_argument("--workload", default="gpt2-small", choices=sorted(WORKLOADS))
     ap.add_argument("--loss-scale", type=float, default=4096.0)
     ap.add_argument("--max-ctas", type=int, default=0, help="with --gemm: cap the persistent grid")
+    ap.add_argument("--trio-table", action="store_true",
+                    help="GEMM-trio microbench over M in {4096,16384} x four (K,N); one JSON line")
     ap.add_argument("--gemm-trio", action="store_true", help="add per-shape GEMM timings")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle timing")
     ap.add_argument("--profile", action="store_true",
@@ -506,6 +571,8 @@ def main():
     args = ap.parse_args()
     if args.gemm:
         run_single_gemm(args)
+    elif args.trio_table:
+        run_trio_table(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:
