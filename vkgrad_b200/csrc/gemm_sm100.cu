@@ -19,6 +19,9 @@
 // Every mbarrier wait is bounded by a clock64 budget; a wait that gives up
 // sets an error word the host reads at the next synchronisation, the CTA
 // stops issuing work, frees its TMEM and returns.
+#include <algorithm>
+#include <string>
+
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -223,39 +226,172 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, float4 (&v)[
   }
 }
 
+// Per-CTA constants shared by the three roles.
+struct CtaCtx {
+  uint32_t base, stage_bytes, full0, empty0, tfull0, tempty0, tmem_base;
+  int n_stages;
+  volatile uint32_t* abort_flag;
+  uint8_t* epi_stage;
+};
+
+// TMA producer (one lane): stream the operand k-blocks of work unit t into the ring.
+__device__ __forceinline__ bool produce_unit(const CtaCtx& cx, const GemmParams& p,
+                                             const CUtensorMap* tmA, const CUtensorMap* tmB, int t,
+                                             int& stage, uint32_t& phase) {
+  TileCoord tc = tile_coord(p, t);
+  int kb0, nkb;
+  kb_range(p, tc, kb0, nkb);
+  if (p.split_k > 1) tc.z1 = 0;   // operands are not batched along the slice index
+  for (int kb = 0; kb < nkb; ++kb) {
+    if (!mbar_wait(cx.empty0 + 8 * stage, phase ^ 1u, cx.abort_flag, p.err, 0x100u + stage)) return false;
+    const uint32_t fb = cx.full0 + 8 * stage;
+    mbar_expect_tx(fb, cx.stage_bytes);
+    const uint32_t sa = cx.base + stage * cx.stage_bytes;
+    const uint32_t sb = sa + A_STAGE_BYTES;
+    const int k0 = (kb0 + kb) * BK;
+    if (!p.a_mn) {
+      tma_load_4d(sa, tmA, fb, k0, tc.m0, tc.z0, tc.z1);
+    } else {
+      tma_load_4d(sa, tmA, fb, tc.m0, k0, tc.z0, tc.z1);
+      tma_load_4d(sa + 8192, tmA, fb, tc.m0 + 64, k0, tc.z0, tc.z1);
+    }
+    if (!p.b_mn) {
+      tma_load_4d(sb, tmB, fb, k0, tc.n0, tc.z0, tc.z1);
+    } else {
+      for (int g = 0; g < p.bn / 64; ++g)
+        tma_load_4d(sb + g * 8192, tmB, fb, tc.n0 + 64 * g, k0, tc.z0, tc.z1);
+    }
+    if (++stage == cx.n_stages) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+  return true;
+}
+
+// MMA issue (one lane): accumulate work unit t into one of the two TMEM accumulators.
+__device__ __forceinline__ bool mma_unit(const CtaCtx& cx, const GemmParams& p, int t, int& stage,
+                                         uint32_t& phase, int& acc, uint32_t& acc_phase) {
+  int kb0, nkb;
+  kb_range(p, tile_coord(p, t), kb0, nkb);
+  if (nkb <= 0) return true;   // skipped tile: no accumulator, no epilogue
+  if (!mbar_wait(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x200u + acc)) return false;
+  tcgen05_fence_after();
+  const uint32_t d_tmem = cx.tmem_base + (uint32_t)(acc * ACC_COLS);
+  for (int kb = 0; kb < nkb; ++kb) {
+    if (!mbar_wait(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x300u + stage)) return false;
+    tcgen05_fence_after();
+    const uint32_t sa = cx.base + stage * cx.stage_bytes;
+    const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+    for (int k = 0; k < BK / UMMA_K; ++k) {
+      // K-major: 16 elements further along the 128-byte row.  MN-major:
+      // two 8-row groups (2 x 1024 bytes) further down.
+      uint64_t ad = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                           : make_smem_desc(sa + k * 32, 16, 1024);
+      uint64_t bd = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                           : make_smem_desc(sb + k * 32, 16, 1024);
+      umma_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+    }
+    umma_commit(cx.empty0 + 8 * stage);  // frees the stage when these MMAs retire
+    if (++stage == cx.n_stages) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+  umma_commit(cx.tfull0 + 8 * acc);  // accumulator complete -> epilogue
+  acc ^= 1;
+  if (acc == 0) acc_phase ^= 1u;
+  return true;
+}
+
+// Epilogue warp: drain this warp's share of the accumulator of work unit t.
 template <int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmParams p) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
+__device__ __forceinline__ bool epilogue_unit(const CtaCtx& cx, const GemmParams& p, int t, int warp,
+                                              int lane, int& acc, uint32_t& acc_phase) {
+  const int q = warp & 3;  // TMEM lane quarter this warp may read
+  TileCoord tc = tile_coord(p, t);
+  {
+    int kb0, nkb;
+    kb_range(p, tc, kb0, nkb);
+    if (nkb <= 0) return true;
+  }
+  if (!mbar_wait(cx.tfull0 + 8 * acc, acc_phase, cx.abort_flag, p.err, 0x400u + acc)) return false;
+  tcgen05_fence_after();
+  // TMEM gives each lane one row; the chunk is transposed through shared memory so
+  // that global loads and stores are row-contiguous (4 lanes x 16 B per row).  Rows
+  // are 64 B apart with the 16-byte chunk index XOR-ed by (row >> 1) & 3: conflict-free
+  // both for the row-per-lane writes and the row-contiguous reads.
+  uint8_t* stage = cx.epi_stage + (warp - 2) * EPI_STAGE_BYTES;
+  const int sub_row = lane >> 2;        // 0..7: row within a group of eight
+  const int sub_chunk = lane & 3;       // which 16-byte chunk (4 columns) of the row
+  const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
+  const int row_base = tc.m0 + q * 32;
+  const uint32_t t_row = cx.tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+  for (int c0 = 16 * ((warp - 2) >> 2); c0 < p.bn; c0 += 64) {
+    if (tc.n0 + c0 >= p.N) break;  // uniform across the warp
+    uint32_t r[16];
+    tmem_ld16(t_row + c0, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+          make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    __syncwarp();
+    const int col = tc.n0 + c0 + sub_chunk * 4;
+    if (col < p.N) {
+      float4 v[4];
+      long long off[4];
+      unsigned ok = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rr = 8 * i + sub_row;
+        const int row = row_base + rr;
+        v[i] = *reinterpret_cast<const float4*>(stage + rr * 64 + ((sub_chunk ^ ((rr >> 1) & 3)) << 4));
+        off[i] = batch_off + (long long)row * p.ldc + col;
+        ok |= (row < p.M ? 1u : 0u) << i;
+      }
+      epilogue_chunk<MODE>(p, v, off, ok, col);
+    }
+    __syncwarp();
+  }
+  tcgen05_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(cx.tempty0 + 8 * acc);
+  acc ^= 1;
+  if (acc == 0) acc_phase ^= 1u;
+  return true;
+}
+
+// Barriers, TMEM and the role-independent constants of a CTA.
+__device__ __forceinline__ void cta_setup(CtaCtx& cx, uint8_t* smem_raw, int bn, int stages) {
   // 128B-swizzled tiles want 1024-byte alignment.
-  uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t b_stage_bytes = (uint32_t)p.bn * 128u;
-  const uint32_t stage_bytes = A_STAGE_BYTES + b_stage_bytes;
-  // Epilogue staging (one swizzled 32x32 fp32 chunk per epilogue warp), then the barrier block.
-  float* epi_stage = reinterpret_cast<float*>(gen_base + RING_BYTES);
+  cx.base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (cx.base - smem_u32(smem_raw));
+  cx.stage_bytes = A_STAGE_BYTES + (uint32_t)bn * 128u;
+  cx.n_stages = stages;
+  // Epilogue staging (one swizzled 32x16 fp32 chunk per epilogue warp), then the barrier block.
+  cx.epi_stage = gen_base + RING_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES);
-  const uint32_t bar_base = base + RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
+  const uint32_t bar_base = cx.base + RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
   // full[s] at +8s, empty[s] at +64+8s, tmem_full[a] at +128+8a, tmem_empty[a] at +144+8a
-  const uint32_t full0 = bar_base, empty0 = bar_base + 64, tfull0 = bar_base + 128,
-                 tempty0 = bar_base + 144;
+  cx.full0 = bar_base;
+  cx.empty0 = bar_base + 64;
+  cx.tfull0 = bar_base + 128;
+  cx.tempty0 = bar_base + 144;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 20);
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 21);
-
+  cx.abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 21);
   const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, 1);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(cx.full0 + 8 * s, 1);
+      mbar_init(cx.empty0 + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(tfull0 + 8 * a, 1);
-      mbar_init(tempty0 + 8 * a, EPI_WARPS);
+      mbar_init(cx.tfull0 + 8 * a, 1);
+      mbar_init(cx.tempty0 + 8 * a, EPI_WARPS);
     }
-    *abort_flag = 0u;
+    *cx.abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -269,168 +405,114 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  cx.tmem_base = *tmem_slot;
+}
 
-  const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * (p.split_k > 1 ? p.split_k : p.nb1);
-
-  if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        TileCoord tc = tile_coord(p, t);
-        int kb0, nkb;
-        kb_range(p, tc, kb0, nkb);
-        if (p.split_k > 1) tc.z1 = 0;   // operands are not batched along the slice index
-        for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag, p.err, 0x100u + stage)) {
-            ok = false;
-            break;
-          }
-          const uint32_t fb = full0 + 8 * stage;
-          mbar_expect_tx(fb, stage_bytes);
-          const uint32_t sa = base + stage * stage_bytes;
-          const uint32_t sb = sa + A_STAGE_BYTES;
-          const int k0 = (kb0 + kb) * BK;
-          if (!p.a_mn) {
-            tma_load_4d(sa, &tmA, fb, k0, tc.m0, tc.z0, tc.z1);
-          } else {
-            tma_load_4d(sa, &tmA, fb, tc.m0, k0, tc.z0, tc.z1);
-            tma_load_4d(sa + 8192, &tmA, fb, tc.m0 + 64, k0, tc.z0, tc.z1);
-          }
-          if (!p.b_mn) {
-            tma_load_4d(sb, &tmB, fb, k0, tc.n0, tc.z0, tc.z1);
-          } else {
-            for (int g = 0; g < p.bn / 64; ++g)
-              tma_load_4d(sb + g * 8192, &tmB, fb, tc.n0 + 64 * g, k0, tc.z0, tc.z1);
-          }
-          if (++stage == p.stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int kb0, nkb;
-        kb_range(p, tile_coord(p, t), kb0, nkb);
-        if (nkb <= 0) continue;   // skipped tile: no accumulator, no epilogue
-        if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag, p.err, 0x200u + acc)) break;
-        tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
-        for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.err, 0x300u + stage)) {
-            ok = false;
-            break;
-          }
-          tcgen05_fence_after();
-          const uint32_t sa = base + stage * stage_bytes;
-          const uint32_t sb = sa + A_STAGE_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // K-major: 16 elements further along the 128-byte row.  MN-major:
-            // two 8-row groups (2 x 1024 bytes) further down.
-            uint64_t ad = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024)
-                                 : make_smem_desc(sa + k * 32, 16, 1024);
-            uint64_t bd = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024)
-                                 : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
-          }
-          umma_commit(empty0 + 8 * stage);  // frees the stage when these MMAs retire
-          if (++stage == p.stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-        if (!ok) break;
-        umma_commit(tfull0 + 8 * acc);  // accumulator complete -> epilogue
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
-      }
-    }
-  } else {
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      TileCoord tc = tile_coord(p, t);
-      {
-        int kb0, nkb;
-        kb_range(p, tc, kb0, nkb);
-        if (nkb <= 0) continue;
-      }
-      if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.err, 0x400u + acc)) break;
-      tcgen05_fence_after();
-      // TMEM gives each lane one row; the chunk is transposed through shared memory so
-      // that global loads and stores are row-contiguous (4 lanes x 16 B per row).  Rows
-      // are 64 B apart with the 16-byte chunk index XOR-ed by (row >> 1) & 3: conflict-free
-      // both for the row-per-lane writes and the row-contiguous reads.
-      uint8_t* stage = reinterpret_cast<uint8_t*>(epi_stage) + (warp - 2) * EPI_STAGE_BYTES;
-      const int sub_row = lane >> 2;        // 0..7: row within a group of eight
-      const int sub_chunk = lane & 3;       // which 16-byte chunk (4 columns) of the row
-      const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
-      const int row_base = tc.m0 + q * 32;
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
-      for (int c0 = 16 * ((warp - 2) >> 2); c0 < p.bn; c0 += 64) {
-        if (tc.n0 + c0 >= p.N) break;  // uniform across the warp
-        uint32_t r[16];
-        tmem_ld16(t_row + c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
-              make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        __syncwarp();
-        const int col = tc.n0 + c0 + sub_chunk * 4;
-        if (col < p.N) {
-          float4 v[4];
-          long long off[4];
-          unsigned ok = 0;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int rr = 8 * i + sub_row;
-            const int row = row_base + rr;
-            v[i] = *reinterpret_cast<const float4*>(stage + rr * 64 + ((sub_chunk ^ ((rr >> 1) & 3)) << 4));
-            off[i] = batch_off + (long long)row * p.ldc + col;
-            ok |= (row < p.M ? 1u : 0u) << i;
-          }
-          epilogue_chunk<MODE>(p, v, off, ok, col);
-        }
-        __syncwarp();
-      }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
-    }
-  }
-
-  // Teardown: everyone meets, then the allocating warp frees TMEM.
+// Teardown: everyone meets, then the allocating warp frees TMEM.
+__device__ __forceinline__ void cta_teardown(const CtaCtx& cx) {
   __syncwarp();
   tcgen05_fence_before();
   __syncthreads();
-  if (*abort_flag) {
+  if (*cx.abort_flag) {
     // Give copies that may still be in flight time to land before the CTA's
     // shared memory is released.
     long long t0 = clock64();
     while (clock64() - t0 < 2000000ll) {
     }
   }
-  if (warp == 1) {
+  if ((threadIdx.x >> 5) == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(cx.tmem_base),
                  "r"((uint32_t)TMEM_COLS)
                  : "memory");
   }
+}
+
+// One GEMM: CTA b takes tiles b, b + gridDim.x, ...
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  CtaCtx cx;
+  cta_setup(cx, smem_raw, p.bn, p.stages);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * (p.split_k > 1 ? p.split_k : p.nb1);
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x)
+        if (!produce_unit(cx, p, &tmA, &tmB, t, stage, phase)) break;
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x)
+        if (!mma_unit(cx, p, t, stage, phase, acc, acc_phase)) break;
+    }
+  } else {
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x)
+      if (!epilogue_unit<MODE>(cx, p, t, warp, lane, acc, acc_phase)) break;
+  }
+  cta_teardown(cx);
+}
+
+// Two independent GEMMs of the same tile width in one launch.  Their work units are dealt
+// to the CTAs by a host-made table (longest units first, each to the least loaded CTA), so
+// the tail of one problem fills up with units of the other:
+//   cta_start[b] .. cta_start[b + 1] index `units`; a unit is (problem << 28) | tile.
+constexpr int UNIT_TILE_MASK = (1 << 28) - 1;
+
+template <int MODE_A, int MODE_B>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+                         const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                         const GemmParams pa, const GemmParams pb, const int* __restrict__ cta_start,
+                         const int* __restrict__ units) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  CtaCtx cx;
+  cta_setup(cx, smem_raw, pa.bn, pa.stages);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int u_begin = cta_start[blockIdx.x], u_end = cta_start[blockIdx.x + 1];
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int ui = u_begin; ui < u_end; ++ui) {
+        const int u = units[ui], t = u & UNIT_TILE_MASK;
+        const bool ok = (u >> 28) == 0 ? produce_unit(cx, pa, &tmA0, &tmB0, t, stage, phase)
+                                       : produce_unit(cx, pb, &tmA1, &tmB1, t, stage, phase);
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int ui = u_begin; ui < u_end; ++ui) {
+        const int u = units[ui], t = u & UNIT_TILE_MASK;
+        const bool ok = (u >> 28) == 0 ? mma_unit(cx, pa, t, stage, phase, acc, acc_phase)
+                                       : mma_unit(cx, pb, t, stage, phase, acc, acc_phase);
+        if (!ok) break;
+      }
+    }
+  } else {
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int ui = u_begin; ui < u_end; ++ui) {
+      const int u = units[ui], t = u & UNIT_TILE_MASK;
+      const bool ok = (u >> 28) == 0 ? epilogue_unit<MODE_A>(cx, pa, t, warp, lane, acc, acc_phase)
+                                     : epilogue_unit<MODE_B>(cx, pb, t, warp, lane, acc, acc_phase);
+      if (!ok) break;
+    }
+  }
+  cta_teardown(cx);
 }
 
 // Adds the K slices of a split GEMM in slice order and writes C (fp32, row pitch ldc).
@@ -450,11 +532,18 @@ __global__ void k_splitk_reduce(const float4* __restrict__ ws, float* __restrict
 }
 
 typedef void (*GemmKernel)(const CUtensorMap, const CUtensorMap, const GemmParams);
+typedef void (*PairKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                           const GemmParams, const GemmParams, const int*, const int*);
 struct Specialised {
   int mode;
   GemmKernel fn;
 };
+struct SpecialisedPair {
+  int mode_a, mode_b;
+  PairKernel fn;
+};
 #define VKG_SPEC(m) {(m), gemm_tcgen05_kernel<(m)>}
+#define VKG_SPEC2(ma, mb) {(ma), (mb), gemm_pair_tcgen05_kernel<(ma), (mb)>}
 // The epilogues the training step uses; anything else runs the generic kernel.
 const Specialised kSpecialised[] = {
     VKG_SPEC(0),                                   // fp32 out: dW, dX into layernorm, scores
@@ -466,6 +555,13 @@ const Specialised kSpecialised[] = {
     VKG_SPEC(E_DACT | E_F16),                      // fc2 dX: * GELU'(z), narrow
 };
 const int kNumSpecialised = sizeof(kSpecialised) / sizeof(kSpecialised[0]);
+// The (dX, dW) pairs of a Dense backward.
+const SpecialisedPair kPairs[] = {
+    VKG_SPEC2(0, 0),                               // fc1, qkv: dX fp32 into layernorm backward
+    VKG_SPEC2(E_DACT | E_F16, 0),                  // fc2: dX * GELU'(z), narrowed
+    VKG_SPEC2(E_F16, 0),                           // proj: dX narrowed for the attention backward
+};
+const int kNumPairs = sizeof(kPairs) / sizeof(kPairs[0]);
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -542,10 +638,16 @@ void plan_gemm(int M, int N, int K, int batch, int sms, bool may_split, int64_t 
   }
 }
 
-}  // namespace
+// One GEMM made ready to launch: kernel parameters, operand maps, epilogue mask.
+struct Problem {
+  GemmParams p;
+  CUtensorMap tmA, tmB;
+  int mode;
+  bool vec;
+  long long total_tiles;
+};
 
-extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
-  if (vkg_bind(dev)) return 1;
+int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem* out) {
   VKG_REQUIRE(a, "null gemm args");
   VKG_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0, "gemm: M, N, K must be positive (%d, %d, %d)",
               a->M, a->N, a->K);
@@ -570,9 +672,10 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
               "workspace, and N, ldc multiples of 4");
   int bn = 0, want_split = 1;
   plan_gemm(a->M, a->N, a->K, batch, dev->sm_count, may_split && a->split_k != 1,
-            a->workspace_bytes, a->tile_n, a->split_k > 1 ? a->split_k : 0, &bn, &want_split);
+            a->workspace_bytes, force_bn ? force_bn : a->tile_n, a->split_k > 1 ? a->split_k : 0, &bn,
+            &want_split);
 
-  GemmParams p;
+  GemmParams& p = out->p;
   memset(&p, 0, sizeof(p));
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.nb0 = nb0; p.nb1 = nb1;
@@ -621,7 +724,8 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
     if (ptrs[i] && ((uintptr_t)ptrs[i] & 15)) vec = false;
   p.vec_ok = vec ? 1 : 0;
 
-  CUtensorMap tmA, tmB;
+  CUtensorMap& tmA = out->tmA;
+  CUtensorMap& tmB = out->tmB;
   if (!a->trans_a) {
     VKG_REQUIRE(a->lda >= a->K, "gemm: lda %lld < K %d", (long long)a->lda, a->K);
     if (make_map(dev, &tmA, a->A, a->in_dtype, a->K, a->M, a->lda, nb0, a->sA0, nb1, a->sA1, BK, BM, "A"))
@@ -641,36 +745,188 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
       return 1;
   }
 
-  if (!dev->gemm_attr_set) {
-    VKG_REQUIRE((size_t)SMEM_BYTES <= dev->gemm_smem_optin,
-                "gemm needs %d bytes of shared memory, device offers %zu", SMEM_BYTES,
-                dev->gemm_smem_optin);
-    VKG_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<E_GENERIC>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    for (int i = 0; i < kNumSpecialised; ++i)
-      VKG_CUDA(cudaFuncSetAttribute(kSpecialised[i].fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_BYTES));
-    dev->gemm_attr_set = true;
-  }
-  long long total_tiles = (long long)p.tiles_m * p.tiles_n * batch * p.split_k;
-  VKG_REQUIRE(total_tiles < (1ll << 31), "gemm: too many tiles");
-  int ctas = a->max_ctas > 0 ? a->max_ctas : dev->sm_count;
-  if (ctas > total_tiles) ctas = (int)total_tiles;
-  int mode = (a->bias ? E_BIAS : 0) | (a->pre ? E_PRE : 0) | (a->act ? E_ACT : 0) |
-             (a->dact_z ? E_DACT : 0) | (a->residual ? E_RES : 0) | (a->C2 ? E_C2 : 0) |
-             (a->c_dtype == VKG_F16 ? E_F16 : a->c_dtype == VKG_BF16 ? E_BF16 : 0);
-  GemmKernel fn = gemm_tcgen05_kernel<E_GENERIC>;
-  if (vec) {
-    for (int i = 0; i < kNumSpecialised; ++i)
-      if (kSpecialised[i].mode == mode) fn = kSpecialised[i].fn;
-  }
-  fn<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(tmA, tmB, p);
-  if (vkg_check_launch("gemm_tcgen05_kernel")) return 1;
-  if (p.split_k > 1) {
-    const long long n4 = (long long)a->M * (a->N / 4);
-    k_splitk_reduce<<<vkg_blocks(n4, 256, (int64_t)dev->sm_count * 8), 256, 0, dev->stream>>>(
-        (const float4*)a->workspace, (float*)a->C, a->M, a->N / 4, a->ldc, p.split_k);
-    return vkg_check_launch("splitk_reduce");
-  }
+  out->vec = vec;
+  out->total_tiles = (long long)p.tiles_m * p.tiles_n * batch * p.split_k;
+  VKG_REQUIRE(out->total_tiles <= UNIT_TILE_MASK, "gemm: too many tiles");
+  out->mode = (a->bias ? E_BIAS : 0) | (a->pre ? E_PRE : 0) | (a->act ? E_ACT : 0) |
+              (a->dact_z ? E_DACT : 0) | (a->residual ? E_RES : 0) | (a->C2 ? E_C2 : 0) |
+              (a->c_dtype == VKG_F16 ? E_F16 : a->c_dtype == VKG_BF16 ? E_BF16 : 0);
+  if (!vec) out->mode = E_GENERIC;
   return 0;
+}
+
+int ensure_attrs(vkg_device* dev) {
+  if (dev->gemm_attr_set) return 0;
+  VKG_REQUIRE((size_t)SMEM_BYTES <= dev->gemm_smem_optin,
+              "gemm needs %d bytes of shared memory, device offers %zu", SMEM_BYTES,
+              dev->gemm_smem_optin);
+  VKG_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<E_GENERIC>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  for (int i = 0; i < kNumSpecialised; ++i)
+    VKG_CUDA(cudaFuncSetAttribute(kSpecialised[i].fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  SMEM_BYTES));
+  for (int i = 0; i < kNumPairs; ++i)
+    VKG_CUDA(cudaFuncSetAttribute(kPairs[i].fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  SMEM_BYTES));
+  dev->gemm_attr_set = true;
+  return 0;
+}
+
+GemmKernel pick_kernel(int mode) {
+  for (int i = 0; i < kNumSpecialised; ++i)
+    if (kSpecialised[i].mode == mode) return kSpecialised[i].fn;
+  return gemm_tcgen05_kernel<E_GENERIC>;
+}
+
+// The kernel compiled for this pair of epilogue masks, or null.
+PairKernel pick_pair_kernel(int mode_a, int mode_b) {
+  for (int i = 0; i < kNumPairs; ++i)
+    if (kPairs[i].mode_a == mode_a && kPairs[i].mode_b == mode_b) return kPairs[i].fn;
+  return nullptr;
+}
+
+int reduce_slices(vkg_device* dev, const vkg_gemm_args* a, const GemmParams& p) {
+  if (p.split_k <= 1) return 0;
+  const long long n4 = (long long)a->M * (a->N / 4);
+  k_splitk_reduce<<<vkg_blocks(n4, 256, (int64_t)dev->sm_count * 8), 256, 0, dev->stream>>>(
+      (const float4*)a->workspace, (float*)a->C, a->M, a->N / 4, a->ldc, p.split_k);
+  return vkg_check_launch("splitk_reduce");
+}
+
+// ---- unit tables of paired launches ---------------------------------------------------------
+//
+// Cost of a unit in k-block times: its k-blocks plus what the epilogue of one tile adds.
+struct PairPlan {
+  int* dev_table = nullptr;   // cta_start[ctas + 1] followed by units[n]
+  int ctas = 0;
+};
+typedef std::map<std::string, PairPlan> PlanMap;
+
+std::string pair_key(const Problem& x, const Problem& y, int sms) {
+  char buf[256];
+  snprintf(buf, sizeof(buf), "%d,%d,%d,%d,%d,%d|%d,%d,%d,%d,%d,%d|%d", x.p.M, x.p.N, x.p.K, x.p.bn,
+           x.p.split_k, x.mode, y.p.M, y.p.N, y.p.K, y.p.bn, y.p.split_k, y.mode, sms);
+  return buf;
+}
+
+double unit_cost(const Problem& q, int t) {
+  int kb0, nkb;
+  GemmParams p = q.p;
+  // same arithmetic as the device: slice length when K is split, all k-blocks otherwise
+  if (p.split_k > 1) {
+    const int per_batch = p.tiles_m * p.tiles_n;
+    const int z1 = (t / per_batch) / p.nb0;
+    kb0 = z1 * p.kb_per_split;
+    nkb = std::min(p.kb_per_split, p.num_kb - kb0);
+  } else {
+    nkb = p.num_kb;
+  }
+  const bool wide = (q.mode & (E_F16 | E_BF16)) == 0;
+  const double epi = (wide ? 4.0 : 2.5) + ((q.mode & (E_DACT | E_RES | E_PRE)) ? 2.5 : 0.0);
+  return nkb + epi;
+}
+
+int make_pair_plan(vkg_device* dev, const Problem& x, const Problem& y, PairPlan* plan) {
+  const int ctas = dev->sm_count;
+  struct Unit { double cost; int id; };
+  std::vector<Unit> units;
+  for (int t = 0; t < (int)x.total_tiles; ++t) units.push_back({unit_cost(x, t), t});
+  for (int t = 0; t < (int)y.total_tiles; ++t) units.push_back({unit_cost(y, t), (1 << 28) | t});
+  std::stable_sort(units.begin(), units.end(), [](const Unit& a, const Unit& b) { return a.cost > b.cost; });
+  std::vector<std::vector<int>> per(ctas);
+  std::vector<double> load(ctas, 0.0);
+  for (const Unit& u : units) {
+    int best = 0;
+    for (int c = 1; c < ctas; ++c)
+      if (load[c] < load[best]) best = c;
+    per[best].push_back(u.id);
+    load[best] += u.cost;
+  }
+  std::vector<int> table(ctas + 1, 0);
+  for (int c = 0; c < ctas; ++c) table[c + 1] = table[c] + (int)per[c].size();
+  for (int c = 0; c < ctas; ++c) {
+    // tiles of one problem in index order within a CTA: neighbours share operand rows in L2
+    std::sort(per[c].begin(), per[c].end());
+    table.insert(table.end(), per[c].begin(), per[c].end());
+  }
+  // unit indices in the table are relative to the start of the unit array
+  VKG_CUDA(cudaMalloc(&plan->dev_table, table.size() * sizeof(int)));
+  VKG_CUDA(cudaMemcpy(plan->dev_table, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice));
+  plan->ctas = ctas;
+  return 0;
+}
+
+int pair_setup(vkg_device* dev, const vkg_gemm_args* a, const vkg_gemm_args* b, Problem* x, Problem* y,
+               PairPlan** plan, bool may_create) {
+  VKG_REQUIRE(a && b, "gemm_pair: null gemm args");
+  const int nba = (a->nb0 > 0 ? a->nb0 : 1) * (a->nb1 > 0 ? a->nb1 : 1);
+  const int nbb = (b->nb0 > 0 ? b->nb0 : 1) * (b->nb1 > 0 ? b->nb1 : 1);
+  VKG_REQUIRE(nba == 1 && nbb == 1 && a->causal == 0 && b->causal == 0,
+              "gemm_pair: both GEMMs must be unbatched and not causal");
+  VKG_REQUIRE(a->in_dtype == b->in_dtype, "gemm_pair: operand types differ");
+  if (build_problem(dev, a, 256, x) || build_problem(dev, b, 256, y)) return 1;
+  VKG_REQUIRE(x->p.bn == y->p.bn, "gemm_pair: tile widths differ (%d, %d)", x->p.bn, y->p.bn);
+  if (!dev->gemm_plans) dev->gemm_plans = new PlanMap();
+  PlanMap& plans = *static_cast<PlanMap*>(dev->gemm_plans);
+  const std::string key = pair_key(*x, *y, dev->sm_count);
+  auto it = plans.find(key);
+  if (it == plans.end()) {
+    VKG_REQUIRE(may_create && !dev->capturing,
+                "gemm_pair: no unit table for this pair of shapes; call vkg_gemm_pair_prepare "
+                "before the stream capture begins");
+    PairPlan plan;
+    if (make_pair_plan(dev, *x, *y, &plan)) return 1;
+    it = plans.emplace(key, plan).first;
+  }
+  *plan = &it->second;
+  return 0;
+}
+
+}  // namespace
+
+void vkg_gemm_release_plans(vkg_device* dev) {
+  if (!dev || !dev->gemm_plans) return;
+  PlanMap* plans = static_cast<PlanMap*>(dev->gemm_plans);
+  for (auto& kv : *plans) cudaFree(kv.second.dev_table);
+  delete plans;
+  dev->gemm_plans = nullptr;
+}
+
+extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
+  if (vkg_bind(dev)) return 1;
+  Problem q;
+  if (build_problem(dev, a, 0, &q)) return 1;
+  if (ensure_attrs(dev)) return 1;
+  int ctas = a->max_ctas > 0 ? a->max_ctas : dev->sm_count;
+  if (ctas > q.total_tiles) ctas = (int)q.total_tiles;
+  pick_kernel(q.mode)<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(q.tmA, q.tmB, q.p);
+  if (vkg_check_launch("gemm_tcgen05_kernel")) return 1;
+  return reduce_slices(dev, a, q.p);
+}
+
+extern "C" int vkg_gemm_pair_prepare(vkg_device* dev, const vkg_gemm_args* a, const vkg_gemm_args* b) {
+  if (vkg_bind(dev)) return 1;
+  Problem x, y;
+  PairPlan* plan = nullptr;
+  return pair_setup(dev, a, b, &x, &y, &plan, true);
+}
+
+extern "C" int vkg_gemm_pair(vkg_device* dev, const vkg_gemm_args* a, const vkg_gemm_args* b) {
+  if (vkg_bind(dev)) return 1;
+  Problem x, y;
+  PairPlan* plan = nullptr;
+  if (pair_setup(dev, a, b, &x, &y, &plan, true)) return 1;
+  if (ensure_attrs(dev)) return 1;
+  PairKernel fn = pick_pair_kernel(x.mode, y.mode);
+  if (!fn) {
+    // no kernel for this pair of epilogues: two launches, same results
+    if (vkg_gemm(dev, a)) return 1;
+    return vkg_gemm(dev, b);
+  }
+  fn<<<plan->ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(x.tmA, x.tmB, y.tmA, y.tmB, x.p, y.p,
+                                                          plan->dev_table,
+                                                          plan->dev_table + plan->ctas + 1);
+  if (vkg_check_launch("gemm_tcgen05_kernel (pair)")) return 1;
+  if (reduce_slices(dev, a, x.p)) return 1;
+  return reduce_slices(dev, b, y.p);
 }

@@ -48,17 +48,13 @@ def _ptr(buf):
     return buf.dptr
 
 
-def gemm(dev, a, b, c, m, n, k, trans_a=False, trans_b=False, graph=None, repeat=1,
-         nb0=1, nb1=1, lda=None, ldb=None, ldc=None, sa=(0, 0), sb=(0, 0), sc=(0, 0),
-         a_off=0, b_off=0, c_off=0, in_dtype=F16, c_dtype=F32, bias=None, act=ACT_NONE,
-         pre=None, dact_z=None, dact=ACT_NONE, residual=None, c2=None, tile_n=0,
-         max_ctas=0, alpha=1.0, split_k=0, causal=0, name="gemm"):
-    """C = op(A) op(B) with the fused epilogue of vkg_gemm (include/vkgrad_b200.h).
-
-    Offsets (a_off, b_off, c_off) are in elements and apply to C, c2, pre,
-    dact_z and residual alike, so a head's slice of a wider matrix can be
-    addressed in place.  Returns GPU seconds when run eagerly, 0.0 when recorded.
-    """
+def _gemm_args(dev, a, b, c, m, n, k, trans_a=False, trans_b=False,
+               nb0=1, nb1=1, lda=None, ldb=None, ldc=None, sa=(0, 0), sb=(0, 0), sc=(0, 0),
+               a_off=0, b_off=0, c_off=0, in_dtype=F16, c_dtype=F32, bias=None, act=ACT_NONE,
+               pre=None, dact_z=None, dact=ACT_NONE, residual=None, c2=None, tile_n=0,
+               max_ctas=0, alpha=1.0, split_k=0, causal=0):
+    """Fill a vkg_gemm_args (include/vkgrad_b200.h).  Offsets are in elements and apply to
+    C, c2, pre, dact_z and residual alike."""
     args = GemmArgs()
     args.trans_a, args.trans_b = int(bool(trans_a)), int(bool(trans_b))
     args.M, args.N, args.K = int(m), int(n), int(k)
@@ -94,15 +90,55 @@ def gemm(dev, a, b, c, m, n, k, trans_a=False, trans_b=False, graph=None, repeat
         ws = dev.scratch((int(split_k) if split_k > 1 else 8) * m * n * 4)
         args.workspace = ws.dptr
         args.workspace_bytes = ws.size
+    return args
+
+
+def gemm(dev, a, b, c, m, n, k, trans_a=False, trans_b=False, graph=None, repeat=1, name="gemm",
+         **kw):
+    """C = op(A) op(B) with the fused epilogue of vkg_gemm (include/vkgrad_b200.h).
+
+    Keyword arguments as in _gemm_args: a head's slice of a wider matrix can be
+    addressed in place through the element offsets.  Returns GPU seconds when run
+    eagerly, 0.0 when recorded.
+    """
+    args = _gemm_args(dev, a, b, c, m, n, k, trans_a=trans_a, trans_b=trans_b, **kw)
     lib, h = dev.lib, dev.handle
 
     def go():
         _check(lib.vkg_gemm(h, C.byref(args)), f"{name} {m}x{n}x{k}")
 
     if graph is not None:
-        nb = nb0 * nb1
+        nb = args.nb0 * args.nb1
+        esz_c = 4 if args.c_dtype == F32 else 2
         graph.add(go, name, nb * (2 * m * k + 2 * k * n + esz_c * m * n))
         graph.mm_split.append((nb * 2 * (m * k + k * n), nb * m * n * esz_c))
+        return 0.0
+    return dev.run_op(go, repeat)
+
+
+def gemm_pair(dev, first, second, graph=None, repeat=1, name="gemm_pair"):
+    """Two independent GEMMs in one launch (vkg_gemm_pair): `first` and `second` are
+    (a, b, c, m, n, k, kwargs) tuples as for gemm().  Used for the dX and dW of a Linear
+    backward (autograd.py:217-227), which share dY and do not depend on each other."""
+    xa = _gemm_args(dev, *first[:6], **first[6])
+    ya = _gemm_args(dev, *second[:6], **second[6])
+    if xa.workspace and ya.workspace:
+        # the two problems run at the same time and would share the device's scratch
+        raise VkError(f"{name}: only one of the two GEMMs may split K (pass split_k=1 to the other)")
+    lib, h = dev.lib, dev.handle
+    _check(lib.vkg_gemm_pair_prepare(h, C.byref(xa), C.byref(ya)), f"{name} prepare")
+
+    def go():
+        _check(lib.vkg_gemm_pair(h, C.byref(xa), C.byref(ya)), name)
+
+    if graph is not None:
+        total = 0
+        for args in (xa, ya):
+            m, n, k = args.M, args.N, args.K
+            esz_c = 4 if args.c_dtype == F32 else 2
+            total += 2 * m * k + 2 * k * n + esz_c * m * n
+            graph.mm_split.append((2 * (m * k + k * n), m * n * esz_c))
+        graph.add(go, name, total)
         return 0.0
     return dev.run_op(go, repeat)
 
