@@ -345,7 +345,7 @@ def run_single_gemm(args):
     fill_random16(dev, b)
     kw = dict(trans_a=bool(ta), trans_b=bool(tb), nb0=nb, sa=(m * k, 0), sb=(k * n, 0),
               sc=(m * n, 0), c_dtype=F16 if c16 else F32, tile_n=args.tile_n, split_k=args.split_k,
-              max_ctas=args.max_ctas)
+              max_ctas=args.max_ctas, cta_pair=args.cta_pair)
     gemm(dev, a, b, c, m, n, k, repeat=max(args.warmup, 1), **kw)
     t = gemm(dev, a, b, c, m, n, k, repeat=args.steps, **kw) / args.steps
     print(json.dumps({"gemm": args.gemm, "us": t * 1e6,
@@ -555,6 +555,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gpt2-small", choices=sorted(WORKLOADS))
     ap.add_argument("--loss-scale", type=float, default=4096.0)
+    ap.add_argument("--cta-pair", type=int, default=0,
+                    help="with --gemm: 1 = 256x256 tiles on CTA pairs, -1 = never, 0 = library's choice")
     ap.add_argument("--max-ctas", type=int, default=0, help="with --gemm: cap the persistent grid")
     ap.add_argument("--trio-table", action="store_true",
                     help="GEMM-trio microbench over M in {4096,16384} x four (K,N); one JSON line")

@@ -151,6 +151,10 @@ typedef struct vkg_gemm_args {
                                    tile's last row are skipped (P V, dS K);
                                 3: A stored K x M is lower-triangular in (k, m) -- k-blocks
                                    before the tile's first row are skipped (P^T dO, dS^T Q). */
+  int32_t cta_pair;          /* 256 x 256 tiles computed by two CTAs of a cluster with one
+                                tcgen05.mma.cta_group::2 (each CTA loads half of the B tile):
+                                0 = the library decides, 1 = always (when the shape allows it),
+                                -1 = never.  Not available with causal != 0. */
 } vkg_gemm_args;
 
 int vkg_gemm(vkg_device* dev, const vkg_gemm_args* args);

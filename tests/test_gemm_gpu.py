@@ -315,3 +315,68 @@ def test_paired_backward_equals_two_launches(dev, rows, fin, fout, mode):
     assert relerr(dw1, orc.matmul16(x, dy, True, False)) < TOL
     for b in (bx, bw, bdy, bz):
         b.destroy()
+
+
+@pytest.mark.parametrize("m,n,k,ta,tb,split_k", [
+    (512, 512, 256, False, False, 1),      # Y = X W, B stored K x N
+    (512, 768, 320, False, True, 1),       # dX = dY W^T, B stored N x K
+    (768, 512, 1024, True, False, 1),      # dW = X^T dY, A stored K x M
+    (1000, 520, 200, False, False, 1),     # ragged M, N, K
+    (136, 264, 72, False, True, 1),        # a second row block of 8 rows, one tile column and a bit
+    (768, 768, 4096, True, False, 4),      # dW with K split over four slices
+    (4096, 3072, 768, False, False, 1),    # more tiles than CTA pairs
+])
+def test_cta_pair_tiles(dev, m, n, k, ta, tb, split_k):
+    """256 x 256 tiles on 2-CTA clusters (tcgen05.mma.cta_group::2) against the oracle and,
+    bit for bit, against the single-CTA kernel: both accumulate K in the same order."""
+    from vkgrad_b200.kernels import gemm
+    rng = np.random.default_rng(m * 7 + n)
+    a = rng.standard_normal((k, m) if ta else (m, k)).astype(np.float16)
+    b = rng.standard_normal((n, k) if tb else (k, n)).astype(np.float16)
+    ba, bb = up(dev, a), up(dev, b)
+    outs = []
+    for pair in (-1, 1):
+        bc = dev.buffer(m * n * 4, "cached")
+        bc.array(np.float32)[:] = np.nan
+        bc.flush()
+        gemm(dev, ba, bb, bc, m, n, k, trans_a=ta, trans_b=tb, split_k=split_k, cta_pair=pair)
+        outs.append(down(dev, bc, np.float32, (m, n)))
+        bc.destroy()
+    ref = orc.matmul16(a, b, ta, tb)
+    assert relerr(outs[1], ref) < TOL
+    if split_k == 1:
+        assert np.array_equal(outs[0], outs[1])
+    for x in (ba, bb):
+        x.destroy()
+
+
+def test_cta_pair_fused_epilogues(dev):
+    """The training step's epilogues on CTA-pair tiles: bias + keep z + GELU + fp16, and
+    GELU'(z) scaling with fp16 output, against the single-CTA kernel."""
+    from vkgrad_b200._lib import ACT_GELU, F16
+    from vkgrad_b200.kernels import gemm
+    m, n, k = 640, 512, 192
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    w = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float16)
+    bias = rng.standard_normal(n).astype(np.float32)
+    z_in = rng.standard_normal((m, n)).astype(np.float32)
+    bx, bw, bb, bz = up(dev, x), up(dev, w), up(dev, bias), up(dev, z_in)
+    res = []
+    for pair in (-1, 1):
+        y16 = dev.buffer(m * n * 2, "cached")
+        z32 = dev.buffer(m * n * 4, "cached")
+        d16 = dev.buffer(m * n * 2, "cached")
+        gemm(dev, bx, bw, y16, m, n, k, c_dtype=F16, bias=bb, act=ACT_GELU, pre=z32, cta_pair=pair)
+        gemm(dev, bx, bw, d16, m, n, k, c_dtype=F16, dact_z=bz, dact=ACT_GELU, cta_pair=pair)
+        res.append((down(dev, y16, np.float16, (m, n)), down(dev, z32, np.float32, (m, n)),
+                    down(dev, d16, np.float16, (m, n))))
+        for b in (y16, z32, d16):
+            b.destroy()
+    for got, want in zip(res[1], res[0]):
+        assert np.array_equal(got, want)
+    zref = orc.matmul16(x, w) + bias
+    assert relerr(res[1][1], zref) < TOL
+    assert relerr(res[1][0].astype(np.float32), orc.gelu(zref)) < 5e-3
+    for b in (bx, bw, bb, bz):
+        b.destroy()

@@ -44,6 +44,7 @@ class GemmArgs(C.Structure):
         ("workspace", vp),
         ("workspace_bytes", i64),
         ("causal", C.c_int32),
+        ("cta_pair", C.c_int32),
     ]
 
 

@@ -69,7 +69,8 @@ struct TileCoord {
   int z0, z1, m0, n0;
 };
 
-__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int t) {
+// bm: rows of C per tile (BM, or 2 * BM for a CTA pair); m_off: this CTA's rows inside it.
+__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int t, int bm = BM, int m_off = 0) {
   int per_batch = p.tiles_m * p.tiles_n;
   int z = t / per_batch;
   int r = t - z * per_batch;
@@ -79,7 +80,7 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int t) {
   int gsize = min(p.tiles_m - first_m, GROUP_M);
   int in_band = r - g * band;
   TileCoord c;
-  c.m0 = (first_m + in_band % gsize) * BM;
+  c.m0 = (first_m + in_band % gsize) * bm + m_off;
   c.n0 = (in_band / gsize) * p.bn;
   c.z0 = z % p.nb0;
   c.z1 = z / p.nb0;
@@ -462,6 +463,229 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   cta_teardown(cx);
 }
 
+// ---- CTA pairs -----------------------------------------------------------------------------
+//
+// 256 x 256 tiles on a 2-CTA cluster: each CTA loads its 128 rows of A and its 128 of the
+// tile's 256 columns of B, the even-ranked CTA issues tcgen05.mma.cta_group::2 for both, and
+// each CTA's TMEM receives the accumulators of its own 128 rows.  Per k-block a CTA pulls
+// 32 KB through L2 instead of 48 KB for the same 128 x 256 outputs, which is what bounds the
+// single-CTA kernel on the K = 768 shapes.  Barriers: TMA of both CTAs counts bytes on the
+// leader's full[s]; the leader's commits arrive on empty[s] / tmem_full[a] of both CTAs;
+// the epilogue warps of both CTAs arrive on the leader's tmem_empty[a].
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_B_STAGE_BYTES = (PAIR_BN / 2) * 128;
+constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;
+constexpr int PAIR_STAGES = RING_BYTES / PAIR_STAGE_BYTES;   // 6
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  CtaCtx cx;
+  cx.base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (cx.base - smem_u32(smem_raw));
+  cx.stage_bytes = PAIR_STAGE_BYTES;
+  cx.n_stages = PAIR_STAGES;
+  cx.epi_stage = gen_base + RING_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES);
+  const uint32_t bar_base = cx.base + RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
+  cx.full0 = bar_base;
+  cx.empty0 = bar_base + 64;
+  cx.tfull0 = bar_base + 128;
+  cx.tempty0 = bar_base + 144;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 20);
+  cx.abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 21);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(cx.full0 + 8 * s, 1);     // the leader's own arrive.expect_tx
+      mbar_init(cx.empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(cx.tfull0 + 8 * a, 1);
+      mbar_init(cx.tempty0 + 8 * a, 2 * EPI_WARPS);   // the epilogue warps of both CTAs
+    }
+    *cx.abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    // each CTA takes the whole of its own TMEM, so accumulator addresses agree in the pair
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32((const void*)tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();        // the peer's barriers exist before anything is signalled on them
+  tcgen05_fence_after();
+  cx.tmem_base = *tmem_slot;
+
+  const int n_pairs = (int)gridDim.x >> 1, pair = (int)blockIdx.x >> 1;
+  const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * (p.split_k > 1 ? p.split_k : p.nb1);
+  const int m_off = (int)rank * BM;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+        TileCoord tc = tile_coord(p, t, 2 * BM, m_off);
+        int kb0, nkb;
+        kb_range(p, tc, kb0, nkb);
+        if (p.split_k > 1) tc.z1 = 0;
+        const int nb = tc.n0 + (int)rank * (PAIR_BN / 2);    // this CTA's columns of B
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(cx.empty0 + 8 * stage, phase ^ 1u, cx.abort_flag, p.err, 0x500u + stage)) {
+            ok = false;
+            break;
+          }
+          if (rank == 0) mbar_expect_tx(cx.full0 + 8 * stage, 2 * PAIR_STAGE_BYTES);
+          const uint32_t fb = mapa_shared(cx.full0 + 8 * stage, 0);
+          const uint32_t sa = cx.base + stage * PAIR_STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          const int k0 = (kb0 + kb) * BK;
+          if (!p.a_mn) {
+            tma_load_4d_pair(sa, &tmA, fb, k0, tc.m0, tc.z0, tc.z1);
+          } else {
+            tma_load_4d_pair(sa, &tmA, fb, tc.m0, k0, tc.z0, tc.z1);
+            tma_load_4d_pair(sa + 8192, &tmA, fb, tc.m0 + 64, k0, tc.z0, tc.z1);
+          }
+          if (!p.b_mn) {
+            tma_load_4d_pair(sb, &tmB, fb, k0, nb, tc.z0, tc.z1);
+          } else {
+            tma_load_4d_pair(sb, &tmB, fb, nb, k0, tc.z0, tc.z1);
+            tma_load_4d_pair(sb + 8192, &tmB, fb, nb + 64, k0, tc.z0, tc.z1);
+          }
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+        int kb0, nkb;
+        kb_range(p, tile_coord(p, t, 2 * BM, 0), kb0, nkb);
+        if (nkb <= 0) continue;
+        if (!mbar_wait(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x600u + acc)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = cx.tmem_base + (uint32_t)(acc * ACC_COLS);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x700u + stage)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sa = cx.base + stage * PAIR_STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t ad = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                                 : make_smem_desc(sa + k * 32, 16, 1024);
+            uint64_t bd = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                                 : make_smem_desc(sb + k * 32, 16, 1024);
+            umma2_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma2_commit(cx.empty0 + 8 * stage);
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma2_commit(cx.tfull0 + 8 * acc);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < total_tiles; t += n_pairs) {
+      TileCoord tc = tile_coord(p, t, 2 * BM, m_off);
+      {
+        int kb0, nkb;
+        kb_range(p, tc, kb0, nkb);
+        if (nkb <= 0) continue;
+      }
+      if (!mbar_wait(cx.tfull0 + 8 * acc, acc_phase, cx.abort_flag, p.err, 0x800u + acc)) break;
+      tcgen05_fence_after();
+      uint8_t* stage = cx.epi_stage + (warp - 2) * EPI_STAGE_BYTES;
+      const int sub_row = lane >> 2;
+      const int sub_chunk = lane & 3;
+      const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
+      const int row_base = tc.m0 + q * 32;
+      const uint32_t t_row = cx.tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+      for (int c0 = 16 * ((warp - 2) >> 2); c0 < PAIR_BN; c0 += 64) {
+        if (tc.n0 + c0 >= p.N) break;
+        uint32_t r[16];
+        tmem_ld16(t_row + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+              make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        __syncwarp();
+        const int col = tc.n0 + c0 + sub_chunk * 4;
+        if (col < p.N) {
+          float4 v[4];
+          long long off[4];
+          unsigned ok = 0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int rr = 8 * i + sub_row;
+            const int row = row_base + rr;
+            v[i] = *reinterpret_cast<const float4*>(stage + rr * 64 + ((sub_chunk ^ ((rr >> 1) & 3)) << 4));
+            off[i] = batch_off + (long long)row * p.ldc + col;
+            ok |= (row < p.M ? 1u : 0u) << i;
+          }
+          epilogue_chunk<MODE>(p, v, off, ok, col);
+        }
+        __syncwarp();
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(cx.tempty0 + 8 * acc);
+        else mbar_arrive_cluster(mapa_shared(cx.tempty0 + 8 * acc, 0));
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // Neither CTA may leave while the other can still read its shared memory or signal its
+  // barriers.
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (*cx.abort_flag) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(cx.tmem_base),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
 // Two independent GEMMs of the same tile width in one launch.  Their work units are dealt
 // to the CTAs by a host-made table (longest units first, each to the least loaded CTA), so
 // the tail of one problem fills up with units of the other:
@@ -555,6 +779,18 @@ const Specialised kSpecialised[] = {
     VKG_SPEC(E_DACT | E_F16),                      // fc2 dX: * GELU'(z), narrow
 };
 const int kNumSpecialised = sizeof(kSpecialised) / sizeof(kSpecialised[0]);
+#define VKG_SPEC_CP(m) {(m), gemm_cta_pair_kernel<(m)>}
+// The same epilogues on 256 x 256 tiles computed by CTA pairs.
+const Specialised kCtaPair[] = {
+    VKG_SPEC_CP(0),
+    VKG_SPEC_CP(E_F16),
+    VKG_SPEC_CP(E_BIAS),
+    VKG_SPEC_CP(E_BIAS | E_F16),
+    VKG_SPEC_CP(E_BIAS | E_RES),
+    VKG_SPEC_CP(E_BIAS | E_PRE | E_ACT | E_F16),
+    VKG_SPEC_CP(E_DACT | E_F16),
+};
+const int kNumCtaPair = sizeof(kCtaPair) / sizeof(kCtaPair[0]);
 // The (dX, dW) pairs of a Dense backward.
 const SpecialisedPair kPairs[] = {
     VKG_SPEC2(0, 0),                               // fc1, qkv: dX fp32 into layernorm backward
@@ -604,8 +840,9 @@ int make_map(vkg_device* dev, CUtensorMap* map, const void* ptr, int dtype, int6
 // the SMs with wide tiles (the dW shapes: few output tiles, K = rows of the batch),
 // K is split across CTAs and a second pass adds the slices.
 void plan_gemm(int M, int N, int K, int batch, int sms, bool may_split, int64_t ws_bytes,
-               int force_bn, int force_split, int* out_bn, int* out_split) {
-  const int tiles_m = (M + BM - 1) / BM;
+               int force_bn, int force_split, int* out_bn, int* out_split, int bm = BM,
+               double* out_us = nullptr) {
+  const int tiles_m = (M + bm - 1) / bm;
   const int num_kb = (K + BK - 1) / BK;
   const int n_round = ((N + 63) / 64) * 64;
   const int cand[4] = {256, 192, 128, 64};
@@ -636,6 +873,7 @@ void plan_gemm(int M, int N, int K, int batch, int sms, bool may_split, int64_t 
       }
     }
   }
+  if (out_us) *out_us = best;
 }
 
 // One GEMM made ready to launch: kernel parameters, operand maps, epilogue mask.
@@ -647,7 +885,9 @@ struct Problem {
   long long total_tiles;
 };
 
-int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem* out) {
+// use_pair: 256 x 256 tiles for gemm_cta_pair_kernel (the caller has checked the shape).
+int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem* out,
+                  bool use_pair = false) {
   VKG_REQUIRE(a, "null gemm args");
   VKG_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0, "gemm: M, N, K must be positive (%d, %d, %d)",
               a->M, a->N, a->K);
@@ -671,15 +911,17 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
               "gemm: split_k needs an unbatched GEMM with a plain fp32 output, a 16-byte aligned "
               "workspace, and N, ldc multiples of 4");
   int bn = 0, want_split = 1;
-  plan_gemm(a->M, a->N, a->K, batch, dev->sm_count, may_split && a->split_k != 1,
-            a->workspace_bytes, force_bn ? force_bn : a->tile_n, a->split_k > 1 ? a->split_k : 0, &bn,
-            &want_split);
+  const int bm = use_pair ? 2 * BM : BM;
+  plan_gemm(a->M, a->N, a->K, batch, use_pair ? dev->sm_count / 2 : dev->sm_count,
+            may_split && a->split_k != 1, a->workspace_bytes,
+            use_pair ? PAIR_BN : (force_bn ? force_bn : a->tile_n), a->split_k > 1 ? a->split_k : 0,
+            &bn, &want_split, bm);
 
   GemmParams& p = out->p;
   memset(&p, 0, sizeof(p));
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.nb0 = nb0; p.nb1 = nb1;
-  p.tiles_m = (a->M + BM - 1) / BM;
+  p.tiles_m = (a->M + bm - 1) / bm;
   p.tiles_n = (a->N + bn - 1) / bn;
   p.bn = bn;
   p.num_kb = (a->K + BK - 1) / BK;
@@ -690,7 +932,7 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
   p.b_mn = a->trans_b ? 0 : 1;
   const uint32_t fmt = a->in_dtype == VKG_BF16 ? 1u : 0u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a_mn << 15) |
-            ((uint32_t)p.b_mn << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            ((uint32_t)p.b_mn << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(bm >> 4) << 24);
   p.c_dtype = a->c_dtype; p.act = a->act; p.dact = a->dact;
   p.ldc = a->ldc; p.sC0 = a->sC0; p.sC1 = a->sC1;
   p.C = a->C; p.C2 = a->C2; p.bias = a->bias; p.pre = a->pre;
@@ -737,7 +979,8 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
   }
   if (a->trans_b) {
     VKG_REQUIRE(a->ldb >= a->K, "gemm: ldb %lld < K %d (B stored N x K)", (long long)a->ldb, a->K);
-    if (make_map(dev, &tmB, a->B, a->in_dtype, a->K, a->N, a->ldb, nb0, a->sB0, nb1, a->sB1, BK, bn, "B^T"))
+    if (make_map(dev, &tmB, a->B, a->in_dtype, a->K, a->N, a->ldb, nb0, a->sB0, nb1, a->sB1, BK,
+                 use_pair ? PAIR_BN / 2 : bn, "B^T"))
       return 1;
   } else {
     VKG_REQUIRE(a->ldb >= a->N, "gemm: ldb %lld < N %d", (long long)a->ldb, a->N);
@@ -767,6 +1010,11 @@ int ensure_attrs(vkg_device* dev) {
                                   SMEM_BYTES));
   for (int i = 0; i < kNumPairs; ++i)
     VKG_CUDA(cudaFuncSetAttribute(kPairs[i].fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  SMEM_BYTES));
+  VKG_CUDA(cudaFuncSetAttribute(gemm_cta_pair_kernel<E_GENERIC>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  for (int i = 0; i < kNumCtaPair; ++i)
+    VKG_CUDA(cudaFuncSetAttribute(kCtaPair[i].fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   SMEM_BYTES));
   dev->gemm_attr_set = true;
   return 0;
@@ -894,7 +1142,46 @@ void vkg_gemm_release_plans(vkg_device* dev) {
 
 extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(a, "null gemm args");
   Problem q;
+  // 256 x 256 tiles on CTA pairs: only where a pair has at least two full row blocks and a
+  // full-width tile to work on, and never for the causal attention shortcuts
+  const bool pair_ok = a->causal == 0 && a->M > BM && a->N >= PAIR_BN / 2 && dev->sm_count >= 2 &&
+                       (a->tile_n == 0 || a->tile_n == PAIR_BN) && a->max_ctas == 0;
+  bool use_pair = pair_ok && a->cta_pair > 0;
+  if (pair_ok && a->cta_pair == 0) {
+    // Measured on B200: CTA-pair tiles are about 10 % faster once the launch has several
+    // waves of them (or K is split for a few-tile dW), and slower when 74 pairs get one
+    // wave and a bit of 256 x 256 tiles.
+    if (build_problem(dev, a, 0, &q, true)) return 1;
+    use_pair = q.p.split_k > 1 || q.total_tiles >= 3ll * (dev->sm_count / 2);
+  }
+  if (use_pair) {
+    if (build_problem(dev, a, 0, &q, true)) return 1;
+    if (ensure_attrs(dev)) return 1;
+    GemmKernel fn = gemm_cta_pair_kernel<E_GENERIC>;
+    for (int i = 0; i < kNumCtaPair; ++i)
+      if (kCtaPair[i].mode == q.mode) fn = kCtaPair[i].fn;
+    long long pairs = dev->sm_count / 2;
+    if (pairs > q.total_tiles) pairs = q.total_tiles;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr;
+    memset(&attr, 0, sizeof(attr));
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    VKG_CUDA(cudaLaunchKernelEx(&cfg, fn, q.tmA, q.tmB, q.p));
+    if (vkg_check_launch("gemm_cta_pair_kernel")) return 1;
+    return reduce_slices(dev, a, q.p);
+  }
   if (build_problem(dev, a, 0, &q)) return 1;
   if (ensure_attrs(dev)) return 1;
   int ctas = a->max_ctas > 0 ? a->max_ctas : dev->sm_count;

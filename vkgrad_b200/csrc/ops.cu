@@ -213,6 +213,33 @@ __global__ void k_embed_bwd(const float* __restrict__ dx, const uint32_t* __rest
   }
 }
 
+// Four columns per thread (D a multiple of 4, 16-byte aligned tables): one 16-byte access
+// per operand, and one 16-byte vector atomic per table in the backward.
+__global__ void k_embed_v4(const float4* __restrict__ tok, const float4* __restrict__ pos,
+                           const uint32_t* __restrict__ ids, const uint32_t* __restrict__ seg,
+                           float4* __restrict__ x, int n4, int D4, int T) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+    const int bt = i / D4, d = i - bt * D4;
+    int t = bt % T;
+    if (seg) t -= (int)seg[bt];
+    const float4 a = tok[(int64_t)ids[bt] * D4 + d], b = pos[(int64_t)t * D4 + d];
+    x[i] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+  }
+}
+
+__global__ void k_embed_bwd_v4(const float4* __restrict__ dx, const uint32_t* __restrict__ ids,
+                               const uint32_t* __restrict__ seg, float4* __restrict__ dtok,
+                               float4* __restrict__ dpos, int n4, int D4, int T) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+    const int bt = i / D4, d = i - bt * D4;
+    int t = bt % T;
+    if (seg) t -= (int)seg[bt];
+    const float4 g = dx[i];
+    atomicAdd(dtok + (int64_t)ids[bt] * D4 + d, g);
+    atomicAdd(dpos + (int64_t)t * D4 + d, g);
+  }
+}
+
 // ---- column sums ------------------------------------------------------------------
 
 // The reference's col_sum: one thread per column over fp32 rows (kernels.py:753).
@@ -1309,6 +1336,11 @@ extern "C" int vkg_embed(vkg_device* dev, const float* tok, const float* pos, co
                          const uint32_t* seg, float* x, int64_t n, int D, int T) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(tok && pos && ids && x && n > 0, "embed: bad arguments");
+  if (D % 4 == 0 && n < (1ll << 31) && ((((uintptr_t)tok | (uintptr_t)pos | (uintptr_t)x) & 15) == 0)) {
+    k_embed_v4<<<flat_grid(dev, n / 4), TPB, 0, dev->stream>>>(
+        (const float4*)tok, (const float4*)pos, ids, seg, (float4*)x, (int)(n / 4), D / 4, T);
+    return vkg_check_launch("embed_v4");
+  }
   k_embed<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(tok, pos, ids, seg, x, n, D, T);
   return vkg_check_launch("embed");
 }
@@ -1317,6 +1349,11 @@ extern "C" int vkg_embed_bwd(vkg_device* dev, const float* dx, const uint32_t* i
                              const uint32_t* seg, float* dtok, float* dpos, int64_t n, int D, int T) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(dx && ids && dtok && dpos && n > 0, "embed_bwd: bad arguments");
+  if (D % 4 == 0 && n < (1ll << 31) && ((((uintptr_t)dx | (uintptr_t)dtok | (uintptr_t)dpos) & 15) == 0)) {
+    k_embed_bwd_v4<<<flat_grid(dev, n / 4), TPB, 0, dev->stream>>>(
+        (const float4*)dx, ids, seg, (float4*)dtok, (float4*)dpos, (int)(n / 4), D / 4, T);
+    return vkg_check_launch("embed_bwd_v4");
+  }
   k_embed_bwd<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(dx, ids, seg, dtok, dpos, n, D, T);
   return vkg_check_launch("embed_bwd");
 }

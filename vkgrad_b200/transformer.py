@@ -36,8 +36,9 @@ from .vk import _check
 
 NCHUNK = 32  # kept for callers that pass it to col_sum_chunk (transformer.py:20)
 CAUSAL_BLOCK = 128  # row-tile height of the GEMM: where its causal K ranges stop
-# Dense.backward issues dX and dW as one paired launch (VKG_PAIR_BACKWARD=0: two launches)
-PAIR_BACKWARD = os.environ.get("VKG_PAIR_BACKWARD", "1") != "0"
+# VKG_PAIR_BACKWARD=1: Dense.backward issues dX and dW as one table-scheduled launch
+# (vkg_gemm_pair).  Off by default: the dW GEMM gains more from CTA-pair tiles on its own.
+PAIR_BACKWARD = os.environ.get("VKG_PAIR_BACKWARD", "0") != "0"
 FUSED_HEAD_DIM = 64  # head size the fused attention kernels are written for
 _LN_FUSED_MAX_D = 1536  # shared-memory limit of the fused dgamma/dbeta reduction
 
