@@ -159,17 +159,6 @@ typedef struct vkg_gemm_args {
 
 int vkg_gemm(vkg_device* dev, const vkg_gemm_args* args);
 
-/* Two independent, unbatched GEMMs in ONE launch: the dX = dY W^T and dW = X^T dY that
- * every Linear backward issues back to back (autograd.py:217-227, transformer.py:97-103).
- * Neither fills the 148 SMs a whole number of times on its own; here the tiles of both
- * (K slices for a split dW) are dealt to the CTAs by a table made on the host, longest
- * first, so the tail of one runs beside the other.  Results are those of vkg_gemm(a)
- * followed by vkg_gemm(b), bit for bit; max_ctas is ignored.  The table is built at the
- * first call for a pair of shapes and kept with the device; that first call uploads it
- * synchronously, so it must come before a stream capture -- vkg_gemm_pair_prepare does
- * only that. */
-int vkg_gemm_pair_prepare(vkg_device* dev, const vkg_gemm_args* a, const vkg_gemm_args* b);
-int vkg_gemm_pair(vkg_device* dev, const vkg_gemm_args* a, const vkg_gemm_args* b);
 
 /* ---- MLP-step fused ops: replaces kernels.make_kernels (kernels.py:699-862) */
 

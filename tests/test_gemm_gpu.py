@@ -265,58 +265,6 @@ def test_split_k(dev, m, n, k, ta, tb, split_k):
         x.destroy()
 
 
-@pytest.mark.parametrize("rows,fin,fout,mode", [
-    (1024, 768, 3072, "plain"),      # dX fp32 + split dW (fc1 / qkv backward shape family)
-    (1024, 3072, 768, "dgelu"),      # dX * GELU'(z) narrowed to fp16 + dW (fc2 backward)
-    (640, 256, 264, "f16"),          # ragged sizes, fp16 dX (proj backward), dW not split
-    (136, 72, 1000, "plain"),        # fewer tiles than SMs: some CTAs get no unit
-])
-def test_paired_backward_equals_two_launches(dev, rows, fin, fout, mode):
-    """vkg_gemm_pair(dX, dW) must give bit for bit what vkg_gemm(dX); vkg_gemm(dW) gives
-    (autograd.py:217-227 issues the two one after the other), and match the oracle."""
-    from vkgrad_b200._lib import ACT_GELU, F16, F32
-    from vkgrad_b200.kernels import gemm, gemm_pair
-    rng = np.random.default_rng(rows + fin)
-    x = rng.standard_normal((rows, fin)).astype(np.float16)
-    w = (rng.standard_normal((fin, fout)) / np.sqrt(fin)).astype(np.float16)
-    dy = rng.standard_normal((rows, fout)).astype(np.float16)
-    z = rng.standard_normal((rows, fin)).astype(np.float32)
-    bx, bw, bdy, bz = (up(dev, a) for a in (x, w, dy, z))
-    c_dtype, esz = (F32, 4) if mode == "plain" else (F16, 2)
-    kw_dx = dict(trans_b=True, c_dtype=c_dtype, split_k=1)
-    if mode == "dgelu":
-        kw_dx.update(dact_z=bz, dact=ACT_GELU)
-    outs = []
-    for paired in (False, True):
-        bdx = dev.buffer(rows * fin * esz, "cached")
-        bdw = dev.buffer(fin * fout * 4, "cached")
-        for b in (bdx, bdw):
-            b.array(np.uint8)[:] = 0xFF
-            b.flush()
-        dxa = (bdy, bw, bdx, rows, fin, fout, kw_dx)
-        dwa = (bx, bdy, bdw, fin, fout, rows, dict(trans_a=True))
-        if paired:
-            gemm_pair(dev, dxa, dwa)
-            gemm_pair(dev, dxa, dwa)      # second call reuses the unit table
-        else:
-            gemm(dev, *dxa[:6], **dxa[6])
-            gemm(dev, *dwa[:6], **dwa[6])
-        outs.append((down(dev, bdx, np.float32 if esz == 4 else np.float16, (rows, fin)),
-                     down(dev, bdw, np.float32, (fin, fout))))
-        bdx.destroy()
-        bdw.destroy()
-    (dx0, dw0), (dx1, dw1) = outs
-    assert np.array_equal(dx0, dx1)
-    assert np.array_equal(dw0, dw1)
-    ref_dx = orc.matmul16(dy, w, False, True)
-    if mode == "dgelu":
-        ref_dx = ref_dx * orc.dgelu(z)
-    assert relerr(dx1.astype(np.float32), ref_dx) < TOL
-    assert relerr(dw1, orc.matmul16(x, dy, True, False)) < TOL
-    for b in (bx, bw, bdy, bz):
-        b.destroy()
-
-
 @pytest.mark.parametrize("m,n,k,ta,tb,split_k", [
     (512, 512, 256, False, False, 1),      # Y = X W, B stored K x N
     (512, 768, 320, False, True, 1),       # dX = dY W^T, B stored N x K

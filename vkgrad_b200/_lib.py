@@ -76,8 +76,6 @@ _SIGNATURES = {
     "vkg_graph_destroy": (i32, [vp]),
     "vkg_graph_kernel_count": (i32, [vp, C.POINTER(i32)]),
     "vkg_gemm": (i32, [vp, C.POINTER(GemmArgs)]),
-    "vkg_gemm_pair_prepare": (i32, [vp, C.POINTER(GemmArgs), C.POINTER(GemmArgs)]),
-    "vkg_gemm_pair": (i32, [vp, C.POINTER(GemmArgs), C.POINTER(GemmArgs)]),
     "vkg_bias_act": (i32, [vp, vp, vp, vp, vp, i64, i32, i32]),
     "vkg_bias_act_bwd": (i32, [vp, vp, vp, vp, vp, i64, i32]),
     "vkg_bias": (i32, [vp, vp, vp, vp, i64, i32]),

@@ -36,11 +36,7 @@ struct vkg_device {
   void* encode_tiled = nullptr;
   size_t gemm_smem_optin = 0;
   bool gemm_attr_set = false;
-  // unit tables of paired GEMM launches, owned by gemm_sm100.cu
-  void* gemm_plans = nullptr;
 };
-
-void vkg_gemm_release_plans(vkg_device* dev);
 
 struct vkg_graph {
   cudaGraph_t graph = nullptr;

@@ -19,9 +19,6 @@
 // Every mbarrier wait is bounded by a clock64 budget; a wait that gives up
 // sets an error word the host reads at the next synchronisation, the CTA
 // stops issuing work, frees its TMEM and returns.
-#include <algorithm>
-#include <string>
-
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -686,59 +683,6 @@ gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   }
 }
 
-// Two independent GEMMs of the same tile width in one launch.  Their work units are dealt
-// to the CTAs by a host-made table (longest units first, each to the least loaded CTA), so
-// the tail of one problem fills up with units of the other:
-//   cta_start[b] .. cta_start[b + 1] index `units`; a unit is (problem << 28) | tile.
-constexpr int UNIT_TILE_MASK = (1 << 28) - 1;
-
-template <int MODE_A, int MODE_B>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
-                         const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
-                         const GemmParams pa, const GemmParams pb, const int* __restrict__ cta_start,
-                         const int* __restrict__ units) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  CtaCtx cx;
-  cta_setup(cx, smem_raw, pa.bn, pa.stages);
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const int u_begin = cta_start[blockIdx.x], u_end = cta_start[blockIdx.x + 1];
-  if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int ui = u_begin; ui < u_end; ++ui) {
-        const int u = units[ui], t = u & UNIT_TILE_MASK;
-        const bool ok = (u >> 28) == 0 ? produce_unit(cx, pa, &tmA0, &tmB0, t, stage, phase)
-                                       : produce_unit(cx, pb, &tmA1, &tmB1, t, stage, phase);
-        if (!ok) break;
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
-      for (int ui = u_begin; ui < u_end; ++ui) {
-        const int u = units[ui], t = u & UNIT_TILE_MASK;
-        const bool ok = (u >> 28) == 0 ? mma_unit(cx, pa, t, stage, phase, acc, acc_phase)
-                                       : mma_unit(cx, pb, t, stage, phase, acc, acc_phase);
-        if (!ok) break;
-      }
-    }
-  } else {
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    for (int ui = u_begin; ui < u_end; ++ui) {
-      const int u = units[ui], t = u & UNIT_TILE_MASK;
-      const bool ok = (u >> 28) == 0 ? epilogue_unit<MODE_A>(cx, pa, t, warp, lane, acc, acc_phase)
-                                     : epilogue_unit<MODE_B>(cx, pb, t, warp, lane, acc, acc_phase);
-      if (!ok) break;
-    }
-  }
-  cta_teardown(cx);
-}
-
 // Adds the K slices of a split GEMM in slice order and writes C (fp32, row pitch ldc).
 __global__ void k_splitk_reduce(const float4* __restrict__ ws, float* __restrict__ C, int M, int N4,
                                 long long ldc, int splits) {
@@ -756,18 +700,11 @@ __global__ void k_splitk_reduce(const float4* __restrict__ ws, float* __restrict
 }
 
 typedef void (*GemmKernel)(const CUtensorMap, const CUtensorMap, const GemmParams);
-typedef void (*PairKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                           const GemmParams, const GemmParams, const int*, const int*);
 struct Specialised {
   int mode;
   GemmKernel fn;
 };
-struct SpecialisedPair {
-  int mode_a, mode_b;
-  PairKernel fn;
-};
 #define VKG_SPEC(m) {(m), gemm_tcgen05_kernel<(m)>}
-#define VKG_SPEC2(ma, mb) {(ma), (mb), gemm_pair_tcgen05_kernel<(ma), (mb)>}
 // The epilogues the training step uses; anything else runs the generic kernel.
 const Specialised kSpecialised[] = {
     VKG_SPEC(0),                                   // fp32 out: dW, dX into layernorm, scores
@@ -791,14 +728,6 @@ const Specialised kCtaPair[] = {
     VKG_SPEC_CP(E_DACT | E_F16),
 };
 const int kNumCtaPair = sizeof(kCtaPair) / sizeof(kCtaPair[0]);
-// The (dX, dW) pairs of a Dense backward.
-const SpecialisedPair kPairs[] = {
-    VKG_SPEC2(0, 0),                               // fc1, qkv: dX fp32 into layernorm backward
-    VKG_SPEC2(E_DACT | E_F16, 0),                  // fc2: dX * GELU'(z), narrowed
-    VKG_SPEC2(E_F16, 0),                           // proj: dX narrowed for the attention backward
-};
-const int kNumPairs = sizeof(kPairs) / sizeof(kPairs[0]);
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -990,7 +919,7 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
 
   out->vec = vec;
   out->total_tiles = (long long)p.tiles_m * p.tiles_n * batch * p.split_k;
-  VKG_REQUIRE(out->total_tiles <= UNIT_TILE_MASK, "gemm: too many tiles");
+  VKG_REQUIRE(out->total_tiles < (1ll << 30), "gemm: too many tiles");
   out->mode = (a->bias ? E_BIAS : 0) | (a->pre ? E_PRE : 0) | (a->act ? E_ACT : 0) |
               (a->dact_z ? E_DACT : 0) | (a->residual ? E_RES : 0) | (a->C2 ? E_C2 : 0) |
               (a->c_dtype == VKG_F16 ? E_F16 : a->c_dtype == VKG_BF16 ? E_BF16 : 0);
@@ -1008,9 +937,6 @@ int ensure_attrs(vkg_device* dev) {
   for (int i = 0; i < kNumSpecialised; ++i)
     VKG_CUDA(cudaFuncSetAttribute(kSpecialised[i].fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   SMEM_BYTES));
-  for (int i = 0; i < kNumPairs; ++i)
-    VKG_CUDA(cudaFuncSetAttribute(kPairs[i].fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  SMEM_BYTES));
   VKG_CUDA(cudaFuncSetAttribute(gemm_cta_pair_kernel<E_GENERIC>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   for (int i = 0; i < kNumCtaPair; ++i)
@@ -1026,13 +952,6 @@ GemmKernel pick_kernel(int mode) {
   return gemm_tcgen05_kernel<E_GENERIC>;
 }
 
-// The kernel compiled for this pair of epilogue masks, or null.
-PairKernel pick_pair_kernel(int mode_a, int mode_b) {
-  for (int i = 0; i < kNumPairs; ++i)
-    if (kPairs[i].mode_a == mode_a && kPairs[i].mode_b == mode_b) return kPairs[i].fn;
-  return nullptr;
-}
-
 int reduce_slices(vkg_device* dev, const vkg_gemm_args* a, const GemmParams& p) {
   if (p.split_k <= 1) return 0;
   const long long n4 = (long long)a->M * (a->N / 4);
@@ -1041,104 +960,7 @@ int reduce_slices(vkg_device* dev, const vkg_gemm_args* a, const GemmParams& p) 
   return vkg_check_launch("splitk_reduce");
 }
 
-// ---- unit tables of paired launches ---------------------------------------------------------
-//
-// Cost of a unit in k-block times: its k-blocks plus what the epilogue of one tile adds.
-struct PairPlan {
-  int* dev_table = nullptr;   // cta_start[ctas + 1] followed by units[n]
-  int ctas = 0;
-};
-typedef std::map<std::string, PairPlan> PlanMap;
-
-std::string pair_key(const Problem& x, const Problem& y, int sms) {
-  char buf[256];
-  snprintf(buf, sizeof(buf), "%d,%d,%d,%d,%d,%d|%d,%d,%d,%d,%d,%d|%d", x.p.M, x.p.N, x.p.K, x.p.bn,
-           x.p.split_k, x.mode, y.p.M, y.p.N, y.p.K, y.p.bn, y.p.split_k, y.mode, sms);
-  return buf;
-}
-
-double unit_cost(const Problem& q, int t) {
-  int kb0, nkb;
-  GemmParams p = q.p;
-  // same arithmetic as the device: slice length when K is split, all k-blocks otherwise
-  if (p.split_k > 1) {
-    const int per_batch = p.tiles_m * p.tiles_n;
-    const int z1 = (t / per_batch) / p.nb0;
-    kb0 = z1 * p.kb_per_split;
-    nkb = std::min(p.kb_per_split, p.num_kb - kb0);
-  } else {
-    nkb = p.num_kb;
-  }
-  const bool wide = (q.mode & (E_F16 | E_BF16)) == 0;
-  const double epi = (wide ? 4.0 : 2.5) + ((q.mode & (E_DACT | E_RES | E_PRE)) ? 2.5 : 0.0);
-  return nkb + epi;
-}
-
-int make_pair_plan(vkg_device* dev, const Problem& x, const Problem& y, PairPlan* plan) {
-  const int ctas = dev->sm_count;
-  struct Unit { double cost; int id; };
-  std::vector<Unit> units;
-  for (int t = 0; t < (int)x.total_tiles; ++t) units.push_back({unit_cost(x, t), t});
-  for (int t = 0; t < (int)y.total_tiles; ++t) units.push_back({unit_cost(y, t), (1 << 28) | t});
-  std::stable_sort(units.begin(), units.end(), [](const Unit& a, const Unit& b) { return a.cost > b.cost; });
-  std::vector<std::vector<int>> per(ctas);
-  std::vector<double> load(ctas, 0.0);
-  for (const Unit& u : units) {
-    int best = 0;
-    for (int c = 1; c < ctas; ++c)
-      if (load[c] < load[best]) best = c;
-    per[best].push_back(u.id);
-    load[best] += u.cost;
-  }
-  std::vector<int> table(ctas + 1, 0);
-  for (int c = 0; c < ctas; ++c) table[c + 1] = table[c] + (int)per[c].size();
-  for (int c = 0; c < ctas; ++c) {
-    // tiles of one problem in index order within a CTA: neighbours share operand rows in L2
-    std::sort(per[c].begin(), per[c].end());
-    table.insert(table.end(), per[c].begin(), per[c].end());
-  }
-  // unit indices in the table are relative to the start of the unit array
-  VKG_CUDA(cudaMalloc(&plan->dev_table, table.size() * sizeof(int)));
-  VKG_CUDA(cudaMemcpy(plan->dev_table, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice));
-  plan->ctas = ctas;
-  return 0;
-}
-
-int pair_setup(vkg_device* dev, const vkg_gemm_args* a, const vkg_gemm_args* b, Problem* x, Problem* y,
-               PairPlan** plan, bool may_create) {
-  VKG_REQUIRE(a && b, "gemm_pair: null gemm args");
-  const int nba = (a->nb0 > 0 ? a->nb0 : 1) * (a->nb1 > 0 ? a->nb1 : 1);
-  const int nbb = (b->nb0 > 0 ? b->nb0 : 1) * (b->nb1 > 0 ? b->nb1 : 1);
-  VKG_REQUIRE(nba == 1 && nbb == 1 && a->causal == 0 && b->causal == 0,
-              "gemm_pair: both GEMMs must be unbatched and not causal");
-  VKG_REQUIRE(a->in_dtype == b->in_dtype, "gemm_pair: operand types differ");
-  if (build_problem(dev, a, 256, x) || build_problem(dev, b, 256, y)) return 1;
-  VKG_REQUIRE(x->p.bn == y->p.bn, "gemm_pair: tile widths differ (%d, %d)", x->p.bn, y->p.bn);
-  if (!dev->gemm_plans) dev->gemm_plans = new PlanMap();
-  PlanMap& plans = *static_cast<PlanMap*>(dev->gemm_plans);
-  const std::string key = pair_key(*x, *y, dev->sm_count);
-  auto it = plans.find(key);
-  if (it == plans.end()) {
-    VKG_REQUIRE(may_create && !dev->capturing,
-                "gemm_pair: no unit table for this pair of shapes; call vkg_gemm_pair_prepare "
-                "before the stream capture begins");
-    PairPlan plan;
-    if (make_pair_plan(dev, *x, *y, &plan)) return 1;
-    it = plans.emplace(key, plan).first;
-  }
-  *plan = &it->second;
-  return 0;
-}
-
 }  // namespace
-
-void vkg_gemm_release_plans(vkg_device* dev) {
-  if (!dev || !dev->gemm_plans) return;
-  PlanMap* plans = static_cast<PlanMap*>(dev->gemm_plans);
-  for (auto& kv : *plans) cudaFree(kv.second.dev_table);
-  delete plans;
-  dev->gemm_plans = nullptr;
-}
 
 extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   if (vkg_bind(dev)) return 1;
@@ -1190,31 +1012,4 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   pick_kernel(q.mode)<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(q.tmA, q.tmB, q.p);
   if (vkg_check_launch("gemm_tcgen05_kernel")) return 1;
   return reduce_slices(dev, a, q.p);
-}
-
-extern "C" int vkg_gemm_pair_prepare(vkg_device* dev, const vkg_gemm_args* a, const vkg_gemm_args* b) {
-  if (vkg_bind(dev)) return 1;
-  Problem x, y;
-  PairPlan* plan = nullptr;
-  return pair_setup(dev, a, b, &x, &y, &plan, true);
-}
-
-extern "C" int vkg_gemm_pair(vkg_device* dev, const vkg_gemm_args* a, const vkg_gemm_args* b) {
-  if (vkg_bind(dev)) return 1;
-  Problem x, y;
-  PairPlan* plan = nullptr;
-  if (pair_setup(dev, a, b, &x, &y, &plan, true)) return 1;
-  if (ensure_attrs(dev)) return 1;
-  PairKernel fn = pick_pair_kernel(x.mode, y.mode);
-  if (!fn) {
-    // no kernel for this pair of epilogues: two launches, same results
-    if (vkg_gemm(dev, a)) return 1;
-    return vkg_gemm(dev, b);
-  }
-  fn<<<plan->ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(x.tmA, x.tmB, y.tmA, y.tmB, x.p, y.p,
-                                                          plan->dev_table,
-                                                          plan->dev_table + plan->ctas + 1);
-  if (vkg_check_launch("gemm_tcgen05_kernel (pair)")) return 1;
-  if (reduce_slices(dev, a, x.p)) return 1;
-  return reduce_slices(dev, b, y.p);
 }

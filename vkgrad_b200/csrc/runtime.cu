@@ -77,7 +77,6 @@ extern "C" int vkg_device_destroy(vkg_device* dev) {
   if (!dev) return 0;
   cudaSetDevice(dev->ordinal);
   cudaStreamSynchronize(dev->stream);
-  vkg_gemm_release_plans(dev);
   if (dev->ev0) cudaEventDestroy(dev->ev0);
   if (dev->ev1) cudaEventDestroy(dev->ev1);
   if (dev->err_host) cudaFreeHost((void*)dev->err_host);

@@ -117,33 +117,6 @@ def gemm(dev, a, b, c, m, n, k, trans_a=False, trans_b=False, graph=None, repeat
     return dev.run_op(go, repeat)
 
 
-def gemm_pair(dev, first, second, graph=None, repeat=1, name="gemm_pair"):
-    """Two independent GEMMs in one launch (vkg_gemm_pair): `first` and `second` are
-    (a, b, c, m, n, k, kwargs) tuples as for gemm().  Used for the dX and dW of a Linear
-    backward (autograd.py:217-227), which share dY and do not depend on each other."""
-    xa = _gemm_args(dev, *first[:6], **first[6])
-    ya = _gemm_args(dev, *second[:6], **second[6])
-    if xa.workspace and ya.workspace:
-        # the two problems run at the same time and would share the device's scratch
-        raise VkError(f"{name}: only one of the two GEMMs may split K (pass split_k=1 to the other)")
-    lib, h = dev.lib, dev.handle
-    _check(lib.vkg_gemm_pair_prepare(h, C.byref(xa), C.byref(ya)), f"{name} prepare")
-
-    def go():
-        _check(lib.vkg_gemm_pair(h, C.byref(xa), C.byref(ya)), name)
-
-    if graph is not None:
-        total = 0
-        for args in (xa, ya):
-            m, n, k = args.M, args.N, args.K
-            esz_c = 4 if args.c_dtype == F32 else 2
-            total += 2 * m * k + 2 * k * n + esz_c * m * n
-            graph.mm_split.append((2 * (m * k + k * n), m * n * esz_c))
-        graph.add(go, name, total)
-        return 0.0
-    return dev.run_op(go, repeat)
-
-
 class Matmul:
     """One matmul configuration (kernels.py:232-315).
 

@@ -24,21 +24,16 @@ A static loss scale can be applied in the loss kernel (`loss_scale`); parameter
 gradients then carry that factor until AdamW divides it out.
 """
 
-import os
-
 import numpy as np
 
 from ._lib import ACT_GELU, ACT_NONE, F16, F32
 from .autograd import Ctx, Param
-from .kernels import gemm, gemm_pair
+from .kernels import gemm
 from .tkernels import make_transformer_kernels
 from .vk import _check
 
 NCHUNK = 32  # kept for callers that pass it to col_sum_chunk (transformer.py:20)
 CAUSAL_BLOCK = 128  # row-tile height of the GEMM: where its causal K ranges stop
-# VKG_PAIR_BACKWARD=1: Dense.backward issues dX and dW as one table-scheduled launch
-# (vkg_gemm_pair).  Off by default: the dW GEMM gains more from CTA-pair tiles on its own.
-PAIR_BACKWARD = os.environ.get("VKG_PAIR_BACKWARD", "0") != "0"
 FUSED_HEAD_DIM = 64  # head size the fused attention kernels are written for
 _LN_FUSED_MAX_D = 1536  # shared-memory limit of the fused dgamma/dbeta reduction
 
@@ -156,21 +151,15 @@ class Dense:
         dxsum), so the column-sum pass is skipped."""
         c, dev = self.ctx, self.ctx.dev
         R, I, O = self.rows, self.in_f, self.out_f
-        dw = (self.x16, dy16, self.W.g32, I, O, R, dict(trans_a=True))
-        if need_dx and dx is None:
-            if self.dx32 is None:
-                self.dx32 = c.buf(R * I * 4)
-            dx, dx_dtype = self.dx32, F32
-        if need_dx and PAIR_BACKWARD:
-            # dX and dW share dY and nothing else: one launch, tiles of both dealt over the SMs
-            dxa = (dy16, self.W.w16, dx, R, I, O,
-                   dict(trans_b=True, c_dtype=dx_dtype, dact_z=dact_z, dact=dact, split_k=1))
-            gemm_pair(dev, dxa, dw, graph=graph, name=f"{self.name}.dX+dW")
-        else:
-            gemm(dev, *dw[:6], graph=graph, name=f"{self.name}.dW", **dw[6])
-            if need_dx:
-                gemm(dev, dy16, self.W.w16, dx, R, I, O, trans_b=True, graph=graph, c_dtype=dx_dtype,
-                     dact_z=dact_z, dact=dact, name=f"{self.name}.dX")
+        gemm(dev, self.x16, dy16, self.W.g32, I, O, R, trans_a=True, graph=graph,
+             name=f"{self.name}.dW")
+        if need_dx:
+            if dx is None:
+                if self.dx32 is None:
+                    self.dx32 = c.buf(R * I * 4)
+                dx, dx_dtype = self.dx32, F32
+            gemm(dev, dy16, self.W.w16, dx, R, I, O, trans_b=True, graph=graph, c_dtype=dx_dtype,
+                 dact_z=dact_z, dact=dact, name=f"{self.name}.dX")
         if not bias_grad_done:
             c.col_sum(dy16, self.b.g32, O, R, graph=graph)
         return dx if need_dx else None
