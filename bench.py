@@ -227,7 +227,7 @@ def time_attention(dev, B, T, H, hd):
 
     def bwd():
         _check(lib.vkg_attn_bwd(h, qkv.dptr, dout.dptr, out.dptr, lse.dptr, None, dqkv.dptr,
-                                delta.dptr, B, T, H, hd, scale), "bwd")
+                                delta.dptr, None, None, B, T, H, hd, scale), "bwd")
     res = {}
     for name, fn in (("fwd_us", fwd), ("bwd_us", bwd)):
         dev.run_op(fn, 2)

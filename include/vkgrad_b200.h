@@ -155,7 +155,15 @@ typedef struct vkg_gemm_args {
                                 tcgen05.mma.cta_group::2 (each CTA loads half of the B tile):
                                 0 = the library decides, 1 = always (when the shape allows it),
                                 -1 = never.  Not available with causal != 0. */
+  float* colsum;             /* optional, N floats: column sums of the output as stored (after
+                                the epilogue and the narrowing), the bias gradient of the layer
+                                that produced this GEMM's dY (replaces the col_sum pass of
+                                transformer.py:30-36 over it).  Deterministic.  Unbatched,
+                                causal == 0, K not split. */
+  float* colsum_scratch;     /* with colsum: vkg_gemm_colsum_scratch_floats(M, N) floats */
 } vkg_gemm_args;
+
+int64_t vkg_gemm_colsum_scratch_floats(int M, int N);
 
 int vkg_gemm(vkg_device* dev, const vkg_gemm_args* args);
 
@@ -245,10 +253,16 @@ int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* seg,
  * as three launches: delta = rowsum(dO * O), a dK/dV kernel (one CTA per key tile)
  * and a dQ kernel (one CTA per query tile), both rebuilding P from lse2.
  * dout16 is the (B*T, D) fp16 gradient of out16; dqkv16 (B*T, 3D) fp16 receives
- * [dQ | dK | dV]; delta is B*H*T floats of scratch.  Deterministic (no atomics). */
+ * [dQ | dK | dV]; delta is B*H*T floats of scratch.  Deterministic (no atomics).
+ * dbias (optional, 3D floats) receives the column sums of dqkv16 as stored -- the gradient
+ * of the qkv bias, which the reference takes with a col_sum pass over the merged gradient
+ * (transformer.py:30-36, 183-186); dbias_scratch then holds
+ * vkg_attn_bwd_dbias_scratch_floats(B, T, H, hd) floats. */
 int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout16,
                  const void* out16, const float* lse2, const uint32_t* seg,
-                 void* dqkv16, float* delta, int B, int T, int H, int hd, float scale);
+                 void* dqkv16, float* delta, float* dbias, float* dbias_scratch,
+                 int B, int T, int H, int hd, float scale);
+int64_t vkg_attn_bwd_dbias_scratch_floats(int B, int T, int H, int hd);
 /* split_qkv / merge_qkv_grad / merge_heads / split_heads (tkernels.py:195-300). */
 int vkg_split_qkv(vkg_device* dev, const float* qkv, const float* bias, void* q16,
                   void* k16, void* v16, int64_t n, int D, int T, int H, int hd);

@@ -98,14 +98,23 @@ def test_backward(dev, B, T, H, packed):
     segp = None if bs is None else bs.dptr
     _check(dev.lib.vkg_attn_fwd(dev.handle, bq.dptr, segp, bo.dptr, bl.dptr, B, T, H, hd, scale),
            "attn_fwd")
-    outs = []
+    outs, sums = [], []
+    bdb = up(dev, np.full(3 * D, np.nan, np.float32))
+    bsc = dev.buffer(4 * dev.lib.vkg_attn_bwd_dbias_scratch_floats(B, T, H, hd), "device")
     for _ in range(2):
         _check(dev.lib.vkg_attn_bwd(dev.handle, bq.dptr, bdo.dptr, bo.dptr, bl.dptr, segp, bdq.dptr,
-                                    bdelta.dptr, B, T, H, hd, scale), "attn_bwd")
+                                    bdelta.dptr, bdb.dptr, bsc.dptr, B, T, H, hd, scale), "attn_bwd")
         dev.sync()
         outs.append(get(bdq, np.float16, (B * T, 3 * D)).astype(np.float32))
+        sums.append(get(bdb, np.float32, (3 * D,)))
     assert np.array_equal(outs[0], outs[1]), "backward is not deterministic"
+    assert np.array_equal(sums[0], sums[1]), "bias gradient is not deterministic"
     got = outs[0]
+    # the qkv bias gradient is the column sum of the stored fp16 gradient
+    want_db = got.astype(np.float64).sum(0)
+    assert np.abs(sums[0] - want_db).max() <= 1e-4 * max(np.abs(want_db).max(), 1.0)
+    bdb.destroy()
+    bsc.destroy()
     assert np.isfinite(got).all()
     q, k, v, p, o, lse2, mask = reference_attention(qkv, B, T, H, scale, seg)
     dao = dout.astype(np.float32).reshape(B, T, H, hd).transpose(0, 2, 1, 3)

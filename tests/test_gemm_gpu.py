@@ -328,3 +328,67 @@ def test_cta_pair_fused_epilogues(dev):
     assert relerr(res[1][0].astype(np.float32), orc.gelu(zref)) < 5e-3
     for b in (bx, bw, bb, bz):
         b.destroy()
+
+
+def test_cta_pair_batched_bf16(dev):
+    """CTA-pair tiles over a batch of matrices with bf16 operands: the batch index walks the
+    tensor maps exactly as in the single-CTA kernel."""
+    from vkgrad_b200._lib import BF16
+    from vkgrad_b200.kernels import gemm
+    nb, m, n, k = 3, 384, 320, 136
+    rng = np.random.default_rng(11)
+
+    def to_bf16_bits(x):
+        u = x.astype(np.float32).view(np.uint32)
+        return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+    a32 = rng.standard_normal((nb, m, k)).astype(np.float32)
+    b32 = rng.standard_normal((nb, k, n)).astype(np.float32)
+    a16, b16 = to_bf16_bits(a32), to_bf16_bits(b32)
+    ar = (a16.astype(np.uint32) << 16).view(np.float32)
+    br = (b16.astype(np.uint32) << 16).view(np.float32)
+    ba, bb = up(dev, a16), up(dev, b16)
+    outs = []
+    for pair in (-1, 1):
+        bc = dev.buffer(nb * m * n * 4, "cached")
+        gemm(dev, ba, bb, bc, m, n, k, nb0=nb, sa=(m * k, 0), sb=(k * n, 0), sc=(m * n, 0),
+             in_dtype=BF16, cta_pair=pair)
+        outs.append(down(dev, bc, np.float32, (nb, m, n)))
+        bc.destroy()
+    assert np.array_equal(outs[0], outs[1])
+    assert relerr(outs[1], np.einsum("bmk,bkn->bmn", ar, br)) < TOL
+    for x in (ba, bb):
+        x.destroy()
+
+
+@pytest.mark.parametrize("m,n,k,pair", [(640, 520, 192, -1), (1000, 264, 72, -1), (640, 520, 192, 1),
+                                        (384, 512, 128, 1)])
+def test_epilogue_column_sums(dev, m, n, k, pair):
+    """colsum: the bias gradient of the layer below comes out of the GEMM that writes its dY
+    (fp16, scaled by GELU'(z)); it must equal the column sums of that stored fp16 matrix
+    (what transformer.py:30-36 computes in a separate pass), twice in a row bit for bit."""
+    from vkgrad_b200._lib import ACT_GELU, F16
+    from vkgrad_b200.kernels import gemm
+    rng = np.random.default_rng(m + n)
+    dy = rng.standard_normal((m, k)).astype(np.float16)
+    w = (rng.standard_normal((n, k)) / np.sqrt(k)).astype(np.float16)
+    z = rng.standard_normal((m, n)).astype(np.float32)
+    bdy, bw, bz = up(dev, dy), up(dev, w), up(dev, z)
+    sums = []
+    for _ in range(2):
+        d16 = dev.buffer(m * n * 2, "cached")
+        cs = dev.buffer(n * 4, "cached")
+        cs.array(np.float32)[:] = np.nan
+        cs.flush()
+        gemm(dev, bdy, bw, d16, m, n, k, trans_b=True, c_dtype=F16, dact_z=bz, dact=ACT_GELU,
+             colsum=cs, cta_pair=pair)
+        got = down(dev, d16, np.float16, (m, n)).astype(np.float64)
+        sums.append(down(dev, cs, np.float32, (n,)))
+        d16.destroy()
+        cs.destroy()
+    assert np.array_equal(sums[0], sums[1])
+    want = got.sum(0)
+    assert np.abs(sums[1] - want).max() <= 1e-4 * max(np.abs(want).max(), 1.0)
+    assert relerr(got.astype(np.float32), orc.matmul16(dy, w, False, True) * orc.dgelu(z)) < 5e-3
+    for b in (bdy, bw, bz):
+        b.destroy()

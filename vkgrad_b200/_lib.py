@@ -45,6 +45,8 @@ class GemmArgs(C.Structure):
         ("workspace_bytes", i64),
         ("causal", C.c_int32),
         ("cta_pair", C.c_int32),
+        ("colsum", vp),
+        ("colsum_scratch", vp),
     ]
 
 
@@ -76,6 +78,7 @@ _SIGNATURES = {
     "vkg_graph_destroy": (i32, [vp]),
     "vkg_graph_kernel_count": (i32, [vp, C.POINTER(i32)]),
     "vkg_gemm": (i32, [vp, C.POINTER(GemmArgs)]),
+    "vkg_gemm_colsum_scratch_floats": (i64, [i32, i32]),
     "vkg_bias_act": (i32, [vp, vp, vp, vp, vp, i64, i32, i32]),
     "vkg_bias_act_bwd": (i32, [vp, vp, vp, vp, vp, i64, i32]),
     "vkg_bias": (i32, [vp, vp, vp, vp, i64, i32]),
@@ -94,7 +97,8 @@ _SIGNATURES = {
     "vkg_attn_softmax": (i32, [vp, vp, vp, vp, i64, i32, i32, f32, i32]),
     "vkg_attn_softmax_bwd": (i32, [vp, vp, vp, vp, i64, i32, f32, i32]),
     "vkg_attn_fwd": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32]),
-    "vkg_attn_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32]),
+    "vkg_attn_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32]),
+    "vkg_attn_bwd_dbias_scratch_floats": (i64, [i32, i32, i32, i32]),
     "vkg_split_qkv": (i32, [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32]),
     "vkg_merge_qkv_grad": (i32, [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32]),
     "vkg_merge_heads": (i32, [vp, vp, vp, i64, i32, i32, i32, i32]),

@@ -42,6 +42,7 @@ struct AttnParams {
   float* lse2;             // (B*H, T): row log2-sum-exp of the scaled scores
   const float* delta;      // backward: rowsum(dO * O), (B*H, T)
   __half* dqkv;            // backward: (rows, 3D)
+  float* colsum;           // backward, optional: [B * nqt * 4][3D] partial column sums of dqkv
   uint32_t* err;
 };
 
@@ -377,6 +378,26 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rd
   }
 }
 
+// Column sums of one warp's 32 rows x NC columns (fp16 values as stored, 0 for rows that do not
+// exist) into dst[0 .. NC): the block goes through shared memory row by row (pitch NC + 1
+// words, conflict-free both ways) and lane c adds column c, c + 32, ... top to bottom, so
+// the result does not depend on timing.  `pad` is this warp's private 32 x (NC + 1) floats.
+template <int NC>
+__device__ __forceinline__ void warp_col_sums(const float (&val)[NC], float* pad, int lane,
+                                              float* dst) {
+#pragma unroll
+  for (int c = 0; c < NC; ++c) pad[lane * (NC + 1) + c] = val[c];
+  __syncwarp();
+#pragma unroll
+  for (int c0 = 0; c0 < NC; c0 += 32) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int r = 0; r < 32; ++r) s += pad[r * (NC + 1) + c0 + lane];
+    dst[c0 + lane] = s;
+  }
+  __syncwarp();
+}
+
 // dK / dV: one CTA per (key tile, head, sequence); loops over the query tiles at or
 // below the diagonal.  TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384).
 // P and dS are double-buffered (buffer = iteration & 1) so the softmax warps can build the
@@ -564,6 +585,18 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
         }
       }
+      if (p.colsum) {
+        // the qkv bias gradient: column sums of dV / dK as stored; every MMA has retired
+        // and every operand tile has been consumed, so the tile area is free to use
+        float val[64];
+#pragma unroll
+        for (int c = 0; c < 64; ++c)
+          val[c] = key < p.T ? __half2float(__float2half_rn(__uint_as_float(rr[c]))) : 0.f;
+        float* pad = reinterpret_cast<float*>(gbase) + (warp - 2) * 32 * 65;
+        float* dst = p.colsum + ((size_t)(b * p.nqt + kt) * 4 + (warp & 3)) * 3 * p.D +
+                     (half == 0 ? 2 : 1) * p.D + h * FA_HD;
+        warp_col_sums<64>(val, pad, lane, dst);
+      }
     }
   }
   __syncwarp();
@@ -740,6 +773,16 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
           *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
         }
       }
+      if (p.colsum) {
+        float val[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          val[c] = q_ok ? __half2float(__float2half_rn(__uint_as_float(rr[c]))) : 0.f;
+        float* pad = reinterpret_cast<float*>(gbase) + (warp - 2) * 32 * 33;
+        float* dst = p.colsum + ((size_t)(b * p.nqt + qt) * 4 + (warp & 3)) * 3 * p.D + h * FA_HD +
+                     half * 32;
+        warp_col_sums<32>(val, pad, lane, dst);
+      }
     }
   }
   __syncwarp();
@@ -818,7 +861,8 @@ extern "C" int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* 
 
 extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout16, const void* out16,
                             const float* lse2, const uint32_t* seg, void* dqkv16, float* delta,
-                            int B, int T, int H, int hd, float scale) {
+                            float* dbias, float* dbias_scratch, int B, int T, int H, int hd,
+                            float scale) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(qkv16 && dout16 && out16 && lse2 && dqkv16 && delta && B > 0 && T > 0 && H > 0,
               "attn_bwd: bad arguments");
@@ -839,6 +883,8 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
   p.delta = delta;
   p.dqkv = (__half*)dqkv16;
   p.err = dev->err_dev;
+  VKG_REQUIRE(!dbias || dbias_scratch, "attn_bwd: dbias needs dbias_scratch");
+  p.colsum = dbias ? dbias_scratch : nullptr;
   static bool attr_set = false;
   if (!attr_set) {
     VKG_CUDA(cudaFuncSetAttribute(attn_bwd_kv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -856,5 +902,13 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
   attn_bwd_kv_kernel<<<ctas, BW_THREADS, KV_SMEM, dev->stream>>>(tm, tmdo, p);
   if (vkg_check_launch("attn_bwd_kv_kernel")) return 1;
   attn_bwd_q_kernel<<<ctas, BW_THREADS, DQ_SMEM, dev->stream>>>(tm, tmdo, p);
-  return vkg_check_launch("attn_bwd_q_kernel");
+  if (vkg_check_launch("attn_bwd_q_kernel")) return 1;
+  if (dbias)
+    return vkg_launch_col_sum_final(dev, dbias_scratch, dbias, 3 * D, B * p.nqt * 4, 0);
+  return 0;
+}
+
+extern "C" int64_t vkg_attn_bwd_dbias_scratch_floats(int B, int T, int H, int hd) {
+  if (B <= 0 || T <= 0 || H <= 0 || hd <= 0) return 0;
+  return (int64_t)B * ((T + FA_T - 1) / FA_T) * 4 * 3 * H * hd;
 }

@@ -46,6 +46,10 @@ struct vkg_graph {
 
 void vkg_set_error(const char* fmt, ...);
 
+// ops.cu: sums[c] (+)= sum over nchunk rows of partial[k][c], rows added in a fixed order
+int vkg_launch_col_sum_final(vkg_device* dev, const float* partial, float* sums, int ncol, int nchunk,
+                             int accumulate);
+
 #define VKG_FAIL(...)            \
   do {                           \
     vkg_set_error(__VA_ARGS__);  \

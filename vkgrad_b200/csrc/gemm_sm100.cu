@@ -58,6 +58,7 @@ struct GemmParams {
   float* pre;
   const float* dact_z;
   const float* residual;
+  float* colsum;               // optional: [4 * row blocks][N] partial column sums of the output
   float alpha;
   uint32_t* err;
 };
@@ -108,6 +109,7 @@ __device__ __forceinline__ void kb_range(const GemmParams& p, const TileCoord& c
 // alignment flag) at run time; the specialised masks assume 16-byte aligned operands.
 enum : int {
   E_BIAS = 1, E_PRE = 2, E_ACT = 4, E_DACT = 8, E_RES = 16, E_C2 = 32, E_F16 = 64, E_BF16 = 128,
+  E_COLSUM = 256,
   E_GENERIC = 1 << 20
 };
 
@@ -156,10 +158,17 @@ __device__ __forceinline__ void st4(float* p, long long off, float4 v, bool vec)
 // row-contiguous 64-byte pieces.  All loads of one kind are issued before the first
 // dependent use: C may alias the inputs as far as the compiler knows, so a
 // load-compute-store loop would serialise eight memory round trips.
+//
+// lanes: the lanes of the warp that call this together (those whose columns exist).
+// cs_row: which row of p.colsum this warp's 32 rows add up into.  The sums are taken over
+// the values as stored (after the narrowing), rows in a fixed order: lanes first add their
+// four rows, then the eight row groups are folded by shuffles.
 template <int MODE>
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, float4 (&v)[4],
-                                               const long long (&off)[4], unsigned ok, int col) {
+                                               const long long (&off)[4], unsigned ok, int col,
+                                               int cs_row, unsigned lanes) {
   constexpr bool G = (MODE & E_GENERIC) != 0;
+  const bool has_colsum = G ? (p.colsum != nullptr) : (MODE & E_COLSUM) != 0;
   const bool vec = G ? (p.vec_ok != 0) : true;
   const bool has_bias = G ? (p.bias != nullptr) : (MODE & E_BIAS) != 0;
   const bool has_pre = G ? (p.pre != nullptr) : (MODE & E_PRE) != 0;
@@ -208,6 +217,30 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, float4 (&v)[
     for (int i = 0; i < 4; ++i) {
       v[i].x += extra[i].x; v[i].y += extra[i].y; v[i].z += extra[i].z; v[i].w += extra[i].w;
     }
+  }
+  if (has_colsum) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (!((ok >> i) & 1u)) continue;
+      float4 t = v[i];
+      if (c_dtype == VKG_F16) {
+        t.x = __half2float(__float2half_rn(t.x)); t.y = __half2float(__float2half_rn(t.y));
+        t.z = __half2float(__float2half_rn(t.z)); t.w = __half2float(__float2half_rn(t.w));
+      } else if (c_dtype == VKG_BF16) {
+        t.x = __bfloat162float(__float2bfloat16_rn(t.x)); t.y = __bfloat162float(__float2bfloat16_rn(t.y));
+        t.z = __bfloat162float(__float2bfloat16_rn(t.z)); t.w = __bfloat162float(__float2bfloat16_rn(t.w));
+      }
+      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+#pragma unroll
+    for (int d = 4; d < 32; d <<= 1) {
+      s.x += __shfl_xor_sync(lanes, s.x, d);
+      s.y += __shfl_xor_sync(lanes, s.y, d);
+      s.z += __shfl_xor_sync(lanes, s.z, d);
+      s.w += __shfl_xor_sync(lanes, s.w, d);
+    }
+    if ((threadIdx.x & 31) < 4) st4(p.colsum, (long long)cs_row * p.N + col, s, vec);
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -337,6 +370,7 @@ __device__ __forceinline__ bool epilogue_unit(const CtaCtx& cx, const GemmParams
           make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
     __syncwarp();
     const int col = tc.n0 + c0 + sub_chunk * 4;
+    const unsigned lanes = __ballot_sync(0xffffffffu, col < p.N);
     if (col < p.N) {
       float4 v[4];
       long long off[4];
@@ -349,7 +383,7 @@ __device__ __forceinline__ bool epilogue_unit(const CtaCtx& cx, const GemmParams
         off[i] = batch_off + (long long)row * p.ldc + col;
         ok |= (row < p.M ? 1u : 0u) << i;
       }
-      epilogue_chunk<MODE>(p, v, off, ok, col);
+      epilogue_chunk<MODE>(p, v, off, ok, col, (tc.m0 / BM) * 4 + q, lanes);
     }
     __syncwarp();
   }
@@ -637,6 +671,7 @@ gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
         __syncwarp();
         const int col = tc.n0 + c0 + sub_chunk * 4;
+        const unsigned lanes = __ballot_sync(0xffffffffu, col < p.N);
         if (col < p.N) {
           float4 v[4];
           long long off[4];
@@ -649,7 +684,7 @@ gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             off[i] = batch_off + (long long)row * p.ldc + col;
             ok |= (row < p.M ? 1u : 0u) << i;
           }
-          epilogue_chunk<MODE>(p, v, off, ok, col);
+          epilogue_chunk<MODE>(p, v, off, ok, col, (tc.m0 / BM) * 4 + q, lanes);
         }
         __syncwarp();
       }
@@ -714,6 +749,7 @@ const Specialised kSpecialised[] = {
     VKG_SPEC(E_BIAS | E_RES),                      // proj / fc2 forward: + bias + residual
     VKG_SPEC(E_BIAS | E_PRE | E_ACT | E_F16),      // fc1 forward: bias, keep z, GELU, narrow
     VKG_SPEC(E_DACT | E_F16),                      // fc2 dX: * GELU'(z), narrow
+    VKG_SPEC(E_DACT | E_F16 | E_COLSUM),           // the same + column sums = fc1's bias gradient
 };
 const int kNumSpecialised = sizeof(kSpecialised) / sizeof(kSpecialised[0]);
 #define VKG_SPEC_CP(m) {(m), gemm_cta_pair_kernel<(m)>}
@@ -866,6 +902,11 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
   p.ldc = a->ldc; p.sC0 = a->sC0; p.sC1 = a->sC1;
   p.C = a->C; p.C2 = a->C2; p.bias = a->bias; p.pre = a->pre;
   p.dact_z = a->dact_z; p.residual = a->residual;
+  if (a->colsum) {
+    VKG_REQUIRE(a->colsum_scratch && batch == 1 && a->causal == 0 && a->split_k <= 1,
+                "gemm: colsum needs colsum_scratch, one matrix, causal == 0 and an unsplit K");
+    p.colsum = a->colsum_scratch;
+  }
   p.alpha = a->alpha == 0.0f ? 1.0f : a->alpha;
   p.err = dev->err_dev;
   p.split_k = 1;
@@ -922,7 +963,8 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
   VKG_REQUIRE(out->total_tiles < (1ll << 30), "gemm: too many tiles");
   out->mode = (a->bias ? E_BIAS : 0) | (a->pre ? E_PRE : 0) | (a->act ? E_ACT : 0) |
               (a->dact_z ? E_DACT : 0) | (a->residual ? E_RES : 0) | (a->C2 ? E_C2 : 0) |
-              (a->c_dtype == VKG_F16 ? E_F16 : a->c_dtype == VKG_BF16 ? E_BF16 : 0);
+              (a->c_dtype == VKG_F16 ? E_F16 : a->c_dtype == VKG_BF16 ? E_BF16 : 0) |
+              (a->colsum ? E_COLSUM : 0);
   if (!vec) out->mode = E_GENERIC;
   return 0;
 }
@@ -960,7 +1002,23 @@ int reduce_slices(vkg_device* dev, const vkg_gemm_args* a, const GemmParams& p) 
   return vkg_check_launch("splitk_reduce");
 }
 
+// Adds the per-warp partial column sums a launch left in colsum_scratch: four rows per
+// 128-row block the kernel worked on (tile_rows = BM, or 2 * BM for CTA pairs, whose last tile
+// may add a block that lies wholly past M and holds zeros).
+int finish_colsum(vkg_device* dev, const vkg_gemm_args* a, int tile_rows) {
+  if (!a->colsum) return 0;
+  const int blocks = ((a->M + tile_rows - 1) / tile_rows) * (tile_rows / BM);
+  return vkg_launch_col_sum_final(dev, a->colsum_scratch, a->colsum, a->N, 4 * blocks, 0);
+}
+
 }  // namespace
+
+// four partial rows (one per 32-row warp slot) for every 128-row block of the M rows padded
+// to the 256-row tiles of a CTA pair
+extern "C" int64_t vkg_gemm_colsum_scratch_floats(int M, int N) {
+  if (M <= 0 || N <= 0) return 0;
+  return (int64_t)4 * 2 * ((M + 2 * BM - 1) / (2 * BM)) * N;
+}
 
 extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   if (vkg_bind(dev)) return 1;
@@ -1003,7 +1061,8 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
     cfg.numAttrs = 1;
     VKG_CUDA(cudaLaunchKernelEx(&cfg, fn, q.tmA, q.tmB, q.p));
     if (vkg_check_launch("gemm_cta_pair_kernel")) return 1;
-    return reduce_slices(dev, a, q.p);
+    if (reduce_slices(dev, a, q.p)) return 1;
+    return finish_colsum(dev, a, 2 * BM);
   }
   if (build_problem(dev, a, 0, &q)) return 1;
   if (ensure_attrs(dev)) return 1;
@@ -1011,5 +1070,6 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   if (ctas > q.total_tiles) ctas = (int)q.total_tiles;
   pick_kernel(q.mode)<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(q.tmA, q.tmB, q.p);
   if (vkg_check_launch("gemm_tcgen05_kernel")) return 1;
-  return reduce_slices(dev, a, q.p);
+  if (reduce_slices(dev, a, q.p)) return 1;
+  return finish_colsum(dev, a, BM);
 }

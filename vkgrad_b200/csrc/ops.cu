@@ -984,6 +984,13 @@ extern "C" int64_t vkg_col_sum_scratch_floats(int ncol, int nrow) {
   return (int64_t)col_sum_chunks(ncol, nrow) * ncol;
 }
 
+int vkg_launch_col_sum_final(vkg_device* dev, const float* partial, float* sums, int ncol, int nchunk,
+                             int accumulate) {
+  k_col_sum_final<<<(ncol + 31) / 32, 32 * CSF_SLICES, 0, dev->stream>>>(partial, sums, ncol, nchunk,
+                                                                         accumulate);
+  return vkg_check_launch("col_sum_final");
+}
+
 extern "C" int vkg_col_sum_det(vkg_device* dev, const void* g, int g_dtype, float* sums,
                                float* scratch, int ncol, int nrow, int accumulate) {
   if (vkg_bind(dev)) return 1;

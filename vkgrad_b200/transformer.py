@@ -146,9 +146,11 @@ class Dense:
         return out
 
     def backward(self, dy16, need_dx=True, graph=None, dx=None, dx_dtype=F32, dact_z=None,
-                 dact=ACT_NONE, bias_grad_done=False):
+                 dact=ACT_NONE, bias_grad_done=False, dx_colsum=None):
         """bias_grad_done: the producer of dy16 already wrote b.g32 (LayerNorm.backward's
-        dxsum), so the column-sum pass is skipped."""
+        dxsum, or a GEMM's dx_colsum), so the column-sum pass is skipped.
+        dx_colsum: fp32 buffer that receives the column sums of dx as stored -- the bias
+        gradient of the layer below when dx is that layer's dY."""
         c, dev = self.ctx, self.ctx.dev
         R, I, O = self.rows, self.in_f, self.out_f
         gemm(dev, self.x16, dy16, self.W.g32, I, O, R, trans_a=True, graph=graph,
@@ -159,7 +161,7 @@ class Dense:
                     self.dx32 = c.buf(R * I * 4)
                 dx, dx_dtype = self.dx32, F32
             gemm(dev, dy16, self.W.w16, dx, R, I, O, trans_b=True, graph=graph, c_dtype=dx_dtype,
-                 dact_z=dact_z, dact=dact, name=f"{self.name}.dX")
+                 dact_z=dact_z, dact=dact, colsum=dx_colsum, name=f"{self.name}.dX")
         if not bias_grad_done:
             c.col_sum(dy16, self.b.g32, O, R, graph=graph)
         return dx if need_dx else None
@@ -258,12 +260,17 @@ class Attention:
         if self.fused:
             seg_f = None if self._seg is None else self._seg.dptr
 
+            # the kernels that write dqkv also fold its column sums: the qkv bias gradient
+            scratch = c.shared_buf("attn_dbias", 4 * lib.vkg_attn_bwd_dbias_scratch_floats(
+                self.B, T, self.H, hd))
+
             def bwd():
                 _check(lib.vkg_attn_bwd(h, self.qkv16.dptr, self.dao16.dptr, self.ao16.dptr,
                                         self.lse2.dptr, seg_f, self.dqkv16.dptr, self.delta.dptr,
+                                        self.qkv.b.g32.dptr, scratch.dptr,
                                         self.B, T, self.H, hd, float(self.scale)), "attn_bwd")
             c.launch(graph, bwd, "attn_bwd", self.rows * self.D * 16)
-            return self.qkv.backward(self.dqkv16, need_dx=True, graph=graph)
+            return self.qkv.backward(self.dqkv16, need_dx=True, graph=graph, bias_grad_done=True)
         # dV = P^T dO  -> slice 2 of dqkv
         self._bgemm(self.p16, self.dao16, self.dqkv16, T, hd, T, graph, ta=True, b_merged=True,
                     c_in_qkv=2, c_dtype=F16, causal=3, name="dv")
@@ -320,9 +327,11 @@ class Block:
         fc2.b.g32.  below: the block that consumes this block's input gradient; its fc2
         bias gradient is then produced by this block's last layernorm backward."""
         # MLP branch; the residual sends the same gradient down both paths.
+        # fc2's dX is fc1's dY: its column sums are fc1's bias gradient, taken in the epilogue
         self.fc2.backward(d16, graph=graph, dx=self.dh16, dx_dtype=F16, dact_z=self.z1,
-                          dact=ACT_GELU, bias_grad_done=fc2_bias_grad_done)
-        dln2 = self.fc1.backward(self.dh16, graph=graph)
+                          dact=ACT_GELU, bias_grad_done=fc2_bias_grad_done,
+                          dx_colsum=self.fc1.b.g32)
+        dln2 = self.fc1.backward(self.dh16, graph=graph, bias_grad_done=True)
         fuse = self.ln2.can_sum_dx()
         dres1 = self.ln2.backward(dln2, graph=graph, dres=d32,
                                   dxsum=self.attn.proj.b.g32 if fuse else None)
