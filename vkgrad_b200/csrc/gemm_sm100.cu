@@ -16,6 +16,11 @@
 // and "B stored K x N" are loaded as MN-major tiles and the shared-memory /
 // instruction descriptors say so.
 //
+// Two kernels share the role code: gemm_tcgen05_kernel (128 x {64..256} tiles, one CTA
+// each) and gemm_cta_pair_kernel (256 x 256 tiles on 2-CTA clusters with
+// tcgen05.mma.cta_group::2, each CTA loading its rows of A and half of the B tile), which
+// the host picks for launches with many waves of tiles and for split-K shapes.
+//
 // Every mbarrier wait is bounded by a clock64 budget; a wait that gives up
 // sets an error word the host reads at the next synchronisation, the CTA
 // stops issuing work, frees its TMEM and returns.
