@@ -165,6 +165,13 @@ typedef struct vkg_gemm_args {
 
 int64_t vkg_gemm_colsum_scratch_floats(int M, int N);
 
+/* No reference counterpart.  Launches a one-thread kernel that waits, with the bounded wait
+ * all tcgen05 / TMA kernels of this library use, on an mbarrier nothing arrives on, for at
+ * most budget_cycles (<= 1e8) SM cycles.  The wait gives up, the kernel returns normally, and
+ * the next vkg_sync reports the timeout like it would for a real kernel; the device stays
+ * usable.  For tests of the failure path. */
+int vkg_selftest_wait_timeout(vkg_device* dev, int64_t budget_cycles);
+
 int vkg_gemm(vkg_device* dev, const vkg_gemm_args* args);
 
 

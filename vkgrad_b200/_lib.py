@@ -79,6 +79,7 @@ _SIGNATURES = {
     "vkg_graph_kernel_count": (i32, [vp, C.POINTER(i32)]),
     "vkg_gemm": (i32, [vp, C.POINTER(GemmArgs)]),
     "vkg_gemm_colsum_scratch_floats": (i64, [i32, i32]),
+    "vkg_selftest_wait_timeout": (i32, [vp, i64]),
     "vkg_bias_act": (i32, [vp, vp, vp, vp, vp, i64, i32, i32]),
     "vkg_bias_act_bwd": (i32, [vp, vp, vp, vp, vp, i64, i32]),
     "vkg_bias": (i32, [vp, vp, vp, vp, i64, i32]),

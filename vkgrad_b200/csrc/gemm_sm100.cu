@@ -1007,6 +1007,20 @@ int reduce_slices(vkg_device* dev, const vkg_gemm_args* a, const GemmParams& p) 
   return vkg_check_launch("splitk_reduce");
 }
 
+// A barrier that nothing ever arrives on, waited for with the kernels' own bounded wait and a
+// small budget: the error path every device-side wait takes when its partner never shows up
+// (flag the abort, record where, return), without a fault and with the context intact.
+__global__ void k_wait_selftest(uint32_t* err, long long budget) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0u;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait<true>(smem_u32(&bar), 0, &abort_flag, err, 0x5e1fu, budget);
+  }
+}
+
 // Adds the per-warp partial column sums a launch left in colsum_scratch: four rows per
 // 128-row block the kernel worked on (tile_rows = BM, or 2 * BM for CTA pairs, whose last tile
 // may add a block that lies wholly past M and holds zeros).
@@ -1023,6 +1037,14 @@ int finish_colsum(vkg_device* dev, const vkg_gemm_args* a, int tile_rows) {
 extern "C" int64_t vkg_gemm_colsum_scratch_floats(int M, int N) {
   if (M <= 0 || N <= 0) return 0;
   return (int64_t)4 * 2 * ((M + 2 * BM - 1) / (2 * BM)) * N;
+}
+
+extern "C" int vkg_selftest_wait_timeout(vkg_device* dev, int64_t budget_cycles) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(budget_cycles > 0 && budget_cycles <= 100000000ll,
+              "selftest: budget must be between 1 and 1e8 cycles");
+  k_wait_selftest<<<1, 32, 0, dev->stream>>>(dev->err_dev, (long long)budget_cycles);
+  return vkg_check_launch("wait_selftest");
 }
 
 extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {

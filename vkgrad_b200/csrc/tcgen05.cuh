@@ -56,9 +56,12 @@ __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity
 
 // Bounded wait.  Returns false when the wait gave up or another role already
 // flagged an abort; the caller then leaves its loop.  SPIN polls instead of suspending.
+// `budget` is the clock64 allowance (the kernels use WAIT_BUDGET_CYCLES; the wait self-test
+// a millisecond's worth).
 template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* err, uint32_t where) {
+                                          uint32_t* err, uint32_t where,
+                                          long long budget = WAIT_BUDGET_CYCLES) {
   if (SPIN ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   uint32_t spins = 0;
@@ -66,7 +69,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (SPIN ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1u;
         if (atomicCAS(err, 0u, VKG_ERR_WAIT_TIMEOUT) == 0u) err[1] = where;
         __threadfence_system();
