@@ -165,6 +165,18 @@ typedef struct vkg_gemm_args {
 
 int64_t vkg_gemm_colsum_scratch_floats(int M, int N);
 
+/* Many independent plain GEMMs (fp32 output, unbatched, no epilogue extras) in ONE launch: the
+ * dW = X^T dY of every Linear of a model (autograd.py:217-219, transformer.py:97-98), which
+ * have too few tiles each to fill the GPU and thousands together.  Results are those of
+ * vkg_gemm on each problem with split_k = 1, bit for bit.  vkg_gemm_group_prepare builds the
+ * launch table in device memory the caller owns (vkg_gemm_group_table_bytes(n) bytes, 128-byte
+ * aligned; synchronous, so before any stream capture; operand pointers are baked in);
+ * vkg_gemm_group_launch enqueues the launch and may be captured. */
+int64_t vkg_gemm_group_table_bytes(int n);
+int vkg_gemm_group_prepare(vkg_device* dev, const vkg_gemm_args* args, int n, void* table,
+                           int* total_units);
+int vkg_gemm_group_launch(vkg_device* dev, const void* table, int n, int total_units);
+
 /* No reference counterpart.  Launches a one-thread kernel that waits, with the bounded wait
  * all tcgen05 / TMA kernels of this library use, on an mbarrier nothing arrives on, for at
  * most budget_cycles (<= 1e8) SM cycles.  The wait gives up, the kernel returns normally, and

@@ -414,3 +414,37 @@ def test_bounded_wait_reports_and_leaves_the_device_usable(dev):
     assert relerr(down(dev, bc, np.float32, (m, n)), orc.matmul16(a, b)) < TOL
     for x in (ba, bb, bc):
         x.destroy()
+
+
+def test_grouped_dw_launch_equals_separate_launches(dev):
+    """vkg_gemm_group: the dW = X^T dY of several Linears in one launch must give, bit for bit,
+    what one unsplit vkg_gemm per Linear gives, and match the oracle."""
+    from vkgrad_b200.kernels import gemm, gemm_group
+    rows = 1024
+    shapes = [(768, 2304), (768, 768), (768, 3072), (3072, 768), (200, 264)]   # (in, out)
+    rng = np.random.default_rng(9)
+    xs = [rng.standard_normal((rows, i)).astype(np.float16) for i, _ in shapes]
+    dys = [rng.standard_normal((rows, o)).astype(np.float16) for _, o in shapes]
+    bx = [up(dev, x) for x in xs]
+    bdy = [up(dev, d) for d in dys]
+    res = []
+    for grouped in (False, True):
+        outs = [dev.buffer(i * o * 4, "cached") for i, o in shapes]
+        for b in outs:
+            b.array(np.uint8)[:] = 0xFF
+            b.flush()
+        probs = [(bx[j], bdy[j], outs[j], i, o, rows, dict(trans_a=True))
+                 for j, (i, o) in enumerate(shapes)]
+        if grouped:
+            gemm_group(dev, probs)
+        else:
+            for pr in probs:
+                gemm(dev, *pr[:6], split_k=1, cta_pair=-1, **pr[6])
+        res.append([down(dev, outs[j], np.float32, shapes[j]) for j in range(len(shapes))])
+        for b in outs:
+            b.destroy()
+    for j in range(len(shapes)):
+        assert np.array_equal(res[0][j], res[1][j]), shapes[j]
+        assert relerr(res[1][j], orc.matmul16(xs[j], dys[j], True, False)) < TOL
+    for b in bx + bdy:
+        b.destroy()

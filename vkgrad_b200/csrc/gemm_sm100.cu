@@ -503,6 +503,74 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   cta_teardown(cx);
 }
 
+// ---- grouped launch ------------------------------------------------------------------------
+//
+// Many independent GEMMs of the same tile width in one persistent launch: the dW = X^T dY of
+// every Linear of a model, which have few tiles each (18..72 against 148 SMs) but thousands
+// together.  Their tiles form one list, CTA b takes list entries b, b + gridDim.x, ...; with
+// equal K (the rows of the batch) all entries cost the same, so the SMs stay level without
+// splitting K and without a reduction pass.  The table lives in device memory: tensor maps,
+// kernel parameters and the index of each problem's first list entry.
+struct __align__(128) GroupEntry {
+  CUtensorMap tmA, tmB;
+  GemmParams p;
+  int first_unit;
+};
+constexpr int GROUP_MAX = 256;   // problems per launch (their first_unit values sit in shared memory)
+
+// problem that list entry u belongs to: the last one whose first_unit is <= u
+__device__ __forceinline__ int group_find(const int* first, int n, int u) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (first[mid] <= u) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_group_kernel(const GroupEntry* __restrict__ table, int n_problems, int total_units, int bn,
+                  int stages) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ int first[GROUP_MAX];
+  for (int i = threadIdx.x; i < n_problems; i += blockDim.x) first[i] = table[i].first_unit;
+  CtaCtx cx;
+  cta_setup(cx, smem_raw, bn, stages);     // its __syncthreads also publishes first[]
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+        const int pi = group_find(first, n_problems, u);
+        const GemmParams p = table[pi].p;
+        if (!produce_unit(cx, p, &table[pi].tmA, &table[pi].tmB, u - first[pi], stage, phase)) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+        const int pi = group_find(first, n_problems, u);
+        const GemmParams p = table[pi].p;
+        if (!mma_unit(cx, p, u - first[pi], stage, phase, acc, acc_phase)) break;
+      }
+    }
+  } else {
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+      const int pi = group_find(first, n_problems, u);
+      const GemmParams p = table[pi].p;
+      if (!epilogue_unit<0>(cx, p, u - first[pi], warp, lane, acc, acc_phase)) break;
+    }
+  }
+  cta_teardown(cx);
+}
+
 // ---- CTA pairs -----------------------------------------------------------------------------
 //
 // 256 x 256 tiles on a 2-CTA cluster: each CTA loads its 128 rows of A and its 128 of the
@@ -1053,6 +1121,66 @@ extern "C" int vkg_selftest_wait_timeout(vkg_device* dev, int64_t budget_cycles)
               "selftest: budget must be between 1 and 1e8 cycles");
   k_wait_selftest<<<1, 32, 0, dev->stream>>>(dev->err_dev, (long long)budget_cycles);
   return vkg_check_launch("wait_selftest");
+}
+
+extern "C" int64_t vkg_gemm_group_table_bytes(int n) {
+  return n > 0 ? (int64_t)n * (int64_t)sizeof(GroupEntry) : 0;
+}
+
+// Builds the table of a grouped launch in `table` (device memory, 128-byte aligned,
+// vkg_gemm_group_table_bytes(n) bytes).  Synchronous: call it outside a stream capture.
+extern "C" int vkg_gemm_group_prepare(vkg_device* dev, const vkg_gemm_args* args, int n, void* table,
+                                      int* total_units) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(args && table && total_units && n > 0 && n <= GROUP_MAX,
+              "gemm_group: between 1 and %d problems and a table", GROUP_MAX);
+  VKG_REQUIRE(((uintptr_t)table & 127) == 0, "gemm_group: table must be 128-byte aligned");
+  VKG_REQUIRE(!dev->capturing, "gemm_group: prepare the table before the stream capture begins");
+  std::vector<GroupEntry> host(n);
+  long long units = 0;
+  for (int i = 0; i < n; ++i) {
+    const vkg_gemm_args* a = &args[i];
+    const int nb = (a->nb0 > 0 ? a->nb0 : 1) * (a->nb1 > 0 ? a->nb1 : 1);
+    VKG_REQUIRE(nb == 1 && a->causal == 0 && !a->bias && !a->pre && !a->act && !a->dact_z &&
+                    !a->residual && !a->C2 && !a->colsum && a->c_dtype == VKG_F32 &&
+                    (a->alpha == 0.0f || a->alpha == 1.0f),
+                "gemm_group: problem %d is not a plain fp32-output, unbatched GEMM", i);
+    VKG_REQUIRE(a->in_dtype == args[0].in_dtype, "gemm_group: operand types differ");
+    vkg_gemm_args one = *a;
+    one.split_k = 1;
+    one.workspace = nullptr;
+    one.workspace_bytes = 0;
+    Problem q;
+    if (build_problem(dev, &one, 256, &q)) return 1;
+    VKG_REQUIRE(q.mode == 0, "gemm_group: problem %d needs 16-byte aligned rows", i);
+    memset(&host[i], 0, sizeof(GroupEntry));
+    host[i].tmA = q.tmA;
+    host[i].tmB = q.tmB;
+    host[i].p = q.p;
+    host[i].first_unit = (int)units;
+    units += q.total_tiles;
+    VKG_REQUIRE(units < (1ll << 30), "gemm_group: too many tiles");
+  }
+  VKG_CUDA(cudaMemcpy(table, host.data(), (size_t)n * sizeof(GroupEntry), cudaMemcpyHostToDevice));
+  *total_units = (int)units;
+  return 0;
+}
+
+extern "C" int vkg_gemm_group_launch(vkg_device* dev, const void* table, int n, int total_units) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(table && n > 0 && n <= GROUP_MAX && total_units > 0, "gemm_group: bad arguments");
+  if (ensure_attrs(dev)) return 1;
+  static bool attr_set = false;
+  if (!attr_set) {
+    VKG_CUDA(cudaFuncSetAttribute(gemm_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  SMEM_BYTES));
+    attr_set = true;
+  }
+  int ctas = dev->sm_count < total_units ? dev->sm_count : total_units;
+  const int stages = RING_BYTES / (A_STAGE_BYTES + 256 * 128);
+  gemm_group_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(
+      static_cast<const GroupEntry*>(table), n, total_units, 256, stages);
+  return vkg_check_launch("gemm_group_kernel");
 }
 
 extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {

@@ -124,6 +124,38 @@ def gemm(dev, a, b, c, m, n, k, trans_a=False, trans_b=False, graph=None, repeat
     return dev.run_op(go, repeat)
 
 
+def gemm_group(dev, problems, graph=None, repeat=1, name="gemm_group"):
+    """Many independent plain GEMMs in one launch (vkg_gemm_group_*): `problems` is a list of
+    (a, b, c, m, n, k, kwargs) as for gemm(), fp32 outputs without epilogue extras.  Used for
+    the dW of every Linear of a model (autograd.py:217-219): few tiles each, thousands
+    together.  The launch table is built here, once; the returned thunk only launches."""
+    n = len(problems)
+    arr = (GemmArgs * n)()
+    keep = []
+    for i, pr in enumerate(problems):
+        args = _gemm_args(dev, *pr[:6], **dict(pr[6], split_k=1))
+        keep.append(args)
+        C.memmove(C.byref(arr, i * C.sizeof(GemmArgs)), C.byref(args), C.sizeof(GemmArgs))
+    lib, h = dev.lib, dev.handle
+    table = dev.buffer(lib.vkg_gemm_group_table_bytes(n), "device")
+    units = C.c_int32(0)
+    _check(lib.vkg_gemm_group_prepare(h, arr, n, table.dptr, C.byref(units)), f"{name} prepare")
+
+    def go():
+        _check(lib.vkg_gemm_group_launch(h, table.dptr, n, units.value), name)
+
+    go.table = table       # lives as long as the recorded launch
+    if graph is not None:
+        total = 0
+        for args in keep:
+            m, nn, k = args.M, args.N, args.K
+            total += 2 * m * k + 2 * k * nn + 4 * m * nn
+            graph.mm_split.append((2 * (m * k + k * nn), 4 * m * nn))
+        graph.add(go, name, total)
+        return 0.0
+    return dev.run_op(go, repeat)
+
+
 class Matmul:
     """One matmul configuration (kernels.py:232-315).
 

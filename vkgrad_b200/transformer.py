@@ -28,12 +28,13 @@ import numpy as np
 
 from ._lib import ACT_GELU, ACT_NONE, F16, F32
 from .autograd import Ctx, Param
-from .kernels import gemm
+from .kernels import gemm, gemm_group
 from .tkernels import make_transformer_kernels
 from .vk import _check
 
 NCHUNK = 32  # kept for callers that pass it to col_sum_chunk (transformer.py:20)
 CAUSAL_BLOCK = 128  # row-tile height of the GEMM: where its causal K ranges stop
+GROUP_DW = True        # GPT.record issues the dW GEMMs of all blocks as one grouped launch
 FUSED_HEAD_DIM = 64  # head size the fused attention kernels are written for
 _LN_FUSED_MAX_D = 1536  # shared-memory limit of the fused dgamma/dbeta reduction
 
@@ -146,15 +147,20 @@ class Dense:
         return out
 
     def backward(self, dy16, need_dx=True, graph=None, dx=None, dx_dtype=F32, dact_z=None,
-                 dact=ACT_NONE, bias_grad_done=False, dx_colsum=None):
+                 dact=ACT_NONE, bias_grad_done=False, dx_colsum=None, dw_sink=None):
         """bias_grad_done: the producer of dy16 already wrote b.g32 (LayerNorm.backward's
         dxsum, or a GEMM's dx_colsum), so the column-sum pass is skipped.
         dx_colsum: fp32 buffer that receives the column sums of dx as stored -- the bias
-        gradient of the layer below when dx is that layer's dY."""
+        gradient of the layer below when dx is that layer's dY.
+        dw_sink: a list; the dW GEMM is appended to it instead of being launched, for one
+        grouped launch over all layers (the caller keeps x16 and dy16 intact until then)."""
         c, dev = self.ctx, self.ctx.dev
         R, I, O = self.rows, self.in_f, self.out_f
-        gemm(dev, self.x16, dy16, self.W.g32, I, O, R, trans_a=True, graph=graph,
-             name=f"{self.name}.dW")
+        if dw_sink is not None:
+            dw_sink.append((self.x16, dy16, self.W.g32, I, O, R, dict(trans_a=True)))
+        else:
+            gemm(dev, self.x16, dy16, self.W.g32, I, O, R, trans_a=True, graph=graph,
+                 name=f"{self.name}.dW")
         if need_dx:
             if dx is None:
                 if self.dx32 is None:
@@ -251,12 +257,12 @@ class Attention:
                     c_dtype=F16, causal=2, name="pv")
         return self.proj.forward(self.ao16, graph=graph, out=out, residual=residual)
 
-    def backward(self, dy16, graph=None, proj_bias_grad_done=False):
+    def backward(self, dy16, graph=None, proj_bias_grad_done=False, dw_sink=None):
         """dy16: gradient of the projection's output.  Returns d(ln1 output), fp32."""
         c, lib, h = self.ctx, self.ctx.dev.lib, self.ctx.dev.handle
         T, hd = self.T, self.hd
         self.proj.backward(dy16, need_dx=True, graph=graph, dx=self.dao16, dx_dtype=F16,
-                           bias_grad_done=proj_bias_grad_done)
+                           bias_grad_done=proj_bias_grad_done, dw_sink=dw_sink)
         if self.fused:
             seg_f = None if self._seg is None else self._seg.dptr
 
@@ -270,7 +276,8 @@ class Attention:
                                         self.qkv.b.g32.dptr, scratch.dptr,
                                         self.B, T, self.H, hd, float(self.scale)), "attn_bwd")
             c.launch(graph, bwd, "attn_bwd", self.rows * self.D * 16)
-            return self.qkv.backward(self.dqkv16, need_dx=True, graph=graph, bias_grad_done=True)
+            return self.qkv.backward(self.dqkv16, need_dx=True, graph=graph, bias_grad_done=True,
+                                     dw_sink=dw_sink)
         # dV = P^T dO  -> slice 2 of dqkv
         self._bgemm(self.p16, self.dao16, self.dqkv16, T, hd, T, graph, ta=True, b_merged=True,
                     c_in_qkv=2, c_dtype=F16, causal=3, name="dv")
@@ -288,7 +295,7 @@ class Attention:
                     c_dtype=F16, causal=2, name="dq")
         self._bgemm(self.ds16, self.qkv16, self.dqkv16, T, hd, T, graph, ta=True, b_in_qkv=0,
                     c_in_qkv=1, c_dtype=F16, causal=3, name="dk")
-        return self.qkv.backward(self.dqkv16, need_dx=True, graph=graph)
+        return self.qkv.backward(self.dqkv16, need_dx=True, graph=graph, dw_sink=dw_sink)
 
 
 class Block:
@@ -308,7 +315,8 @@ class Block:
         self.res2 = ctx.buf(self.rows * D * 4)
         self.z1 = ctx.buf(self.rows * 4 * D * 4)
         self.h16 = ctx.buf(self.rows * 4 * D * 2)
-        self.dh16 = ctx.shared_buf("mlp_dh16", self.rows * 4 * D * 2)
+        # fc1's dY: kept per block, the grouped dW launch at the end of the backward reads it
+        self.dh16 = ctx.buf(self.rows * 4 * D * 2)
 
     def forward(self, x32, graph=None, seg=None):
         self.x32 = x32
@@ -319,7 +327,7 @@ class Block:
         self.fc2.forward(self.h16, graph=graph, out=self.res2, residual=self.res1)
         return self.res2
 
-    def backward(self, d32, d16, graph=None, fc2_bias_grad_done=False, below=None):
+    def backward(self, d32, d16, graph=None, fc2_bias_grad_done=False, below=None, dw_sink=None):
         """d32/d16: gradient of the block output in both precisions.
         Returns the gradient of the block input as (fp32, fp16).
 
@@ -330,13 +338,14 @@ class Block:
         # fc2's dX is fc1's dY: its column sums are fc1's bias gradient, taken in the epilogue
         self.fc2.backward(d16, graph=graph, dx=self.dh16, dx_dtype=F16, dact_z=self.z1,
                           dact=ACT_GELU, bias_grad_done=fc2_bias_grad_done,
-                          dx_colsum=self.fc1.b.g32)
-        dln2 = self.fc1.backward(self.dh16, graph=graph, bias_grad_done=True)
+                          dx_colsum=self.fc1.b.g32, dw_sink=dw_sink)
+        dln2 = self.fc1.backward(self.dh16, graph=graph, bias_grad_done=True, dw_sink=dw_sink)
         fuse = self.ln2.can_sum_dx()
         dres1 = self.ln2.backward(dln2, graph=graph, dres=d32,
                                   dxsum=self.attn.proj.b.g32 if fuse else None)
         # attention branch
-        dln1 = self.attn.backward(self.ln2.dx16, graph=graph, proj_bias_grad_done=fuse)
+        dln1 = self.attn.backward(self.ln2.dx16, graph=graph, proj_bias_grad_done=fuse,
+                                  dw_sink=dw_sink)
         dx = self.ln1.backward(dln1, graph=graph, dres=dres1,
                                dxsum=below.fc2.b.g32 if (below is not None and fuse) else None)
         return dx, self.ln1.dx16
@@ -458,11 +467,17 @@ class GPT:
         fuse = self.lnf.can_sum_dx() and L > 0
         d32 = self.lnf.backward(d, graph=gh, dxsum=self.blocks[-1].fc2.b.g32 if fuse else None)
         d16 = self.lnf.dx16
+        # the blocks' dW GEMMs (4 per block, 18..72 tiles each) are collected and issued as
+        # one grouped launch once every dY exists
+        dw_sink = [] if GROUP_DW and L > 0 else None
         for k in range(L):
             i = L - 1 - k
             d32, d16 = self.blocks[i].backward(d32, d16, graph=g(L + 2 + k), fc2_bias_grad_done=fuse,
-                                               below=self.blocks[i - 1] if i > 0 else None)
+                                               below=self.blocks[i - 1] if i > 0 else None,
+                                               dw_sink=dw_sink)
         ge = g(2 * L + 2)
+        if dw_sink:
+            gemm_group(c.dev, dw_sink, graph=ge, name="blocks.dW")
         seg_p = None if seg is None else seg.dptr
 
         def emb_bwd():
