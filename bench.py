@@ -193,7 +193,7 @@ def gemm_shape_table(B, T, D, H, L, V, fused_attention=True):
     t = []
     for (i, o) in ((D, 3 * D), (D, D), (D, 4 * D), (4 * D, D)):
         t.append((L, dict(m=R, n=o, k=i, ta=False, tb=False)))          # Y  = X W
-        t.append((L, dict(m=i, n=o, k=R, ta=True, tb=False)))           # dW = X^T dY
+        t.append((L, dict(m=i, n=o, k=R, ta=True, tb=False, grouped=True)))   # dW = X^T dY
         t.append((L, dict(m=R, n=i, k=o, ta=False, tb=True)))           # dX = dY W^T
     if not fused_attention:
         nb = B * H
@@ -259,9 +259,33 @@ def fill_random16(dev, buf, scale=1.0):
 
 def time_gemm_shapes(dev, table):
     """CUDA-event time of each shape (back-to-back launches on the device stream)."""
-    from vkgrad_b200.kernels import gemm
+    from vkgrad_b200.kernels import gemm, gemm_group
     total_t, total_f, rows = 0.0, 0.0, []
+    # the blocks' dW GEMMs run as ONE grouped launch in the step: time them that way, every
+    # problem on its own operands
+    grouped = [(count, s) for count, s in table if s.get("grouped")]
+    if grouped:
+        probs, bufs, fl = [], [], 0.0
+        for count, s in grouped:
+            m, n, k = s["m"], s["n"], s["k"]
+            for _ in range(count):
+                a, b, c = dev.buffer(m * k * 2, "device"), dev.buffer(k * n * 2, "device"), \
+                    dev.buffer(m * n * 4, "device")
+                fill_random16(dev, a)
+                fill_random16(dev, b)
+                bufs += [a, b, c]
+                probs.append((a, b, c, m, n, k, dict(trans_a=True)))
+                fl += 2.0 * m * n * k
+        gemm_group(dev, probs, repeat=2)
+        t = min(gemm_group(dev, probs, repeat=5) / 5 for _ in range(3))
+        rows.append({"grouped_dw_problems": len(probs), "us": t * 1e6, "tflops": fl / t / 1e12})
+        total_t += t
+        total_f += fl
+        for x in bufs:
+            x.destroy()
     for count, s in table:
+        if s.get("grouped"):
+            continue
         nb = s.get("nb", 1)
         m, n, k = s["m"], s["n"], s["k"]
         a = dev.buffer(nb * m * k * 2, "device")
@@ -522,7 +546,8 @@ def run_gpu_arm(args):
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": 66.1e6, "peak_source": peak_src,
-                         "kernel": "gemm_tcgen05_kernel (all its launches in one step)",
+                         "kernel": "gemm_tcgen05_kernel, gemm_cta_pair_kernel and gemm_group_kernel "
+                                   "(all their launches in one step)",
                          "traffic_note": "ncu dram read+write bytes of ONE launch of the "
                                          "8192x3072x768 fp32-out shape (algorithmic minimum 118 MB; "
                                          "the output largely stays in L2); see profiles/",
