@@ -1193,12 +1193,12 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
                        (a->tile_n == 0 || a->tile_n == PAIR_BN) && a->max_ctas == 0;
   bool use_pair = pair_ok && a->cta_pair > 0;
   if (pair_ok && a->cta_pair == 0) {
-    // Measured on B200: CTA-pair tiles are about 10 % faster on launches with many waves of
+    // Measured on B200: CTA-pair tiles are about 10 % faster on launches with six or more waves of
     // them (the vocabulary-sized GEMMs) and on few-tile dW shapes whose K is split; with a
     // handful of waves they time the same alone and a little slower inside a training step,
     // and with one wave and a bit they lose.
     if (build_problem(dev, a, 0, &q, true)) return 1;
-    use_pair = q.p.split_k > 1 || q.total_tiles >= 8ll * (dev->sm_count / 2);
+    use_pair = q.p.split_k > 1 || q.total_tiles >= 6ll * (dev->sm_count / 2);
   }
   if (use_pair) {
     if (build_problem(dev, a, 0, &q, true)) return 1;

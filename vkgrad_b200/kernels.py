@@ -35,7 +35,7 @@ CONFIGS = [(sg, wm, wn, lds)
            if sg * 32 <= 1024 and wm * wn <= 16]
 
 TILE_N_CHOICES = (64, 128, 192, 256)
-SPLIT_K_MAX_TILE_BYTES = 16 << 20   # outputs larger than this already fill the GPU
+SPLIT_K_MAX_TILE_BYTES = 32 << 20   # outputs larger than this already fill the GPU
 
 
 def _ptr(buf):
