@@ -170,11 +170,13 @@ int64_t vkg_gemm_colsum_scratch_floats(int M, int N);
  * have too few tiles each to fill the GPU and thousands together.  Results are those of
  * vkg_gemm on each problem with split_k = 1, bit for bit.  vkg_gemm_group_prepare builds the
  * launch table in device memory the caller owns (vkg_gemm_group_table_bytes(n) bytes, 128-byte
- * aligned; synchronous, so before any stream capture; operand pointers are baked in);
- * vkg_gemm_group_launch enqueues the launch and may be captured. */
+ * aligned; synchronous, so before any stream capture; operand pointers are baked in) and
+ * returns in *total_units the value to hand to vkg_gemm_group_launch, which enqueues the
+ * launch and may be captured.  cta_pair > 0 asks for 256 x 256 tiles on 2-CTA clusters (used
+ * when every problem has more than 128 rows; *total_units is then negative). */
 int64_t vkg_gemm_group_table_bytes(int n);
 int vkg_gemm_group_prepare(vkg_device* dev, const vkg_gemm_args* args, int n, void* table,
-                           int* total_units);
+                           int cta_pair, int* total_units);
 int vkg_gemm_group_launch(vkg_device* dev, const void* table, int n, int total_units);
 
 /* No reference counterpart.  Launches a one-thread kernel that waits, with the bounded wait

@@ -416,12 +416,15 @@ def test_bounded_wait_reports_and_leaves_the_device_usable(dev):
         x.destroy()
 
 
-def test_grouped_dw_launch_equals_separate_launches(dev):
+@pytest.mark.parametrize("pair", [-1, 1])
+def test_grouped_dw_launch_equals_separate_launches(dev, pair):
     """vkg_gemm_group: the dW = X^T dY of several Linears in one launch must give, bit for bit,
     what one unsplit vkg_gemm per Linear gives, and match the oracle."""
     from vkgrad_b200.kernels import gemm, gemm_group
     rows = 1024
     shapes = [(768, 2304), (768, 768), (768, 3072), (3072, 768), (200, 264)]   # (in, out)
+    if pair < 0:
+        shapes.append((72, 136))       # a single row block: only without CTA pairs
     rng = np.random.default_rng(9)
     xs = [rng.standard_normal((rows, i)).astype(np.float16) for i, _ in shapes]
     dys = [rng.standard_normal((rows, o)).astype(np.float16) for _, o in shapes]
@@ -436,7 +439,7 @@ def test_grouped_dw_launch_equals_separate_launches(dev):
         probs = [(bx[j], bdy[j], outs[j], i, o, rows, dict(trans_a=True))
                  for j, (i, o) in enumerate(shapes)]
         if grouped:
-            gemm_group(dev, probs)
+            gemm_group(dev, probs, cta_pair=pair)
         else:
             for pr in probs:
                 gemm(dev, *pr[:6], split_k=1, cta_pair=-1, **pr[6])

@@ -81,7 +81,7 @@ _SIGNATURES = {
     "vkg_gemm_colsum_scratch_floats": (i64, [i32, i32]),
     "vkg_selftest_wait_timeout": (i32, [vp, i64]),
     "vkg_gemm_group_table_bytes": (i64, [i32]),
-    "vkg_gemm_group_prepare": (i32, [vp, C.POINTER(GemmArgs), i32, vp, C.POINTER(i32)]),
+    "vkg_gemm_group_prepare": (i32, [vp, C.POINTER(GemmArgs), i32, vp, i32, C.POINTER(i32)]),
     "vkg_gemm_group_launch": (i32, [vp, vp, i32, i32]),
     "vkg_bias_act": (i32, [vp, vp, vp, vp, vp, i64, i32, i32]),
     "vkg_bias_act_bwd": (i32, [vp, vp, vp, vp, vp, i64, i32]),

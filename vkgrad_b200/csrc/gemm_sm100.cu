@@ -585,19 +585,10 @@ constexpr int PAIR_B_STAGE_BYTES = (PAIR_BN / 2) * 128;
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;
 constexpr int PAIR_STAGES = RING_BYTES / PAIR_STAGE_BYTES;   // 6
 
-template <int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const GemmParams p) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
+// Barriers, TMEM and constants of one CTA of a pair; ends with a cluster-wide barrier so the
+// peer's mbarriers exist before anything is signalled on them.
+__device__ __forceinline__ void pair_setup(CtaCtx& cx, uint8_t* smem_raw) {
   const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  if (threadIdx.x == 0) {
-    prefetch_tensormap(&tmA);
-    prefetch_tensormap(&tmB);
-  }
-  CtaCtx cx;
   cx.base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (cx.base - smem_u32(smem_raw));
   cx.stage_bytes = PAIR_STAGE_BYTES;
@@ -638,150 +629,12 @@ gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   tcgen05_fence_after();
   cx.tmem_base = *tmem_slot;
 
-  const int n_pairs = (int)gridDim.x >> 1, pair = (int)blockIdx.x >> 1;
-  const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * (p.split_k > 1 ? p.split_k : p.nb1);
-  const int m_off = (int)rank * BM;
+}
 
-  if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
-        TileCoord tc = tile_coord(p, t, 2 * BM, m_off);
-        int kb0, nkb;
-        kb_range(p, tc, kb0, nkb);
-        if (p.split_k > 1) tc.z1 = 0;
-        const int nb = tc.n0 + (int)rank * (PAIR_BN / 2);    // this CTA's columns of B
-        for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(cx.empty0 + 8 * stage, phase ^ 1u, cx.abort_flag, p.err, 0x500u + stage)) {
-            ok = false;
-            break;
-          }
-          if (rank == 0) mbar_expect_tx(cx.full0 + 8 * stage, 2 * PAIR_STAGE_BYTES);
-          const uint32_t fb = mapa_shared(cx.full0 + 8 * stage, 0);
-          const uint32_t sa = cx.base + stage * PAIR_STAGE_BYTES;
-          const uint32_t sb = sa + A_STAGE_BYTES;
-          const int k0 = (kb0 + kb) * BK;
-          if (!p.a_mn) {
-            tma_load_4d_pair(sa, &tmA, fb, k0, tc.m0, tc.z0, tc.z1);
-          } else {
-            tma_load_4d_pair(sa, &tmA, fb, tc.m0, k0, tc.z0, tc.z1);
-            tma_load_4d_pair(sa + 8192, &tmA, fb, tc.m0 + 64, k0, tc.z0, tc.z1);
-          }
-          if (!p.b_mn) {
-            tma_load_4d_pair(sb, &tmB, fb, k0, nb, tc.z0, tc.z1);
-          } else {
-            tma_load_4d_pair(sb, &tmB, fb, nb, k0, tc.z0, tc.z1);
-            tma_load_4d_pair(sb + 8192, &tmB, fb, nb + 64, k0, tc.z0, tc.z1);
-          }
-          if (++stage == PAIR_STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
-      bool ok = true;
-      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
-        int kb0, nkb;
-        kb_range(p, tile_coord(p, t, 2 * BM, 0), kb0, nkb);
-        if (nkb <= 0) continue;
-        if (!mbar_wait(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x600u + acc)) break;
-        tcgen05_fence_after();
-        const uint32_t d_tmem = cx.tmem_base + (uint32_t)(acc * ACC_COLS);
-        for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x700u + stage)) {
-            ok = false;
-            break;
-          }
-          tcgen05_fence_after();
-          const uint32_t sa = cx.base + stage * PAIR_STAGE_BYTES;
-          const uint32_t sb = sa + A_STAGE_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            uint64_t ad = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024)
-                                 : make_smem_desc(sa + k * 32, 16, 1024);
-            uint64_t bd = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024)
-                                 : make_smem_desc(sb + k * 32, 16, 1024);
-            umma2_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
-          }
-          umma2_commit(cx.empty0 + 8 * stage);
-          if (++stage == PAIR_STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-        if (!ok) break;
-        umma2_commit(cx.tfull0 + 8 * acc);
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
-      }
-    }
-  } else {
-    const int q = warp & 3;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    for (int t = pair; t < total_tiles; t += n_pairs) {
-      TileCoord tc = tile_coord(p, t, 2 * BM, m_off);
-      {
-        int kb0, nkb;
-        kb_range(p, tc, kb0, nkb);
-        if (nkb <= 0) continue;
-      }
-      if (!mbar_wait(cx.tfull0 + 8 * acc, acc_phase, cx.abort_flag, p.err, 0x800u + acc)) break;
-      tcgen05_fence_after();
-      uint8_t* stage = cx.epi_stage + (warp - 2) * EPI_STAGE_BYTES;
-      const int sub_row = lane >> 2;
-      const int sub_chunk = lane & 3;
-      const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
-      const int row_base = tc.m0 + q * 32;
-      const uint32_t t_row = cx.tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
-      for (int c0 = 16 * ((warp - 2) >> 2); c0 < PAIR_BN; c0 += 64) {
-        if (tc.n0 + c0 >= p.N) break;
-        uint32_t r[16];
-        tmem_ld16(t_row + c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
-              make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        __syncwarp();
-        const int col = tc.n0 + c0 + sub_chunk * 4;
-        const unsigned lanes = __ballot_sync(0xffffffffu, col < p.N);
-        if (col < p.N) {
-          float4 v[4];
-          long long off[4];
-          unsigned ok = 0;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int rr = 8 * i + sub_row;
-            const int row = row_base + rr;
-            v[i] = *reinterpret_cast<const float4*>(stage + rr * 64 + ((sub_chunk ^ ((rr >> 1) & 3)) << 4));
-            off[i] = batch_off + (long long)row * p.ldc + col;
-            ok |= (row < p.M ? 1u : 0u) << i;
-          }
-          epilogue_chunk<MODE>(p, v, off, ok, col, (tc.m0 / BM) * 4 + q, lanes);
-        }
-        __syncwarp();
-      }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (rank == 0) mbar_arrive(cx.tempty0 + 8 * acc);
-        else mbar_arrive_cluster(mapa_shared(cx.tempty0 + 8 * acc, 0));
-      }
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
-    }
-  }
-
-  // Neither CTA may leave while the other can still read its shared memory or signal its
-  // barriers.
+// Neither CTA may leave while the other can still read its shared memory or signal its
+// barriers.
+__device__ __forceinline__ void pair_teardown(const CtaCtx& cx) {
+  const int warp = threadIdx.x >> 5;
   __syncwarp();
   tcgen05_fence_before();
   __syncthreads();
@@ -797,6 +650,219 @@ gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                  "r"((uint32_t)TMEM_COLS)
                  : "memory");
   }
+}
+
+// TMA producer of one CTA of the pair: its 128 rows of A and its half of the B tile.
+__device__ __forceinline__ bool pair_produce_unit(const CtaCtx& cx, const GemmParams& p,
+                                                  const CUtensorMap* tmA, const CUtensorMap* tmB,
+                                                  int t, uint32_t rank, int& stage, uint32_t& phase) {
+  TileCoord tc = tile_coord(p, t, 2 * BM, (int)rank * BM);
+  int kb0, nkb;
+  kb_range(p, tc, kb0, nkb);
+  if (p.split_k > 1) tc.z1 = 0;
+  const int nb = tc.n0 + (int)rank * (PAIR_BN / 2);    // this CTA's columns of B
+  for (int kb = 0; kb < nkb; ++kb) {
+    if (!mbar_wait(cx.empty0 + 8 * stage, phase ^ 1u, cx.abort_flag, p.err, 0x500u + stage)) return false;
+    if (rank == 0) mbar_expect_tx(cx.full0 + 8 * stage, 2 * PAIR_STAGE_BYTES);
+    const uint32_t fb = mapa_shared(cx.full0 + 8 * stage, 0);
+    const uint32_t sa = cx.base + stage * PAIR_STAGE_BYTES;
+    const uint32_t sb = sa + A_STAGE_BYTES;
+    const int k0 = (kb0 + kb) * BK;
+    if (!p.a_mn) {
+      tma_load_4d_pair(sa, tmA, fb, k0, tc.m0, tc.z0, tc.z1);
+    } else {
+      tma_load_4d_pair(sa, tmA, fb, tc.m0, k0, tc.z0, tc.z1);
+      tma_load_4d_pair(sa + 8192, tmA, fb, tc.m0 + 64, k0, tc.z0, tc.z1);
+    }
+    if (!p.b_mn) {
+      tma_load_4d_pair(sb, tmB, fb, k0, nb, tc.z0, tc.z1);
+    } else {
+      tma_load_4d_pair(sb, tmB, fb, nb, k0, tc.z0, tc.z1);
+      tma_load_4d_pair(sb + 8192, tmB, fb, nb + 64, k0, tc.z0, tc.z1);
+    }
+    if (++stage == PAIR_STAGES) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+  return true;
+}
+
+// MMA issue for the pair (one lane of the even-ranked CTA).
+__device__ __forceinline__ bool pair_mma_unit(const CtaCtx& cx, const GemmParams& p, int t, int& stage,
+                                              uint32_t& phase, int& acc, uint32_t& acc_phase) {
+  int kb0, nkb;
+  kb_range(p, tile_coord(p, t, 2 * BM, 0), kb0, nkb);
+  if (nkb <= 0) return true;
+  if (!mbar_wait(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x600u + acc)) return false;
+  tcgen05_fence_after();
+  const uint32_t d_tmem = cx.tmem_base + (uint32_t)(acc * ACC_COLS);
+  for (int kb = 0; kb < nkb; ++kb) {
+    if (!mbar_wait(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x700u + stage)) return false;
+    tcgen05_fence_after();
+    const uint32_t sa = cx.base + stage * PAIR_STAGE_BYTES;
+    const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+    for (int k = 0; k < BK / UMMA_K; ++k) {
+      uint64_t ad = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                           : make_smem_desc(sa + k * 32, 16, 1024);
+      uint64_t bd = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                           : make_smem_desc(sb + k * 32, 16, 1024);
+      umma2_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+    }
+    umma2_commit(cx.empty0 + 8 * stage);
+    if (++stage == PAIR_STAGES) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+  umma2_commit(cx.tfull0 + 8 * acc);
+  acc ^= 1;
+  if (acc == 0) acc_phase ^= 1u;
+  return true;
+}
+
+// Epilogue warp of one CTA of the pair: its 128 rows of the 256 x 256 tile.
+template <int MODE>
+__device__ __forceinline__ bool pair_epilogue_unit(const CtaCtx& cx, const GemmParams& p, int t,
+                                                   uint32_t rank, int warp, int lane, int& acc,
+                                                   uint32_t& acc_phase) {
+  const int q = warp & 3;
+  const TileCoord tc = tile_coord(p, t, 2 * BM, (int)rank * BM);
+  {
+    int kb0, nkb;
+    kb_range(p, tc, kb0, nkb);
+    if (nkb <= 0) return true;
+  }
+  if (!mbar_wait(cx.tfull0 + 8 * acc, acc_phase, cx.abort_flag, p.err, 0x800u + acc)) return false;
+  tcgen05_fence_after();
+  uint8_t* stage = cx.epi_stage + (warp - 2) * EPI_STAGE_BYTES;
+  const int sub_row = lane >> 2;
+  const int sub_chunk = lane & 3;
+  const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
+  const int row_base = tc.m0 + q * 32;
+  const uint32_t t_row = cx.tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+  for (int c0 = 16 * ((warp - 2) >> 2); c0 < PAIR_BN; c0 += 64) {
+    if (tc.n0 + c0 >= p.N) break;
+    uint32_t r[16];
+    tmem_ld16(t_row + c0, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+          make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    __syncwarp();
+    const int col = tc.n0 + c0 + sub_chunk * 4;
+    const unsigned lanes = __ballot_sync(0xffffffffu, col < p.N);
+    if (col < p.N) {
+      float4 v[4];
+      long long off[4];
+      unsigned ok = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rr = 8 * i + sub_row;
+        const int row = row_base + rr;
+        v[i] = *reinterpret_cast<const float4*>(stage + rr * 64 + ((sub_chunk ^ ((rr >> 1) & 3)) << 4));
+        off[i] = batch_off + (long long)row * p.ldc + col;
+        ok |= (row < p.M ? 1u : 0u) << i;
+      }
+      epilogue_chunk<MODE>(p, v, off, ok, col, (tc.m0 / BM) * 4 + q, lanes);
+    }
+    __syncwarp();
+  }
+  tcgen05_fence_before();
+  __syncwarp();
+  if (lane == 0) {
+    if (rank == 0) mbar_arrive(cx.tempty0 + 8 * acc);
+    else mbar_arrive_cluster(mapa_shared(cx.tempty0 + 8 * acc, 0));
+  }
+  acc ^= 1;
+  if (acc == 0) acc_phase ^= 1u;
+  return true;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  CtaCtx cx;
+  pair_setup(cx, smem_raw);
+  const int n_pairs = (int)gridDim.x >> 1, pair = (int)blockIdx.x >> 1;
+  const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * (p.split_k > 1 ? p.split_k : p.nb1);
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = pair; t < total_tiles; t += n_pairs)
+        if (!pair_produce_unit(cx, p, &tmA, &tmB, t, rank, stage, phase)) break;
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int t = pair; t < total_tiles; t += n_pairs)
+        if (!pair_mma_unit(cx, p, t, stage, phase, acc, acc_phase)) break;
+    }
+  } else {
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < total_tiles; t += n_pairs)
+      if (!pair_epilogue_unit<MODE>(cx, p, t, rank, warp, lane, acc, acc_phase)) break;
+  }
+  pair_teardown(cx);
+}
+
+// The grouped launch on CTA pairs: list entries are 256 x 256 tiles.
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_group_pair_kernel(const GroupEntry* __restrict__ table, int n_problems, int total_units) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ int first[GROUP_MAX];
+  for (int i = threadIdx.x; i < n_problems; i += blockDim.x) first[i] = table[i].first_unit;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  CtaCtx cx;
+  pair_setup(cx, smem_raw);       // its __syncthreads also publishes first[]
+  const int n_pairs = (int)gridDim.x >> 1, pair = (int)blockIdx.x >> 1;
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int u = pair; u < total_units; u += n_pairs) {
+        const int pi = group_find(first, n_problems, u);
+        const GemmParams p = table[pi].p;
+        if (!pair_produce_unit(cx, p, &table[pi].tmA, &table[pi].tmB, u - first[pi], rank, stage, phase))
+          break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int u = pair; u < total_units; u += n_pairs) {
+        const int pi = group_find(first, n_problems, u);
+        const GemmParams p = table[pi].p;
+        if (!pair_mma_unit(cx, p, u - first[pi], stage, phase, acc, acc_phase)) break;
+      }
+    }
+  } else {
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int u = pair; u < total_units; u += n_pairs) {
+      const int pi = group_find(first, n_problems, u);
+      const GemmParams p = table[pi].p;
+      if (!pair_epilogue_unit<0>(cx, p, u - first[pi], rank, warp, lane, acc, acc_phase)) break;
+    }
+  }
+  pair_teardown(cx);
 }
 
 // Adds the K slices of a split GEMM in slice order and writes C (fp32, row pitch ldc).
@@ -1130,7 +1196,7 @@ extern "C" int64_t vkg_gemm_group_table_bytes(int n) {
 // Builds the table of a grouped launch in `table` (device memory, 128-byte aligned,
 // vkg_gemm_group_table_bytes(n) bytes).  Synchronous: call it outside a stream capture.
 extern "C" int vkg_gemm_group_prepare(vkg_device* dev, const vkg_gemm_args* args, int n, void* table,
-                                      int* total_units) {
+                                      int cta_pair, int* total_units) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(args && table && total_units && n > 0 && n <= GROUP_MAX,
               "gemm_group: between 1 and %d problems and a table", GROUP_MAX);
@@ -1138,6 +1204,9 @@ extern "C" int vkg_gemm_group_prepare(vkg_device* dev, const vkg_gemm_args* args
   VKG_REQUIRE(!dev->capturing, "gemm_group: prepare the table before the stream capture begins");
   std::vector<GroupEntry> host(n);
   long long units = 0;
+  // CTA-pair tiles (256 x 256) when asked for and every problem has more than one row block
+  bool use_pair = cta_pair > 0 && dev->sm_count >= 2;
+  for (int i = 0; i < n && use_pair; ++i) use_pair = args[i].M > BM && args[i].N >= PAIR_BN / 2;
   for (int i = 0; i < n; ++i) {
     const vkg_gemm_args* a = &args[i];
     const int nb = (a->nb0 > 0 ? a->nb0 : 1) * (a->nb1 > 0 ? a->nb1 : 1);
@@ -1151,7 +1220,7 @@ extern "C" int vkg_gemm_group_prepare(vkg_device* dev, const vkg_gemm_args* args
     one.workspace = nullptr;
     one.workspace_bytes = 0;
     Problem q;
-    if (build_problem(dev, &one, 256, &q)) return 1;
+    if (build_problem(dev, &one, 256, &q, use_pair)) return 1;
     VKG_REQUIRE(q.mode == 0, "gemm_group: problem %d needs 16-byte aligned rows", i);
     memset(&host[i], 0, sizeof(GroupEntry));
     host[i].tmA = q.tmA;
@@ -1162,19 +1231,44 @@ extern "C" int vkg_gemm_group_prepare(vkg_device* dev, const vkg_gemm_args* args
     VKG_REQUIRE(units < (1ll << 30), "gemm_group: too many tiles");
   }
   VKG_CUDA(cudaMemcpy(table, host.data(), (size_t)n * sizeof(GroupEntry), cudaMemcpyHostToDevice));
-  *total_units = (int)units;
+  // a negative count tells vkg_gemm_group_launch that the entries are CTA-pair tiles
+  *total_units = use_pair ? -(int)units : (int)units;
   return 0;
 }
 
 extern "C" int vkg_gemm_group_launch(vkg_device* dev, const void* table, int n, int total_units) {
   if (vkg_bind(dev)) return 1;
-  VKG_REQUIRE(table && n > 0 && n <= GROUP_MAX && total_units > 0, "gemm_group: bad arguments");
+  VKG_REQUIRE(table && n > 0 && n <= GROUP_MAX && total_units != 0, "gemm_group: bad arguments");
   if (ensure_attrs(dev)) return 1;
   static bool attr_set = false;
   if (!attr_set) {
     VKG_CUDA(cudaFuncSetAttribute(gemm_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   SMEM_BYTES));
+    VKG_CUDA(cudaFuncSetAttribute(gemm_group_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  SMEM_BYTES));
     attr_set = true;
+  }
+  if (total_units < 0) {
+    const int units = -total_units;
+    int pairs = dev->sm_count / 2;
+    if (pairs > units) pairs = units;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr;
+    memset(&attr, 0, sizeof(attr));
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    VKG_CUDA(cudaLaunchKernelEx(&cfg, gemm_group_pair_kernel, static_cast<const GroupEntry*>(table), n,
+                                units));
+    return vkg_check_launch("gemm_group_pair_kernel");
   }
   int ctas = dev->sm_count < total_units ? dev->sm_count : total_units;
   const int stages = RING_BYTES / (A_STAGE_BYTES + 256 * 128);

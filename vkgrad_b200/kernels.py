@@ -124,7 +124,7 @@ def gemm(dev, a, b, c, m, n, k, trans_a=False, trans_b=False, graph=None, repeat
     return dev.run_op(go, repeat)
 
 
-def gemm_group(dev, problems, graph=None, repeat=1, name="gemm_group"):
+def gemm_group(dev, problems, graph=None, repeat=1, name="gemm_group", cta_pair=1):
     """Many independent plain GEMMs in one launch (vkg_gemm_group_*): `problems` is a list of
     (a, b, c, m, n, k, kwargs) as for gemm(), fp32 outputs without epilogue extras.  Used for
     the dW of every Linear of a model (autograd.py:217-219): few tiles each, thousands
@@ -139,7 +139,8 @@ def gemm_group(dev, problems, graph=None, repeat=1, name="gemm_group"):
     lib, h = dev.lib, dev.handle
     table = dev.buffer(lib.vkg_gemm_group_table_bytes(n), "device")
     units = C.c_int32(0)
-    _check(lib.vkg_gemm_group_prepare(h, arr, n, table.dptr, C.byref(units)), f"{name} prepare")
+    _check(lib.vkg_gemm_group_prepare(h, arr, n, table.dptr, int(cta_pair), C.byref(units)),
+           f"{name} prepare")
 
     def go():
         _check(lib.vkg_gemm_group_launch(h, table.dptr, n, units.value), name)
