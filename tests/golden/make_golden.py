@@ -124,7 +124,9 @@ def flatten_grads(G, L):
 
 
 def main():
-    ref_path = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python make_golden.py <path to a checkout of the reference>")
+    ref_path = sys.argv[1]
     rk, rta, rtt, rh = import_reference(ref_path)
 
     mm = {}
