@@ -429,9 +429,10 @@ def run_gpu_arm(args):
     dev.copy(ids_host, ids_dev, R * 4)
     dev.copy(tgt_host, tgt_dev, R * 4)
 
-    core = DataParallelStep(rep, ids_dev, tgt_dev, name="step_resident")
+    core = DataParallelStep(rep, ids_dev, tgt_dev, name="step_resident",
+                            overlap_chunks=args.overlap_chunks)
     e2e = DataParallelStep(rep, ids_dev, tgt_dev, host_ids=ids_host, host_targets=tgt_host,
-                           name="step_e2e")
+                           name="step_e2e", overlap_chunks=args.overlap_chunks)
     lr = 6e-4
 
     def barrier():
@@ -580,6 +581,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gpt2-small", choices=sorted(WORKLOADS))
     ap.add_argument("--loss-scale", type=float, default=4096.0)
+    ap.add_argument("--overlap-chunks", type=int, default=1,
+                    help="N>1: parts the gradient all-reduce is cut into and overlapped with AdamW "
+                         "(1 = one all-reduce, then AdamW)")
     ap.add_argument("--cta-pair", type=int, default=0,
                     help="with --gemm: 1 = 256x256 tiles on CTA pairs, -1 = never, 0 = library's choice")
     ap.add_argument("--max-ctas", type=int, default=0, help="with --gemm: cap the persistent grid")

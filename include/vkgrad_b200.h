@@ -358,6 +358,15 @@ int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint8_t id[128]
 int vkg_comm_destroy(vkg_comm* comm);
 /* In-place sum over ranks of `count` elements of dtype, on the device stream. */
 int vkg_allreduce_sum(vkg_comm* comm, void* buf, int64_t count, int dtype);
+/* The same all-reduce on a second stream, so that the optimiser can update one part of the
+ * gradient bucket while the next part is still being summed (the reference's step_from_arena,
+ * dataparallel.py:131-144, runs pull and AdamW strictly after the push).  side_begin orders the
+ * side stream after everything enqueued on the device's stream so far; allreduce_sum_side
+ * enqueues there and marks its end with event `slot` (0..15); side_wait makes the device's
+ * stream wait for that event.  Not for use inside a stream capture. */
+int vkg_comm_side_begin(vkg_comm* comm);
+int vkg_allreduce_sum_side(vkg_comm* comm, void* buf, int64_t count, int dtype, int slot);
+int vkg_comm_side_wait(vkg_comm* comm, int slot);
 /* max over ranks of one host double (timing), and a barrier. */
 int vkg_comm_max_double(vkg_comm* comm, double* value);
 int vkg_comm_barrier(vkg_comm* comm);

@@ -150,3 +150,28 @@ def test_bench_reference_arm_line_shape(monkeypatch, capsys):
     assert line["impl"] == "reference" and line["cpu_baseline"]["kind"] == "port"
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["value"] > 0
     assert line["cpu_baseline"]["cores"] == os.cpu_count()
+
+
+def test_bucket_chunks_cover_the_bucket_on_tensor_boundaries():
+    """The parts the gradient bucket is all-reduced in are contiguous, end on tensor
+    boundaries, cover every float once and keep every parameter in exactly one part."""
+    from vkgrad_b200.dataparallel import _bucket_chunks
+    sizes = [38608896, 786432] + [768, 768, 1769472, 2304, 589824, 768, 2359296, 3072] * 12 + [768, 768]
+    offs, off = [], 0
+    for n in sizes:
+        offs.append(off)
+        off += (n + 3) // 4 * 4
+    params = list(range(len(sizes)))
+    for k in (1, 2, 6, 16, 1000):
+        parts = _bucket_chunks(params, offs, off, k)
+        assert 1 <= len(parts) <= max(k, 1)
+        assert parts[0][0] == 0 and sum(c for _, c, _ in parts) == off
+        seen = []
+        for (first, count, ps), nxt in zip(parts, parts[1:] + [None]):
+            assert count > 0 and ps
+            assert first == offs[ps[0]]
+            if nxt is not None:
+                assert first + count == nxt[0]
+            seen += ps
+        assert seen == params
+    assert _bucket_chunks(params[:1], offs[:1], 40, 6) == [(0, 40, params[:1])]

@@ -124,6 +124,9 @@ _SIGNATURES = {
     "vkg_comm_create": (i32, [vp, i32, i32, C.POINTER(C.c_uint8), C.POINTER(vp)]),
     "vkg_comm_destroy": (i32, [vp]),
     "vkg_allreduce_sum": (i32, [vp, vp, i64, i32]),
+    "vkg_comm_side_begin": (i32, [vp]),
+    "vkg_allreduce_sum_side": (i32, [vp, vp, i64, i32, i32]),
+    "vkg_comm_side_wait": (i32, [vp, i32]),
     "vkg_comm_max_double": (i32, [vp, C.POINTER(C.c_double)]),
     "vkg_comm_barrier": (i32, [vp]),
 }

@@ -356,8 +356,7 @@ class AdamW:
         self.grad_scale = 0.0
         self.hp = ctx.buf(8 * 4, "shared")
         self.hpv = self.hp.array(np.float32)
-        self._table = None
-        self._table_key = None
+        self._tables = {}
         self._set_hp(lr)
 
     def _set_hp(self, lr):
@@ -370,33 +369,36 @@ class AdamW:
         self.t += 1
         self._set_hp(self.lr if lr is None else lr)
 
-    def _get_table(self):
-        key = tuple((p.w32.dptr, p.g32.dptr, p.m.dptr, p.v.dptr, p.w16.dptr) for p in self.params)
-        if self._table is not None and key == self._table_key:
-            return self._table
+    def _get_table(self, params):
+        key = tuple((p.w32.dptr, p.g32.dptr, p.m.dptr, p.v.dptr, p.w16.dptr) for p in params)
+        if key in self._tables:
+            return self._tables[key]
         d = self.ctx.dev
-        n = len(self.params)
+        n = len(params)
         arr = lambda vals: (C.c_void_p * n)(*vals)
-        sizes = (C.c_int64 * n)(*[p.n for p in self.params])
-        wds = (C.c_float * n)(*[0.0 if p.no_decay else self.wd for p in self.params])
+        sizes = (C.c_int64 * n)(*[p.n for p in params])
+        wds = (C.c_float * n)(*[0.0 if p.no_decay else self.wd for p in params])
         t = C.c_void_p()
         _check(d.lib.vkg_adamw_table_create(
             d.handle, n, arr([k[0] for k in key]), arr([k[1] for k in key]),
             arr([k[2] for k in key]), arr([k[3] for k in key]), arr([k[4] for k in key]),
             sizes, wds, C.byref(t)), "adamw_table")
-        self._table, self._table_key = t, key   # an older table stays alive for its graphs
+        self._tables[key] = t      # tables of older pointer sets stay alive for their graphs
         return t
 
-    def record(self, graph):
-        self._launch(graph)
+    def record(self, graph, params=None):
+        """params: update only these (a subset of the optimiser's parameters, e.g. one part of
+        a gradient bucket whose all-reduce has finished); default all."""
+        self._launch(graph, params)
 
-    def _launch(self, graph):
+    def _launch(self, graph, params=None):
         d = self.ctx.dev
-        table = self._get_table()
+        params = self.params if params is None else list(params)
+        table = self._get_table(params)
 
         def go():
             _check(d.lib.vkg_adamw_multi(d.handle, table, self.hp.dptr), "adamw")
-        self.ctx.launch(graph, go, "adamw_multi", 30 * sum(p.n for p in self.params))
+        self.ctx.launch(graph, go, "adamw_multi", 30 * sum(p.n for p in params))
 
     def step(self, lr=None):
         """Eager step."""

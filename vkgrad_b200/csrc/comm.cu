@@ -61,11 +61,18 @@ int load_nccl() {
 
 }  // namespace
 
+constexpr int VKG_COMM_SLOTS = 16;
+
 struct vkg_comm {
   vkg_device* dev = nullptr;
   ncclComm_t comm = nullptr;
   int rank = 0, nranks = 1;
   double* scratch_dev = nullptr;
+  // a second stream for collectives that run beside the compute stream, and the events that
+  // order the two (created at first use)
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr;
+  cudaEvent_t ev_done[VKG_COMM_SLOTS] = {};
 };
 
 #define VKG_NCCL(expr)                                                              \
@@ -129,6 +136,13 @@ extern "C" int vkg_comm_destroy(vkg_comm* comm) {
   if (!comm) return 0;
   if (comm->dev) cudaSetDevice(comm->dev->ordinal);
   if (comm->dev) cudaStreamSynchronize(comm->dev->stream);
+  if (comm->side) {
+    cudaStreamSynchronize(comm->side);
+    for (int i = 0; i < VKG_COMM_SLOTS; ++i)
+      if (comm->ev_done[i]) cudaEventDestroy(comm->ev_done[i]);
+    if (comm->ev_fork) cudaEventDestroy(comm->ev_fork);
+    cudaStreamDestroy(comm->side);
+  }
   if (comm->scratch_dev) cudaFree(comm->scratch_dev);
   if (comm->comm) g_nccl.CommDestroy(comm->comm);
   delete comm;
@@ -141,6 +155,50 @@ extern "C" int vkg_allreduce_sum(vkg_comm* comm, void* buf, int64_t count, int d
   int t = dtype == VKG_F32 ? NCCL_FLOAT32 : dtype == VKG_F16 ? NCCL_FLOAT16 : dtype == VKG_BF16 ? NCCL_BFLOAT16 : -1;
   VKG_REQUIRE(t >= 0, "allreduce: unknown dtype %d", dtype);
   VKG_NCCL(g_nccl.AllReduce(buf, buf, (size_t)count, t, NCCL_SUM, comm->comm, comm->dev->stream));
+  return 0;
+}
+
+// ---- collectives beside the compute stream -------------------------------------------------
+//
+// vkg_comm_side_begin: everything enqueued on the device's stream so far happens before what
+// follows on the side stream.  vkg_allreduce_sum_side: the all-reduce on the side stream;
+// `slot` names the event that marks its end.  vkg_comm_side_wait: the device's stream waits
+// for that event -- so the optimiser can update one part of the bucket while the next part
+// is still being reduced.
+static int side_init(vkg_comm* comm) {
+  if (comm->side) return 0;
+  VKG_CUDA(cudaStreamCreateWithFlags(&comm->side, cudaStreamNonBlocking));
+  VKG_CUDA(cudaEventCreateWithFlags(&comm->ev_fork, cudaEventDisableTiming));
+  for (int i = 0; i < VKG_COMM_SLOTS; ++i)
+    VKG_CUDA(cudaEventCreateWithFlags(&comm->ev_done[i], cudaEventDisableTiming));
+  return 0;
+}
+
+extern "C" int vkg_comm_side_begin(vkg_comm* comm) {
+  VKG_REQUIRE(comm, "comm_side_begin: null communicator");
+  if (vkg_bind(comm->dev)) return 1;
+  if (side_init(comm)) return 1;
+  VKG_CUDA(cudaEventRecord(comm->ev_fork, comm->dev->stream));
+  VKG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_fork, 0));
+  return 0;
+}
+
+extern "C" int vkg_allreduce_sum_side(vkg_comm* comm, void* buf, int64_t count, int dtype, int slot) {
+  VKG_REQUIRE(comm && buf && count > 0 && slot >= 0 && slot < VKG_COMM_SLOTS,
+              "allreduce_side: bad arguments (slot 0..%d)", VKG_COMM_SLOTS - 1);
+  if (vkg_bind(comm->dev)) return 1;
+  if (side_init(comm)) return 1;
+  int t = dtype == VKG_F32 ? NCCL_FLOAT32 : dtype == VKG_F16 ? NCCL_FLOAT16 : dtype == VKG_BF16 ? NCCL_BFLOAT16 : -1;
+  VKG_REQUIRE(t >= 0, "allreduce_side: unknown dtype %d", dtype);
+  VKG_NCCL(g_nccl.AllReduce(buf, buf, (size_t)count, t, NCCL_SUM, comm->comm, comm->side));
+  VKG_CUDA(cudaEventRecord(comm->ev_done[slot], comm->side));
+  return 0;
+}
+
+extern "C" int vkg_comm_side_wait(vkg_comm* comm, int slot) {
+  VKG_REQUIRE(comm && comm->side && slot >= 0 && slot < VKG_COMM_SLOTS, "comm_side_wait: bad arguments");
+  if (vkg_bind(comm->dev)) return 1;
+  VKG_CUDA(cudaStreamWaitEvent(comm->dev->stream, comm->ev_done[slot], 0));
   return 0;
 }
 
