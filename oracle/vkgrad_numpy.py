@@ -335,3 +335,67 @@ def make_gpt_params(D, H, n_layer, T, pad_vocab, seed=0, std=0.02, bias_std=0.0,
         P["head.W"] = nrm(D, pad_vocab)
         P["head.b"] = bias(pad_vocab)
     return P
+
+
+# -- GPT-2 forward from a Hugging Face state dict (test_hf_gpt2.py:33-66) ----------------
+
+def gpt2_logits(W, H, ids):
+    """Logits (n, vocab) of GPT-2 for one sequence of n token ids, straight from tensors
+    under GPT2Model names (wte.weight, h.<i>.attn.c_attn.weight, ...): Conv1D is
+    x @ weight + bias with weight (in, out); c_attn yields q, k, v in that order; a head is
+    a contiguous slice of D/H columns; tanh GELU; layernorm eps 1e-5; the head is wte^T.
+    Deliberately independent of the name mapping the package's loader uses."""
+    ids = np.asarray(ids).astype(np.int64)
+    n = len(ids)
+    wte = np.asarray(W["wte.weight"], np.float64)
+    D = wte.shape[1]
+    hd = D // H
+    get = lambda name: np.asarray(W[name], np.float64)
+    norm = lambda x, name: layernorm_fwd(x, get(name + ".weight"), get(name + ".bias"))[0]
+    lin = lambda x, name: x @ get(name + ".weight") + get(name + ".bias")
+    causal = np.tril(np.ones((n, n), dtype=bool))
+    x = wte[ids] + get("wpe.weight")[:n]
+    i = 0
+    while f"h.{i}.ln_1.weight" in W:
+        pre = f"h.{i}."
+        qkv = lin(norm(x, pre + "ln_1"), pre + "attn.c_attn")
+        q, k, v = (qkv[:, j * D:(j + 1) * D].reshape(n, H, hd).transpose(1, 0, 2) for j in range(3))
+        s = np.where(causal, (q @ k.transpose(0, 2, 1)) / np.sqrt(hd), -np.inf)
+        p = np.exp(s - s.max(axis=-1, keepdims=True))
+        p = p / p.sum(axis=-1, keepdims=True)
+        x = x + lin((p @ v).transpose(1, 0, 2).reshape(n, D), pre + "attn.c_proj")
+        x = x + lin(gelu(lin(norm(x, pre + "ln_2"), pre + "mlp.c_fc")), pre + "mlp.c_proj")
+        i += 1
+    return norm(x, "ln_f") @ wte.T
+
+
+def perplexity(logits, ids):
+    """exp(mean next-token cross entropy) of logits (n, vocab) on ids (n,)
+    (test_hf_gpt2.py:69-73)."""
+    lg = np.asarray(logits[:-1], np.float64)
+    top = lg.max(axis=-1, keepdims=True)
+    lse = top[:, 0] + np.log(np.exp(lg - top).sum(axis=-1))
+    nxt = np.asarray(ids)[1:]
+    return float(np.exp((lse - lg[np.arange(len(nxt)), nxt]).mean()))
+
+
+def make_hf_gpt2_tensors(D, H, n_layer, n_ctx, vocab, seed=0, std=0.08, prefix="", dtype=np.float32):
+    """A synthetic GPT-2 state dict under Hugging Face names (a stand-in for the real
+    checkpoints, which are not available offline): weights N(0, std), layernorm gains
+    1 + N(0, 0.1), biases N(0, 0.1); includes the attn.bias mask buffers real files carry."""
+    rng = np.random.default_rng(seed)
+    nrm = lambda *s, sd=std: (rng.standard_normal(s) * sd).astype(dtype)
+    W = {"wte.weight": nrm(vocab, D), "wpe.weight": nrm(n_ctx, D)}
+    for i in range(n_layer):
+        p = f"h.{i}."
+        for ln in ("ln_1", "ln_2"):
+            W[p + ln + ".weight"] = (1 + nrm(D, sd=0.1)).astype(dtype)
+            W[p + ln + ".bias"] = nrm(D, sd=0.1)
+        for name, (fi, fo) in (("attn.c_attn", (D, 3 * D)), ("attn.c_proj", (D, D)),
+                               ("mlp.c_fc", (D, 4 * D)), ("mlp.c_proj", (4 * D, D))):
+            W[p + name + ".weight"] = nrm(fi, fo)
+            W[p + name + ".bias"] = nrm(fo, sd=0.1)
+        W[p + "attn.bias"] = np.tril(np.ones((1, 1, n_ctx, n_ctx), np.uint8))
+    W["ln_f.weight"] = (1 + nrm(D, sd=0.1)).astype(dtype)
+    W["ln_f.bias"] = nrm(D, sd=0.1)
+    return {prefix + k: v for k, v in W.items()}

@@ -10,6 +10,8 @@ the reference's numpy functions are executed:
   test_autograd.numpy_forward_backward     (test_autograd.py:21-46)
   test_transformer.np_model                (test_transformer.py:38-151)
   examples.hetero_mnist.cpu_backward       (examples/hetero_mnist.py:38-68)
+  test_hf_gpt2.ref_logits, perplexity      (test_hf_gpt2.py:33-73)
+  hf_gpt2.read_safetensors                 (hf_gpt2.py:36-59; reads tiny_gpt2.safetensors back)
 
 Inputs come from numpy seeds with the same draws the reference's tests make
 (test_kernels.py:10-16, test_autograd.py:53-75, test_transformer.py:222-243),
@@ -48,7 +50,9 @@ def import_reference(path):
     import test_autograd as ref_test_autograd
     import test_transformer as ref_test_transformer
     from examples import hetero_mnist as ref_hetero
-    return ref_kernels, ref_test_autograd, ref_test_transformer, ref_hetero
+    import hf_gpt2 as ref_hf
+    import test_hf_gpt2 as ref_test_hf
+    return ref_kernels, ref_test_autograd, ref_test_transformer, ref_hetero, ref_hf, ref_test_hf
 
 
 def digest(*arrays):
@@ -112,6 +116,21 @@ def gpt_inputs(name):
     return dict(B=B, T=T, D=D, H=H, L=L, vocab=vocab, pad_vocab=pad_vocab, tie=tie), P, ids, tgt, seg, w
 
 
+HF_CASES = {  # name: (D, H, n_layer, n_ctx, vocab, tokens in the prompt)
+    "hf_small": (32, 2, 2, 32, 80, 24),
+    "hf_hd64": (128, 2, 2, 128, 96, 100),   # head dimension 64: the fused attention kernels
+}
+
+
+def hf_inputs(name):
+    """Synthetic GPT-2 state dict under Hugging Face names and a prompt (stand-ins for the
+    real checkpoint and the tokenised paragraph of test_hf_gpt2.py:20-30)."""
+    D, H, L, n_ctx, vocab, n = HF_CASES[name]
+    W = orc.make_hf_gpt2_tensors(D, H, L, n_ctx, vocab, seed=21)
+    ids = np.random.default_rng(22).integers(0, vocab, n)
+    return dict(D=D, H=H, n_layer=L, n_ctx=n_ctx, vocab=vocab), W, ids
+
+
 def flatten_grads(G, L):
     out = {}
     for k, v in G.items():
@@ -127,7 +146,7 @@ def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: python make_golden.py <path to a checkout of the reference>")
     ref_path = sys.argv[1]
-    rk, rta, rtt, rh = import_reference(ref_path)
+    rk, rta, rtt, rh, rhf, rthf = import_reference(ref_path)
 
     mm = {}
     for i, (m, n, k, ta, tb) in enumerate(MATMUL_CASES):
@@ -167,6 +186,29 @@ def main():
         flat["inputs_digest"] = np.array([digest(ids, tgt, P["tok"], P["b0"]["qkv.W"])], np.uint64)
         np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **flat)
         print(f"{name}: loss {loss:.6f}, {len(flat) - 2} gradient tensors")
+    hf = {}
+    for name in HF_CASES:
+        cfg, W, ids = hf_inputs(name)
+        logits = rthf.ref_logits(W, cfg["H"], ids)
+        hf[f"{name}_logits"] = logits.astype(np.float32)
+        hf[f"{name}_ppl"] = np.array([rthf.perplexity(logits, ids)], np.float64)
+        hf[f"{name}_in"] = np.array([digest(ids, W["wte.weight"], W["h.1.mlp.c_fc.weight"])], np.uint64)
+        print(f"{name}: logits {logits.shape}, perplexity {hf[f'{name}_ppl'][0]:.4f}")
+    np.savez_compressed(os.path.join(HERE, "hf_gpt2.npz"), **hf)
+
+    # a checkpoint file written by this repo's writer and read back by the reference's reader
+    from vkgrad_b200 import hf_gpt2 as our_hf
+    tiny = orc.make_hf_gpt2_tensors(32, 2, 1, 16, 48, seed=23, prefix="transformer.")
+    tiny["lm_head.weight"] = tiny["transformer.wte.weight"].copy()   # tied, as CodeGPT ships it
+    path = os.path.join(HERE, "tiny_gpt2.safetensors")
+    our_hf.write_safetensors(path, tiny, metadata={"format": "pt"})
+    back = rhf.read_safetensors(path)
+    assert set(back) == set(tiny)
+    assert all(back[k].dtype == tiny[k].dtype and np.array_equal(back[k], tiny[k]) for k in tiny)
+    stripped = rhf.gpt2_tensors(path)
+    assert "lm_head.weight" not in stripped and "h.0.attn.bias" not in stripped
+    print(f"tiny_gpt2.safetensors: {os.path.getsize(path)} bytes, {len(back)} tensors, "
+          f"{len(stripped)} after the reference's gpt2_tensors")
     print("fixtures written to", HERE)
 
 
