@@ -12,6 +12,7 @@ the reference's numpy functions are executed:
   examples.hetero_mnist.cpu_backward       (examples/hetero_mnist.py:38-68)
   test_hf_gpt2.ref_logits, perplexity      (test_hf_gpt2.py:33-73)
   hf_gpt2.read_safetensors                 (hf_gpt2.py:36-59; reads tiny_gpt2.safetensors back)
+  examples.train_lm.encode                 (examples/train_lm.py:60-67)
 
 Inputs come from numpy seeds with the same draws the reference's tests make
 (test_kernels.py:10-16, test_autograd.py:53-75, test_transformer.py:222-243),
@@ -52,7 +53,9 @@ def import_reference(path):
     from examples import hetero_mnist as ref_hetero
     import hf_gpt2 as ref_hf
     import test_hf_gpt2 as ref_test_hf
-    return ref_kernels, ref_test_autograd, ref_test_transformer, ref_hetero, ref_hf, ref_test_hf
+    from examples import train_lm as ref_lm
+    return (ref_kernels, ref_test_autograd, ref_test_transformer, ref_hetero, ref_hf, ref_test_hf,
+            ref_lm)
 
 
 def digest(*arrays):
@@ -131,6 +134,12 @@ def hf_inputs(name):
     return dict(D=D, H=H, n_layer=L, n_ctx=n_ctx, vocab=vocab), W, ids
 
 
+def lm_bytes(n=8192, seed=31):
+    """Bytes with a skewed, text-like frequency profile (more distinct values than ids)."""
+    rng = np.random.default_rng(seed)
+    return np.clip(rng.normal(100, 22, n), 0, 255).astype(np.uint8)
+
+
 def flatten_grads(G, L):
     out = {}
     for k, v in G.items():
@@ -146,7 +155,7 @@ def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: python make_golden.py <path to a checkout of the reference>")
     ref_path = sys.argv[1]
-    rk, rta, rtt, rh, rhf, rthf = import_reference(ref_path)
+    rk, rta, rtt, rh, rhf, rthf, rlm = import_reference(ref_path)
 
     mm = {}
     for i, (m, n, k, ta, tb) in enumerate(MATMUL_CASES):
@@ -209,6 +218,13 @@ def main():
     assert "lm_head.weight" not in stripped and "h.0.attn.bias" not in stripped
     print(f"tiny_gpt2.safetensors: {os.path.getsize(path)} bytes, {len(back)} tensors, "
           f"{len(stripped)} after the reference's gpt2_tensors")
+    # byte -> id table of the language-model driver on a skewed byte stream
+    data = lm_bytes()
+    ids, itos = rlm.encode(data, 48)
+    np.savez_compressed(os.path.join(HERE, "lm_encode.npz"), ids=ids.astype(np.uint16),
+                        itos_ids=np.array(sorted(itos), np.int64),
+                        itos_chars=np.array([ord(itos[k]) for k in sorted(itos)], np.int64),
+                        data_digest=np.array([digest(data)], np.uint64))
     print("fixtures written to", HERE)
 
 
