@@ -25,19 +25,20 @@ from .vk import Device
 
 # ---- corpus ------------------------------------------------------------------------------
 
-def synthetic_corpus(n_bytes=1 << 20, seed=0):
+def synthetic_corpus(n_bytes=1 << 20, seed=0, order=2):
     """A byte stream with learnable structure, standing in for the text corpus of
     train_lm.py:37-57: a random Markov chain over 64 printable symbols whose context is the
-    last two symbols; the favoured successor is taken 85 % of the time."""
+    last `order` (1 or 2) symbols; the favoured successor is taken 85 % of the time."""
     rng = np.random.default_rng(seed)
-    successors = rng.integers(0, 64, (64 * 64, 4)).astype(np.int64)
+    mask = 64 ** order - 1
+    successors = rng.integers(0, 64, (mask + 1, 4)).astype(np.int64)
     choice = np.where(rng.random(n_bytes) < 0.85, 0, rng.integers(0, 4, n_bytes))
     out = np.empty(n_bytes, np.uint8)
     state = 0
     for i in range(n_bytes):
         s = successors[state, choice[i]]
         out[i] = 32 + s
-        state = (state * 64 + s) & 4095
+        state = (state * 64 + s) & mask
     return out
 
 
