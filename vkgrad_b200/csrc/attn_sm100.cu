@@ -378,33 +378,53 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rd
   }
 }
 
-// Column sums of one warp's 32 rows x NC columns (fp16 values as stored, 0 for rows that do not
-// exist) into dst[0 .. NC): the block goes through shared memory row by row (pitch NC + 1
-// words, conflict-free both ways) and lane c adds column c, c + 32, ... top to bottom, so
-// the result does not depend on timing.  `pad` is this warp's private 32 x (NC + 1) floats.
+// Column sums of one warp's 32 rows x NC columns (lane = row; fp16 values as stored, 0 for rows
+// that do not exist) without shared memory: a reduce-scatter over the lanes.  Each step halves
+// the columns a lane holds and adds the partner lane's share of the half it keeps, so after five
+// steps lane l holds the sums of columns l * NC / 32 .. (l + 1) * NC / 32 - 1 and writes them to
+// dst.  The order of the additions is fixed, so the result does not depend on timing.
 template <int NC>
-__device__ __forceinline__ void warp_col_sums(const float (&val)[NC], float* pad, int lane,
-                                              float* dst) {
+__device__ __forceinline__ void warp_col_sums(float (&v)[NC], int lane, float* dst) {
+  static_assert(NC == 32 || NC == 64, "one or two columns per lane");
 #pragma unroll
-  for (int c = 0; c < NC; ++c) pad[lane * (NC + 1) + c] = val[c];
-  __syncwarp();
+  for (int step = 0; step < 5; ++step) {
+    const int off = 16 >> step, n = NC >> (step + 1);
+    const bool upper = (lane & off) != 0;
 #pragma unroll
-  for (int c0 = 0; c0 < NC; c0 += 32) {
-    float s = 0.f;
-#pragma unroll 8
-    for (int r = 0; r < 32; ++r) s += pad[r * (NC + 1) + c0 + lane];
-    dst[c0 + lane] = s;
+    for (int c = 0; c < n; ++c) {
+      const float keep = upper ? v[c + n] : v[c];
+      const float send = upper ? v[c] : v[c + n];
+      v[c] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
   }
-  __syncwarp();
+  constexpr int PER = NC / 32;
+#pragma unroll
+  for (int c = 0; c < PER; ++c) dst[lane * PER + c] = v[c];
 }
 
-// dK / dV: one CTA per (key tile, head, sequence); loops over the query tiles at or
-// below the diagonal.  TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384).
-// P and dS are double-buffered (buffer = iteration & 1) so the softmax warps can build the
+// Item number j of persistent CTA c out of G: rows of G items are dealt left to right and right
+// to left in turn, which spreads items sorted by falling cost almost evenly (within 3 % of the
+// mean for 8 query tiles x 96 heads on 148 CTAs; plain round-robin is 16 % off).
+__device__ __forceinline__ int snake_item(int j, int G, int c) {
+  return j * G + ((j & 1) ? G - 1 - c : c);
+}
+
+// dK / dV: persistent CTAs, one per SM, each taking (key tile, head, sequence) items
+// blockIdx.x, blockIdx.x + gridDim.x, ... (items are ordered heaviest key tile first) and, per
+// item, looping over the query tiles at or below the diagonal.  The pipeline runs across item
+// boundaries: barrier phases follow a per-CTA count of (item, query tile) steps, the producer
+// reloads K / V as soon as the item's last S / dP products have retired (kv_free) and the tensor
+// core starts the next item's first S / dP before this item's last dV / dK, so a CTA pays the
+// load -> S -> softmax -> dV latency chain once per launch instead of once per item (measured
+// at 5.6 us per item when every item was its own CTA).  The accumulators are handed back by the
+// softmax warps (acc_free) before the next item's first dV / dK overwrites them.
+// TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384).
+// P and dS are double-buffered (buffer = step & 1) so the softmax warps can build the
 // next tile's P / dS while the tensor core still reads the previous ones for dV / dK.
 constexpr int KV_K = 0, KV_V = FA_TILE_BYTES, KV_Q = 2 * FA_TILE_BYTES, KV_DO = 4 * FA_TILE_BYTES,
               KV_P = 6 * FA_TILE_BYTES, KV_DS = 8 * FA_TILE_BYTES, KV_PDS_STRIDE = 4 * FA_TILE_BYTES,
               KV_BAR = 14 * FA_TILE_BYTES, KV_SMEM = KV_BAR + 256 + 1024;
+constexpr int BW_NBAR = 14;
 
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
@@ -414,21 +434,17 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
   uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar = base + KV_BAR;
   // 0 kv_full, 1-2 qd_full, 3-4 qd_empty, 5 sdp_full, 6 sdp_free, 7/10 pds_full[2],
-  // 8/11 pds_free[2], 9 out_full
+  // 8/11 pds_free[2], 9 out_full, 12 kv_free, 13 acc_free
   auto B_ = [bar](int i) { return bar + 8u * i; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 128);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 136);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int HB = p.H * p.B;
-  const int kt = (int)(blockIdx.x / HB);            // key tile; tile 0 has the most work, first
-  const int hb = blockIdx.x % HB;
-  const int h = hb % p.H, b = hb / p.H;
-  const int row0 = b * p.T, k0 = kt * FA_T;
-  const int ni = p.nqt - kt;                         // query tiles kt .. nqt-1
+  const int n_items = p.nqt * HB, G = (int)gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 12; ++i)
-      mbar_init(B_(i), (i == 6 || i == 7 || i == 10) ? FA_SOFTMAX_WARPS : 1);
+    for (int i = 0; i < BW_NBAR; ++i)
+      mbar_init(B_(i), (i == 6 || i == 7 || i == 10 || i == 13) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -442,28 +458,47 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(B_(0), 2 * FA_TILE_BYTES);
-      tma_load_2d(base + KV_K, &tm, B_(0), p.D + h * FA_HD, row0 + k0);
-      tma_load_2d(base + KV_V, &tm, B_(0), 2 * p.D + h * FA_HD, row0 + k0);
-      for (int it = 0; it < ni; ++it) {
-        const int s = it & 1;
-        if (!mbar_wait<true>(B_(3 + s), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4100u + s)) break;
-        mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
-        const int qrow = row0 + (kt + it) * FA_T;
-        tma_load_2d(base + KV_Q + s * FA_TILE_BYTES, &tm, B_(1 + s), h * FA_HD, qrow);
-        tma_load_2d(base + KV_DO + s * FA_TILE_BYTES, &tmdo, B_(1 + s), h * FA_HD, qrow);
+      int g = 0, j = 0;        // steps and items this CTA has started
+      bool ok = true;
+      for (;; ++j) {
+        const int item = snake_item(j, G, (int)blockIdx.x);
+        if (item >= n_items || !ok) break;
+        const int kt = item / HB, hb = item % HB;
+        const int h = hb % p.H, b = hb / p.H;
+        const int row0 = b * p.T, k0 = kt * FA_T, ni = p.nqt - kt;
+        // K / V of the previous item are read by its S / dP products only
+        if (j > 0 && !mbar_wait<true>(B_(12), (j - 1) & 1, abort_flag, p.err, 0x4900u)) break;
+        mbar_expect_tx(B_(0), 2 * FA_TILE_BYTES);
+        tma_load_2d(base + KV_K, &tm, B_(0), p.D + h * FA_HD, row0 + k0);
+        tma_load_2d(base + KV_V, &tm, B_(0), 2 * p.D + h * FA_HD, row0 + k0);
+        for (int it = 0; it < ni; ++it, ++g) {
+          const int s = g & 1;
+          if (!mbar_wait<true>(B_(3 + s), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4100u + s)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
+          const int qrow = row0 + (kt + it) * FA_T;
+          tma_load_2d(base + KV_Q + s * FA_TILE_BYTES, &tm, B_(1 + s), h * FA_HD, qrow);
+          tma_load_2d(base + KV_DO + s * FA_TILE_BYTES, &tmdo, B_(1 + s), h * FA_HD, qrow);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);    // [q x hd] . [key x hd]^T
       const uint32_t idesc_g = make_idesc(0, 1, 1, FA_HD);   // [q x key]^T . [q x hd]
-      bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x4200u);
       const uint32_t sk = base + KV_K, sv = base + KV_V;
-      auto issue_sdp = [&](int n) -> bool {   // S = Q_n K^T and dP = dO_n V^T
-        const int s = n & 1;
-        if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x4300u + s) &&
-              mbar_wait<true>(B_(6), (n & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
+      // cursor of the S / dP issue: always one step ahead of the dV / dK loop below, also
+      // across an item boundary
+      int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, g_a = 0;
+      int ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
+      auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of step g_a
+        if (item_a >= n_items) return true;
+        if (it_a == 0 && !mbar_wait<true>(B_(0), j_a & 1, abort_flag, p.err, 0x4200u)) return false;
+        const int s = g_a & 1;
+        if (!(mbar_wait<true>(B_(1 + s), (g_a >> 1) & 1, abort_flag, p.err, 0x4300u + s) &&
+              mbar_wait<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
           return false;
         tcgen05_fence_after();
         const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
@@ -476,95 +511,65 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           umma_f16(tdP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024),
                    idesc_s, k ? 1u : 0u);
         umma_commit(B_(5));
+        if (it_a == ni_a - 1) umma_commit(B_(12));    // the item's K / V may be replaced
+        ++g_a;
+        if (++it_a == ni_a) {
+          item_a = snake_item(++j_a, G, (int)blockIdx.x);
+          it_a = 0;
+          ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
+        }
         return true;
       };
-      // software pipeline: the next tile's S / dP are issued before this tile's dV / dK, so
-      // the tensor core is busy while the softmax warps turn S, dP into P, dS
-      if (ok) ok = issue_sdp(0);
-      for (int it = 0; it < ni && ok; ++it) {
-        const int s = it & 1;
-        if (it + 1 < ni) {
-          ok = issue_sdp(it + 1);
+      bool ok = issue_sdp();
+      int g = 0, j = 0;
+      for (;; ++j) {
+        const int item = snake_item(j, G, (int)blockIdx.x);
+        if (item >= n_items || !ok) break;
+        const int ni = p.nqt - item / HB;
+        for (int it = 0; it < ni; ++it, ++g) {
+          // the next step's S / dP go first (also when that means waiting for a new item's
+          // operands: issuing dV / dK first measured slower), so the tensor core is busy while
+          // the softmax warps turn S, dP into P, dS
+          ok = issue_sdp();
           if (!ok) break;
+          const int s = g & 1, pb = g & 1;     // Q / dO stage and P / dS buffer of this step
+          ok = mbar_wait<true>(B_(7 + 3 * pb), (g >> 1) & 1, abort_flag, p.err, 0x4500u);
+          if (!ok) break;
+          if (it == 0 && j > 0) {              // the previous item's dV / dK have been read out
+            ok = mbar_wait<true>(B_(13), (j - 1) & 1, abort_flag, p.err, 0x4a00u);
+            if (!ok) break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
+          const uint32_t sp = base + KV_P + pb * KV_PDS_STRIDE, sds = base + KV_DS + pb * KV_PDS_STRIDE;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)      // K = 128 query rows, 16 at a time
+            umma_f16(tdV, make_smem_desc(sp + kk * 2048, FA_TILE_BYTES, 1024),
+                     make_smem_desc(sdo + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_f16(tdK, make_smem_desc(sds + kk * 2048, FA_TILE_BYTES, 1024),
+                     make_smem_desc(sq + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
+          umma_commit(B_(3 + s));        // Q / dO stage free
+          umma_commit(B_(8 + 3 * pb));   // this P / dS buffer free
+          if (it == ni - 1) umma_commit(B_(9));
         }
-        const int pb = it & 1;     // P / dS buffer of this iteration
-        ok = mbar_wait<true>(B_(7 + 3 * pb), (it >> 1) & 1, abort_flag, p.err, 0x4500u);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
-        const uint32_t sp = base + KV_P + pb * KV_PDS_STRIDE, sds = base + KV_DS + pb * KV_PDS_STRIDE;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)      // K = 128 query rows, 16 at a time
-          umma_f16(tdV, make_smem_desc(sp + kk * 2048, FA_TILE_BYTES, 1024),
-                   make_smem_desc(sdo + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tdK, make_smem_desc(sds + kk * 2048, FA_TILE_BYTES, 1024),
-                   make_smem_desc(sq + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
-        umma_commit(B_(3 + s));        // Q / dO stage free
-        umma_commit(B_(8 + 3 * pb));   // this P / dS buffer free
       }
-      if (ok) umma_commit(B_(9));
     }
   } else {
     const int half = (warp - 2) >> 2;            // which 64 of the tile's 128 keys
     const int r = (warp & 3) * 32 + lane;
     const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
     bool ok = true;
-    // row statistics of query tile kt + it; the next tile's are fetched one iteration ahead
-    const float* lse_h = p.lse2 + (size_t)(b * p.H + h) * p.T;
-    const float* delta_h = p.delta + (size_t)(b * p.H + h) * p.T;
-    auto row_stat = [&](int qi, float& lse, float& dl, int& st) {
-      const bool q_ok = qi < p.T;
-      const int i = q_ok ? qi : 0;
-      lse = lse_h[i];
-      dl = delta_h[i];
-      st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
-    };
-    float lse_n, dl_n;
-    int st_n;
-    row_stat(kt * FA_T + r, lse_n, dl_n, st_n);
-    for (int it = 0; it < ni && ok; ++it) {
-      const int qt = kt + it;
-      const int qi = qt * FA_T + r;
-      const bool q_ok = qi < p.T;
-      // a row past the end of the sequence gets lse = +inf, hence P = 0 and dS = 0
-      const float nlse = q_ok ? -lse_n : -INFINITY, dsc = -dl_n * p.scale;
-      const int st = st_n;
-      if (it + 1 < ni) row_stat(qi + FA_T, lse_n, dl_n, st_n);
-      const bool need_mask = (qt == kt) || (p.seg != nullptr);
-      ok = mbar_wait<true>(B_(5), it & 1, abort_flag, p.err, 0x4600u);
-      if (!ok) break;
-      tcgen05_fence_after();
-      uint32_t rs[64], rdp[64];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, rs + c * 16);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld16(tdP + t_lane + half * 64 + c * 16, rdp + c * 16);
-      tmem_wait_ld();
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(B_(6));          // S / dP may be overwritten
-      const int pb = it & 1;
-      ok = mbar_wait<true>(B_(8 + 3 * pb), ((it >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // buffer free
-      if (!ok) break;
-      uint8_t* sp = gbase + KV_P + pb * KV_PDS_STRIDE;
-      uint8_t* sds = gbase + KV_DS + pb * KV_PDS_STRIDE;
-      if (need_mask) {
-        bwd_chunk<true>(rs, rdp, 2 * half, r, k0, qi, st, p.cscale, p.scale, nlse, dsc, sp, sds);
-        bwd_chunk<true>(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, p.cscale, p.scale, nlse, dsc,
-                        sp, sds);
-      } else {
-        bwd_chunk<false>(rs, rdp, 2 * half, r, k0, qi, st, p.cscale, p.scale, nlse, dsc, sp, sds);
-        bwd_chunk<false>(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, p.cscale, p.scale, nlse, dsc,
-                         sp, sds);
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
-    }
-    if (ok) ok = mbar_wait<true>(B_(9), 0, abort_flag, p.err, 0x4800u);
-    if (ok) {
+    // dV / dK of a finished item: wait for its last products, read the accumulators, hand them
+    // back, store.  Runs after the NEXT item's first step, so the hand-off to the tensor core
+    // (S, dP -> P, dS) does not stall at an item boundary.
+    int pend_item = -1, pend_j = 0;
+    auto store_item = [&](int item, int jj) -> bool {
+      const int kt = item / HB, hb = item % HB;
+      const int h = hb % p.H, b = hb / p.H;
+      const int row0 = b * p.T, k0 = kt * FA_T;
+      if (!mbar_wait<true>(B_(9), jj & 1, abort_flag, p.err, 0x4800u)) return false;
       tcgen05_fence_after();
       const int key = k0 + r;     // accumulator rows are keys here
       // half 0 stores dV (slice 2 of dqkv), half 1 stores dK (slice 1)
@@ -573,6 +578,9 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld16(t + c * 16, rr + c * 16);
       tmem_wait_ld();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(13));           // the accumulators may be overwritten
       if (key < p.T) {
         __half* dst = p.dqkv + (size_t)(row0 + key) * 3 * p.D + (half == 0 ? 2 : 1) * p.D + h * FA_HD;
 #pragma unroll
@@ -586,18 +594,102 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
         }
       }
       if (p.colsum) {
-        // the qkv bias gradient: column sums of dV / dK as stored; every MMA has retired
-        // and every operand tile has been consumed, so the tile area is free to use
+        // the qkv bias gradient: column sums of dV / dK as stored
         float val[64];
 #pragma unroll
         for (int c = 0; c < 64; ++c)
           val[c] = key < p.T ? __half2float(__float2half_rn(__uint_as_float(rr[c]))) : 0.f;
-        float* pad = reinterpret_cast<float*>(gbase) + (warp - 2) * 32 * 65;
         float* dst = p.colsum + ((size_t)(b * p.nqt + kt) * 4 + (warp & 3)) * 3 * p.D +
                      (half == 0 ? 2 : 1) * p.D + h * FA_HD;
-        warp_col_sums<64>(val, pad, lane, dst);
+        warp_col_sums<64>(val, lane, dst);
       }
+      return true;
+    };
+    // statistics of this thread's row in the first query tile of an item
+    auto first_stat = [&](int item, float& lse, float& dl, int& st) {
+      const int kt = item / HB, hb = item % HB;
+      const int qi = kt * FA_T + r;
+      const bool q_ok = qi < p.T;
+      const size_t i = (size_t)((hb / p.H) * p.H + hb % p.H) * p.T + (q_ok ? qi : 0);
+      lse = p.lse2[i];
+      dl = p.delta[i];
+      st = (p.seg && q_ok) ? (int)p.seg[(hb / p.H) * p.T + qi] : 0;
+    };
+    float lse_f = 0.f, dl_f = 0.f;
+    int st_f = 0;
+    if ((int)blockIdx.x < n_items) first_stat((int)blockIdx.x, lse_f, dl_f, st_f);
+    int g = 0, j = 0;
+    for (;; ++j) {
+      const int item = snake_item(j, G, (int)blockIdx.x);
+      if (item >= n_items || !ok) break;
+      const int kt = item / HB, hb = item % HB;
+      const int h = hb % p.H, b = hb / p.H;
+      const int row0 = b * p.T, k0 = kt * FA_T, ni = p.nqt - kt;
+      // row statistics of query tile kt + it; the next tile's are fetched one step ahead, the
+      // first tile's of the next item one item ahead (a load from global memory at the start
+      // of an item would sit on the critical path)
+      const float* lse_h = p.lse2 + (size_t)(b * p.H + h) * p.T;
+      const float* delta_h = p.delta + (size_t)(b * p.H + h) * p.T;
+      auto row_stat = [&](int qi, float& lse, float& dl, int& st) {
+        const bool q_ok = qi < p.T;
+        const int i = q_ok ? qi : 0;
+        lse = lse_h[i];
+        dl = delta_h[i];
+        st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
+      };
+      float lse_n = lse_f, dl_n = dl_f;
+      int st_n = st_f;
+      {
+        const int nxt = snake_item(j + 1, G, (int)blockIdx.x);
+        if (nxt < n_items) first_stat(nxt, lse_f, dl_f, st_f);
+      }
+      for (int it = 0; it < ni && ok; ++it, ++g) {
+        const int qt = kt + it;
+        const int qi = qt * FA_T + r;
+        const bool q_ok = qi < p.T;
+        // a row past the end of the sequence gets lse = +inf, hence P = 0 and dS = 0
+        const float nlse = q_ok ? -lse_n : -INFINITY, dsc = -dl_n * p.scale;
+        const int st = st_n;
+        if (it + 1 < ni) row_stat(qi + FA_T, lse_n, dl_n, st_n);
+        const bool need_mask = (qt == kt) || (p.seg != nullptr);
+        ok = mbar_wait<true>(B_(5), g & 1, abort_flag, p.err, 0x4600u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        uint32_t rs[64], rdp[64];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, rs + c * 16);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld16(tdP + t_lane + half * 64 + c * 16, rdp + c * 16);
+        tmem_wait_ld();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(B_(6));          // S / dP may be overwritten
+        const int pb = g & 1;
+        ok = mbar_wait<true>(B_(8 + 3 * pb), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // buffer free
+        if (!ok) break;
+        uint8_t* sp = gbase + KV_P + pb * KV_PDS_STRIDE;
+        uint8_t* sds = gbase + KV_DS + pb * KV_PDS_STRIDE;
+        if (need_mask) {
+          bwd_chunk<true>(rs, rdp, 2 * half, r, k0, qi, st, p.cscale, p.scale, nlse, dsc, sp, sds);
+          bwd_chunk<true>(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, p.cscale, p.scale, nlse, dsc,
+                          sp, sds);
+        } else {
+          bwd_chunk<false>(rs, rdp, 2 * half, r, k0, qi, st, p.cscale, p.scale, nlse, dsc, sp, sds);
+          bwd_chunk<false>(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, p.cscale, p.scale, nlse, dsc,
+                           sp, sds);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
+        if (pend_item >= 0) {      // the previous item's accumulators, now surely complete
+          ok = store_item(pend_item, pend_j);
+          pend_item = -1;
+        }
+      }
+      pend_item = item;       // read this item's dV / dK out after the next item's first step
+      pend_j = j;
     }
+    if (ok && pend_item >= 0) ok = store_item(pend_item, pend_j);
   }
   __syncwarp();
   tcgen05_fence_before();
@@ -613,8 +705,10 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
   }
 }
 
-// dQ: one CTA per (query tile, head, sequence); loops over the key tiles up to the
-// diagonal.  TMEM: S [0,128) dP [128,256) dQ [256,320).
+// dQ: persistent CTAs like the dK / dV kernel; an item is a (query tile, head, sequence),
+// heaviest query tile first, and loops over the key tiles up to the diagonal.  Q / dO are the
+// per-item operands (reloaded once the item's last S / dP have retired: qd_free), K / V the
+// per-step ones.  TMEM: S [0,128) dP [128,256) dQ [256,320).
 constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_K = 2 * FA_TILE_BYTES, DQ_V = 4 * FA_TILE_BYTES,
               DQ_DS = 6 * FA_TILE_BYTES, DQ_DS_STRIDE = 2 * FA_TILE_BYTES,   // dS double-buffered
               DQ_BAR = 10 * FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
@@ -627,21 +721,17 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar = base + DQ_BAR;
   // 0 qd_full, 1-2 kv_full, 3-4 kv_empty, 5 sdp_full, 6 sdp_free, 7/10 ds_full[2],
-  // 8/11 ds_free[2], 9 out_full
+  // 8/11 ds_free[2], 9 out_full, 12 qd_free, 13 acc_free
   auto B_ = [bar](int i) { return bar + 8u * i; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 128);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 136);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int HB = p.H * p.B;
-  const int qt = p.nqt - 1 - (int)(blockIdx.x / HB);
-  const int hb = blockIdx.x % HB;
-  const int h = hb % p.H, b = hb / p.H;
-  const int row0 = b * p.T, q0 = qt * FA_T;
-  const int nj = qt + 1;
+  const int n_items = p.nqt * HB, G = (int)gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 12; ++i)
-      mbar_init(B_(i), (i == 6 || i == 7 || i == 10) ? FA_SOFTMAX_WARPS : 1);
+    for (int i = 0; i < BW_NBAR; ++i)
+      mbar_init(B_(i), (i == 6 || i == 7 || i == 10 || i == 13) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -655,28 +745,44 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(B_(0), 2 * FA_TILE_BYTES);
-      tma_load_2d(base + DQ_Q, &tm, B_(0), h * FA_HD, row0 + q0);
-      tma_load_2d(base + DQ_DO, &tmdo, B_(0), h * FA_HD, row0 + q0);
-      for (int j = 0; j < nj; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait<true>(B_(3 + s), ((j >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5100u + s)) break;
-        mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
-        tma_load_2d(base + DQ_K + s * FA_TILE_BYTES, &tm, B_(1 + s), p.D + h * FA_HD, row0 + j * FA_T);
-        tma_load_2d(base + DQ_V + s * FA_TILE_BYTES, &tm, B_(1 + s), 2 * p.D + h * FA_HD,
-                    row0 + j * FA_T);
+      int g = 0, j = 0;
+      bool ok = true;
+      for (;; ++j) {
+        const int item = snake_item(j, G, (int)blockIdx.x);
+        if (item >= n_items || !ok) break;
+        const int qt = p.nqt - 1 - item / HB, hb = item % HB;
+        const int h = hb % p.H, b = hb / p.H;
+        const int row0 = b * p.T, q0 = qt * FA_T, nj = qt + 1;
+        if (j > 0 && !mbar_wait<true>(B_(12), (j - 1) & 1, abort_flag, p.err, 0x5900u)) break;
+        mbar_expect_tx(B_(0), 2 * FA_TILE_BYTES);
+        tma_load_2d(base + DQ_Q, &tm, B_(0), h * FA_HD, row0 + q0);
+        tma_load_2d(base + DQ_DO, &tmdo, B_(0), h * FA_HD, row0 + q0);
+        for (int kt = 0; kt < nj; ++kt, ++g) {
+          const int s = g & 1;
+          if (!mbar_wait<true>(B_(3 + s), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5100u + s)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
+          tma_load_2d(base + DQ_K + s * FA_TILE_BYTES, &tm, B_(1 + s), p.D + h * FA_HD, row0 + kt * FA_T);
+          tma_load_2d(base + DQ_V + s * FA_TILE_BYTES, &tm, B_(1 + s), 2 * p.D + h * FA_HD,
+                      row0 + kt * FA_T);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
       const uint32_t idesc_q = make_idesc(0, 0, 1, FA_HD);   // dS (K-major) . K (MN-major), N = 64
-      bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x5200u);
       const uint32_t sq = base + DQ_Q, sdo = base + DQ_DO;
-      auto issue_sdp = [&](int n) -> bool {   // S = Q K_n^T and dP = dO V_n^T
-        const int s = n & 1;
-        if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x5300u + s) &&
-              mbar_wait<true>(B_(6), (n & 1) ^ 1u, abort_flag, p.err, 0x5400u)))
+      int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, g_a = 0;
+      int ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;      // key tiles of the item: qt + 1
+      auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of step g_a
+        if (item_a >= n_items) return true;
+        if (it_a == 0 && !mbar_wait<true>(B_(0), j_a & 1, abort_flag, p.err, 0x5200u)) return false;
+        const int s = g_a & 1;
+        if (!(mbar_wait<true>(B_(1 + s), (g_a >> 1) & 1, abort_flag, p.err, 0x5300u + s) &&
+              mbar_wait<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x5400u)))
           return false;
         tcgen05_fence_after();
         const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES, sv = base + DQ_V + s * FA_TILE_BYTES;
@@ -689,78 +795,65 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
           umma_f16(tdP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024),
                    idesc_s, k ? 1u : 0u);
         umma_commit(B_(5));
+        if (it_a == ni_a - 1) umma_commit(B_(12));    // the item's Q / dO may be replaced
+        ++g_a;
+        if (++it_a == ni_a) {
+          item_a = snake_item(++j_a, G, (int)blockIdx.x);
+          it_a = 0;
+          ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
+        }
         return true;
       };
-      if (ok) ok = issue_sdp(0);
-      for (int j = 0; j < nj && ok; ++j) {
-        const int s = j & 1;
-        if (j + 1 < nj) {
-          ok = issue_sdp(j + 1);
+      bool ok = issue_sdp();
+      int g = 0, j = 0;
+      for (;; ++j) {
+        const int item = snake_item(j, G, (int)blockIdx.x);
+        if (item >= n_items || !ok) break;
+        const int nj = p.nqt - item / HB;
+        for (int kt = 0; kt < nj; ++kt, ++g) {
+          ok = issue_sdp();
           if (!ok) break;
-        }
-        const int pb = j & 1;
-        ok = mbar_wait<true>(B_(7 + 3 * pb), (j >> 1) & 1, abort_flag, p.err, 0x5500u);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES;
-        const uint32_t sds = base + DQ_DS + pb * DQ_DS_STRIDE;
+          const int s = g & 1, pb = g & 1;
+          ok = mbar_wait<true>(B_(7 + 3 * pb), (g >> 1) & 1, abort_flag, p.err, 0x5500u);
+          if (!ok) break;
+          if (kt == 0 && j > 0) {
+            ok = mbar_wait<true>(B_(13), (j - 1) & 1, abort_flag, p.err, 0x5a00u);
+            if (!ok) break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES;
+          const uint32_t sds = base + DQ_DS + pb * DQ_DS_STRIDE;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)      // K = 128 keys
-          umma_f16(tdQ, make_smem_desc(sds + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                   make_smem_desc(sk + kk * 2048, 8192, 1024), idesc_q, (j | kk) ? 1u : 0u);
-        umma_commit(B_(3 + s));        // K / V stage free
-        umma_commit(B_(8 + 3 * pb));   // this dS buffer free
+          for (int kk = 0; kk < 8; ++kk)      // K = 128 keys
+            umma_f16(tdQ, make_smem_desc(sds + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
+                     make_smem_desc(sk + kk * 2048, 8192, 1024), idesc_q, (kt | kk) ? 1u : 0u);
+          umma_commit(B_(3 + s));        // K / V stage free
+          umma_commit(B_(8 + 3 * pb));   // this dS buffer free
+          if (kt == nj - 1) umma_commit(B_(9));
+        }
       }
-      if (ok) umma_commit(B_(9));
     }
   } else {
     const int half = (warp - 2) >> 2;
     const int r = (warp & 3) * 32 + lane;
     const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
-    const int qi = q0 + r;
-    const bool q_ok = qi < p.T;
-    const size_t sidx = (size_t)(b * p.H + h) * p.T + (q_ok ? qi : 0);
-    const float nlse = q_ok ? -p.lse2[sidx] : -INFINITY, dsc = -p.delta[sidx] * p.scale;
-    const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
     bool ok = true;
-    for (int j = 0; j < nj && ok; ++j) {
-      const bool need_mask = (j == qt) || (p.seg != nullptr);
-      ok = mbar_wait<true>(B_(5), j & 1, abort_flag, p.err, 0x5600u);
-      if (!ok) break;
-      tcgen05_fence_after();
-      uint32_t rs[64], rdp[64];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, rs + c * 16);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld16(tdP + t_lane + half * 64 + c * 16, rdp + c * 16);
-      tmem_wait_ld();
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(B_(6));
-      const int pb = j & 1;
-      ok = mbar_wait<true>(B_(8 + 3 * pb), ((j >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
-      if (!ok) break;
-      uint8_t* sds = gbase + DQ_DS + pb * DQ_DS_STRIDE;
-      if (need_mask) {
-        bwd_chunk<true>(rs, rdp, 2 * half, r, j * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
-        bwd_chunk<true>(rs + 32, rdp + 32, 2 * half + 1, r, j * FA_T, qi, st, p.cscale, p.scale, nlse,
-                        dsc, nullptr, sds);
-      } else {
-        bwd_chunk<false>(rs, rdp, 2 * half, r, j * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
-        bwd_chunk<false>(rs + 32, rdp + 32, 2 * half + 1, r, j * FA_T, qi, st, p.cscale, p.scale, nlse,
-                         dsc, nullptr, sds);
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
-    }
-    if (ok) ok = mbar_wait<true>(B_(9), 0, abort_flag, p.err, 0x5800u);
-    if (ok) {
+    // dQ of a finished item, read out after the NEXT item's first step (see the dK / dV kernel)
+    int pend_item = -1, pend_j = 0;
+    auto store_item = [&](int item, int jj) -> bool {
+      const int qt = p.nqt - 1 - item / HB, hb = item % HB;
+      const int h = hb % p.H, b = hb / p.H;
+      const int row0 = b * p.T, qi = qt * FA_T + r;
+      const bool q_ok = qi < p.T;
+      if (!mbar_wait<true>(B_(9), jj & 1, abort_flag, p.err, 0x5800u)) return false;
       tcgen05_fence_after();
       uint32_t rr[32];                             // this half's 32 of the 64 dQ columns
       tmem_ld16(tdQ + t_lane + half * 32, rr);
       tmem_ld16(tdQ + t_lane + half * 32 + 16, rr + 16);
       tmem_wait_ld();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(13));           // dQ may be overwritten
       if (q_ok) {
         __half* dst = p.dqkv + (size_t)(row0 + qi) * 3 * p.D + h * FA_HD + half * 32;
 #pragma unroll
@@ -778,12 +871,80 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < 32; ++c)
           val[c] = q_ok ? __half2float(__float2half_rn(__uint_as_float(rr[c]))) : 0.f;
-        float* pad = reinterpret_cast<float*>(gbase) + (warp - 2) * 32 * 33;
         float* dst = p.colsum + ((size_t)(b * p.nqt + qt) * 4 + (warp & 3)) * 3 * p.D + h * FA_HD +
                      half * 32;
-        warp_col_sums<32>(val, pad, lane, dst);
+        warp_col_sums<32>(val, lane, dst);
       }
+      return true;
+    };
+    // statistics of this thread's query row in an item
+    auto item_stat = [&](int item, float& lse, float& dl, int& st) {
+      const int qt = p.nqt - 1 - item / HB, hb = item % HB;
+      const int qi = qt * FA_T + r;
+      const bool q_ok = qi < p.T;
+      const size_t i = (size_t)((hb / p.H) * p.H + hb % p.H) * p.T + (q_ok ? qi : 0);
+      lse = p.lse2[i];
+      dl = p.delta[i];
+      st = (p.seg && q_ok) ? (int)p.seg[(hb / p.H) * p.T + qi] : 0;
+    };
+    float lse_f = 0.f, dl_f = 0.f;
+    int st_f = 0;
+    if ((int)blockIdx.x < n_items) item_stat((int)blockIdx.x, lse_f, dl_f, st_f);
+    int g = 0, j = 0;
+    for (;; ++j) {
+      const int item = snake_item(j, G, (int)blockIdx.x);
+      if (item >= n_items || !ok) break;
+      const int qt = p.nqt - 1 - item / HB, hb = item % HB;
+      const int h = hb % p.H, b = hb / p.H;
+      const int row0 = b * p.T, q0 = qt * FA_T, nj = qt + 1;
+      const int qi = q0 + r;
+      const bool q_ok = qi < p.T;
+      // this row's statistics were fetched while the previous item was being worked on
+      const float nlse = q_ok ? -lse_f : -INFINITY, dsc = -dl_f * p.scale;
+      const int st = st_f;
+      {
+        const int nxt = snake_item(j + 1, G, (int)blockIdx.x);
+        if (nxt < n_items) item_stat(nxt, lse_f, dl_f, st_f);
+      }
+      for (int kt = 0; kt < nj && ok; ++kt, ++g) {
+        const bool need_mask = (kt == qt) || (p.seg != nullptr);
+        ok = mbar_wait<true>(B_(5), g & 1, abort_flag, p.err, 0x5600u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        uint32_t rs[64], rdp[64];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, rs + c * 16);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld16(tdP + t_lane + half * 64 + c * 16, rdp + c * 16);
+        tmem_wait_ld();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(B_(6));
+        const int pb = g & 1;
+        ok = mbar_wait<true>(B_(8 + 3 * pb), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
+        if (!ok) break;
+        uint8_t* sds = gbase + DQ_DS + pb * DQ_DS_STRIDE;
+        if (need_mask) {
+          bwd_chunk<true>(rs, rdp, 2 * half, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
+          bwd_chunk<true>(rs + 32, rdp + 32, 2 * half + 1, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse,
+                          dsc, nullptr, sds);
+        } else {
+          bwd_chunk<false>(rs, rdp, 2 * half, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
+          bwd_chunk<false>(rs + 32, rdp + 32, 2 * half + 1, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse,
+                           dsc, nullptr, sds);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
+        if (pend_item >= 0) {
+          ok = store_item(pend_item, pend_j);
+          pend_item = -1;
+        }
+      }
+      pend_item = item;       // read this item's dQ out after the next item's first step
+      pend_j = j;
     }
+    if (ok && pend_item >= 0) ok = store_item(pend_item, pend_j);
   }
   __syncwarp();
   tcgen05_fence_before();
@@ -898,7 +1059,10 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
   attn_delta_kernel<<<(unsigned)((items * 8 + 255) / 256), 256, 0, dev->stream>>>(
       (const __half*)dout16, (const __half*)out16, delta, B, T, H);
   if (vkg_check_launch("attn_delta_kernel")) return 1;
-  const unsigned ctas = (unsigned)((long long)p.nqt * H * B);
+  const long long n_items = (long long)p.nqt * H * B;
+  VKG_REQUIRE(n_items < (1ll << 31), "attn_bwd: too many tiles");
+  // persistent kernels: one CTA per SM (their shared memory allows no more), items dealt round-robin
+  const unsigned ctas = (unsigned)(n_items < dev->sm_count ? n_items : dev->sm_count);
   attn_bwd_kv_kernel<<<ctas, BW_THREADS, KV_SMEM, dev->stream>>>(tm, tmdo, p);
   if (vkg_check_launch("attn_bwd_kv_kernel")) return 1;
   attn_bwd_q_kernel<<<ctas, BW_THREADS, DQ_SMEM, dev->stream>>>(tm, tmdo, p);
