@@ -708,10 +708,17 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
 // dQ: persistent CTAs like the dK / dV kernel; an item is a (query tile, head, sequence),
 // heaviest query tile first, and loops over the key tiles up to the diagonal.  Q / dO are the
 // per-item operands (reloaded once the item's last S / dP have retired: qd_free), K / V the
-// per-step ones.  TMEM: S [0,128) dP [128,256) dQ [256,320).
-constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_K = 2 * FA_TILE_BYTES, DQ_V = 4 * FA_TILE_BYTES,
-              DQ_DS = 6 * FA_TILE_BYTES, DQ_DS_STRIDE = 2 * FA_TILE_BYTES,   // dS double-buffered
-              DQ_BAR = 10 * FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
+// per-step ones, in a ring of three stages: a stage is read by S / dP of its step and again by
+// dQ of the same step a softmax later, so with two stages the load of step g + 1 had to wait for
+// dQ of step g - 1 and the chain dQ -> load -> S / dP set the pace (2.2 us per step measured on
+// the dK / dV kernel, which has no room for a third stage, against 1.1 us of tensor work here).
+// TMEM: S [0,128) dP [128,256) dQ [256,320).
+constexpr int DQ_STAGES = 3;
+constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_K = 2 * FA_TILE_BYTES,
+              DQ_V = (2 + DQ_STAGES) * FA_TILE_BYTES, DQ_DS = (2 + 2 * DQ_STAGES) * FA_TILE_BYTES,
+              DQ_DS_STRIDE = 2 * FA_TILE_BYTES,   // dS double-buffered
+              DQ_BAR = (6 + 2 * DQ_STAGES) * FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
+constexpr int DQ_NBAR = 14 + 2 * DQ_STAGES, DQ_KV_FULL = 14, DQ_KV_EMPTY = 14 + DQ_STAGES;
 
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
@@ -720,17 +727,17 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar = base + DQ_BAR;
-  // 0 qd_full, 1-2 kv_full, 3-4 kv_empty, 5 sdp_full, 6 sdp_free, 7/10 ds_full[2],
-  // 8/11 ds_free[2], 9 out_full, 12 qd_free, 13 acc_free
+  // 0 qd_full, 5 sdp_full, 6 sdp_free, 7/10 ds_full[2], 8/11 ds_free[2], 9 out_full, 12 qd_free,
+  // 13 acc_free, 14.. kv_full[stage], then kv_empty[stage]
   auto B_ = [bar](int i) { return bar + 8u * i; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 128);
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 136);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 192);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 200);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int HB = p.H * p.B;
   const int n_items = p.nqt * HB, G = (int)gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < BW_NBAR; ++i)
+    for (int i = 0; i < DQ_NBAR; ++i)
       mbar_init(B_(i), (i == 6 || i == 7 || i == 10 || i == 13) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -758,14 +765,16 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
         tma_load_2d(base + DQ_Q, &tm, B_(0), h * FA_HD, row0 + q0);
         tma_load_2d(base + DQ_DO, &tmdo, B_(0), h * FA_HD, row0 + q0);
         for (int kt = 0; kt < nj; ++kt, ++g) {
-          const int s = g & 1;
-          if (!mbar_wait<true>(B_(3 + s), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5100u + s)) {
+          const int s = g % DQ_STAGES;
+          const uint32_t ph = (uint32_t)(g / DQ_STAGES) & 1u;
+          if (!mbar_wait<true>(B_(DQ_KV_EMPTY + s), ph ^ 1u, abort_flag, p.err, 0x5100u + s)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
-          tma_load_2d(base + DQ_K + s * FA_TILE_BYTES, &tm, B_(1 + s), p.D + h * FA_HD, row0 + kt * FA_T);
-          tma_load_2d(base + DQ_V + s * FA_TILE_BYTES, &tm, B_(1 + s), 2 * p.D + h * FA_HD,
+          mbar_expect_tx(B_(DQ_KV_FULL + s), 2 * FA_TILE_BYTES);
+          tma_load_2d(base + DQ_K + s * FA_TILE_BYTES, &tm, B_(DQ_KV_FULL + s), p.D + h * FA_HD,
+                      row0 + kt * FA_T);
+          tma_load_2d(base + DQ_V + s * FA_TILE_BYTES, &tm, B_(DQ_KV_FULL + s), 2 * p.D + h * FA_HD,
                       row0 + kt * FA_T);
         }
       }
@@ -780,8 +789,9 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of step g_a
         if (item_a >= n_items) return true;
         if (it_a == 0 && !mbar_wait<true>(B_(0), j_a & 1, abort_flag, p.err, 0x5200u)) return false;
-        const int s = g_a & 1;
-        if (!(mbar_wait<true>(B_(1 + s), (g_a >> 1) & 1, abort_flag, p.err, 0x5300u + s) &&
+        const int s = g_a % DQ_STAGES;
+        if (!(mbar_wait<true>(B_(DQ_KV_FULL + s), (uint32_t)(g_a / DQ_STAGES) & 1u, abort_flag, p.err,
+                              0x5300u + s) &&
               mbar_wait<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x5400u)))
           return false;
         tcgen05_fence_after();
@@ -813,7 +823,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
         for (int kt = 0; kt < nj; ++kt, ++g) {
           ok = issue_sdp();
           if (!ok) break;
-          const int s = g & 1, pb = g & 1;
+          const int s = g % DQ_STAGES, pb = g & 1;
           ok = mbar_wait<true>(B_(7 + 3 * pb), (g >> 1) & 1, abort_flag, p.err, 0x5500u);
           if (!ok) break;
           if (kt == 0 && j > 0) {
@@ -827,7 +837,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
           for (int kk = 0; kk < 8; ++kk)      // K = 128 keys
             umma_f16(tdQ, make_smem_desc(sds + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
                      make_smem_desc(sk + kk * 2048, 8192, 1024), idesc_q, (kt | kk) ? 1u : 0u);
-          umma_commit(B_(3 + s));        // K / V stage free
+          umma_commit(B_(DQ_KV_EMPTY + s));   // K / V stage free
           umma_commit(B_(8 + 3 * pb));   // this dS buffer free
           if (kt == nj - 1) umma_commit(B_(9));
         }
