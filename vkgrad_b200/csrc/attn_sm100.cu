@@ -378,6 +378,50 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rd
   }
 }
 
+// The same chunk in two phases, for a consumer whose P / dS buffer is still being read: the
+// values are formed and packed into registers first (four 16-byte groups each), and written
+// with bwd_chunk_store once the buffer is free.
+template <bool MASK>
+__device__ __forceinline__ void bwd_chunk_regs(const uint32_t* rs, const uint32_t* rdp, int c,
+                                               int key0, int qi, int st, float cscale, float scale,
+                                               float nlse, float dsc, uint4* outp, uint4* outd) {
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    __half2 hp[4], hd[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float pv[2], dv[2];
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const int idx = u * 8 + 2 * e + w;
+        float pr = vkg_ex2(fmaf(__uint_as_float(rs[idx]), cscale, nlse));
+        if (MASK) {
+          const int key = key0 + c * 32 + idx;
+          if (key > qi || key < st) pr = 0.f;
+        }
+        pv[w] = pr;
+        dv[w] = pr * fmaf(__uint_as_float(rdp[idx]), scale, dsc);
+      }
+      hp[e] = __floats2half2_rn(pv[0], pv[1]);
+      hd[e] = __floats2half2_rn(dv[0], dv[1]);
+    }
+    outp[u] = *reinterpret_cast<uint4*>(hp);
+    outd[u] = *reinterpret_cast<uint4*>(hd);
+  }
+}
+
+__device__ __forceinline__ void bwd_chunk_store(int c, int r, const uint4* outp, const uint4* outd,
+                                                uint8_t* sp, uint8_t* sds) {
+  const uint32_t row_off = (uint32_t)(r * 128), rx = (uint32_t)(r & 7);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int cc = c * 4 + u;
+    const uint32_t off = (uint32_t)((cc >> 3) * FA_TILE_BYTES) + row_off + ((((uint32_t)cc & 7u) ^ rx) << 4);
+    *reinterpret_cast<uint4*>(sp + off) = outp[u];
+    *reinterpret_cast<uint4*>(sds + off) = outd[u];
+  }
+}
+
 // Column sums of one warp's 32 rows x NC columns (lane = row; fp16 values as stored, 0 for rows
 // that do not exist) without shared memory: a reduce-scatter over the lanes.  Each step halves
 // the columns a lane holds and adds the partner lane's share of the half it keeps, so after five
@@ -419,12 +463,21 @@ __device__ __forceinline__ int snake_item(int j, int G, int c) {
 // at 5.6 us per item when every item was its own CTA).  The accumulators are handed back by the
 // softmax warps (acc_free) before the next item's first dV / dK overwrites them.
 // TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384).
-// P and dS are double-buffered (buffer = step & 1) so the softmax warps can build the
-// next tile's P / dS while the tensor core still reads the previous ones for dV / dK.
-constexpr int KV_K = 0, KV_V = FA_TILE_BYTES, KV_Q = 2 * FA_TILE_BYTES, KV_DO = 4 * FA_TILE_BYTES,
-              KV_P = 6 * FA_TILE_BYTES, KV_DS = 8 * FA_TILE_BYTES, KV_PDS_STRIDE = 4 * FA_TILE_BYTES,
-              KV_BAR = 14 * FA_TILE_BYTES, KV_SMEM = KV_BAR + 256 + 1024;
+// Q / dO go through a ring of four stages and P / dS have ONE buffer.  A Q / dO stage is read
+// by S / dP of its step and again by dV / dK of the same step a softmax later; with two stages
+// (and P / dS double-buffered, which is what the shared memory then allowed) the load of step
+// g + 1 waited for dV / dK of step g - 1 and the chain dV / dK -> load -> S / dP set the pace:
+// 2.25 us per step measured against 1.45 us of tensor work.  With one P / dS buffer the softmax
+// warps form the next step's P / dS in registers while the tensor core still reads the buffer
+// for dV / dK, and only their stores wait for it.
+constexpr int KV_STAGES = 4;
+constexpr int KV_K = 0, KV_V = FA_TILE_BYTES, KV_Q = 2 * FA_TILE_BYTES,
+              KV_DO = (2 + KV_STAGES) * FA_TILE_BYTES, KV_P = (2 + 2 * KV_STAGES) * FA_TILE_BYTES,
+              KV_DS = KV_P + 2 * FA_TILE_BYTES, KV_BAR = KV_DS + 2 * FA_TILE_BYTES,
+              KV_SMEM = KV_BAR + 256 + 1024;
+constexpr int KV_NBAR = 14 + 2 * KV_STAGES, KV_QD_FULL = 14, KV_QD_EMPTY = 14 + KV_STAGES;
 constexpr int BW_NBAR = 14;
+static_assert(KV_SMEM <= 227 * 1024, "dK / dV kernel: shared memory");
 
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
@@ -433,18 +486,18 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar = base + KV_BAR;
-  // 0 kv_full, 1-2 qd_full, 3-4 qd_empty, 5 sdp_full, 6 sdp_free, 7/10 pds_full[2],
-  // 8/11 pds_free[2], 9 out_full, 12 kv_free, 13 acc_free
+  // 0 kv_full, 5 sdp_full, 6 sdp_free, 7 pds_full, 8 pds_free, 9 out_full, 12 kv_free,
+  // 13 acc_free, 14.. qd_full[stage], then qd_empty[stage]
   auto B_ = [bar](int i) { return bar + 8u * i; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 128);
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 136);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 192);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + KV_BAR + 200);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int HB = p.H * p.B;
   const int n_items = p.nqt * HB, G = (int)gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < BW_NBAR; ++i)
-      mbar_init(B_(i), (i == 6 || i == 7 || i == 10 || i == 13) ? FA_SOFTMAX_WARPS : 1);
+    for (int i = 0; i < KV_NBAR; ++i)
+      mbar_init(B_(i), (i == 6 || i == 7 || i == 13) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -472,15 +525,16 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
         tma_load_2d(base + KV_K, &tm, B_(0), p.D + h * FA_HD, row0 + k0);
         tma_load_2d(base + KV_V, &tm, B_(0), 2 * p.D + h * FA_HD, row0 + k0);
         for (int it = 0; it < ni; ++it, ++g) {
-          const int s = g & 1;
-          if (!mbar_wait<true>(B_(3 + s), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4100u + s)) {
+          const int s = g % KV_STAGES;
+          const uint32_t ph = (uint32_t)(g / KV_STAGES) & 1u;
+          if (!mbar_wait<true>(B_(KV_QD_EMPTY + s), ph ^ 1u, abort_flag, p.err, 0x4100u + s)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(B_(1 + s), 2 * FA_TILE_BYTES);
+          mbar_expect_tx(B_(KV_QD_FULL + s), 2 * FA_TILE_BYTES);
           const int qrow = row0 + (kt + it) * FA_T;
-          tma_load_2d(base + KV_Q + s * FA_TILE_BYTES, &tm, B_(1 + s), h * FA_HD, qrow);
-          tma_load_2d(base + KV_DO + s * FA_TILE_BYTES, &tmdo, B_(1 + s), h * FA_HD, qrow);
+          tma_load_2d(base + KV_Q + s * FA_TILE_BYTES, &tm, B_(KV_QD_FULL + s), h * FA_HD, qrow);
+          tma_load_2d(base + KV_DO + s * FA_TILE_BYTES, &tmdo, B_(KV_QD_FULL + s), h * FA_HD, qrow);
         }
       }
     }
@@ -496,8 +550,9 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of step g_a
         if (item_a >= n_items) return true;
         if (it_a == 0 && !mbar_wait<true>(B_(0), j_a & 1, abort_flag, p.err, 0x4200u)) return false;
-        const int s = g_a & 1;
-        if (!(mbar_wait<true>(B_(1 + s), (g_a >> 1) & 1, abort_flag, p.err, 0x4300u + s) &&
+        const int s = g_a % KV_STAGES;
+        if (!(mbar_wait<true>(B_(KV_QD_FULL + s), (uint32_t)(g_a / KV_STAGES) & 1u, abort_flag, p.err,
+                              0x4300u + s) &&
               mbar_wait<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
           return false;
         tcgen05_fence_after();
@@ -532,8 +587,8 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           // the softmax warps turn S, dP into P, dS
           ok = issue_sdp();
           if (!ok) break;
-          const int s = g & 1, pb = g & 1;     // Q / dO stage and P / dS buffer of this step
-          ok = mbar_wait<true>(B_(7 + 3 * pb), (g >> 1) & 1, abort_flag, p.err, 0x4500u);
+          const int s = g % KV_STAGES;         // Q / dO stage of this step
+          ok = mbar_wait<true>(B_(7), g & 1, abort_flag, p.err, 0x4500u);     // P / dS written
           if (!ok) break;
           if (it == 0 && j > 0) {              // the previous item's dV / dK have been read out
             ok = mbar_wait<true>(B_(13), (j - 1) & 1, abort_flag, p.err, 0x4a00u);
@@ -541,7 +596,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           }
           tcgen05_fence_after();
           const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
-          const uint32_t sp = base + KV_P + pb * KV_PDS_STRIDE, sds = base + KV_DS + pb * KV_PDS_STRIDE;
+          const uint32_t sp = base + KV_P, sds = base + KV_DS;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)      // K = 128 query rows, 16 at a time
             umma_f16(tdV, make_smem_desc(sp + kk * 2048, FA_TILE_BYTES, 1024),
@@ -550,8 +605,8 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           for (int kk = 0; kk < 8; ++kk)
             umma_f16(tdK, make_smem_desc(sds + kk * 2048, FA_TILE_BYTES, 1024),
                      make_smem_desc(sq + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
-          umma_commit(B_(3 + s));        // Q / dO stage free
-          umma_commit(B_(8 + 3 * pb));   // this P / dS buffer free
+          umma_commit(B_(KV_QD_EMPTY + s));   // Q / dO stage free
+          umma_commit(B_(8));                 // P / dS may be overwritten
           if (it == ni - 1) umma_commit(B_(9));
         }
       }
@@ -664,23 +719,26 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(B_(6));          // S / dP may be overwritten
-        const int pb = g & 1;
-        ok = mbar_wait<true>(B_(8 + 3 * pb), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // buffer free
-        if (!ok) break;
-        uint8_t* sp = gbase + KV_P + pb * KV_PDS_STRIDE;
-        uint8_t* sds = gbase + KV_DS + pb * KV_PDS_STRIDE;
+        // P and dS of this step, packed, in registers; the buffer is still being read
+        uint4 hp[8], hd[8];
         if (need_mask) {
-          bwd_chunk<true>(rs, rdp, 2 * half, r, k0, qi, st, p.cscale, p.scale, nlse, dsc, sp, sds);
-          bwd_chunk<true>(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, p.cscale, p.scale, nlse, dsc,
-                          sp, sds);
+          bwd_chunk_regs<true>(rs, rdp, 2 * half, k0, qi, st, p.cscale, p.scale, nlse, dsc, hp, hd);
+          bwd_chunk_regs<true>(rs + 32, rdp + 32, 2 * half + 1, k0, qi, st, p.cscale, p.scale, nlse, dsc,
+                               hp + 4, hd + 4);
         } else {
-          bwd_chunk<false>(rs, rdp, 2 * half, r, k0, qi, st, p.cscale, p.scale, nlse, dsc, sp, sds);
-          bwd_chunk<false>(rs + 32, rdp + 32, 2 * half + 1, r, k0, qi, st, p.cscale, p.scale, nlse, dsc,
-                           sp, sds);
+          bwd_chunk_regs<false>(rs, rdp, 2 * half, k0, qi, st, p.cscale, p.scale, nlse, dsc, hp, hd);
+          bwd_chunk_regs<false>(rs + 32, rdp + 32, 2 * half + 1, k0, qi, st, p.cscale, p.scale, nlse, dsc,
+                                hp + 4, hd + 4);
         }
+        ok = mbar_wait<true>(B_(8), (g & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // dV / dK of step g - 1 done
+        if (!ok) break;
+        uint8_t* sp = gbase + KV_P;
+        uint8_t* sds = gbase + KV_DS;
+        bwd_chunk_store(2 * half, r, hp, hd, sp, sds);
+        bwd_chunk_store(2 * half + 1, r, hp + 4, hd + 4, sp, sds);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
+        if (lane == 0) mbar_arrive(B_(7));
         if (pend_item >= 0) {      // the previous item's accumulators, now surely complete
           ok = store_item(pend_item, pend_j);
           pend_item = -1;
