@@ -422,6 +422,31 @@ __device__ __forceinline__ void bwd_chunk_store(int c, int r, const uint4* outp,
   }
 }
 
+// Store a warp's block of 32 rows x NU 16-byte groups (lane = row, v[u] = group u of the row)
+// to global rows of `pitch` bytes so that every store instruction writes whole contiguous row
+// segments: the block goes through the warp's private staging area (32 x NU x 16 bytes, XOR
+// swizzled so both passes are conflict-free) and comes back with 32 / NU rows per instruction.
+// One row per lane (128-byte rows 4608 bytes apart for a 768-wide model) measured 1.5 us per
+// item on the softmax warps' critical path.  rows_ok = how many of the 32 rows exist.
+template <int NU>
+__device__ __forceinline__ void warp_store_rows(const uint4 (&v)[NU], uint8_t* stage, int lane,
+                                                uint8_t* dst_row0, size_t pitch, int rows_ok) {
+  static_assert(NU == 4 || NU == 8, "64- or 128-byte row segments");
+#pragma unroll
+  for (int u = 0; u < NU; ++u)
+    *reinterpret_cast<uint4*>(stage + lane * (NU * 16) + ((u ^ (lane & (NU - 1))) << 4)) = v[u];
+  __syncwarp();
+  constexpr int RPI = 32 / NU;        // rows per store instruction
+  const int u = lane % NU;
+#pragma unroll
+  for (int i = 0; i < NU; ++i) {
+    const int row = i * RPI + lane / NU;
+    const uint4 x = *reinterpret_cast<const uint4*>(stage + row * (NU * 16) + ((u ^ (row & (NU - 1))) << 4));
+    if (row < rows_ok) *reinterpret_cast<uint4*>(dst_row0 + (size_t)row * pitch + u * 16) = x;
+  }
+  __syncwarp();
+}
+
 // Column sums of one warp's 32 rows x NC columns (lane = row; fp16 values as stored, 0 for rows
 // that do not exist) without shared memory: a reduce-scatter over the lanes.  Each step halves
 // the columns a lane holds and adds the partner lane's share of the half it keeps, so after five
@@ -463,20 +488,19 @@ __device__ __forceinline__ int snake_item(int j, int G, int c) {
 // at 5.6 us per item when every item was its own CTA).  The accumulators are handed back by the
 // softmax warps (acc_free) before the next item's first dV / dK overwrites them.
 // TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384).
-// Q / dO go through a ring of four stages and P / dS have ONE buffer.  A Q / dO stage is read
+// Q / dO go through a ring of three stages and P / dS have ONE buffer.  A Q / dO stage is read
 // by S / dP of its step and again by dV / dK of the same step a softmax later; with two stages
 // (and P / dS double-buffered, which is what the shared memory then allowed) the load of step
 // g + 1 waited for dV / dK of step g - 1 and the chain dV / dK -> load -> S / dP set the pace:
 // 2.25 us per step measured against 1.45 us of tensor work.  With one P / dS buffer the softmax
 // warps form the next step's P / dS in registers while the tensor core still reads the buffer
 // for dV / dK, and only their stores wait for it.
-constexpr int KV_STAGES = 4;
+constexpr int KV_STAGES = 3;
 constexpr int KV_K = 0, KV_V = FA_TILE_BYTES, KV_Q = 2 * FA_TILE_BYTES,
               KV_DO = (2 + KV_STAGES) * FA_TILE_BYTES, KV_P = (2 + 2 * KV_STAGES) * FA_TILE_BYTES,
-              KV_DS = KV_P + 2 * FA_TILE_BYTES, KV_BAR = KV_DS + 2 * FA_TILE_BYTES,
-              KV_SMEM = KV_BAR + 256 + 1024;
+              KV_DS = KV_P + 2 * FA_TILE_BYTES, KV_OUT = KV_DS + 2 * FA_TILE_BYTES,   // output staging
+              KV_BAR = KV_OUT + 2 * FA_TILE_BYTES, KV_SMEM = KV_BAR + 256 + 1024;
 constexpr int KV_NBAR = 14 + 2 * KV_STAGES, KV_QD_FULL = 14, KV_QD_EMPTY = 14 + KV_STAGES;
-constexpr int BW_NBAR = 14;
 static_assert(KV_SMEM <= 227 * 1024, "dK / dV kernel: shared memory");
 
 __global__ void __launch_bounds__(BW_THREADS, 1)
@@ -636,17 +660,21 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(13));           // the accumulators may be overwritten
-      if (key < p.T) {
-        __half* dst = p.dqkv + (size_t)(row0 + key) * 3 * p.D + (half == 0 ? 2 : 1) * p.D + h * FA_HD;
+      {
+        uint4 hv[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-          __half2 hv[4];
+          __half2 h2[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            hv[e] = __floats2half2_rn(__uint_as_float(rr[u * 8 + 2 * e]),
+            h2[e] = __floats2half2_rn(__uint_as_float(rr[u * 8 + 2 * e]),
                                       __uint_as_float(rr[u * 8 + 2 * e + 1]));
-          *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
+          hv[u] = *reinterpret_cast<uint4*>(h2);
         }
+        const int key_w = k0 + (warp & 3) * 32;      // first key of this warp's 32 rows
+        __half* dst = p.dqkv + (size_t)(row0 + key_w) * 3 * p.D + (half == 0 ? 2 : 1) * p.D + h * FA_HD;
+        warp_store_rows<8>(hv, gbase + KV_OUT + (warp - 2) * 4096, lane, reinterpret_cast<uint8_t*>(dst),
+                           (size_t)3 * p.D * 2, p.T - key_w);
       }
       if (p.colsum) {
         // the qkv bias gradient: column sums of dV / dK as stored
@@ -775,7 +803,9 @@ constexpr int DQ_STAGES = 3;
 constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_K = 2 * FA_TILE_BYTES,
               DQ_V = (2 + DQ_STAGES) * FA_TILE_BYTES, DQ_DS = (2 + 2 * DQ_STAGES) * FA_TILE_BYTES,
               DQ_DS_STRIDE = 2 * FA_TILE_BYTES,   // dS double-buffered
-              DQ_BAR = (6 + 2 * DQ_STAGES) * FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
+              DQ_OUT = (6 + 2 * DQ_STAGES) * FA_TILE_BYTES,    // output staging, one tile
+              DQ_BAR = DQ_OUT + FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
+static_assert(DQ_SMEM <= 227 * 1024, "dQ kernel: shared memory");
 constexpr int DQ_NBAR = 14 + 2 * DQ_STAGES, DQ_KV_FULL = 14, DQ_KV_EMPTY = 14 + DQ_STAGES;
 
 __global__ void __launch_bounds__(BW_THREADS, 1)
@@ -922,17 +952,21 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(13));           // dQ may be overwritten
-      if (q_ok) {
-        __half* dst = p.dqkv + (size_t)(row0 + qi) * 3 * p.D + h * FA_HD + half * 32;
+      {
+        uint4 hv[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          __half2 hv[4];
+          __half2 h2[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            hv[e] = __floats2half2_rn(__uint_as_float(rr[u * 8 + 2 * e]),
+            h2[e] = __floats2half2_rn(__uint_as_float(rr[u * 8 + 2 * e]),
                                       __uint_as_float(rr[u * 8 + 2 * e + 1]));
-          *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
+          hv[u] = *reinterpret_cast<uint4*>(h2);
         }
+        const int q_w = qt * FA_T + (warp & 3) * 32;   // first query row of this warp's 32
+        __half* dst = p.dqkv + (size_t)(row0 + q_w) * 3 * p.D + h * FA_HD + half * 32;
+        warp_store_rows<4>(hv, gbase + DQ_OUT + (warp - 2) * 2048, lane, reinterpret_cast<uint8_t*>(dst),
+                           (size_t)3 * p.D * 2, p.T - q_w);
       }
       if (p.colsum) {
         float val[32];
