@@ -103,6 +103,31 @@ __device__ __forceinline__ float fwd_p_tile(const uint32_t (&r)[64], int key0, i
   return l;
 }
 
+// Store a warp's block of 32 rows x NU 16-byte groups (lane = row, v[u] = group u of the row)
+// to global rows of `pitch` bytes so that every store instruction writes whole contiguous row
+// segments: the block goes through the warp's private staging area (32 x NU x 16 bytes, XOR
+// swizzled so both passes are conflict-free) and comes back with 32 / NU rows per instruction.
+// One row per lane (128-byte rows 4608 bytes apart for a 768-wide model) measured 1.5 us per
+// item on the softmax warps' critical path.  rows_ok = how many of the 32 rows exist.
+template <int NU>
+__device__ __forceinline__ void warp_store_rows(const uint4 (&v)[NU], uint8_t* stage, int lane,
+                                                uint8_t* dst_row0, size_t pitch, int rows_ok) {
+  static_assert(NU == 4 || NU == 8, "64- or 128-byte row segments");
+#pragma unroll
+  for (int u = 0; u < NU; ++u)
+    *reinterpret_cast<uint4*>(stage + lane * (NU * 16) + ((u ^ (lane & (NU - 1))) << 4)) = v[u];
+  __syncwarp();
+  constexpr int RPI = 32 / NU;        // rows per store instruction
+  const int u = lane % NU;
+#pragma unroll
+  for (int i = 0; i < NU; ++i) {
+    const int row = i * RPI + lane / NU;
+    const uint4 x = *reinterpret_cast<const uint4*>(stage + row * (NU * 16) + ((u ^ (row & (NU - 1))) << 4));
+    if (row < rows_ok) *reinterpret_cast<uint4*>(dst_row0 + (size_t)row * pitch + u * 16) = x;
+  }
+  __syncwarp();
+}
+
 __global__ void __launch_bounds__(FA_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -276,17 +301,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       tmem_ld16(tO + t_lane + half * 32, r);
       tmem_ld16(tO + t_lane + half * 32 + 16, r + 16);
       tmem_wait_ld();
-      if (q_ok) {
-        __half* dst = p.out + (size_t)(row0 + qi) * p.D + h * FA_HD + half * 32;
+      {
+        uint4 hv[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          __half2 hv[4];
+          __half2 h2[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            hv[e] = __floats2half2_rn(__uint_as_float(r[u * 8 + 2 * e]) * inv_l,
+            h2[e] = __floats2half2_rn(__uint_as_float(r[u * 8 + 2 * e]) * inv_l,
                                       __uint_as_float(r[u * 8 + 2 * e + 1]) * inv_l);
-          *reinterpret_cast<uint4*>(dst + u * 8) = *reinterpret_cast<uint4*>(hv);
+          hv[u] = *reinterpret_cast<uint4*>(h2);
         }
+        // every product has retired (o_full), so the P buffer serves as the staging area
+        const int q_w = q0 + (warp & 3) * 32;
+        __half* dst = p.out + (size_t)(row0 + q_w) * p.D + h * FA_HD + half * 32;
+        warp_store_rows<4>(hv, gbase + FW_P + (warp - 2) * 2048, lane, reinterpret_cast<uint8_t*>(dst),
+                           (size_t)p.D * 2, p.T - q_w);
       }
     }
   }
@@ -420,31 +450,6 @@ __device__ __forceinline__ void bwd_chunk_store(int c, int r, const uint4* outp,
     *reinterpret_cast<uint4*>(sp + off) = outp[u];
     *reinterpret_cast<uint4*>(sds + off) = outd[u];
   }
-}
-
-// Store a warp's block of 32 rows x NU 16-byte groups (lane = row, v[u] = group u of the row)
-// to global rows of `pitch` bytes so that every store instruction writes whole contiguous row
-// segments: the block goes through the warp's private staging area (32 x NU x 16 bytes, XOR
-// swizzled so both passes are conflict-free) and comes back with 32 / NU rows per instruction.
-// One row per lane (128-byte rows 4608 bytes apart for a 768-wide model) measured 1.5 us per
-// item on the softmax warps' critical path.  rows_ok = how many of the 32 rows exist.
-template <int NU>
-__device__ __forceinline__ void warp_store_rows(const uint4 (&v)[NU], uint8_t* stage, int lane,
-                                                uint8_t* dst_row0, size_t pitch, int rows_ok) {
-  static_assert(NU == 4 || NU == 8, "64- or 128-byte row segments");
-#pragma unroll
-  for (int u = 0; u < NU; ++u)
-    *reinterpret_cast<uint4*>(stage + lane * (NU * 16) + ((u ^ (lane & (NU - 1))) << 4)) = v[u];
-  __syncwarp();
-  constexpr int RPI = 32 / NU;        // rows per store instruction
-  const int u = lane % NU;
-#pragma unroll
-  for (int i = 0; i < NU; ++i) {
-    const int row = i * RPI + lane / NU;
-    const uint4 x = *reinterpret_cast<const uint4*>(stage + row * (NU * 16) + ((u ^ (row & (NU - 1))) << 4));
-    if (row < rows_ok) *reinterpret_cast<uint4*>(dst_row0 + (size_t)row * pitch + u * 16) = x;
-  }
-  __syncwarp();
 }
 
 // Column sums of one warp's 32 rows x NC columns (lane = row; fp16 values as stored, 0 for rows
