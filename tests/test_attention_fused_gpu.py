@@ -75,7 +75,11 @@ def test_forward(dev, B, T, H, packed):
         x.destroy()
 
 
-@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 320, 2), (1, 1024, 2), (2, 72, 1)])
+# The backward kernels are persistent (one CTA per SM takes several (tile, head, sequence)
+# items); the last two cases have 200 and 396 items, i.e. two and three rows of the snake-order
+# dealing on 148 SMs, one of them with a ragged last tile, so item boundaries are crossed.
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 320, 2), (1, 1024, 2), (2, 72, 1),
+                                   (5, 600, 8), (3, 384, 44)])
 @pytest.mark.parametrize("packed", [False, True])
 def test_backward(dev, B, T, H, packed):
     from vkgrad_b200.vk import _check
