@@ -302,6 +302,20 @@ int vkg_split_heads(vkg_device* dev, const float* src, void* dst16, int64_t n,
 int vkg_col_sum_det(vkg_device* dev, const void* g, int g_dtype, float* sums,
                     float* scratch, int ncol, int nrow, int accumulate);
 int64_t vkg_col_sum_scratch_floats(int ncol, int nrow);
+/* Deferred final passes.  The reference issues one dispatch per column-sum stage
+ * (col_sum_zero + col_sum_chunk per bias gradient, transformer.py:30-36; two per
+ * layernorm, tkernels.py:238-270).  Here the producers (vkg_layernorm_bwd with dgamma,
+ * vkg_attn_bwd with dbias, vkg_gemm with colsum) leave partial sums in their scratch and
+ * finish with a short second pass; between vkg_finals_defer(dev, 1) and vkg_finals_flush
+ * those second passes are collected instead of launched and flush runs them all as one
+ * launch.  While deferral is on, every producer call must be given scratch of its own,
+ * which has to stay untouched until the flush has run; the destinations hold their sums
+ * only after the flush.  vkg_finals_defer(dev, 0) with passes pending is an error;
+ * vkg_finals_defer(dev, -1) switches deferral off and drops pending passes (for a
+ * recording that was abandoned half way). */
+int vkg_finals_defer(vkg_device* dev, int on);
+int vkg_finals_flush(vkg_device* dev);
+
 /* No counterpart in the reference.  The same deterministic column sum as
  * vkg_col_sum_det for callers that are not allowed to allocate device memory
  * (a plugin inside a process that owns the allocator, a latency-critical loop,

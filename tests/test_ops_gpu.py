@@ -353,3 +353,78 @@ def test_bucket_pack_roundtrip(dev, pool):
         _check(dev.lib.vkg_bucket_unpack16(dev.handle, b16.dptr, dt, back.dptr, 1000, 0.125), "unpack")
         dev.sync()
         assert relerr(pool.get(back, np.float32, (1000,)), x) < (1e-3 if dt == F16 else 8e-3)
+
+
+def test_deferred_final_passes_equal_immediate_ones(dev, pool, K):
+    """vkg_finals_defer / vkg_finals_flush: layernorm-parameter sums and a column sum whose
+    second passes are collected and run as one launch give what the immediate passes give
+    (to rounding: the collected pass adds each column in 32 slices, the stand-alone column
+    sum in 8), nothing is written before the flush, and a pending list refuses to be
+    switched off."""
+    import ctypes as C
+    from vkgrad_b200.vk import VkError, _check
+    lib, h = dev.lib, dev.handle
+    rows, D = 1024, 256
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((rows, D)).astype(np.float32)
+    dy = rng.standard_normal((rows, D)).astype(np.float32)
+    gamma = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    mu = x.mean(1).astype(np.float32)
+    rstd = (1 / np.sqrt(x.var(1) + 1e-5)).astype(np.float32)
+
+    def up(a):
+        b = dev.buffer(a.nbytes, "cached")
+        b.array(a.dtype, a.shape)[...] = a
+        b.flush()
+        return b
+
+    def down(b, shape):
+        b.invalidate()
+        return b.array(np.float32, shape).copy()
+
+    bx, bdy, bg, bmu, brs = up(x), up(dy), up(gamma), up(mu), up(rstd)
+    dx, dx16 = dev.buffer(rows * D * 4, "device"), dev.buffer(rows * D * 2, "device")
+    n_sc = lib.vkg_layernorm_bwd_scratch_floats(rows, D)
+    results = []
+    for deferred in (False, True):
+        dg, db, dxs = (up(np.full(D, np.nan, np.float32)) for _ in range(3))
+        sc1, sc2 = dev.buffer(n_sc * 4, "device"), dev.buffer(n_sc * 4, "device")
+        if deferred:
+            _check(lib.vkg_finals_defer(h, 1), "defer")
+        # two producers with scratch of their own, as deferral demands
+        _check(lib.vkg_layernorm_bwd(h, bdy.dptr, bx.dptr, bg.dptr, bmu.dptr, brs.dptr, None, dx.dptr,
+                                     dx16.dptr, None, None, dg.dptr, db.dptr, dxs.dptr, sc1.dptr,
+                                     rows, D), "ln_bwd")
+        dg2, db2 = up(np.full(D, np.nan, np.float32)), up(np.full(D, np.nan, np.float32))
+        _check(lib.vkg_layernorm_bwd(h, bx.dptr, bdy.dptr, bg.dptr, bmu.dptr, brs.dptr, None, dx.dptr,
+                                     dx16.dptr, None, None, dg2.dptr, db2.dptr, None, sc2.dptr,
+                                     rows, D), "ln_bwd 2")
+        if deferred:
+            dev.sync()
+            assert np.isnan(down(dg, (D,))).all(), "written before the flush"
+            assert lib.vkg_finals_defer(h, 0) != 0          # two passes are pending
+            _check(lib.vkg_finals_flush(h), "flush")
+            _check(lib.vkg_finals_flush(h), "empty flush")   # nothing left: no launch, no error
+        dev.sync()
+        results.append([down(b, (D,)) for b in (dg, db, dxs, dg2, db2)])
+        for b in (dg, db, dxs, dg2, db2, sc1, sc2):
+            b.destroy()
+    for a, b in zip(*results):
+        assert np.isfinite(a).all() and np.isfinite(b).all()
+        assert np.abs(a - b).max() <= 1e-5 * max(np.abs(a).max(), 1.0)
+    # against numpy: dbeta = column sums of dy
+    assert np.abs(results[1][1] - dy.sum(0)).max() < 1e-3
+    assert np.abs(results[1][4] - x.sum(0)).max() < 1e-3
+    # switching off with nothing pending is fine; -1 drops pending passes
+    _check(lib.vkg_finals_defer(h, 1), "defer")
+    sc = dev.buffer(n_sc * 4, "device")
+    dg, db = up(np.zeros(D, np.float32)), up(np.zeros(D, np.float32))
+    _check(lib.vkg_layernorm_bwd(h, bdy.dptr, bx.dptr, bg.dptr, bmu.dptr, brs.dptr, None, dx.dptr,
+                                 dx16.dptr, None, None, dg.dptr, db.dptr, None, sc.dptr, rows, D), "ln")
+    _check(lib.vkg_finals_defer(h, -1), "drop")
+    _check(lib.vkg_finals_defer(h, 0), "off")
+    dev.sync()
+    assert not down(dg, (D,)).any()
+    for b in (bx, bdy, bg, bmu, brs, dx, dx16, sc, dg, db):
+        b.destroy()
+

@@ -98,6 +98,8 @@ _SIGNATURES = {
     "vkg_layernorm": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32]),
     "vkg_layernorm_bwd": (i32, [vp] + [vp] * 14 + [i32, i32]),
     "vkg_layernorm_bwd_scratch_floats": (i64, [i32, i32]),
+    "vkg_finals_defer": (i32, [vp, i32]),
+    "vkg_finals_flush": (i32, [vp]),
     "vkg_attn_softmax": (i32, [vp, vp, vp, vp, i64, i32, i32, f32, i32]),
     "vkg_attn_softmax_bwd": (i32, [vp, vp, vp, vp, i64, i32, f32, i32]),
     "vkg_attn_fwd": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32]),

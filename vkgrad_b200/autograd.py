@@ -104,6 +104,8 @@ class Ctx:
 
     def destroy(self):
         self.dev.sync()
+        # a recording abandoned half way must not leave deferred passes behind
+        self.dev.lib.vkg_finals_defer(self.dev.handle, -1)
         for b in self._owned:
             b.destroy()
         self._owned = []

@@ -19,6 +19,15 @@
 // Error codes written by kernels into vkg_device::err_flag (host-mapped).
 #define VKG_ERR_WAIT_TIMEOUT 1u   // a bounded mbarrier wait gave up
 
+// One deferred final pass: out[c / D][c % D] (+)= sum over nchunk rows of partial[k][c], c < W,
+// with up to three destinations of D columns each (W = D, 2 D or 3 D).
+struct vkg_final_entry {
+  const float* partial;
+  float* dst[3];
+  int W, D, nchunk, accumulate;
+  int first_block, reserved;
+};
+
 struct vkg_device {
   int ordinal = 0;
   cudaStream_t stream = nullptr;
@@ -36,6 +45,10 @@ struct vkg_device {
   void* encode_tiled = nullptr;
   size_t gemm_smem_optin = 0;
   bool gemm_attr_set = false;
+  // vkg_finals_defer / vkg_finals_flush: final passes of two-stage column sums collected
+  // instead of launched, then run as one launch
+  bool defer_finals = false;
+  std::vector<vkg_final_entry> finals;
 };
 
 struct vkg_graph {
@@ -46,7 +59,8 @@ struct vkg_graph {
 
 void vkg_set_error(const char* fmt, ...);
 
-// ops.cu: sums[c] (+)= sum over nchunk rows of partial[k][c], rows added in a fixed order
+// ops.cu: sums[c] (+)= sum over nchunk rows of partial[k][c], rows added in a fixed order;
+// collected for vkg_finals_flush while vkg_finals_defer is on
 int vkg_launch_col_sum_final(vkg_device* dev, const float* partial, float* sums, int ncol, int nchunk,
                              int accumulate);
 

@@ -986,6 +986,11 @@ extern "C" int64_t vkg_col_sum_scratch_floats(int ncol, int nrow) {
 
 int vkg_launch_col_sum_final(vkg_device* dev, const float* partial, float* sums, int ncol, int nchunk,
                              int accumulate) {
+  if (dev->defer_finals) {
+    dev->finals.push_back(vkg_final_entry{partial, {sums, nullptr, nullptr}, ncol, ncol, nchunk,
+                                          accumulate, 0, 0});
+    return 0;
+  }
   k_col_sum_final<<<(ncol + 31) / 32, 32 * CSF_SLICES, 0, dev->stream>>>(partial, sums, ncol, nchunk,
                                                                          accumulate);
   return vkg_check_launch("col_sum_final");
@@ -1011,6 +1016,77 @@ extern "C" int vkg_col_sum_det(vkg_device* dev, const void* g, int g_dtype, floa
   k_col_sum_final<<<(ncol + 31) / 32, 32 * CSF_SLICES, 0, dev->stream>>>(scratch, sums, ncol, nchunk,
                                                                          accumulate);
   return vkg_check_launch("col_sum_final");
+}
+
+// ---- deferred final passes -------------------------------------------------------------
+//
+// The second stage of a two-stage column sum is a few microseconds of work behind a launch;
+// a GPT-2-small backward has 49 of them (layernorm parameters, qkv and fc1 bias gradients),
+// each between two large kernels.  While deferral is on they are collected on the host and
+// vkg_finals_flush runs them all as ONE launch: the table travels as the kernel's parameter,
+// a CTA finds its entry by its block number.  Results do not depend on timing: each column is
+// added by 32 slices (slice s takes rows s, s + 32, ...) that are then added in order.
+constexpr int FIN_SLICES = 32;
+constexpr int FIN_MAX = 64;      // entries per launch: 64 * 56 bytes stay under the 4 KB limit
+struct FinalTable {
+  int n, reserved;
+  vkg_final_entry e[FIN_MAX];
+};
+
+__global__ void __launch_bounds__(32 * FIN_SLICES)
+k_finals_multi(const __grid_constant__ FinalTable tab) {
+  __shared__ float red[FIN_SLICES][32];
+  int e = 0;
+  while (e + 1 < tab.n && (int)blockIdx.x >= tab.e[e + 1].first_block) ++e;
+  const float* __restrict__ partial = tab.e[e].partial;
+  const int W = tab.e[e].W, D = tab.e[e].D, nchunk = tab.e[e].nchunk;
+  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = ((int)blockIdx.x - tab.e[e].first_block) * 32 + lane;
+  float s = 0.f;
+  if (c < W)
+    for (int k = slice; k < nchunk; k += FIN_SLICES) s += partial[(size_t)k * W + c];
+  red[slice][lane] = s;
+  __syncthreads();
+  if (slice == 0 && c < W) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < FIN_SLICES; ++k) t += red[k][lane];
+    float* d = tab.e[e].dst[c / D] + (c % D);
+    *d = tab.e[e].accumulate ? *d + t : t;
+  }
+}
+
+extern "C" int vkg_finals_defer(vkg_device* dev, int on) {
+  if (vkg_bind(dev)) return 1;
+  if (on < 0) dev->finals.clear();     // drop what an abandoned recording left behind
+  VKG_REQUIRE(on > 0 || dev->finals.empty(), "finals_defer: %d final passes are pending; call vkg_finals_flush",
+              (int)dev->finals.size());
+  dev->defer_finals = on > 0;
+  return 0;
+}
+
+extern "C" int vkg_finals_flush(vkg_device* dev) {
+  if (vkg_bind(dev)) return 1;
+  dev->defer_finals = false;
+  std::vector<vkg_final_entry> todo;
+  todo.swap(dev->finals);
+  for (size_t i0 = 0; i0 < todo.size(); i0 += FIN_MAX) {
+    FinalTable tab;
+    memset(&tab, 0, sizeof(tab));
+    int blocks = 0;
+    for (size_t i = i0; i < todo.size() && i < i0 + FIN_MAX; ++i) {
+      vkg_final_entry en = todo[i];
+      VKG_REQUIRE(en.partial && en.dst[0] && en.W > 0 && en.D > 0 && en.W <= 3 * en.D && en.nchunk > 0 &&
+                      (en.W <= en.D || en.dst[1]) && (en.W <= 2 * en.D || en.dst[2]),
+                  "finals_flush: malformed entry");
+      en.first_block = blocks;
+      blocks += (en.W + 31) / 32;
+      tab.e[tab.n++] = en;
+    }
+    k_finals_multi<<<blocks, 32 * FIN_SLICES, 0, dev->stream>>>(tab);
+    if (vkg_check_launch("finals_multi")) return 1;
+  }
+  return 0;
 }
 
 // ---- column sums for callers that cannot allocate -----------------------------------
@@ -1278,6 +1354,11 @@ extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* 
   if (fused) {
     VKG_REQUIRE(!dxsum || (D % 128 == 0 && D <= 1024 && aligned),
                 "layernorm_bwd: dxsum needs 16-byte aligned operands");
+    if (dev->defer_finals) {
+      dev->finals.push_back(vkg_final_entry{scratch, {dgamma, dbeta, dxsum}, nparts * D, D, nblocks,
+                                            0, 0, 0});
+      return 0;
+    }
     k_ln_param_final<<<(nparts * D + 31) / 32, 32 * LNF_SLICES, 0, dev->stream>>>(
         scratch, dgamma, dbeta, dxsum, D, nblocks, nparts);
     return vkg_check_launch("ln_param_final");

@@ -52,7 +52,8 @@ def _gemm_args(dev, a, b, c, m, n, k, trans_a=False, trans_b=False,
                nb0=1, nb1=1, lda=None, ldb=None, ldc=None, sa=(0, 0), sb=(0, 0), sc=(0, 0),
                a_off=0, b_off=0, c_off=0, in_dtype=F16, c_dtype=F32, bias=None, act=ACT_NONE,
                pre=None, dact_z=None, dact=ACT_NONE, residual=None, c2=None, tile_n=0,
-               max_ctas=0, alpha=1.0, split_k=0, causal=0, cta_pair=0, colsum=None):
+               max_ctas=0, alpha=1.0, split_k=0, causal=0, cta_pair=0, colsum=None,
+               colsum_scratch=None):
     """Fill a vkg_gemm_args (include/vkgrad_b200.h).  Offsets are in elements and apply to
     C, c2, pre, dact_z and residual alike."""
     args = GemmArgs()
@@ -86,9 +87,13 @@ def _gemm_args(dev, a, b, c, m, n, k, trans_a=False, trans_b=False,
     args.cta_pair = int(cta_pair)
     if colsum is not None:
         # column sums of the stored output, folded by the epilogue warps; the partial rows
-        # live in the device scratch until the launch's own final pass has read them
+        # live in scratch until the final pass has read them: the launch's own, or, under
+        # vkg_finals_defer, the collected one, which needs scratch no other call touches
         args.colsum = _ptr(colsum)
-        args.colsum_scratch = dev.scratch(dev.lib.vkg_gemm_colsum_scratch_floats(int(m), int(n)) * 4).dptr
+        need = dev.lib.vkg_gemm_colsum_scratch_floats(int(m), int(n)) * 4
+        if colsum_scratch is not None and colsum_scratch.size < need:
+            raise VkError(f"colsum_scratch holds {colsum_scratch.size} bytes, {need} needed")
+        args.colsum_scratch = (dev.scratch(need) if colsum_scratch is None else colsum_scratch).dptr
         args.split_k = 1
         split_k = 1
     plain = (bias is None and pre is None and dact_z is None and residual is None and c2 is None

@@ -66,6 +66,7 @@ class LayerNorm:
         self.rstd = ctx.buf(rows * 4)
         self.dx = ctx.buf(rows * D * 4)
         self.dx16 = ctx.buf(rows * D * 2)
+        self._scratch = None
 
     def forward(self, x32, graph=None):
         self.x32 = x32
@@ -94,7 +95,11 @@ class LayerNorm:
             raise ValueError("dxsum needs D to be a multiple of 128 and at most 1024")
         dxsum_p = None if dxsum is None else dxsum.dptr
         if D <= _LN_FUSED_MAX_D:
-            scratch = dev.scratch(lib.vkg_layernorm_bwd_scratch_floats(R, D) * 4)
+            # partial parameter sums; private to this layer because the final pass may be a
+            # deferred one (GPT.record collects them into one launch)
+            if self._scratch is None:
+                self._scratch = c.buf(lib.vkg_layernorm_bwd_scratch_floats(R, D) * 4)
+            scratch = self._scratch
 
             def go():
                 _check(lib.vkg_layernorm_bwd(h, dy32.dptr, x32.dptr, self.g.w32.dptr, self.mu.dptr,
@@ -131,6 +136,7 @@ class Dense:
         self.b = Param(ctx, (out_f,), np.zeros(out_f, np.float32), name + ".b", no_decay=True)
         self.acc = None
         self.dx32 = None
+        self._colsum_scratch = None
 
     def forward(self, x16, graph=None, out=None, c_dtype=F32, act=ACT_NONE, pre=None,
                 residual=None, c2=None):
@@ -166,8 +172,14 @@ class Dense:
                 if self.dx32 is None:
                     self.dx32 = c.buf(R * I * 4)
                 dx, dx_dtype = self.dx32, F32
+            cs = None
+            if dx_colsum is not None:
+                # private, because the final pass over it may be a deferred one
+                if self._colsum_scratch is None:
+                    self._colsum_scratch = c.buf(dev.lib.vkg_gemm_colsum_scratch_floats(R, I) * 4)
+                cs = self._colsum_scratch
             gemm(dev, dy16, self.W.w16, dx, R, I, O, trans_b=True, graph=graph, c_dtype=dx_dtype,
-                 dact_z=dact_z, dact=dact, colsum=dx_colsum, name=f"{self.name}.dX")
+                 dact_z=dact_z, dact=dact, colsum=dx_colsum, colsum_scratch=cs, name=f"{self.name}.dX")
         if not bias_grad_done:
             c.col_sum(dy16, self.b.g32, O, R, graph=graph)
         return dx if need_dx else None
@@ -194,6 +206,7 @@ class Attention:
         self.ao16 = ctx.buf(self.rows * D * 2)
         self.dao16 = ctx.buf(self.rows * D * 2)
         self.dqkv16 = ctx.buf(self.rows * 3 * D * 2)
+        self._dbias_scratch = None
         if self.fused:
             self.lse2 = ctx.buf(self.nbh * T * 4)
             self.delta = ctx.shared_buf("attn_delta", self.nbh * T * 4)
@@ -267,8 +280,10 @@ class Attention:
             seg_f = None if self._seg is None else self._seg.dptr
 
             # the kernels that write dqkv also fold its column sums: the qkv bias gradient
-            scratch = c.shared_buf("attn_dbias", 4 * lib.vkg_attn_bwd_dbias_scratch_floats(
-                self.B, T, self.H, hd))
+            if self._dbias_scratch is None:    # private: its final pass may be a deferred one
+                self._dbias_scratch = c.buf(4 * lib.vkg_attn_bwd_dbias_scratch_floats(
+                    self.B, T, self.H, hd))
+            scratch = self._dbias_scratch
 
             def bwd():
                 _check(lib.vkg_attn_bwd(h, self.qkv16.dptr, self.dao16.dptr, self.ao16.dptr,
@@ -452,6 +467,9 @@ class GPT:
         if not backward:
             return
         gh = g(L + 1)
+        # the short second passes of the bias and layernorm-parameter sums (49 in a 12-layer
+        # model) are collected and run as one launch after the last kernel of the backward
+        c.launch(gh, lambda: _check(lib.vkg_finals_defer(h, 1), "finals_defer"), "finals_defer")
         if self.tie:
             # dh = dlogits tok ; head's share of dtok = dlogits^T h (overwrites tok.g32)
             gemm(c.dev, self.dlog16, self.tok.w16, self.dh32, R, D, V, graph=gh, name="head.dX")
@@ -485,6 +503,8 @@ class GPT:
             _check(lib.vkg_embed_bwd(h, d32.dptr, ids_buf.dptr, seg_p, self.tok.g32.dptr,
                                      self.pos.g32.dptr, R * D, D, self.T), "embed_bwd")
         c.launch(ge, emb_bwd, "embed_bwd", R * D * 12)
+        c.launch(ge, lambda: _check(lib.vkg_finals_flush(h), "finals_flush"), "finals_flush",
+                 4 * sum(p.n for p in self.params() if len(p.shape) == 1))
 
     def read_loss(self):
         self.loss.invalidate()
