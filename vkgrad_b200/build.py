@@ -35,8 +35,8 @@ def _digest():
     names = sorted(os.listdir(CSRC)) + ["../../include/vkgrad_b200.h"]
     for name in names:
         path = os.path.join(CSRC, name)
-        if name.startswith(".") or not os.path.isfile(path):
-            continue
+        if name.startswith(".") or not os.path.isfile(path) or name.endswith(".o"):
+            continue        # sources and headers only: object files are products
         h.update(name.encode())
         with open(path, "rb") as f:
             h.update(f.read())
