@@ -1001,10 +1001,8 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
     for (;; ++j) {
       const int item = snake_item(j, G, (int)blockIdx.x);
       if (item >= n_items || !ok) break;
-      const int qt = p.nqt - 1 - item / HB, hb = item % HB;
-      const int h = hb % p.H, b = hb / p.H;
-      const int row0 = b * p.T, q0 = qt * FA_T, nj = qt + 1;
-      const int qi = q0 + r;
+      const int qt = p.nqt - 1 - item / HB, nj = qt + 1;
+      const int qi = qt * FA_T + r;
       const bool q_ok = qi < p.T;
       // this row's statistics were fetched while the previous item was being worked on
       const float nlse = q_ok ? -lse_f : -INFINITY, dsc = -dl_f * p.scale;
