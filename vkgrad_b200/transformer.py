@@ -448,6 +448,9 @@ class GPT:
         submits, with the reference's stage numbering (transformer.py:339-345):
         i < L embedding (stage 0) and block i forward; L head and loss; L+1 head and
         lnf backward; L+2+k block L-1-k backward; 2L+2 embedding backward.
+        Stage graphs must be finished in stage order: the backward collects its short final
+        passes from stage L+1 on and runs them in stage 2L+2 (vkg_finals_defer / _flush act
+        when a graph is finished, not when it is recorded).
         weights: optional per-row loss weights replacing the 1/rows mean; the loss
         buffer then holds each row's unweighted cross entropy, 0 where the weight
         is 0 (kernels.py:793-827).
