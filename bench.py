@@ -16,6 +16,11 @@ Keys beyond the base contract:
   roofline  all tcgen05 GEMM launches of one step, each shape timed with CUDA events
             in this process: achieved = algorithmic FLOP / time, peak = measured
             cuBLAS bf16 burst TFLOP/s of MEASURED_PEAKS.json
+  kernels   the HBM-bound kernels of the step timed alone (CUDA events), against the
+            measured copy bandwidth
+  gaps_ms   ms_per_step minus the sum over every kernel family of count x isolated time
+  gemm_trio the GEMM-trio microbench (BASELINE config 2) with numpy's sgemm beside it
+  c1_mlp    the MLP step of BASELINE config 1 with its numpy twins (SGD and AdamW)
   cpu_baseline  the CPU oracle (numpy restatement of the reference's step) on a
             bounded sample, rank 0 only
 `--impl reference` times that CPU oracle alone with all host threads.
@@ -41,6 +46,24 @@ WORKLOADS = {
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
                   "nvlink_gbs": 770.0}   # nvlink: peer copy per direction measured on this pool
+
+
+def profile_traffic():
+    """DRAM read + write bytes of one launch of the 8192x3072x768 fp32-out GEMM, read from the
+    committed ncu summary of that capture (profiles/); None when the summary is absent."""
+    import re
+    path = os.path.join(ROOT, "profiles", "gemm_tcgen05_8192x3072x768_ncu_full.md")
+    note = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the 8192x3072x768 "
+            "fp32-out shape (algorithmic minimum 118 MB; much of the output is still in L2 when "
+            "the kernel ends), parsed from profiles/gemm_tcgen05_8192x3072x768_ncu_full.md")
+    try:
+        with open(path) as f:
+            m = re.search(r"traffic \(read \+ write\)\s*\|\s*([0-9.]+)\s*MB", f.read())
+        if m:
+            return float(m.group(1)) * 1e6, note
+    except OSError:
+        pass
+    return None, "no ncu summary of the GEMM found under profiles/"
 
 
 def load_peaks():
@@ -102,53 +125,84 @@ class ClockSampler:
 
 
 # ---- CPU oracle arm ---------------------------------------------------------------------
+#
+# The CPU figure is one number, taken one way by both arms: forward + backward of the full
+# model on ONE sequence of the real context length (1 x T tokens; fewer only if the time
+# budget forces it), and AdamW over every parameter timed by itself, because the optimiser
+# is paid once per step whatever the batch.  tokens/s is then quoted for the benchmark's
+# batch: B*T / (B * t_fwd_bwd(1 x T) + t_adamw).
 
-_CPU_PARAMS = {}
+_CPU_STATE = {}
 
 
-def cpu_step_seconds(B, T, D, H, L, V, seed=0, repeats=1):
-    """One full oracle step (fwd + bwd + AdamW on every tensor) at batch B; seconds."""
+def _cpu_state(T, D, H, L, V, seed=0):
     from oracle import vkgrad_numpy as orc
     Vp = (V + 15) // 16 * 16
     key = (T, D, H, L, Vp, seed)
-    if key not in _CPU_PARAMS:
-        _CPU_PARAMS.clear()
-        _CPU_PARAMS[key] = orc.make_gpt_params(D, H, L, T, Vp, seed=seed, tie=True)
-    P = _CPU_PARAMS[key]
-    rng = np.random.default_rng(seed + 1)
+    if _CPU_STATE.get("key") != key:
+        _CPU_STATE.clear()
+        P = orc.make_gpt_params(D, H, L, T, Vp, seed=seed, tie=True)
+        flat = [("tok", None), ("pos", None), ("lnf.g", None), ("lnf.b", None)]
+        flat += [(f"b{l}", k) for l in range(L) for k in P[f"b{l}"]]
+        get = lambda k, kk: P[k] if kk is None else P[k][kk]
+        _CPU_STATE.update(key=key, P=P, flat=flat, t=0,
+                          m={f: np.zeros_like(get(*f)) for f in flat},
+                          v={f: np.zeros_like(get(*f)) for f in flat})
+    return _CPU_STATE
+
+
+def cpu_step_seconds(B, T, D, H, L, V, seed=0):
+    """One oracle step at batch B: (seconds forward+backward, seconds AdamW, loss)."""
+    from oracle import vkgrad_numpy as orc
+    st = _cpu_state(T, D, H, L, V, seed)
+    P = st["P"]
+    rng = np.random.default_rng(seed + 1 + st["t"])
     ids = rng.integers(0, V, B * T).astype(np.uint32)
     tgt = rng.integers(0, V, B * T).astype(np.uint32)
-    best = float("inf")
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        loss, G, _ = orc.gpt_forward_backward(P, ids, tgt, B, T, D, H, L, V)
-        G["tok"] = G["tok"] + G.pop("head.W").T
-        G.pop("head.b")
-        for k, g in G.items():
-            items = g.items() if isinstance(g, dict) else [(None, g)]
-            for kk, gg in items:
-                w = P[k][kk] if kk is not None else P[k]
-                m = np.zeros_like(w)
-                out = orc.adamw_step(w, gg, m, m, 1, wd=0.01 if w.ndim == 2 else 0.0)
-                if kk is not None:
-                    P[k][kk] = out[0]
-                else:
-                    P[k] = out[0]
-        P["head.W"] = P["tok"].T
-        best = min(best, time.perf_counter() - t0)
-    return best, loss
+    t0 = time.perf_counter()
+    loss, G, _ = orc.gpt_forward_backward(P, ids, tgt, B, T, D, H, L, V)
+    G["tok"] = G["tok"] + G.pop("head.W").T
+    G.pop("head.b")
+    t1 = time.perf_counter()
+    st["t"] += 1
+    for k, kk in st["flat"]:
+        w, g = (P[k], G[k]) if kk is None else (P[k][kk], G[k][kk])
+        out = orc.adamw_step(w, g, st["m"][(k, kk)], st["v"][(k, kk)], st["t"], lr=6e-4,
+                             wd=0.01 if w.ndim == 2 else 0.0)
+        if kk is None:
+            P[k] = out[0]
+        else:
+            P[k][kk] = out[0]
+        st["m"][(k, kk)], st["v"][(k, kk)] = out[1], out[2]
+    P["head.W"] = P["tok"].T
+    t2 = time.perf_counter()
+    return t1 - t0, t2 - t1, loss
 
 
-def cpu_sample_shape(name, budget_s, n_steps):
-    """Largest (B, T) sample of the workload whose n_steps fit the time budget."""
+def cpu_sample_T(name, budget_s, n_steps):
+    """Longest sequence (the real context length if it fits) whose n_steps fit the budget.
+    The probe step is a real one and is returned so that it is not wasted."""
     B, T, D, H, L, V = WORKLOADS[name]
-    t_probe, _ = cpu_step_seconds(1, 64, D, H, L, V)
-    per_token = t_probe / 64
-    for cand_T in (T, T // 2, T // 4, T // 8):
-        est = per_token * cand_T * (1.0 + 0.25 * cand_T / T) * n_steps
-        if est <= budget_s:
-            return 1, cand_T
-    return 1, T // 16
+    fb, ad, _ = cpu_step_seconds(1, T, D, H, L, V)
+    if (fb + ad) * n_steps <= budget_s:
+        return T, (fb, ad)
+    for cand in (T // 2, T // 4, T // 8):
+        # forward/backward shrink about linearly with the tokens, AdamW does not shrink
+        if (fb * cand / T + ad) * n_steps <= budget_s:
+            return cand, None
+    return T // 16, None
+
+
+def cpu_line_fields(name, fb, ad, st):
+    """tokens/s for the benchmark's batch from the per-sequence and per-step parts."""
+    B, T, D, H, L, V = WORKLOADS[name]
+    seqs = B * T / st                     # samples of st tokens in one step of the real batch
+    step_s = seqs * fb + ad
+    sample = (f"forward+backward of the full {L}-layer model on 1x{st} tokens "
+              f"({fb * 1e3:.0f} ms) and AdamW over every parameter ({ad * 1e3:.0f} ms), "
+              f"numpy oracle restating the reference's np_model; quoted for the batch of "
+              f"{B}x{T} tokens as {B * T} / ({seqs:.0f} x fwd_bwd + adamw)")
+    return B * T / step_s, step_s, sample
 
 
 def run_reference_arm(args):
@@ -157,30 +211,47 @@ def run_reference_arm(args):
         return
     name = args.workload
     B, T, D, H, L, V = WORKLOADS[name]
-    sb, st = cpu_sample_shape(name, 150.0, args.steps + args.warmup)
-    for _ in range(args.warmup):
-        cpu_step_seconds(sb, st, D, H, L, V)
+    st, probe = cpu_sample_T(name, 240.0, args.steps + args.warmup)
+    done = 1 if (probe is not None and st == T) else 0     # the probe was a warm-up step
+    for _ in range(max(args.warmup - done, 0)):
+        cpu_step_seconds(1, st, D, H, L, V)
+    fb_sum = ad_sum = 0.0
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_step_seconds(sb, st, D, H, L, V)
+        fb, ad, _ = cpu_step_seconds(1, st, D, H, L, V)
+        fb_sum += fb
+        ad_sum += ad
     dt = time.perf_counter() - t0
-    tok_s = args.steps * sb * st / dt
+    fb, ad = fb_sum / args.steps, ad_sum / args.steps
+    tok_s, step_s, sample = cpu_line_fields(name, fb, ad, st)
     cores = os.cpu_count()
-    sample = (f"{sb}x{st} tokens per step, full {L}-layer model, fwd+bwd+AdamW in numpy "
-              f"(oracle/vkgrad_numpy.py restating the reference's np_model)")
+    from oracle import vkgrad_numpy as orc
+    mm_only = orc.matmuls_only_step_seconds(1, st, D, H, L, (V + 15) // 16 * 16)
     line = {
         "impl": "reference", "metric": "gpt_train_tokens_per_s", "value": tok_s, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "tokens_per_step": sb * st, "parallelism": "cpu"},
+        "config": workload_config(name, 1, float(args.loss_scale)),
         "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": sample},
+                         "sample": sample, "fwd_bwd_s": fb, "adamw_s": ad, "sample_tokens": st,
+                         "measured_s": dt,
+                         "matmuls_only_tokens_per_s": st / mm_only,
+                         "matmuls_only_note": "examples/charlm.py:60-96 restated: the reference's "
+                                              "own lower bound, dominant forward matmuls only"},
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def workload_config(name, world, loss_scale):
+    B, T, D, H, L, V = WORKLOADS[name]
+    return {"workload": name, "layers": L, "d_model": D, "heads": H, "ctx": T, "vocab": V,
+            "tied": True, "batch_per_gpu": f"{B}x{T}", "global_batch_tokens": B * T * world,
+            "parallelism": f"dp{world}", "loss_scale": loss_scale, "optimizer": "AdamW",
+            "l2": "working set per step >> 126 MB L2 (no flush needed)"}
 
 
 # ---- GPU arm ---------------------------------------------------------------------------------
@@ -207,8 +278,9 @@ def gemm_shape_table(B, T, D, H, L, V, fused_attention=True):
 
 
 def time_attention(dev, B, T, H, hd):
-    """CUDA-event time of the fused attention forward and backward for one layer."""
-    import ctypes as C
+    """CUDA-event time of the fused attention forward and backward for one layer, on N(0,1)
+    q/k/v and dO, with the qkv bias-gradient sums folded in as in the training step (their
+    short final pass is collected, not launched, also as in the step)."""
     from vkgrad_b200.vk import _check
     D = H * hd
     lib, h = dev.lib, dev.handle
@@ -218,8 +290,10 @@ def time_attention(dev, B, T, H, hd):
     dqkv = dev.buffer(B * T * 3 * D * 2, "device")
     lse = dev.buffer(B * H * T * 4, "device")
     delta = dev.buffer(B * H * T * 4, "device")
-    for b in (qkv, dout):
-        _check(lib.vkg_memset0(h, b.dptr, b.size), "memset")
+    dbias = dev.buffer(3 * D * 4, "device")
+    scratch = dev.buffer(4 * lib.vkg_attn_bwd_dbias_scratch_floats(B, T, H, hd), "device")
+    fill_random16(dev, qkv)
+    fill_random16(dev, dout)
     scale = 1.0 / np.sqrt(hd)
 
     def fwd():
@@ -227,17 +301,93 @@ def time_attention(dev, B, T, H, hd):
 
     def bwd():
         _check(lib.vkg_attn_bwd(h, qkv.dptr, dout.dptr, out.dptr, lse.dptr, None, dqkv.dptr,
-                                delta.dptr, None, None, B, T, H, hd, scale), "bwd")
+                                delta.dptr, dbias.dptr, scratch.dptr, B, T, H, hd, scale), "bwd")
     res = {}
+    _check(lib.vkg_finals_defer(h, 1), "defer")
     for name, fn in (("fwd_us", fwd), ("bwd_us", bwd)):
         dev.run_op(fn, 2)
         res[name] = min(dev.run_op(fn, 10) / 10 for _ in range(3)) * 1e6
+    _check(lib.vkg_finals_defer(h, -1), "defer off")
     flop = 2.0 * (B * H) * T * T * hd
     res["fwd_tflops_full_TxT"] = 2 * flop / res["fwd_us"] / 1e6
     res["bwd_tflops_full_TxT"] = 4 * flop / res["bwd_us"] / 1e6
-    for b in (qkv, dout, out, dqkv, lse, delta):
+    for b in (qkv, dout, out, dqkv, lse, delta, dbias, scratch):
         b.destroy()
     return res
+
+
+def time_row_kernels(dev, rep, hbm_gbs):
+    """The HBM-bound kernels of the step timed alone on the model's own buffers (rotating over
+    the layers so that the working set is larger than L2).  Returns {name: {us, count,
+    bytes, gbs, frac_hbm}}; bytes are the algorithmic bytes per launch."""
+    from vkgrad_b200.vk import _check
+    lib, h = dev.lib, dev.handle
+    m, opt = rep.model, rep.opt
+    R, D, V, Vp, L, T = m.rows, m.D, m.vocab, m.pad_vocab, len(m.blocks), m.T
+    out = {}
+
+    def timed(fns, reps=4):
+        def go():
+            for f in fns:
+                f()
+        dev.run_op(go, 1)
+        return min(dev.run_op(go, reps) / (reps * len(fns)) for _ in range(3))
+
+    def entry(name, t, count, nbytes):
+        out[name] = {"us": t * 1e6, "count": count, "bytes": nbytes, "gbs": nbytes / t / 1e9,
+                     "frac_hbm": nbytes / t / 1e9 / hbm_gbs}
+
+    lns = [ln for b in m.blocks for ln in (b.ln1, b.ln2)] + [m.lnf]
+    fwd = [lambda ln=ln: _check(lib.vkg_layernorm(h, ln.x32.dptr, ln.g.w32.dptr, ln.b.w32.dptr,
+                                                  ln.y16.dptr, ln.mu.dptr, ln.rstd.dptr, R, D), "ln")
+           for ln in lns]
+    entry("layernorm", timed(fwd), len(lns), R * D * 6 + R * 8)
+    if all(ln._scratch is not None for ln in lns):
+        _check(lib.vkg_finals_defer(h, 1), "defer")
+        n = len(lns)
+        bwd = [lambda ln=ln, dy=lns[(i + 1) % n].dx, dres=lns[(i + 2) % n].dx: _check(
+            lib.vkg_layernorm_bwd(h, dy.dptr, ln.x32.dptr, ln.g.w32.dptr, ln.mu.dptr, ln.rstd.dptr,
+                                  dres.dptr, ln.dx.dptr, ln.dx16.dptr, None, None, ln.g.g32.dptr,
+                                  ln.b.g32.dptr, None, ln._scratch.dptr, R, D), "ln_bwd")
+               for i, ln in enumerate(lns)]
+        entry("layernorm_bwd", timed(bwd, reps=2), len(lns), R * D * 18)
+        # the collected final passes: as many entries as a step collects (2 per block + 1
+        # from layernorm, 1 per block each from attention and the fc2-dX epilogue)
+        _check(lib.vkg_finals_defer(h, -1), "drop")
+        n_fin = (2 * L + 1) + 2 * L
+        _check(lib.vkg_finals_defer(h, 1), "defer")
+        for f in (bwd * 3)[:n_fin]:
+            f()
+        dev.sync()
+        t_fin = dev.run_op(lambda: _check(lib.vkg_finals_flush(h), "flush"), 1)
+        entry("finals", t_fin, 1, n_fin * 3 * D * 4 * 256)
+    scale = m.loss_scale / R
+    ce = lambda: _check(lib.vkg_softmax_ce(h, m.logits.dptr, rep_targets(rep).dptr, None,
+                                           m.dlog16.dptr, None, m.loss.dptr, R, Vp, V, scale), "ce")
+    entry("softmax_ce", timed([ce], reps=3), 1, R * Vp * 6)
+    table = opt._get_table(opt.params)
+    n_par = sum(p.n for p in opt.params)
+    ad = lambda: _check(lib.vkg_adamw_multi(h, table, opt.hp.dptr), "adamw")
+    entry("adamw", timed([ad], reps=3), 1, n_par * 30)
+    ids = rep_ids(rep)
+    emb = lambda: _check(lib.vkg_embed(h, m.tok.w32.dptr, m.pos.w32.dptr, ids.dptr, None,
+                                       m.x0.dptr, R * D, D, T), "embed")
+    entry("embed", timed([emb]), 1, R * D * 12)
+
+    def emb_bwd():
+        _check(lib.vkg_memset0(h, m.pos.g32.dptr, m.pos.n * 4), "zero")
+        _check(lib.vkg_embed_bwd(h, m.x0.dptr, ids.dptr, None, m.tok.g32.dptr, m.pos.g32.dptr,
+                                 R * D, D, T), "embed_bwd")
+    entry("embed_bwd", timed([emb_bwd]), 1, R * D * 12)
+    return out
+
+
+def rep_ids(rep):
+    return rep._bench_ids
+
+
+def rep_targets(rep):
+    return rep._bench_targets
 
 
 _RANDOM_BLOCKS = {}
@@ -312,15 +462,13 @@ TRIO_SHAPES = [(m, k, n) for m in (4096, 16384)
                for (k, n) in ((768, 768), (768, 3072), (3072, 768), (1024, 4096))]
 
 
-def run_trio_table(args):
-    """--trio-table: the GEMM-trio microbench, Y = X W, dX = dY W^T, dW = X^T dY with fp32
-    outputs on M in {4096, 16384} x four (K, N); X, dY ~ N(0,1), W ~ N(0, 1/K).  One JSON line."""
-    from vkgrad_b200 import vk
+def trio_summary(dev, peak, warm=3, reps=11, with_cpu=True):
+    """The GEMM-trio microbench: Y = X W, dX = dY W^T, dW = X^T dY with fp32 outputs on
+    M in {4096, 16384} x four (K, N); X, dY ~ N(0,1), W ~ N(0, 1/K).  With with_cpu the same
+    products through numpy's sgemm on the widened operands (kernels.py:606-610), one pass."""
     from vkgrad_b200.kernels import gemm
-    dev = vk.Device(0)
-    peaks, peak_src = load_peaks()
-    peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
-    rows, tot_f, tot_t = [], 0.0, 0.0
+    rows, tot_f, tot_t, cpu_f, cpu_t = [], 0.0, 0.0, 0.0, 0.0
+    rng = np.random.default_rng(5)
     for m, k, n in TRIO_SHAPES:
         x, w, dy = dev.buffer(m * k * 2, "device"), dev.buffer(k * n * 2, "device"), \
             dev.buffer(m * n * 2, "device")
@@ -332,8 +480,7 @@ def run_trio_table(args):
                ("dX", (dy, w, out, m, k, n), {"trans_b": True}),
                ("dW", (x, dy, out, k, n, m), {"trans_a": True})]
         for name, a, kw in ops:
-            gemm(dev, *a, repeat=max(args.warmup, 3), **kw)
-            reps = max(args.steps, 11)
+            gemm(dev, *a, repeat=warm, **kw)
             t = min(gemm(dev, *a, repeat=reps, **kw) / reps for _ in range(3))
             fl = 2.0 * m * n * k
             rows.append({"op": name, "m": m, "k": k, "n": n, "us": t * 1e6, "tflops": fl / t / 1e12,
@@ -342,15 +489,87 @@ def run_trio_table(args):
             tot_t += t
         for b in (x, w, dy, out):
             b.destroy()
-    print(json.dumps({"metric": "gemm_trio_tflops", "value": tot_f / tot_t / 1e12, "unit": "TFLOP/s",
+        if with_cpu:
+            xs = rng.standard_normal((m, k)).astype(np.float16).astype(np.float32)
+            ws = rng.standard_normal((k, n)).astype(np.float16).astype(np.float32)
+            ds = rng.standard_normal((m, n)).astype(np.float16).astype(np.float32)
+            for a, b in ((xs, ws), (ds, ws.T), (xs.T, ds)):
+                t0 = time.perf_counter()
+                np.matmul(a, b)
+                cpu_t += time.perf_counter() - t0
+                cpu_f += 2.0 * m * n * k
+    worst = min(rows, key=lambda r: r["tflops"])
+    best = max(rows, key=lambda r: r["tflops"])
+    res = {"tflops": tot_f / tot_t / 1e12, "frac_of_peak": tot_f / tot_t / 1e12 / peak,
+           "cases": len(rows), "out_dtype": "f32", "worst": worst, "best": best, "rows": rows}
+    if with_cpu:
+        res["cpu_baseline"] = {"value": cpu_f / cpu_t / 1e12, "unit": "TFLOP/s",
+                               "cores": os.cpu_count(), "kind": "port",
+                               "sample": "the same 24 products once each through numpy sgemm"}
+    return res
+
+
+def run_trio_table(args):
+    """--trio-table: the GEMM-trio microbench alone, one JSON line."""
+    from vkgrad_b200 import vk
+    dev = vk.Device(0)
+    peaks, peak_src = load_peaks()
+    peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    r = trio_summary(dev, peak, max(args.warmup, 3), max(args.steps, 11), not args.no_cpu)
+    print(json.dumps({"metric": "gemm_trio_tflops", "value": r["tflops"], "unit": "TFLOP/s",
                       "n_gpus": 1, "higher_is_better": True, "dtype": "f16", "data": "synthetic",
                       "config": {"workload": "gemm-trio", "shapes": len(TRIO_SHAPES), "ops": 3,
                                  "out_dtype": "f32"},
-                      "roofline": {"bound": "tensor", "achieved": tot_f / tot_t / 1e12, "peak": peak,
-                                   "unit": "TFLOP/s", "frac": tot_f / tot_t / 1e12 / peak,
+                      "roofline": {"bound": "tensor", "achieved": r["tflops"], "peak": peak,
+                                   "unit": "TFLOP/s", "frac": r["frac_of_peak"],
                                    "peak_source": peak_src},
-                      "rows": rows}), flush=True)
+                      "cpu_baseline": r.get("cpu_baseline"), "rows": r["rows"]}), flush=True)
     dev.destroy()
+
+
+def c1_mlp_summary(dev, with_cpu=True, steps=200):
+    """BASELINE config 1: MLP 784-256-256-10 (ReLU, softmax cross-entropy, AdamW lr 1e-3),
+    batch 256, one recorded training step replayed `steps` times; beside it the numpy step of
+    examples/mnist.py:83-118 on the same shape, with its SGD update and with AdamW."""
+    import ctypes as C
+    from oracle import vkgrad_numpy as orc
+    from vkgrad_b200.autograd import MLP, AdamW, Ctx, TrainStep
+    from vkgrad_b200.vk import _check
+    x, y, params = orc.make_mlp_case(256, (784, 256, 256), 10, 16, seed=0)
+    ctx = Ctx(dev)
+    try:
+        model = MLP(ctx, 256, [784, 256, 256], 10, pad_classes=16, act="relu")
+        for p, w in zip(model.params(), params):
+            p.set(w)
+        xb, yb = ctx.buf(x.size * 2, "shared"), ctx.buf(256 * 4, "shared")
+        xb.array(np.float16, x.shape)[:] = x
+        yb.array(np.uint32, (256,))[:] = y
+        opt = AdamW(ctx, model.params(), lr=1e-3)
+        step = TrainStep(model, opt, xb, yb)
+        first, _ = step(1e-3)
+        for _ in range(20):
+            opt.advance(1e-3)
+            step.graph.submit_async()
+        dev.sync()
+        _check(dev.lib.vkg_timer_begin(dev.handle), "timer")
+        for _ in range(steps):
+            opt.advance(1e-3)
+            step.graph.submit_async()
+        sec = C.c_double(0.0)
+        _check(dev.lib.vkg_timer_end(dev.handle, C.byref(sec)), "timer")
+        res = {"workload": "mlp 784-256-256-10 relu, batch 256, AdamW", "us_per_step":
+               sec.value / steps * 1e6, "samples_per_s": 256 * steps / sec.value,
+               "launches_per_step": step.graph.n_kernels, "loss_first": first,
+               "loss_last": model.read_loss()}
+    finally:
+        ctx.destroy()
+    if with_cpu:
+        sgd = orc.mlp_train_step_seconds(x, y, params, 10, act="relu", optimizer="sgd")
+        adw = orc.mlp_train_step_seconds(x, y, params, 10, act="relu", optimizer="adamw")
+        res["cpu_baseline"] = {"sgd_us_per_step": sgd * 1e6, "adamw_us_per_step": adw * 1e6,
+                               "value": 256 / adw, "unit": "samples/s", "cores": os.cpu_count(),
+                               "kind": "port", "sample": "best of 20 numpy steps, same shape"}
+    return res
 
 
 def run_single_gemm(args):
@@ -400,6 +619,8 @@ def run_gpu_arm(args):
     peaks, peak_src = load_peaks()
 
     dev = vk.Device(local)
+    if args.pdl is not None:
+        vk._check(dev.lib.vkg_set_pdl(dev.handle, int(args.pdl)), "set_pdl")
     comm = Comm.from_env(dev) if world > 1 else None
     loss_scale = float(args.loss_scale)
 
@@ -420,6 +641,7 @@ def run_gpu_arm(args):
     rep = Replica(dev, build, comm=comm)
     ctx, model = rep.ctx, rep.model
     ids_dev, tgt_dev = ctx.buf(R * 4), ctx.buf(R * 4)
+    rep._bench_ids, rep._bench_targets = ids_dev, tgt_dev
     ids_host, tgt_host = rep.xbuf, rep.ybuf
     rng = np.random.default_rng(1000 + rank)    # each rank its own token stream
     batches = [(rng.integers(0, V, R).astype(np.uint32), rng.integers(0, V, R).astype(np.uint32))
@@ -520,25 +742,33 @@ def run_gpu_arm(args):
         attn = time_attention(dev, B, T, H, D // H) if fused else None
         achieved = flops_total / gemm_t / 1e12
         peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        hbm = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
         alg = step_flops(B, T, D, H, L, V)
+        ms = dt / args.steps * 1e3
+        kernels = time_row_kernels(dev, rep, hbm)
+        # what the launches of a step lose between kernels: step time minus every kernel
+        # family timed alone (same process, same clocks regime, CUDA events)
+        parts = {"gemm": gemm_t * 1e3}
+        if attn is not None:
+            parts["attention"] = L * (attn["fwd_us"] + attn["bwd_us"]) * 1e-3
+        for k, v in kernels.items():
+            parts[k] = v["count"] * v["us"] * 1e-3
+        comm_ms = nvlink["allreduce_ms"] if nvlink is not None else 0.0
+        gaps = ms - sum(parts.values()) - comm_ms
         cpu = None
         if not args.no_cpu:
-            sb, st = cpu_sample_shape(name, 25.0, 1)
-            t_cpu, _ = cpu_step_seconds(sb, st, D, H, L, V)
-            cpu = {"value": sb * st / t_cpu, "unit": "tokens/s", "cores": os.cpu_count(),
-                   "kind": "port",
-                   "sample": f"one step of {sb}x{st} tokens, full {L}-layer model, numpy oracle"}
-        ms = dt / args.steps * 1e3
+            st, probe = cpu_sample_T(name, 40.0, 1)
+            fb, ad = probe if (probe is not None and st == T) else cpu_step_seconds(1, st, D, H, L, V)[:2]
+            tok_s, _, sample = cpu_line_fields(name, fb, ad, st)
+            cpu = {"value": tok_s, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+                   "sample": sample, "fwd_bwd_s": fb, "adamw_s": ad, "sample_tokens": st}
+        traffic, traffic_note = profile_traffic()
         line = {
             "metric": "gpt_train_tokens_per_s", "value": tokens_step * args.steps / dt,
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
-            "config": {"workload": name, "layers": L, "d_model": D, "heads": H, "ctx": T,
-                       "vocab": V, "tied": True, "batch_per_gpu": f"{B}x{T}",
-                       "global_batch_tokens": tokens_step, "parallelism": f"dp{world}",
-                       "loss_scale": loss_scale, "optimizer": "AdamW",
-                       "l2": "working set per step >> 126 MB L2 (no flush needed)"},
+            "config": workload_config(name, world, loss_scale),
             "e2e": {"value": tokens_step * args.steps / dt_e2e, "unit": "tokens/s",
                     "h2d_bytes_per_step": 2 * R * 4, "d2h_bytes_per_step": R * 4,
                     "ms_per_step": dt_e2e / args.steps * 1e3},
@@ -546,15 +776,17 @@ def run_gpu_arm(args):
             "launches_per_step": core.n_kernels,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": 66.1e6, "peak_source": peak_src,
+                         "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                          "kernel": "gemm_tcgen05_kernel, gemm_cta_pair_kernel and gemm_group_kernel "
                                    "(all their launches in one step)",
-                         "traffic_note": "ncu dram read+write bytes of ONE launch of the "
-                                         "8192x3072x768 fp32-out shape (algorithmic minimum 118 MB; "
-                                         "the output largely stays in L2); see profiles/",
+                         "traffic_note": traffic_note,
                          "gemm_ms_per_step": gemm_t * 1e3,
                          "gemm_tflop_per_step": flops_total / 1e12},
             "attention_per_layer": attn,
+            "kernels": kernels,
+            "parts_ms": parts,
+            "gaps_ms": gaps,
+            "pdl": bool(args.pdl) if args.pdl is not None else os.environ.get("VKG_PDL", "1") != "0",
             "step_tensor_frac": alg / (dt / args.steps) / 1e12 / peak,
             "algorithmic_tflop_per_step": alg / 1e12,
             "cpu_baseline": cpu,
@@ -562,6 +794,11 @@ def run_gpu_arm(args):
             "replica_drift": drift,
             "nvlink": nvlink,
         }
+        if world == 1 and not args.no_extras:
+            line["gemm_trio"] = trio_summary(dev, peak, with_cpu=not args.no_cpu)
+            if not args.gemm_trio:
+                line["gemm_trio"].pop("rows")
+            line["c1_mlp"] = c1_mlp_summary(dev, with_cpu=not args.no_cpu)
         if args.gemm_trio:
             line["gemm_shapes"] = rows
     barrier()
@@ -591,6 +828,10 @@ def main():
                     help="GEMM-trio microbench over M in {4096,16384} x four (K,N); one JSON line")
     ap.add_argument("--gemm-trio", action="store_true", help="add per-shape GEMM timings")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle timing")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the GEMM-trio and MLP (BASELINE configs 1 and 2) parts of the line")
+    ap.add_argument("--pdl", type=int, default=None, choices=[0, 1],
+                    help="programmatic dependent launch off / on (default: the library's, on)")
     ap.add_argument("--profile", action="store_true",
                     help="run only the device-resident steps (for an ncu launch list)")
     ap.add_argument("--gemm", default=None,

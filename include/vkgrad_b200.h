@@ -56,6 +56,13 @@ int vkg_device_info(vkg_device* dev, char* name, size_t name_cap, int* sm_count,
                     size_t* total_bytes, int* cc_major, int* cc_minor);
 /* Opaque cudaStream_t of the device, for callers that interoperate. */
 void* vkg_device_stream(vkg_device* dev);
+/* No counterpart in the reference (Vulkan orders dispatches with pipeline barriers).
+ * Programmatic dependent launch for this device's kernels: when on (the default; the
+ * environment variable VKG_PDL=0 starts a device with it off) a kernel may be scheduled
+ * while its predecessor on the stream drains and waits, before its first global access,
+ * until the predecessor has completed.  Results do not depend on the setting.  It is
+ * sampled when a launch is enqueued or recorded. */
+int vkg_set_pdl(vkg_device* dev, int on);
 /* Waits for the stream; reports a kernel error flag (bounded waits that gave
  * up) as a failure, like the reference's 10 s fence timeout (vk.py:1335-1339). */
 int vkg_sync(vkg_device* dev);
@@ -203,9 +210,11 @@ int vkg_bias(vkg_device* dev, const float* acc, const float* bias, float* z,
 /* col_sum (kernels.py:753-761): sums[c] = sum_r g[r*ncol + c], fp32 input. */
 int vkg_col_sum(vkg_device* dev, const float* g, float* sums, int ncol, int nrow);
 /* softmax_ce / softmax_ce_w (kernels.py:766-827).  Per row: loss, and
- * dl = (softmax - onehot) * (w ? w[row] : grad_scale); classes >= ncls are
- * masked to exactly 0.  grad_scale is 1/rows for the reference's mean, times a
- * static loss scale when one is used.  dl16 is written in f16; dl32 optional. */
+ * dl = (softmax - onehot) * (w ? w[row] * (grad_scale ? grad_scale : 1) : grad_scale);
+ * classes >= ncls are masked to exactly 0.  Without weights grad_scale is 1/rows for
+ * the reference's mean, times a static loss scale when one is used; with weights
+ * (which already carry the normalisation) it is the static loss scale alone, 0 or 1
+ * for none.  dl16 is written in f16; dl32 optional. */
 int vkg_softmax_ce(vkg_device* dev, const float* logits, const uint32_t* labels,
                    const float* w, void* dl16, float* dl32, float* loss,
                    int rows, int stride, int ncls, float grad_scale);
@@ -318,14 +327,14 @@ int vkg_finals_flush(vkg_device* dev);
 
 /* No counterpart in the reference.  The same deterministic column sum as
  * vkg_col_sum_det for callers that are not allowed to allocate device memory
- * (a plugin inside a process that owns the allocator, a latency-critical loop,
- * code running inside a stream capture): the partial sums go to a 4 MiB array
+ * (a plugin inside a process that owns the allocator, a latency-critical loop):
+ * the partial sums go to a 4 MiB array
  * built into the library instead of caller scratch, and the call performs no
  * cudaMalloc / cudaFree.  Shapes whose partial sums need more than
  * vkg_col_sum_static_max_floats() floats (see vkg_col_sum_scratch_floats) are
  * refused with an error.  The first call on each device looks the array's
  * device address up (cudaGetSymbolAddress); make that first call before any
- * stream capture begins.  All calls on a device share the one array: two calls
+ * stream capture begins (during a capture it returns an error instead).  All calls on a device share the one array: two calls
  * whose kernels may overlap on the GPU (different streams or devices handles on
  * the same GPU) race on it, so keep them on one stream. */
 int vkg_col_sum_static(vkg_device* dev, const void* g, int g_dtype, float* sums,

@@ -399,3 +399,62 @@ def make_hf_gpt2_tensors(D, H, n_layer, n_ctx, vocab, seed=0, std=0.08, prefix="
     W["ln_f.weight"] = (1 + nrm(D, sd=0.1)).astype(dtype)
     W["ln_f.bias"] = nrm(D, sd=0.1)
     return {prefix + k: v for k, v in W.items()}
+
+
+# -- timed CPU twins the reference itself reports next to its GPU numbers -----------------
+
+def mlp_train_step_seconds(x, labels, params, n_cls, act="gelu", optimizer="sgd", steps=20,
+                           lr=1e-3):
+    """Best-of-`steps` wall time of one full numpy training step of the MLP: forward,
+    backward and the update, like examples/mnist.py:83-118 (which updates with plain SGD,
+    mnist.py:115-116).  optimizer="adamw" replaces the update by the AdamW restatement
+    above on every tensor (weight decay on matrices only, autograd.py:334)."""
+    import time
+    P = [np.array(p, dtype=np.float32) for p in params]
+    M = [np.zeros_like(p) for p in P]
+    V = [np.zeros_like(p) for p in P]
+    x32 = np.asarray(x, dtype=np.float32)
+    best = float("inf")
+    for t in range(1, steps + 1):
+        t0 = time.perf_counter()
+        _, grads = mlp_forward_backward(x32, P, labels, n_cls, act=act)
+        for i, g in enumerate(grads):
+            if optimizer == "sgd":
+                P[i] -= np.float32(lr) * g.astype(np.float32)
+            else:
+                P[i], M[i], V[i], _ = adamw_step(P[i], g, M[i], V[i], t, lr=lr,
+                                                 wd=0.01 if P[i].ndim == 2 else 0.0)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def matmuls_only_step_seconds(B, T, D, H, n_layer, vocab, reps=1):
+    """The reference's own lower bound for a CPU transformer step (examples/charlm.py:60-96):
+    only the dominant matmuls and the attention of a forward pass plus two stand-in
+    backward matmuls per layer, in fp32 numpy; best of `reps`."""
+    import time
+    rows, hd = B * T, D // H
+    rng = np.random.default_rng(0)
+    f = np.float32
+    x = rng.standard_normal((rows, D)).astype(f)
+    w_qkv = rng.standard_normal((D, 3 * D)).astype(f)
+    w_proj = rng.standard_normal((D, D)).astype(f)
+    w_fc1 = rng.standard_normal((D, 4 * D)).astype(f)
+    w_fc2 = rng.standard_normal((4 * D, D)).astype(f)
+    w_head = rng.standard_normal((D, vocab)).astype(f)
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        for _ in range(n_layer):
+            qkv = x @ w_qkv
+            q, k, v = (_heads(qkv[:, i * D:(i + 1) * D], B, T, H, hd) for i in range(3))
+            s = q @ k.transpose(0, 1, 3, 2)
+            s = np.exp(s - s.max(-1, keepdims=True))
+            s /= s.sum(-1, keepdims=True)
+            a = _unheads(s @ v, B, T, H, hd) @ w_proj
+            h = (a @ w_fc1) @ w_fc2
+            _ = h.T @ x          # the two matmuls the reference lets stand for the backward
+            _ = h @ w_fc2.T
+        _ = x @ w_head
+        best = min(best, time.perf_counter() - t0)
+    return best

@@ -175,3 +175,20 @@ def test_bucket_chunks_cover_the_bucket_on_tensor_boundaries():
             seen += ps
         assert seen == params
     assert _bucket_chunks(params[:1], offs[:1], 40, 6) == [(0, 40, params[:1])]
+
+
+def test_arena_refuses_a_second_gpu_without_communicator():
+    from vkgrad_b200.dataparallel import HostArena
+    from vkgrad_b200.vk import VkError
+
+    class FakeDev:
+        def __init__(self, o):
+            self.ordinal = o
+
+        def buffer(self, n, kind):
+            return object()
+    arena = HostArena(16)
+    arena.buffer_for(FakeDev(0))
+    arena.buffer_for(FakeDev(0))
+    with pytest.raises(VkError):
+        arena.buffer_for(FakeDev(1))

@@ -60,6 +60,7 @@ _SIGNATURES = {
     "vkg_device_info": (i32, [vp, C.c_char_p, sz, C.POINTER(i32), C.POINTER(sz),
                               C.POINTER(i32), C.POINTER(i32)]),
     "vkg_device_stream": (vp, [vp]),
+    "vkg_set_pdl": (i32, [vp, i32]),
     "vkg_sync": (i32, [vp]),
     "vkg_alloc": (i32, [vp, sz, i32, C.POINTER(vp), C.POINTER(vp)]),
     "vkg_free": (i32, [vp, vp, vp, i32]),

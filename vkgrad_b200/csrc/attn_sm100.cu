@@ -149,7 +149,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   const int nj = qt + 1;                                 // key tiles 0..qt
   const int row0 = b * p.T;                              // first row of this sequence
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
+    prefetch_tensormap(&tm);
     for (int i = 0; i < 12; ++i) mbar_init(B_(i), (i == 8 || i == 9) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -159,6 +161,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
+  pdl_wait();      // the projection that wrote qkv has completed
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tO = tmem + 128;
 
@@ -247,7 +250,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     int it = 0;
     // pass 1: row maximum of the scaled scores (no exponentials)
     for (int j = 0; j < nj && ok; ++j, ++it) {
-      ok = mbar_wait<true>(B_(7), it & 1, abort_flag, p.err, 0x3100u);
+      ok = mbar_wait_warp<true>(B_(7), it & 1, abort_flag, p.err, 0x3100u);
       if (!ok) break;
       tcgen05_fence_after();
       const bool need_mask = (j == qt) || (p.seg != nullptr);
@@ -269,7 +272,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     asm volatile("bar.sync 1, 256;" ::: "memory");
     // pass 2: P = exp2(t - m) rounded to fp16 (normalised by 1/l at the very end), l in fp32
     for (int j = 0; j < nj && ok; ++j, ++it) {
-      ok = mbar_wait<true>(B_(7), it & 1, abort_flag, p.err, 0x3150u);
+      ok = mbar_wait_warp<true>(B_(7), it & 1, abort_flag, p.err, 0x3150u);
       if (!ok) break;
       tcgen05_fence_after();
       const bool need_mask = (j == qt) || (p.seg != nullptr);
@@ -280,7 +283,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(8));
-      ok = mbar_wait<true>(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x3200u);   // P buffer free
+      ok = mbar_wait_warp<true>(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x3200u);   // P buffer free
       if (!ok) break;
       uint8_t* prow = gbase + FW_P + half * FA_TILE_BYTES + qr * 128;
       if (need_mask) l += fwd_p_tile<true>(r, j * FA_T + half * 64, qi, st, p.cscale, nm, prow, qr & 7);
@@ -294,7 +297,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     l = xchg[qr] + xchg[128 + qr];
     const float inv_l = 1.0f / l;               // l >= 1: key == query is always valid
     if (half == 0 && q_ok) p.lse2[(size_t)(b * p.H + h) * p.T + qi] = m + log2f(l);
-    if (ok) ok = mbar_wait<true>(B_(11), 0, abort_flag, p.err, 0x3300u);
+    if (ok) ok = mbar_wait_warp<true>(B_(11), 0, abort_flag, p.err, 0x3300u);
     if (ok) {
       tcgen05_fence_after();
       uint32_t r[32];                            // this half's 32 of the 64 output columns
@@ -340,6 +343,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
 // delta[row, h] = sum_d dO * O (equals sum_j dP_ij P_ij of tkernels.py:176-179).
 __global__ void attn_delta_kernel(const __half* __restrict__ dout, const __half* __restrict__ out,
                                   float* __restrict__ delta, int B, int T, int H) {
+  pdl_trigger();
+  pdl_wait();
   // eight lanes per (row, head): one 16-byte load of dO and of O each
   const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;   // (row, h)
   const int sub = threadIdx.x & 7;
@@ -524,7 +529,10 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
   const int HB = p.H * p.B;
   const int n_items = p.nqt * HB, G = (int)gridDim.x;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
+    prefetch_tensormap(&tm);
+    prefetch_tensormap(&tmdo);
     for (int i = 0; i < KV_NBAR; ++i)
       mbar_init(B_(i), (i == 6 || i == 7 || i == 13) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
@@ -535,6 +543,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
+  pdl_wait();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 320;
 
@@ -653,7 +662,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       const int kt = item / HB, hb = item % HB;
       const int h = hb % p.H, b = hb / p.H;
       const int row0 = b * p.T, k0 = kt * FA_T;
-      if (!mbar_wait<true>(B_(9), jj & 1, abort_flag, p.err, 0x4800u)) return false;
+      if (!mbar_wait_warp<true>(B_(9), jj & 1, abort_flag, p.err, 0x4800u)) return false;
       tcgen05_fence_after();
       const int key = k0 + r;     // accumulator rows are keys here
       // half 0 stores dV (slice 2 of dqkv), half 1 stores dK (slice 1)
@@ -740,7 +749,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
         const int st = st_n;
         if (it + 1 < ni) row_stat(qi + FA_T, lse_n, dl_n, st_n);
         const bool need_mask = (qt == kt) || (p.seg != nullptr);
-        ok = mbar_wait<true>(B_(5), g & 1, abort_flag, p.err, 0x4600u);
+        ok = mbar_wait_warp<true>(B_(5), g & 1, abort_flag, p.err, 0x4600u);
         if (!ok) break;
         tcgen05_fence_after();
         uint32_t rs[64], rdp[64];
@@ -763,7 +772,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           bwd_chunk_regs<false>(rs + 32, rdp + 32, 2 * half + 1, k0, qi, st, p.cscale, p.scale, nlse, dsc,
                                 hp + 4, hd + 4);
         }
-        ok = mbar_wait<true>(B_(8), (g & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // dV / dK of step g - 1 done
+        ok = mbar_wait_warp<true>(B_(8), (g & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // dV / dK of step g - 1 done
         if (!ok) break;
         uint8_t* sp = gbase + KV_P;
         uint8_t* sds = gbase + KV_DS;
@@ -829,7 +838,10 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   const int HB = p.H * p.B;
   const int n_items = p.nqt * HB, G = (int)gridDim.x;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
+    prefetch_tensormap(&tm);
+    prefetch_tensormap(&tmdo);
     for (int i = 0; i < DQ_NBAR; ++i)
       mbar_init(B_(i), (i == 6 || i == 7 || i == 10 || i == 13) ? FA_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
@@ -840,6 +852,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
+  pdl_wait();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
 
@@ -948,7 +961,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       const int h = hb % p.H, b = hb / p.H;
       const int row0 = b * p.T, qi = qt * FA_T + r;
       const bool q_ok = qi < p.T;
-      if (!mbar_wait<true>(B_(9), jj & 1, abort_flag, p.err, 0x5800u)) return false;
+      if (!mbar_wait_warp<true>(B_(9), jj & 1, abort_flag, p.err, 0x5800u)) return false;
       tcgen05_fence_after();
       uint32_t rr[32];                             // this half's 32 of the 64 dQ columns
       tmem_ld16(tdQ + t_lane + half * 32, rr);
@@ -1013,7 +1026,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       }
       for (int kt = 0; kt < nj && ok; ++kt, ++g) {
         const bool need_mask = (kt == qt) || (p.seg != nullptr);
-        ok = mbar_wait<true>(B_(5), g & 1, abort_flag, p.err, 0x5600u);
+        ok = mbar_wait_warp<true>(B_(5), g & 1, abort_flag, p.err, 0x5600u);
         if (!ok) break;
         tcgen05_fence_after();
         uint32_t rs[64], rdp[64];
@@ -1026,7 +1039,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(B_(6));
         const int pb = g & 1;
-        ok = mbar_wait<true>(B_(8 + 3 * pb), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
+        ok = mbar_wait_warp<true>(B_(8 + 3 * pb), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
         if (!ok) break;
         uint8_t* sds = gbase + DQ_DS + pb * DQ_DS_STRIDE;
         if (need_mask) {
@@ -1113,15 +1126,14 @@ extern "C" int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* 
   p.out = (__half*)out16;
   p.lse2 = lse2;
   p.err = dev->err_dev;
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (!dev->attn_fwd_attr_set) {
     VKG_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   FW_SMEM));
-    attr_set = true;
+    dev->attn_fwd_attr_set = true;
   }
   const long long ctas = (long long)p.nqt * H * B;
   VKG_REQUIRE(ctas < (1ll << 31), "attn_fwd: too many tiles");
-  attn_fwd_kernel<<<(unsigned)ctas, FA_THREADS, FW_SMEM, dev->stream>>>(tm, p);
+  VKG_CUDA(vkg_launch(dev, attn_fwd_kernel, dim3((unsigned)ctas), dim3(FA_THREADS), FW_SMEM, 1, tm, p));
   return vkg_check_launch("attn_fwd_kernel");
 }
 
@@ -1151,26 +1163,25 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
   p.err = dev->err_dev;
   VKG_REQUIRE(!dbias || dbias_scratch, "attn_bwd: dbias needs dbias_scratch");
   p.colsum = dbias ? dbias_scratch : nullptr;
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (!dev->attn_bwd_attr_set) {
     VKG_CUDA(cudaFuncSetAttribute(attn_bwd_kv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   KV_SMEM));
     VKG_CUDA(cudaFuncSetAttribute(attn_bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   DQ_SMEM));
-    attr_set = true;
+    dev->attn_bwd_attr_set = true;
   }
   const long long items = (long long)B * T * H;
   VKG_REQUIRE((((uintptr_t)dout16 | (uintptr_t)out16) & 15) == 0, "attn_bwd: dO and O must be 16-byte aligned");
-  attn_delta_kernel<<<(unsigned)((items * 8 + 255) / 256), 256, 0, dev->stream>>>(
-      (const __half*)dout16, (const __half*)out16, delta, B, T, H);
+  VKG_CUDA(vkg_launch(dev, attn_delta_kernel, dim3((unsigned)((items * 8 + 255) / 256)), dim3(256), 0, 1,
+                      (const __half*)dout16, (const __half*)out16, delta, B, T, H));
   if (vkg_check_launch("attn_delta_kernel")) return 1;
   const long long n_items = (long long)p.nqt * H * B;
   VKG_REQUIRE(n_items < (1ll << 31), "attn_bwd: too many tiles");
   // persistent kernels: one CTA per SM (their shared memory allows no more), items dealt round-robin
   const unsigned ctas = (unsigned)(n_items < dev->sm_count ? n_items : dev->sm_count);
-  attn_bwd_kv_kernel<<<ctas, BW_THREADS, KV_SMEM, dev->stream>>>(tm, tmdo, p);
+  VKG_CUDA(vkg_launch(dev, attn_bwd_kv_kernel, dim3(ctas), dim3(BW_THREADS), KV_SMEM, 1, tm, tmdo, p));
   if (vkg_check_launch("attn_bwd_kv_kernel")) return 1;
-  attn_bwd_q_kernel<<<ctas, BW_THREADS, DQ_SMEM, dev->stream>>>(tm, tmdo, p);
+  VKG_CUDA(vkg_launch(dev, attn_bwd_q_kernel, dim3(ctas), dim3(BW_THREADS), DQ_SMEM, 1, tm, tmdo, p));
   if (vkg_check_launch("attn_bwd_q_kernel")) return 1;
   if (dbias)
     return vkg_launch_col_sum_final(dev, dbias_scratch, dbias, 3 * D, B * p.nqt * 4, 0);

@@ -44,7 +44,13 @@ struct vkg_device {
   // machine without a driver.
   void* encode_tiled = nullptr;
   size_t gemm_smem_optin = 0;
+  // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is per device: one flag per kernel family
   bool gemm_attr_set = false;
+  bool group_attr_set = false;
+  bool attn_fwd_attr_set = false;
+  bool attn_bwd_attr_set = false;
+  // programmatic dependent launch for the kernels of a training step (vkg_set_pdl)
+  bool pdl = true;
   // vkg_finals_defer / vkg_finals_flush: final passes of two-stage column sums collected
   // instead of launched, then run as one launch
   bool defer_finals = false;
@@ -116,6 +122,53 @@ static inline unsigned vkg_blocks(int64_t n, int per_block, int64_t cap = (1ll <
   if (b < 1) b = 1;
   if (b > cap) b = cap;
   return (unsigned)b;
+}
+
+// ---- programmatic dependent launch ------------------------------------------
+//
+// A kernel launched through vkg_launch() may become resident while the kernel before it on
+// the stream is still draining: its CTAs take the SMs the predecessor's last CTAs leave, run
+// their prologue (barrier set-up, TMEM allocation, tensor-map prefetch) and then block in
+// pdl_wait() until the predecessor has completed and its writes are visible.  Rules every such
+// kernel keeps: pdl_wait() is executed by every thread before its first global-memory access
+// (loads, stores and TMA alike, so neither RAW nor WAR hazards arise), also by threads that
+// would return early -- a kernel that could complete without waiting would let ITS successor
+// overtake the predecessor; pdl_trigger() may come first, it only allows the successor to be
+// scheduled once every CTA of this grid has started.  Both are no-ops for a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Launch on the device's stream, with the programmatic-serialisation attribute when the
+// device has it switched on (and `cluster` > 1 for a thread-block cluster along x).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t vkg_launch(vkg_device* dev, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                     size_t smem, int cluster, Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[2];
+  memset(attr, 0, sizeof(attr));
+  int n = 0;
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (dev->pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = (unsigned)n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // ---- device helpers shared by the elementwise kernels ----------------------

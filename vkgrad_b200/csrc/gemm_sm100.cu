@@ -352,7 +352,7 @@ __device__ __forceinline__ bool epilogue_unit(const CtaCtx& cx, const GemmParams
     kb_range(p, tc, kb0, nkb);
     if (nkb <= 0) return true;
   }
-  if (!mbar_wait(cx.tfull0 + 8 * acc, acc_phase, cx.abort_flag, p.err, 0x400u + acc)) return false;
+  if (!mbar_wait_warp(cx.tfull0 + 8 * acc, acc_phase, cx.abort_flag, p.err, 0x400u + acc)) return false;
   tcgen05_fence_after();
   // TMEM gives each lane one row; the chunk is transposed through shared memory so
   // that global loads and stores are row-contiguous (4 lanes x 16 B per row).  Rows
@@ -471,12 +471,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  pdl_trigger();
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
   }
   CtaCtx cx;
   cta_setup(cx, smem_raw, p.bn, p.stages);
+  pdl_wait();      // barriers, TMEM and tensor maps are ready; operands may still be in flight
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * (p.split_k > 1 ? p.split_k : p.nb1);
@@ -534,9 +536,12 @@ gemm_group_kernel(const GroupEntry* __restrict__ table, int n_problems, int tota
                   int stages) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ int first[GROUP_MAX];
+  pdl_trigger();
+  // the table was written by the host long before this launch, not by the kernel before it
   for (int i = threadIdx.x; i < n_problems; i += blockDim.x) first[i] = table[i].first_unit;
   CtaCtx cx;
   cta_setup(cx, smem_raw, bn, stages);     // its __syncthreads also publishes first[]
+  pdl_wait();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   if (warp == 0) {
@@ -734,7 +739,7 @@ __device__ __forceinline__ bool pair_epilogue_unit(const CtaCtx& cx, const GemmP
     kb_range(p, tc, kb0, nkb);
     if (nkb <= 0) return true;
   }
-  if (!mbar_wait(cx.tfull0 + 8 * acc, acc_phase, cx.abort_flag, p.err, 0x800u + acc)) return false;
+  if (!mbar_wait_warp(cx.tfull0 + 8 * acc, acc_phase, cx.abort_flag, p.err, 0x800u + acc)) return false;
   tcgen05_fence_after();
   uint8_t* stage = cx.epi_stage + (warp - 2) * EPI_STAGE_BYTES;
   const int sub_row = lane >> 2;
@@ -789,12 +794,14 @@ gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
+  pdl_trigger();
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
   }
   CtaCtx cx;
   pair_setup(cx, smem_raw);
+  pdl_wait();
   const int n_pairs = (int)gridDim.x >> 1, pair = (int)blockIdx.x >> 1;
   const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * (p.split_k > 1 ? p.split_k : p.nb1);
   if (warp == 0) {
@@ -825,12 +832,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_group_pair_kernel(const GroupEntry* __restrict__ table, int n_problems, int total_units) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ int first[GROUP_MAX];
+  pdl_trigger();
   for (int i = threadIdx.x; i < n_problems; i += blockDim.x) first[i] = table[i].first_unit;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   CtaCtx cx;
   pair_setup(cx, smem_raw);       // its __syncthreads also publishes first[]
+  pdl_wait();
   const int n_pairs = (int)gridDim.x >> 1, pair = (int)blockIdx.x >> 1;
   if (warp == 0) {
     if (lane == 0) {
@@ -868,6 +877,8 @@ gemm_group_pair_kernel(const GroupEntry* __restrict__ table, int n_problems, int
 // Adds the K slices of a split GEMM in slice order and writes C (fp32, row pitch ldc).
 __global__ void k_splitk_reduce(const float4* __restrict__ ws, float* __restrict__ C, int M, int N4,
                                 long long ldc, int splits) {
+  pdl_trigger();
+  pdl_wait();
   const long long per = (long long)M * N4;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per;
        i += (long long)gridDim.x * blockDim.x) {
@@ -909,6 +920,7 @@ const Specialised kCtaPair[] = {
     VKG_SPEC_CP(E_BIAS | E_RES),
     VKG_SPEC_CP(E_BIAS | E_PRE | E_ACT | E_F16),
     VKG_SPEC_CP(E_DACT | E_F16),
+    VKG_SPEC_CP(E_DACT | E_F16 | E_COLSUM),
 };
 const int kNumCtaPair = sizeof(kCtaPair) / sizeof(kCtaPair[0]);
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1144,8 +1156,9 @@ GemmKernel pick_kernel(int mode) {
 int reduce_slices(vkg_device* dev, const vkg_gemm_args* a, const GemmParams& p) {
   if (p.split_k <= 1) return 0;
   const long long n4 = (long long)a->M * (a->N / 4);
-  k_splitk_reduce<<<vkg_blocks(n4, 256, (int64_t)dev->sm_count * 8), 256, 0, dev->stream>>>(
-      (const float4*)a->workspace, (float*)a->C, a->M, a->N / 4, a->ldc, p.split_k);
+  VKG_CUDA(vkg_launch(dev, k_splitk_reduce, dim3(vkg_blocks(n4, 256, (int64_t)dev->sm_count * 8)),
+                      dim3(256), 0, 1, (const float4*)a->workspace, (float*)a->C, a->M, a->N / 4,
+                      (long long)a->ldc, p.split_k));
   return vkg_check_launch("splitk_reduce");
 }
 
@@ -1240,40 +1253,25 @@ extern "C" int vkg_gemm_group_launch(vkg_device* dev, const void* table, int n, 
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(table && n > 0 && n <= GROUP_MAX && total_units != 0, "gemm_group: bad arguments");
   if (ensure_attrs(dev)) return 1;
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (!dev->group_attr_set) {
     VKG_CUDA(cudaFuncSetAttribute(gemm_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   SMEM_BYTES));
     VKG_CUDA(cudaFuncSetAttribute(gemm_group_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   SMEM_BYTES));
-    attr_set = true;
+    dev->group_attr_set = true;
   }
   if (total_units < 0) {
     const int units = -total_units;
     int pairs = dev->sm_count / 2;
     if (pairs > units) pairs = units;
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
-    cfg.stream = dev->stream;
-    cudaLaunchAttribute attr;
-    memset(&attr, 0, sizeof(attr));
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    VKG_CUDA(cudaLaunchKernelEx(&cfg, gemm_group_pair_kernel, static_cast<const GroupEntry*>(table), n,
-                                units));
+    VKG_CUDA(vkg_launch(dev, gemm_group_pair_kernel, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
+                        SMEM_BYTES, 2, static_cast<const GroupEntry*>(table), n, units));
     return vkg_check_launch("gemm_group_pair_kernel");
   }
   int ctas = dev->sm_count < total_units ? dev->sm_count : total_units;
   const int stages = RING_BYTES / (A_STAGE_BYTES + 256 * 128);
-  gemm_group_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(
-      static_cast<const GroupEntry*>(table), n, total_units, 256, stages);
+  VKG_CUDA(vkg_launch(dev, gemm_group_kernel, dim3((unsigned)ctas), dim3(NUM_THREADS), SMEM_BYTES, 1,
+                      static_cast<const GroupEntry*>(table), n, total_units, 256, stages));
   return vkg_check_launch("gemm_group_kernel");
 }
 
@@ -1302,21 +1300,8 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
       if (kCtaPair[i].mode == q.mode) fn = kCtaPair[i].fn;
     long long pairs = dev->sm_count / 2;
     if (pairs > q.total_tiles) pairs = q.total_tiles;
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
-    cfg.stream = dev->stream;
-    cudaLaunchAttribute attr;
-    memset(&attr, 0, sizeof(attr));
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    VKG_CUDA(cudaLaunchKernelEx(&cfg, fn, q.tmA, q.tmB, q.p));
+    VKG_CUDA(vkg_launch(dev, fn, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS), SMEM_BYTES, 2, q.tmA,
+                        q.tmB, q.p));
     if (vkg_check_launch("gemm_cta_pair_kernel")) return 1;
     if (reduce_slices(dev, a, q.p)) return 1;
     return finish_colsum(dev, a, 2 * BM);
@@ -1325,7 +1310,8 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   if (ensure_attrs(dev)) return 1;
   int ctas = a->max_ctas > 0 ? a->max_ctas : dev->sm_count;
   if (ctas > q.total_tiles) ctas = (int)q.total_tiles;
-  pick_kernel(q.mode)<<<ctas, NUM_THREADS, SMEM_BYTES, dev->stream>>>(q.tmA, q.tmB, q.p);
+  VKG_CUDA(vkg_launch(dev, pick_kernel(q.mode), dim3((unsigned)ctas), dim3(NUM_THREADS), SMEM_BYTES, 1,
+                      q.tmA, q.tmB, q.p));
   if (vkg_check_launch("gemm_tcgen05_kernel")) return 1;
   if (reduce_slices(dev, a, q.p)) return 1;
   return finish_colsum(dev, a, BM);

@@ -218,6 +218,8 @@ __global__ void k_embed_bwd(const float* __restrict__ dx, const uint32_t* __rest
 __global__ void k_embed_v4(const float4* __restrict__ tok, const float4* __restrict__ pos,
                            const uint32_t* __restrict__ ids, const uint32_t* __restrict__ seg,
                            float4* __restrict__ x, int n4, int D4, int T) {
+  pdl_trigger();
+  pdl_wait();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
     const int bt = i / D4, d = i - bt * D4;
     int t = bt % T;
@@ -230,6 +232,8 @@ __global__ void k_embed_v4(const float4* __restrict__ tok, const float4* __restr
 __global__ void k_embed_bwd_v4(const float4* __restrict__ dx, const uint32_t* __restrict__ ids,
                                const uint32_t* __restrict__ seg, float4* __restrict__ dtok,
                                float4* __restrict__ dpos, int n4, int D4, int T) {
+  pdl_trigger();
+  pdl_wait();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
     const int bt = i / D4, d = i - bt * D4;
     int t = bt % T;
@@ -360,7 +364,8 @@ k_softmax_ce(const float* __restrict__ logits, const uint32_t* __restrict__ labe
   float* d32 = dl32 ? dl32 + (int64_t)row * stride : nullptr;
   float wi = grad_scale;
   if (w) {
-    wi = w[row];
+    // per-row weights replace the mean; a non-zero grad_scale then is a static loss scale
+    wi = w[row] * (grad_scale != 0.0f ? grad_scale : 1.0f);
     if (wi == 0.0f) {
       for (int c = threadIdx.x; c < stride; c += TPB) {
         if (d16) d16[c] = __float2half_rn(0.f);
@@ -428,6 +433,8 @@ __global__ void __launch_bounds__(CE_THREADS)
 k_softmax_ce_reg(const float* __restrict__ logits, const uint32_t* __restrict__ labels,
                  const float* __restrict__ w, __half* __restrict__ dl16, float* __restrict__ dl32,
                  float* __restrict__ loss, int stride, int ncls, float grad_scale, int pf_rows) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float s_red[CE_THREADS / 32];
   __shared__ float s_bcast;
   const int row = blockIdx.x;
@@ -437,7 +444,7 @@ k_softmax_ce_reg(const float* __restrict__ logits, const uint32_t* __restrict__ 
   float wi = grad_scale;
   bool skip = false;
   if (w) {
-    wi = w[row];
+    wi = w[row] * (grad_scale != 0.0f ? grad_scale : 1.0f);
     skip = wi == 0.0f;
   }
   float4 v[NV];
@@ -557,6 +564,8 @@ __global__ void k_layernorm_vec(const float* __restrict__ x, const float* __rest
                                 const float* __restrict__ beta, __half* __restrict__ y16,
                                 float* __restrict__ mu, float* __restrict__ rstd, int rows) {
   constexpr int D = NV * 128;
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
   if (row >= rows) return;
@@ -702,6 +711,8 @@ k_layernorm_bwd_vec(const float* __restrict__ dy, const float* __restrict__ x,
                     float* __restrict__ dx, __half* __restrict__ dx16,
                     float* __restrict__ scratch, int rows, int nparts) {
   constexpr int D = NV * 128;
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[LNV_WARPS][32 * 4 + 4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float4 g[NV], ag[NV], ab[NV], ax[NV];   // ax: column sums of the output (nparts == 3)
@@ -880,6 +891,8 @@ constexpr int ADAM_CHUNK = 4096;  // elements per block
 __global__ void __launch_bounds__(TPB)
 k_adamw_multi(const AdamTensor* __restrict__ tensors, const int2* __restrict__ blockmap,
               const float* __restrict__ hp) {
+  pdl_trigger();
+  pdl_wait();
   const float lr = hp[0], b1 = hp[1], b2 = hp[2], bc1 = hp[3], bc2 = hp[4], eps = hp[5];
   const float gs = hp[6] != 0.0f ? hp[6] : 1.0f;
   const int2 bm = blockmap[blockIdx.x];
@@ -1035,6 +1048,8 @@ struct FinalTable {
 
 __global__ void __launch_bounds__(32 * FIN_SLICES)
 k_finals_multi(const __grid_constant__ FinalTable tab) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[FIN_SLICES][32];
   int e = 0;
   while (e + 1 < tab.n && (int)blockIdx.x >= tab.e[e + 1].first_block) ++e;
@@ -1083,7 +1098,7 @@ extern "C" int vkg_finals_flush(vkg_device* dev) {
       blocks += (en.W + 31) / 32;
       tab.e[tab.n++] = en;
     }
-    k_finals_multi<<<blocks, 32 * FIN_SLICES, 0, dev->stream>>>(tab);
+    VKG_CUDA(vkg_launch(dev, k_finals_multi, dim3((unsigned)blocks), dim3(32 * FIN_SLICES), 0, 1, tab));
     if (vkg_check_launch("finals_multi")) return 1;
   }
   return 0;
@@ -1092,9 +1107,8 @@ extern "C" int vkg_finals_flush(vkg_device* dev) {
 // ---- column sums for callers that cannot allocate -----------------------------------
 //
 // Some hosts of this library may not call cudaMalloc once they are running: a plugin
-// loaded into a process whose memory pool is owned by someone else, a real-time loop
-// that must not take the allocator's locks, or code between the begin and end of a
-// stream capture, where allocation is refused.  For them the partial sums of the
+// loaded into a process whose memory pool is owned by someone else, or a real-time loop
+// that must not take the allocator's locks.  For them the partial sums of the
 // two-stage column reduction live in a fixed array inside the library image instead
 // of caller-provided scratch.  Every GPU that loads the library carries the array
 // (4 MiB) until the process exits.
@@ -1113,6 +1127,12 @@ int colsum_static_address(vkg_device* dev, float** out) {
   if (it != g_colsum_static_ptr.end()) {
     *out = it->second;
     return 0;
+  }
+  if (dev->capturing) {
+    // the look-up may load the module, which is not allowed while a stream is being captured
+    vkg_set_error("col_sum_static: the first call on a device sets the array's address up and "
+                  "must come before any stream capture on that device");
+    return 1;
   }
   float* ptr = nullptr;
   cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_colsum_static);
@@ -1173,9 +1193,9 @@ extern "C" int vkg_softmax_ce(vkg_device* dev, const float* logits, const uint32
     // wide rows: one read of the logits, everything else from registers
     const int nv = (n4 + CE_THREADS - 1) / CE_THREADS;
 #define VKG_CE(NV)                                                                              \
-  k_softmax_ce_reg<NV><<<rows, CE_THREADS, 0, dev->stream>>>(logits, labels, w, (__half*)dl16, dl32, \
-                                                             loss, stride, ncls, grad_scale,     \
-                                                             dev->sm_count * (NV <= 8 ? 2 : 1))
+  VKG_CUDA(vkg_launch(dev, k_softmax_ce_reg<NV>, dim3((unsigned)rows), dim3(CE_THREADS), 0, 1, logits, \
+                      labels, w, (__half*)dl16, dl32, loss, stride, ncls, grad_scale,             \
+                      dev->sm_count * (NV <= 8 ? 2 : 1)))
     if (nv <= 8) VKG_CE(8);
     else if (nv <= 12) VKG_CE(12);
     else VKG_CE(17);
@@ -1243,7 +1263,8 @@ extern "C" int vkg_adamw_multi(vkg_device* dev, void* table, const float* hp) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(table && hp, "adamw_multi: bad arguments");
   AdamTable* t = (AdamTable*)table;
-  k_adamw_multi<<<t->nblocks, TPB, 0, dev->stream>>>(t->tensors, t->blockmap, hp);
+  VKG_CUDA(vkg_launch(dev, k_adamw_multi, dim3((unsigned)t->nblocks), dim3(TPB), 0, 1, t->tensors,
+                      t->blockmap, hp));
   return vkg_check_launch("adamw_multi");
 }
 
@@ -1269,7 +1290,8 @@ extern "C" int vkg_layernorm(vkg_device* dev, const float* x, const float* gamma
   if (aligned && D % 128 == 0 && D <= 1024) {
     const unsigned grid = (rows + wpb - 1) / wpb;
 #define VKG_LN(NV) \
-  k_layernorm_vec<NV><<<grid, wpb * 32, 0, dev->stream>>>(x, gamma, beta, (__half*)y16, mu, rstd, rows)
+  VKG_CUDA(vkg_launch(dev, k_layernorm_vec<NV>, dim3(grid), dim3(wpb * 32), 0, 1, x, gamma, beta, \
+                      (__half*)y16, mu, rstd, rows))
     switch (D / 128) {
       case 1: VKG_LN(1); break;
       case 2: VKG_LN(2); break;
@@ -1305,8 +1327,9 @@ static void launch_ln_bwd_vec(vkg_device* dev, int nblocks, const float* dy, con
                               const float* gamma, const float* mu, const float* rstd,
                               const float* dres, float* dx, void* dx16, float* scratch, int rows,
                               int nparts) {
-  k_layernorm_bwd_vec<NV><<<nblocks, LNV_WARPS * 32, 0, dev->stream>>>(
-      dy, x, gamma, mu, rstd, dres, dx, (__half*)dx16, scratch, rows, nparts);
+  // a failed launch is picked up by the caller's vkg_check_launch
+  vkg_launch(dev, k_layernorm_bwd_vec<NV>, dim3((unsigned)nblocks), dim3(LNV_WARPS * 32), 0, 1, dy, x,
+             gamma, mu, rstd, dres, dx, (__half*)dx16, scratch, rows, nparts);
 }
 
 extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* x, const float* gamma,
@@ -1425,8 +1448,8 @@ extern "C" int vkg_embed(vkg_device* dev, const float* tok, const float* pos, co
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(tok && pos && ids && x && n > 0, "embed: bad arguments");
   if (D % 4 == 0 && n < (1ll << 31) && ((((uintptr_t)tok | (uintptr_t)pos | (uintptr_t)x) & 15) == 0)) {
-    k_embed_v4<<<flat_grid(dev, n / 4), TPB, 0, dev->stream>>>(
-        (const float4*)tok, (const float4*)pos, ids, seg, (float4*)x, (int)(n / 4), D / 4, T);
+    VKG_CUDA(vkg_launch(dev, k_embed_v4, dim3(flat_grid(dev, n / 4)), dim3(TPB), 0, 1, (const float4*)tok,
+                        (const float4*)pos, ids, seg, (float4*)x, (int)(n / 4), D / 4, T));
     return vkg_check_launch("embed_v4");
   }
   k_embed<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(tok, pos, ids, seg, x, n, D, T);
@@ -1438,8 +1461,8 @@ extern "C" int vkg_embed_bwd(vkg_device* dev, const float* dx, const uint32_t* i
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(dx && ids && dtok && dpos && n > 0, "embed_bwd: bad arguments");
   if (D % 4 == 0 && n < (1ll << 31) && ((((uintptr_t)dx | (uintptr_t)dtok | (uintptr_t)dpos) & 15) == 0)) {
-    k_embed_bwd_v4<<<flat_grid(dev, n / 4), TPB, 0, dev->stream>>>(
-        (const float4*)dx, ids, seg, (float4*)dtok, (float4*)dpos, (int)(n / 4), D / 4, T);
+    VKG_CUDA(vkg_launch(dev, k_embed_bwd_v4, dim3(flat_grid(dev, n / 4)), dim3(TPB), 0, 1,
+                        (const float4*)dx, ids, seg, (float4*)dtok, (float4*)dpos, (int)(n / 4), D / 4, T));
     return vkg_check_launch("embed_bwd_v4");
   }
   k_embed_bwd<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(dx, ids, seg, dtok, dpos, n, D, T);

@@ -3,6 +3,8 @@
 // (vk.Device / vk.Buffer / vk.Graph); nothing here computes.
 #include "common.cuh"
 
+#include <cstdlib>
+
 static thread_local char g_err[1024] = "";
 
 void vkg_set_error(const char* fmt, ...) {
@@ -69,7 +71,16 @@ extern "C" int vkg_device_create(int ordinal, vkg_device** out) {
     VKG_FAIL("cuTensorMapEncodeTiled is not available from this driver");
   }
   d->encode_tiled = fn;
+  const char* pdl = getenv("VKG_PDL");
+  d->pdl = !(pdl && pdl[0] == '0');
   *out = d;
+  return 0;
+}
+
+extern "C" int vkg_set_pdl(vkg_device* dev, int on) {
+  if (!dev) VKG_FAIL("null device");
+  VKG_REQUIRE(!dev->capturing, "set_pdl: not while a graph is being recorded");
+  dev->pdl = on != 0;
   return 0;
 }
 

@@ -79,6 +79,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same wait for a whole warp that goes on to a .sync.aligned instruction (tcgen05.ld) or
+// a __syncwarp: all 32 lanes must call it.  Each lane polls on its own, then the warp votes, so
+// either every lane carries on or every lane leaves -- a lane that ran out of budget at the
+// very moment the phase completed for its neighbours cannot strand them in the aligned
+// instruction that follows.
+template <bool SPIN = false>
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               uint32_t* err, uint32_t where,
+                                               long long budget = WAIT_BUDGET_CYCLES) {
+  const bool ok = mbar_wait<SPIN>(bar, parity, abort_flag, err, where, budget);
+  return __all_sync(0xffffffffu, ok);
+}
+
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
   asm volatile(

@@ -180,6 +180,12 @@ class HostArena:
     def buffer_for(self, dev):
         key = dev.ordinal
         if key not in self._buffers:
+            if self._buffers:
+                # device memory of one GPU: replicas on another GPU would each sum into a
+                # private arena and still divide by n_workers
+                raise VkError(f"HostArena already lives on GPU {next(iter(self._buffers))}; "
+                              f"replicas on GPU {key} exchange gradients through a Comm "
+                              f"(NCCL all-reduce), not through the arena")
             self._buffers[key] = dev.buffer(self.nbytes, "device")
         return self._buffers[key]
 

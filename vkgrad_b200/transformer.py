@@ -461,7 +461,8 @@ class GPT:
         R, V, D = self.rows, self.pad_vocab, self.D
         logits = self.forward(ids_buf, graph=g, seg=seg)
         w_p = None if weights is None else weights.dptr
-        scale = self.loss_scale / R
+        # per-row weights carry their own normalisation; the static loss scale multiplies both
+        scale = self.loss_scale / R if weights is None else self.loss_scale
 
         def ce():
             _check(lib.vkg_softmax_ce(h, logits.dptr, targets_buf.dptr, w_p, self.dlog16.dptr, None,
