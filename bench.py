@@ -786,7 +786,7 @@ def run_gpu_arm(args):
             "kernels": kernels,
             "parts_ms": parts,
             "gaps_ms": gaps,
-            "pdl": bool(args.pdl) if args.pdl is not None else os.environ.get("VKG_PDL", "1") != "0",
+            "pdl": bool(args.pdl) if args.pdl is not None else os.environ.get("VKG_PDL", "0") == "1",
             "step_tensor_frac": alg / (dt / args.steps) / 1e12 / peak,
             "algorithmic_tflop_per_step": alg / 1e12,
             "cpu_baseline": cpu,
@@ -831,7 +831,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the GEMM-trio and MLP (BASELINE configs 1 and 2) parts of the line")
     ap.add_argument("--pdl", type=int, default=None, choices=[0, 1],
-                    help="programmatic dependent launch off / on (default: the library's, on)")
+                    help="programmatic dependent launch off / on (default: the library's, off)")
     ap.add_argument("--profile", action="store_true",
                     help="run only the device-resident steps (for an ncu launch list)")
     ap.add_argument("--gemm", default=None,

@@ -57,15 +57,43 @@ int vkg_device_info(vkg_device* dev, char* name, size_t name_cap, int* sm_count,
 /* Opaque cudaStream_t of the device, for callers that interoperate. */
 void* vkg_device_stream(vkg_device* dev);
 /* No counterpart in the reference (Vulkan orders dispatches with pipeline barriers).
- * Programmatic dependent launch for this device's kernels: when on (the default; the
- * environment variable VKG_PDL=0 starts a device with it off) a kernel may be scheduled
- * while its predecessor on the stream drains and waits, before its first global access,
- * until the predecessor has completed.  Results do not depend on the setting.  It is
- * sampled when a launch is enqueued or recorded. */
+ * Programmatic dependent launch for this device's kernels: when on, a kernel may be
+ * scheduled while its predecessor on the stream drains and waits, before its first global
+ * access, until the predecessor has completed.  Results do not depend on the setting.  It
+ * is sampled when a launch is enqueued or recorded.  Off by default (the environment
+ * variable VKG_PDL=1 starts a device with it on): back-to-back eager launches of one
+ * kernel gain about 2 %, but a recorded training step measured 0.1 to 0.4 ms SLOWER with
+ * programmatic edges in its CUDA graph, whichever kernel families carried them. */
 int vkg_set_pdl(vkg_device* dev, int on);
+/* No counterpart in the reference.  Switches that change how kernels are launched, never
+ * what they compute; sampled when a launch is enqueued or recorded, so two recordings of
+ * the same step can be compared in one process.
+ *   VKG_TUNE_PDL           0 / 1, same as vkg_set_pdl
+ *   VKG_TUNE_PDL_FAMILIES  bit mask of kernel families programmatic launch applies to
+ *                          (1 GEMM, 2 CTA-pair GEMM, 4 grouped GEMM, 8 attention forward,
+ *                          16 attention backward, 32 layernorm, 64 layernorm backward,
+ *                          128 softmax-CE, 256 AdamW, 512 the small kernels)
+ *   VKG_TUNE_TMA_STORE     0: GEMM epilogues store per lane; 1 (default): epilogues
+ *                          without fused reads store their tiles through tensor maps
+ *   VKG_TUNE_WAIT_TIMEOUT_MS  limit of a host wait on a device that has a communicator
+ *                          (default 60 000): see vkg_sync */
+enum { VKG_TUNE_PDL = 0, VKG_TUNE_PDL_FAMILIES = 1, VKG_TUNE_TMA_STORE = 2,
+       VKG_TUNE_WAIT_TIMEOUT_MS = 3 };
+int vkg_set_tuning(vkg_device* dev, int key, int64_t value);
 /* Waits for the stream; reports a kernel error flag (bounded waits that gave
- * up) as a failure, like the reference's 10 s fence timeout (vk.py:1335-1339). */
+ * up) as a failure, like the reference's 10 s fence timeout (vk.py:884-888, 1335-1339).
+ * While a communicator is attached to the device this and every other host wait
+ * (vkg_timer_end, vkg_graph_launch, vkg_download, vkg_comm_max_double) polls against a
+ * deadline instead of blocking: on an asynchronous NCCL error, or when the limit expires (a
+ * collective whose peer never arrived), the communicator is aborted with ncclCommAbort,
+ * the call fails, and later collectives on that communicator fail at once. */
 int vkg_sync(vkg_device* dev);
+/* No counterpart in the reference.  Runs the deadline loop of the host waits against a
+ * scripted device, without a GPU: "done" after ready_after_polls queries (negative: never),
+ * an asynchronous communicator error from its async_error_at-th check on (negative:
+ * never).  Returns what the wait returns; *aborted = number of aborts issued. */
+int vkg_selftest_wait_deadline(int64_t ready_after_polls, int64_t async_error_at,
+                               double timeout_s, int* aborted);
 
 /* dev.buffer(size, kind) (vk.py:1256, memory kinds vk.py:1161-1200).
  * kind 0 "device": HBM only.  kind 1 "shared": pinned, mapped host memory the

@@ -192,3 +192,37 @@ def test_arena_refuses_a_second_gpu_without_communicator():
     arena.buffer_for(FakeDev(0))
     with pytest.raises(VkError):
         arena.buffer_for(FakeDev(1))
+
+
+# ---- bounded host waits (the analogue of the reference's 10 s fence timeout, vk.py:884-888) ----
+
+def _wait_selftest(ready_after, error_at, timeout_s):
+    import ctypes as C
+    from vkgrad_b200 import _lib
+    lib = _lib.load()
+    aborted = C.c_int32(-1)
+    rc = lib.vkg_selftest_wait_deadline(ready_after, error_at, timeout_s, C.byref(aborted))
+    return rc, aborted.value, _lib.last_error()
+
+
+def test_host_wait_returns_when_the_device_finishes():
+    rc, aborted, _ = _wait_selftest(500, -1, 5.0)
+    assert rc == 0 and aborted == 0
+
+
+def test_host_wait_gives_up_at_the_deadline_and_aborts_the_communicator():
+    import time
+    t0 = time.perf_counter()
+    rc, aborted, msg = _wait_selftest(-1, -1, 0.2)
+    dt = time.perf_counter() - t0
+    assert rc != 0 and aborted == 1
+    assert "did not finish within" in msg and "aborted" in msg
+    assert 0.2 <= dt < 2.0
+
+
+def test_host_wait_reports_an_asynchronous_communicator_error_before_the_deadline():
+    import time
+    t0 = time.perf_counter()
+    rc, aborted, msg = _wait_selftest(-1, 3, 30.0)
+    assert rc != 0 and aborted == 1 and "asynchronous error" in msg
+    assert time.perf_counter() - t0 < 5.0

@@ -61,7 +61,9 @@ _SIGNATURES = {
                               C.POINTER(i32), C.POINTER(i32)]),
     "vkg_device_stream": (vp, [vp]),
     "vkg_set_pdl": (i32, [vp, i32]),
+    "vkg_set_tuning": (i32, [vp, i32, i64]),
     "vkg_sync": (i32, [vp]),
+    "vkg_selftest_wait_deadline": (i32, [i64, i64, C.c_double, C.POINTER(i32)]),
     "vkg_alloc": (i32, [vp, sz, i32, C.POINTER(vp), C.POINTER(vp)]),
     "vkg_free": (i32, [vp, vp, vp, i32]),
     "vkg_upload": (i32, [vp, vp, vp, sz]),

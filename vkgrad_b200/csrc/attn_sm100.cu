@@ -1133,7 +1133,7 @@ extern "C" int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* 
   }
   const long long ctas = (long long)p.nqt * H * B;
   VKG_REQUIRE(ctas < (1ll << 31), "attn_fwd: too many tiles");
-  VKG_CUDA(vkg_launch(dev, attn_fwd_kernel, dim3((unsigned)ctas), dim3(FA_THREADS), FW_SMEM, 1, tm, p));
+  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_FWD, attn_fwd_kernel, dim3((unsigned)ctas), dim3(FA_THREADS), FW_SMEM, 1, tm, p));
   return vkg_check_launch("attn_fwd_kernel");
 }
 
@@ -1172,16 +1172,16 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
   }
   const long long items = (long long)B * T * H;
   VKG_REQUIRE((((uintptr_t)dout16 | (uintptr_t)out16) & 15) == 0, "attn_bwd: dO and O must be 16-byte aligned");
-  VKG_CUDA(vkg_launch(dev, attn_delta_kernel, dim3((unsigned)((items * 8 + 255) / 256)), dim3(256), 0, 1,
+  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_delta_kernel, dim3((unsigned)((items * 8 + 255) / 256)), dim3(256), 0, 1,
                       (const __half*)dout16, (const __half*)out16, delta, B, T, H));
   if (vkg_check_launch("attn_delta_kernel")) return 1;
   const long long n_items = (long long)p.nqt * H * B;
   VKG_REQUIRE(n_items < (1ll << 31), "attn_bwd: too many tiles");
   // persistent kernels: one CTA per SM (their shared memory allows no more), items dealt round-robin
   const unsigned ctas = (unsigned)(n_items < dev->sm_count ? n_items : dev->sm_count);
-  VKG_CUDA(vkg_launch(dev, attn_bwd_kv_kernel, dim3(ctas), dim3(BW_THREADS), KV_SMEM, 1, tm, tmdo, p));
+  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_kv_kernel, dim3(ctas), dim3(BW_THREADS), KV_SMEM, 1, tm, tmdo, p));
   if (vkg_check_launch("attn_bwd_kv_kernel")) return 1;
-  VKG_CUDA(vkg_launch(dev, attn_bwd_q_kernel, dim3(ctas), dim3(BW_THREADS), DQ_SMEM, 1, tm, tmdo, p));
+  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_q_kernel, dim3(ctas), dim3(BW_THREADS), DQ_SMEM, 1, tm, tmdo, p));
   if (vkg_check_launch("attn_bwd_q_kernel")) return 1;
   if (dbias)
     return vkg_launch_col_sum_final(dev, dbias_scratch, dbias, 3 * D, B * p.nqt * 4, 0);

@@ -21,6 +21,8 @@ struct NcclApi {
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   const char* (*GetLastError)(ncclComm_t) = nullptr;
+  int (*CommAbort)(ncclComm_t) = nullptr;
+  int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
 };
 
 NcclApi g_nccl;
@@ -50,6 +52,8 @@ int load_nccl() {
       h, "ncclAllReduce");
   api.GetErrorString = (const char* (*)(int))dlsym(h, "ncclGetErrorString");
   api.GetLastError = (const char* (*)(ncclComm_t))dlsym(h, "ncclGetLastError");
+  api.CommAbort = (int (*)(ncclComm_t))dlsym(h, "ncclCommAbort");
+  api.CommGetAsyncError = (int (*)(ncclComm_t, int*))dlsym(h, "ncclCommGetAsyncError");
   if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllReduce ||
       !api.GetErrorString) {
     vkg_set_error("libnccl is missing a required symbol");
@@ -74,6 +78,26 @@ struct vkg_comm {
   cudaEvent_t ev_fork = nullptr;
   cudaEvent_t ev_done[VKG_COMM_SLOTS] = {};
 };
+
+// Hooks the device's host waits call while this communicator is attached (common.cuh).
+static int comm_async_error(void* ctx) {
+  vkg_comm* c = static_cast<vkg_comm*>(ctx);
+  if (!c->comm || !g_nccl.CommGetAsyncError) return 0;
+  int state = 0;
+  if (g_nccl.CommGetAsyncError(c->comm, &state) != 0 || state != 0) {
+    vkg_set_error("NCCL reported an asynchronous error: %s",
+                  g_nccl.GetErrorString ? g_nccl.GetErrorString(state) : "?");
+    return 1;
+  }
+  return 0;
+}
+
+static void comm_abort(void* ctx) {
+  vkg_comm* c = static_cast<vkg_comm*>(ctx);
+  if (c->comm && g_nccl.CommAbort) g_nccl.CommAbort(c->comm);
+  else if (c->comm) g_nccl.CommDestroy(c->comm);
+  c->comm = nullptr;     // every later collective on it fails instead of hanging
+}
 
 #define VKG_NCCL(expr)                                                              \
   do {                                                                              \
@@ -128,12 +152,20 @@ extern "C" int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint
     VKG_FAIL("comm_create: first collective failed (%s / %s)", r ? g_nccl.GetErrorString(r) : "ok",
              cudaGetErrorString(e));
   }
+  dev->wait_ctx = c;
+  dev->on_async_error = comm_async_error;
+  dev->on_abort = comm_abort;
   *out = c;
   return 0;
 }
 
 extern "C" int vkg_comm_destroy(vkg_comm* comm) {
   if (!comm) return 0;
+  if (comm->dev && comm->dev->wait_ctx == comm) {
+    comm->dev->wait_ctx = nullptr;
+    comm->dev->on_async_error = nullptr;
+    comm->dev->on_abort = nullptr;
+  }
   if (comm->dev) cudaSetDevice(comm->dev->ordinal);
   if (comm->dev) cudaStreamSynchronize(comm->dev->stream);
   if (comm->side) {
@@ -151,6 +183,7 @@ extern "C" int vkg_comm_destroy(vkg_comm* comm) {
 
 extern "C" int vkg_allreduce_sum(vkg_comm* comm, void* buf, int64_t count, int dtype) {
   VKG_REQUIRE(comm && buf && count > 0, "allreduce: bad arguments");
+  VKG_REQUIRE(comm->comm, "allreduce: the communicator was aborted");
   if (vkg_bind(comm->dev)) return 1;
   int t = dtype == VKG_F32 ? NCCL_FLOAT32 : dtype == VKG_F16 ? NCCL_FLOAT16 : dtype == VKG_BF16 ? NCCL_BFLOAT16 : -1;
   VKG_REQUIRE(t >= 0, "allreduce: unknown dtype %d", dtype);
@@ -186,6 +219,7 @@ extern "C" int vkg_comm_side_begin(vkg_comm* comm) {
 extern "C" int vkg_allreduce_sum_side(vkg_comm* comm, void* buf, int64_t count, int dtype, int slot) {
   VKG_REQUIRE(comm && buf && count > 0 && slot >= 0 && slot < VKG_COMM_SLOTS,
               "allreduce_side: bad arguments (slot 0..%d)", VKG_COMM_SLOTS - 1);
+  VKG_REQUIRE(comm->comm, "allreduce_side: the communicator was aborted");
   if (vkg_bind(comm->dev)) return 1;
   if (side_init(comm)) return 1;
   int t = dtype == VKG_F32 ? NCCL_FLOAT32 : dtype == VKG_F16 ? NCCL_FLOAT16 : dtype == VKG_BF16 ? NCCL_BFLOAT16 : -1;
@@ -204,14 +238,14 @@ extern "C" int vkg_comm_side_wait(vkg_comm* comm, int slot) {
 
 extern "C" int vkg_comm_max_double(vkg_comm* comm, double* value) {
   VKG_REQUIRE(comm && value, "comm_max_double: bad arguments");
+  VKG_REQUIRE(comm->comm, "comm_max_double: the communicator was aborted");
   if (vkg_bind(comm->dev)) return 1;
   cudaStream_t s = comm->dev->stream;
   VKG_CUDA(cudaMemcpyAsync(comm->scratch_dev, value, sizeof(double), cudaMemcpyHostToDevice, s));
   VKG_NCCL(g_nccl.AllReduce(comm->scratch_dev, comm->scratch_dev, 1, NCCL_FLOAT64, NCCL_MAX,
                             comm->comm, s));
   VKG_CUDA(cudaMemcpyAsync(value, comm->scratch_dev, sizeof(double), cudaMemcpyDeviceToHost, s));
-  VKG_CUDA(cudaStreamSynchronize(s));
-  return 0;
+  return vkg_wait_device(comm->dev, nullptr, "comm_max_double");
 }
 
 extern "C" int vkg_comm_barrier(vkg_comm* comm) {

@@ -50,7 +50,18 @@ struct vkg_device {
   bool attn_fwd_attr_set = false;
   bool attn_bwd_attr_set = false;
   // programmatic dependent launch for the kernels of a training step (vkg_set_pdl)
-  bool pdl = true;
+  // GEMM epilogues without fused reads store C through tensor maps (VKG_TMA_STORE=0: per lane)
+  bool tma_store = true;
+  bool pdl = false;
+  unsigned pdl_mask = 0xffffffffu;   // kernel families (VKG_K_*) it applies to
+  // While a communicator is attached, host waits on this device poll against a deadline
+  // instead of blocking: a collective whose peer never arrives must not hang the process.
+  // on_async_error returns non-zero (and sets the error text) when the communicator reports a
+  // failure; on_abort tears the communicator down so the stream can drain.
+  void* wait_ctx = nullptr;
+  int (*on_async_error)(void* ctx) = nullptr;
+  void (*on_abort)(void* ctx) = nullptr;
+  double wait_timeout_s = 60.0;
   // vkg_finals_defer / vkg_finals_flush: final passes of two-stage column sums collected
   // instead of launched, then run as one launch
   bool defer_finals = false;
@@ -64,6 +75,21 @@ struct vkg_graph {
 };
 
 void vkg_set_error(const char* fmt, ...);
+
+// The deadline loop of every host wait (runtime.cu).  query() returns 0 when the work is done,
+// 1 when it is still running, anything else on a failure it has already described with
+// vkg_set_error.  Without an abort hook the loop is a plain blocking wait on `query`.
+struct vkg_wait_hooks {
+  int (*query)(void* ctx);
+  void* query_ctx;
+  int (*async_error)(void* ctx);
+  void (*abort)(void* ctx);
+  void* comm_ctx;
+  double timeout_s;
+};
+int vkg_wait_with_deadline(const vkg_wait_hooks* h, const char* what);
+// Waits for the device's stream (ev == nullptr) or for an event recorded on it.
+int vkg_wait_device(vkg_device* dev, cudaEvent_t ev, const char* what);
 
 // ops.cu: sums[c] (+)= sum over nchunk rows of partial[k][c], rows added in a fixed order;
 // collected for vkg_finals_flush while vkg_finals_defer is on
@@ -137,14 +163,21 @@ static inline unsigned vkg_blocks(int64_t n, int per_block, int64_t cap = (1ll <
 // scheduled once every CTA of this grid has started.  Both are no-ops for a plain launch.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() {
+#ifndef VKG_PDL_NO_TRIGGER
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
 }
 
 // Launch on the device's stream, with the programmatic-serialisation attribute when the
 // device has it switched on (and `cluster` > 1 for a thread-block cluster along x).
+enum : unsigned {
+  VKG_K_GEMM = 1, VKG_K_GEMM_PAIR = 2, VKG_K_GEMM_GROUP = 4, VKG_K_ATTN_FWD = 8, VKG_K_ATTN_BWD = 16,
+  VKG_K_LN = 32, VKG_K_LN_BWD = 64, VKG_K_CE = 128, VKG_K_ADAMW = 256, VKG_K_SMALL = 512
+};
+
 template <typename... KArgs, typename... Args>
-static inline cudaError_t vkg_launch(vkg_device* dev, void (*kernel)(KArgs...), dim3 grid, dim3 block,
-                                     size_t smem, int cluster, Args&&... args) {
+static inline cudaError_t vkg_launch(vkg_device* dev, unsigned family, void (*kernel)(KArgs...),
+                                     dim3 grid, dim3 block, size_t smem, int cluster, Args&&... args) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = grid;
@@ -161,7 +194,7 @@ static inline cudaError_t vkg_launch(vkg_device* dev, void (*kernel)(KArgs...), 
     attr[n].val.clusterDim.z = 1;
     ++n;
   }
-  if (dev->pdl) {
+  if (dev->pdl && (dev->pdl_mask & family)) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;

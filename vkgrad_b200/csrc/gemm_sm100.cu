@@ -65,6 +65,7 @@ struct GemmParams {
   const float* residual;
   float* colsum;               // optional: [4 * row blocks][N] partial column sums of the output
   float alpha;
+  int tma_store;               // epilogue stores C (and pre) through tensor maps
   uint32_t* err;
 };
 
@@ -262,6 +263,93 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, float4 (&v)[
   }
 }
 
+// Epilogues that only WRITE (plain, bias, bias + keep z + activation, narrowing) can leave the
+// transposition to the TMA: the warp keeps the TMEM layout (lane = row, 16 columns), applies
+// the fused arithmetic in registers, writes its 32 x 16 chunk into the staging area in the
+// hardware's swizzled layout and one lane issues a tensor-map store of the box.  Compared
+// with the per-lane path this drops the shared-memory read-back, the address arithmetic, the
+// predicates (the box is clipped at the tensor's edge) and the global store instructions.
+constexpr int E_NO_TMA = E_DACT | E_RES | E_C2 | E_COLSUM | E_GENERIC;
+
+// 32 x 16 fp32: 64-byte rows, 16-byte piece j of row r at ((j ^ ((r >> 1) & 3)) << 4) -- the
+// 64-byte swizzle of the tensor map, and conflict-free for one-row-per-lane writes.
+__device__ __forceinline__ void stage_chunk_f32(const float (&v)[16], uint8_t* stage, int lane) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<float4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+        make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+}
+
+// 32 x 16 halves: 32-byte rows, piece j of row r at ((j ^ ((r >> 2) & 1)) << 4) (32-byte swizzle)
+template <bool BF>
+__device__ __forceinline__ void stage_chunk_16(const float (&v)[16], uint8_t* stage, int lane) {
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    uint4 pk;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (BF) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
+        w[e] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
+        w[e] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(stage + lane * 32 + ((j ^ ((lane >> 2) & 1)) << 4)) = pk;
+  }
+}
+
+// One 32 x 16 chunk (rows row0.., columns col..) through the write-only epilogue.  The staging
+// area is reused as soon as the previous store has finished reading it; bulk async-groups
+// belong to the issuing thread, so lane 0 waits and the warp meets it.
+template <int MODE>
+__device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CUtensorMap* tmC,
+                                                   const CUtensorMap* tmP, const uint32_t (&r)[16],
+                                                   uint8_t* stage, int lane, int col, int row0, int z0,
+                                                   int z1) {
+  float v[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+  if (MODE & E_BIAS) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (col + 4 * g < p.N) {       // N is a multiple of 8, the chunk may reach 8 past it
+        const float4 b = *reinterpret_cast<const float4*>(p.bias + col + 4 * g);
+        v[4 * g] += b.x; v[4 * g + 1] += b.y; v[4 * g + 2] += b.z; v[4 * g + 3] += b.w;
+      }
+    }
+  }
+  const uint32_t stage_s = smem_u32(stage);
+  if (MODE & E_PRE) {
+    if (lane == 0) bulk_wait_read_all();
+    __syncwarp();
+    stage_chunk_f32(v, stage, lane);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_4d(tmP, stage_s, col, row0, z0, z1);
+      bulk_commit_group();
+    }
+  }
+  if (MODE & E_ACT) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = vkg_act(v[j], p.act);
+  }
+  if (lane == 0) bulk_wait_read_all();
+  __syncwarp();
+  if (MODE & E_F16) stage_chunk_16<false>(v, stage, lane);
+  else if (MODE & E_BF16) stage_chunk_16<true>(v, stage, lane);
+  else stage_chunk_f32(v, stage, lane);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_4d(tmC, stage_s, col, row0, z0, z1);
+    bulk_commit_group();
+  }
+}
+
 // Per-CTA constants shared by the three roles.
 struct CtaCtx {
   uint32_t base, stage_bytes, full0, empty0, tfull0, tempty0, tmem_base;
@@ -343,8 +431,9 @@ __device__ __forceinline__ bool mma_unit(const CtaCtx& cx, const GemmParams& p, 
 
 // Epilogue warp: drain this warp's share of the accumulator of work unit t.
 template <int MODE>
-__device__ __forceinline__ bool epilogue_unit(const CtaCtx& cx, const GemmParams& p, int t, int warp,
-                                              int lane, int& acc, uint32_t& acc_phase) {
+__device__ __forceinline__ bool epilogue_unit(const CtaCtx& cx, const GemmParams& p,
+                                              const CUtensorMap* tmC, const CUtensorMap* tmP, int t,
+                                              int warp, int lane, int& acc, uint32_t& acc_phase) {
   const int q = warp & 3;  // TMEM lane quarter this warp may read
   TileCoord tc = tile_coord(p, t);
   {
@@ -364,11 +453,17 @@ __device__ __forceinline__ bool epilogue_unit(const CtaCtx& cx, const GemmParams
   const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
   const int row_base = tc.m0 + q * 32;
   const uint32_t t_row = cx.tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+  const bool tma_out = (MODE & E_NO_TMA) == 0 && p.tma_store != 0;
   for (int c0 = 16 * ((warp - 2) >> 2); c0 < p.bn; c0 += 64) {
     if (tc.n0 + c0 >= p.N) break;  // uniform across the warp
     uint32_t r[16];
     tmem_ld16(t_row + c0, r);
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if ((MODE & E_NO_TMA) == 0 && tma_out) {
+      if (row_base < p.M)
+        epilogue_chunk_tma<MODE>(p, tmC, tmP, r, stage, lane, tc.n0 + c0, row_base, tc.z0, tc.z1);
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
@@ -469,6 +564,7 @@ __device__ __forceinline__ void cta_teardown(const CtaCtx& cx) {
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmP,
                     const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   pdl_trigger();
@@ -500,7 +596,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x)
-      if (!epilogue_unit<MODE>(cx, p, t, warp, lane, acc, acc_phase)) break;
+      if (!epilogue_unit<MODE>(cx, p, &tmC, &tmP, t, warp, lane, acc, acc_phase)) break;
+    if (lane == 0) bulk_wait_read_all();   // the staging area outlives its last tile store
   }
   cta_teardown(cx);
 }
@@ -514,7 +611,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // splitting K and without a reduction pass.  The table lives in device memory: tensor maps,
 // kernel parameters and the index of each problem's first list entry.
 struct __align__(128) GroupEntry {
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
   GemmParams p;
   int first_unit;
 };
@@ -570,8 +667,10 @@ gemm_group_kernel(const GroupEntry* __restrict__ table, int n_problems, int tota
     for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
       const int pi = group_find(first, n_problems, u);
       const GemmParams p = table[pi].p;
-      if (!epilogue_unit<0>(cx, p, u - first[pi], warp, lane, acc, acc_phase)) break;
+      if (!epilogue_unit<0>(cx, p, &table[pi].tmC, nullptr, u - first[pi], warp, lane, acc, acc_phase))
+        break;
     }
+    if (lane == 0) bulk_wait_read_all();
   }
   cta_teardown(cx);
 }
@@ -729,7 +828,8 @@ __device__ __forceinline__ bool pair_mma_unit(const CtaCtx& cx, const GemmParams
 
 // Epilogue warp of one CTA of the pair: its 128 rows of the 256 x 256 tile.
 template <int MODE>
-__device__ __forceinline__ bool pair_epilogue_unit(const CtaCtx& cx, const GemmParams& p, int t,
+__device__ __forceinline__ bool pair_epilogue_unit(const CtaCtx& cx, const GemmParams& p,
+                                                   const CUtensorMap* tmC, const CUtensorMap* tmP, int t,
                                                    uint32_t rank, int warp, int lane, int& acc,
                                                    uint32_t& acc_phase) {
   const int q = warp & 3;
@@ -747,11 +847,17 @@ __device__ __forceinline__ bool pair_epilogue_unit(const CtaCtx& cx, const GemmP
   const long long batch_off = (long long)tc.z0 * p.sC0 + (long long)tc.z1 * p.sC1;
   const int row_base = tc.m0 + q * 32;
   const uint32_t t_row = cx.tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+  const bool tma_out = (MODE & E_NO_TMA) == 0 && p.tma_store != 0;
   for (int c0 = 16 * ((warp - 2) >> 2); c0 < PAIR_BN; c0 += 64) {
     if (tc.n0 + c0 >= p.N) break;
     uint32_t r[16];
     tmem_ld16(t_row + c0, r);
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if ((MODE & E_NO_TMA) == 0 && tma_out) {
+      if (row_base < p.M)
+        epilogue_chunk_tma<MODE>(p, tmC, tmP, r, stage, lane, tc.n0 + c0, row_base, tc.z0, tc.z1);
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
@@ -789,6 +895,7 @@ __device__ __forceinline__ bool pair_epilogue_unit(const CtaCtx& cx, const GemmP
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmP,
                      const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5;
@@ -822,7 +929,8 @@ gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = pair; t < total_tiles; t += n_pairs)
-      if (!pair_epilogue_unit<MODE>(cx, p, t, rank, warp, lane, acc, acc_phase)) break;
+      if (!pair_epilogue_unit<MODE>(cx, p, &tmC, &tmP, t, rank, warp, lane, acc, acc_phase)) break;
+    if (lane == 0) bulk_wait_read_all();
   }
   pair_teardown(cx);
 }
@@ -868,8 +976,11 @@ gemm_group_pair_kernel(const GroupEntry* __restrict__ table, int n_problems, int
     for (int u = pair; u < total_units; u += n_pairs) {
       const int pi = group_find(first, n_problems, u);
       const GemmParams p = table[pi].p;
-      if (!pair_epilogue_unit<0>(cx, p, u - first[pi], rank, warp, lane, acc, acc_phase)) break;
+      if (!pair_epilogue_unit<0>(cx, p, &table[pi].tmC, nullptr, u - first[pi], rank, warp, lane, acc,
+                                 acc_phase))
+        break;
     }
+    if (lane == 0) bulk_wait_read_all();
   }
   pair_teardown(cx);
 }
@@ -892,7 +1003,8 @@ __global__ void k_splitk_reduce(const float4* __restrict__ ws, float* __restrict
   }
 }
 
-typedef void (*GemmKernel)(const CUtensorMap, const CUtensorMap, const GemmParams);
+typedef void (*GemmKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                           const GemmParams);
 struct Specialised {
   int mode;
   GemmKernel fn;
@@ -957,6 +1069,39 @@ int make_map(vkg_device* dev, CUtensorMap* map, const void* ptr, int dtype, int6
   return 0;
 }
 
+// 4-D map {N, M, nb0, nb1} over the output (fp32 or 16-bit) for the epilogue's tile stores:
+// boxes of 16 columns x 32 rows in the 64-byte (fp32) or 32-byte (16-bit) swizzle the staging
+// area is written in.  *ok = false (and no error) when the layout cannot be described: the
+// epilogue then stores per lane.
+int make_out_map(vkg_device* dev, CUtensorMap* map, const void* ptr, int dtype, int64_t n_cols,
+                 int64_t n_rows, int64_t ld, int nb0, int64_t s0, int nb1, int64_t s1, bool* ok) {
+  *ok = false;
+  const int64_t es = dtype == VKG_F32 ? 4 : 2;
+  const int64_t pitch = ld * es;
+  const int64_t st0 = nb0 > 1 ? s0 * es : pitch * n_rows;
+  const int64_t st1 = nb1 > 1 ? s1 * es : (nb0 > 1 ? st0 * nb0 : pitch * n_rows);
+  if (((uintptr_t)ptr & 15) || (pitch & 15) || (st0 & 15) || (st1 & 15) || st0 <= 0 || st1 <= 0 ||
+      pitch >= (1ll << 40) || st0 >= (1ll << 40) || st1 >= (1ll << 40))
+    return 0;
+  cuuint64_t dims[4] = {(cuuint64_t)n_cols, (cuuint64_t)n_rows, (cuuint64_t)nb0, (cuuint64_t)nb1};
+  cuuint64_t strides[3] = {(cuuint64_t)pitch, (cuuint64_t)st0, (cuuint64_t)st1};
+  cuuint32_t box[4] = {16, 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == VKG_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == VKG_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = ((EncodeTiledFn)dev->encode_tiled)(
+      map, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      es == 4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    vkg_set_error("cuTensorMapEncodeTiled failed for the output map with code %d", (int)r);
+    return 1;
+  }
+  *ok = true;
+  return 0;
+}
+
 // Tile width and K split for one GEMM, from a small time model (microseconds).
 // Measured on B200: a k-block (64 K-elements, four tcgen05.mma) costs 0.33 us even for a
 // 64-column tile and only 0.41 us for 256 columns, so narrow tiles waste the tensor
@@ -1003,7 +1148,7 @@ void plan_gemm(int M, int N, int K, int batch, int sms, bool may_split, int64_t 
 // One GEMM made ready to launch: kernel parameters, operand maps, epilogue mask.
 struct Problem {
   GemmParams p;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC, tmP;
   int mode;
   bool vec;
   long long total_tiles;
@@ -1125,6 +1270,21 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
               (a->c_dtype == VKG_F16 ? E_F16 : a->c_dtype == VKG_BF16 ? E_BF16 : 0) |
               (a->colsum ? E_COLSUM : 0);
   if (!vec) out->mode = E_GENERIC;
+  // write-only epilogues store their tiles through tensor maps over C (and pre); p.C, p.ldc
+  // and the batch strides already describe the split-K workspace when K is split
+  memset(&out->tmC, 0, sizeof(CUtensorMap));
+  memset(&out->tmP, 0, sizeof(CUtensorMap));
+  if (dev->tma_store && (out->mode & E_NO_TMA) == 0) {
+    const int z1n = p.split_k > 1 ? p.split_k : nb1;
+    bool ok_c = false, ok_p = true;
+    if (make_out_map(dev, &out->tmC, p.C, p.split_k > 1 ? VKG_F32 : a->c_dtype, p.N, p.M, p.ldc, nb0,
+                     p.sC0, z1n, p.sC1, &ok_c))
+      return 1;
+    if (ok_c && a->pre &&
+        make_out_map(dev, &out->tmP, a->pre, VKG_F32, p.N, p.M, p.ldc, nb0, p.sC0, z1n, p.sC1, &ok_p))
+      return 1;
+    p.tma_store = (ok_c && ok_p) ? 1 : 0;
+  }
   return 0;
 }
 
@@ -1156,7 +1316,7 @@ GemmKernel pick_kernel(int mode) {
 int reduce_slices(vkg_device* dev, const vkg_gemm_args* a, const GemmParams& p) {
   if (p.split_k <= 1) return 0;
   const long long n4 = (long long)a->M * (a->N / 4);
-  VKG_CUDA(vkg_launch(dev, k_splitk_reduce, dim3(vkg_blocks(n4, 256, (int64_t)dev->sm_count * 8)),
+  VKG_CUDA(vkg_launch(dev, VKG_K_SMALL, k_splitk_reduce, dim3(vkg_blocks(n4, 256, (int64_t)dev->sm_count * 8)),
                       dim3(256), 0, 1, (const float4*)a->workspace, (float*)a->C, a->M, a->N / 4,
                       (long long)a->ldc, p.split_k));
   return vkg_check_launch("splitk_reduce");
@@ -1238,6 +1398,7 @@ extern "C" int vkg_gemm_group_prepare(vkg_device* dev, const vkg_gemm_args* args
     memset(&host[i], 0, sizeof(GroupEntry));
     host[i].tmA = q.tmA;
     host[i].tmB = q.tmB;
+    host[i].tmC = q.tmC;
     host[i].p = q.p;
     host[i].first_unit = (int)units;
     units += q.total_tiles;
@@ -1264,13 +1425,13 @@ extern "C" int vkg_gemm_group_launch(vkg_device* dev, const void* table, int n, 
     const int units = -total_units;
     int pairs = dev->sm_count / 2;
     if (pairs > units) pairs = units;
-    VKG_CUDA(vkg_launch(dev, gemm_group_pair_kernel, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
+    VKG_CUDA(vkg_launch(dev, VKG_K_GEMM_GROUP, gemm_group_pair_kernel, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
                         SMEM_BYTES, 2, static_cast<const GroupEntry*>(table), n, units));
     return vkg_check_launch("gemm_group_pair_kernel");
   }
   int ctas = dev->sm_count < total_units ? dev->sm_count : total_units;
   const int stages = RING_BYTES / (A_STAGE_BYTES + 256 * 128);
-  VKG_CUDA(vkg_launch(dev, gemm_group_kernel, dim3((unsigned)ctas), dim3(NUM_THREADS), SMEM_BYTES, 1,
+  VKG_CUDA(vkg_launch(dev, VKG_K_GEMM_GROUP, gemm_group_kernel, dim3((unsigned)ctas), dim3(NUM_THREADS), SMEM_BYTES, 1,
                       static_cast<const GroupEntry*>(table), n, total_units, 256, stages));
   return vkg_check_launch("gemm_group_kernel");
 }
@@ -1300,8 +1461,8 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
       if (kCtaPair[i].mode == q.mode) fn = kCtaPair[i].fn;
     long long pairs = dev->sm_count / 2;
     if (pairs > q.total_tiles) pairs = q.total_tiles;
-    VKG_CUDA(vkg_launch(dev, fn, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS), SMEM_BYTES, 2, q.tmA,
-                        q.tmB, q.p));
+    VKG_CUDA(vkg_launch(dev, VKG_K_GEMM_PAIR, fn, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS), SMEM_BYTES, 2, q.tmA,
+                        q.tmB, q.tmC, q.tmP, q.p));
     if (vkg_check_launch("gemm_cta_pair_kernel")) return 1;
     if (reduce_slices(dev, a, q.p)) return 1;
     return finish_colsum(dev, a, 2 * BM);
@@ -1310,8 +1471,8 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   if (ensure_attrs(dev)) return 1;
   int ctas = a->max_ctas > 0 ? a->max_ctas : dev->sm_count;
   if (ctas > q.total_tiles) ctas = (int)q.total_tiles;
-  VKG_CUDA(vkg_launch(dev, pick_kernel(q.mode), dim3((unsigned)ctas), dim3(NUM_THREADS), SMEM_BYTES, 1,
-                      q.tmA, q.tmB, q.p));
+  VKG_CUDA(vkg_launch(dev, VKG_K_GEMM, pick_kernel(q.mode), dim3((unsigned)ctas), dim3(NUM_THREADS), SMEM_BYTES, 1,
+                      q.tmA, q.tmB, q.tmC, q.tmP, q.p));
   if (vkg_check_launch("gemm_tcgen05_kernel")) return 1;
   if (reduce_slices(dev, a, q.p)) return 1;
   return finish_colsum(dev, a, BM);

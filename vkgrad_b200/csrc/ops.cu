@@ -1098,7 +1098,7 @@ extern "C" int vkg_finals_flush(vkg_device* dev) {
       blocks += (en.W + 31) / 32;
       tab.e[tab.n++] = en;
     }
-    VKG_CUDA(vkg_launch(dev, k_finals_multi, dim3((unsigned)blocks), dim3(32 * FIN_SLICES), 0, 1, tab));
+    VKG_CUDA(vkg_launch(dev, VKG_K_SMALL, k_finals_multi, dim3((unsigned)blocks), dim3(32 * FIN_SLICES), 0, 1, tab));
     if (vkg_check_launch("finals_multi")) return 1;
   }
   return 0;
@@ -1193,7 +1193,7 @@ extern "C" int vkg_softmax_ce(vkg_device* dev, const float* logits, const uint32
     // wide rows: one read of the logits, everything else from registers
     const int nv = (n4 + CE_THREADS - 1) / CE_THREADS;
 #define VKG_CE(NV)                                                                              \
-  VKG_CUDA(vkg_launch(dev, k_softmax_ce_reg<NV>, dim3((unsigned)rows), dim3(CE_THREADS), 0, 1, logits, \
+  VKG_CUDA(vkg_launch(dev, VKG_K_CE, k_softmax_ce_reg<NV>, dim3((unsigned)rows), dim3(CE_THREADS), 0, 1, logits, \
                       labels, w, (__half*)dl16, dl32, loss, stride, ncls, grad_scale,             \
                       dev->sm_count * (NV <= 8 ? 2 : 1)))
     if (nv <= 8) VKG_CE(8);
@@ -1263,7 +1263,7 @@ extern "C" int vkg_adamw_multi(vkg_device* dev, void* table, const float* hp) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(table && hp, "adamw_multi: bad arguments");
   AdamTable* t = (AdamTable*)table;
-  VKG_CUDA(vkg_launch(dev, k_adamw_multi, dim3((unsigned)t->nblocks), dim3(TPB), 0, 1, t->tensors,
+  VKG_CUDA(vkg_launch(dev, VKG_K_ADAMW, k_adamw_multi, dim3((unsigned)t->nblocks), dim3(TPB), 0, 1, t->tensors,
                       t->blockmap, hp));
   return vkg_check_launch("adamw_multi");
 }
@@ -1290,7 +1290,7 @@ extern "C" int vkg_layernorm(vkg_device* dev, const float* x, const float* gamma
   if (aligned && D % 128 == 0 && D <= 1024) {
     const unsigned grid = (rows + wpb - 1) / wpb;
 #define VKG_LN(NV) \
-  VKG_CUDA(vkg_launch(dev, k_layernorm_vec<NV>, dim3(grid), dim3(wpb * 32), 0, 1, x, gamma, beta, \
+  VKG_CUDA(vkg_launch(dev, VKG_K_LN, k_layernorm_vec<NV>, dim3(grid), dim3(wpb * 32), 0, 1, x, gamma, beta, \
                       (__half*)y16, mu, rstd, rows))
     switch (D / 128) {
       case 1: VKG_LN(1); break;
@@ -1328,7 +1328,7 @@ static void launch_ln_bwd_vec(vkg_device* dev, int nblocks, const float* dy, con
                               const float* dres, float* dx, void* dx16, float* scratch, int rows,
                               int nparts) {
   // a failed launch is picked up by the caller's vkg_check_launch
-  vkg_launch(dev, k_layernorm_bwd_vec<NV>, dim3((unsigned)nblocks), dim3(LNV_WARPS * 32), 0, 1, dy, x,
+  vkg_launch(dev, VKG_K_LN_BWD, k_layernorm_bwd_vec<NV>, dim3((unsigned)nblocks), dim3(LNV_WARPS * 32), 0, 1, dy, x,
              gamma, mu, rstd, dres, dx, (__half*)dx16, scratch, rows, nparts);
 }
 
@@ -1448,7 +1448,7 @@ extern "C" int vkg_embed(vkg_device* dev, const float* tok, const float* pos, co
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(tok && pos && ids && x && n > 0, "embed: bad arguments");
   if (D % 4 == 0 && n < (1ll << 31) && ((((uintptr_t)tok | (uintptr_t)pos | (uintptr_t)x) & 15) == 0)) {
-    VKG_CUDA(vkg_launch(dev, k_embed_v4, dim3(flat_grid(dev, n / 4)), dim3(TPB), 0, 1, (const float4*)tok,
+    VKG_CUDA(vkg_launch(dev, VKG_K_SMALL, k_embed_v4, dim3(flat_grid(dev, n / 4)), dim3(TPB), 0, 1, (const float4*)tok,
                         (const float4*)pos, ids, seg, (float4*)x, (int)(n / 4), D / 4, T));
     return vkg_check_launch("embed_v4");
   }
@@ -1461,7 +1461,7 @@ extern "C" int vkg_embed_bwd(vkg_device* dev, const float* dx, const uint32_t* i
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(dx && ids && dtok && dpos && n > 0, "embed_bwd: bad arguments");
   if (D % 4 == 0 && n < (1ll << 31) && ((((uintptr_t)dx | (uintptr_t)dtok | (uintptr_t)dpos) & 15) == 0)) {
-    VKG_CUDA(vkg_launch(dev, k_embed_bwd_v4, dim3(flat_grid(dev, n / 4)), dim3(TPB), 0, 1,
+    VKG_CUDA(vkg_launch(dev, VKG_K_SMALL, k_embed_bwd_v4, dim3(flat_grid(dev, n / 4)), dim3(TPB), 0, 1,
                         (const float4*)dx, ids, seg, (float4*)dtok, (float4*)dpos, (int)(n / 4), D / 4, T));
     return vkg_check_launch("embed_bwd_v4");
   }

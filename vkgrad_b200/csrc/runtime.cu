@@ -3,7 +3,9 @@
 // (vk.Device / vk.Buffer / vk.Graph); nothing here computes.
 #include "common.cuh"
 
+#include <chrono>
 #include <cstdlib>
+#include <thread>
 
 static thread_local char g_err[1024] = "";
 
@@ -72,7 +74,11 @@ extern "C" int vkg_device_create(int ordinal, vkg_device** out) {
   }
   d->encode_tiled = fn;
   const char* pdl = getenv("VKG_PDL");
-  d->pdl = !(pdl && pdl[0] == '0');
+  d->pdl = pdl && pdl[0] == '1';    // off unless asked for: it measured slower inside CUDA graphs
+  const char* ts = getenv("VKG_TMA_STORE");
+  d->tma_store = !(ts && ts[0] == '0');
+  const char* mask = getenv("VKG_PDL_MASK");     // kernel families, for experiments
+  if (mask && mask[0]) d->pdl_mask = (unsigned)strtoul(mask, nullptr, 0);
   *out = d;
   return 0;
 }
@@ -81,6 +87,22 @@ extern "C" int vkg_set_pdl(vkg_device* dev, int on) {
   if (!dev) VKG_FAIL("null device");
   VKG_REQUIRE(!dev->capturing, "set_pdl: not while a graph is being recorded");
   dev->pdl = on != 0;
+  return 0;
+}
+
+extern "C" int vkg_set_tuning(vkg_device* dev, int key, int64_t value) {
+  if (!dev) VKG_FAIL("null device");
+  VKG_REQUIRE(!dev->capturing, "set_tuning: not while a graph is being recorded");
+  switch (key) {
+    case VKG_TUNE_PDL: dev->pdl = value != 0; break;
+    case VKG_TUNE_PDL_FAMILIES: dev->pdl_mask = (unsigned)value; break;
+    case VKG_TUNE_TMA_STORE: dev->tma_store = value != 0; break;
+    case VKG_TUNE_WAIT_TIMEOUT_MS:
+      VKG_REQUIRE(value > 0, "set_tuning: the wait limit must be positive");
+      dev->wait_timeout_s = (double)value * 1e-3;
+      break;
+    default: VKG_FAIL("set_tuning: unknown key %d", key);
+  }
   return 0;
 }
 
@@ -121,9 +143,100 @@ static int check_err_flag(vkg_device* dev) {
   return 0;
 }
 
+// ---- host waits ------------------------------------------------------------------------
+//
+// The reference turns a fence that does not signal within 10 s into VkError (vk.py:884-888,
+// 1335-1339).  Here a step can hang only in a collective whose peer never arrives, so waits
+// on a device with a communicator poll against a deadline; on expiry the communicator is
+// aborted (which lets the stream drain) and the call fails.
+int vkg_wait_with_deadline(const vkg_wait_hooks* h, const char* what) {
+  const auto t0 = std::chrono::steady_clock::now();
+  for (long long polls = 0;; ++polls) {
+    const int q = h->query(h->query_ctx);
+    if (q == 0) return 0;
+    if (q != 1) return 1;
+    if (h->async_error && (polls & 63) == 63 && h->async_error(h->comm_ctx)) {
+      if (h->abort) h->abort(h->comm_ctx);
+      return 1;
+    }
+    const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if (h->abort && waited > h->timeout_s) {
+      h->abort(h->comm_ctx);
+      vkg_set_error("%s: the device did not finish within %.1f s (a collective whose peer never "
+                    "arrived?); the communicator was aborted", what, h->timeout_s);
+      return 1;
+    }
+    // spin for the first 200 us (a training step's tail), then yield the core
+    if (waited > 200e-6) std::this_thread::sleep_for(std::chrono::microseconds(waited > 0.05 ? 500 : 20));
+  }
+}
+
+namespace {
+struct DeviceQuery {
+  vkg_device* dev;
+  cudaEvent_t ev;
+};
+int query_device(void* ctx) {
+  DeviceQuery* q = static_cast<DeviceQuery*>(ctx);
+  cudaError_t e = q->ev ? cudaEventQuery(q->ev) : cudaStreamQuery(q->dev->stream);
+  if (e == cudaSuccess) return 0;
+  if (e == cudaErrorNotReady) {
+    cudaGetLastError();
+    return 1;
+  }
+  vkg_set_error("device wait failed: %s", cudaGetErrorString(e));
+  return 2;
+}
+}  // namespace
+
+int vkg_wait_device(vkg_device* dev, cudaEvent_t ev, const char* what) {
+  if (!dev->on_abort) {          // no communicator: nothing can hang, block in the driver
+    if (ev) VKG_CUDA(cudaEventSynchronize(ev));
+    else VKG_CUDA(cudaStreamSynchronize(dev->stream));
+    return 0;
+  }
+  DeviceQuery q{dev, ev};
+  vkg_wait_hooks h{query_device, &q, dev->on_async_error, dev->on_abort, dev->wait_ctx,
+                   dev->wait_timeout_s};
+  return vkg_wait_with_deadline(&h, what);
+}
+
+// The deadline loop against a scripted device, for tests without a GPU: the "stream" reports
+// done after ready_after_polls queries (never, if negative), the "communicator" reports an
+// asynchronous error from its async_error_at-th check on (never, if negative).  *aborted
+// receives how often the abort hook ran.
+namespace {
+struct FakeWait {
+  long long polls, ready_after, checks, error_at;
+  int aborted;
+};
+int fake_query(void* ctx) {
+  FakeWait* f = static_cast<FakeWait*>(ctx);
+  return (f->ready_after >= 0 && f->polls++ >= f->ready_after) ? 0 : 1;
+}
+int fake_async_error(void* ctx) {
+  FakeWait* f = static_cast<FakeWait*>(ctx);
+  if (f->error_at >= 0 && f->checks++ >= f->error_at) {
+    vkg_set_error("communicator reported an asynchronous error (scripted)");
+    return 1;
+  }
+  return 0;
+}
+void fake_abort(void* ctx) { static_cast<FakeWait*>(ctx)->aborted++; }
+}  // namespace
+
+extern "C" int vkg_selftest_wait_deadline(int64_t ready_after_polls, int64_t async_error_at,
+                                          double timeout_s, int* aborted) {
+  FakeWait f{0, ready_after_polls, 0, async_error_at, 0};
+  vkg_wait_hooks h{fake_query, &f, fake_async_error, fake_abort, &f, timeout_s};
+  const int rc = vkg_wait_with_deadline(&h, "selftest");
+  if (aborted) *aborted = f.aborted;
+  return rc;
+}
+
 extern "C" int vkg_sync(vkg_device* dev) {
   if (vkg_bind(dev)) return 1;
-  VKG_CUDA(cudaStreamSynchronize(dev->stream));
+  if (vkg_wait_device(dev, nullptr, "sync")) return 1;
   return check_err_flag(dev);
 }
 
@@ -179,7 +292,7 @@ extern "C" int vkg_upload(vkg_device* dev, void* dptr, const void* hptr, size_t 
 extern "C" int vkg_download(vkg_device* dev, void* hptr, const void* dptr, size_t bytes) {
   if (vkg_bind(dev)) return 1;
   VKG_CUDA(cudaMemcpyAsync(hptr, dptr, bytes, cudaMemcpyDeviceToHost, dev->stream));
-  VKG_CUDA(cudaStreamSynchronize(dev->stream));
+  if (vkg_wait_device(dev, nullptr, "download")) return 1;
   return check_err_flag(dev);
 }
 
@@ -216,7 +329,7 @@ extern "C" int vkg_timer_begin(vkg_device* dev) {
 extern "C" int vkg_timer_end(vkg_device* dev, double* seconds) {
   if (vkg_bind(dev)) return 1;
   VKG_CUDA(cudaEventRecord(dev->ev1, dev->stream));
-  VKG_CUDA(cudaEventSynchronize(dev->ev1));
+  if (vkg_wait_device(dev, dev->ev1, "timer_end")) return 1;
   float ms = 0.f;
   VKG_CUDA(cudaEventElapsedTime(&ms, dev->ev0, dev->ev1));
   if (seconds) *seconds = (double)ms * 1e-3;
@@ -268,7 +381,7 @@ extern "C" int vkg_graph_launch(vkg_device* dev, vkg_graph* g, double* seconds) 
   VKG_CUDA(cudaEventRecord(dev->ev0, dev->stream));
   VKG_CUDA(cudaGraphLaunch(g->exec, dev->stream));
   VKG_CUDA(cudaEventRecord(dev->ev1, dev->stream));
-  VKG_CUDA(cudaEventSynchronize(dev->ev1));
+  if (vkg_wait_device(dev, dev->ev1, "graph_launch")) return 1;
   float ms = 0.f;
   VKG_CUDA(cudaEventElapsedTime(&ms, dev->ev0, dev->ev1));
   if (seconds) *seconds = (double)ms * 1e-3;
