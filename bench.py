@@ -651,10 +651,16 @@ def run_gpu_arm(args):
     dev.copy(ids_host, ids_dev, R * 4)
     dev.copy(tgt_host, tgt_dev, R * 4)
 
-    core = DataParallelStep(rep, ids_dev, tgt_dev, name="step_resident",
-                            overlap_chunks=args.overlap_chunks)
+    # the exchange of all but the last part of the bucket runs beside the backward, on a second
+    # communicator held to a few CTAs
+    groups = args.overlap_groups if world > 1 else 1
+    side = None
+    if groups > 1 and args.side_ctas > 0:
+        side = Comm.from_env(dev, port_offset=211, max_ctas=args.side_ctas)
+    dp_kw = dict(overlap_groups=groups, side_comm=side, side_sms=args.side_ctas if groups > 1 else 0)
+    core = DataParallelStep(rep, ids_dev, tgt_dev, name="step_resident", **dp_kw)
     e2e = DataParallelStep(rep, ids_dev, tgt_dev, host_ids=ids_host, host_targets=tgt_host,
-                           name="step_e2e", overlap_chunks=args.overlap_chunks)
+                           name="step_e2e", **dp_kw)
     lr = 6e-4
 
     def barrier():
@@ -686,8 +692,9 @@ def run_gpu_arm(args):
             print(json.dumps({"profile_only": True, "ms_per_step": dt / args.steps * 1e3,
                               "launches_per_step": core.n_kernels}), flush=True)
         barrier()
-        if comm is not None:
-            comm.destroy()
+        for c_ in (side, comm):
+            if c_ is not None:
+                c_.destroy()
         rep.destroy()
         dev.destroy()
         return
@@ -710,12 +717,16 @@ def run_gpu_arm(args):
         dt_e2e = comm.max_double(dt_e2e)
     clocks = sampler.stop(t_wall0, t_wall2) if sampler else None
 
-    # replicas must still be bit-identical (the reference's drift == 0 claim)
+    # replicas must still be bit-identical (the reference's drift == 0 claim); the sums also
+    # let two runs with the same arguments be compared: every kernel of the step adds in a
+    # fixed order, so they agree to the last bit
+    sums = {nm: float(np.abs(p.numpy().astype(np.float64)).sum())
+            for nm, p in (("b0.fc1.W", model.blocks[0].fc1.W), ("tok", model.tok),
+                          ("pos", model.pos))}
     drift = 0.0
     if comm is not None:
-        w = model.blocks[0].fc1.W.numpy().astype(np.float64)
-        chk = float(np.abs(w).sum())
-        drift = comm.max_double(chk) - (-comm.max_double(-chk))
+        for chk in sums.values():
+            drift = max(drift, comm.max_double(chk) - (-comm.max_double(-chk)))
 
     # the exchange step alone: fp32 all-reduce of the flat gradient bucket, max over ranks
     nvlink = None
@@ -731,7 +742,16 @@ def run_gpu_arm(args):
                   "allreduce_ms": t_ar * 1e3, "achieved": wire / t_ar / 1e9, "peak": nv_peak,
                   "unit": "GB/s", "frac": wire / t_ar / 1e9 / nv_peak,
                   "peak_note": "peer-copy bandwidth per direction measured on this pool",
-                  "overlapped": False}
+                  "overlapped": core.parts is not None, "exposed_ms": t_ar * 1e3}
+        if core.parts is not None:
+            # what still runs on the compute stream after the backward: the last part alone
+            first, count = core.parts[-1]
+            barrier()
+            t_last = dev.run_op(lambda: comm.allreduce_sum(rep.bucket, count, offset_bytes=4 * first),
+                                reps) / reps
+            nvlink["exposed_ms"] = comm.max_double(t_last) * 1e3
+            nvlink["parts_bytes"] = [4 * c for _, c in core.parts]
+            nvlink["side_ctas"] = args.side_ctas
 
     tokens_step = R * world
     line = None
@@ -753,7 +773,7 @@ def run_gpu_arm(args):
             parts["attention"] = L * (attn["fwd_us"] + attn["bwd_us"]) * 1e-3
         for k, v in kernels.items():
             parts[k] = v["count"] * v["us"] * 1e-3
-        comm_ms = nvlink["allreduce_ms"] if nvlink is not None else 0.0
+        comm_ms = nvlink["exposed_ms"] if nvlink is not None else 0.0
         gaps = ms - sum(parts.values()) - comm_ms
         cpu = None
         if not args.no_cpu:
@@ -792,6 +812,7 @@ def run_gpu_arm(args):
             "cpu_baseline": cpu,
             "loss": {"resident": loss_core, "e2e": last_loss},
             "replica_drift": drift,
+            "weight_abs_sums": {k: repr(v) for k, v in sums.items()},
             "nvlink": nvlink,
         }
         if world == 1 and not args.no_extras:
@@ -802,8 +823,9 @@ def run_gpu_arm(args):
         if args.gemm_trio:
             line["gemm_shapes"] = rows
     barrier()
-    if comm is not None:
-        comm.destroy()
+    for c_ in (side, comm):
+        if c_ is not None:
+            c_.destroy()
     rep.destroy()
     dev.destroy()
     if line is not None:
@@ -818,9 +840,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gpt2-small", choices=sorted(WORKLOADS))
     ap.add_argument("--loss-scale", type=float, default=4096.0)
-    ap.add_argument("--overlap-chunks", type=int, default=1,
-                    help="N>1: parts the gradient all-reduce is cut into and overlapped with AdamW "
-                         "(1 = one all-reduce, then AdamW)")
+    ap.add_argument("--overlap-groups", type=int, default=3,
+                    help="N>1: groups of blocks whose gradients are all-reduced beside the rest of "
+                         "the backward (1 = one all-reduce after the backward)")
+    ap.add_argument("--side-ctas", type=int, default=8,
+                    help="N>1: CTAs NCCL may use for the overlapped parts (SMs the persistent "
+                         "kernels leave free meanwhile); 0 = share the main communicator")
     ap.add_argument("--cta-pair", type=int, default=0,
                     help="with --gemm: 1 = 256x256 tiles on CTA pairs, -1 = never, 0 = library's choice")
     ap.add_argument("--max-ctas", type=int, default=0, help="with --gemm: cap the persistent grid")

@@ -76,9 +76,12 @@ int vkg_set_pdl(vkg_device* dev, int on);
  *   VKG_TUNE_TMA_STORE     0: GEMM epilogues store per lane; 1 (default): epilogues
  *                          without fused reads store their tiles through tensor maps
  *   VKG_TUNE_WAIT_TIMEOUT_MS  limit of a host wait on a device that has a communicator
- *                          (default 60 000): see vkg_sync */
+ *                          (default 60 000): see vkg_sync
+ *   VKG_TUNE_SM_LIMIT      most CTAs a persistent kernel (GEMM, grouped GEMM, attention
+ *                          backward) launches; 0 = one per SM.  May also change during a
+ *                          recording: launches recorded after the call use the new value */
 enum { VKG_TUNE_PDL = 0, VKG_TUNE_PDL_FAMILIES = 1, VKG_TUNE_TMA_STORE = 2,
-       VKG_TUNE_WAIT_TIMEOUT_MS = 3 };
+       VKG_TUNE_WAIT_TIMEOUT_MS = 3, VKG_TUNE_SM_LIMIT = 4 };
 int vkg_set_tuning(vkg_device* dev, int key, int64_t value);
 /* Waits for the stream; reports a kernel error flag (bounded waits that gave
  * up) as a failure, like the reference's 10 s fence timeout (vk.py:884-888, 1335-1339).
@@ -376,6 +379,14 @@ int vkg_embed(vkg_device* dev, const float* tok, const float* pos,
 int vkg_embed_bwd(vkg_device* dev, const float* dx, const uint32_t* ids,
                   const uint32_t* seg, float* dtok, float* dpos, int64_t n, int D,
                   int T);
+/* The same scatter-add without atomics: rows that hit one table row are added in row
+ * order by one warp, so the result is bit-reproducible from run to run (the reference's
+ * float atomics are not).  D a multiple of 128 up to 1024; scratch holds
+ * vkg_embed_bwd_scratch_bytes(n / D) bytes. */
+int64_t vkg_embed_bwd_scratch_bytes(int64_t rows);
+int vkg_embed_bwd_det(vkg_device* dev, const float* dx, const uint32_t* ids,
+                      const uint32_t* seg, float* dtok, float* dpos, void* scratch,
+                      int64_t n, int D, int T);
 /* residual (tkernels.py:364-371): out = res + acc + bias[i % D]. */
 int vkg_residual(vkg_device* dev, const float* acc, const float* bias,
                  const float* res, float* out, int64_t n, int D);
@@ -406,6 +417,11 @@ int vkg_bucket_unpack16(vkg_device* dev, const void* src16, int dtype, float* ds
 int vkg_comm_unique_id(uint8_t id[128]);
 int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint8_t id[128],
                     vkg_comm** out);
+/* The same with NCCL held to at most max_ctas CTAs (ncclConfig_t.maxCTAs; 0 = NCCL's own
+ * choice): for collectives that run on the side stream while the compute stream keeps the
+ * other SMs busy (see VKG_TUNE_SM_LIMIT). */
+int vkg_comm_create_limited(vkg_device* dev, int rank, int nranks, const uint8_t id[128],
+                            int max_ctas, vkg_comm** out);
 int vkg_comm_destroy(vkg_comm* comm);
 /* In-place sum over ranks of `count` elements of dtype, on the device stream. */
 int vkg_allreduce_sum(vkg_comm* comm, void* buf, int64_t count, int dtype);

@@ -152,29 +152,38 @@ def test_bench_reference_arm_line_shape(monkeypatch, capsys):
     assert line["cpu_baseline"]["cores"] == os.cpu_count()
 
 
-def test_bucket_chunks_cover_the_bucket_on_tensor_boundaries():
-    """The parts the gradient bucket is all-reduced in are contiguous, end on tensor
-    boundaries, cover every float once and keep every parameter in exactly one part."""
-    from vkgrad_b200.dataparallel import _bucket_chunks
-    sizes = [38608896, 786432] + [768, 768, 1769472, 2304, 589824, 768, 2359296, 3072] * 12 + [768, 768]
+def test_bucket_parts_follow_the_backward_order():
+    """The parts of the flat bucket a data-parallel step sums while the backward still runs:
+    whole tensors, disjoint, covering the bucket, in the order their gradients complete."""
+    from vkgrad_b200.dataparallel import backward_flush_points, bucket_parts_for_flush
+
+    class P:
+        def __init__(self, n):
+            self.n = n
+
+    class Blk:
+        def __init__(self, ps):
+            self._ps = ps
+
+        def params(self):
+            return iter(self._ps)
+    tok, pos, lnf = P(1000), P(64), [P(8), P(8)]
+    blocks = [Blk([P(8), P(30), P(7)]) for _ in range(12)]
+    params = [tok, pos] + [p for b in blocks for p in b.params()] + lnf
     offs, off = [], 0
-    for n in sizes:
+    for p in params:
         offs.append(off)
-        off += (n + 3) // 4 * 4
-    params = list(range(len(sizes)))
-    for k in (1, 2, 6, 16, 1000):
-        parts = _bucket_chunks(params, offs, off, k)
-        assert 1 <= len(parts) <= max(k, 1)
-        assert parts[0][0] == 0 and sum(c for _, c, _ in parts) == off
-        seen = []
-        for (first, count, ps), nxt in zip(parts, parts[1:] + [None]):
-            assert count > 0 and ps
-            assert first == offs[ps[0]]
-            if nxt is not None:
-                assert first + count == nxt[0]
-            seen += ps
-        assert seen == params
-    assert _bucket_chunks(params[:1], offs[:1], 40, 6) == [(0, 40, params[:1])]
+        off += (p.n + 3) // 4 * 4
+    assert backward_flush_points(12, 3) == [8, 4]
+    assert backward_flush_points(12, 1) == [] and backward_flush_points(1, 3) == []
+    assert backward_flush_points(2, 8) == [1]
+    parts = bucket_parts_for_flush(params, offs, off, blocks, [8, 4])
+    per_block = 8 + 32 + 8
+    assert parts[0] == (1000 + 64 + 8 * per_block, 4 * per_block + 16)      # blocks 8..11 + lnf
+    assert parts[1] == (1000 + 64 + 4 * per_block, 4 * per_block)           # blocks 4..7
+    assert parts[2] == (0, 1000 + 64 + 4 * per_block)                       # tables + blocks 0..3
+    assert sum(c for _, c in parts) == off
+    assert bucket_parts_for_flush(params, offs, off, blocks, []) == [(0, off)]
 
 
 def test_arena_refuses_a_second_gpu_without_communicator():

@@ -258,6 +258,50 @@ def test_embedding(dev, pool, K):
     assert np.array_equal(pool.get(x, np.float32, (B * T, D)), tok[ids] + pos[t - seg])
 
 
+@pytest.mark.parametrize("packed", [False, True])
+@pytest.mark.parametrize("B,T,D,V", [(2, 16, 128, 7), (3, 130, 256, 40), (8, 1024, 768, 50257)])
+def test_embedding_backward_without_atomics(dev, pool, B, T, D, V, packed):
+    """vkg_embed_bwd_det: the scatter-add of tkernels.py:317-360 with the rows of one table row
+    added in row order -- equal to a sequential sum bit for bit, twice in a row, also with
+    many repeated tokens, packed samples and a table that already holds a gradient."""
+    from vkgrad_b200.vk import _check
+    rng = np.random.default_rng(B * T + D)
+    R = B * T
+    ids = rng.integers(0, V, R).astype(np.uint32)
+    ids[:: 3] = ids[0]                       # a long chain as well as short ones
+    seg = np.zeros(R, np.uint32)
+    if packed:
+        for b in range(B):
+            cut = int(rng.integers(1, T))
+            seg[b * T + cut:(b + 1) * T] = cut
+    dx = rng.standard_normal((R, D)).astype(np.float32)
+    tok0 = rng.standard_normal((V, D)).astype(np.float32)     # the tied head's share
+    t = np.arange(R) % T - seg.astype(np.int64)
+    rt, rp = tok0.copy(), np.zeros((T, D), np.float32)
+    # sequential fp32 sums per table row, rows in increasing order, then one add into the table
+    acc_t, acc_p = {}, {}
+    for r in range(R):
+        k = int(ids[r])
+        acc_t[k] = dx[r].copy() if k not in acc_t else acc_t[k] + dx[r]
+        k = int(t[r])
+        acc_p[k] = dx[r].copy() if k not in acc_p else acc_p[k] + dx[r]
+    for k, v in acc_t.items():
+        rt[k] = rt[k] + v
+    for k, v in acc_p.items():
+        rp[k] = rp[k] + v
+    lib, h = dev.lib, dev.handle
+    scratch = dev.buffer(lib.vkg_embed_bwd_scratch_bytes(R), "device")
+    pool.bufs.append(scratch)
+    dxb, idb = pool.up(dx), pool.up(ids)
+    segb = pool.up(seg) if packed else None
+    for _ in range(2):
+        dtok, dpos = pool.up(tok0), pool.out(np.float32, (T, D), fill=0)
+        _check(lib.vkg_embed_bwd_det(h, dxb.dptr, idb.dptr, None if segb is None else segb.dptr,
+                                     dtok.dptr, dpos.dptr, scratch.dptr, R * D, D, T), "embed_bwd_det")
+        assert np.array_equal(pool.get(dtok, np.float32, (V, D)), rt)
+        assert np.array_equal(pool.get(dpos, np.float32, (T, D)), rp)
+
+
 def test_residual_add_cast(dev, pool, K):
     rng = np.random.default_rng(7)
     R, D = 33, 40

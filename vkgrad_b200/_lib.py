@@ -12,6 +12,8 @@ LIB_PATH = os.path.join(HERE, "libvkgrad_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 ACT_NONE, ACT_GELU, ACT_RELU = 0, 1, 2
+# keys of vkg_set_tuning (include/vkgrad_b200.h)
+TUNE_PDL, TUNE_PDL_FAMILIES, TUNE_TMA_STORE, TUNE_WAIT_TIMEOUT_MS, TUNE_SM_LIMIT = 0, 1, 2, 3, 4
 
 vp = C.c_void_p
 i32 = C.c_int
@@ -118,6 +120,8 @@ _SIGNATURES = {
     "vkg_col_sum_static_max_floats": (i64, []),
     "vkg_embed": (i32, [vp, vp, vp, vp, vp, vp, i64, i32, i32]),
     "vkg_embed_bwd": (i32, [vp, vp, vp, vp, vp, vp, i64, i32, i32]),
+    "vkg_embed_bwd_det": (i32, [vp, vp, vp, vp, vp, vp, vp, i64, i32, i32]),
+    "vkg_embed_bwd_scratch_bytes": (i64, [i64]),
     "vkg_residual": (i32, [vp, vp, vp, vp, vp, i64, i32]),
     "vkg_add": (i32, [vp, vp, vp, vp, vp, i64]),
     "vkg_add_bias": (i32, [vp, vp, vp, i64, i32]),
@@ -127,6 +131,7 @@ _SIGNATURES = {
     "vkg_bucket_unpack16": (i32, [vp, vp, i32, vp, i64, f32]),
     "vkg_comm_unique_id": (i32, [C.POINTER(C.c_uint8)]),
     "vkg_comm_create": (i32, [vp, i32, i32, C.POINTER(C.c_uint8), C.POINTER(vp)]),
+    "vkg_comm_create_limited": (i32, [vp, i32, i32, C.POINTER(C.c_uint8), i32, C.POINTER(vp)]),
     "vkg_comm_destroy": (i32, [vp]),
     "vkg_allreduce_sum": (i32, [vp, vp, i64, i32]),
     "vkg_comm_side_begin": (i32, [vp]),
@@ -139,6 +144,7 @@ _SIGNATURES = {
 # Entries whose int return value is not a status code.
 _NOT_STATUS = {"vkg_last_error", "vkg_version", "vkg_device_stream",
                "vkg_layernorm_bwd_scratch_floats", "vkg_col_sum_scratch_floats",
+               "vkg_embed_bwd_scratch_bytes",
                "vkg_col_sum_static_max_floats"}
 
 _lib = None

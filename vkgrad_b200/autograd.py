@@ -17,6 +17,8 @@ parameters instead of one dispatch per tensor (autograd.py:331-335).
 
 import ctypes as C
 
+import zlib
+
 import numpy as np
 
 from . import _lib
@@ -177,7 +179,10 @@ class Linear:
         self.activation = activation
         self.act = _ACTS[act] if activation else ACT_NONE
         self.need_dx = need_dx
-        rng = np.random.default_rng(abs(hash(name)) % (2 ** 32))
+        # seeded by the layer's name through a stable hash: the same weights in every process
+        # (the reference draws from hash(name), which Python salts per process,
+        # autograd.py:172-173 / transformer.py:80-82; its tests overwrite the weights anyway)
+        rng = np.random.default_rng(zlib.crc32(name.encode()))
         w = (rng.standard_normal((in_f, out_f)) * np.sqrt(2.0 / in_f)).astype(np.float32)
         self.W = Param(ctx, (in_f, out_f), w, name + ".W")
         self.b = Param(ctx, (out_f,), np.zeros(out_f, np.float32), name + ".b", no_decay=True)

@@ -1178,7 +1178,8 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
   const long long n_items = (long long)p.nqt * H * B;
   VKG_REQUIRE(n_items < (1ll << 31), "attn_bwd: too many tiles");
   // persistent kernels: one CTA per SM (their shared memory allows no more), items dealt round-robin
-  const unsigned ctas = (unsigned)(n_items < dev->sm_count ? n_items : dev->sm_count);
+  const int sms = vkg_persistent_ctas(dev);
+  const unsigned ctas = (unsigned)(n_items < sms ? n_items : sms);
   VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_kv_kernel, dim3(ctas), dim3(BW_THREADS), KV_SMEM, 1, tm, tmdo, p));
   if (vkg_check_launch("attn_bwd_kv_kernel")) return 1;
   VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_q_kernel, dim3(ctas), dim3(BW_THREADS), DQ_SMEM, 1, tm, tmdo, p));

@@ -4,6 +4,8 @@
 // the library loads (and single-GPU work runs) on a machine without it.
 #include <dlfcn.h>
 
+#include <climits>
+
 #include "common.cuh"
 
 namespace {
@@ -17,12 +19,27 @@ struct NcclApi {
   void* handle = nullptr;
   int (*GetUniqueId)(ncclUniqueId*) = nullptr;
   int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  int (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, void*) = nullptr;
   int (*CommDestroy)(ncclComm_t) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   const char* (*GetLastError)(ncclComm_t) = nullptr;
   int (*CommAbort)(ncclComm_t) = nullptr;
   int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
+};
+
+// ncclConfig_t as NCCL 2.18 laid it out (later releases only append fields and accept the
+// shorter structure, told apart by `size` and `version`).  Unset fields carry INT_MIN / NULL.
+struct NcclConfig218 {
+  size_t size;
+  unsigned int magic;
+  unsigned int version;
+  int blocking;
+  int cgaClusterSize;
+  int minCTAs;
+  int maxCTAs;
+  const char* netName;
+  int splitShare;
 };
 
 NcclApi g_nccl;
@@ -47,6 +64,8 @@ int load_nccl() {
   api.handle = h;
   api.GetUniqueId = (int (*)(ncclUniqueId*))dlsym(h, "ncclGetUniqueId");
   api.CommInitRank = (int (*)(ncclComm_t*, int, ncclUniqueId, int))dlsym(h, "ncclCommInitRank");
+  api.CommInitRankConfig =
+      (int (*)(ncclComm_t*, int, ncclUniqueId, int, void*))dlsym(h, "ncclCommInitRankConfig");
   api.CommDestroy = (int (*)(ncclComm_t))dlsym(h, "ncclCommDestroy");
   api.AllReduce = (int (*)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t))dlsym(
       h, "ncclAllReduce");
@@ -80,23 +99,30 @@ struct vkg_comm {
 };
 
 // Hooks the device's host waits call while this communicator is attached (common.cuh).
+// ctx is the device; every communicator attached to it is checked / aborted.
 static int comm_async_error(void* ctx) {
-  vkg_comm* c = static_cast<vkg_comm*>(ctx);
-  if (!c->comm || !g_nccl.CommGetAsyncError) return 0;
-  int state = 0;
-  if (g_nccl.CommGetAsyncError(c->comm, &state) != 0 || state != 0) {
-    vkg_set_error("NCCL reported an asynchronous error: %s",
-                  g_nccl.GetErrorString ? g_nccl.GetErrorString(state) : "?");
-    return 1;
+  vkg_device* dev = static_cast<vkg_device*>(ctx);
+  for (void* v : dev->comms) {
+    vkg_comm* c = static_cast<vkg_comm*>(v);
+    if (!c->comm || !g_nccl.CommGetAsyncError) continue;
+    int state = 0;
+    if (g_nccl.CommGetAsyncError(c->comm, &state) != 0 || state != 0) {
+      vkg_set_error("NCCL reported an asynchronous error: %s",
+                    g_nccl.GetErrorString ? g_nccl.GetErrorString(state) : "?");
+      return 1;
+    }
   }
   return 0;
 }
 
 static void comm_abort(void* ctx) {
-  vkg_comm* c = static_cast<vkg_comm*>(ctx);
-  if (c->comm && g_nccl.CommAbort) g_nccl.CommAbort(c->comm);
-  else if (c->comm) g_nccl.CommDestroy(c->comm);
-  c->comm = nullptr;     // every later collective on it fails instead of hanging
+  vkg_device* dev = static_cast<vkg_device*>(ctx);
+  for (void* v : dev->comms) {
+    vkg_comm* c = static_cast<vkg_comm*>(v);
+    if (c->comm && g_nccl.CommAbort) g_nccl.CommAbort(c->comm);
+    else if (c->comm) g_nccl.CommDestroy(c->comm);
+    c->comm = nullptr;     // every later collective on it fails instead of hanging
+  }
 }
 
 #define VKG_NCCL(expr)                                                              \
@@ -119,6 +145,11 @@ extern "C" int vkg_comm_unique_id(uint8_t id[128]) {
 
 extern "C" int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint8_t id[128],
                                vkg_comm** out) {
+  return vkg_comm_create_limited(dev, rank, nranks, id, 0, out);
+}
+
+extern "C" int vkg_comm_create_limited(vkg_device* dev, int rank, int nranks, const uint8_t id[128],
+                                       int max_ctas, vkg_comm** out) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(out && id, "comm_create: null argument");
   VKG_REQUIRE(nranks >= 1 && rank >= 0 && rank < nranks, "comm_create: rank %d of %d", rank, nranks);
@@ -129,7 +160,23 @@ extern "C" int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint
   c->dev = dev;
   c->rank = rank;
   c->nranks = nranks;
-  int r = g_nccl.CommInitRank(&c->comm, nranks, uid, rank);
+  int r;
+  if (max_ctas > 0) {
+    if (!g_nccl.CommInitRankConfig) {
+      delete c;
+      VKG_FAIL("comm_create: this NCCL has no ncclCommInitRankConfig (needed for max_ctas)");
+    }
+    NcclConfig218 cfg;
+    cfg.size = sizeof(cfg);
+    cfg.magic = 0xcafebeefu;
+    cfg.version = 21800;
+    cfg.blocking = cfg.cgaClusterSize = cfg.minCTAs = cfg.splitShare = INT_MIN;
+    cfg.maxCTAs = max_ctas;
+    cfg.netName = nullptr;
+    r = g_nccl.CommInitRankConfig(&c->comm, nranks, uid, rank, &cfg);
+  } else {
+    r = g_nccl.CommInitRank(&c->comm, nranks, uid, rank);
+  }
   if (r != 0) {
     delete c;
     VKG_FAIL("ncclCommInitRank failed: %s", g_nccl.GetErrorString(r));
@@ -152,7 +199,8 @@ extern "C" int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint
     VKG_FAIL("comm_create: first collective failed (%s / %s)", r ? g_nccl.GetErrorString(r) : "ok",
              cudaGetErrorString(e));
   }
-  dev->wait_ctx = c;
+  dev->comms.push_back(c);
+  dev->wait_ctx = dev;
   dev->on_async_error = comm_async_error;
   dev->on_abort = comm_abort;
   *out = c;
@@ -161,10 +209,18 @@ extern "C" int vkg_comm_create(vkg_device* dev, int rank, int nranks, const uint
 
 extern "C" int vkg_comm_destroy(vkg_comm* comm) {
   if (!comm) return 0;
-  if (comm->dev && comm->dev->wait_ctx == comm) {
-    comm->dev->wait_ctx = nullptr;
-    comm->dev->on_async_error = nullptr;
-    comm->dev->on_abort = nullptr;
+  if (comm->dev) {
+    std::vector<void*>& v = comm->dev->comms;
+    for (size_t i = 0; i < v.size(); ++i)
+      if (v[i] == comm) {
+        v.erase(v.begin() + i);
+        break;
+      }
+    if (v.empty()) {
+      comm->dev->wait_ctx = nullptr;
+      comm->dev->on_async_error = nullptr;
+      comm->dev->on_abort = nullptr;
+    }
   }
   if (comm->dev) cudaSetDevice(comm->dev->ordinal);
   if (comm->dev) cudaStreamSynchronize(comm->dev->stream);

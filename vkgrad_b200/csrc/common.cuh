@@ -62,11 +62,20 @@ struct vkg_device {
   int (*on_async_error)(void* ctx) = nullptr;
   void (*on_abort)(void* ctx) = nullptr;
   double wait_timeout_s = 60.0;
+  std::vector<void*> comms;          // communicators attached to this device (comm.cu)
+  // Persistent kernels (GEMMs, grouped GEMMs, attention backward) launch at most this many
+  // CTAs; 0 = one per SM.  Lowered while a collective runs beside the compute stream so that
+  // the collective's CTAs find free SMs instead of delaying a statically scheduled grid.
+  int sm_limit = 0;
   // vkg_finals_defer / vkg_finals_flush: final passes of two-stage column sums collected
   // instead of launched, then run as one launch
   bool defer_finals = false;
   std::vector<vkg_final_entry> finals;
 };
+
+static inline int vkg_persistent_ctas(const vkg_device* dev) {
+  return dev->sm_limit > 0 && dev->sm_limit < dev->sm_count ? dev->sm_limit : dev->sm_count;
+}
 
 struct vkg_graph {
   cudaGraph_t graph = nullptr;

@@ -1181,7 +1181,7 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
               "workspace, and N, ldc multiples of 4");
   int bn = 0, want_split = 1;
   const int bm = use_pair ? 2 * BM : BM;
-  plan_gemm(a->M, a->N, a->K, batch, use_pair ? dev->sm_count / 2 : dev->sm_count,
+  plan_gemm(a->M, a->N, a->K, batch, use_pair ? vkg_persistent_ctas(dev) / 2 : vkg_persistent_ctas(dev),
             may_split && a->split_k != 1, a->workspace_bytes,
             use_pair ? PAIR_BN : (force_bn ? force_bn : a->tile_n), a->split_k > 1 ? a->split_k : 0,
             &bn, &want_split, bm);
@@ -1423,13 +1423,13 @@ extern "C" int vkg_gemm_group_launch(vkg_device* dev, const void* table, int n, 
   }
   if (total_units < 0) {
     const int units = -total_units;
-    int pairs = dev->sm_count / 2;
+    int pairs = vkg_persistent_ctas(dev) / 2;
     if (pairs > units) pairs = units;
     VKG_CUDA(vkg_launch(dev, VKG_K_GEMM_GROUP, gemm_group_pair_kernel, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
                         SMEM_BYTES, 2, static_cast<const GroupEntry*>(table), n, units));
     return vkg_check_launch("gemm_group_pair_kernel");
   }
-  int ctas = dev->sm_count < total_units ? dev->sm_count : total_units;
+  int ctas = vkg_persistent_ctas(dev) < total_units ? vkg_persistent_ctas(dev) : total_units;
   const int stages = RING_BYTES / (A_STAGE_BYTES + 256 * 128);
   VKG_CUDA(vkg_launch(dev, VKG_K_GEMM_GROUP, gemm_group_kernel, dim3((unsigned)ctas), dim3(NUM_THREADS), SMEM_BYTES, 1,
                       static_cast<const GroupEntry*>(table), n, total_units, 256, stages));
@@ -1451,7 +1451,7 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
     // handful of waves they time the same alone and a little slower inside a training step,
     // and with one wave and a bit they lose.
     if (build_problem(dev, a, 0, &q, true)) return 1;
-    use_pair = q.p.split_k > 1 || q.total_tiles >= 6ll * (dev->sm_count / 2);
+    use_pair = q.p.split_k > 1 || q.total_tiles >= 6ll * (vkg_persistent_ctas(dev) / 2);
   }
   if (use_pair) {
     if (build_problem(dev, a, 0, &q, true)) return 1;
@@ -1459,7 +1459,7 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
     GemmKernel fn = gemm_cta_pair_kernel<E_GENERIC>;
     for (int i = 0; i < kNumCtaPair; ++i)
       if (kCtaPair[i].mode == q.mode) fn = kCtaPair[i].fn;
-    long long pairs = dev->sm_count / 2;
+    long long pairs = vkg_persistent_ctas(dev) / 2;
     if (pairs > q.total_tiles) pairs = q.total_tiles;
     VKG_CUDA(vkg_launch(dev, VKG_K_GEMM_PAIR, fn, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS), SMEM_BYTES, 2, q.tmA,
                         q.tmB, q.tmC, q.tmP, q.p));
@@ -1469,7 +1469,7 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   }
   if (build_problem(dev, a, 0, &q)) return 1;
   if (ensure_attrs(dev)) return 1;
-  int ctas = a->max_ctas > 0 ? a->max_ctas : dev->sm_count;
+  int ctas = a->max_ctas > 0 ? a->max_ctas : vkg_persistent_ctas(dev);
   if (ctas > q.total_tiles) ctas = (int)q.total_tiles;
   VKG_CUDA(vkg_launch(dev, VKG_K_GEMM, pick_kernel(q.mode), dim3((unsigned)ctas), dim3(NUM_THREADS), SMEM_BYTES, 1,
                       q.tmA, q.tmB, q.tmC, q.tmP, q.p));

@@ -244,6 +244,105 @@ __global__ void k_embed_bwd_v4(const float4* __restrict__ dx, const uint32_t* __
   }
 }
 
+// Deterministic scatter-add of the embedding backward (the reference adds with float atomics,
+// tkernels.py:317-360, whose order changes from run to run).  Rows that hit the same table
+// row are linked into a chain in row order; the warp that owns a chain's first row walks it,
+// adds the rows in that order in registers and updates the table row once.
+//
+// Table `which`: 0 the token table (key = ids[r]), 1 the position table (key = r % T, minus
+// the start of the row's packed sample).  keys[which][rows_p] (rows_p = rows rounded up to 4,
+// the padding holds -2), next[which][rows] = the next row with r's key or -1,
+// has_prev[which][rows] = 1 when an earlier row has it.
+__device__ __forceinline__ int embed_key(int which, int r, const uint32_t* ids, const uint32_t* seg,
+                                         int T) {
+  if (which == 0) return (int)ids[r];
+  int t = r % T;
+  if (seg) t -= (int)seg[r];
+  return t;
+}
+
+__global__ void k_embed_keys(const uint32_t* __restrict__ ids, const uint32_t* __restrict__ seg,
+                             int* __restrict__ keys, int* __restrict__ has_prev, int rows, int rows_p,
+                             int T) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 2 * rows_p) return;
+  const int which = i / rows_p, r = i - which * rows_p;
+  keys[i] = r < rows ? embed_key(which, r, ids, seg, T) : -2;
+  if (r < rows) has_prev[which * rows + r] = 0;
+}
+
+// One warp per (table, row): the lanes look through the later rows 128 keys at a time (one
+// 16-byte load each) and stop at the first chunk that holds the row's key; the smallest such
+// row is the successor, whatever the timing.
+__global__ void __launch_bounds__(256)
+k_embed_chain(const int* __restrict__ keys, int* __restrict__ next, int* __restrict__ has_prev,
+              int rows, int rows_p) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= 2 * rows) return;
+  const int which = w / rows, r = w - which * rows;
+  const int* k = keys + (size_t)which * rows_p;
+  const int key = k[r];
+  int found = -1;
+  for (int j0 = ((r + 1) & ~3) + lane * 4; ; j0 += 128) {
+    unsigned m = 0;
+    if (j0 < rows_p) {
+      const int4 v = *reinterpret_cast<const int4*>(k + j0);
+      m = (v.x == key && j0 > r ? 1u : 0u) | (v.y == key && j0 + 1 > r ? 2u : 0u) |
+          (v.z == key && j0 + 2 > r ? 4u : 0u) | (v.w == key && j0 + 3 > r ? 8u : 0u);
+    }
+    const unsigned any = __ballot_sync(0xffffffffu, m != 0u);
+    if (any) {
+      const int src = __ffs(any) - 1;
+      const int mine = j0 + __ffs(m) - 1;       // meaningful on lane `src` only
+      found = __shfl_sync(0xffffffffu, mine, src);
+      break;
+    }
+    if (__all_sync(0xffffffffu, j0 + 128 - lane * 4 >= rows_p)) break;   // the warp is past the end
+  }
+  if (lane == 0) {
+    next[which * rows + r] = found;
+    if (found >= 0) has_prev[which * rows + found] = 1;   // one writer: its predecessor
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256)
+k_embed_bwd_chain(const float* __restrict__ dx, const uint32_t* __restrict__ ids,
+                  const uint32_t* __restrict__ seg, const int* __restrict__ next,
+                  const int* __restrict__ has_prev, float* __restrict__ dtok, float* __restrict__ dpos,
+                  int rows, int T) {
+  constexpr int D = NV * 128;
+  pdl_trigger();
+  pdl_wait();
+  const int which = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r0 = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (r0 >= rows || has_prev[which * rows + r0]) return;
+  float4 acc[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = r0; r >= 0; r = next[which * rows + r]) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const float4 g = *reinterpret_cast<const float4*>(dx + (size_t)r * D + (i * 32 + lane) * 4);
+      acc[i].x += g.x; acc[i].y += g.y; acc[i].z += g.z; acc[i].w += g.w;
+    }
+  }
+  float* row = (which == 0 ? dtok : dpos) + (size_t)embed_key(which, r0, ids, seg, T) * D;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float4* p = reinterpret_cast<float4*>(row + (i * 32 + lane) * 4);
+    float4 v = *p;
+    v.x += acc[i].x; v.y += acc[i].y; v.z += acc[i].z; v.w += acc[i].w;
+    *p = v;
+  }
+}
+
 // ---- column sums ------------------------------------------------------------------
 
 // The reference's col_sum: one thread per column over fp32 rows (kernels.py:753).
@@ -728,12 +827,23 @@ k_layernorm_bwd_vec(const float* __restrict__ dy, const float* __restrict__ x,
   for (int row = blockIdx.x * LNV_WARPS + warp; row < rows; row += warps_total) {
     const size_t base = (size_t)row * D;
     const float m = mu[row], r = rstd[row];
-    float4 xv[NV], dv[NV];
+    // all three streams of the row are requested before anything is consumed: the kernel
+    // holds one CTA per SM (its registers), so memory latency is hidden by loads in flight
+    // per warp, not by other warps
+    float4 xv[NV], dv[NV], rv[NV];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       xv[i] = *reinterpret_cast<const float4*>(x + base + (i * 32 + lane) * 4);
       dv[i] = *reinterpret_cast<const float4*>(dy + base + (i * 32 + lane) * 4);
+    }
+    if (dres) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        rv[i] = *reinterpret_cast<const float4*>(dres + base + (i * 32 + lane) * 4);
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) rv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -756,10 +866,7 @@ k_layernorm_bwd_vec(const float* __restrict__ dy, const float* __restrict__ x,
       o.z = r * (dv[i].z * g[i].z - s1 - xv[i].z * s2);
       o.w = r * (dv[i].w * g[i].w - s1 - xv[i].w * s2);
       const size_t off = base + (i * 32 + lane) * 4;
-      if (dres) {
-        float4 d = *reinterpret_cast<const float4*>(dres + off);
-        o.x += d.x; o.y += d.y; o.z += d.z; o.w += d.w;
-      }
+      o.x += rv[i].x; o.y += rv[i].y; o.z += rv[i].z; o.w += rv[i].w;
       if (dx) *reinterpret_cast<float4*>(dx + off) = o;
       if (dx16) {
         __half2 a = __floats2half2_rn(o.x, o.y), b = __floats2half2_rn(o.z, o.w);
@@ -1467,6 +1574,49 @@ extern "C" int vkg_embed_bwd(vkg_device* dev, const float* dx, const uint32_t* i
   }
   k_embed_bwd<<<flat_grid(dev, n), TPB, 0, dev->stream>>>(dx, ids, seg, dtok, dpos, n, D, T);
   return vkg_check_launch("embed_bwd");
+}
+
+extern "C" int64_t vkg_embed_bwd_scratch_bytes(int64_t rows) {
+  // keys[2][rows rounded up to 4], next[2][rows], has_prev[2][rows]
+  return rows > 0 ? (6 * rows + 8) * (int64_t)sizeof(int) : 0;
+}
+
+extern "C" int vkg_embed_bwd_det(vkg_device* dev, const float* dx, const uint32_t* ids,
+                                 const uint32_t* seg, float* dtok, float* dpos, void* scratch,
+                                 int64_t n, int D, int T) {
+  if (vkg_bind(dev)) return 1;
+  VKG_REQUIRE(dx && ids && dtok && dpos && scratch && n > 0 && D > 0 && T > 0,
+              "embed_bwd_det: bad arguments");
+  VKG_REQUIRE(D % 128 == 0 && D <= 1024 && n % D == 0 && n / D < (1ll << 30) &&
+                  ((((uintptr_t)dx | (uintptr_t)dtok | (uintptr_t)dpos | (uintptr_t)scratch) & 15) == 0),
+              "embed_bwd_det: D must be a multiple of 128 up to 1024 and the tables 16-byte aligned "
+              "(use vkg_embed_bwd otherwise)");
+  const int rows = (int)(n / D), rows_p = (rows + 3) & ~3;
+  int* keys = static_cast<int*>(scratch);
+  int* next = keys + 2 * (size_t)rows_p;
+  int* has_prev = next + 2 * (size_t)rows;
+  VKG_CUDA(vkg_launch(dev, VKG_K_SMALL, k_embed_keys, dim3((unsigned)((2 * rows_p + 255) / 256)),
+                      dim3(256), 0, 1, ids, seg, keys, has_prev, rows, rows_p, T));
+  if (vkg_check_launch("embed_keys")) return 1;
+  VKG_CUDA(vkg_launch(dev, VKG_K_SMALL, k_embed_chain, dim3((unsigned)((2 * rows + 7) / 8)), dim3(256), 0,
+                      1, (const int*)keys, next, has_prev, rows, rows_p));
+  if (vkg_check_launch("embed_chain")) return 1;
+  const dim3 grid((unsigned)((rows + 7) / 8), 2);
+#define VKG_EB(NV)                                                                               \
+  VKG_CUDA(vkg_launch(dev, VKG_K_SMALL, k_embed_bwd_chain<NV>, grid, dim3(256), 0, 1, dx, ids, seg, \
+                      (const int*)next, (const int*)has_prev, dtok, dpos, rows, T))
+  switch (D / 128) {
+    case 1: VKG_EB(1); break;
+    case 2: VKG_EB(2); break;
+    case 3: VKG_EB(3); break;
+    case 4: VKG_EB(4); break;
+    case 5: VKG_EB(5); break;
+    case 6: VKG_EB(6); break;
+    case 7: VKG_EB(7); break;
+    default: VKG_EB(8); break;
+  }
+#undef VKG_EB
+  return vkg_check_launch("embed_bwd_chain");
 }
 
 extern "C" int vkg_residual(vkg_device* dev, const float* acc, const float* bias, const float* res,

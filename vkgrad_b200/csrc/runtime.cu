@@ -92,11 +92,18 @@ extern "C" int vkg_set_pdl(vkg_device* dev, int on) {
 
 extern "C" int vkg_set_tuning(vkg_device* dev, int key, int64_t value) {
   if (!dev) VKG_FAIL("null device");
-  VKG_REQUIRE(!dev->capturing, "set_tuning: not while a graph is being recorded");
+  // the SM limit is host state read when a launch is enqueued: it may change between the
+  // launches of one recording
+  VKG_REQUIRE(!dev->capturing || key == VKG_TUNE_SM_LIMIT,
+              "set_tuning: not while a graph is being recorded");
   switch (key) {
     case VKG_TUNE_PDL: dev->pdl = value != 0; break;
     case VKG_TUNE_PDL_FAMILIES: dev->pdl_mask = (unsigned)value; break;
     case VKG_TUNE_TMA_STORE: dev->tma_store = value != 0; break;
+    case VKG_TUNE_SM_LIMIT:
+      VKG_REQUIRE(value >= 0, "set_tuning: the SM limit cannot be negative");
+      dev->sm_limit = (int)value;
+      break;
     case VKG_TUNE_WAIT_TIMEOUT_MS:
       VKG_REQUIRE(value > 0, "set_tuning: the wait limit must be positive");
       dev->wait_timeout_s = (double)value * 1e-3;

@@ -107,12 +107,16 @@ def _recv_exact(s, n):
 class Comm:
     """An NCCL communicator bound to one Device (one process per GPU)."""
 
-    def __init__(self, dev, rank, world, unique_id):
+    def __init__(self, dev, rank, world, unique_id, max_ctas=0):
+        """max_ctas > 0 holds NCCL to that many CTAs: for a communicator whose collectives run
+        beside the compute stream."""
         self.dev, self.rank, self.world = dev, rank, world
         uid = (C.c_uint8 * 128).from_buffer_copy(unique_id)
         h = C.c_void_p()
-        _check(dev.lib.vkg_comm_create(dev.handle, rank, world, uid, C.byref(h)), "comm_create")
+        _check(dev.lib.vkg_comm_create_limited(dev.handle, rank, world, uid, int(max_ctas),
+                                               C.byref(h)), "comm_create")
         self.handle = h
+        self.max_ctas = int(max_ctas)
 
     @staticmethod
     def make_unique_id(lib):
@@ -121,14 +125,14 @@ class Comm:
         return bytes(uid)
 
     @classmethod
-    def from_env(cls, dev, port_offset=101):
+    def from_env(cls, dev, port_offset=101, max_ctas=0):
         """Build from RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT (torchrun's variables)."""
         rank = int(os.environ.get("RANK", "0"))
         world = int(os.environ.get("WORLD_SIZE", "1"))
         addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
         port = (int(os.environ.get("MASTER_PORT", "29500")) + port_offset) % 65536
         uid = exchange_unique_id(rank, world, lambda: cls.make_unique_id(dev.lib), addr, port)
-        return cls(dev, rank, world, uid)
+        return cls(dev, rank, world, uid, max_ctas=max_ctas)
 
     def allreduce_sum(self, buf, count, dtype=F32, offset_bytes=0):
         _check(self.dev.lib.vkg_allreduce_sum(self.handle, buf.dptr + offset_bytes, count, dtype),
@@ -214,31 +218,6 @@ def flatten_gradients(ctx, params):
     return bucket, offs, off
 
 
-def _bucket_chunks(params, offsets, total, n_chunks):
-    """Cut the flat gradient bucket into at most n_chunks contiguous parts of about equal size
-    that end on tensor boundaries: [(first_float, n_floats, params_in_part)]."""
-    params = list(params)
-    if n_chunks <= 1 or len(params) < 2:
-        return [(0, total, params)]
-    ends = list(offsets[1:]) + [total]
-    parts, start_i, start_off = [], 0, 0
-    for k in range(1, n_chunks + 1):
-        target = total * k // n_chunks
-        # the first tensor boundary at or past the target (never an empty part)
-        i = start_i
-        while i < len(params) - 1 and ends[i] < target:
-            i += 1
-        if k == n_chunks:
-            i = len(params) - 1
-        if i < start_i:
-            continue
-        parts.append((start_off, ends[i] - start_off, params[start_i:i + 1]))
-        start_i, start_off = i + 1, ends[i]
-        if start_i >= len(params):
-            break
-    return parts
-
-
 class Replica:
     """One device's copy of the model plus its part in the exchange (dataparallel.py:102-150).
 
@@ -311,79 +290,119 @@ class DataParallelStep:
     host buffers copied to the device inside the step, so per-step data written by
     the caller is picked up by every replay.
 
-    With more than one worker the step is two CUDA graphs with the NCCL call enqueued
-    between them on the same stream (no host synchronisation in between).
-    overlap_chunks=k > 1 instead all-reduces the bucket in k parts on a side stream and runs
-    one AdamW graph per part on the compute stream, each waiting only for its own part, so
-    the optimiser works on part j while part j + 1 is still being summed.  Measured on
-    B200s it does not pay: equal at 2 GPUs (11.96 vs 11.97 ms per step), 0.45 ms slower at 8
-    (12.87 vs 12.39 ms) -- the memory-bound AdamW and the collective slow each other down --
-    so one all-reduce is the default.  in_graph=True captures the all-reduce into a single
-    graph instead.
+    With more than one worker the step is several CUDA graphs with the NCCL calls enqueued
+    between them (no host synchronisation in between); in_graph=True captures the one
+    all-reduce into a single graph instead.
+
+    overlap_groups=k > 1 hides most of the exchange under the backward (the reference's
+    workers push each tensor as soon as it exists, dataparallel.py:119-126).  The blocks are
+    cut into k groups from the top; as soon as the backward of a group is done, its dW GEMMs
+    and final passes run (GPT.record(flush_after=...)), which completes that part of the flat
+    bucket, and its all-reduce starts on a side stream while the compute stream goes on with
+    the blocks below.  Only the last part -- the lowest blocks and the embedding tables,
+    whose gradient is final only after the embedding backward -- is summed on the compute
+    stream after the backward.  The sums are the same fp32 NCCL sums over the same bytes, so
+    replicas stay bit-identical and results equal the unsplit exchange bit for bit.
+    The side stream should use `side_comm`, a communicator held to a few CTAs
+    (Comm(..., max_ctas=n)); the persistent kernels recorded after the first flush then launch
+    sm_count - side_sms CTAs so that NCCL's CTAs find free SMs instead of delaying a statically
+    scheduled grid by a whole wave.
     """
 
     def __init__(self, replica, ids_dev, targets_dev, host_ids=None, host_targets=None,
-                 name="dp_step", in_graph=False, overlap_chunks=1, **record_kwargs):
+                 name="dp_step", in_graph=False, overlap_groups=1, side_comm=None, side_sms=0,
+                 **record_kwargs):
         self.replica = replica
         self.model, self.opt = replica.model, replica.opt
         dev = self.dev = replica.dev
         lib, h = dev.lib, dev.handle
-        g = dev.graph(name)
+        comm = replica.comm
+        workers = comm.world if comm is not None else 1
+        blocks = getattr(self.model, "blocks", None)
+        k = int(overlap_groups)
+        split = (comm is not None and comm.world > 1 and not in_graph and k > 1
+                 and blocks is not None and len(blocks) >= k)
+        self.between = None
+        self.parts = None
+        upload = None
         if host_ids is not None:
             pairs = [(ids_dev, host_ids), (targets_dev, host_targets)]
 
             def upload():
                 for d, s in pairs:
                     _check(lib.vkg_copy_h2d_async(h, d.dptr, s.hptr, min(d.size, s.size)), "h2d")
-            g.add(upload, "h2d_inputs", sum(min(d.size, s.size) for d, s in pairs))
-            g.n_dispatch -= 1
-        self.model.record(ids_dev, targets_dev, g, **record_kwargs)
-        comm = replica.comm
-        self.between = None
-        self.graphs = [g]
-        workers = comm.world if comm is not None else 1
+            upload.nbytes = sum(min(d.size, s.size) for d, s in pairs)
+
+        def first_graph(g):
+            if upload is not None:
+                g.add(upload, "h2d_inputs", upload.nbytes)
+                g.n_dispatch -= 1
+            return g
+
         self.opt.grad_scale = 1.0 / (workers * replica.loss_scale)
-        self.chunks = None
-        if comm is not None and comm.world > 1 and not in_graph:
+        if split:
+            L = len(blocks)
+            flush = backward_flush_points(L, k)
+            gs = [dev.graph(f"{name}_{j}") for j in range(len(flush) + 1)]
+            first_graph(gs[0])
+
+            def stage(s):
+                if s < L + 2:
+                    return gs[0]
+                i = L - 1 - (s - (L + 2))          # block whose backward this stage is
+                return gs[sum(1 for f in flush if f > i)]
+            sm_limit = dev.sm_count - int(side_sms) if side_sms > 0 else 0
+            self.model.record(ids_dev, targets_dev, stage, flush_after=flush,
+                              sm_limit_after_flush=sm_limit, **record_kwargs)
+            for g in gs:
+                g.finish()
+            self.parts = bucket_parts_for_flush(replica.params, replica.offsets, replica.total,
+                                                blocks, flush)
+            self.side = side_comm if side_comm is not None else comm
+            g_opt = dev.graph(name + "_opt")
+            self.opt.record(g_opt)
+            g_opt.finish()
+            self.graphs = gs + [g_opt]
+        elif comm is not None and comm.world > 1 and not in_graph:
+            g = first_graph(dev.graph(name))
+            self.model.record(ids_dev, targets_dev, g, **record_kwargs)
             g.finish()
             bucket, total = replica.bucket, replica.total
-            groups = _bucket_chunks(replica.params, replica.offsets, total, overlap_chunks)
-            if len(groups) > 1:
-                # all-reduce the bucket in parts on the side stream; AdamW over part k runs on
-                # the compute stream while part k + 1 is still being summed
-                self.chunks = []
-                for k, (first, count, params) in enumerate(groups):
-                    gk = dev.graph(f"{name}_opt{k}")
-                    self.opt.record(gk, params=params)
-                    gk.finish()
-                    self.chunks.append((first, count, gk))
-                    self.graphs.append(gk)
-            else:
-                self.between = lambda: comm.allreduce_sum(bucket, total)
-                g = dev.graph(name + "_opt")
-                self.graphs.append(g)
-                self.opt.record(g)
-                g.finish()
+            self.between = lambda: comm.allreduce_sum(bucket, total)
+            g_opt = dev.graph(name + "_opt")
+            self.opt.record(g_opt)
+            g_opt.finish()
+            self.graphs = [g, g_opt]
         else:
+            g = first_graph(dev.graph(name))
+            self.model.record(ids_dev, targets_dev, g, **record_kwargs)
             replica.push_gradients(graph=g)
             self.opt.record(g)
             g.finish()
+            self.graphs = [g]
         self.n_dispatch = sum(x.n_dispatch for x in self.graphs)
         self.n_kernels = sum(x.n_kernels for x in self.graphs)
 
     def enqueue(self, lr=None):
         """Advance the schedule and launch without waiting (pair with dev.sync())."""
         self.opt.advance(lr)
+        if self.parts is not None:
+            comm, side, bucket = self.replica.comm, self.side, self.replica.bucket
+            n = len(self.parts)
+            for j, (first, count) in enumerate(self.parts):
+                self.graphs[j].submit_async()
+                if j < n - 1:
+                    # this part of the bucket is complete: sum it beside the rest of the backward
+                    side.side_begin()
+                    side.allreduce_sum_side(bucket, count, j, offset_bytes=4 * first)
+                else:
+                    comm.allreduce_sum(bucket, count, offset_bytes=4 * first)
+            for j in range(n - 1):
+                side.side_wait(j)
+            self.graphs[-1].submit_async()
+            return
         self.graphs[0].submit_async()
-        if self.chunks is not None:
-            comm, bucket = self.replica.comm, self.replica.bucket
-            comm.side_begin()
-            for k, (first, count, _) in enumerate(self.chunks):
-                comm.allreduce_sum_side(bucket, count, k, offset_bytes=4 * first)
-            for k, (_, _, gk) in enumerate(self.chunks):
-                comm.side_wait(k)
-                gk.submit_async()
-        elif self.between is not None:
+        if self.between is not None:
             self.between()
             self.graphs[1].submit_async()
 
@@ -394,6 +413,39 @@ class DataParallelStep:
         s = C.c_double(0.0)
         _check(lib.vkg_timer_end(h, C.byref(s)), "step")
         return self.model.read_loss(), s.value
+
+
+def backward_flush_points(n_blocks, groups):
+    """Block indices after whose backward a group's gradients are complete: the blocks are cut
+    into `groups` runs of (almost) equal length from the top; the lowest run has no flush point
+    (it ends with the embedding backward).  12 blocks in 3 groups -> [8, 4]."""
+    groups = max(1, min(int(groups), n_blocks))
+    pts = []
+    for j in range(1, groups):
+        i = n_blocks - (n_blocks * j) // groups
+        if 0 < i < n_blocks and i not in pts:
+            pts.append(i)
+    return pts
+
+
+def bucket_parts_for_flush(params, offsets, total, blocks, flush):
+    """[(first_float, n_floats)] of the flat bucket, in the order the parts complete during the
+    backward: part 0 = blocks flush[0].. and everything after them in params() order (the final
+    layernorm), part j = blocks flush[j] .. flush[j-1]-1, last part = everything below
+    flush[-1] (embedding tables first in params() order, and the lowest blocks)."""
+    params = list(params)
+    index = {id(p): n for n, p in enumerate(params)}
+    starts = []
+    for f in flush:
+        first = next(iter(blocks[f].params()))
+        starts.append(offsets[index[id(first)]])
+    parts, hi = [], total
+    for st in starts:
+        parts.append((st, hi - st))
+        hi = st
+    parts.append((0, hi))
+    assert all(c > 0 for _, c in parts) and sum(c for _, c in parts) == total
+    return parts
 
 
 class GradAccum:

@@ -24,9 +24,11 @@ A static loss scale can be applied in the loss kernel (`loss_scale`); parameter
 gradients then carry that factor until AdamW divides it out.
 """
 
+import zlib
+
 import numpy as np
 
-from ._lib import ACT_GELU, ACT_NONE, F16, F32
+from ._lib import ACT_GELU, ACT_NONE, F16, F32, TUNE_SM_LIMIT
 from .autograd import Ctx, Param
 from .kernels import gemm, gemm_group
 from .tkernels import make_transformer_kernels
@@ -129,7 +131,10 @@ class Dense:
     def __init__(self, ctx, rows, in_f, out_f, name="", scale=None):
         self.ctx, self.rows, self.in_f, self.out_f = ctx, rows, in_f, out_f
         self.name = name
-        rng = np.random.default_rng(abs(hash(name)) % (2 ** 32))
+        # seeded by the layer's name through a stable hash: the same weights in every process
+        # (the reference draws from hash(name), which Python salts per process,
+        # autograd.py:172-173 / transformer.py:80-82; its tests overwrite the weights anyway)
+        rng = np.random.default_rng(zlib.crc32(name.encode()))
         s = scale if scale is not None else np.sqrt(2.0 / in_f)
         w = (rng.standard_normal((in_f, out_f)) * s).astype(np.float32)
         self.W = Param(ctx, (in_f, out_f), w, name + ".W")
@@ -441,7 +446,8 @@ class GPT:
             self.head.forward(hf, graph=g(L), out=self.logits)
         return self.logits
 
-    def record(self, ids_buf, targets_buf, graph, backward=True, seg=None, weights=None):
+    def record(self, ids_buf, targets_buf, graph, backward=True, seg=None, weights=None,
+               flush_after=(), sm_limit_after_flush=0):
         """Record the loss and, unless backward=False, every gradient.
 
         graph may be a stage -> Graph callable that spreads the step over several
@@ -454,6 +460,12 @@ class GPT:
         weights: optional per-row loss weights replacing the 1/rows mean; the loss
         buffer then holds each row's unweighted cross entropy, 0 where the weight
         is 0 (kernels.py:793-827).
+        flush_after: block indices; once the backward of such a block is recorded, the dW GEMMs
+        collected so far are issued as a group and the pending final passes run, in that
+        block's stage graph -- every gradient of the blocks above it (and of lnf) is then
+        complete, so a data-parallel step can start summing that part of the bucket while the
+        blocks below are still in their backward.  sm_limit_after_flush > 0 caps the persistent
+        kernels recorded after the first flush at that many CTAs (room for the collective).
         """
         c, lib, h = self.ctx, self.ctx.dev.lib, self.ctx.dev.handle
         g = graph if callable(graph) else (lambda stage: graph)
@@ -492,23 +504,53 @@ class GPT:
         # the blocks' dW GEMMs (4 per block, 18..72 tiles each) are collected and issued as
         # one grouped launch once every dY exists
         dw_sink = [] if GROUP_DW and L > 0 else None
+        flush_after = set(int(i) for i in flush_after)
+        limited = False
         for k in range(L):
             i = L - 1 - k
-            d32, d16 = self.blocks[i].backward(d32, d16, graph=g(L + 2 + k), fc2_bias_grad_done=fuse,
+            gk = g(L + 2 + k)
+            d32, d16 = self.blocks[i].backward(d32, d16, graph=gk, fc2_bias_grad_done=fuse,
                                                below=self.blocks[i - 1] if i > 0 else None,
                                                dw_sink=dw_sink)
+            if i in flush_after and i > 0:
+                if dw_sink:
+                    gemm_group(c.dev, dw_sink, graph=gk, name=f"blocks{i}+.dW")
+                    dw_sink = []
+                c.launch(gk, lambda: _check(lib.vkg_finals_flush(h), "finals_flush"), "finals_flush")
+                c.launch(gk, lambda: _check(lib.vkg_finals_defer(h, 1), "finals_defer"),
+                         "finals_defer")
+                if sm_limit_after_flush > 0 and not limited:
+                    limited = True
+                    c.launch(gk, lambda: _check(lib.vkg_set_tuning(h, TUNE_SM_LIMIT,
+                                                                   int(sm_limit_after_flush)),
+                                                "sm_limit"), "sm_limit")
         ge = g(2 * L + 2)
         if dw_sink:
             gemm_group(c.dev, dw_sink, graph=ge, name="blocks.dW")
         seg_p = None if seg is None else seg.dptr
 
+        # rows that share a token (or a position) are added in row order by one warp, so the
+        # whole step is bit-reproducible; table widths the kernel has no instance for keep
+        # the reference's atomic scatter-add
+        det = D % 128 == 0 and D <= 1024
+        if det and getattr(self, "_emb_scratch", None) is None:
+            self._emb_scratch = c.buf(lib.vkg_embed_bwd_scratch_bytes(R))
+
         def emb_bwd():
             _check(lib.vkg_memset0(h, self.pos.g32.dptr, self.pos.n * 4), "zero pos grad")
+            if det:
+                _check(lib.vkg_embed_bwd_det(h, d32.dptr, ids_buf.dptr, seg_p, self.tok.g32.dptr,
+                                             self.pos.g32.dptr, self._emb_scratch.dptr, R * D, D,
+                                             self.T), "embed_bwd_det")
+                return
             _check(lib.vkg_embed_bwd(h, d32.dptr, ids_buf.dptr, seg_p, self.tok.g32.dptr,
                                      self.pos.g32.dptr, R * D, D, self.T), "embed_bwd")
         c.launch(ge, emb_bwd, "embed_bwd", R * D * 12)
         c.launch(ge, lambda: _check(lib.vkg_finals_flush(h), "finals_flush"), "finals_flush",
                  4 * sum(p.n for p in self.params() if len(p.shape) == 1))
+        if limited:
+            c.launch(ge, lambda: _check(lib.vkg_set_tuning(h, TUNE_SM_LIMIT, 0), "sm_limit"),
+                     "sm_limit")
 
     def read_loss(self):
         self.loss.invalidate()
