@@ -527,6 +527,59 @@ def run_trio_table(args):
     dev.destroy()
 
 
+def c5_summary(dev, steps=5, warmup=3):
+    """BASELINE config 5: the 24-layer d_model 1024 / 16 heads decoder (354.8 M parameters with
+    the tied embedding), 4 x 1024 tokens, one recorded step (forward + backward + AdamW)
+    replayed `steps` times with resident inputs."""
+    import ctypes as C
+    from vkgrad_b200 import vk
+    from vkgrad_b200.autograd import AdamW
+    from vkgrad_b200.dataparallel import DataParallelStep, Replica
+    from vkgrad_b200.transformer import GPT, TCtx
+    B, T, D, H, L, V = WORKLOADS["gpt-24l"]
+    R = B * T
+
+    def build(d):
+        ctx = TCtx(d)
+        model = GPT(ctx, B, T, D, H, L, V, tie=True, loss_scale=4096.0)
+        rng = np.random.default_rng(0)
+        for p in model.params():
+            if p.name.endswith(".g"):
+                p.set(np.ones(p.shape, np.float32))
+            elif len(p.shape) == 1:
+                p.set(np.zeros(p.shape, np.float32))
+            else:
+                p.set((rng.standard_normal(p.shape) * 0.02).astype(np.float32))
+        opt = AdamW(ctx, model.params(), lr=6e-4, wd=0.01)
+        return ctx, model, opt, ctx.buf(R * 4, "shared"), ctx.buf(R * 4, "shared")
+    rep = Replica(dev, build)
+    try:
+        ids, tgt = rep.ctx.buf(R * 4), rep.ctx.buf(R * 4)
+        rng = np.random.default_rng(5)
+        rep.xbuf.array(np.uint32)[:] = rng.integers(0, V, R)
+        rep.ybuf.array(np.uint32)[:] = rng.integers(0, V, R)
+        dev.copy(rep.xbuf, ids, R * 4)
+        dev.copy(rep.ybuf, tgt, R * 4)
+        step = DataParallelStep(rep, ids, tgt, name="c5")
+        for _ in range(warmup):
+            step.enqueue(6e-4)
+        dev.sync()
+        vk._check(dev.lib.vkg_timer_begin(dev.handle), "timer")
+        for _ in range(steps):
+            step.enqueue(6e-4)
+        sec = C.c_double(0.0)
+        vk._check(dev.lib.vkg_timer_end(dev.handle, C.byref(sec)), "timer")
+        ms = sec.value / steps * 1e3
+        n_par = rep.model.n_params()
+        return {"workload": "gpt-24l: 24 layers, d_model 1024, 16 heads, ctx 1024, vocab 50257 tied, "
+                            "batch 4x1024", "params": n_par, "ms_per_step": ms,
+                "tokens_per_s": R / (ms * 1e-3), "launches_per_step": step.n_kernels,
+                "algorithmic_tflop_per_step": step_flops(B, T, D, H, L, V) / 1e12,
+                "loss": rep.model.read_loss()}
+    finally:
+        rep.destroy()
+
+
 def c1_mlp_summary(dev, with_cpu=True, steps=200):
     """BASELINE config 1: MLP 784-256-256-10 (ReLU, softmax cross-entropy, AdamW lr 1e-3),
     batch 256, one recorded training step replayed `steps` times; beside it the numpy step of
@@ -827,6 +880,11 @@ def run_gpu_arm(args):
         if c_ is not None:
             c_.destroy()
     rep.destroy()
+    if line is not None and world == 1 and not args.no_extras and name == "gpt2-small":
+        peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        line["c5_gpt_24l"] = c5_summary(dev)
+        line["c5_gpt_24l"]["step_tensor_frac"] = (line["c5_gpt_24l"]["algorithmic_tflop_per_step"] /
+                                                  (line["c5_gpt_24l"]["ms_per_step"] * 1e-3) / peak)
     dev.destroy()
     if line is not None:
         print(json.dumps(line), flush=True)

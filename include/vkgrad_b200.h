@@ -79,9 +79,11 @@ int vkg_set_pdl(vkg_device* dev, int on);
  *                          (default 60 000): see vkg_sync
  *   VKG_TUNE_SM_LIMIT      most CTAs a persistent kernel (GEMM, grouped GEMM, attention
  *                          backward) launches; 0 = one per SM.  May also change during a
- *                          recording: launches recorded after the call use the new value */
+ *                          recording: launches recorded after the call use the new value
+ *   VKG_TUNE_PAIR_MIN_WAVES  tenths of a tile per CTA pair from which vkg_gemm with
+ *                          cta_pair == 0 takes 256 x 256 CTA-pair tiles */
 enum { VKG_TUNE_PDL = 0, VKG_TUNE_PDL_FAMILIES = 1, VKG_TUNE_TMA_STORE = 2,
-       VKG_TUNE_WAIT_TIMEOUT_MS = 3, VKG_TUNE_SM_LIMIT = 4 };
+       VKG_TUNE_WAIT_TIMEOUT_MS = 3, VKG_TUNE_SM_LIMIT = 4, VKG_TUNE_PAIR_MIN_WAVES = 5 };
 int vkg_set_tuning(vkg_device* dev, int key, int64_t value);
 /* Waits for the stream; reports a kernel error flag (bounded waits that gave
  * up) as a failure, like the reference's 10 s fence timeout (vk.py:884-888, 1335-1339).

@@ -96,8 +96,8 @@ def _gpt_step_case(dev, name, B, T, D, H, L, V, loss_scale, seed):
                        "adamw_max_abs_diff": chk})
         assert abs(loss - ref_loss) < 1e-3 * abs(ref_loss), (loss, ref_loss)
         assert abs(step_loss - loss) <= 1e-6 * abs(loss)
-        assert max(errs.values()) < 2e-3, worst
-        assert np.median(list(errs.values())) < 1e-3
+        # the bar for fp32-accumulated gradients: 1e-3 of each tensor's largest entry, every tensor
+        assert max(errs.values()) < 1e-3, worst
         assert max(chk.values()) < 1e-6, chk
     finally:
         rep.destroy()

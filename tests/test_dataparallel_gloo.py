@@ -181,8 +181,10 @@ class FakeOpt:
         self.lr = self.lr if lr is None else lr
 
     def record(self, graph, params=None):
+        ps = self.params if params is None else list(params)
+
         def go():
-            for p in self.params:
+            for p in ps:
                 w, p.m, p.v, _ = orc.adamw_step(p.w, p.g32.arr.reshape(p.shape), p.m, p.v, self.t,
                                                 lr=self.lr, wd=0.01 if p.w.ndim == 2 else 0.0,
                                                 gscale=self.grad_scale)
@@ -275,18 +277,19 @@ def test_overlapped_exchange_equals_one_all_reduce_and_the_single_process_oracle
     # the unsplit step: backward graph, ONE all-reduce of the whole bucket, optimiser graph
     kinds = [e[0] for e in plain[0][1][:3]]
     assert kinds == ["graph", "allreduce", "graph"] and plain[0][1][1][1:] == (0, FakeReplica(1, 1.0, []).total)
-    # the split step of 6 blocks in 3 groups: flushes after blocks 4 and 2; the upper two parts go
-    # to the side stream right after their graph, the last part follows the last backward graph,
-    # and the optimiser waits for both side sums
+    # the split step of 6 blocks in 3 groups: flushes after blocks 4 and 2; every part goes to a
+    # side stream right after the graph that completes it; the optimiser over the two upper
+    # parts waits for their sums only and runs while the last part is still being summed
     log = split[0][1]
     per_step = len(log) // 2
     names = [e[0] for e in log[:per_step]]
     assert names == ["graph", "side_begin", "allreduce_side", "graph", "side_begin", "allreduce_side",
-                     "graph", "allreduce", "side_wait", "side_wait", "graph"]
+                     "graph", "side_begin", "allreduce_side", "side_wait", "side_wait", "graph",
+                     "side_wait", "graph"]
+    assert [e[1] for e in log[:per_step] if e[0] == "side_wait"] == [0, 1, 2]
     assert split[0][2][:2] == [4, 2]
     sides = [e for e in log[:per_step] if e[0] == "allreduce_side"]
-    last = [e for e in log[:per_step] if e[0] == "allreduce"][0]
     total = FakeReplica(1, 1.0, []).total
     assert sides[0][1] + sides[0][2] == total                      # top part reaches the bucket's end
     assert sides[1][1] + sides[1][2] == sides[0][1]                # parts tile the bucket downwards
-    assert last[1] == 0 and last[2] == sides[1][1]
+    assert sides[2][1] == 0 and sides[2][2] == sides[1][1]

@@ -135,9 +135,18 @@ def test_gpt_against_faithful_oracle(dev, name, staged):
     assert abs(loss - ref_loss) < 1e-3 * abs(ref_loss)
     exp = expected(mg.flatten_grads(G, cfg["L"]), cfg["tie"])
     errs = {k: relerr(got[k], exp[k].reshape(got[k].shape)) for k in exp}
-    # fp16 rounding of a value that sits on a rounding boundary can differ between the
-    # GPU's fp32 sum order and numpy's; its effect stays a few 1e-4 of the tensor's max.
-    assert max(errs.values()) < 2e-3, sorted(errs.items(), key=lambda kv: -kv[1])[:5]
+    worst = sorted(errs.items(), key=lambda kv: -kv[1])[:5]
+    out = os.path.join(os.path.dirname(GOLD.rstrip("/")), "..", "gpurun_out")
+    if os.path.isdir(out):        # where a run's artefacts are collected, when that folder exists
+        import json
+        with open(os.path.join(out, f"parity_fixture_{name}.json"), "w") as f:
+            json.dump({"loss_rel_err": abs(loss - ref_loss) / abs(ref_loss), "worst_tensors": worst,
+                       "median_err": float(np.median(list(errs.values())))}, f, indent=1)
+    # These fixtures are tiny (D = 32..64, a few hundred rows): one fp16 value that sits on a
+    # rounding boundary and falls the other way under the GPU's fp32 summation order is a
+    # visible share of a small tensor's maximum.  At the benchmark's shapes every tensor is
+    # within 1e-3 (tests/test_bench_shapes_gpu.py).
+    assert max(errs.values()) < 2e-3, worst
     assert np.median(list(errs.values())) < 1e-3
 
 

@@ -3,18 +3,24 @@
 // and its backward chain (transformer.py:167-182) without ever writing the T x T score,
 // probability or gradient tensors to HBM.
 //
-// Forward, one CTA per (128-query tile, head, sequence), 192 threads:
+// Forward, one CTA per (128-query tile, head, sequence), 320 threads, two CTAs per SM:
 //   warp 0      TMA producer: Q once, then K tiles (pass 1), then K and V tiles (pass 2)
 //   warp 1      TMEM allocation + single-thread tcgen05.mma issue
-//   warps 2..5  softmax: TMEM lane = query row, so every thread owns one row and the
-//               row maximum / sum need no cross-thread reduction
+//   warps 2..9  softmax: TMEM lane = query row; two warps share a lane quarter, each takes 64
+//               of a tile's 128 keys, so a thread owns half of one row and the row maximum /
+//               sum need one exchange through shared memory per pass, no shuffles
 // Two passes over the key tiles instead of the usual running rescale of O:
-//   pass 1  S = Q K^T  -> row max m and row sum l (online)
-//   pass 2  S again, P = exp(S - m) / l rounded to fp16 into swizzled shared memory,
-//           O += P V accumulated in TMEM
+//   pass 1  S = Q K^T  -> row maximum m only (no exponentials)
+//   pass 2  S again, P~ = exp2(S c - m) rounded to fp16 into swizzled shared memory,
+//           O~ += P~ V accumulated in TMEM, row sum l of the UN-rounded P~ in fp32;
+//           O = O~ / l when the tile is stored
 // QK^T has K = 64, so doing it twice costs little and keeps O free of rescaling.
-// The fp16 rounding points are the reference's: P is rounded before P V
-// (tkernels.py:123), O is stored fp16 (tkernels.py:284).
+// Rounding points against the reference: it rounds the NORMALISED probability P = P~ / l to
+// fp16 before P V (tkernels.py:123); here the un-normalised P~ (in (0, 1], the row's largest
+// entry exactly 1) is rounded and 1 / l is applied to the fp32 accumulator, so O carries the
+// same relative rounding per product and one division less per score.  The backward kernels
+// rebuild the normalised P from the saved log-sum-exp and round that, as the reference does
+// (tkernels.py:123, 183); O, dQ, dK, dV are stored fp16 as there (tkernels.py:284, 228-230).
 // Every wait is bounded (see tcgen05.cuh); a wait that gives up flags the error word,
 // all roles leave their loops, TMEM is freed and the CTA returns.
 #include "common.cuh"

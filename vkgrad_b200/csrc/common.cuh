@@ -67,6 +67,9 @@ struct vkg_device {
   // CTAs; 0 = one per SM.  Lowered while a collective runs beside the compute stream so that
   // the collective's CTAs find free SMs instead of delaying a statically scheduled grid.
   int sm_limit = 0;
+  // vkg_gemm takes 256 x 256 CTA-pair tiles on its own (cta_pair == 0) from this many
+  // tiles per CTA pair on, in tenths (VKG_TUNE_PAIR_MIN_WAVES)
+  int pair_min_waves_x10 = 60;
   // vkg_finals_defer / vkg_finals_flush: final passes of two-stage column sums collected
   // instead of launched, then run as one launch
   bool defer_finals = false;

@@ -1451,7 +1451,8 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
     // handful of waves they time the same alone and a little slower inside a training step,
     // and with one wave and a bit they lose.
     if (build_problem(dev, a, 0, &q, true)) return 1;
-    use_pair = q.p.split_k > 1 || q.total_tiles >= 6ll * (vkg_persistent_ctas(dev) / 2);
+    use_pair = q.p.split_k > 1 ||
+               10ll * q.total_tiles >= (long long)dev->pair_min_waves_x10 * (vkg_persistent_ctas(dev) / 2);
   }
   if (use_pair) {
     if (build_problem(dev, a, 0, &q, true)) return 1;

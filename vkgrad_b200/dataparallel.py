@@ -300,9 +300,11 @@ class DataParallelStep:
     and final passes run (GPT.record(flush_after=...)), which completes that part of the flat
     bucket, and its all-reduce starts on a side stream while the compute stream goes on with
     the blocks below.  Only the last part -- the lowest blocks and the embedding tables,
-    whose gradient is final only after the embedding backward -- is summed on the compute
-    stream after the backward.  The sums are the same fp32 NCCL sums over the same bytes, so
-    replicas stay bit-identical and results equal the unsplit exchange bit for bit.
+    whose gradient is final only after the embedding backward -- is summed after the
+    backward, and AdamW over the parameters of the earlier parts runs meanwhile (the
+    optimiser is one launch per set of parts).  The sums are the same fp32 NCCL sums over the
+    same bytes, so replicas stay bit-identical and results equal the unsplit exchange bit for
+    bit.
     The side stream should use `side_comm`, a communicator held to a few CTAs
     (Comm(..., max_ctas=n)); the persistent kernels recorded after the first flush then launch
     sm_count - side_sms CTAs so that NCCL's CTAs find free SMs instead of delaying a statically
@@ -359,10 +361,21 @@ class DataParallelStep:
             self.parts = bucket_parts_for_flush(replica.params, replica.offsets, replica.total,
                                                 blocks, flush)
             self.side = side_comm if side_comm is not None else comm
-            g_opt = dev.graph(name + "_opt")
-            self.opt.record(g_opt)
-            g_opt.finish()
-            self.graphs = gs + [g_opt]
+            # the optimiser in two launches: the parameters whose sums arrive during the
+            # backward, then those of the last part
+            last_first = self.parts[-1][0] + self.parts[-1][1]
+            early = [p for p, o in zip(replica.params, replica.offsets) if o >= last_first]
+            late = [p for p, o in zip(replica.params, replica.offsets) if o < last_first]
+            self.opt_graphs = []
+            for tag, ps in (("a", early), ("b", late)):
+                if ps:
+                    go = dev.graph(f"{name}_opt{tag}")
+                    self.opt.record(go, params=ps)
+                    go.finish()
+                    self.opt_graphs.append(go)
+            if not early:
+                self.opt_graphs.insert(0, None)
+            self.graphs = gs + [g for g in self.opt_graphs if g is not None]
         elif comm is not None and comm.world > 1 and not in_graph:
             g = first_graph(dev.graph(name))
             self.model.record(ids_dev, targets_dev, g, **record_kwargs)
@@ -391,15 +404,18 @@ class DataParallelStep:
             n = len(self.parts)
             for j, (first, count) in enumerate(self.parts):
                 self.graphs[j].submit_async()
-                if j < n - 1:
-                    # this part of the bucket is complete: sum it beside the rest of the backward
-                    side.side_begin()
-                    side.allreduce_sum_side(bucket, count, j, offset_bytes=4 * first)
-                else:
-                    comm.allreduce_sum(bucket, count, offset_bytes=4 * first)
+                # this part of the bucket is complete: sum it beside what follows on the compute
+                # stream -- the rest of the backward, or, for the last part, the optimiser over
+                # the earlier parts (on the main communicator: nothing persistent runs then)
+                c = side if j < n - 1 else comm
+                c.side_begin()
+                c.allreduce_sum_side(bucket, count, j, offset_bytes=4 * first)
             for j in range(n - 1):
                 side.side_wait(j)
-            self.graphs[-1].submit_async()
+            if self.opt_graphs[0] is not None:
+                self.opt_graphs[0].submit_async()
+            comm.side_wait(n - 1)
+            self.opt_graphs[1].submit_async()
             return
         self.graphs[0].submit_async()
         if self.between is not None:
