@@ -674,7 +674,14 @@ def run_gpu_arm(args):
     dev = vk.Device(local)
     if args.pdl is not None:
         vk._check(dev.lib.vkg_set_pdl(dev.handle, int(args.pdl)), "set_pdl")
-    comm = Comm.from_env(dev) if world > 1 else None
+    # N > 1: the communicator of the compute stream and, for the parts of the exchange that run
+    # beside the backward, a second one held to a few CTAs
+    comm = side = None
+    groups = args.overlap_groups if world > 1 else 1
+    if world > 1 and groups > 1 and args.side_ctas > 0:
+        comm, side = Comm.pair_from_env(dev, args.side_ctas)
+    elif world > 1:
+        comm = Comm.from_env(dev)
     loss_scale = float(args.loss_scale)
 
     def build(d):
@@ -704,12 +711,6 @@ def run_gpu_arm(args):
     dev.copy(ids_host, ids_dev, R * 4)
     dev.copy(tgt_host, tgt_dev, R * 4)
 
-    # the exchange of all but the last part of the bucket runs beside the backward, on a second
-    # communicator held to a few CTAs
-    groups = args.overlap_groups if world > 1 else 1
-    side = None
-    if groups > 1 and args.side_ctas > 0:
-        side = Comm.from_env(dev, port_offset=211, max_ctas=args.side_ctas)
     dp_kw = dict(overlap_groups=groups, side_comm=side, side_sms=args.side_ctas if groups > 1 else 0)
     core = DataParallelStep(rep, ids_dev, tgt_dev, name="step_resident", **dp_kw)
     e2e = DataParallelStep(rep, ids_dev, tgt_dev, host_ids=ids_host, host_targets=tgt_host,

@@ -64,8 +64,10 @@ def _worker(rank, world, port, groups, steps, q):
         from vkgrad_b200.dataparallel import Comm, DataParallelStep, Replica
         from vkgrad_b200.transformer import GPT, TCtx
         dev = vk.Device(rank)
-        comm = Comm.from_env(dev)
-        side = Comm.from_env(dev, port_offset=37, max_ctas=4) if groups > 1 else None
+        if groups > 1:
+            comm, side = Comm.pair_from_env(dev, 4)
+        else:
+            comm, side = Comm.from_env(dev), None
         P = params()
 
         def build(d):

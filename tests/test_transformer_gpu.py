@@ -142,12 +142,9 @@ def test_gpt_against_faithful_oracle(dev, name, staged):
         with open(os.path.join(out, f"parity_fixture_{name}.json"), "w") as f:
             json.dump({"loss_rel_err": abs(loss - ref_loss) / abs(ref_loss), "worst_tensors": worst,
                        "median_err": float(np.median(list(errs.values())))}, f, indent=1)
-    # These fixtures are tiny (D = 32..64, a few hundred rows): one fp16 value that sits on a
-    # rounding boundary and falls the other way under the GPU's fp32 summation order is a
-    # visible share of a small tensor's maximum.  At the benchmark's shapes every tensor is
-    # within 1e-3 (tests/test_bench_shapes_gpu.py).
-    assert max(errs.values()) < 2e-3, worst
-    assert np.median(list(errs.values())) < 1e-3
+    # the bar for fp32-accumulated gradients: 1e-3 of each tensor's largest entry (measured:
+    # worst tensor 4.9e-4 over the three fixtures)
+    assert max(errs.values()) < 1e-3, worst
 
 
 def test_negative_control_seg_matters(dev):
@@ -247,4 +244,10 @@ def test_long_context_causal_tiles(dev, T, H, D, fused):
     exp = expected(mg.flatten_grads(G, L), True)
     errs = {k: relerr(got[k], exp[k].reshape(got[k].shape)) for k in exp}
     assert all(np.isfinite(v) for v in errs.values())
-    assert max(errs.values()) < 2e-3, sorted(errs.items(), key=lambda kv: -kv[1])[:5]
+    worst = sorted(errs.items(), key=lambda kv: -kv[1])[:5]
+    out = os.path.join(os.path.dirname(GOLD.rstrip("/")), "..", "gpurun_out")
+    if os.path.isdir(out):
+        import json
+        with open(os.path.join(out, f"parity_long_T{T}_H{H}_D{D}_{fused}.json"), "w") as f:
+            json.dump({"loss_rel_err": abs(loss - ref_loss) / abs(ref_loss), "worst_tensors": worst}, f)
+    assert max(errs.values()) < 2e-3, worst

@@ -1157,22 +1157,52 @@ __global__ void __launch_bounds__(32 * FIN_SLICES)
 k_finals_multi(const __grid_constant__ FinalTable tab) {
   pdl_trigger();
   pdl_wait();
-  __shared__ float red[FIN_SLICES][32];
+  __shared__ float4 red4[FIN_SLICES][32];
   int e = 0;
   while (e + 1 < tab.n && (int)blockIdx.x >= tab.e[e + 1].first_block) ++e;
   const float* __restrict__ partial = tab.e[e].partial;
   const int W = tab.e[e].W, D = tab.e[e].D, nchunk = tab.e[e].nchunk;
   const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  if (tab.e[e].reserved) {
+    // four columns per lane (W, D multiples of 4, 16-byte aligned rows): a block covers 128
+    // columns with one 16-byte load per lane and row.  Per column the order of the additions is
+    // the same as below -- slice s takes rows s, s + 32, ..., the slices are added in order.
+    const int c = (((int)blockIdx.x - tab.e[e].first_block) * 32 + lane) * 4;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < W)
+      for (int k = slice; k < nchunk; k += FIN_SLICES) {
+        const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)k * W + c);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
+    red4[slice][lane] = s;
+    __syncthreads();
+    if (slice == 0 && c < W) {
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < FIN_SLICES; ++k) {
+        const float4 u = red4[k][lane];
+        t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+      }
+      float4* d = reinterpret_cast<float4*>(tab.e[e].dst[c / D] + (c % D));
+      if (tab.e[e].accumulate) {
+        const float4 o = *d;
+        t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w;
+      }
+      *d = t;
+    }
+    return;
+  }
+  float* red = reinterpret_cast<float*>(red4);       // [FIN_SLICES][32] floats
   const int c = ((int)blockIdx.x - tab.e[e].first_block) * 32 + lane;
   float s = 0.f;
   if (c < W)
     for (int k = slice; k < nchunk; k += FIN_SLICES) s += partial[(size_t)k * W + c];
-  red[slice][lane] = s;
+  red[slice * 32 + lane] = s;
   __syncthreads();
   if (slice == 0 && c < W) {
     float t = 0.f;
 #pragma unroll
-    for (int k = 0; k < FIN_SLICES; ++k) t += red[k][lane];
+    for (int k = 0; k < FIN_SLICES; ++k) t += red[k * 32 + lane];
     float* d = tab.e[e].dst[c / D] + (c % D);
     *d = tab.e[e].accumulate ? *d + t : t;
   }
@@ -1202,7 +1232,12 @@ extern "C" int vkg_finals_flush(vkg_device* dev) {
                       (en.W <= en.D || en.dst[1]) && (en.W <= 2 * en.D || en.dst[2]),
                   "finals_flush: malformed entry");
       en.first_block = blocks;
-      blocks += (en.W + 31) / 32;
+      // 16-byte columns when every row of the partials and every destination allows it
+      bool vec = en.W % 4 == 0 && en.D % 4 == 0 && ((uintptr_t)en.partial & 15) == 0;
+      for (int d = 0; d < 3; ++d)
+        if (en.dst[d] && ((uintptr_t)en.dst[d] & 15)) vec = false;
+      en.reserved = vec ? 1 : 0;
+      blocks += vec ? (en.W + 127) / 128 : (en.W + 31) / 32;
       tab.e[tab.n++] = en;
     }
     VKG_CUDA(vkg_launch(dev, VKG_K_SMALL, k_finals_multi, dim3((unsigned)blocks), dim3(32 * FIN_SLICES), 0, 1, tab));

@@ -134,6 +134,21 @@ class Comm:
         uid = exchange_unique_id(rank, world, lambda: cls.make_unique_id(dev.lib), addr, port)
         return cls(dev, rank, world, uid, max_ctas=max_ctas)
 
+    @classmethod
+    def pair_from_env(cls, dev, side_max_ctas, port_offset=101):
+        """(main, side): the communicator for the compute stream and one held to
+        side_max_ctas CTAs for collectives beside it, from ONE rendezvous (both ids travel in
+        the same message)."""
+        rank = int(os.environ.get("RANK", "0"))
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+        port = (int(os.environ.get("MASTER_PORT", "29500")) + port_offset) % 65536
+        ids = exchange_unique_id(rank, world,
+                                 lambda: cls.make_unique_id(dev.lib) + cls.make_unique_id(dev.lib),
+                                 addr, port)
+        return (cls(dev, rank, world, ids[:128]),
+                cls(dev, rank, world, ids[128:256], max_ctas=side_max_ctas))
+
     def allreduce_sum(self, buf, count, dtype=F32, offset_bytes=0):
         _check(self.dev.lib.vkg_allreduce_sum(self.handle, buf.dptr + offset_bytes, count, dtype),
                "allreduce")
