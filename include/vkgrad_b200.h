@@ -81,9 +81,13 @@ int vkg_set_pdl(vkg_device* dev, int on);
  *                          backward) launches; 0 = one per SM.  May also change during a
  *                          recording: launches recorded after the call use the new value
  *   VKG_TUNE_PAIR_MIN_WAVES  tenths of a tile per CTA pair from which vkg_gemm with
- *                          cta_pair == 0 takes 256 x 256 CTA-pair tiles */
+ *                          cta_pair == 0 takes 256 x 256 CTA-pair tiles
+ *   VKG_TUNE_ATTN_ONE_PASS 1 (default): the fused attention forward computes every score tile
+ *                          once and keeps a lazily rescaled running row maximum; 0: two
+ *                          passes over the keys (row maximum first) */
 enum { VKG_TUNE_PDL = 0, VKG_TUNE_PDL_FAMILIES = 1, VKG_TUNE_TMA_STORE = 2,
-       VKG_TUNE_WAIT_TIMEOUT_MS = 3, VKG_TUNE_SM_LIMIT = 4, VKG_TUNE_PAIR_MIN_WAVES = 5 };
+       VKG_TUNE_WAIT_TIMEOUT_MS = 3, VKG_TUNE_SM_LIMIT = 4, VKG_TUNE_PAIR_MIN_WAVES = 5,
+       VKG_TUNE_ATTN_ONE_PASS = 6 };
 int vkg_set_tuning(vkg_device* dev, int key, int64_t value);
 /* Waits for the stream; reports a kernel error flag (bounded waits that gave
  * up) as a failure, like the reference's 10 s fence timeout (vk.py:884-888, 1335-1339).
@@ -427,9 +431,11 @@ int vkg_comm_create_limited(vkg_device* dev, int rank, int nranks, const uint8_t
 int vkg_comm_destroy(vkg_comm* comm);
 /* In-place sum over ranks of `count` elements of dtype, on the device stream. */
 int vkg_allreduce_sum(vkg_comm* comm, void* buf, int64_t count, int dtype);
-/* The same all-reduce on a second stream, so that the optimiser can update one part of the
- * gradient bucket while the next part is still being summed (the reference's step_from_arena,
- * dataparallel.py:131-144, runs pull and AdamW strictly after the push).  side_begin orders the
+/* The same all-reduce on a second stream, so that a part of the gradient bucket whose
+ * gradients are complete is summed while the compute stream goes on with the rest of the
+ * backward (the reference's workers push each tensor as soon as it exists,
+ * dataparallel.py:119-126), and the optimiser over parts already summed runs while the last
+ * part is still in flight.  side_begin orders the
  * side stream after everything enqueued on the device's stream so far; allreduce_sum_side
  * enqueues there and marks its end with event `slot` (0..15); side_wait makes the device's
  * stream wait for that event.  Not for use inside a stream capture. */

@@ -45,13 +45,35 @@ def reference_attention(qkv, B, T, H, scale, seg=None):
     return q, k, v, p, o, lse2, mask
 
 
+@pytest.fixture
+def one_pass(dev):
+    """Switches the forward to the one-pass kernel for the test and back afterwards."""
+    from vkgrad_b200._lib import TUNE_ATTN_ONE_PASS
+    from vkgrad_b200.vk import _check
+
+    def set_(on):
+        _check(dev.lib.vkg_set_tuning(dev.handle, TUNE_ATTN_ONE_PASS, int(on)), "tune")
+    yield set_
+    set_(0)
+
+
 @pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 320, 2), (1, 1024, 3), (3, 72, 1)])
 @pytest.mark.parametrize("packed", [False, True])
-def test_forward(dev, B, T, H, packed):
+@pytest.mark.parametrize("kernel", ["two_pass", "one_pass", "one_pass_rescaled"])
+def test_forward(dev, one_pass, B, T, H, packed, kernel):
     from vkgrad_b200.vk import _check
+    one_pass(kernel != "two_pass")
     hd, D = 64, H * 64
     rng = np.random.default_rng(T + H)
     qkv = rng.standard_normal((B * T, 3 * D)).astype(np.float16)
+    if kernel == "one_pass_rescaled":
+        # scores that grow along the keys by far more than 2^8 from tile to tile: the running
+        # reference maximum must move, and O~ and the row sums must be rescaled, several times
+        q = np.abs(qkv[:, :D].astype(np.float32)) * 0.5 + 0.5
+        ramp = (np.arange(B * T) % T)[:, None] / 8.0
+        k = np.abs(qkv[:, D:2 * D].astype(np.float32)) * 0.05 * (1.0 + ramp)
+        qkv[:, :D] = q.astype(np.float16)
+        qkv[:, D:2 * D] = k.astype(np.float16)
     seg = None
     if packed:
         seg = np.zeros((B, T), np.uint32)

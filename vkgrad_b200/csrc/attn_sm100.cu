@@ -4,17 +4,18 @@
 // probability or gradient tensors to HBM.
 //
 // Forward, one CTA per (128-query tile, head, sequence), 320 threads, two CTAs per SM:
-//   warp 0      TMA producer: Q once, then K tiles (pass 1), then K and V tiles (pass 2)
+//   warp 0      TMA producer: Q once, then the K and V tiles
 //   warp 1      TMEM allocation + single-thread tcgen05.mma issue
 //   warps 2..9  softmax: TMEM lane = query row; two warps share a lane quarter, each takes 64
-//               of a tile's 128 keys, so a thread owns half of one row and the row maximum /
-//               sum need one exchange through shared memory per pass, no shuffles
-// Two passes over the key tiles instead of the usual running rescale of O:
+//               of a tile's 128 keys, so a thread owns half of one row
+// Two kernels.  attn_fwd1_kernel (the default) makes one pass: S = Q K^T once per key tile,
+// P~ = exp2(S c - m) against a running reference maximum m that is moved -- and O~ and the row
+// sum rescaled -- only when a tile exceeds it by more than 2^8.  attn_fwd_kernel makes two:
 //   pass 1  S = Q K^T  -> row maximum m only (no exponentials)
-//   pass 2  S again, P~ = exp2(S c - m) rounded to fp16 into swizzled shared memory,
-//           O~ += P~ V accumulated in TMEM, row sum l of the UN-rounded P~ in fp32;
-//           O = O~ / l when the tile is stored
-// QK^T has K = 64, so doing it twice costs little and keeps O free of rescaling.
+//   pass 2  S again, P~ = exp2(S c - m), O~ += P~ V, no rescaling at all
+// (QK^T has K = 64, so doing it twice costs little: 45 vs 41 us per layer at 8 x 1024 x 12.)
+// In both, P~ is rounded to fp16 into swizzled shared memory, O~ accumulates in TMEM, the row
+// sum l of the UN-rounded P~ is kept in fp32, and O = O~ / l when the tile is stored.
 // Rounding points against the reference: it rounds the NORMALISED probability P = P~ / l to
 // fp16 before P V (tkernels.py:123); here the un-normalised P~ (in (0, 1], the row's largest
 // entry exactly 1) is rounded and 1 / l is applied to the fp32 accumulator, so O carries the
@@ -58,8 +59,10 @@ constexpr int FW_K = FW_Q + FA_TILE_BYTES;            // two K stages
 constexpr int FW_V = FW_K + 2 * FA_TILE_BYTES;        // one V stage
 constexpr int FW_P = FW_V + FA_TILE_BYTES;            // P: two 64-key blocks of 128 rows x 128 B
 constexpr int FW_BAR = FW_P + 2 * FA_TILE_BYTES;
-constexpr int FW_XCHG = FW_BAR + 256;                 // [2][128] floats: row statistics exchange
-constexpr int FW_SMEM = FW_XCHG + 1024 + 1024;
+constexpr int FW_XCHG = FW_BAR + 256;                 // row statistics exchange: [2][128] floats; the
+                                                      // one-pass kernel: [2][2][128] tagged 8-byte
+                                                      // slots, then [2][128] floats
+constexpr int FW_SMEM = FW_XCHG + 4096 + 1024 + 1024;
 
 // P and dS tiles use the 128B-swizzled layout of TMA and the UMMA descriptors: 16-byte
 // piece c8 (8 keys) of row r of a 64-key block sits at r * 128 + ((c8 ^ (r & 7)) << 4).
@@ -327,6 +330,248 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         warp_store_rows<4>(hv, gbase + FW_P + (warp - 2) * 2048, lane, reinterpret_cast<uint8_t*>(dst),
                            (size_t)p.D * 2, p.T - q_w);
       }
+    }
+  }
+
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// ---- forward, one pass ------------------------------------------------------------------
+//
+// The same CTA shape and roles, but every S = Q K^T is computed once: the softmax warps keep a
+// running reference maximum m per row, P~ = exp2(S c - m) goes to the tensor core as before,
+// and O~ and the row sum l are rescaled only when a tile's row maximum exceeds the reference by
+// more than 2^8 (then the warps multiply their columns of O~ in TMEM by exp2(m_old - m_new)).
+// With the threshold P~ stays below 256, well inside fp16, and its relative rounding is that of
+// the two-pass kernel; for ordinary score ranges no rescale ever runs.  The two warps that share
+// a row (64 keys each) exchange their tile maxima through shared memory with a tagged slot and
+// a bounded poll -- no named barrier inside the loop, so an aborting warp cannot strand its
+// partner.  The rescale sits between "P V of the previous tile has retired" (the wait that
+// guards the P buffer anyway) and this warp's arrival on p_full, so it needs no barrier of its
+// own: O~ is quiet exactly there.
+constexpr float FW1_LAZY = 8.0f;      // log2 of the largest P~ the running reference allows
+
+__global__ void __launch_bounds__(FA_THREADS, 2)
+attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar = base + FW_BAR;
+  // barriers: 0 q_full, 1-2 k_full, 3-4 k_empty, 5 v_full, 6 v_empty, 7 s_full, 8 s_free,
+  //           9 p_full, 10 p_free, 11 o_full
+  auto B_ = [bar](int i) { return bar + 8u * i; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + FW_BAR + 128);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + FW_BAR + 136);
+  // [parity][half][row] (tag, value) pairs for the per-tile maxima; the final row sums reuse it
+  volatile unsigned long long* xslot = reinterpret_cast<volatile unsigned long long*>(gbase + FW_XCHG);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int HB = p.H * p.B;
+  const int qt = p.nqt - 1 - (int)(blockIdx.x / HB);   // heaviest query tiles first
+  const int hb = blockIdx.x % HB;
+  const int h = hb % p.H, b = hb / p.H;
+  const int q0 = qt * FA_T;
+  const int nj = qt + 1;
+  const int row0 = b * p.T;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tm);
+    for (int i = 0; i < 12; ++i) mbar_init(B_(i), (i == 8 || i == 9) ? FA_SOFTMAX_WARPS : 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < 2 * 2 * FA_T; i += blockDim.x) xslot[i] = 0ull;   // tag 0 = empty
+  if (warp == 1) tmem_alloc(tmem_slot, 256);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  pdl_wait();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(B_(0), FA_TILE_BYTES);
+      tma_load_2d(base + FW_Q, &tm, B_(0), h * FA_HD, row0 + q0);
+      for (int j = 0; j < nj; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait<true>(B_(3 + s), ((j >> 1) & 1) ^ 1u, abort_flag, p.err, 0x6100u + s)) break;
+        mbar_expect_tx(B_(1 + s), FA_TILE_BYTES);
+        tma_load_2d(base + FW_K + s * FA_TILE_BYTES, &tm, B_(1 + s), p.D + h * FA_HD, row0 + j * FA_T);
+        if (!mbar_wait<true>(B_(6), (j & 1) ^ 1u, abort_flag, p.err, 0x6200u)) break;
+        mbar_expect_tx(B_(5), FA_TILE_BYTES);
+        tma_load_2d(base + FW_V, &tm, B_(5), 2 * p.D + h * FA_HD, row0 + j * FA_T);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
+      const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);
+      bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x7000u);
+      const uint32_t sq = base + FW_Q;
+      auto issue_s = [&](int n) -> bool {
+        const int s = n & 1;
+        if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x7100u + s) &&
+              mbar_wait<true>(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x7200u)))
+          return false;
+        tcgen05_fence_after();
+        const uint32_t sk = base + FW_K + s * FA_TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
+                   idesc_s, k ? 1u : 0u);
+        umma_commit(B_(3 + s));   // K stage free once these retire
+        umma_commit(B_(7));       // S ready
+        return true;
+      };
+      int n = 0;
+      if (ok) ok = issue_s(n++);
+      for (int j = 0; j < nj && ok; ++j) {
+        if (j + 1 < nj) {          // the next scores first: the tensor core works while P(j) forms
+          ok = issue_s(n++);
+          if (!ok) break;
+        }
+        ok = mbar_wait<true>(B_(9), j & 1, abort_flag, p.err, 0x7300u) &&
+             mbar_wait<true>(B_(5), j & 1, abort_flag, p.err, 0x7400u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t sp = base + FW_P, sv = base + FW_V;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tO, make_smem_desc(sp + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
+                   make_smem_desc(sv + kk * 2048, 8192, 1024), idesc_o, (j | kk) ? 1u : 0u);
+        umma_commit(B_(6));     // V free
+        umma_commit(B_(10));    // P free, and O~ quiet until the next p_full
+      }
+      if (ok) umma_commit(B_(11));
+    }
+  } else {
+    const int half = (warp - 2) >> 2;
+    const int qr = (warp & 3) * 32 + lane;      // row within the tile = TMEM lane
+    const int qi = q0 + qr;
+    const bool q_ok = qi < p.T;
+    const int st = (p.seg && q_ok) ? (int)p.seg[row0 + qi] : 0;
+    const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
+    float m_ref = -1e30f, l = 0.f;              // reference maximum (scaled units), row sum
+    bool ok = true;
+    for (int j = 0; j < nj && ok; ++j) {
+      ok = mbar_wait_warp<true>(B_(7), j & 1, abort_flag, p.err, 0x8100u);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const bool need_mask = (j == qt) || (p.seg != nullptr);
+      uint32_t r[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, r + c * 16);
+      tmem_wait_ld();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(8));        // S may be overwritten
+      // this half's maximum of the row, then the partner's through its tagged slot
+      float mt = need_mask ? fwd_max_tile<true>(r, j * FA_T + half * 64, qi, st, -1e30f)
+                           : fwd_max_tile<false>(r, 0, 0, 0, -1e30f);
+      const unsigned long long tag = (unsigned long long)(unsigned)(j + 1) << 32;
+      xslot[((j & 1) * 2 + half) * FA_T + qr] = tag | (unsigned long long)__float_as_uint(mt);
+      float mo = -1e30f;
+      {
+        volatile unsigned long long* theirs = xslot + ((j & 1) * 2 + (1 - half)) * FA_T + qr;
+        long long t0 = 0;
+        for (unsigned spins = 0;; ++spins) {
+          const unsigned long long v = *theirs;
+          if ((v >> 32) == (unsigned long long)(unsigned)(j + 1)) {
+            mo = __uint_as_float((uint32_t)v);
+            break;
+          }
+          if ((spins & 255u) == 255u) {
+            if (*abort_flag) { ok = false; break; }
+            if (t0 == 0) t0 = clock64();
+            else if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
+              *abort_flag = 1u;
+              if (atomicCAS(p.err, 0u, VKG_ERR_WAIT_TIMEOUT) == 0u) p.err[1] = 0x8150u;
+              __threadfence_system();
+              ok = false;
+              break;
+            }
+          }
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const float m_row = fmaxf(mt, mo) * p.cscale;
+      // the previous P V has retired: the P buffer is free and O~ is quiet
+      ok = mbar_wait_warp<true>(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x8200u);
+      if (!ok) break;
+      if (j == 0) {
+        m_ref = m_row;
+      } else {
+        const bool grow = m_row > m_ref + FW1_LAZY;
+        if (__any_sync(0xffffffffu, grow)) {
+          // rescale this half's 32 columns of O~ (aligned TMEM accesses: the whole warp goes)
+          const float alpha = grow ? vkg_ex2(m_ref - m_row) : 1.0f;
+          tcgen05_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {          // 16 columns at a time: r[] is still live
+            uint32_t o[16];
+            tmem_ld16(tO + t_lane + half * 32 + c * 16, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st16(tO + t_lane + half * 32 + c * 16, o);
+          }
+          tmem_wait_st();
+          l *= alpha;
+          if (grow) m_ref = m_row;
+        }
+      }
+      const float nm = -m_ref;
+      uint8_t* prow = gbase + FW_P + half * FA_TILE_BYTES + qr * 128;
+      if (need_mask) l += fwd_p_tile<true>(r, j * FA_T + half * 64, qi, st, p.cscale, nm, prow, qr & 7);
+      else l += fwd_p_tile<false>(r, 0, 0, 0, p.cscale, nm, prow, qr & 7);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(9));        // this warp's part of P is in shared memory
+    }
+    // row sums of the two halves (both hold the same reference maximum)
+    float* xchg = reinterpret_cast<float*>(gbase + FW_XCHG + 2 * 2 * FA_T * 8);
+    xchg[half * 128 + qr] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l = xchg[qr] + xchg[128 + qr];
+    const float inv_l = 1.0f / l;               // l > 0: key == query is always valid
+    if (half == 0 && q_ok) p.lse2[(size_t)(b * p.H + h) * p.T + qi] = m_ref + log2f(l);
+    if (ok) ok = mbar_wait_warp<true>(B_(11), 0, abort_flag, p.err, 0x8300u);
+    if (ok) {
+      tcgen05_fence_after();
+      uint32_t r[32];
+      tmem_ld16(tO + t_lane + half * 32, r);
+      tmem_ld16(tO + t_lane + half * 32 + 16, r + 16);
+      tmem_wait_ld();
+      uint4 hv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        __half2 h2[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          h2[e] = __floats2half2_rn(__uint_as_float(r[u * 8 + 2 * e]) * inv_l,
+                                    __uint_as_float(r[u * 8 + 2 * e + 1]) * inv_l);
+        hv[u] = *reinterpret_cast<uint4*>(h2);
+      }
+      const int q_w = q0 + (warp & 3) * 32;
+      __half* dst = p.out + (size_t)(row0 + q_w) * p.D + h * FA_HD + half * 32;
+      warp_store_rows<4>(hv, gbase + FW_P + (warp - 2) * 2048, lane, reinterpret_cast<uint8_t*>(dst),
+                         (size_t)p.D * 2, p.T - q_w);
     }
   }
 
@@ -1135,11 +1380,14 @@ extern "C" int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* 
   if (!dev->attn_fwd_attr_set) {
     VKG_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   FW_SMEM));
+    VKG_CUDA(cudaFuncSetAttribute(attn_fwd1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  FW_SMEM));
     dev->attn_fwd_attr_set = true;
   }
   const long long ctas = (long long)p.nqt * H * B;
   VKG_REQUIRE(ctas < (1ll << 31), "attn_fwd: too many tiles");
-  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_FWD, attn_fwd_kernel, dim3((unsigned)ctas), dim3(FA_THREADS), FW_SMEM, 1, tm, p));
+  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_FWD, dev->attn_one_pass ? attn_fwd1_kernel : attn_fwd_kernel,
+                      dim3((unsigned)ctas), dim3(FA_THREADS), FW_SMEM, 1, tm, p));
   return vkg_check_launch("attn_fwd_kernel");
 }
 

@@ -252,8 +252,8 @@ extern "C" int vkg_allreduce_sum(vkg_comm* comm, void* buf, int64_t count, int d
 // vkg_comm_side_begin: everything enqueued on the device's stream so far happens before what
 // follows on the side stream.  vkg_allreduce_sum_side: the all-reduce on the side stream;
 // `slot` names the event that marks its end.  vkg_comm_side_wait: the device's stream waits
-// for that event -- so the optimiser can update one part of the bucket while the next part
-// is still being reduced.
+// for that event -- so a finished part of the bucket is summed while the backward of the
+// blocks below still runs, and the optimiser starts on the parts that have arrived.
 static int side_init(vkg_comm* comm) {
   if (comm->side) return 0;
   VKG_CUDA(cudaStreamCreateWithFlags(&comm->side, cudaStreamNonBlocking));

@@ -67,6 +67,9 @@ struct vkg_device {
   // CTAs; 0 = one per SM.  Lowered while a collective runs beside the compute stream so that
   // the collective's CTAs find free SMs instead of delaying a statically scheduled grid.
   int sm_limit = 0;
+  // fused attention forward: one pass with a lazily rescaled running maximum (default), or
+  // the two-pass kernel (VKG_TUNE_ATTN_ONE_PASS)
+  bool attn_one_pass = true;
   // vkg_gemm takes 256 x 256 CTA-pair tiles on its own (cta_pair == 0) from this many
   // tiles per CTA pair on, in tenths (VKG_TUNE_PAIR_MIN_WAVES)
   int pair_min_waves_x10 = 60;

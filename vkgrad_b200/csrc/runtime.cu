@@ -77,6 +77,8 @@ extern "C" int vkg_device_create(int ordinal, vkg_device** out) {
   d->pdl = pdl && pdl[0] == '1';    // off unless asked for: it measured slower inside CUDA graphs
   const char* ts = getenv("VKG_TMA_STORE");
   d->tma_store = !(ts && ts[0] == '0');
+  const char* a1 = getenv("VKG_ATTN_ONE_PASS");
+  if (a1 && a1[0]) d->attn_one_pass = a1[0] == '1';
   const char* lim = getenv("VKG_SM_LIMIT");      // persistent kernels' grid cap, for experiments
   if (lim && lim[0]) d->sm_limit = atoi(lim);
   const char* mask = getenv("VKG_PDL_MASK");     // kernel families, for experiments
@@ -110,6 +112,7 @@ extern "C" int vkg_set_tuning(vkg_device* dev, int key, int64_t value) {
       VKG_REQUIRE(value >= 0, "set_tuning: the threshold cannot be negative");
       dev->pair_min_waves_x10 = (int)value;
       break;
+    case VKG_TUNE_ATTN_ONE_PASS: dev->attn_one_pass = value != 0; break;
     case VKG_TUNE_WAIT_TIMEOUT_MS:
       VKG_REQUIRE(value > 0, "set_tuning: the wait limit must be positive");
       dev->wait_timeout_s = (double)value * 1e-3;
