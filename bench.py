@@ -649,6 +649,19 @@ def run_single_gemm(args):
     dev.destroy()
 
 
+def run_single_attention(args):
+    """--attn B,T,H: the fused attention forward and backward of one layer alone, `steps`
+    launches each on N(0,1) q/k/v and dO; for ncu captures with a small footprint."""
+    from vkgrad_b200 import vk
+    B, T, H = [int(x) for x in args.attn.split(",")[:3]]
+    dev = vk.Device(0)
+    res = None
+    for _ in range(max(args.steps, 1)):
+        res = time_attention(dev, B, T, H, 64)
+    print(json.dumps({"attn": args.attn, **res}), flush=True)
+    dev.destroy()
+
+
 def run_gpu_arm(args):
     from vkgrad_b200 import vk
     from vkgrad_b200.autograd import AdamW
@@ -918,6 +931,8 @@ def main():
                     help="programmatic dependent launch off / on (default: the library's, off)")
     ap.add_argument("--profile", action="store_true",
                     help="run only the device-resident steps (for an ncu launch list)")
+    ap.add_argument("--attn", default=None,
+                    help="B,T,H: time the fused attention kernels of one layer instead of the step")
     ap.add_argument("--gemm", default=None,
                     help="M,N,K,ta,tb,batch[,c16]: time one GEMM shape instead of the step")
     ap.add_argument("--watchdog", type=int, default=900,
@@ -925,7 +940,9 @@ def main():
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--split-k", type=int, default=0)
     args = ap.parse_args()
-    if args.gemm:
+    if args.attn:
+        run_single_attention(args)
+    elif args.gemm:
         run_single_gemm(args)
     elif args.trio_table:
         run_trio_table(args)
