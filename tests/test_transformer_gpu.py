@@ -250,4 +250,8 @@ def test_long_context_causal_tiles(dev, T, H, D, fused):
         import json
         with open(os.path.join(out, f"parity_long_T{T}_H{H}_D{D}_{fused}.json"), "w") as f:
             json.dump({"loss_rel_err": abs(loss - ref_loss) / abs(ref_loss), "worst_tensors": worst}, f)
+    # 2e-3 here, not the 1e-3 of the other GPT cases: a 1-layer model with N(0, 0.08) weights and
+    # 0.1 biases; measured worst tensor b0.ln1.g 1.2e-3 (T=384, two heads of 64), the other
+    # three cases <= 5.6e-4 -- one fp16 value on a rounding boundary that falls the other way
+    # under the GPU's summation order is a visible share of a 128-entry tensor's maximum
     assert max(errs.values()) < 2e-3, worst
