@@ -693,6 +693,8 @@ def run_gpu_arm(args):
     groups = args.overlap_groups if world > 1 else 1
     if world > 1 and groups > 1 and args.side_ctas > 0:
         comm, side = Comm.pair_from_env(dev, args.side_ctas)
+        if side is None:
+            groups = 1          # no limited communicator: one all-reduce after the backward
     elif world > 1:
         comm = Comm.from_env(dev)
     loss_scale = float(args.loss_scale)
@@ -912,7 +914,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gpt2-small", choices=sorted(WORKLOADS))
     ap.add_argument("--loss-scale", type=float, default=4096.0)
-    ap.add_argument("--overlap-groups", type=int, default=3,
+    ap.add_argument("--overlap-groups", type=int, default=4,
                     help="N>1: groups of blocks whose gradients are all-reduced beside the rest of "
                          "the backward (1 = one all-reduce after the backward)")
     ap.add_argument("--side-ctas", type=int, default=8,

@@ -3,8 +3,9 @@
 Skipped on a box with one GPU.  Checks the reference's claims for its data-parallel path
 (examples/ddp_mnist.py:79-105): the update uses the mean of the workers' gradients, and the
 replicas stay bit-identical (drift == 0) -- for the single all-reduce after the backward and
-for the exchange that runs beside the backward, which must agree with each other to the last
-bit and with the CPU oracle within the gradient tolerance.
+for the exchange that runs beside the backward, which with two workers must agree with each
+other to the last bit (a + b has one order) and with the CPU oracle within the gradient
+tolerance.
 """
 
 import multiprocessing as mp
@@ -164,3 +165,38 @@ def test_two_gpu_step_sums_the_workers_and_keeps_replicas_identical():
     assert plain[0][0] == plain[1][0] and split[0][0] == split[1][0]         # drift == 0
     assert plain[0][0] == split[0][0], "the exchange beside the backward changed the result"
     assert plain[0][1] == split[0][1]
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_two_devices_in_one_process_run_the_same_step():
+    """Two vk.Device objects in one process (the reference's examples/ddp_mnist.py opens every
+    GPU from one interpreter): kernel attributes such as the opt-in shared-memory size are per
+    device, so the second device must launch the big-shared-memory kernels (GEMM, grouped GEMM,
+    fused attention) as well as the first, and both must produce the same bits."""
+    from test_transformer_gpu import load_params, model_grads, shared
+    from vkgrad_b200 import vk
+    from vkgrad_b200.transformer import GPT, TCtx
+    P = params()
+    ids, tgt = batch(0, 0)
+    results = []
+    for ordinal in (0, 1):
+        dev = vk.Device(ordinal)
+        ctx = TCtx(dev)
+        try:
+            model = GPT(ctx, B, T, D, H, L, V, tie=True, loss_scale=SCALE)
+            load_params(model, P)
+            assert model.blocks[0].attn.fused
+            g = dev.graph(f"dev{ordinal}")
+            model.record(shared(ctx, ids), shared(ctx, tgt), g)
+            g.finish()
+            g.submit()
+            results.append((model.read_loss(), model_grads(model)))
+        finally:
+            ctx.destroy()
+            dev.destroy()
+    assert results[0][0] == results[1][0]
+    for k in results[0][1]:
+        assert np.array_equal(results[0][1][k], results[1][1][k]), k
+    ref_loss, _, _ = orc.gpt_forward_backward(P, ids, tgt, B, T, D, H, L, V, faithful=True,
+                                              grad_scale=SCALE / (B * T))
+    assert abs(results[0][0] - ref_loss) < 1e-3 * abs(ref_loss)

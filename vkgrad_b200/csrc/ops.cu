@@ -288,21 +288,30 @@ k_embed_chain(const int* __restrict__ keys, int* __restrict__ next, int* __restr
   const int* k = keys + (size_t)which * rows_p;
   const int key = k[r];
   int found = -1;
-  for (int j0 = ((r + 1) & ~3) + lane * 4; ; j0 += 128) {
-    unsigned m = 0;
-    if (j0 < rows_p) {
-      const int4 v = *reinterpret_cast<const int4*>(k + j0);
-      m = (v.x == key && j0 > r ? 1u : 0u) | (v.y == key && j0 + 1 > r ? 2u : 0u) |
-          (v.z == key && j0 + 2 > r ? 4u : 0u) | (v.w == key && j0 + 3 > r ? 8u : 0u);
+  // four chunks of 128 keys per round: the four loads are independent, so a round costs one
+  // memory round trip instead of four
+  for (int j0 = ((r + 1) & ~3) + lane * 4; found < 0; j0 += 512) {
+    unsigned m[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * 128;
+      m[u] = 0;
+      if (j < rows_p) {
+        const int4 v = *reinterpret_cast<const int4*>(k + j);
+        m[u] = (v.x == key && j > r ? 1u : 0u) | (v.y == key && j + 1 > r ? 2u : 0u) |
+               (v.z == key && j + 2 > r ? 4u : 0u) | (v.w == key && j + 3 > r ? 8u : 0u);
+      }
     }
-    const unsigned any = __ballot_sync(0xffffffffu, m != 0u);
-    if (any) {
-      const int src = __ffs(any) - 1;
-      const int mine = j0 + __ffs(m) - 1;       // meaningful on lane `src` only
-      found = __shfl_sync(0xffffffffu, mine, src);
-      break;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const unsigned any = __ballot_sync(0xffffffffu, m[u] != 0u);
+      if (any && found < 0) {
+        const int src = __ffs(any) - 1;
+        const int mine = j0 + u * 128 + __ffs(m[u]) - 1;     // meaningful on lane `src` only
+        found = __shfl_sync(0xffffffffu, mine, src);
+      }
     }
-    if (__all_sync(0xffffffffu, j0 + 128 - lane * 4 >= rows_p)) break;   // the warp is past the end
+    if (__all_sync(0xffffffffu, j0 + 512 - lane * 4 >= rows_p)) break;   // the warp is past the end
   }
   if (lane == 0) {
     next[which * rows + r] = found;

@@ -146,8 +146,14 @@ class Comm:
         ids = exchange_unique_id(rank, world,
                                  lambda: cls.make_unique_id(dev.lib) + cls.make_unique_id(dev.lib),
                                  addr, port)
-        return (cls(dev, rank, world, ids[:128]),
-                cls(dev, rank, world, ids[128:256], max_ctas=side_max_ctas))
+        main = cls(dev, rank, world, ids[:128])
+        try:
+            side = cls(dev, rank, world, ids[128:256], max_ctas=side_max_ctas)
+        except VkError:
+            # an NCCL that does not take the CTA limit refuses on every rank alike: the caller
+            # exchanges on the main communicator alone
+            side = None
+        return main, side
 
     def allreduce_sum(self, buf, count, dtype=F32, offset_bytes=0):
         _check(self.dev.lib.vkg_allreduce_sum(self.handle, buf.dptr + offset_bytes, count, dtype),
@@ -318,8 +324,9 @@ class DataParallelStep:
     whose gradient is final only after the embedding backward -- is summed after the
     backward, and AdamW over the parameters of the earlier parts runs meanwhile (the
     optimiser is one launch per set of parts).  The sums are the same fp32 NCCL sums over the
-    same bytes, so replicas stay bit-identical and results equal the unsplit exchange bit for
-    bit.
+    same bytes, so replicas stay bit-identical; with two workers the result also equals the
+    unsplit exchange bit for bit, with more it agrees to rounding (the order in which NCCL adds
+    the ranks' values of an element depends on where the element sits in its message).
     The side stream should use `side_comm`, a communicator held to a few CTAs
     (Comm(..., max_ctas=n)); the persistent kernels recorded after the first flush then launch
     sm_count - side_sms CTAs so that NCCL's CTAs find free SMs instead of delaying a statically
