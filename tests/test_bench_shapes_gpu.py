@@ -32,9 +32,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _report(name, payload):
-    """Leave the measured errors where a run's artefacts are collected, when that folder exists."""
-    out = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out):
+    """Leave the measured errors in the folder VKG_TEST_REPORT_DIR names, when it is set."""
+    out = os.environ.get("VKG_TEST_REPORT_DIR")
+    if out and os.path.isdir(out):
         with open(os.path.join(out, f"parity_{name}.json"), "w") as f:
             json.dump(payload, f, indent=1, sort_keys=True)
 

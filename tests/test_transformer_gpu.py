@@ -136,8 +136,8 @@ def test_gpt_against_faithful_oracle(dev, name, staged):
     exp = expected(mg.flatten_grads(G, cfg["L"]), cfg["tie"])
     errs = {k: relerr(got[k], exp[k].reshape(got[k].shape)) for k in exp}
     worst = sorted(errs.items(), key=lambda kv: -kv[1])[:5]
-    out = os.path.join(os.path.dirname(GOLD.rstrip("/")), "..", "gpurun_out")
-    if os.path.isdir(out):        # where a run's artefacts are collected, when that folder exists
+    out = os.environ.get("VKG_TEST_REPORT_DIR")      # measured errors, for the design notes
+    if out and os.path.isdir(out):
         import json
         with open(os.path.join(out, f"parity_fixture_{name}.json"), "w") as f:
             json.dump({"loss_rel_err": abs(loss - ref_loss) / abs(ref_loss), "worst_tensors": worst,
@@ -245,8 +245,8 @@ def test_long_context_causal_tiles(dev, T, H, D, fused):
     errs = {k: relerr(got[k], exp[k].reshape(got[k].shape)) for k in exp}
     assert all(np.isfinite(v) for v in errs.values())
     worst = sorted(errs.items(), key=lambda kv: -kv[1])[:5]
-    out = os.path.join(os.path.dirname(GOLD.rstrip("/")), "..", "gpurun_out")
-    if os.path.isdir(out):
+    out = os.environ.get("VKG_TEST_REPORT_DIR")
+    if out and os.path.isdir(out):
         import json
         with open(os.path.join(out, f"parity_long_T{T}_H{H}_D{D}_{fused}.json"), "w") as f:
             json.dump({"loss_rel_err": abs(loss - ref_loss) / abs(ref_loss), "worst_tensors": worst}, f)
