@@ -202,7 +202,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);     // Q K^T: both K-major, N = 128 keys
       const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);    // P V: P K-major, V MN-major, N = 64
       bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x2000u);
-      const uint32_t sq = base + FW_Q;
+      // descriptor halves (tcgen05.cuh): start address and leading offset in the low word
+      const uint32_t d_hi = smem_desc_hi(1024);
+      const uint32_t q_lo = smem_desc_lo(base + FW_Q, 16), k_lo = smem_desc_lo(base + FW_K, 16);
+      const uint32_t p_lo = smem_desc_lo(base + FW_P, 16), v_lo = smem_desc_lo(base + FW_V, 8192);
       // S number n (n counts both passes): wait for its K stage and for the softmax warps
       // to have pulled the previous S out of TMEM, then issue Q K^T.
       auto issue_s = [&](int n) -> bool {
@@ -211,11 +214,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
               mbar_wait<true>(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x2200u)))
           return false;
         tcgen05_fence_after();
-        const uint32_t sk = base + FW_K + s * FA_TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
-                   idesc_s, k ? 1u : 0u);
+        umma_f16_chain<4>(tS, q_lo, 2, k_lo + (uint32_t)s * (FA_TILE_BYTES >> 4), 2, d_hi, idesc_s, 0u);
         umma_commit(B_(3 + s));   // K stage free once these retire
         umma_commit(B_(7));       // S ready
         return true;
@@ -234,11 +233,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
              mbar_wait<true>(B_(5), j & 1, abort_flag, p.err, 0x2400u);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t sp = base + FW_P, sv = base + FW_V;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tO, make_smem_desc(sp + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                   make_smem_desc(sv + kk * 2048, 8192, 1024), idesc_o, (j | kk) ? 1u : 0u);
+        // P: two 64-key blocks, K-major; V: MN-major, 16 keys = two 8-row groups further down
+        umma_f16_chain<4>(tO, p_lo, 2, v_lo, 128, d_hi, idesc_o, j ? 1u : 0u);
+        umma_f16_chain<4>(tO, p_lo + (FA_TILE_BYTES >> 4), 2, v_lo + 4 * 128, 128, d_hi, idesc_o, 1u);
         umma_commit(B_(6));     // V free
         umma_commit(B_(10));    // P free
       }
@@ -421,18 +418,17 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
       const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);
       bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x7000u);
-      const uint32_t sq = base + FW_Q;
+      // descriptor halves (tcgen05.cuh): start address and leading offset in the low word
+      const uint32_t d_hi = smem_desc_hi(1024);
+      const uint32_t q_lo = smem_desc_lo(base + FW_Q, 16), k_lo = smem_desc_lo(base + FW_K, 16);
+      const uint32_t p_lo = smem_desc_lo(base + FW_P, 16), v_lo = smem_desc_lo(base + FW_V, 8192);
       auto issue_s = [&](int n) -> bool {
         const int s = n & 1;
         if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x7100u + s) &&
               mbar_wait<true>(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x7200u)))
           return false;
         tcgen05_fence_after();
-        const uint32_t sk = base + FW_K + s * FA_TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
-                   idesc_s, k ? 1u : 0u);
+        umma_f16_chain<4>(tS, q_lo, 2, k_lo + (uint32_t)s * (FA_TILE_BYTES >> 4), 2, d_hi, idesc_s, 0u);
         umma_commit(B_(3 + s));   // K stage free once these retire
         umma_commit(B_(7));       // S ready
         return true;
@@ -448,11 +444,9 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
              mbar_wait<true>(B_(5), j & 1, abort_flag, p.err, 0x7400u);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t sp = base + FW_P, sv = base + FW_V;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tO, make_smem_desc(sp + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                   make_smem_desc(sv + kk * 2048, 8192, 1024), idesc_o, (j | kk) ? 1u : 0u);
+        // P: two 64-key blocks, K-major; V: MN-major, 16 keys = two 8-row groups further down
+        umma_f16_chain<4>(tO, p_lo, 2, v_lo, 128, d_hi, idesc_o, j ? 1u : 0u);
+        umma_f16_chain<4>(tO, p_lo + (FA_TILE_BYTES >> 4), 2, v_lo + 4 * 128, 128, d_hi, idesc_o, 1u);
         umma_commit(B_(6));     // V free
         umma_commit(B_(10));    // P free, and O~ quiet until the next p_full
       }
@@ -831,7 +825,13 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);    // [q x hd] . [key x hd]^T
       const uint32_t idesc_g = make_idesc(0, 1, 1, FA_HD);   // [q x key]^T . [q x hd]
-      const uint32_t sk = base + KV_K, sv = base + KV_V;
+      // descriptor halves (tcgen05.cuh): K-major operands of S / dP, MN-major ones of dV / dK
+      const uint32_t d_hi = smem_desc_hi(1024);
+      const uint32_t k_lo = smem_desc_lo(base + KV_K, 16), v_lo = smem_desc_lo(base + KV_V, 16);
+      const uint32_t q_lo = smem_desc_lo(base + KV_Q, 16), do_lo = smem_desc_lo(base + KV_DO, 16);
+      const uint32_t qm_lo = smem_desc_lo(base + KV_Q, 8192), dom_lo = smem_desc_lo(base + KV_DO, 8192);
+      const uint32_t pt_lo = smem_desc_lo(base + KV_P, FA_TILE_BYTES);
+      const uint32_t dst_lo = smem_desc_lo(base + KV_DS, FA_TILE_BYTES);
       // cursor of the S / dP issue: always one step ahead of the dV / dK loop below, also
       // across an item boundary
       int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, g_a = 0;
@@ -845,15 +845,9 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
               mbar_wait<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
           return false;
         tcgen05_fence_after();
-        const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
-                   idesc_s, k ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_f16(tdP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024),
-                   idesc_s, k ? 1u : 0u);
+        const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
+        umma_f16_chain<4>(tS, q_lo + so, 2, k_lo, 2, d_hi, idesc_s, 0u);
+        umma_f16_chain<4>(tdP, do_lo + so, 2, v_lo, 2, d_hi, idesc_s, 0u);
         umma_commit(B_(5));
         if (it_a == ni_a - 1) umma_commit(B_(12));    // the item's K / V may be replaced
         ++g_a;
@@ -884,16 +878,11 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
             if (!ok) break;
           }
           tcgen05_fence_after();
-          const uint32_t sq = base + KV_Q + s * FA_TILE_BYTES, sdo = base + KV_DO + s * FA_TILE_BYTES;
-          const uint32_t sp = base + KV_P, sds = base + KV_DS;
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)      // K = 128 query rows, 16 at a time
-            umma_f16(tdV, make_smem_desc(sp + kk * 2048, FA_TILE_BYTES, 1024),
-                     make_smem_desc(sdo + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_f16(tdK, make_smem_desc(sds + kk * 2048, FA_TILE_BYTES, 1024),
-                     make_smem_desc(sq + kk * 2048, 8192, 1024), idesc_g, (it | kk) ? 1u : 0u);
+          // K = 128 query rows, 16 at a time: every operand is MN-major here (P^T, dS^T with their
+          // two 64-key blocks a tile apart; dO, Q with their 8-row groups 1024 bytes apart)
+          const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
+          umma_f16_chain<8>(tdV, pt_lo, 128, dom_lo + so, 128, d_hi, idesc_g, it ? 1u : 0u);
+          umma_f16_chain<8>(tdK, dst_lo, 128, qm_lo + so, 128, d_hi, idesc_g, it ? 1u : 0u);
           umma_commit(B_(KV_QD_EMPTY + s));   // Q / dO stage free
           umma_commit(B_(8));                 // P / dS may be overwritten
           if (it == ni - 1) umma_commit(B_(9));
@@ -1140,7 +1129,10 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
       const uint32_t idesc_q = make_idesc(0, 0, 1, FA_HD);   // dS (K-major) . K (MN-major), N = 64
-      const uint32_t sq = base + DQ_Q, sdo = base + DQ_DO;
+      const uint32_t d_hi = smem_desc_hi(1024);      // descriptor halves (tcgen05.cuh)
+      const uint32_t q_lo = smem_desc_lo(base + DQ_Q, 16), do_lo = smem_desc_lo(base + DQ_DO, 16);
+      const uint32_t k_lo = smem_desc_lo(base + DQ_K, 16), v_lo = smem_desc_lo(base + DQ_V, 16);
+      const uint32_t km_lo = smem_desc_lo(base + DQ_K, 8192), ds_lo = smem_desc_lo(base + DQ_DS, 16);
       int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, g_a = 0;
       int ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;      // key tiles of the item: qt + 1
       auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of step g_a
@@ -1152,15 +1144,9 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
               mbar_wait<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x5400u)))
           return false;
         tcgen05_fence_after();
-        const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES, sv = base + DQ_V + s * FA_TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_f16(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024),
-                   idesc_s, k ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_f16(tdP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024),
-                   idesc_s, k ? 1u : 0u);
+        const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
+        umma_f16_chain<4>(tS, q_lo, 2, k_lo + so, 2, d_hi, idesc_s, 0u);
+        umma_f16_chain<4>(tdP, do_lo, 2, v_lo + so, 2, d_hi, idesc_s, 0u);
         umma_commit(B_(5));
         if (it_a == ni_a - 1) umma_commit(B_(12));    // the item's Q / dO may be replaced
         ++g_a;
@@ -1188,12 +1174,11 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
             if (!ok) break;
           }
           tcgen05_fence_after();
-          const uint32_t sk = base + DQ_K + s * FA_TILE_BYTES;
-          const uint32_t sds = base + DQ_DS + pb * DQ_DS_STRIDE;
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)      // K = 128 keys
-            umma_f16(tdQ, make_smem_desc(sds + (kk >> 2) * FA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                     make_smem_desc(sk + kk * 2048, 8192, 1024), idesc_q, (kt | kk) ? 1u : 0u);
+          // K = 128 keys: dS in two K-major 64-key blocks, K MN-major
+          const uint32_t ds = ds_lo + (uint32_t)pb * (DQ_DS_STRIDE >> 4);
+          const uint32_t km = km_lo + (uint32_t)s * (FA_TILE_BYTES >> 4);
+          umma_f16_chain<4>(tdQ, ds, 2, km, 128, d_hi, idesc_q, kt ? 1u : 0u);
+          umma_f16_chain<4>(tdQ, ds + (FA_TILE_BYTES >> 4), 2, km + 4 * 128, 128, d_hi, idesc_q, 1u);
           umma_commit(B_(DQ_KV_EMPTY + s));   // K / V stage free
           umma_commit(B_(8 + 3 * pb));   // this dS buffer free
           if (kt == nj - 1) umma_commit(B_(9));

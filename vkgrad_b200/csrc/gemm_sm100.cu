@@ -402,21 +402,22 @@ __device__ __forceinline__ bool mma_unit(const CtaCtx& cx, const GemmParams& p, 
   if (!mbar_wait(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x200u + acc)) return false;
   tcgen05_fence_after();
   const uint32_t d_tmem = cx.tmem_base + (uint32_t)(acc * ACC_COLS);
+  // Descriptor halves of ring stage 0; a K step of 16 elements is 32 bytes further along the
+  // 128-byte row for a K-major operand and two 8-row groups (2 x 1024 bytes) further down for
+  // an MN-major one; a stage is stage_bytes further on.  All in units of 16 bytes.
+  const uint32_t d_hi = smem_desc_hi(1024);
+  const uint32_t a_lo0 = smem_desc_lo(cx.base, p.a_mn ? 8192 : 16);
+  const uint32_t b_lo0 = smem_desc_lo(cx.base + A_STAGE_BYTES, p.b_mn ? 8192 : 16);
+  const uint32_t a_step = p.a_mn ? 128u : 2u, b_step = p.b_mn ? 128u : 2u;
+  const uint32_t stage16 = cx.stage_bytes >> 4;
   for (int kb = 0; kb < nkb; ++kb) {
     if (!mbar_wait(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x300u + stage)) return false;
     tcgen05_fence_after();
-    const uint32_t sa = cx.base + stage * cx.stage_bytes;
-    const uint32_t sb = sa + A_STAGE_BYTES;
+    const uint32_t a_lo = a_lo0 + (uint32_t)stage * stage16, b_lo = b_lo0 + (uint32_t)stage * stage16;
 #pragma unroll
-    for (int k = 0; k < BK / UMMA_K; ++k) {
-      // K-major: 16 elements further along the 128-byte row.  MN-major:
-      // two 8-row groups (2 x 1024 bytes) further down.
-      uint64_t ad = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024)
-                           : make_smem_desc(sa + k * 32, 16, 1024);
-      uint64_t bd = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024)
-                           : make_smem_desc(sb + k * 32, 16, 1024);
-      umma_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
-    }
+    for (int k = 0; k < BK / UMMA_K; ++k)
+      umma_f16(d_tmem, smem_desc_pack(a_lo + k * a_step, d_hi), smem_desc_pack(b_lo + k * b_step, d_hi),
+               p.idesc, (kb | k) != 0 ? 1u : 0u);
     umma_commit(cx.empty0 + 8 * stage);  // frees the stage when these MMAs retire
     if (++stage == cx.n_stages) {
       stage = 0;
@@ -801,19 +802,19 @@ __device__ __forceinline__ bool pair_mma_unit(const CtaCtx& cx, const GemmParams
   if (!mbar_wait(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x600u + acc)) return false;
   tcgen05_fence_after();
   const uint32_t d_tmem = cx.tmem_base + (uint32_t)(acc * ACC_COLS);
+  const uint32_t d_hi = smem_desc_hi(1024);       // descriptor halves as in mma_unit
+  const uint32_t a_lo0 = smem_desc_lo(cx.base, p.a_mn ? 8192 : 16);
+  const uint32_t b_lo0 = smem_desc_lo(cx.base + A_STAGE_BYTES, p.b_mn ? 8192 : 16);
+  const uint32_t a_step = p.a_mn ? 128u : 2u, b_step = p.b_mn ? 128u : 2u;
   for (int kb = 0; kb < nkb; ++kb) {
     if (!mbar_wait(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x700u + stage)) return false;
     tcgen05_fence_after();
-    const uint32_t sa = cx.base + stage * PAIR_STAGE_BYTES;
-    const uint32_t sb = sa + A_STAGE_BYTES;
+    const uint32_t a_lo = a_lo0 + (uint32_t)stage * (PAIR_STAGE_BYTES >> 4);
+    const uint32_t b_lo = b_lo0 + (uint32_t)stage * (PAIR_STAGE_BYTES >> 4);
 #pragma unroll
-    for (int k = 0; k < BK / UMMA_K; ++k) {
-      uint64_t ad = p.a_mn ? make_smem_desc(sa + k * 2048, 8192, 1024)
-                           : make_smem_desc(sa + k * 32, 16, 1024);
-      uint64_t bd = p.b_mn ? make_smem_desc(sb + k * 2048, 8192, 1024)
-                           : make_smem_desc(sb + k * 32, 16, 1024);
-      umma2_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
-    }
+    for (int k = 0; k < BK / UMMA_K; ++k)
+      umma2_f16(d_tmem, smem_desc_pack(a_lo + k * a_step, d_hi), smem_desc_pack(b_lo + k * b_step, d_hi),
+                p.idesc, (kb | k) != 0 ? 1u : 0u);
     umma2_commit(cx.empty0 + 8 * stage);
     if (++stage == PAIR_STAGES) {
       stage = 0;

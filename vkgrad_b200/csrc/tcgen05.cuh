@@ -118,6 +118,22 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+// The same descriptor as two 32-bit halves.  The high word (stride between 8-row groups,
+// version, swizzle) is constant per operand; the low word carries the start address (>> 4) and
+// the leading-dimension offset, so stepping along K or to the next ring stage is ONE integer
+// add on it.  The thread that issues tcgen05.mma is a single lane with nothing to hide its
+// latencies behind: a descriptor rebuilt from shifts and masks per instruction costs that lane
+// about 125 cycles per MMA, more than an N <= 128 instruction takes on the tensor core.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint32_t smem_desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint64_t smem_desc_pack(uint32_t lo, uint32_t hi) {
+  return ((uint64_t)hi << 32) | (uint64_t)lo;
+}
+
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                          uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -126,6 +142,19 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// NK instructions along K into one accumulator: the operands' descriptor low words advance by
+// a_step / b_step (units of 16 bytes) per instruction, `hi` is their common high word; the
+// first instruction overwrites the accumulator unless acc_first is set.
+template <int NK>
+__device__ __forceinline__ void umma_f16_chain(uint32_t tmem_d, uint32_t a_lo, uint32_t a_step,
+                                               uint32_t b_lo, uint32_t b_step, uint32_t hi,
+                                               uint32_t idesc, uint32_t acc_first) {
+#pragma unroll
+  for (int k = 0; k < NK; ++k)
+    umma_f16(tmem_d, smem_desc_pack(a_lo + k * a_step, hi), smem_desc_pack(b_lo + k * b_step, hi), idesc,
+             k ? 1u : acc_first);
 }
 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
