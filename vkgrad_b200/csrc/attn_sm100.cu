@@ -36,7 +36,8 @@ constexpr int FA_HD = 64;          // head dimension
 constexpr int FA_TILE_BYTES = FA_T * FA_HD * 2;  // 16 KB: one 128 x 64 fp16 tile, 128 B rows
 constexpr int FA_THREADS = 320;      // producer + MMA + eight softmax warps
 constexpr int FA_SOFTMAX_WARPS = 8;
-constexpr int BW_THREADS = 320;
+constexpr int BW_SOFTMAX_WARPS = 16;   // backward: four warps per TMEM lane quarter, 32 keys of a row each
+constexpr int BW_THREADS = (2 + BW_SOFTMAX_WARPS) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnParams {
@@ -108,6 +109,31 @@ __device__ __forceinline__ float fwd_p_tile(const uint32_t (&r)[64], int key0, i
       hv[e] = __floats2half2_rn(pv[0], pv[1]);
     }
     *reinterpret_cast<uint4*>(prow + (((uint32_t)u ^ x) << 4)) = *reinterpret_cast<uint4*>(hv);
+  }
+  return l;
+}
+
+// The same exponentials for a P~ that stays in tensor memory: the fp16 pairs (keys 2i, 2i + 1)
+// replace r[i], ready for tcgen05.st; returns the fp32 sum of the un-rounded values.
+template <bool MASK>
+__device__ __forceinline__ float fwd_p_pack(uint32_t (&r)[64], int key0, int qi, int st, float cscale,
+                                            float nm) {
+  float l = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float pv[2];
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      float pr = vkg_ex2(fmaf(__uint_as_float(r[2 * i + w]), cscale, nm));
+      if (MASK) {
+        const int key = key0 + 2 * i + w;
+        if (key > qi || key < st) pr = 0.f;
+      }
+      pv[w] = pr;
+    }
+    l += pv[0] + pv[1];
+    const __half2 h = __floats2half2_rn(pv[0], pv[1]);
+    r[i] = *reinterpret_cast<const uint32_t*>(&h);
   }
   return l;
 }
@@ -397,7 +423,7 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   tcgen05_fence_after();
   pdl_wait();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;
+  const uint32_t tS = tmem, tO = tmem + 128, tP = tmem + 192;   // P~: 128 keys, two per column
 
   if (warp == 0) {
     if (lane == 0) {
@@ -421,7 +447,7 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       // descriptor halves (tcgen05.cuh): start address and leading offset in the low word
       const uint32_t d_hi = smem_desc_hi(1024);
       const uint32_t q_lo = smem_desc_lo(base + FW_Q, 16), k_lo = smem_desc_lo(base + FW_K, 16);
-      const uint32_t p_lo = smem_desc_lo(base + FW_P, 16), v_lo = smem_desc_lo(base + FW_V, 8192);
+      const uint32_t v_lo = smem_desc_lo(base + FW_V, 8192);
       auto issue_s = [&](int n) -> bool {
         const int s = n & 1;
         if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x7100u + s) &&
@@ -444,9 +470,8 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
              mbar_wait<true>(B_(5), j & 1, abort_flag, p.err, 0x7400u);
         if (!ok) break;
         tcgen05_fence_after();
-        // P: two 64-key blocks, K-major; V: MN-major, 16 keys = two 8-row groups further down
-        umma_f16_chain<4>(tO, p_lo, 2, v_lo, 128, d_hi, idesc_o, j ? 1u : 0u);
-        umma_f16_chain<4>(tO, p_lo + (FA_TILE_BYTES >> 4), 2, v_lo + 4 * 128, 128, d_hi, idesc_o, 1u);
+        // P~ from tensor memory; V: MN-major, 16 keys = two 8-row groups further down
+        umma_f16_ts_chain<8>(tO, tP, v_lo, 128, d_hi, idesc_o, j ? 1u : 0u);
         umma_commit(B_(6));     // V free
         umma_commit(B_(10));    // P free, and O~ quiet until the next p_full
       }
@@ -530,13 +555,16 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         }
       }
       const float nm = -m_ref;
-      uint8_t* prow = gbase + FW_P + half * FA_TILE_BYTES + qr * 128;
-      if (need_mask) l += fwd_p_tile<true>(r, j * FA_T + half * 64, qi, st, p.cscale, nm, prow, qr & 7);
-      else l += fwd_p_tile<false>(r, 0, 0, 0, p.cscale, nm, prow, qr & 7);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // P~ packed two keys per register, overwriting the scores they came from, then into
+      // this half's 32 columns of the P~ area
+      if (need_mask) l += fwd_p_pack<true>(r, j * FA_T + half * 64, qi, st, p.cscale, nm);
+      else l += fwd_p_pack<false>(r, 0, 0, 0, p.cscale, nm);
+      tmem_st16(tP + t_lane + half * 32, r);
+      tmem_st16(tP + t_lane + half * 32 + 16, r + 16);
+      tmem_wait_st();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(B_(9));        // this warp's part of P is in shared memory
+      if (lane == 0) mbar_arrive(B_(9));        // this warp's part of P~ is in tensor memory
     }
     // row sums of the two halves (both hold the same reference maximum)
     float* xchg = reinterpret_cast<float*>(gbase + FW_XCHG + 2 * 2 * FA_T * 8);
@@ -779,7 +807,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
     prefetch_tensormap(&tm);
     prefetch_tensormap(&tmdo);
     for (int i = 0; i < KV_NBAR; ++i)
-      mbar_init(B_(i), (i == 6 || i == 7 || i == 13) ? FA_SOFTMAX_WARPS : 1);
+      mbar_init(B_(i), (i == 6 || i == 7 || i == 13) ? BW_SOFTMAX_WARPS : 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -890,7 +918,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       }
     }
   } else {
-    const int half = (warp - 2) >> 2;            // which 64 of the tile's 128 keys
+    const int part = (warp - 2) >> 2;            // which 32 of the tile's 128 keys
     const int r = (warp & 3) * 32 + lane;
     const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
     bool ok = true;
@@ -905,19 +933,21 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       if (!mbar_wait_warp<true>(B_(9), jj & 1, abort_flag, p.err, 0x4800u)) return false;
       tcgen05_fence_after();
       const int key = k0 + r;     // accumulator rows are keys here
-      // half 0 stores dV (slice 2 of dqkv), half 1 stores dK (slice 1)
-      uint32_t rr[64];
-      const uint32_t t = (half == 0 ? tdV : tdK) + t_lane;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld16(t + c * 16, rr + c * 16);
+      // parts 0, 1 store the two 32-column halves of dV (slice 2 of dqkv), parts 2, 3 those of
+      // dK (slice 1)
+      uint32_t rr[32];
+      const int slice = part < 2 ? 2 : 1, col0 = (part & 1) * 32;
+      const uint32_t t = (part < 2 ? tdV : tdK) + t_lane + (uint32_t)col0;
+      tmem_ld16(t, rr);
+      tmem_ld16(t + 16, rr + 16);
       tmem_wait_ld();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(13));           // the accumulators may be overwritten
       {
-        uint4 hv[8];
+        uint4 hv[4];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < 4; ++u) {
           __half2 h2[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
@@ -926,19 +956,19 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
           hv[u] = *reinterpret_cast<uint4*>(h2);
         }
         const int key_w = k0 + (warp & 3) * 32;      // first key of this warp's 32 rows
-        __half* dst = p.dqkv + (size_t)(row0 + key_w) * 3 * p.D + (half == 0 ? 2 : 1) * p.D + h * FA_HD;
-        warp_store_rows<8>(hv, gbase + KV_OUT + (warp - 2) * 4096, lane, reinterpret_cast<uint8_t*>(dst),
+        __half* dst = p.dqkv + (size_t)(row0 + key_w) * 3 * p.D + slice * p.D + h * FA_HD + col0;
+        warp_store_rows<4>(hv, gbase + KV_OUT + (warp - 2) * 2048, lane, reinterpret_cast<uint8_t*>(dst),
                            (size_t)3 * p.D * 2, p.T - key_w);
       }
       if (p.colsum) {
         // the qkv bias gradient: column sums of dV / dK as stored
-        float val[64];
+        float val[32];
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
+        for (int c = 0; c < 32; ++c)
           val[c] = key < p.T ? __half2float(__float2half_rn(__uint_as_float(rr[c]))) : 0.f;
-        float* dst = p.colsum + ((size_t)(b * p.nqt + kt) * 4 + (warp & 3)) * 3 * p.D +
-                     (half == 0 ? 2 : 1) * p.D + h * FA_HD;
-        warp_col_sums<64>(val, lane, dst);
+        float* dst = p.colsum + ((size_t)(b * p.nqt + kt) * 4 + (warp & 3)) * 3 * p.D + slice * p.D +
+                     h * FA_HD + col0;
+        warp_col_sums<32>(val, lane, dst);
       }
       return true;
     };
@@ -992,32 +1022,24 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
         ok = mbar_wait_warp<true>(B_(5), g & 1, abort_flag, p.err, 0x4600u);
         if (!ok) break;
         tcgen05_fence_after();
-        uint32_t rs[64], rdp[64];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, rs + c * 16);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld16(tdP + t_lane + half * 64 + c * 16, rdp + c * 16);
+        uint32_t rs[32], rdp[32];
+        tmem_ld16(tS + t_lane + part * 32, rs);
+        tmem_ld16(tS + t_lane + part * 32 + 16, rs + 16);
+        tmem_ld16(tdP + t_lane + part * 32, rdp);
+        tmem_ld16(tdP + t_lane + part * 32 + 16, rdp + 16);
         tmem_wait_ld();
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(B_(6));          // S / dP may be overwritten
         // P and dS of this step, packed, in registers; the buffer is still being read
-        uint4 hp[8], hd[8];
-        if (need_mask) {
-          bwd_chunk_regs<true>(rs, rdp, 2 * half, k0, qi, st, p.cscale, p.scale, nlse, dsc, hp, hd);
-          bwd_chunk_regs<true>(rs + 32, rdp + 32, 2 * half + 1, k0, qi, st, p.cscale, p.scale, nlse, dsc,
-                               hp + 4, hd + 4);
-        } else {
-          bwd_chunk_regs<false>(rs, rdp, 2 * half, k0, qi, st, p.cscale, p.scale, nlse, dsc, hp, hd);
-          bwd_chunk_regs<false>(rs + 32, rdp + 32, 2 * half + 1, k0, qi, st, p.cscale, p.scale, nlse, dsc,
-                                hp + 4, hd + 4);
-        }
+        uint4 hp[4], hd[4];
+        if (need_mask) bwd_chunk_regs<true>(rs, rdp, part, k0, qi, st, p.cscale, p.scale, nlse, dsc, hp, hd);
+        else bwd_chunk_regs<false>(rs, rdp, part, k0, qi, st, p.cscale, p.scale, nlse, dsc, hp, hd);
         ok = mbar_wait_warp<true>(B_(8), (g & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // dV / dK of step g - 1 done
         if (!ok) break;
         uint8_t* sp = gbase + KV_P;
         uint8_t* sds = gbase + KV_DS;
-        bwd_chunk_store(2 * half, r, hp, hd, sp, sds);
-        bwd_chunk_store(2 * half + 1, r, hp + 4, hd + 4, sp, sds);
+        bwd_chunk_store(part, r, hp, hd, sp, sds);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(B_(7));
@@ -1083,7 +1105,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
     prefetch_tensormap(&tm);
     prefetch_tensormap(&tmdo);
     for (int i = 0; i < DQ_NBAR; ++i)
-      mbar_init(B_(i), (i == 6 || i == 7 || i == 10 || i == 13) ? FA_SOFTMAX_WARPS : 1);
+      mbar_init(B_(i), (i == 6 || i == 7 || i == 10) ? BW_SOFTMAX_WARPS : (i == 13 ? 8 : 1));
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1186,7 +1208,8 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       }
     }
   } else {
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;            // which 32 of a key tile's 128 keys
+    const int half = part;                       // parts 0 and 1 also read the 64 dQ columns out
     const int r = (warp & 3) * 32 + lane;
     const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
     bool ok = true;
@@ -1265,11 +1288,11 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
         ok = mbar_wait_warp<true>(B_(5), g & 1, abort_flag, p.err, 0x5600u);
         if (!ok) break;
         tcgen05_fence_after();
-        uint32_t rs[64], rdp[64];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld16(tS + t_lane + half * 64 + c * 16, rs + c * 16);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld16(tdP + t_lane + half * 64 + c * 16, rdp + c * 16);
+        uint32_t rs[32], rdp[32];
+        tmem_ld16(tS + t_lane + part * 32, rs);
+        tmem_ld16(tS + t_lane + part * 32 + 16, rs + 16);
+        tmem_ld16(tdP + t_lane + part * 32, rdp);
+        tmem_ld16(tdP + t_lane + part * 32 + 16, rdp + 16);
         tmem_wait_ld();
         tcgen05_fence_before();
         __syncwarp();
@@ -1278,27 +1301,22 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
         ok = mbar_wait_warp<true>(B_(8 + 3 * pb), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
         if (!ok) break;
         uint8_t* sds = gbase + DQ_DS + pb * DQ_DS_STRIDE;
-        if (need_mask) {
-          bwd_chunk<true>(rs, rdp, 2 * half, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
-          bwd_chunk<true>(rs + 32, rdp + 32, 2 * half + 1, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse,
-                          dsc, nullptr, sds);
-        } else {
-          bwd_chunk<false>(rs, rdp, 2 * half, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
-          bwd_chunk<false>(rs + 32, rdp + 32, 2 * half + 1, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse,
-                           dsc, nullptr, sds);
-        }
+        if (need_mask)
+          bwd_chunk<true>(rs, rdp, part, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
+        else
+          bwd_chunk<false>(rs, rdp, part, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
         if (pend_item >= 0) {
-          ok = store_item(pend_item, pend_j);
+          if (part < 2) ok = store_item(pend_item, pend_j);
           pend_item = -1;
         }
       }
       pend_item = item;       // read this item's dQ out after the next item's first step
       pend_j = j;
     }
-    if (ok && pend_item >= 0) ok = store_item(pend_item, pend_j);
+    if (ok && pend_item >= 0 && part < 2) ok = store_item(pend_item, pend_j);
   }
   __syncwarp();
   tcgen05_fence_before();

@@ -157,6 +157,29 @@ __device__ __forceinline__ void umma_f16_chain(uint32_t tmem_d, uint32_t a_lo, u
              k ? 1u : acc_first);
 }
 
+// The same instruction with the A operand in tensor memory: lane = row of A, two consecutive K
+// elements of a 16-bit type per 32-bit column (even K in the low half), so one K = 16 step
+// reads 8 columns.  A operand written there with tcgen05.st never passes through shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// NK such instructions along K: A advances 8 columns, B's descriptor low word by b_step.
+template <int NK>
+__device__ __forceinline__ void umma_f16_ts_chain(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo,
+                                                  uint32_t b_step, uint32_t hi, uint32_t idesc,
+                                                  uint32_t acc_first) {
+#pragma unroll
+  for (int k = 0; k < NK; ++k)
+    umma_f16_ts(tmem_d, tmem_a + 8 * k, smem_desc_pack(b_lo + k * b_step, hi), idesc, k ? 1u : acc_first);
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
