@@ -36,9 +36,18 @@ constexpr int FA_HD = 64;          // head dimension
 constexpr int FA_TILE_BYTES = FA_T * FA_HD * 2;  // 16 KB: one 128 x 64 fp16 tile, 128 B rows
 constexpr int FA_THREADS = 320;      // producer + MMA + eight softmax warps
 constexpr int FA_SOFTMAX_WARPS = 8;
-constexpr int BW_SOFTMAX_WARPS = 16;   // backward: four warps per TMEM lane quarter, 32 keys of a row each
+constexpr int BW_SOFTMAX_WARPS = 16;   // dK / dV kernel: four warps per TMEM lane quarter, 32 keys of a row each
+#ifndef VKG_ATTN_DQ_WARPS
+#define VKG_ATTN_DQ_WARPS 16
+#endif
+constexpr int DQ_SOFTMAX_WARPS = VKG_ATTN_DQ_WARPS;   // dQ kernel: 2 or 4 warps per lane quarter
+constexpr int DQ_THREADS = (2 + DQ_SOFTMAX_WARPS) * 32;
 constexpr int BW_THREADS = (2 + BW_SOFTMAX_WARPS) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
+#ifndef VKG_ATTN_SOFTMAX_SPIN
+#define VKG_ATTN_SOFTMAX_SPIN 0
+#endif
+constexpr bool SM_SPIN = VKG_ATTN_SOFTMAX_SPIN != 0;
 
 struct AttnParams {
   int B, T, H, D;
@@ -224,49 +233,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);     // Q K^T: both K-major, N = 128 keys
-      const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);    // P V: P K-major, V MN-major, N = 64
-      bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x2000u);
-      // descriptor halves (tcgen05.cuh): start address and leading offset in the low word
-      const uint32_t d_hi = smem_desc_hi(1024);
-      const uint32_t q_lo = smem_desc_lo(base + FW_Q, 16), k_lo = smem_desc_lo(base + FW_K, 16);
-      const uint32_t p_lo = smem_desc_lo(base + FW_P, 16), v_lo = smem_desc_lo(base + FW_V, 8192);
-      // S number n (n counts both passes): wait for its K stage and for the softmax warps
-      // to have pulled the previous S out of TMEM, then issue Q K^T.
-      auto issue_s = [&](int n) -> bool {
-        const int s = n & 1;
-        if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x2100u + s) &&
-              mbar_wait<true>(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x2200u)))
-          return false;
-        tcgen05_fence_after();
-        umma_f16_chain<4>(tS, q_lo, 2, k_lo + (uint32_t)s * (FA_TILE_BYTES >> 4), 2, d_hi, idesc_s, 0u);
-        umma_commit(B_(3 + s));   // K stage free once these retire
-        umma_commit(B_(7));       // S ready
-        return true;
-      };
-      // pass 1: S only.  Pass 2 is software-pipelined: S(j+1) is issued before P(j) V, so
-      // the tensor core works on the next scores while the softmax warps finish P(j).
-      int n = 0;
-      for (; n < nj && ok; ++n) ok = issue_s(n);
-      if (ok) ok = issue_s(n++);
-      for (int j = 0; j < nj && ok; ++j) {
-        if (j + 1 < nj) {
-          ok = issue_s(n++);
-          if (!ok) break;
-        }
-        ok = mbar_wait<true>(B_(9), j & 1, abort_flag, p.err, 0x2300u) &&
-             mbar_wait<true>(B_(5), j & 1, abort_flag, p.err, 0x2400u);
+    // the whole warp runs this converged; one elected lane issues each tcgen05 instruction
+    const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);     // Q K^T: both K-major, N = 128 keys
+    const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);    // P V: P K-major, V MN-major, N = 64
+    bool ok = mbar_wait_warp<true>(B_(0), 0, abort_flag, p.err, 0x2000u);
+    // descriptor halves (tcgen05.cuh): start address and leading offset in the low word
+    const uint32_t d_hi = smem_desc_hi(1024);
+    const uint32_t q_lo = smem_desc_lo(base + FW_Q, 16), k_lo = smem_desc_lo(base + FW_K, 16);
+    const uint32_t p_lo = smem_desc_lo(base + FW_P, 16), v_lo = smem_desc_lo(base + FW_V, 8192);
+    // S number n (n counts both passes): wait for its K stage and for the softmax warps
+    // to have pulled the previous S out of TMEM, then issue Q K^T.
+    auto issue_s = [&](int n) -> bool {
+      const int s = n & 1;
+      if (!(mbar_wait_warp<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x2100u + s) &&
+            mbar_wait_warp<true>(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x2200u)))
+        return false;
+      tcgen05_fence_after();
+      umma_f16_chain<4>(tS, q_lo, 2, k_lo + (uint32_t)s * (FA_TILE_BYTES >> 4), 2, d_hi, idesc_s, 0u);
+      umma_commit_one(B_(3 + s));   // K stage free once these retire
+      umma_commit_one(B_(7));       // S ready
+      return true;
+    };
+    // pass 1: S only.  Pass 2 is software-pipelined: S(j+1) is issued before P(j) V, so
+    // the tensor core works on the next scores while the softmax warps finish P(j).
+    int n = 0;
+    for (; n < nj && ok; ++n) ok = issue_s(n);
+    if (ok) ok = issue_s(n++);
+    for (int j = 0; j < nj && ok; ++j) {
+      if (j + 1 < nj) {
+        ok = issue_s(n++);
         if (!ok) break;
-        tcgen05_fence_after();
-        // P: two 64-key blocks, K-major; V: MN-major, 16 keys = two 8-row groups further down
-        umma_f16_chain<4>(tO, p_lo, 2, v_lo, 128, d_hi, idesc_o, j ? 1u : 0u);
-        umma_f16_chain<4>(tO, p_lo + (FA_TILE_BYTES >> 4), 2, v_lo + 4 * 128, 128, d_hi, idesc_o, 1u);
-        umma_commit(B_(6));     // V free
-        umma_commit(B_(10));    // P free
       }
-      if (ok) umma_commit(B_(11));
+      ok = mbar_wait_warp<true>(B_(9), j & 1, abort_flag, p.err, 0x2300u) &&
+           mbar_wait_warp<true>(B_(5), j & 1, abort_flag, p.err, 0x2400u);
+      if (!ok) break;
+      tcgen05_fence_after();
+      // P: two 64-key blocks, K-major; V: MN-major, 16 keys = two 8-row groups further down
+      umma_f16_chain<4>(tO, p_lo, 2, v_lo, 128, d_hi, idesc_o, j ? 1u : 0u);
+      umma_f16_chain<4>(tO, p_lo + (FA_TILE_BYTES >> 4), 2, v_lo + 4 * 128, 128, d_hi, idesc_o, 1u);
+      umma_commit_one(B_(6));     // V free
+      umma_commit_one(B_(10));    // P free
     }
+    if (ok) umma_commit_one(B_(11));
   } else {
     // Softmax: two warps per TMEM lane quarter; `half` picks which 64 of the tile's 128
     // keys this warp handles.  Each thread owns one query row of its half.
@@ -282,7 +290,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     int it = 0;
     // pass 1: row maximum of the scaled scores (no exponentials)
     for (int j = 0; j < nj && ok; ++j, ++it) {
-      ok = mbar_wait_warp<true>(B_(7), it & 1, abort_flag, p.err, 0x3100u);
+      ok = mbar_wait_warp<SM_SPIN>(B_(7), it & 1, abort_flag, p.err, 0x3100u);
       if (!ok) break;
       tcgen05_fence_after();
       const bool need_mask = (j == qt) || (p.seg != nullptr);
@@ -304,7 +312,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     asm volatile("bar.sync 1, 256;" ::: "memory");
     // pass 2: P = exp2(t - m) rounded to fp16 (normalised by 1/l at the very end), l in fp32
     for (int j = 0; j < nj && ok; ++j, ++it) {
-      ok = mbar_wait_warp<true>(B_(7), it & 1, abort_flag, p.err, 0x3150u);
+      ok = mbar_wait_warp<SM_SPIN>(B_(7), it & 1, abort_flag, p.err, 0x3150u);
       if (!ok) break;
       tcgen05_fence_after();
       const bool need_mask = (j == qt) || (p.seg != nullptr);
@@ -315,7 +323,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(8));
-      ok = mbar_wait_warp<true>(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x3200u);   // P buffer free
+      ok = mbar_wait_warp<SM_SPIN>(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x3200u);   // P buffer free
       if (!ok) break;
       uint8_t* prow = gbase + FW_P + half * FA_TILE_BYTES + qr * 128;
       if (need_mask) l += fwd_p_tile<true>(r, j * FA_T + half * 64, qi, st, p.cscale, nm, prow, qr & 7);
@@ -329,7 +337,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     l = xchg[qr] + xchg[128 + qr];
     const float inv_l = 1.0f / l;               // l >= 1: key == query is always valid
     if (half == 0 && q_ok) p.lse2[(size_t)(b * p.H + h) * p.T + qi] = m + log2f(l);
-    if (ok) ok = mbar_wait_warp<true>(B_(11), 0, abort_flag, p.err, 0x3300u);
+    if (ok) ok = mbar_wait_warp<SM_SPIN>(B_(11), 0, abort_flag, p.err, 0x3300u);
     if (ok) {
       tcgen05_fence_after();
       uint32_t r[32];                            // this half's 32 of the 64 output columns
@@ -440,43 +448,42 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
-      const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);
-      bool ok = mbar_wait<true>(B_(0), 0, abort_flag, p.err, 0x7000u);
-      // descriptor halves (tcgen05.cuh): start address and leading offset in the low word
-      const uint32_t d_hi = smem_desc_hi(1024);
-      const uint32_t q_lo = smem_desc_lo(base + FW_Q, 16), k_lo = smem_desc_lo(base + FW_K, 16);
-      const uint32_t v_lo = smem_desc_lo(base + FW_V, 8192);
-      auto issue_s = [&](int n) -> bool {
-        const int s = n & 1;
-        if (!(mbar_wait<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x7100u + s) &&
-              mbar_wait<true>(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x7200u)))
-          return false;
-        tcgen05_fence_after();
-        umma_f16_chain<4>(tS, q_lo, 2, k_lo + (uint32_t)s * (FA_TILE_BYTES >> 4), 2, d_hi, idesc_s, 0u);
-        umma_commit(B_(3 + s));   // K stage free once these retire
-        umma_commit(B_(7));       // S ready
-        return true;
-      };
-      int n = 0;
-      if (ok) ok = issue_s(n++);
-      for (int j = 0; j < nj && ok; ++j) {
-        if (j + 1 < nj) {          // the next scores first: the tensor core works while P(j) forms
-          ok = issue_s(n++);
-          if (!ok) break;
-        }
-        ok = mbar_wait<true>(B_(9), j & 1, abort_flag, p.err, 0x7300u) &&
-             mbar_wait<true>(B_(5), j & 1, abort_flag, p.err, 0x7400u);
+    // the whole warp runs this converged; one elected lane issues each tcgen05 instruction
+    const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
+    const uint32_t idesc_o = make_idesc(0, 0, 1, FA_HD);
+    bool ok = mbar_wait_warp<true>(B_(0), 0, abort_flag, p.err, 0x7000u);
+    // descriptor halves (tcgen05.cuh): start address and leading offset in the low word
+    const uint32_t d_hi = smem_desc_hi(1024);
+    const uint32_t q_lo = smem_desc_lo(base + FW_Q, 16), k_lo = smem_desc_lo(base + FW_K, 16);
+    const uint32_t v_lo = smem_desc_lo(base + FW_V, 8192);
+    auto issue_s = [&](int n) -> bool {
+      const int s = n & 1;
+      if (!(mbar_wait_warp<true>(B_(1 + s), (n >> 1) & 1, abort_flag, p.err, 0x7100u + s) &&
+            mbar_wait_warp<true>(B_(8), (n & 1) ^ 1u, abort_flag, p.err, 0x7200u)))
+        return false;
+      tcgen05_fence_after();
+      umma_f16_chain<4>(tS, q_lo, 2, k_lo + (uint32_t)s * (FA_TILE_BYTES >> 4), 2, d_hi, idesc_s, 0u);
+      umma_commit_one(B_(3 + s));   // K stage free once these retire
+      umma_commit_one(B_(7));       // S ready
+      return true;
+    };
+    int n = 0;
+    if (ok) ok = issue_s(n++);
+    for (int j = 0; j < nj && ok; ++j) {
+      if (j + 1 < nj) {          // the next scores first: the tensor core works while P(j) forms
+        ok = issue_s(n++);
         if (!ok) break;
-        tcgen05_fence_after();
-        // P~ from tensor memory; V: MN-major, 16 keys = two 8-row groups further down
-        umma_f16_ts_chain<8>(tO, tP, v_lo, 128, d_hi, idesc_o, j ? 1u : 0u);
-        umma_commit(B_(6));     // V free
-        umma_commit(B_(10));    // P free, and O~ quiet until the next p_full
       }
-      if (ok) umma_commit(B_(11));
+      ok = mbar_wait_warp<true>(B_(9), j & 1, abort_flag, p.err, 0x7300u) &&
+           mbar_wait_warp<true>(B_(5), j & 1, abort_flag, p.err, 0x7400u);
+      if (!ok) break;
+      tcgen05_fence_after();
+      // P~ from tensor memory; V: MN-major, 16 keys = two 8-row groups further down
+      umma_f16_ts_chain<8>(tO, tP, v_lo, 128, d_hi, idesc_o, j ? 1u : 0u);
+      umma_commit_one(B_(6));     // V free
+      umma_commit_one(B_(10));    // P free, and O~ quiet until the next p_full
     }
+    if (ok) umma_commit_one(B_(11));
   } else {
     const int half = (warp - 2) >> 2;
     const int qr = (warp & 3) * 32 + lane;      // row within the tile = TMEM lane
@@ -487,7 +494,7 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     float m_ref = -1e30f, l = 0.f;              // reference maximum (scaled units), row sum
     bool ok = true;
     for (int j = 0; j < nj && ok; ++j) {
-      ok = mbar_wait_warp<true>(B_(7), j & 1, abort_flag, p.err, 0x8100u);
+      ok = mbar_wait_warp<SM_SPIN>(B_(7), j & 1, abort_flag, p.err, 0x8100u);
       if (!ok) break;
       tcgen05_fence_after();
       const bool need_mask = (j == qt) || (p.seg != nullptr);
@@ -530,7 +537,7 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
       if (!ok) break;
       const float m_row = fmaxf(mt, mo) * p.cscale;
       // the previous P V has retired: the P buffer is free and O~ is quiet
-      ok = mbar_wait_warp<true>(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x8200u);
+      ok = mbar_wait_warp<SM_SPIN>(B_(10), (j & 1) ^ 1u, abort_flag, p.err, 0x8200u);
       if (!ok) break;
       if (j == 0) {
         m_ref = m_row;
@@ -573,7 +580,7 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     l = xchg[qr] + xchg[128 + qr];
     const float inv_l = 1.0f / l;               // l > 0: key == query is always valid
     if (half == 0 && q_ok) p.lse2[(size_t)(b * p.H + h) * p.T + qi] = m_ref + log2f(l);
-    if (ok) ok = mbar_wait_warp<true>(B_(11), 0, abort_flag, p.err, 0x8300u);
+    if (ok) ok = mbar_wait_warp<SM_SPIN>(B_(11), 0, abort_flag, p.err, 0x8300u);
     if (ok) {
       tcgen05_fence_after();
       uint32_t r[32];
@@ -850,71 +857,70 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);    // [q x hd] . [key x hd]^T
-      const uint32_t idesc_g = make_idesc(0, 1, 1, FA_HD);   // [q x key]^T . [q x hd]
-      // descriptor halves (tcgen05.cuh): K-major operands of S / dP, MN-major ones of dV / dK
-      const uint32_t d_hi = smem_desc_hi(1024);
-      const uint32_t k_lo = smem_desc_lo(base + KV_K, 16), v_lo = smem_desc_lo(base + KV_V, 16);
-      const uint32_t q_lo = smem_desc_lo(base + KV_Q, 16), do_lo = smem_desc_lo(base + KV_DO, 16);
-      const uint32_t qm_lo = smem_desc_lo(base + KV_Q, 8192), dom_lo = smem_desc_lo(base + KV_DO, 8192);
-      const uint32_t pt_lo = smem_desc_lo(base + KV_P, FA_TILE_BYTES);
-      const uint32_t dst_lo = smem_desc_lo(base + KV_DS, FA_TILE_BYTES);
-      // cursor of the S / dP issue: always one step ahead of the dV / dK loop below, also
-      // across an item boundary
-      int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, g_a = 0;
-      int ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
-      auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of step g_a
-        if (item_a >= n_items) return true;
-        if (it_a == 0 && !mbar_wait<true>(B_(0), j_a & 1, abort_flag, p.err, 0x4200u)) return false;
-        const int s = g_a % KV_STAGES;
-        if (!(mbar_wait<true>(B_(KV_QD_FULL + s), (uint32_t)(g_a / KV_STAGES) & 1u, abort_flag, p.err,
-                              0x4300u + s) &&
-              mbar_wait<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
-          return false;
+    // the whole warp runs this converged; one elected lane issues each tcgen05 instruction
+    const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);    // [q x hd] . [key x hd]^T
+    const uint32_t idesc_g = make_idesc(0, 1, 1, FA_HD);   // [q x key]^T . [q x hd]
+    // descriptor halves (tcgen05.cuh): K-major operands of S / dP, MN-major ones of dV / dK
+    const uint32_t d_hi = smem_desc_hi(1024);
+    const uint32_t k_lo = smem_desc_lo(base + KV_K, 16), v_lo = smem_desc_lo(base + KV_V, 16);
+    const uint32_t q_lo = smem_desc_lo(base + KV_Q, 16), do_lo = smem_desc_lo(base + KV_DO, 16);
+    const uint32_t qm_lo = smem_desc_lo(base + KV_Q, 8192), dom_lo = smem_desc_lo(base + KV_DO, 8192);
+    const uint32_t pt_lo = smem_desc_lo(base + KV_P, FA_TILE_BYTES);
+    const uint32_t dst_lo = smem_desc_lo(base + KV_DS, FA_TILE_BYTES);
+    // cursor of the S / dP issue: always one step ahead of the dV / dK loop below, also
+    // across an item boundary
+    int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, g_a = 0;
+    int ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
+    auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of step g_a
+      if (item_a >= n_items) return true;
+      if (it_a == 0 && !mbar_wait_warp<true>(B_(0), j_a & 1, abort_flag, p.err, 0x4200u)) return false;
+      const int s = g_a % KV_STAGES;
+      if (!(mbar_wait_warp<true>(B_(KV_QD_FULL + s), (uint32_t)(g_a / KV_STAGES) & 1u, abort_flag, p.err,
+                            0x4300u + s) &&
+            mbar_wait_warp<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
+        return false;
+      tcgen05_fence_after();
+      const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
+      umma_f16_chain<4>(tS, q_lo + so, 2, k_lo, 2, d_hi, idesc_s, 0u);
+      umma_f16_chain<4>(tdP, do_lo + so, 2, v_lo, 2, d_hi, idesc_s, 0u);
+      umma_commit_one(B_(5));
+      if (it_a == ni_a - 1) umma_commit_one(B_(12));    // the item's K / V may be replaced
+      ++g_a;
+      if (++it_a == ni_a) {
+        item_a = snake_item(++j_a, G, (int)blockIdx.x);
+        it_a = 0;
+        ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
+      }
+      return true;
+    };
+    bool ok = issue_sdp();
+    int g = 0, j = 0;
+    for (;; ++j) {
+      const int item = snake_item(j, G, (int)blockIdx.x);
+      if (item >= n_items || !ok) break;
+      const int ni = p.nqt - item / HB;
+      for (int it = 0; it < ni; ++it, ++g) {
+        // the next step's S / dP go first (also when that means waiting for a new item's
+        // operands: issuing dV / dK first measured slower), so the tensor core is busy while
+        // the softmax warps turn S, dP into P, dS
+        ok = issue_sdp();
+        if (!ok) break;
+        const int s = g % KV_STAGES;         // Q / dO stage of this step
+        ok = mbar_wait_warp<true>(B_(7), g & 1, abort_flag, p.err, 0x4500u);     // P / dS written
+        if (!ok) break;
+        if (it == 0 && j > 0) {              // the previous item's dV / dK have been read out
+          ok = mbar_wait_warp<true>(B_(13), (j - 1) & 1, abort_flag, p.err, 0x4a00u);
+          if (!ok) break;
+        }
         tcgen05_fence_after();
+        // K = 128 query rows, 16 at a time: every operand is MN-major here (P^T, dS^T with their
+        // two 64-key blocks a tile apart; dO, Q with their 8-row groups 1024 bytes apart)
         const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
-        umma_f16_chain<4>(tS, q_lo + so, 2, k_lo, 2, d_hi, idesc_s, 0u);
-        umma_f16_chain<4>(tdP, do_lo + so, 2, v_lo, 2, d_hi, idesc_s, 0u);
-        umma_commit(B_(5));
-        if (it_a == ni_a - 1) umma_commit(B_(12));    // the item's K / V may be replaced
-        ++g_a;
-        if (++it_a == ni_a) {
-          item_a = snake_item(++j_a, G, (int)blockIdx.x);
-          it_a = 0;
-          ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
-        }
-        return true;
-      };
-      bool ok = issue_sdp();
-      int g = 0, j = 0;
-      for (;; ++j) {
-        const int item = snake_item(j, G, (int)blockIdx.x);
-        if (item >= n_items || !ok) break;
-        const int ni = p.nqt - item / HB;
-        for (int it = 0; it < ni; ++it, ++g) {
-          // the next step's S / dP go first (also when that means waiting for a new item's
-          // operands: issuing dV / dK first measured slower), so the tensor core is busy while
-          // the softmax warps turn S, dP into P, dS
-          ok = issue_sdp();
-          if (!ok) break;
-          const int s = g % KV_STAGES;         // Q / dO stage of this step
-          ok = mbar_wait<true>(B_(7), g & 1, abort_flag, p.err, 0x4500u);     // P / dS written
-          if (!ok) break;
-          if (it == 0 && j > 0) {              // the previous item's dV / dK have been read out
-            ok = mbar_wait<true>(B_(13), (j - 1) & 1, abort_flag, p.err, 0x4a00u);
-            if (!ok) break;
-          }
-          tcgen05_fence_after();
-          // K = 128 query rows, 16 at a time: every operand is MN-major here (P^T, dS^T with their
-          // two 64-key blocks a tile apart; dO, Q with their 8-row groups 1024 bytes apart)
-          const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
-          umma_f16_chain<8>(tdV, pt_lo, 128, dom_lo + so, 128, d_hi, idesc_g, it ? 1u : 0u);
-          umma_f16_chain<8>(tdK, dst_lo, 128, qm_lo + so, 128, d_hi, idesc_g, it ? 1u : 0u);
-          umma_commit(B_(KV_QD_EMPTY + s));   // Q / dO stage free
-          umma_commit(B_(8));                 // P / dS may be overwritten
-          if (it == ni - 1) umma_commit(B_(9));
-        }
+        umma_f16_chain<8>(tdV, pt_lo, 128, dom_lo + so, 128, d_hi, idesc_g, it ? 1u : 0u);
+        umma_f16_chain<8>(tdK, dst_lo, 128, qm_lo + so, 128, d_hi, idesc_g, it ? 1u : 0u);
+        umma_commit_one(B_(KV_QD_EMPTY + s));   // Q / dO stage free
+        umma_commit_one(B_(8));                 // P / dS may be overwritten
+        if (it == ni - 1) umma_commit_one(B_(9));
       }
     }
   } else {
@@ -930,7 +936,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       const int kt = item / HB, hb = item % HB;
       const int h = hb % p.H, b = hb / p.H;
       const int row0 = b * p.T, k0 = kt * FA_T;
-      if (!mbar_wait_warp<true>(B_(9), jj & 1, abort_flag, p.err, 0x4800u)) return false;
+      if (!mbar_wait_warp<SM_SPIN>(B_(9), jj & 1, abort_flag, p.err, 0x4800u)) return false;
       tcgen05_fence_after();
       const int key = k0 + r;     // accumulator rows are keys here
       // parts 0, 1 store the two 32-column halves of dV (slice 2 of dqkv), parts 2, 3 those of
@@ -1019,7 +1025,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
         const int st = st_n;
         if (it + 1 < ni) row_stat(qi + FA_T, lse_n, dl_n, st_n);
         const bool need_mask = (qt == kt) || (p.seg != nullptr);
-        ok = mbar_wait_warp<true>(B_(5), g & 1, abort_flag, p.err, 0x4600u);
+        ok = mbar_wait_warp<SM_SPIN>(B_(5), g & 1, abort_flag, p.err, 0x4600u);
         if (!ok) break;
         tcgen05_fence_after();
         uint32_t rs[32], rdp[32];
@@ -1035,7 +1041,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
         uint4 hp[4], hd[4];
         if (need_mask) bwd_chunk_regs<true>(rs, rdp, part, k0, qi, st, p.cscale, p.scale, nlse, dsc, hp, hd);
         else bwd_chunk_regs<false>(rs, rdp, part, k0, qi, st, p.cscale, p.scale, nlse, dsc, hp, hd);
-        ok = mbar_wait_warp<true>(B_(8), (g & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // dV / dK of step g - 1 done
+        ok = mbar_wait_warp<SM_SPIN>(B_(8), (g & 1) ^ 1u, abort_flag, p.err, 0x4700u);   // dV / dK of step g - 1 done
         if (!ok) break;
         uint8_t* sp = gbase + KV_P;
         uint8_t* sds = gbase + KV_DS;
@@ -1071,20 +1077,49 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
 // heaviest query tile first, and loops over the key tiles up to the diagonal.  Q / dO are the
 // per-item operands (reloaded once the item's last S / dP have retired: qd_free), K / V the
 // per-step ones, in a ring of three stages: a stage is read by S / dP of its step and again by
-// dQ of the same step a softmax later, so with two stages the load of step g + 1 had to wait for
-// dQ of step g - 1 and the chain dQ -> load -> S / dP set the pace (2.2 us per step measured on
-// the dK / dV kernel, which has no room for a third stage, against 1.1 us of tensor work here).
-// TMEM: S [0,128) dP [128,256) dQ [256,320).
+// dQ of the same step a softmax later.
+// dS never passes through shared memory: the softmax warps write it (fp16 pairs) into one of
+// two areas of tensor memory with tcgen05.st, and dQ += dS K reads it there as the A operand.
+// What paces a step is the warp that issues the MMAs: it shares its scheduler with softmax
+// warps, a wait that is already satisfied costs it about 180 cycles and a loop iteration 400,
+// so its loop is kept as short as it can be (one elected lane per instruction, descriptor
+// halves stepped by adds, no wait that another wait implies).  Splitting a step into two
+// half-steps with two softmax groups half a step apart doubled that warp's waits and commits
+// and measured 15 % slower, although the softmax warps then idled less.
+// TMEM columns: S [0, 128) dP [128, 256) dQ [256, 320) dS [320 + 64 b, +64) for buffer b.
 constexpr int DQ_STAGES = 3;
 constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_K = 2 * FA_TILE_BYTES,
-              DQ_V = (2 + DQ_STAGES) * FA_TILE_BYTES, DQ_DS = (2 + 2 * DQ_STAGES) * FA_TILE_BYTES,
-              DQ_DS_STRIDE = 2 * FA_TILE_BYTES,   // dS double-buffered
-              DQ_OUT = (6 + 2 * DQ_STAGES) * FA_TILE_BYTES,    // output staging, one tile
+              DQ_V = (2 + DQ_STAGES) * FA_TILE_BYTES,
+              DQ_OUT = (2 + 2 * DQ_STAGES) * FA_TILE_BYTES,    // output staging, one tile
               DQ_BAR = DQ_OUT + FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
 static_assert(DQ_SMEM <= 227 * 1024, "dQ kernel: shared memory");
 constexpr int DQ_NBAR = 14 + 2 * DQ_STAGES, DQ_KV_FULL = 14, DQ_KV_EMPTY = 14 + DQ_STAGES;
 
-__global__ void __launch_bounds__(BW_THREADS, 1)
+// dS = P (dP - delta) scale for 32 keys of one query row, as fp16 pairs (keys 2i, 2i + 1) in
+// pk[i], ready for tcgen05.st; P is rebuilt from the saved log-sum-exp as in bwd_chunk_regs.
+template <bool MASK>
+__device__ __forceinline__ void bwd_ds_pack(const uint32_t* rs, const uint32_t* rdp, int key0, int qi,
+                                            int st, float cscale, float scale, float nlse, float dsc,
+                                            uint32_t* pk) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float dv[2];
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      const int idx = 2 * i + w;
+      float pr = vkg_ex2(fmaf(__uint_as_float(rs[idx]), cscale, nlse));
+      if (MASK) {
+        const int key = key0 + idx;
+        if (key > qi || key < st) pr = 0.f;
+      }
+      dv[w] = pr * fmaf(__uint_as_float(rdp[idx]), scale, dsc);
+    }
+    const __half2 h = __floats2half2_rn(dv[0], dv[1]);
+    pk[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+}
+
+__global__ void __launch_bounds__(DQ_THREADS, 1)
 attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
                   const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -1099,13 +1134,14 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int HB = p.H * p.B;
   const int n_items = p.nqt * HB, G = (int)gridDim.x;
+  constexpr int OUT_WARPS = DQ_SOFTMAX_WARPS < 8 ? DQ_SOFTMAX_WARPS : 8;   // warps that read dQ out
 
   pdl_trigger();
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tm);
     prefetch_tensormap(&tmdo);
     for (int i = 0; i < DQ_NBAR; ++i)
-      mbar_init(B_(i), (i == 6 || i == 7 || i == 10) ? BW_SOFTMAX_WARPS : (i == 13 ? 8 : 1));
+      mbar_init(B_(i), (i == 6 || i == 7 || i == 10) ? DQ_SOFTMAX_WARPS : (i == 13 ? OUT_WARPS : 1));
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1116,7 +1152,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   tcgen05_fence_after();
   pdl_wait();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
+  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256, tdS = tmem + 320;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1148,91 +1184,97 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
-      const uint32_t idesc_q = make_idesc(0, 0, 1, FA_HD);   // dS (K-major) . K (MN-major), N = 64
-      const uint32_t d_hi = smem_desc_hi(1024);      // descriptor halves (tcgen05.cuh)
-      const uint32_t q_lo = smem_desc_lo(base + DQ_Q, 16), do_lo = smem_desc_lo(base + DQ_DO, 16);
-      const uint32_t k_lo = smem_desc_lo(base + DQ_K, 16), v_lo = smem_desc_lo(base + DQ_V, 16);
-      const uint32_t km_lo = smem_desc_lo(base + DQ_K, 8192), ds_lo = smem_desc_lo(base + DQ_DS, 16);
-      int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, g_a = 0;
-      int ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;      // key tiles of the item: qt + 1
-      auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of step g_a
-        if (item_a >= n_items) return true;
-        if (it_a == 0 && !mbar_wait<true>(B_(0), j_a & 1, abort_flag, p.err, 0x5200u)) return false;
-        const int s = g_a % DQ_STAGES;
-        if (!(mbar_wait<true>(B_(DQ_KV_FULL + s), (uint32_t)(g_a / DQ_STAGES) & 1u, abort_flag, p.err,
-                              0x5300u + s) &&
-              mbar_wait<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x5400u)))
-          return false;
+    // the whole warp runs this converged; one elected lane issues each tcgen05 instruction
+    const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
+    const uint32_t idesc_q = make_idesc(0, 0, 1, FA_HD);   // dS (tensor memory) . K (MN-major), N = 64
+    const uint32_t d_hi = smem_desc_hi(1024);      // descriptor halves (tcgen05.cuh)
+    const uint32_t q_lo = smem_desc_lo(base + DQ_Q, 16), do_lo = smem_desc_lo(base + DQ_DO, 16);
+    const uint32_t k_lo = smem_desc_lo(base + DQ_K, 16), v_lo = smem_desc_lo(base + DQ_V, 16);
+    const uint32_t km_lo = smem_desc_lo(base + DQ_K, 8192);
+    // cursor of the S / dP issue: one step ahead of the dQ loop below, also across an item
+    // boundary; s_a / ph_a: ring stage and its phase
+    int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, s_a = 0;
+    uint32_t ph_a = 0, par_a = 0;
+    int ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;      // key tiles of the item: qt + 1
+    auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of the cursor's step
+      if (item_a >= n_items) return true;
+      if (it_a == 0 && !mbar_wait_warp<true>(B_(0), j_a & 1, abort_flag, p.err, 0x5200u)) return false;
+      if (!(mbar_wait_warp<true>(B_(DQ_KV_FULL + s_a), ph_a, abort_flag, p.err, 0x5300u + s_a) &&
+            mbar_wait_warp<true>(B_(6), par_a ^ 1u, abort_flag, p.err, 0x5400u)))
+        return false;
+      tcgen05_fence_after();
+      const uint32_t so = (uint32_t)s_a * (FA_TILE_BYTES >> 4);
+      umma_f16_chain<4>(tS, q_lo, 2, k_lo + so, 2, d_hi, idesc_s, 0u);
+      umma_f16_chain<4>(tdP, do_lo, 2, v_lo + so, 2, d_hi, idesc_s, 0u);
+      umma_commit_one(B_(5));
+      if (it_a == ni_a - 1) umma_commit_one(B_(12));    // the item's Q / dO may be replaced
+      par_a ^= 1u;
+      if (++s_a == DQ_STAGES) {
+        s_a = 0;
+        ph_a ^= 1u;
+      }
+      if (++it_a == ni_a) {
+        item_a = snake_item(++j_a, G, (int)blockIdx.x);
+        it_a = 0;
+        ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
+      }
+      return true;
+    };
+    bool ok = issue_sdp();
+    int g = 0, j = 0, s = 0;
+    for (;; ++j) {
+      const int item = snake_item(j, G, (int)blockIdx.x);
+      if (item >= n_items || !ok) break;
+      const int nj = p.nqt - item / HB;
+      for (int kt = 0; kt < nj; ++kt, ++g) {
+        ok = issue_sdp();
+        if (!ok) break;
+        const int pb = g & 1;
+        ok = mbar_wait_warp<true>(B_(7 + 3 * pb), (g >> 1) & 1, abort_flag, p.err, 0x5500u);
+        if (!ok) break;
+        if (kt == 0 && j > 0) {
+          ok = mbar_wait_warp<true>(B_(13), (j - 1) & 1, abort_flag, p.err, 0x5a00u);
+          if (!ok) break;
+        }
         tcgen05_fence_after();
-        const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
-        umma_f16_chain<4>(tS, q_lo, 2, k_lo + so, 2, d_hi, idesc_s, 0u);
-        umma_f16_chain<4>(tdP, do_lo, 2, v_lo + so, 2, d_hi, idesc_s, 0u);
-        umma_commit(B_(5));
-        if (it_a == ni_a - 1) umma_commit(B_(12));    // the item's Q / dO may be replaced
-        ++g_a;
-        if (++it_a == ni_a) {
-          item_a = snake_item(++j_a, G, (int)blockIdx.x);
-          it_a = 0;
-          ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
-        }
-        return true;
-      };
-      bool ok = issue_sdp();
-      int g = 0, j = 0;
-      for (;; ++j) {
-        const int item = snake_item(j, G, (int)blockIdx.x);
-        if (item >= n_items || !ok) break;
-        const int nj = p.nqt - item / HB;
-        for (int kt = 0; kt < nj; ++kt, ++g) {
-          ok = issue_sdp();
-          if (!ok) break;
-          const int s = g % DQ_STAGES, pb = g & 1;
-          ok = mbar_wait<true>(B_(7 + 3 * pb), (g >> 1) & 1, abort_flag, p.err, 0x5500u);
-          if (!ok) break;
-          if (kt == 0 && j > 0) {
-            ok = mbar_wait<true>(B_(13), (j - 1) & 1, abort_flag, p.err, 0x5a00u);
-            if (!ok) break;
-          }
-          tcgen05_fence_after();
-          // K = 128 keys: dS in two K-major 64-key blocks, K MN-major
-          const uint32_t ds = ds_lo + (uint32_t)pb * (DQ_DS_STRIDE >> 4);
-          const uint32_t km = km_lo + (uint32_t)s * (FA_TILE_BYTES >> 4);
-          umma_f16_chain<4>(tdQ, ds, 2, km, 128, d_hi, idesc_q, kt ? 1u : 0u);
-          umma_f16_chain<4>(tdQ, ds + (FA_TILE_BYTES >> 4), 2, km + 4 * 128, 128, d_hi, idesc_q, 1u);
-          umma_commit(B_(DQ_KV_EMPTY + s));   // K / V stage free
-          umma_commit(B_(8 + 3 * pb));   // this dS buffer free
-          if (kt == nj - 1) umma_commit(B_(9));
-        }
+        // K = 128 keys: dS from tensor memory (8 columns per step), K MN-major
+        umma_f16_ts_chain<8>(tdQ, tdS + 64 * pb, km_lo + (uint32_t)s * (FA_TILE_BYTES >> 4), 128, d_hi, idesc_q,
+                             kt ? 1u : 0u);
+        umma_commit_one(B_(DQ_KV_EMPTY + s));   // K / V stage free
+        umma_commit_one(B_(8 + 3 * pb));        // this dS area free
+        if (kt == nj - 1) umma_commit_one(B_(9));
+        if (++s == DQ_STAGES) s = 0;
       }
     }
   } else {
-    const int part = (warp - 2) >> 2;            // which 32 of a key tile's 128 keys
-    const int half = part;                       // parts 0 and 1 also read the 64 dQ columns out
+    constexpr int PARTS = DQ_SOFTMAX_WARPS / 4;  // warps per TMEM lane quarter
+    constexpr int CPT = FA_T / PARTS;            // keys of a row per thread: 32 or 64
+    const int part = (warp - 2) >> 2;            // which CPT of a key tile's 128 keys
     const int r = (warp & 3) * 32 + lane;
     const uint32_t t_lane = ((uint32_t)((warp & 3) * 32)) << 16;
     bool ok = true;
     // dQ of a finished item, read out after the NEXT item's first step (see the dK / dV kernel)
+    // by the first OUT_WARPS warps, 64 / (OUT_WARPS / 4) columns each
+    constexpr int OC = FA_HD / (OUT_WARPS / 4);
     int pend_item = -1, pend_j = 0;
     auto store_item = [&](int item, int jj) -> bool {
       const int qt = p.nqt - 1 - item / HB, hb = item % HB;
       const int h = hb % p.H, b = hb / p.H;
       const int row0 = b * p.T, qi = qt * FA_T + r;
       const bool q_ok = qi < p.T;
-      if (!mbar_wait_warp<true>(B_(9), jj & 1, abort_flag, p.err, 0x5800u)) return false;
+      if (!mbar_wait_warp<SM_SPIN>(B_(9), jj & 1, abort_flag, p.err, 0x5800u)) return false;
       tcgen05_fence_after();
-      uint32_t rr[32];                             // this half's 32 of the 64 dQ columns
-      tmem_ld16(tdQ + t_lane + half * 32, rr);
-      tmem_ld16(tdQ + t_lane + half * 32 + 16, rr + 16);
+      uint32_t rr[OC];
+#pragma unroll
+      for (int c = 0; c < OC / 16; ++c) tmem_ld16(tdQ + t_lane + part * OC + c * 16, rr + c * 16);
       tmem_wait_ld();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(B_(13));           // dQ may be overwritten
       {
-        uint4 hv[4];
+        uint4 hv[OC / 8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < OC / 8; ++u) {
           __half2 h2[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
@@ -1241,18 +1283,18 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
           hv[u] = *reinterpret_cast<uint4*>(h2);
         }
         const int q_w = qt * FA_T + (warp & 3) * 32;   // first query row of this warp's 32
-        __half* dst = p.dqkv + (size_t)(row0 + q_w) * 3 * p.D + h * FA_HD + half * 32;
-        warp_store_rows<4>(hv, gbase + DQ_OUT + (warp - 2) * 2048, lane, reinterpret_cast<uint8_t*>(dst),
-                           (size_t)3 * p.D * 2, p.T - q_w);
+        __half* dst = p.dqkv + (size_t)(row0 + q_w) * 3 * p.D + h * FA_HD + part * OC;
+        warp_store_rows<OC / 8>(hv, gbase + DQ_OUT + (warp - 2) * (OC * 64), lane,
+                                reinterpret_cast<uint8_t*>(dst), (size_t)3 * p.D * 2, p.T - q_w);
       }
       if (p.colsum) {
-        float val[32];
+        float val[OC];
 #pragma unroll
-        for (int c = 0; c < 32; ++c)
+        for (int c = 0; c < OC; ++c)
           val[c] = q_ok ? __half2float(__float2half_rn(__uint_as_float(rr[c]))) : 0.f;
         float* dst = p.colsum + ((size_t)(b * p.nqt + qt) * 4 + (warp & 3)) * 3 * p.D + h * FA_HD +
-                     half * 32;
-        warp_col_sums<32>(val, lane, dst);
+                     part * OC;
+        warp_col_sums<OC>(val, lane, dst);
       }
       return true;
     };
@@ -1285,38 +1327,49 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       }
       for (int kt = 0; kt < nj && ok; ++kt, ++g) {
         const bool need_mask = (kt == qt) || (p.seg != nullptr);
-        ok = mbar_wait_warp<true>(B_(5), g & 1, abort_flag, p.err, 0x5600u);
+        ok = mbar_wait_warp<SM_SPIN>(B_(5), g & 1, abort_flag, p.err, 0x5600u);
         if (!ok) break;
         tcgen05_fence_after();
-        uint32_t rs[32], rdp[32];
-        tmem_ld16(tS + t_lane + part * 32, rs);
-        tmem_ld16(tS + t_lane + part * 32 + 16, rs + 16);
-        tmem_ld16(tdP + t_lane + part * 32, rdp);
-        tmem_ld16(tdP + t_lane + part * 32 + 16, rdp + 16);
+        uint32_t rs[CPT], rdp[CPT];
+#pragma unroll
+        for (int c = 0; c < CPT / 16; ++c) tmem_ld16(tS + t_lane + part * CPT + c * 16, rs + c * 16);
+#pragma unroll
+        for (int c = 0; c < CPT / 16; ++c) tmem_ld16(tdP + t_lane + part * CPT + c * 16, rdp + c * 16);
         tmem_wait_ld();
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(B_(6));
+        // dS as fp16 pairs, overwriting the scores they came from
+        const int key0 = kt * FA_T + part * CPT;
+#pragma unroll
+        for (int c = 0; c < CPT / 32; ++c) {
+          if (need_mask)
+            bwd_ds_pack<true>(rs + 32 * c, rdp + 32 * c, key0 + 32 * c, qi, st, p.cscale, p.scale, nlse, dsc,
+                              rs + 16 * c);
+          else
+            bwd_ds_pack<false>(rs + 32 * c, rdp + 32 * c, 0, 0, 0, p.cscale, p.scale, nlse, dsc, rs + 16 * c);
+        }
         const int pb = g & 1;
-        ok = mbar_wait_warp<true>(B_(8 + 3 * pb), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
+        // dQ of step g - 2 has read this dS area
+        ok = mbar_wait_warp<SM_SPIN>(B_(8 + 3 * pb), ((g >> 1) & 1) ^ 1u, abort_flag, p.err, 0x5700u);
         if (!ok) break;
-        uint8_t* sds = gbase + DQ_DS + pb * DQ_DS_STRIDE;
-        if (need_mask)
-          bwd_chunk<true>(rs, rdp, part, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
-        else
-          bwd_chunk<false>(rs, rdp, part, r, kt * FA_T, qi, st, p.cscale, p.scale, nlse, dsc, nullptr, sds);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tcgen05_fence_after();
+#pragma unroll
+        for (int c = 0; c < CPT / 32; ++c)
+          tmem_st16(tdS + 64 * pb + t_lane + part * (CPT / 2) + c * 16, rs + 16 * c);
+        tmem_wait_st();
+        tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(B_(7 + 3 * pb));
         if (pend_item >= 0) {
-          if (part < 2) ok = store_item(pend_item, pend_j);
+          if (warp - 2 < OUT_WARPS) ok = store_item(pend_item, pend_j);
           pend_item = -1;
         }
       }
       pend_item = item;       // read this item's dQ out after the next item's first step
       pend_j = j;
     }
-    if (ok && pend_item >= 0 && part < 2) ok = store_item(pend_item, pend_j);
+    if (ok && pend_item >= 0 && warp - 2 < OUT_WARPS) ok = store_item(pend_item, pend_j);
   }
   __syncwarp();
   tcgen05_fence_before();
@@ -1439,7 +1492,7 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
   const unsigned ctas = (unsigned)(n_items < sms ? n_items : sms);
   VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_kv_kernel, dim3(ctas), dim3(BW_THREADS), KV_SMEM, 1, tm, tmdo, p));
   if (vkg_check_launch("attn_bwd_kv_kernel")) return 1;
-  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_q_kernel, dim3(ctas), dim3(BW_THREADS), DQ_SMEM, 1, tm, tmdo, p));
+  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_q_kernel, dim3(ctas), dim3(DQ_THREADS), DQ_SMEM, 1, tm, tmdo, p));
   if (vkg_check_launch("attn_bwd_q_kernel")) return 1;
   if (dbias)
     return vkg_launch_col_sum_final(dev, dbias_scratch, dbias, 3 * D, B * p.nqt * 4, 0);

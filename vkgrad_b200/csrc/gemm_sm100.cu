@@ -6,7 +6,7 @@
 //
 // One persistent CTA per SM, 576 threads:
 //   warp 0       TMA producer (one lane)
-//   warp 1       TMEM allocation + MMA issue (one lane)
+//   warp 1       TMEM allocation + MMA issue (converged, one elected lane per instruction)
 //   warps 2..17  epilogue; warp w reads TMEM lanes 32*(w%4) .. +31 and takes every
 //                fourth 16-column chunk.  The epilogue is instruction-issue / latency
 //                bound, so it gets four warps per scheduler and a compile-time mask.
@@ -393,13 +393,14 @@ __device__ __forceinline__ bool produce_unit(const CtaCtx& cx, const GemmParams&
   return true;
 }
 
-// MMA issue (one lane): accumulate work unit t into one of the two TMEM accumulators.
+// MMA issue (the whole warp, converged; one elected lane issues each instruction): accumulate
+// work unit t into one of the two TMEM accumulators.
 __device__ __forceinline__ bool mma_unit(const CtaCtx& cx, const GemmParams& p, int t, int& stage,
                                          uint32_t& phase, int& acc, uint32_t& acc_phase) {
   int kb0, nkb;
   kb_range(p, tile_coord(p, t), kb0, nkb);
   if (nkb <= 0) return true;   // skipped tile: no accumulator, no epilogue
-  if (!mbar_wait(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x200u + acc)) return false;
+  if (!mbar_wait_warp(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x200u + acc)) return false;
   tcgen05_fence_after();
   const uint32_t d_tmem = cx.tmem_base + (uint32_t)(acc * ACC_COLS);
   // Descriptor halves of ring stage 0; a K step of 16 elements is 32 bytes further along the
@@ -411,20 +412,21 @@ __device__ __forceinline__ bool mma_unit(const CtaCtx& cx, const GemmParams& p, 
   const uint32_t a_step = p.a_mn ? 128u : 2u, b_step = p.b_mn ? 128u : 2u;
   const uint32_t stage16 = cx.stage_bytes >> 4;
   for (int kb = 0; kb < nkb; ++kb) {
-    if (!mbar_wait(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x300u + stage)) return false;
+    if (!mbar_wait_warp(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x300u + stage)) return false;
     tcgen05_fence_after();
     const uint32_t a_lo = a_lo0 + (uint32_t)stage * stage16, b_lo = b_lo0 + (uint32_t)stage * stage16;
 #pragma unroll
     for (int k = 0; k < BK / UMMA_K; ++k)
-      umma_f16(d_tmem, smem_desc_pack(a_lo + k * a_step, d_hi), smem_desc_pack(b_lo + k * b_step, d_hi),
-               p.idesc, (kb | k) != 0 ? 1u : 0u);
-    umma_commit(cx.empty0 + 8 * stage);  // frees the stage when these MMAs retire
+      if (elect_one())
+        umma_f16(d_tmem, smem_desc_pack(a_lo + k * a_step, d_hi), smem_desc_pack(b_lo + k * b_step, d_hi),
+                 p.idesc, (kb | k) != 0 ? 1u : 0u);
+    umma_commit_one(cx.empty0 + 8 * stage);  // frees the stage when these MMAs retire
     if (++stage == cx.n_stages) {
       stage = 0;
       phase ^= 1u;
     }
   }
-  umma_commit(cx.tfull0 + 8 * acc);  // accumulator complete -> epilogue
+  umma_commit_one(cx.tfull0 + 8 * acc);  // accumulator complete -> epilogue
   acc ^= 1;
   if (acc == 0) acc_phase ^= 1u;
   return true;
@@ -587,12 +589,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!produce_unit(cx, p, &tmA, &tmB, t, stage, phase)) break;
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x)
-        if (!mma_unit(cx, p, t, stage, phase, acc, acc_phase)) break;
-    }
+    int stage = 0, acc = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x)
+      if (!mma_unit(cx, p, t, stage, phase, acc, acc_phase)) break;
   } else {
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -653,14 +653,12 @@ gemm_group_kernel(const GroupEntry* __restrict__ table, int n_problems, int tota
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
-      for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
-        const int pi = group_find(first, n_problems, u);
-        const GemmParams p = table[pi].p;
-        if (!mma_unit(cx, p, u - first[pi], stage, phase, acc, acc_phase)) break;
-      }
+    int stage = 0, acc = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+      const int pi = group_find(first, n_problems, u);
+      const GemmParams p = table[pi].p;
+      if (!mma_unit(cx, p, u - first[pi], stage, phase, acc, acc_phase)) break;
     }
   } else {
     int acc = 0;
@@ -793,13 +791,13 @@ __device__ __forceinline__ bool pair_produce_unit(const CtaCtx& cx, const GemmPa
   return true;
 }
 
-// MMA issue for the pair (one lane of the even-ranked CTA).
+// MMA issue for the pair (a converged warp of the even-ranked CTA).
 __device__ __forceinline__ bool pair_mma_unit(const CtaCtx& cx, const GemmParams& p, int t, int& stage,
                                               uint32_t& phase, int& acc, uint32_t& acc_phase) {
   int kb0, nkb;
   kb_range(p, tile_coord(p, t, 2 * BM, 0), kb0, nkb);
   if (nkb <= 0) return true;
-  if (!mbar_wait(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x600u + acc)) return false;
+  if (!mbar_wait_warp(cx.tempty0 + 8 * acc, acc_phase ^ 1u, cx.abort_flag, p.err, 0x600u + acc)) return false;
   tcgen05_fence_after();
   const uint32_t d_tmem = cx.tmem_base + (uint32_t)(acc * ACC_COLS);
   const uint32_t d_hi = smem_desc_hi(1024);       // descriptor halves as in mma_unit
@@ -807,21 +805,22 @@ __device__ __forceinline__ bool pair_mma_unit(const CtaCtx& cx, const GemmParams
   const uint32_t b_lo0 = smem_desc_lo(cx.base + A_STAGE_BYTES, p.b_mn ? 8192 : 16);
   const uint32_t a_step = p.a_mn ? 128u : 2u, b_step = p.b_mn ? 128u : 2u;
   for (int kb = 0; kb < nkb; ++kb) {
-    if (!mbar_wait(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x700u + stage)) return false;
+    if (!mbar_wait_warp(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x700u + stage)) return false;
     tcgen05_fence_after();
     const uint32_t a_lo = a_lo0 + (uint32_t)stage * (PAIR_STAGE_BYTES >> 4);
     const uint32_t b_lo = b_lo0 + (uint32_t)stage * (PAIR_STAGE_BYTES >> 4);
 #pragma unroll
     for (int k = 0; k < BK / UMMA_K; ++k)
-      umma2_f16(d_tmem, smem_desc_pack(a_lo + k * a_step, d_hi), smem_desc_pack(b_lo + k * b_step, d_hi),
-                p.idesc, (kb | k) != 0 ? 1u : 0u);
-    umma2_commit(cx.empty0 + 8 * stage);
+      if (elect_one())
+        umma2_f16(d_tmem, smem_desc_pack(a_lo + k * a_step, d_hi), smem_desc_pack(b_lo + k * b_step, d_hi),
+                  p.idesc, (kb | k) != 0 ? 1u : 0u);
+    if (elect_one()) umma2_commit(cx.empty0 + 8 * stage);
     if (++stage == PAIR_STAGES) {
       stage = 0;
       phase ^= 1u;
     }
   }
-  umma2_commit(cx.tfull0 + 8 * acc);
+  if (elect_one()) umma2_commit(cx.tfull0 + 8 * acc);
   acc ^= 1;
   if (acc == 0) acc_phase ^= 1u;
   return true;
@@ -920,7 +919,7 @@ gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         if (!pair_produce_unit(cx, p, &tmA, &tmB, t, rank, stage, phase)) break;
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int t = pair; t < total_tiles; t += n_pairs)
@@ -962,7 +961,7 @@ gemm_group_pair_kernel(const GroupEntry* __restrict__ table, int n_problems, int
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int u = pair; u < total_units; u += n_pairs) {
