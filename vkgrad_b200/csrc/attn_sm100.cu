@@ -41,7 +41,8 @@ constexpr int BW_SOFTMAX_WARPS = 16;   // dK / dV kernel: four warps per TMEM la
 #define VKG_ATTN_DQ_WARPS 16
 #endif
 constexpr int DQ_SOFTMAX_WARPS = VKG_ATTN_DQ_WARPS;   // dQ kernel: 2 or 4 warps per lane quarter
-constexpr int DQ_THREADS = (2 + DQ_SOFTMAX_WARPS) * 32;
+constexpr int DQ_MMA2_WARP = 2 + DQ_SOFTMAX_WARPS;        // the warp that issues dQ += dS K
+constexpr int DQ_THREADS = (3 + DQ_SOFTMAX_WARPS) * 32;
 constexpr int BW_THREADS = (2 + BW_SOFTMAX_WARPS) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 #ifndef VKG_ATTN_SOFTMAX_SPIN
@@ -1184,51 +1185,53 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // the whole warp runs this converged; one elected lane issues each tcgen05 instruction
+    // S = Q K^T and dP = dO V^T of every step.  The whole warp runs this converged; one elected
+    // lane issues each tcgen05 instruction.
     const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);
-    const uint32_t idesc_q = make_idesc(0, 0, 1, FA_HD);   // dS (tensor memory) . K (MN-major), N = 64
     const uint32_t d_hi = smem_desc_hi(1024);      // descriptor halves (tcgen05.cuh)
     const uint32_t q_lo = smem_desc_lo(base + DQ_Q, 16), do_lo = smem_desc_lo(base + DQ_DO, 16);
     const uint32_t k_lo = smem_desc_lo(base + DQ_K, 16), v_lo = smem_desc_lo(base + DQ_V, 16);
-    const uint32_t km_lo = smem_desc_lo(base + DQ_K, 8192);
-    // cursor of the S / dP issue: one step ahead of the dQ loop below, also across an item
-    // boundary; s_a / ph_a: ring stage and its phase
-    int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, s_a = 0;
-    uint32_t ph_a = 0, par_a = 0;
-    int ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;      // key tiles of the item: qt + 1
-    auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of the cursor's step
-      if (item_a >= n_items) return true;
-      if (it_a == 0 && !mbar_wait_warp<true>(B_(0), j_a & 1, abort_flag, p.err, 0x5200u)) return false;
-      if (!(mbar_wait_warp<true>(B_(DQ_KV_FULL + s_a), ph_a, abort_flag, p.err, 0x5300u + s_a) &&
-            mbar_wait_warp<true>(B_(6), par_a ^ 1u, abort_flag, p.err, 0x5400u)))
-        return false;
-      tcgen05_fence_after();
-      const uint32_t so = (uint32_t)s_a * (FA_TILE_BYTES >> 4);
-      umma_f16_chain<4>(tS, q_lo, 2, k_lo + so, 2, d_hi, idesc_s, 0u);
-      umma_f16_chain<4>(tdP, do_lo, 2, v_lo + so, 2, d_hi, idesc_s, 0u);
-      umma_commit_one(B_(5));
-      if (it_a == ni_a - 1) umma_commit_one(B_(12));    // the item's Q / dO may be replaced
-      par_a ^= 1u;
-      if (++s_a == DQ_STAGES) {
-        s_a = 0;
-        ph_a ^= 1u;
-      }
-      if (++it_a == ni_a) {
-        item_a = snake_item(++j_a, G, (int)blockIdx.x);
-        it_a = 0;
-        ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
-      }
-      return true;
-    };
-    bool ok = issue_sdp();
-    int g = 0, j = 0, s = 0;
-    for (;; ++j) {
+    int s = 0;
+    uint32_t ph = 0, par = 0;
+    bool ok = true;
+    for (int j = 0; ok; ++j) {
       const int item = snake_item(j, G, (int)blockIdx.x);
-      if (item >= n_items || !ok) break;
+      if (item >= n_items) break;
+      const int nj = p.nqt - item / HB;               // key tiles of the item: qt + 1
+      ok = mbar_wait_warp<true>(B_(0), j & 1, abort_flag, p.err, 0x5200u);
+      for (int kt = 0; kt < nj && ok; ++kt) {
+        ok = mbar_wait_warp<true>(B_(DQ_KV_FULL + s), ph, abort_flag, p.err, 0x5300u + s) &&
+             mbar_wait_warp<true>(B_(6), par ^ 1u, abort_flag, p.err, 0x5400u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
+        umma_f16_chain<4>(tS, q_lo, 2, k_lo + so, 2, d_hi, idesc_s, 0u);
+        umma_f16_chain<4>(tdP, do_lo, 2, v_lo + so, 2, d_hi, idesc_s, 0u);
+        umma_commit_one(B_(5));
+        if (kt == nj - 1) umma_commit_one(B_(12));    // the item's Q / dO may be replaced
+        par ^= 1u;
+        if (++s == DQ_STAGES) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+  } else if (warp == DQ_MMA2_WARP) {
+    // dQ += dS K of every step, issued by a warp of its own: the instruction stream of one warp
+    // for both (waits, 16 instructions, commits, about 1900 cycles per step next to busy softmax
+    // warps) was what paced the kernel.  Its commits cover this warp's instructions only; a
+    // K / V stage is free when dQ of its step has retired, because the S / dP that read it
+    // retired before the softmax warps could produce the dS this dQ waited for.
+    const uint32_t idesc_q = make_idesc(0, 0, 1, FA_HD);   // dS (tensor memory) . K (MN-major), N = 64
+    const uint32_t d_hi = smem_desc_hi(1024);
+    const uint32_t km_lo = smem_desc_lo(base + DQ_K, 8192);
+    int g = 0, s = 0;
+    bool ok = true;
+    for (int j = 0; ok; ++j) {
+      const int item = snake_item(j, G, (int)blockIdx.x);
+      if (item >= n_items) break;
       const int nj = p.nqt - item / HB;
       for (int kt = 0; kt < nj; ++kt, ++g) {
-        ok = issue_sdp();
-        if (!ok) break;
         const int pb = g & 1;
         ok = mbar_wait_warp<true>(B_(7 + 3 * pb), (g >> 1) & 1, abort_flag, p.err, 0x5500u);
         if (!ok) break;
