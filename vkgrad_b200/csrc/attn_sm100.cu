@@ -58,7 +58,8 @@ struct AttnParams {
   const uint32_t* seg;     // optional packed-sample starts (b*T + t)
   __half* out;             // forward: O, head-merged (rows, D)
   float* lse2;             // (B*H, T): row log2-sum-exp of the scaled scores
-  const float* delta;      // backward: rowsum(dO * O), (B*H, T)
+  const float* delta;      // backward: rowsum(dO * O), (B*H, T); the dQ kernel writes it (delta_out),
+  float* delta_out;        // the dK / dV kernel, launched after it, reads it
   __half* dqkv;            // backward: (rows, 3D)
   float* colsum;           // backward, optional: [B * nqt * 4][3D] partial column sums of dqkv
   uint32_t* err;
@@ -621,41 +622,6 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
 
 // ---- backward --------------------------------------------------------------------------
 //
-// delta[row, h] = sum_d dO * O (equals sum_j dP_ij P_ij of tkernels.py:176-179).
-__global__ void attn_delta_kernel(const __half* __restrict__ dout, const __half* __restrict__ out,
-                                  float* __restrict__ delta, int B, int T, int H) {
-  pdl_trigger();
-  pdl_wait();
-  // eight lanes per (row, head): one 16-byte load of dO and of O each
-  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;   // (row, h)
-  const int sub = threadIdx.x & 7;
-  const bool live = item < (long long)B * T * H;
-  float s = 0.f;
-  int h = 0;
-  long long row = 0;
-  if (live) {
-    h = (int)(item % H);
-    row = item / H;
-    const size_t off = (size_t)row * H * FA_HD + h * FA_HD + sub * 8;
-    const uint4 a = *reinterpret_cast<const uint4*>(dout + off);
-    const uint4 o = *reinterpret_cast<const uint4*>(out + off);
-    const __half2* ah = reinterpret_cast<const __half2*>(&a);
-    const __half2* oh = reinterpret_cast<const __half2*>(&o);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = __half22float2(ah[i]), y = __half22float2(oh[i]);
-      s += x.x * y.x + x.y * y.y;
-    }
-  }
-  s += __shfl_xor_sync(0xffffffffu, s, 1);
-  s += __shfl_xor_sync(0xffffffffu, s, 2);
-  s += __shfl_xor_sync(0xffffffffu, s, 4);
-  if (live && sub == 0) {
-    const int b = (int)(row / T), t = (int)(row % T);
-    delta[(size_t)(b * H + h) * T + t] = s;
-  }
-}
-
 // One 32-key chunk of a (query row, key tile) pair: rebuild P from S and the saved
 // log-sum-exp, form dS = P (dP - delta) scale, and write both (fp16) into the swizzled
 // [query row][key] layout.  `sp` may be null.  nlse = -lse2 (or -inf for a row past the
@@ -1087,11 +1053,15 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
 // halves stepped by adds, no wait that another wait implies).  Splitting a step into two
 // half-steps with two softmax groups half a step apart doubled that warp's waits and commits
 // and measured 15 % slower, although the softmax warps then idled less.
+// This kernel also forms delta = rowsum(dO * O) (tkernels.py:176-179 computes the same number
+// as sum_j dP_ij P_ij): the O tile of an item is loaded beside Q and dO, every softmax thread
+// sums its row's 64 products from shared memory at the start of the item, and the rows are
+// written out for the dK / dV kernel, which is launched after this one.
 // TMEM columns: S [0, 128) dP [128, 256) dQ [256, 320) dS [320 + 64 b, +64) for buffer b.
 constexpr int DQ_STAGES = 3;
-constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_K = 2 * FA_TILE_BYTES,
-              DQ_V = (2 + DQ_STAGES) * FA_TILE_BYTES,
-              DQ_OUT = (2 + 2 * DQ_STAGES) * FA_TILE_BYTES,    // output staging, one tile
+constexpr int DQ_Q = 0, DQ_DO = FA_TILE_BYTES, DQ_O = 2 * FA_TILE_BYTES, DQ_K = 3 * FA_TILE_BYTES,
+              DQ_V = (3 + DQ_STAGES) * FA_TILE_BYTES,
+              DQ_OUT = (3 + 2 * DQ_STAGES) * FA_TILE_BYTES,    // output staging, one tile
               DQ_BAR = DQ_OUT + FA_TILE_BYTES, DQ_SMEM = DQ_BAR + 256 + 1024;
 static_assert(DQ_SMEM <= 227 * 1024, "dQ kernel: shared memory");
 constexpr int DQ_NBAR = 14 + 2 * DQ_STAGES, DQ_KV_FULL = 14, DQ_KV_EMPTY = 14 + DQ_STAGES;
@@ -1122,13 +1092,14 @@ __device__ __forceinline__ void bwd_ds_pack(const uint32_t* rs, const uint32_t* 
 
 __global__ void __launch_bounds__(DQ_THREADS, 1)
 attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmdo,
-                  const AttnParams p) {
+                  const __grid_constant__ CUtensorMap tmo, const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar = base + DQ_BAR;
-  // 0 qd_full, 5 sdp_full, 6 sdp_free, 7/10 ds_full[2], 8/11 ds_free[2], 9 out_full, 12 qd_free,
-  // 13 acc_free, 14.. kv_full[stage], then kv_empty[stage]
+  // 0 qd_full, 1 od_free (delta formed from the dO / O tiles), 5 sdp_full, 6 sdp_free,
+  // 7/10 ds_full[2], 8/11 ds_free[2], 9 out_full, 12 qd_free, 13 acc_free, 14.. kv_full[stage],
+  // then kv_empty[stage]
   auto B_ = [bar](int i) { return bar + 8u * i; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 192);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + DQ_BAR + 200);
@@ -1141,8 +1112,9 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tm);
     prefetch_tensormap(&tmdo);
+    prefetch_tensormap(&tmo);
     for (int i = 0; i < DQ_NBAR; ++i)
-      mbar_init(B_(i), (i == 6 || i == 7 || i == 10) ? DQ_SOFTMAX_WARPS : (i == 13 ? OUT_WARPS : 1));
+      mbar_init(B_(i), (i == 1 || i == 6 || i == 7 || i == 10) ? DQ_SOFTMAX_WARPS : (i == 13 ? OUT_WARPS : 1));
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1165,10 +1137,15 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
         const int qt = p.nqt - 1 - item / HB, hb = item % HB;
         const int h = hb % p.H, b = hb / p.H;
         const int row0 = b * p.T, q0 = qt * FA_T, nj = qt + 1;
-        if (j > 0 && !mbar_wait<true>(B_(12), (j - 1) & 1, abort_flag, p.err, 0x5900u)) break;
-        mbar_expect_tx(B_(0), 2 * FA_TILE_BYTES);
+        // the previous item's Q / dO have been read by its last S / dP, its dO / O by every
+        // softmax warp
+        if (j > 0 && !(mbar_wait<true>(B_(12), (j - 1) & 1, abort_flag, p.err, 0x5900u) &&
+                       mbar_wait<true>(B_(1), (j - 1) & 1, abort_flag, p.err, 0x5b00u)))
+          break;
+        mbar_expect_tx(B_(0), 3 * FA_TILE_BYTES);
         tma_load_2d(base + DQ_Q, &tm, B_(0), h * FA_HD, row0 + q0);
         tma_load_2d(base + DQ_DO, &tmdo, B_(0), h * FA_HD, row0 + q0);
+        tma_load_2d(base + DQ_O, &tmo, B_(0), h * FA_HD, row0 + q0);
         for (int kt = 0; kt < nj; ++kt, ++g) {
           const int s = g % DQ_STAGES;
           const uint32_t ph = (uint32_t)(g / DQ_STAGES) & 1u;
@@ -1302,18 +1279,17 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       return true;
     };
     // statistics of this thread's query row in an item
-    auto item_stat = [&](int item, float& lse, float& dl, int& st) {
+    auto item_stat = [&](int item, float& lse, int& st) {
       const int qt = p.nqt - 1 - item / HB, hb = item % HB;
       const int qi = qt * FA_T + r;
       const bool q_ok = qi < p.T;
       const size_t i = (size_t)((hb / p.H) * p.H + hb % p.H) * p.T + (q_ok ? qi : 0);
       lse = p.lse2[i];
-      dl = p.delta[i];
       st = (p.seg && q_ok) ? (int)p.seg[(hb / p.H) * p.T + qi] : 0;
     };
-    float lse_f = 0.f, dl_f = 0.f;
+    float lse_f = 0.f;
     int st_f = 0;
-    if ((int)blockIdx.x < n_items) item_stat((int)blockIdx.x, lse_f, dl_f, st_f);
+    if ((int)blockIdx.x < n_items) item_stat((int)blockIdx.x, lse_f, st_f);
     int g = 0, j = 0;
     for (;; ++j) {
       const int item = snake_item(j, G, (int)blockIdx.x);
@@ -1322,12 +1298,42 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant_
       const int qi = qt * FA_T + r;
       const bool q_ok = qi < p.T;
       // this row's statistics were fetched while the previous item was being worked on
-      const float nlse = q_ok ? -lse_f : -INFINITY, dsc = -dl_f * p.scale;
+      const float nlse = q_ok ? -lse_f : -INFINITY;
       const int st = st_f;
       {
         const int nxt = snake_item(j + 1, G, (int)blockIdx.x);
-        if (nxt < n_items) item_stat(nxt, lse_f, dl_f, st_f);
+        if (nxt < n_items) item_stat(nxt, lse_f, st_f);
       }
+      // delta of this row from the item's dO and O tiles (128-byte rows, 16-byte pieces XOR-ed
+      // with the row's low three bits, as the tensor map wrote them)
+      ok = mbar_wait_warp<SM_SPIN>(B_(0), j & 1, abort_flag, p.err, 0x5c00u);
+      if (!ok) break;
+      float dl = 0.f;
+      {
+        const uint8_t* dor = gbase + DQ_DO + r * 128;
+        const uint8_t* orow = gbase + DQ_O + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t off = ((uint32_t)c ^ (uint32_t)(r & 7)) << 4;
+          const uint4 a = *reinterpret_cast<const uint4*>(dor + off);
+          const uint4 o = *reinterpret_cast<const uint4*>(orow + off);
+          const __half2* ah = reinterpret_cast<const __half2*>(&a);
+          const __half2* oh = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 x = __half22float2(ah[e]), y = __half22float2(oh[e]);
+            dl = fmaf(x.x, y.x, dl);
+            dl = fmaf(x.y, y.y, dl);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B_(1));             // this warp is done with the dO / O tiles
+      if (part == 0 && q_ok) {
+        const int hb = item % HB;
+        p.delta_out[(size_t)((hb / p.H) * p.H + hb % p.H) * p.T + qi] = dl;
+      }
+      const float dsc = -dl * p.scale;
       for (int kt = 0; kt < nj && ok; ++kt, ++g) {
         const bool need_mask = (kt == qt) || (p.seg != nullptr);
         ok = mbar_wait_warp<SM_SPIN>(B_(5), g & 1, abort_flag, p.err, 0x5600u);
@@ -1460,9 +1466,10 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
   VKG_REQUIRE(hd == FA_HD, "attn_bwd: head dimension must be %d (got %d)", FA_HD, hd);
   VKG_REQUIRE(((uintptr_t)dqkv16 & 15) == 0, "attn_bwd: dqkv must be 16-byte aligned");
   const int D = H * hd;
-  CUtensorMap tm, tmdo;
+  CUtensorMap tm, tmdo, tmo;
   if (make_map_2d(dev, &tm, qkv16, 3 * (int64_t)D, (int64_t)B * T, "qkv")) return 1;
   if (make_map_2d(dev, &tmdo, dout16, (int64_t)D, (int64_t)B * T, "dO")) return 1;
+  if (make_map_2d(dev, &tmo, out16, (int64_t)D, (int64_t)B * T, "O")) return 1;
   AttnParams p;
   memset(&p, 0, sizeof(p));
   p.B = B; p.T = T; p.H = H; p.D = D;
@@ -1472,6 +1479,7 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
   p.seg = seg;
   p.lse2 = const_cast<float*>(lse2);
   p.delta = delta;
+  p.delta_out = delta;
   p.dqkv = (__half*)dqkv16;
   p.err = dev->err_dev;
   VKG_REQUIRE(!dbias || dbias_scratch, "attn_bwd: dbias needs dbias_scratch");
@@ -1483,20 +1491,17 @@ extern "C" int vkg_attn_bwd(vkg_device* dev, const void* qkv16, const void* dout
                                   DQ_SMEM));
     dev->attn_bwd_attr_set = true;
   }
-  const long long items = (long long)B * T * H;
   VKG_REQUIRE((((uintptr_t)dout16 | (uintptr_t)out16) & 15) == 0, "attn_bwd: dO and O must be 16-byte aligned");
-  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_delta_kernel, dim3((unsigned)((items * 8 + 255) / 256)), dim3(256), 0, 1,
-                      (const __half*)dout16, (const __half*)out16, delta, B, T, H));
-  if (vkg_check_launch("attn_delta_kernel")) return 1;
   const long long n_items = (long long)p.nqt * H * B;
   VKG_REQUIRE(n_items < (1ll << 31), "attn_bwd: too many tiles");
-  // persistent kernels: one CTA per SM (their shared memory allows no more), items dealt round-robin
+  // persistent kernels: one CTA per SM (their shared memory allows no more), items dealt in
+  // snake order; the dQ kernel goes first because it also writes delta
   const int sms = vkg_persistent_ctas(dev);
   const unsigned ctas = (unsigned)(n_items < sms ? n_items : sms);
+  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_q_kernel, dim3(ctas), dim3(DQ_THREADS), DQ_SMEM, 1, tm, tmdo, tmo, p));
+  if (vkg_check_launch("attn_bwd_q_kernel")) return 1;
   VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_kv_kernel, dim3(ctas), dim3(BW_THREADS), KV_SMEM, 1, tm, tmdo, p));
   if (vkg_check_launch("attn_bwd_kv_kernel")) return 1;
-  VKG_CUDA(vkg_launch(dev, VKG_K_ATTN_BWD, attn_bwd_q_kernel, dim3(ctas), dim3(DQ_THREADS), DQ_SMEM, 1, tm, tmdo, p));
-  if (vkg_check_launch("attn_bwd_q_kernel")) return 1;
   if (dbias)
     return vkg_launch_col_sum_final(dev, dbias_scratch, dbias, 3 * D, B * p.nqt * 4, 0);
   return 0;
