@@ -317,8 +317,9 @@ int vkg_attn_fwd(vkg_device* dev, const void* qkv16, const uint32_t* seg,
                  void* out16, float* lse2, int B, int T, int H, int hd, float scale);
 /* Backward of vkg_attn_fwd: the reference's split_heads, four batched matmuls,
  * attn_softmax_bwd and merge_qkv_grad (transformer.py:160-186, tkernels.py:167-232)
- * as three launches: delta = rowsum(dO * O), a dK/dV kernel (one CTA per key tile)
- * and a dQ kernel (one CTA per query tile), both rebuilding P from lse2.
+ * as two persistent launches: a dQ kernel (items = query tiles), which also forms
+ * delta = rowsum(dO * O) and leaves it in `delta`, and a dK/dV kernel (items = key tiles),
+ * both rebuilding P from lse2.
  * dout16 is the (B*T, D) fp16 gradient of out16; dqkv16 (B*T, 3D) fp16 receives
  * [dQ | dK | dV]; delta is B*H*T floats of scratch.  Deterministic (no atomics).
  * dbias (optional, 3D floats) receives the column sums of dqkv16 as stored -- the gradient

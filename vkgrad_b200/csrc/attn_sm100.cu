@@ -5,7 +5,8 @@
 //
 // Forward, one CTA per (128-query tile, head, sequence), 320 threads, two CTAs per SM:
 //   warp 0      TMA producer: Q once, then the K and V tiles
-//   warp 1      TMEM allocation + single-thread tcgen05.mma issue
+//   warp 1      TMEM allocation + tcgen05.mma issue (the warp runs converged, one elected lane
+//               per instruction)
 //   warps 2..9  softmax: TMEM lane = query row; two warps share a lane quarter, each takes 64
 //               of a tile's 128 keys, so a thread owns half of one row
 // Two kernels.  attn_fwd1_kernel (the default) makes one pass: S = Q K^T once per key tile,
@@ -13,9 +14,13 @@
 // sum rescaled -- only when a tile exceeds it by more than 2^8.  attn_fwd_kernel makes two:
 //   pass 1  S = Q K^T  -> row maximum m only (no exponentials)
 //   pass 2  S again, P~ = exp2(S c - m), O~ += P~ V, no rescaling at all
-// (QK^T has K = 64, so doing it twice costs little: 45 vs 41 us per layer at 8 x 1024 x 12.)
-// In both, P~ is rounded to fp16 into swizzled shared memory, O~ accumulates in TMEM, the row
-// sum l of the UN-rounded P~ is kept in fp32, and O = O~ / l when the tile is stored.
+// (QK^T has K = 64, so doing it twice costs little: 45 vs 37 us per layer at 8 x 1024 x 12.)
+// In both, P~ is rounded to fp16 -- into tensor memory in the one-pass kernel, where P~ V reads
+// it as the A operand, into swizzled shared memory in the two-pass one --, O~ accumulates in
+// TMEM, the row sum l of the UN-rounded P~ is kept in fp32, and O = O~ / l when the tile is
+// stored.
+// Backward: two persistent kernels, the dQ kernel (which also forms delta = rowsum(dO * O))
+// and the dK / dV kernel; their comments are beside them.
 // Rounding points against the reference: it rounds the NORMALISED probability P = P~ / l to
 // fp16 before P V (tkernels.py:123); here the un-normalised P~ (in (0, 1], the row's largest
 // entry exactly 1) is rounded and 1 / l is applied to the fp32 accumulator, so O carries the
@@ -37,18 +42,15 @@ constexpr int FA_TILE_BYTES = FA_T * FA_HD * 2;  // 16 KB: one 128 x 64 fp16 til
 constexpr int FA_THREADS = 320;      // producer + MMA + eight softmax warps
 constexpr int FA_SOFTMAX_WARPS = 8;
 constexpr int BW_SOFTMAX_WARPS = 16;   // dK / dV kernel: four warps per TMEM lane quarter, 32 keys of a row each
-#ifndef VKG_ATTN_DQ_WARPS
-#define VKG_ATTN_DQ_WARPS 16
-#endif
-constexpr int DQ_SOFTMAX_WARPS = VKG_ATTN_DQ_WARPS;   // dQ kernel: 2 or 4 warps per lane quarter
+constexpr int DQ_SOFTMAX_WARPS = 16;   // dQ kernel: 8 or 16 (2 or 4 per lane quarter; 8 measured 2 % slower)
 constexpr int DQ_MMA2_WARP = 2 + DQ_SOFTMAX_WARPS;        // the warp that issues dQ += dS K
 constexpr int DQ_THREADS = (3 + DQ_SOFTMAX_WARPS) * 32;
 constexpr int BW_THREADS = (2 + BW_SOFTMAX_WARPS) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
-#ifndef VKG_ATTN_SOFTMAX_SPIN
-#define VKG_ATTN_SOFTMAX_SPIN 0
-#endif
-constexpr bool SM_SPIN = VKG_ATTN_SOFTMAX_SPIN != 0;
+// The softmax warps' waits suspend (mbarrier.try_wait with a time hint); the producer's and the
+// MMA warps', which sit on the critical chain, poll.  Polling in the softmax warps too measured
+// the same to 1 us per layer.
+constexpr bool SM_SPIN = false;
 
 struct AttnParams {
   int B, T, H, D;
@@ -623,46 +625,12 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
 // ---- backward --------------------------------------------------------------------------
 //
 // One 32-key chunk of a (query row, key tile) pair: rebuild P from S and the saved
-// log-sum-exp, form dS = P (dP - delta) scale, and write both (fp16) into the swizzled
-// [query row][key] layout.  `sp` may be null.  nlse = -lse2 (or -inf for a row past the
-// end of the sequence, which makes its P exactly 0), dsc = -delta * scale: each element
-// costs two FMAs, one exp2, one multiply and the conversions.  MASK adds the per-element
-// causal / packed-sample test and is only compiled into the tiles that need it.
-template <bool MASK>
-__device__ __forceinline__ void bwd_chunk(const uint32_t* rs, const uint32_t* rdp, int c, int r,
-                                          int key0, int qi, int st, float cscale, float scale,
-                                          float nlse, float dsc, uint8_t* sp, uint8_t* sds) {
-  const uint32_t row_off = (uint32_t)(r * 128), rx = (uint32_t)(r & 7);
-#pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    __half2 hp[4], hd[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float pv[2], dv[2];
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const int idx = u * 8 + 2 * e + w;
-        float pr = vkg_ex2(fmaf(__uint_as_float(rs[idx]), cscale, nlse));
-        if (MASK) {
-          const int key = key0 + c * 32 + idx;
-          if (key > qi || key < st) pr = 0.f;
-        }
-        pv[w] = pr;
-        dv[w] = pr * fmaf(__uint_as_float(rdp[idx]), scale, dsc);
-      }
-      hp[e] = __floats2half2_rn(pv[0], pv[1]);
-      hd[e] = __floats2half2_rn(dv[0], dv[1]);
-    }
-    const int cc = c * 4 + u;
-    const uint32_t off = (uint32_t)((cc >> 3) * FA_TILE_BYTES) + row_off + ((((uint32_t)cc & 7u) ^ rx) << 4);
-    if (sp) *reinterpret_cast<uint4*>(sp + off) = *reinterpret_cast<uint4*>(hp);
-    *reinterpret_cast<uint4*>(sds + off) = *reinterpret_cast<uint4*>(hd);
-  }
-}
-
-// The same chunk in two phases, for a consumer whose P / dS buffer is still being read: the
-// values are formed and packed into registers first (four 16-byte groups each), and written
-// with bwd_chunk_store once the buffer is free.
+// log-sum-exp and form dS = P (dP - delta) scale, both rounded to fp16 and packed into registers
+// (four 16-byte groups each); bwd_chunk_store writes them into the swizzled [query row][key]
+// layout once the buffer, which the tensor core may still be reading, is free.  nlse = -lse2
+// (or -inf for a row past the end of the sequence, which makes its P exactly 0), dsc = -delta *
+// scale: each element costs two FMAs, one exp2, one multiply and the conversions.  MASK adds the
+// per-element causal / packed-sample test and is only compiled into the tiles that need it.
 template <bool MASK>
 __device__ __forceinline__ void bwd_chunk_regs(const uint32_t* rs, const uint32_t* rdp, int c,
                                                int key0, int qi, int st, float cscale, float scale,
