@@ -458,6 +458,70 @@ def time_gemm_shapes(dev, table):
     return total_f, total_t, rows
 
 
+def library_gemm_rows(dev):
+    """Four of the step's GEMM shapes through vkg_gemm (the faster of the single-CTA and the
+    CTA-pair kernel, as a caller may choose) and through the library GEMM (torch.mm -> cuBLAS)
+    in the same process, with fp32 and with fp16 outputs: like for like, since an fp32 output
+    costs both the same 64 KB more per 128 x 256 tile.  For orientation only: torch is on no
+    path of the product, and the section says so if it cannot be imported."""
+    from vkgrad_b200._lib import F16, F32
+    from vkgrad_b200.kernels import gemm
+    try:
+        import torch
+        torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
+        torch.zeros(1, device="cuda")
+    except Exception as e:      # no torch, or torch without this GPU: report, do not fail the bench
+        return {"unavailable": repr(e)[:120]}
+
+    def lib_time(f):
+        for _ in range(3):
+            f()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                f()
+            e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1) / 10 * 1e3
+            best = t if best is None else min(best, t)
+        return best
+
+    rows = []
+    for m, n, k, tb in ((8192, 2304, 768, False), (8192, 3072, 768, False), (8192, 768, 768, False),
+                        (8192, 768, 3072, True)):
+        a, b, c = dev.buffer(m * k * 2, "device"), dev.buffer(k * n * 2, "device"), \
+            dev.buffer(m * n * 4, "device")
+        fill_random16(dev, a)
+        fill_random16(dev, b)
+        row = {"m": m, "n": n, "k": k, "tb": int(tb)}
+        for tag, cd in (("f32", F32), ("f16", F16)):
+            best = None
+            for pair in (-1, 1):
+                kw = dict(trans_b=tb, c_dtype=cd, cta_pair=pair)
+                gemm(dev, a, b, c, m, n, k, repeat=2, **kw)
+                t = min(gemm(dev, a, b, c, m, n, k, repeat=10, **kw) / 10 for _ in range(3)) * 1e6
+                best = t if best is None else min(best, t)
+            row["ours_%s_us" % tag] = best
+        for x in (a, b, c):
+            x.destroy()
+        ta_ = torch.randn(m, k, device="cuda", dtype=torch.float16)
+        tb_ = torch.randn((n, k) if tb else (k, n), device="cuda", dtype=torch.float16)
+        rhs = tb_.t() if tb else tb_
+        row["lib_f16_us"] = lib_time(lambda: torch.mm(ta_, rhs))
+        try:
+            row["lib_f32_us"] = lib_time(lambda: torch.mm(ta_, rhs, out_dtype=torch.float32))
+        except Exception as e:  # an older torch without out_dtype
+            row["lib_f32_us"] = None
+            row["lib_f32_note"] = repr(e)[:80]
+        del ta_, tb_, rhs
+        rows.append(row)
+    return {"rows": rows, "note": "us per launch, best of 3 rounds of 10, N(0,1) operands; ours = "
+            "min(gemm_tcgen05_kernel, gemm_cta_pair_kernel); lib = torch.mm (cuBLAS)"}
+
+
 TRIO_SHAPES = [(m, k, n) for m in (4096, 16384)
                for (k, n) in ((768, 768), (768, 3072), (3072, 768), (1024, 4096))]
 
@@ -901,6 +965,8 @@ def run_gpu_arm(args):
         line["c5_gpt_24l"] = c5_summary(dev)
         line["c5_gpt_24l"]["step_tensor_frac"] = (line["c5_gpt_24l"]["algorithmic_tflop_per_step"] /
                                                   (line["c5_gpt_24l"]["ms_per_step"] * 1e-3) / peak)
+    if line is not None and world == 1 and not args.no_extras:
+        line["library_gemm"] = library_gemm_rows(dev)
     dev.destroy()
     if line is not None:
         print(json.dumps(line), flush=True)
