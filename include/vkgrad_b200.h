@@ -84,10 +84,14 @@ int vkg_set_pdl(vkg_device* dev, int on);
  *                          cta_pair == 0 takes 256 x 256 CTA-pair tiles
  *   VKG_TUNE_ATTN_ONE_PASS 1 (default): the fused attention forward computes every score tile
  *                          once and keeps a lazily rescaled running row maximum; 0: two
- *                          passes over the keys (row maximum first) */
+ *                          passes over the keys (row maximum first)
+ *   VKG_TUNE_PAIR_192      1 (default): vkg_gemm with cta_pair == 0 and tile_n == 0 takes
+ *                          256 x 192 CTA-pair tiles for unbatched outputs one to four such
+ *                          tiles wide (N = 192 .. 768) with K >= 1536 and at least one wave
+ *                          of them; 0: never.  Same bits either way. */
 enum { VKG_TUNE_PDL = 0, VKG_TUNE_PDL_FAMILIES = 1, VKG_TUNE_TMA_STORE = 2,
        VKG_TUNE_WAIT_TIMEOUT_MS = 3, VKG_TUNE_SM_LIMIT = 4, VKG_TUNE_PAIR_MIN_WAVES = 5,
-       VKG_TUNE_ATTN_ONE_PASS = 6 };
+       VKG_TUNE_ATTN_ONE_PASS = 6, VKG_TUNE_PAIR_192 = 7 };
 int vkg_set_tuning(vkg_device* dev, int key, int64_t value);
 /* Waits for the stream; reports a kernel error flag (bounded waits that gave
  * up) as a failure, like the reference's 10 s fence timeout (vk.py:884-888, 1335-1339).
@@ -197,8 +201,9 @@ typedef struct vkg_gemm_args {
                                    before the tile's first row are skipped (P^T dO, dS^T Q). */
   int32_t cta_pair;          /* 256 x 256 tiles computed by two CTAs of a cluster with one
                                 tcgen05.mma.cta_group::2 (each CTA loads half of the B tile):
-                                0 = the library decides, 1 = always (when the shape allows it),
-                                -1 = never.  Not available with causal != 0. */
+                                0 = the library decides, 1 = always (when the shape allows it;
+                                tile_n = 192 then asks for 256 x 192 tiles), -1 = never.  Not
+                                available with causal != 0. */
   float* colsum;             /* optional, N floats: column sums of the output as stored (after
                                 the epilogue and the narrowing), the bias gradient of the layer
                                 that produced this GEMM's dY (replaces the col_sum pass of

@@ -265,6 +265,37 @@ def test_split_k(dev, m, n, k, ta, tb, split_k):
         x.destroy()
 
 
+@pytest.mark.parametrize("m,n,k,ta,tb", [
+    (512, 768, 320, False, True),        # dX = dY W^T: B stored N x K, 96 rows of it per CTA
+    (512, 768, 256, False, False),       # Y = X W: B stored K x N, one and a half 64-column groups per CTA
+    (768, 384, 1024, True, False),       # dW = X^T dY
+    (1000, 520, 200, False, True),       # ragged M, N, K: the last tile has 136 of 192 columns
+    (1000, 520, 200, False, False),
+    (4096, 768, 3072, False, True),      # more tiles than CTA pairs, long K
+])
+def test_cta_pair_tiles_192_wide(dev, m, n, k, ta, tb):
+    """256 x 192 tiles on CTA pairs (cta_pair = 1, tile_n = 192) against the oracle and, bit for
+    bit, against the single-CTA kernel."""
+    from vkgrad_b200.kernels import gemm
+    rng = np.random.default_rng(m * 5 + n)
+    a = rng.standard_normal((k, m) if ta else (m, k)).astype(np.float16)
+    b = rng.standard_normal((n, k) if tb else (k, n)).astype(np.float16)
+    ba, bb = up(dev, a), up(dev, b)
+    outs = []
+    for pair, tn in ((-1, 0), (1, 192)):
+        bc = dev.buffer(m * n * 4, "cached")
+        bc.array(np.float32)[:] = np.nan
+        bc.flush()
+        gemm(dev, ba, bb, bc, m, n, k, trans_a=ta, trans_b=tb, split_k=1, cta_pair=pair, tile_n=tn)
+        outs.append(down(dev, bc, np.float32, (m, n)))
+        bc.destroy()
+    ref = orc.matmul16(a, b, ta, tb)
+    assert relerr(outs[1], ref) < TOL
+    assert np.array_equal(outs[0], outs[1])
+    for x in (ba, bb):
+        x.destroy()
+
+
 @pytest.mark.parametrize("m,n,k,ta,tb,split_k", [
     (512, 512, 256, False, False, 1),      # Y = X W, B stored K x N
     (512, 768, 320, False, True, 1),       # dX = dY W^T, B stored N x K

@@ -14,7 +14,7 @@ F32, F16, BF16 = 0, 1, 2
 ACT_NONE, ACT_GELU, ACT_RELU = 0, 1, 2
 # keys of vkg_set_tuning (include/vkgrad_b200.h)
 TUNE_PDL, TUNE_PDL_FAMILIES, TUNE_TMA_STORE, TUNE_WAIT_TIMEOUT_MS, TUNE_SM_LIMIT = 0, 1, 2, 3, 4
-TUNE_PAIR_MIN_WAVES, TUNE_ATTN_ONE_PASS = 5, 6
+TUNE_PAIR_MIN_WAVES, TUNE_ATTN_ONE_PASS, TUNE_PAIR_192 = 5, 6, 7
 
 vp = C.c_void_p
 i32 = C.c_int

@@ -70,6 +70,7 @@ struct vkg_device {
   // fused attention forward: one pass with a lazily rescaled running maximum (default), or
   // the two-pass kernel (VKG_TUNE_ATTN_ONE_PASS)
   bool attn_one_pass = true;
+  bool pair192 = true;        // vkg_gemm may pick 256 x 192 CTA-pair tiles for N = 768-like outputs
   // vkg_gemm takes 256 x 256 CTA-pair tiles on its own (cta_pair == 0) from this many
   // tiles per CTA pair on, in tenths (VKG_TUNE_PAIR_MIN_WAVES)
   int pair_min_waves_x10 = 60;

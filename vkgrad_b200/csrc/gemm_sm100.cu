@@ -683,19 +683,25 @@ gemm_group_kernel(const GroupEntry* __restrict__ table, int n_problems, int tota
 // single-CTA kernel on the K = 768 shapes.  Barriers: TMA of both CTAs counts bytes on the
 // leader's full[s]; the leader's commits arrive on empty[s] / tmem_full[a] of both CTAs;
 // the epilogue warps of both CTAs arrive on the leader's tmem_empty[a].
-constexpr int PAIR_BN = 256;
-constexpr int PAIR_B_STAGE_BYTES = (PAIR_BN / 2) * 128;
-constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;
-constexpr int PAIR_STAGES = RING_BYTES / PAIR_STAGE_BYTES;   // 6
+constexpr int PAIR_BN = 256;        // widest pair tile; 192 is the other width (N = 768 shapes)
+// Bytes of one CTA's half of the B tile per k-block: bn / 2 rows of 128 bytes when B is K-major,
+// whole 64-column groups of 64 k-rows when it is MN-major (96 columns load two groups).
+__host__ __device__ inline int pair_b_stage_bytes(int bn, int b_mn) {
+  return b_mn ? ((bn / 2 + 63) / 64) * 8192 : (bn / 2) * 128;
+}
+__host__ __device__ inline int pair_stages(int bn, int b_mn) {
+  const int n = RING_BYTES / (A_STAGE_BYTES + pair_b_stage_bytes(bn, b_mn));
+  return n > MAX_STAGES ? MAX_STAGES : n;
+}
 
 // Barriers, TMEM and constants of one CTA of a pair; ends with a cluster-wide barrier so the
 // peer's mbarriers exist before anything is signalled on them.
-__device__ __forceinline__ void pair_setup(CtaCtx& cx, uint8_t* smem_raw) {
+__device__ __forceinline__ void pair_setup(CtaCtx& cx, uint8_t* smem_raw, int bn, int b_mn) {
   const int warp = threadIdx.x >> 5;
   cx.base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (cx.base - smem_u32(smem_raw));
-  cx.stage_bytes = PAIR_STAGE_BYTES;
-  cx.n_stages = PAIR_STAGES;
+  cx.stage_bytes = (uint32_t)(A_STAGE_BYTES + pair_b_stage_bytes(bn, b_mn));
+  cx.n_stages = pair_stages(bn, b_mn);
   cx.epi_stage = gen_base + RING_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES);
   const uint32_t bar_base = cx.base + RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
@@ -706,7 +712,7 @@ __device__ __forceinline__ void pair_setup(CtaCtx& cx, uint8_t* smem_raw) {
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 20);
   cx.abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 21);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PAIR_STAGES; ++s) {
+    for (int s = 0; s < cx.n_stages; ++s) {
       mbar_init(cx.full0 + 8 * s, 1);     // the leader's own arrive.expect_tx
       mbar_init(cx.empty0 + 8 * s, 1);
     }
@@ -763,12 +769,12 @@ __device__ __forceinline__ bool pair_produce_unit(const CtaCtx& cx, const GemmPa
   int kb0, nkb;
   kb_range(p, tc, kb0, nkb);
   if (p.split_k > 1) tc.z1 = 0;
-  const int nb = tc.n0 + (int)rank * (PAIR_BN / 2);    // this CTA's columns of B
+  const int nb = tc.n0 + (int)rank * (p.bn / 2);       // this CTA's columns of B
   for (int kb = 0; kb < nkb; ++kb) {
     if (!mbar_wait(cx.empty0 + 8 * stage, phase ^ 1u, cx.abort_flag, p.err, 0x500u + stage)) return false;
-    if (rank == 0) mbar_expect_tx(cx.full0 + 8 * stage, 2 * PAIR_STAGE_BYTES);
+    if (rank == 0) mbar_expect_tx(cx.full0 + 8 * stage, 2 * cx.stage_bytes);
     const uint32_t fb = mapa_shared(cx.full0 + 8 * stage, 0);
-    const uint32_t sa = cx.base + stage * PAIR_STAGE_BYTES;
+    const uint32_t sa = cx.base + stage * cx.stage_bytes;
     const uint32_t sb = sa + A_STAGE_BYTES;
     const int k0 = (kb0 + kb) * BK;
     if (!p.a_mn) {
@@ -780,10 +786,11 @@ __device__ __forceinline__ bool pair_produce_unit(const CtaCtx& cx, const GemmPa
     if (!p.b_mn) {
       tma_load_4d_pair(sb, tmB, fb, k0, nb, tc.z0, tc.z1);
     } else {
+      // whole 64-column groups: a 96-column half loads two and uses one and a half
       tma_load_4d_pair(sb, tmB, fb, nb, k0, tc.z0, tc.z1);
-      tma_load_4d_pair(sb + 8192, tmB, fb, nb + 64, k0, tc.z0, tc.z1);
+      if (p.bn > 128) tma_load_4d_pair(sb + 8192, tmB, fb, nb + 64, k0, tc.z0, tc.z1);
     }
-    if (++stage == PAIR_STAGES) {
+    if (++stage == cx.n_stages) {
       stage = 0;
       phase ^= 1u;
     }
@@ -807,15 +814,15 @@ __device__ __forceinline__ bool pair_mma_unit(const CtaCtx& cx, const GemmParams
   for (int kb = 0; kb < nkb; ++kb) {
     if (!mbar_wait_warp(cx.full0 + 8 * stage, phase, cx.abort_flag, p.err, 0x700u + stage)) return false;
     tcgen05_fence_after();
-    const uint32_t a_lo = a_lo0 + (uint32_t)stage * (PAIR_STAGE_BYTES >> 4);
-    const uint32_t b_lo = b_lo0 + (uint32_t)stage * (PAIR_STAGE_BYTES >> 4);
+    const uint32_t a_lo = a_lo0 + (uint32_t)stage * (cx.stage_bytes >> 4);
+    const uint32_t b_lo = b_lo0 + (uint32_t)stage * (cx.stage_bytes >> 4);
 #pragma unroll
     for (int k = 0; k < BK / UMMA_K; ++k)
       if (elect_one())
         umma2_f16(d_tmem, smem_desc_pack(a_lo + k * a_step, d_hi), smem_desc_pack(b_lo + k * b_step, d_hi),
                   p.idesc, (kb | k) != 0 ? 1u : 0u);
     if (elect_one()) umma2_commit(cx.empty0 + 8 * stage);
-    if (++stage == PAIR_STAGES) {
+    if (++stage == cx.n_stages) {
       stage = 0;
       phase ^= 1u;
     }
@@ -848,7 +855,7 @@ __device__ __forceinline__ bool pair_epilogue_unit(const CtaCtx& cx, const GemmP
   const int row_base = tc.m0 + q * 32;
   const uint32_t t_row = cx.tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_COLS);
   const bool tma_out = (MODE & E_NO_TMA) == 0 && p.tma_store != 0;
-  for (int c0 = 16 * ((warp - 2) >> 2); c0 < PAIR_BN; c0 += 64) {
+  for (int c0 = 16 * ((warp - 2) >> 2); c0 < p.bn; c0 += 64) {
     if (tc.n0 + c0 >= p.N) break;
     uint32_t r[16];
     tmem_ld16(t_row + c0, r);
@@ -907,7 +914,7 @@ gemm_cta_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     prefetch_tensormap(&tmB);
   }
   CtaCtx cx;
-  pair_setup(cx, smem_raw);
+  pair_setup(cx, smem_raw, p.bn, p.b_mn);
   pdl_wait();
   const int n_pairs = (int)gridDim.x >> 1, pair = (int)blockIdx.x >> 1;
   const int total_tiles = p.tiles_m * p.tiles_n * p.nb0 * (p.split_k > 1 ? p.split_k : p.nb1);
@@ -946,7 +953,7 @@ gemm_group_pair_kernel(const GroupEntry* __restrict__ table, int n_problems, int
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   CtaCtx cx;
-  pair_setup(cx, smem_raw);       // its __syncthreads also publishes first[]
+  pair_setup(cx, smem_raw, PAIR_BN, 1);   // dW problems: both operands MN-major; publishes first[]
   pdl_wait();
   const int n_pairs = (int)gridDim.x >> 1, pair = (int)blockIdx.x >> 1;
   if (warp == 0) {
@@ -1154,9 +1161,9 @@ struct Problem {
   long long total_tiles;
 };
 
-// use_pair: 256 x 256 tiles for gemm_cta_pair_kernel (the caller has checked the shape).
+// use_pair: 256 x pair_bn tiles for gemm_cta_pair_kernel (the caller has checked the shape).
 int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem* out,
-                  bool use_pair = false) {
+                  bool use_pair = false, int pair_bn = PAIR_BN) {
   VKG_REQUIRE(a, "null gemm args");
   VKG_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0, "gemm: M, N, K must be positive (%d, %d, %d)",
               a->M, a->N, a->K);
@@ -1183,7 +1190,7 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
   const int bm = use_pair ? 2 * BM : BM;
   plan_gemm(a->M, a->N, a->K, batch, use_pair ? vkg_persistent_ctas(dev) / 2 : vkg_persistent_ctas(dev),
             may_split && a->split_k != 1, a->workspace_bytes,
-            use_pair ? PAIR_BN : (force_bn ? force_bn : a->tile_n), a->split_k > 1 ? a->split_k : 0,
+            use_pair ? pair_bn : (force_bn ? force_bn : a->tile_n), a->split_k > 1 ? a->split_k : 0,
             &bn, &want_split, bm);
 
   GemmParams& p = out->p;
@@ -1254,7 +1261,7 @@ int build_problem(vkg_device* dev, const vkg_gemm_args* a, int force_bn, Problem
   if (a->trans_b) {
     VKG_REQUIRE(a->ldb >= a->K, "gemm: ldb %lld < K %d (B stored N x K)", (long long)a->ldb, a->K);
     if (make_map(dev, &tmB, a->B, a->in_dtype, a->K, a->N, a->ldb, nb0, a->sB0, nb1, a->sB1, BK,
-                 use_pair ? PAIR_BN / 2 : bn, "B^T"))
+                 use_pair ? pair_bn / 2 : bn, "B^T"))
       return 1;
   } else {
     VKG_REQUIRE(a->ldb >= a->N, "gemm: ldb %lld < N %d", (long long)a->ldb, a->N);
@@ -1436,6 +1443,17 @@ extern "C" int vkg_gemm_group_launch(vkg_device* dev, const void* table, int n, 
   return vkg_check_launch("gemm_group_kernel");
 }
 
+// 256 x 192 pair tiles: for outputs a few 192-column tiles wide (the N = 768 shapes of a
+// d_model-768 step) they fill the second wave better than 256-wide tiles and each CTA pulls
+// 28 KB per k-block (K-major B) where a single-CTA 128 x 192 tile pulls 40 KB.
+bool pair192_pays(vkg_device* dev, const vkg_gemm_args* a) {
+  if (!dev->pair192 || a->N % 192 != 0 || a->N > 4 * 192) return false;
+  const int nb = (a->nb0 > 0 ? a->nb0 : 1) * (a->nb1 > 0 ? a->nb1 : 1);
+  if (nb != 1 || a->split_k > 1 || a->K < 1536) return false;     // K = 768: no gain measured
+  const long long tiles = (long long)((a->M + 2 * BM - 1) / (2 * BM)) * (a->N / 192);
+  return tiles >= vkg_persistent_ctas(dev) / 2;      // at least one full wave of pair tiles
+}
+
 extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   if (vkg_bind(dev)) return 1;
   VKG_REQUIRE(a, "null gemm args");
@@ -1443,8 +1461,9 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
   // 256 x 256 tiles on CTA pairs: only where a pair has at least two full row blocks and a
   // full-width tile to work on, and never for the causal attention shortcuts
   const bool pair_ok = a->causal == 0 && a->M > BM && a->N >= PAIR_BN / 2 && dev->sm_count >= 2 &&
-                       (a->tile_n == 0 || a->tile_n == PAIR_BN) && a->max_ctas == 0;
+                       (a->tile_n == 0 || a->tile_n == PAIR_BN || a->tile_n == 192) && a->max_ctas == 0;
   bool use_pair = pair_ok && a->cta_pair > 0;
+  int pair_bn = a->tile_n == 192 ? 192 : PAIR_BN;
   if (pair_ok && a->cta_pair == 0) {
     // Measured on B200: CTA-pair tiles are about 10 % faster on launches with six or more waves of
     // them (the vocabulary-sized GEMMs) and on few-tile dW shapes whose K is split; with a
@@ -1453,9 +1472,13 @@ extern "C" int vkg_gemm(vkg_device* dev, const vkg_gemm_args* a) {
     if (build_problem(dev, a, 0, &q, true)) return 1;
     use_pair = q.p.split_k > 1 ||
                10ll * q.total_tiles >= (long long)dev->pair_min_waves_x10 * (vkg_persistent_ctas(dev) / 2);
+    if (!use_pair && a->tile_n == 0 && pair192_pays(dev, a)) {
+      use_pair = true;
+      pair_bn = 192;
+    }
   }
   if (use_pair) {
-    if (build_problem(dev, a, 0, &q, true)) return 1;
+    if (build_problem(dev, a, 0, &q, true, pair_bn)) return 1;
     if (ensure_attrs(dev)) return 1;
     GemmKernel fn = gemm_cta_pair_kernel<E_GENERIC>;
     for (int i = 0; i < kNumCtaPair; ++i)

@@ -113,6 +113,7 @@ extern "C" int vkg_set_tuning(vkg_device* dev, int key, int64_t value) {
       dev->pair_min_waves_x10 = (int)value;
       break;
     case VKG_TUNE_ATTN_ONE_PASS: dev->attn_one_pass = value != 0; break;
+    case VKG_TUNE_PAIR_192: dev->pair192 = value != 0; break;
     case VKG_TUNE_WAIT_TIMEOUT_MS:
       VKG_REQUIRE(value > 0, "set_tuning: the wait limit must be positive");
       dev->wait_timeout_s = (double)value * 1e-3;
