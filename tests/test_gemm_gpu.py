@@ -361,6 +361,55 @@ def test_cta_pair_fused_epilogues(dev):
         b.destroy()
 
 
+def test_cta_pair_192_wide_tiles_with_the_steps_epilogues(dev):
+    """256 x 192 CTA-pair tiles with the epilogues the training step runs on them: bias +
+    residual into the fp32 stream (fc2 forward, B stored K x N) and a plain fp32 dX through the
+    transposed weight (B stored N x K), plus an fp16 output, bit for bit against the
+    single-CTA kernel; and the library's own choice (cta_pair = 0, tile_n = 0) on a shape wide
+    and long enough for it to pick them."""
+    from vkgrad_b200._lib import F16
+    from vkgrad_b200.kernels import gemm
+    m, n, k = 1000, 768, 1600
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    w = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float16)
+    wt = np.ascontiguousarray(w.T)
+    bias = rng.standard_normal(n).astype(np.float32)
+    resid = rng.standard_normal((m, n)).astype(np.float32)
+    bx, bw, bwt, bb, br = up(dev, x), up(dev, w), up(dev, wt), up(dev, bias), up(dev, resid)
+    res = []
+    for pair, tn in ((-1, 0), (1, 192)):
+        y32 = dev.buffer(m * n * 4, "cached")
+        d32 = dev.buffer(m * n * 4, "cached")
+        y16 = dev.buffer(m * n * 2, "cached")
+        gemm(dev, bx, bw, y32, m, n, k, bias=bb, residual=br, cta_pair=pair, tile_n=tn)
+        gemm(dev, bx, bwt, d32, m, n, k, trans_b=True, cta_pair=pair, tile_n=tn)
+        gemm(dev, bx, bw, y16, m, n, k, c_dtype=F16, bias=bb, cta_pair=pair, tile_n=tn)
+        res.append((down(dev, y32, np.float32, (m, n)), down(dev, d32, np.float32, (m, n)),
+                    down(dev, y16, np.float16, (m, n))))
+        for b in (y32, d32, y16):
+            b.destroy()
+    for got, want in zip(res[1], res[0]):
+        assert np.array_equal(got, want)
+    ref = orc.matmul16(x, w)
+    assert relerr(res[1][0], ref + bias + resid) < TOL
+    assert relerr(res[1][1], ref) < TOL
+    # the library's own choice: 74 pair tiles of 256 x 192 need 4736 rows at N = 768
+    m2 = 4864
+    x2 = rng.standard_normal((m2, k)).astype(np.float16)
+    bx2 = up(dev, x2)
+    outs = []
+    for pair in (0, -1):
+        c = dev.buffer(m2 * n * 4, "cached")
+        gemm(dev, bx2, bwt, c, m2, n, k, trans_b=True, cta_pair=pair)
+        outs.append(down(dev, c, np.float32, (m2, n)))
+        c.destroy()
+    assert np.array_equal(outs[0], outs[1])
+    assert relerr(outs[0], orc.matmul16(x2, w)) < TOL
+    for b in (bx, bw, bwt, bb, br, bx2):
+        b.destroy()
+
+
 def test_cta_pair_batched_bf16(dev):
     """CTA-pair tiles over a batch of matrices with bf16 operands: the batch index walks the
     tensor maps exactly as in the single-CTA kernel."""
