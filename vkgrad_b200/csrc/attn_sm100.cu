@@ -45,7 +45,8 @@ constexpr int BW_SOFTMAX_WARPS = 16;   // dK / dV kernel: four warps per TMEM la
 constexpr int DQ_SOFTMAX_WARPS = 16;   // dQ kernel: 8 or 16 (2 or 4 per lane quarter; 8 measured 2 % slower)
 constexpr int DQ_MMA2_WARP = 2 + DQ_SOFTMAX_WARPS;        // the warp that issues dQ += dS K
 constexpr int DQ_THREADS = (3 + DQ_SOFTMAX_WARPS) * 32;
-constexpr int BW_THREADS = (2 + BW_SOFTMAX_WARPS) * 32;
+constexpr int KV_MMA2_WARP = 2 + BW_SOFTMAX_WARPS;        // the warp that issues dV / dK
+constexpr int BW_THREADS = (3 + BW_SOFTMAX_WARPS) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 // The softmax warps' waits suspend (mbarrier.try_wait with a time hint); the producer's and the
 // MMA warps', which sit on the critical chain, poll.  Polling in the softmax warps too measured
@@ -792,55 +793,54 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // the whole warp runs this converged; one elected lane issues each tcgen05 instruction
+    // S = Q K^T and dP = dO V^T of every step (dV / dK are issued by a warp of their own, as in
+    // the dQ kernel).  The whole warp runs this converged; one elected lane issues each tcgen05
+    // instruction.
     const uint32_t idesc_s = make_idesc(0, 0, 0, FA_T);    // [q x hd] . [key x hd]^T
-    const uint32_t idesc_g = make_idesc(0, 1, 1, FA_HD);   // [q x key]^T . [q x hd]
-    // descriptor halves (tcgen05.cuh): K-major operands of S / dP, MN-major ones of dV / dK
-    const uint32_t d_hi = smem_desc_hi(1024);
+    const uint32_t d_hi = smem_desc_hi(1024);              // descriptor halves (tcgen05.cuh)
     const uint32_t k_lo = smem_desc_lo(base + KV_K, 16), v_lo = smem_desc_lo(base + KV_V, 16);
     const uint32_t q_lo = smem_desc_lo(base + KV_Q, 16), do_lo = smem_desc_lo(base + KV_DO, 16);
+    int s = 0;
+    uint32_t ph = 0, par = 0;
+    bool ok = true;
+    for (int j = 0; ok; ++j) {
+      const int item = snake_item(j, G, (int)blockIdx.x);
+      if (item >= n_items) break;
+      const int ni = p.nqt - item / HB;
+      ok = mbar_wait_warp<true>(B_(0), j & 1, abort_flag, p.err, 0x4200u);
+      for (int it = 0; it < ni && ok; ++it) {
+        ok = mbar_wait_warp<true>(B_(KV_QD_FULL + s), ph, abort_flag, p.err, 0x4300u + s) &&
+             mbar_wait_warp<true>(B_(6), par ^ 1u, abort_flag, p.err, 0x4400u);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
+        umma_f16_chain<4>(tS, q_lo + so, 2, k_lo, 2, d_hi, idesc_s, 0u);
+        umma_f16_chain<4>(tdP, do_lo + so, 2, v_lo, 2, d_hi, idesc_s, 0u);
+        umma_commit_one(B_(5));
+        if (it == ni - 1) umma_commit_one(B_(12));    // the item's K / V may be replaced
+        par ^= 1u;
+        if (++s == KV_STAGES) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+  } else if (warp == KV_MMA2_WARP) {
+    // dV += P^T dO and dK += dS^T Q of every step.  Its commits cover this warp's instructions
+    // only; a Q / dO stage is free when dV / dK of its step have retired, because the S / dP
+    // that read it retired before the softmax warps could produce the P / dS these waited for.
+    const uint32_t idesc_g = make_idesc(0, 1, 1, FA_HD);   // [q x key]^T . [q x hd]
+    const uint32_t d_hi = smem_desc_hi(1024);
     const uint32_t qm_lo = smem_desc_lo(base + KV_Q, 8192), dom_lo = smem_desc_lo(base + KV_DO, 8192);
     const uint32_t pt_lo = smem_desc_lo(base + KV_P, FA_TILE_BYTES);
     const uint32_t dst_lo = smem_desc_lo(base + KV_DS, FA_TILE_BYTES);
-    // cursor of the S / dP issue: always one step ahead of the dV / dK loop below, also
-    // across an item boundary
-    int item_a = snake_item(0, G, (int)blockIdx.x), it_a = 0, j_a = 0, g_a = 0;
-    int ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
-    auto issue_sdp = [&]() -> bool {   // S = Q K^T and dP = dO V^T of step g_a
-      if (item_a >= n_items) return true;
-      if (it_a == 0 && !mbar_wait_warp<true>(B_(0), j_a & 1, abort_flag, p.err, 0x4200u)) return false;
-      const int s = g_a % KV_STAGES;
-      if (!(mbar_wait_warp<true>(B_(KV_QD_FULL + s), (uint32_t)(g_a / KV_STAGES) & 1u, abort_flag, p.err,
-                            0x4300u + s) &&
-            mbar_wait_warp<true>(B_(6), (g_a & 1) ^ 1u, abort_flag, p.err, 0x4400u)))
-        return false;
-      tcgen05_fence_after();
-      const uint32_t so = (uint32_t)s * (FA_TILE_BYTES >> 4);
-      umma_f16_chain<4>(tS, q_lo + so, 2, k_lo, 2, d_hi, idesc_s, 0u);
-      umma_f16_chain<4>(tdP, do_lo + so, 2, v_lo, 2, d_hi, idesc_s, 0u);
-      umma_commit_one(B_(5));
-      if (it_a == ni_a - 1) umma_commit_one(B_(12));    // the item's K / V may be replaced
-      ++g_a;
-      if (++it_a == ni_a) {
-        item_a = snake_item(++j_a, G, (int)blockIdx.x);
-        it_a = 0;
-        ni_a = item_a < n_items ? p.nqt - item_a / HB : 0;
-      }
-      return true;
-    };
-    bool ok = issue_sdp();
-    int g = 0, j = 0;
-    for (;; ++j) {
+    int g = 0, s = 0;
+    bool ok = true;
+    for (int j = 0; ok; ++j) {
       const int item = snake_item(j, G, (int)blockIdx.x);
-      if (item >= n_items || !ok) break;
+      if (item >= n_items) break;
       const int ni = p.nqt - item / HB;
       for (int it = 0; it < ni; ++it, ++g) {
-        // the next step's S / dP go first (also when that means waiting for a new item's
-        // operands: issuing dV / dK first measured slower), so the tensor core is busy while
-        // the softmax warps turn S, dP into P, dS
-        ok = issue_sdp();
-        if (!ok) break;
-        const int s = g % KV_STAGES;         // Q / dO stage of this step
         ok = mbar_wait_warp<true>(B_(7), g & 1, abort_flag, p.err, 0x4500u);     // P / dS written
         if (!ok) break;
         if (it == 0 && j > 0) {              // the previous item's dV / dK have been read out
@@ -856,6 +856,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant
         umma_commit_one(B_(KV_QD_EMPTY + s));   // Q / dO stage free
         umma_commit_one(B_(8));                 // P / dS may be overwritten
         if (it == ni - 1) umma_commit_one(B_(9));
+        if (++s == KV_STAGES) s = 0;
       }
     }
   } else {
