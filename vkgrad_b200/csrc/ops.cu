@@ -1501,6 +1501,9 @@ extern "C" int vkg_layernorm_bwd(vkg_device* dev, const float* dy, const float* 
     // register-resident rows; every CTA writes its partial sums (possibly zero)
     int nb = (rows + LNV_WARPS - 1) / LNV_WARPS;
     if (nb > nblocks) nb = nblocks;
+    // from D = 640 on a CTA's registers (three row streams and three sets of column sums per
+    // lane) leave room for one CTA per SM only: a second CTA per SM would run as a second wave
+    if (D >= 640 && nb > dev->sm_count) nb = dev->sm_count;
     float* sc = fused ? scratch : nullptr;
     switch (D / 128) {
       case 1: launch_ln_bwd_vec<1>(dev, nb, dy, x, gamma, mu, rstd, dres, dx, dx16, sc, rows, nparts); break;
