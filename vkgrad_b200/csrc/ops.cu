@@ -10,10 +10,6 @@ namespace {
 
 constexpr int TPB = 256;
 
-__device__ __forceinline__ void store16(void* p, int64_t i, float v) {
-  reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
-}
-
 // ---- flat elementwise -------------------------------------------------------
 
 __global__ void k_bias_act(const float* __restrict__ acc, const float* __restrict__ bias,

@@ -55,7 +55,7 @@ extern "C" int vkg_device_create(int ordinal, vkg_device** out) {
   d->cc_minor = prop.minor;
   d->total_bytes = prop.totalGlobalMem;
   d->gemm_smem_optin = prop.sharedMemPerBlockOptin;
-  snprintf(d->name, sizeof(d->name), "%s", prop.name);
+  snprintf(d->name, sizeof(d->name), "%.127s", prop.name);
   VKG_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
   VKG_CUDA(cudaEventCreate(&d->ev0));
   VKG_CUDA(cudaEventCreate(&d->ev1));
